@@ -1,0 +1,304 @@
+#!/usr/bin/env python
+"""Benchmark of the block-quantised GEMV path on B200 (prints ONE JSON line on rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload q8_0_gemv] [--impl reference]
+
+Workload ``q8_0_gemv`` (default) is the decode GEMV of the first benchmark configuration: W 4096 x 4096
+(seed 0, N(0, 0.02), packed to Q8_0), x fp32[4096] (seed 1), batch 1.  One such matrix is 17.8 MB and
+would sit in the 126 MB L2, so a step sweeps COPIES distinct weight copies (same values, different
+addresses, 570 MB in all): every launch streams its weights from HBM.  A step is one pass over all
+copies with one launch per copy, replayed from a CUDA graph.
+
+  value      whole-job GB/s, algorithmic bytes (34 B per 32-weight block + x + y) / device time, inputs
+             resident in HBM, CUDA events on the launching stream, max over ranks.
+  e2e        the same metric through the host-pointer C-ABI call a ZenInfer build would make
+             (zen_cuda_gemv_q8_0): x travels host->device and y device->host inside the timed region.
+  roofline   achieved = algorithmic bytes per launch / mean launch time inside the timed region;
+             peak = MEASURED_PEAKS.json hbm_gbs (a device copy measured on this pool).
+  cpu_baseline  the reference's own CPU kernels (oracle/_ref, built from the reference sources) on
+             the same workload, bounded sample, on this box's host cores.
+
+With --gpus N (under torchrun) every rank owns one 4096-row shard of a (4096*N) x 4096 matrix per copy
+(weak scaling); each launch is followed by the path's one exchange step, an NCCL all-gather of the
+output shards.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, COLS = 4096, 4096
+COPIES = 32
+BLOCK_BYTES, BLOCK_ELEMS = 34, 32
+ALGO_BYTES_PER_LAUNCH = ROWS * (COLS // BLOCK_ELEMS) * BLOCK_BYTES + COLS * 4 + ROWS * 4  # 17,858,560
+WORKLOAD = "Q8_0 decode GEMV batch 1, W 4096x4096 (config 0), %d rotating weight copies" % COPIES
+
+
+def peaks() -> tuple[float, str]:
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs():
+    from zeninfer_b200 import blocks
+    w = np.random.default_rng(0).standard_normal((ROWS, COLS), dtype=np.float32) * np.float32(0.02)
+    packed = np.ascontiguousarray(blocks.quantize_q8_0(w))
+    x = np.random.default_rng(1).standard_normal(COLS, dtype=np.float32)
+    return packed, x
+
+
+def cpu_reference_leg(packed: np.ndarray, x: np.ndarray, budget_s: float, copies: int) -> dict:
+    """Times the reference's own CPU path (zen::quant::gemv through oracle/_ref) on the workload."""
+    os.environ.setdefault("ZEN_CPU_Q8_ACT", "1")  # same arithmetic as the GPU arm: int8 activations
+    import oracle
+    kind = "reference" if oracle.reference_available() else "port"
+    ws = [packed.copy() for _ in range(copies)]  # distinct addresses: the CPU caches do not hold 17.8 MB x copies
+    if kind == "reference":
+        zr = oracle.Reference()
+        cores = min(zr.pool_workers(), os.cpu_count() or 1)
+        run = lambda w: zr.gemv(oracle.Q8_0, w, x, ROWS, COLS, workers=0)  # workers=0: the reference's own policy
+    else:
+        zo = oracle.Oracle()
+        cores = 1
+        run = lambda w: zo.gemv(oracle.Q8_0, w, x, ROWS, COLS, int8_acts=True)
+    run(ws[0])
+    t0 = time.perf_counter()
+    n = 0
+    while True:
+        run(ws[n % copies])
+        n += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return {"value": ALGO_BYTES_PER_LAUNCH * n / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+            "sample": f"{n} GEMV calls over {copies} weight copies in {dt:.1f} s, int8 activations (ZEN_CPU_Q8_ACT=1), reference worker policy"}
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    packed, x = make_inputs()
+    copies = 8
+    per_step_budget = max(0.5, min(20.0, 60.0 / max(1, args.steps + args.warmup)))
+    leg = None
+    for _ in range(args.warmup):
+        leg = cpu_reference_leg(packed, x, per_step_budget, copies)
+    vals, t0 = [], time.perf_counter()
+    for _ in range(args.steps):
+        leg = cpu_reference_leg(packed, x, per_step_budget, copies)
+        vals.append(leg["value"])
+    value = statistics.mean(vals)
+    leg["value"] = value
+    print(json.dumps({
+        "impl": "reference", "metric": "q8_0_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": (time.perf_counter() - t0) * 1e3 / max(1, args.steps),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "inputs larger than the CPU caches (8 weight copies)"},
+        "cpu_baseline": leg, "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default="q8_0_gemv")
+    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU time for the cpu_baseline leg")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup) if args.impl != "reference" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from zeninfer_b200 import Backend
+    from zeninfer_b200.backend import ACT_INT8
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    be = Backend()  # raises if the CUDA library or a B200 is missing: there is no fallback
+    packed, x_host = make_inputs()
+
+    # --- resident inputs: COPIES weight shards on this rank, x and y in HBM ---
+    handles = [be.dev_upload("Q8_0", packed, ROWS, COLS) for _ in range(COPIES)]
+    d_x = torch.from_numpy(x_host).to(dev)
+    d_y = torch.zeros(ROWS, dtype=torch.float32, device=dev)
+    d_all = torch.zeros(ROWS * world, dtype=torch.float32, device=dev) if world > 1 else None
+    stream = torch.cuda.Stream(device=dev)
+
+    def one_pass():
+        for h in handles:
+            be.dev_gemv([h], [d_y.data_ptr()], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream)
+            if world > 1:
+                dist.all_gather_into_tensor(d_all, d_y)
+
+    with torch.cuda.stream(stream):
+        one_pass()  # first launch sets function attributes; keep it out of the capture
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            one_pass()
+        for _ in range(args.warmup):
+            graph.replay()
+        stream.synchronize()
+        be.dev_check(stream.cuda_stream)
+
+        # --- timed region: K graph replays, CUDA events on the launching stream ---
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local) as clocks:
+            e0.record(stream)
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = e0.elapsed_time(e1)
+    be.dev_check(stream.cuda_stream)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    launches = args.steps * COPIES
+    total_bytes = ALGO_BYTES_PER_LAUNCH * launches * world
+    value = total_bytes / (ms * 1e-3) / 1e9
+    per_launch_us = ms * 1e3 / launches
+    achieved = ALGO_BYTES_PER_LAUNCH / (per_launch_us * 1e-6) / 1e9
+    peak, peak_kind = peaks()
+
+    # --- correctness of what was timed (not part of the timed region) ---
+    y_dev = d_y.cpu().numpy()
+
+    # --- e2e: the host-pointer call, host buffers, copies inside the timed region ---
+    e2e_copies = [packed.copy() for _ in range(COPIES)]  # distinct host addresses => distinct resident tensors
+    y_host = None
+    for w in e2e_copies:
+        y_host = be.gemv("Q8_0", w, x_host, ROWS, COLS)  # upload + warm
+    for _ in range(2):
+        for w in e2e_copies:
+            be.gemv("Q8_0", w, x_host, ROWS, COLS)
+    e2e_steps = max(3, min(args.steps, 20))
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        for w in e2e_copies:
+            be.gemv("Q8_0", w, x_host, ROWS, COLS)
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = ALGO_BYTES_PER_LAUNCH * COPIES * e2e_steps * world / e2e_s / 1e9
+    assert np.array_equal(y_host, y_dev), "host-pointer and device-pointer paths disagree"
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_reference_leg(packed, x_host, args.cpu_budget, 8)
+
+    line = {
+        "metric": "q8_0_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "rows_per_gpu": ROWS, "columns": COLS, "batch": 1, "activations": "int8 (bit-exact reference codes)",
+                   "l2": f"inputs larger than L2: {COPIES} weight copies, {COPIES * ALGO_BYTES_PER_LAUNCH / 1e6:.0f} MB per pass",
+                   "launch": "CUDA graph replay, one kernel per copy" + ("; NCCL all-gather of output shards after each" if world > 1 else "")},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                     "traffic": None, "launch_us": per_launch_us, "algorithmic_bytes_per_launch": ALGO_BYTES_PER_LAUNCH},
+        "cpu_baseline": cpu,
+        "clocks": clocks.summary(),
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": COLS * 4 * COPIES, "d2h_bytes_per_step": ROWS * 4 * COPIES,
+                "api": "zen_cuda_gemv_q8_0 (host pointers, weights resident by address)", "steps": e2e_steps},
+        "gpu_launches": launches,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

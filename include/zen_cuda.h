@@ -1,0 +1,170 @@
+/*
+ * zen_cuda.h -- C-ABI of the B200 (sm_100a) backend for ZenInfer's block-quantised
+ * GEMV/GEMM path.  Plain pointers and sizes only; no CUDA or C++ types, so the
+ * reference's host code (or any FFI) can bind it without seeing a vendor header,
+ * which is the same rule the reference's own GPU backends follow
+ * (include/zen/hip_backend.h:8-13).
+ *
+ * Two groups of entry points:
+ *
+ *  1. HOST-POINTER calls.  These are the drop-in surface: one per function the
+ *     reference's dispatch (src/quant.cpp) calls on a GPU backend.  `weights` is a
+ *     host pointer to raw GGUF blocks (the loader's file mapping); the backend keeps
+ *     a device copy keyed by (pointer, rows, columns, format) until it is released.
+ *     `x` / `y` are caller-owned host fp32 buffers; a call returns after `y` is
+ *     written.  Return 1 on success, 0 on failure.  There is no CPU fallback: 0 is
+ *     an error, and zen_cuda_last_error() says why.
+ *
+ *  2. DEVICE-POINTER calls ("zen_cuda_dev_*").  Stream-ordered, no host
+ *     synchronisation, activations stay in HBM between projections.  They replace
+ *     the reference's per-call compute-pool hand-off (src/compute_pool.cpp:93-120)
+ *     on this path, and are what its fused D3D12 submissions
+ *     (include/zen/d3d12_backend.h:289-352) answer on that backend.
+ *
+ * Thread safety: any thread may call; calls are serialised on one backend mutex,
+ * like the reference (src/backends/hip/hip_backend.hip:943).
+ */
+#ifndef ZEN_CUDA_H
+#define ZEN_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+/* GGML tensor type ids of the three formats on the path (GGUF tensor directory). */
+enum { ZEN_CUDA_Q4_0 = 2, ZEN_CUDA_Q8_0 = 8, ZEN_CUDA_Q6_K = 14 };
+
+/* How activations enter the integer dot products.
+ *   ZEN_CUDA_ACT_INT8 : one int8 code per element, bit-identical to the reference's
+ *                       quantise_acts_q8_0 (kernels/avx2.cpp:502-524); results match the
+ *                       reference's ZEN_CPU_Q8_ACT=1 arithmetic.  Q8_0 only.
+ *   ZEN_CUDA_ACT_FP32 : two int8 digits per element (error < scale/512); results match
+ *                       the reference's fp32-activation kernels within 1e-3.  The only
+ *                       mode for Q4_0 and Q6_K, whose reference kernels take fp32. */
+enum { ZEN_CUDA_ACT_INT8 = 1, ZEN_CUDA_ACT_FP32 = 2 };
+
+/* zen::hip::AdapterInfo, include/zen/hip_backend.h:16-23 */
+typedef struct zen_cuda_adapter_info {
+    char name[128];
+    uint64_t dedicated_vram;
+    uint64_t shared_memory;
+    int sm_count;
+    int warp_size;
+    char arch[64]; /* "sm_100" */
+} zen_cuda_adapter_info;
+
+/* zen::hip::Stats, include/zen/hip_backend.h:25-41 */
+typedef struct zen_cuda_stats {
+    uint64_t dispatches;   /* kernels launched */
+    uint64_t submits;      /* host-pointer calls completed */
+    uint64_t batches;
+    uint64_t upload_bytes; /* raw GGUF bytes uploaded */
+    uint64_t weight_bytes; /* device bytes held by resident weights */
+    uint64_t upload_us;
+    uint64_t alloc_us;
+    uint64_t stage_us;
+    uint64_t repack_us;
+    uint64_t transfer_us;
+    uint64_t wait_us;
+    uint64_t launch_us;
+    uint64_t readback_us;
+    uint64_t gpu_us;
+    uint64_t fallbacks;    /* calls that returned 0 */
+} zen_cuda_stats;
+
+/* One matvec target of a batched submission; all tasks share the input.
+ * zen::hip::GemvTask, include/zen/hip_backend.h:64-69 */
+typedef struct zen_cuda_gemv_task {
+    const uint8_t* weights;
+    float* y;
+    size_t rows;
+    size_t columns;
+} zen_cuda_gemv_task;
+
+/* zen::d3d12::GemmTask, include/zen/d3d12_backend.h:118-122 */
+typedef struct zen_cuda_gemm_task {
+    const uint8_t* weights;
+    float* y;
+    size_t rows;
+} zen_cuda_gemm_task;
+
+#define ZEN_CUDA_MAX_BATCH 8 /* zen::hip::kMaxBatch, include/zen/hip_backend.h:70 */
+
+/* ---- lifecycle: zen::hip::enabled/init/shutdown/info/stats, include/zen/hip_backend.h:46-50 */
+int zen_cuda_enabled(void);  /* 1 when a usable device exists and ZEN_BACKEND does not name another backend */
+int zen_cuda_init(void);     /* lazy, cached, thread-safe; a failure is latched until shutdown */
+void zen_cuda_shutdown(void);
+int zen_cuda_info(zen_cuda_adapter_info* out);
+void zen_cuda_get_stats(zen_cuda_stats* out);
+const char* zen_cuda_last_error(void); /* message of the most recent failed call on any thread */
+
+/* ---- host-pointer calls ------------------------------------------------------------------- */
+
+/* Process-wide activation mode for the Q8_0 host-pointer calls (default ZEN_CUDA_ACT_INT8;
+ * also settable with ZEN_CUDA_Q8_ACT=int8|fp32 before init).  Mirrors the reference's
+ * ZEN_CPU_Q8_ACT switch (src/quant.cpp:1088-1092). */
+int zen_cuda_set_q8_act_mode(int mode);
+int zen_cuda_get_q8_act_mode(void);
+
+/* zen::hip::gemv_q8_0, include/zen/hip_backend.h:59-60 */
+int zen_cuda_gemv_q8_0(const uint8_t* weights, const float* x, float* y, size_t rows, size_t columns);
+/* zen::hip::gemm_q8_0, include/zen/hip_backend.h:61-62.  output is token-major [tokens][rows]. */
+int zen_cuda_gemm_q8_0(const uint8_t* weights, const float* input, float* output, size_t tokens, size_t rows, size_t columns);
+/* zen::hip::gemv_q8_0_batch, include/zen/hip_backend.h:72 */
+int zen_cuda_gemv_q8_0_batch(const float* x, const zen_cuda_gemv_task* tasks, size_t count);
+/* zen::d3d12::gemm_q8_0_batch, include/zen/d3d12_backend.h:169 */
+int zen_cuda_gemm_q8_0_batch(const float* x, const zen_cuda_gemm_task* tasks, size_t count, size_t tokens, size_t columns);
+/* zen::d3d12::gemm_q6_k, include/zen/d3d12_backend.h:96-97 (tokens == 1 is the GEMV) */
+int zen_cuda_gemm_q6_k(const uint8_t* weights, const float* input, float* output, size_t tokens, size_t rows, size_t columns);
+/* Q4_0 has no GPU entry point in the reference (its CPU generic route, src/quant.cpp:1135-1162,
+ * is the only implementation); same contract as gemm_q6_k. */
+int zen_cuda_gemm_q4_0(const uint8_t* weights, const float* input, float* output, size_t tokens, size_t rows, size_t columns);
+
+/* zen::d3d12::release_q8_0_weights / release_kquant_weights, include/zen/d3d12_backend.h:80,88.
+ * Call before unmapping or reusing a weight address; drops every resident shape at that address. */
+void zen_cuda_release_weights(const uint8_t* weights);
+
+/* The activation quantiser on its own (the reference's quantise_acts_q8_0, kernels/avx2.cpp:502-524;
+ * shaders/quantize_acts.hlsl).  Host buffers: x [tokens][columns], codes [tokens][columns],
+ * scales [tokens][columns/32]. */
+int zen_cuda_quantize_acts(const float* x, int8_t* codes, float* scales, size_t tokens, size_t columns);
+
+/* ---- device-pointer, stream-ordered calls -------------------------------------------------- */
+
+typedef struct zen_cuda_weights zen_cuda_weights; /* opaque resident tensor */
+
+/* Upload rows [first_row, first_row + nrows) of a raw GGUF tensor of `rows_total` x `columns`
+ * (row sharding for multi-GPU reads only this byte range of the mapping).  The handle stays
+ * valid until zen_cuda_dev_free or shutdown.  Not keyed by pointer. */
+zen_cuda_weights* zen_cuda_dev_upload(int format, const uint8_t* weights, size_t rows_total, size_t columns,
+                                      size_t first_row, size_t nrows);
+void zen_cuda_dev_free(zen_cuda_weights* w);
+size_t zen_cuda_dev_weight_bytes(const zen_cuda_weights* w); /* device bytes held */
+
+/* y[i] = W[i] * x for up to ZEN_CUDA_MAX_BATCH tensors of the same format and column count
+ * sharing x.  d_x: device fp32 [tokens][columns] (tokens <= 8); d_y[i]: device fp32
+ * [tokens][rows_i].  Enqueued on `stream` (a cudaStream_t, or NULL for the backend's own
+ * stream); returns without synchronising.  act_mode is ZEN_CUDA_ACT_*. */
+int zen_cuda_dev_gemv(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
+                      size_t tokens, int act_mode, void* stream);
+
+/* Device quantiser: d_x [tokens][columns] fp32 -> d_codes int8, d_scales fp32 [tokens][columns/32]. */
+int zen_cuda_dev_quantize_acts(const float* d_x, int8_t* d_codes, float* d_scales, size_t tokens, size_t columns, void* stream);
+
+/* Reads and clears the device-side error word the kernels set when a bounded wait gives up
+ * (0 = none).  Synchronises `stream`. */
+int zen_cuda_dev_check(void* stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZEN_CUDA_H */

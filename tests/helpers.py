@@ -1,0 +1,52 @@
+"""Shared test helpers: seeded inputs, vectorised float64 references, the parity gate."""
+from __future__ import annotations
+
+import numpy as np
+
+from zeninfer_b200 import blocks
+
+
+def seeded_weights(fmt: int, rows: int, cols: int, seed: int) -> np.ndarray:
+    """N(0, 0.02) fp32 weights packed to `fmt`; uint8 [rows, row_bytes]."""
+    w = np.random.default_rng(seed).standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02)
+    return np.ascontiguousarray(blocks.quantize(fmt, w))
+
+
+def seeded_acts(tokens: int, cols: int, seed: int) -> np.ndarray:
+    return np.random.default_rng(seed).standard_normal((tokens, cols), dtype=np.float32)
+
+
+def ref_int8_f64(packed_q8_0: np.ndarray, xq: np.ndarray, xsc: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    """Float64 restatement of the int8-activation product (tools/d3d12_gemm_parity.cpp:130-147 shape):
+    y[t, r] = sum_b d_w[r, b] * d_x[t, b] * sum_k q_w[r, b, k] * q_x[t, b, k].  xq: [T, K] int8, xsc: [T, K/32]."""
+    nb = cols // 32
+    b = packed_q8_0.reshape(rows, nb, 34)
+    dw = b[..., :2].copy().view(np.float16).astype(np.float64)[..., 0]            # [rows, nb]
+    qw = b[..., 2:].view(np.int8).astype(np.int32)                                 # [rows, nb, 32]
+    qx = xq.reshape(-1, nb, 32).astype(np.int32)                                   # [T, nb, 32]
+    out = np.empty((qx.shape[0], rows), np.float64)
+    for t in range(qx.shape[0]):
+        isum = np.einsum("rbk,bk->rb", qw, qx[t]).astype(np.float64)
+        out[t] = (isum * dw * xsc[t].astype(np.float64)[None, :]).sum(axis=1)
+    return out
+
+
+def ref_fp32_f64(fmt: int, packed: np.ndarray, x: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    """Float64 dequantise-then-dot, the gate every reference sweep uses (tests/core_tests.cpp:360-367)."""
+    w = blocks.dequantize(fmt, packed, rows, cols).astype(np.float64)
+    return np.asarray(x, np.float64).reshape(-1, cols) @ w.T
+
+
+def assert_parity(got, ref, tol: float = 1e-3, what: str = "") -> float:
+    """The parity gate: max|got-ref| / max|ref| <= tol  (tools/hip_parity.cpp:126-134) AND, per element,
+    |got-ref| <= tol * max(1, |ref|)  (tests/core_tests.cpp:367).  Returns the first figure."""
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    assert np.all(np.isfinite(got)), f"{what}: non-finite output"
+    max_ref = np.abs(ref).max()
+    err = np.abs(got - ref)
+    rel = float(err.max() / max_ref) if max_ref > 0 else float(err.max())
+    assert rel <= tol, f"{what}: max_abs/max_ref = {rel:.3e} > {tol}"
+    assert np.all(err <= tol * np.maximum(1.0, np.abs(ref))), f"{what}: per-element gate failed, worst {err.max():.3e}"
+    return rel

@@ -1,0 +1,230 @@
+"""ctypes binding of include/zen_cuda.h, shaped like the reference's dispatch layer.
+
+``Backend.gemv / gemm / gemv_batch / gemm_batch`` take the same arguments, in the same order and with
+the same meaning, as ``zen::quant::gemv / gemm / gemv_batch / gemm_batch`` (include/zen/quant.h:28-91):
+a format name, host pointers to raw GGUF blocks, fp32 activations, token-major fp32 outputs.  Where
+the reference returns ``false`` and lets the caller try its next route, this raises ``BackendError``:
+the CUDA build has no other route.
+
+NumPy arrays stand in for the reference's raw pointers.  A weight array must stay alive (and keep its
+address) while it is resident, exactly as the reference requires of the loader's file mapping
+(include/zen/hip_backend.h:52-58); call ``release_weights`` before dropping it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Sequence
+
+import numpy as np
+
+from . import blocks
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_PKG, "lib", "libzen_cuda.so")
+
+ACT_INT8, ACT_FP32 = 1, 2
+FORMAT_IDS = {"Q8_0": blocks.Q8_0, "Q4_0": blocks.Q4_0, "Q6_K": blocks.Q6_K}
+
+# every symbol include/zen_cuda.h declares; the CPU test-suite checks the library exports them all
+ABI_SYMBOLS = (
+    "zen_cuda_enabled", "zen_cuda_init", "zen_cuda_shutdown", "zen_cuda_info", "zen_cuda_get_stats",
+    "zen_cuda_last_error", "zen_cuda_set_q8_act_mode", "zen_cuda_get_q8_act_mode",
+    "zen_cuda_gemv_q8_0", "zen_cuda_gemm_q8_0", "zen_cuda_gemv_q8_0_batch", "zen_cuda_gemm_q8_0_batch",
+    "zen_cuda_gemm_q6_k", "zen_cuda_gemm_q4_0", "zen_cuda_release_weights", "zen_cuda_quantize_acts",
+    "zen_cuda_dev_upload", "zen_cuda_dev_free", "zen_cuda_dev_weight_bytes", "zen_cuda_dev_gemv",
+    "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check",
+)
+
+
+class BackendError(RuntimeError):
+    pass
+
+
+class AdapterInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 128), ("dedicated_vram", C.c_uint64), ("shared_memory", C.c_uint64),
+                ("sm_count", C.c_int), ("warp_size", C.c_int), ("arch", C.c_char * 64)]
+
+
+class Stats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in (
+        "dispatches", "submits", "batches", "upload_bytes", "weight_bytes", "upload_us", "alloc_us", "stage_us",
+        "repack_us", "transfer_us", "wait_us", "launch_us", "readback_us", "gpu_us", "fallbacks")]
+
+    def as_dict(self) -> dict:
+        return {n: int(getattr(self, n)) for n, _ in self._fields_}
+
+
+class GemvTask(C.Structure):
+    _fields_ = [("weights", C.c_void_p), ("y", C.c_void_p), ("rows", C.c_size_t), ("columns", C.c_size_t)]
+
+
+class GemmTask(C.Structure):
+    _fields_ = [("weights", C.c_void_p), ("y", C.c_void_p), ("rows", C.c_size_t)]
+
+
+def load_library(path: str | None = None) -> C.CDLL:
+    """dlopen the backend.  Raises BackendError when it has not been built: there is no fallback."""
+    path = path or _LIB_PATH
+    if not os.path.exists(path):
+        raise BackendError(f"{path} is missing: build it with `python -m zeninfer_b200.build` (needs nvcc)")
+    lib = C.CDLL(path)
+    vp, sz, i = C.c_void_p, C.c_size_t, C.c_int
+    lib.zen_cuda_enabled.restype = i
+    lib.zen_cuda_init.restype = i
+    lib.zen_cuda_shutdown.restype = None
+    lib.zen_cuda_info.argtypes = [C.POINTER(AdapterInfo)]
+    lib.zen_cuda_get_stats.argtypes = [C.POINTER(Stats)]
+    lib.zen_cuda_get_stats.restype = None
+    lib.zen_cuda_last_error.restype = C.c_char_p
+    lib.zen_cuda_set_q8_act_mode.argtypes = [i]
+    lib.zen_cuda_gemv_q8_0.argtypes = [vp, vp, vp, sz, sz]
+    lib.zen_cuda_gemm_q8_0.argtypes = [vp, vp, vp, sz, sz, sz]
+    lib.zen_cuda_gemv_q8_0_batch.argtypes = [vp, C.POINTER(GemvTask), sz]
+    lib.zen_cuda_gemm_q8_0_batch.argtypes = [vp, C.POINTER(GemmTask), sz, sz, sz]
+    lib.zen_cuda_gemm_q6_k.argtypes = [vp, vp, vp, sz, sz, sz]
+    lib.zen_cuda_gemm_q4_0.argtypes = [vp, vp, vp, sz, sz, sz]
+    lib.zen_cuda_release_weights.argtypes = [vp]
+    lib.zen_cuda_release_weights.restype = None
+    lib.zen_cuda_quantize_acts.argtypes = [vp, vp, vp, sz, sz]
+    lib.zen_cuda_dev_upload.argtypes = [i, vp, sz, sz, sz, sz]
+    lib.zen_cuda_dev_upload.restype = vp
+    lib.zen_cuda_dev_free.argtypes = [vp]
+    lib.zen_cuda_dev_free.restype = None
+    lib.zen_cuda_dev_weight_bytes.argtypes = [vp]
+    lib.zen_cuda_dev_weight_bytes.restype = sz
+    lib.zen_cuda_dev_gemv.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, i, vp]
+    lib.zen_cuda_dev_quantize_acts.argtypes = [vp, vp, vp, sz, sz, vp]
+    lib.zen_cuda_dev_check.argtypes = [vp]
+    return lib
+
+
+def _addr(a: np.ndarray) -> int:
+    return a.ctypes.data
+
+
+class Backend:
+    """One process, one GPU (the device is LOCAL_RANK when launched under torchrun)."""
+
+    def __init__(self, lib_path: str | None = None) -> None:
+        self.lib = load_library(lib_path)
+        if not self.lib.zen_cuda_init():
+            raise BackendError("zen_cuda_init failed: " + self.last_error())
+
+    # ---- lifecycle (zen::hip::enabled/info/stats/shutdown) ----
+    def enabled(self) -> bool:
+        return bool(self.lib.zen_cuda_enabled())
+
+    def last_error(self) -> str:
+        return (self.lib.zen_cuda_last_error() or b"").decode()
+
+    def info(self) -> dict:
+        a = AdapterInfo()
+        if not self.lib.zen_cuda_info(C.byref(a)):
+            raise BackendError("backend not initialised")
+        return {"name": a.name.decode(), "dedicated_vram": int(a.dedicated_vram), "shared_memory": int(a.shared_memory),
+                "sm_count": a.sm_count, "warp_size": a.warp_size, "arch": a.arch.decode()}
+
+    def stats(self) -> dict:
+        s = Stats()
+        self.lib.zen_cuda_get_stats(C.byref(s))
+        return s.as_dict()
+
+    def shutdown(self) -> None:
+        self.lib.zen_cuda_shutdown()
+
+    def set_q8_act_mode(self, mode: int) -> None:
+        if not self.lib.zen_cuda_set_q8_act_mode(mode):
+            raise BackendError("bad activation mode")
+
+    def _fail(self, what: str):
+        raise BackendError(f"{what}: {self.last_error()}")
+
+    @staticmethod
+    def _weights(w) -> np.ndarray:
+        if not (isinstance(w, np.ndarray) and w.dtype == np.uint8 and w.flags["C_CONTIGUOUS"]):
+            raise TypeError("weights must be a C-contiguous uint8 ndarray that outlives its residency")
+        return w
+
+    # ---- zen::quant::gemv / gemm / gemv_batch / gemm_batch ----
+    def gemv(self, fmt: str, weights: np.ndarray, x, rows: int, columns: int) -> np.ndarray:
+        return self.gemm(fmt, weights, np.asarray(x, np.float32).reshape(1, columns), 1, rows, columns)[0]
+
+    def gemm(self, fmt: str, weights: np.ndarray, x, tokens: int, rows: int, columns: int) -> np.ndarray:
+        w = self._weights(weights)
+        x = np.ascontiguousarray(x, np.float32).reshape(tokens, columns)
+        out = np.empty((tokens, rows), np.float32)
+        if fmt == "Q8_0":
+            ok = (self.lib.zen_cuda_gemv_q8_0(_addr(w), _addr(x), _addr(out), rows, columns) if tokens == 1
+                  else self.lib.zen_cuda_gemm_q8_0(_addr(w), _addr(x), _addr(out), tokens, rows, columns))
+        elif fmt == "Q6_K":
+            ok = self.lib.zen_cuda_gemm_q6_k(_addr(w), _addr(x), _addr(out), tokens, rows, columns)
+        elif fmt == "Q4_0":
+            ok = self.lib.zen_cuda_gemm_q4_0(_addr(w), _addr(x), _addr(out), tokens, rows, columns)
+        else:
+            raise BackendError(f"format {fmt} is not on this path")
+        if not ok:
+            self._fail(f"{fmt} product {tokens}x{rows}x{columns}")
+        return out
+
+    def gemv_batch(self, fmt: str, weights: Sequence[np.ndarray], x, rows: Sequence[int], columns: int) -> list[np.ndarray]:
+        return [o[0] for o in self.gemm_batch(fmt, weights, np.asarray(x, np.float32).reshape(1, columns), rows, 1, columns)]
+
+    def gemm_batch(self, fmt: str, weights: Sequence[np.ndarray], x, rows: Sequence[int], tokens: int, columns: int) -> list[np.ndarray]:
+        if fmt != "Q8_0":  # the reference batches Q8_0 only and loops otherwise (src/quant.cpp:1499-1501)
+            return [self.gemm(fmt, w, x, tokens, r, columns) for w, r in zip(weights, rows)]
+        x = np.ascontiguousarray(x, np.float32).reshape(tokens, columns)
+        outs = [np.empty((tokens, r), np.float32) for r in rows]
+        n = len(outs)
+        if tokens == 1:
+            tasks = (GemvTask * n)(*[GemvTask(_addr(self._weights(w)), _addr(o), r, columns) for w, o, r in zip(weights, outs, rows)])
+            ok = self.lib.zen_cuda_gemv_q8_0_batch(_addr(x), tasks, n)
+        else:
+            tasks = (GemmTask * n)(*[GemmTask(_addr(self._weights(w)), _addr(o), r) for w, o, r in zip(weights, outs, rows)])
+            ok = self.lib.zen_cuda_gemm_q8_0_batch(_addr(x), tasks, n, tokens, columns)
+        if not ok:
+            self._fail("Q8_0 batched product")
+        return outs
+
+    def release_weights(self, weights: np.ndarray) -> None:
+        self.lib.zen_cuda_release_weights(_addr(weights))
+
+    def quantize_acts(self, x) -> tuple[np.ndarray, np.ndarray]:
+        """fp32 [tokens, K] -> (int8 codes [tokens, K], fp32 scales [tokens, K/32]); quantise_acts_q8_0 on the device."""
+        x = np.ascontiguousarray(x, np.float32)
+        tokens, k = x.reshape(-1, x.shape[-1]).shape
+        q = np.empty((tokens, k), np.int8)
+        sc = np.empty((tokens, k // 32), np.float32)
+        if not self.lib.zen_cuda_quantize_acts(_addr(x), _addr(q), _addr(sc), tokens, k):
+            self._fail("quantize_acts")
+        return q.reshape(x.shape), sc.reshape(x.shape[:-1] + (k // 32,))
+
+    # ---- device-pointer calls (addresses are plain ints, e.g. torch.Tensor.data_ptr()) ----
+    def dev_upload(self, fmt: str, weights: np.ndarray, rows_total: int, columns: int, first_row: int = 0, nrows: int | None = None) -> int:
+        nrows = rows_total - first_row if nrows is None else nrows
+        h = self.lib.zen_cuda_dev_upload(FORMAT_IDS[fmt], _addr(self._weights(weights)), rows_total, columns, first_row, nrows)
+        if not h:
+            self._fail(f"upload {fmt} {nrows}x{columns}")
+        return h
+
+    def dev_free(self, handle: int) -> None:
+        self.lib.zen_cuda_dev_free(handle)
+
+    def dev_weight_bytes(self, handle: int) -> int:
+        return int(self.lib.zen_cuda_dev_weight_bytes(handle))
+
+    def dev_gemv(self, handles: Sequence[int], d_y: Sequence[int], d_x: int, tokens: int, act_mode: int, stream: int = 0) -> None:
+        n = len(handles)
+        hs = (C.c_void_p * n)(*handles)
+        ys = (C.c_void_p * n)(*d_y)
+        if not self.lib.zen_cuda_dev_gemv(hs, ys, n, d_x, tokens, act_mode, stream):
+            self._fail("dev_gemv")
+
+    def dev_quantize_acts(self, d_x: int, d_codes: int, d_scales: int, tokens: int, columns: int, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_quantize_acts(d_x, d_codes, d_scales, tokens, columns, stream):
+            self._fail("dev_quantize_acts")
+
+    def dev_check(self, stream: int = 0) -> None:
+        code = self.lib.zen_cuda_dev_check(stream)
+        if code:
+            raise BackendError(f"a device-side wait timed out (code {code})")

@@ -1,0 +1,67 @@
+// Activation quantiser: fp32 -> int8 codes + one fp32 scale per 32 elements.
+//
+// Replaces the reference's quantise_acts_q8_0 (kernels/avx2.cpp:502-524, inlined
+// again at src/quant.cpp:1094-1113; the D3D12 twin is shaders/quantize_acts.hlsl).
+// Codes and scales are bit-identical to it:
+//     d   = amax / 127          (IEEE division, fp32)
+//     inv = 1 / d               (IEEE division; 0 when d == 0)
+//     q   = lround(clamp(x * inv, -127, 127))     round half AWAY from zero
+// so every operation below is an explicitly rounded intrinsic: no fast-math
+// reciprocal, no fused multiply-add, no round-half-even conversion.
+//
+// A second, finer digit is available for the formats the reference evaluates
+// with fp32 activations (Q4_0, Q6_K, and Q8_0 in its default mode): the residual
+// x - d*q is quantised again with scale d/256, so x ~= (d/256) * (256*q + q2)
+// with an error below d/512.  That keeps integer dot products within ~1e-5 of
+// the fp32-activation result.
+#pragma once
+#include "zk_ptx.cuh"
+
+namespace zk {
+
+// Exact for |v| <= 2^23: truncation and the remainder are both representable.
+__device__ __forceinline__ int round_half_away(float v) {
+    const float t = truncf(v);
+    const float f = __fsub_rn(v, t);
+    int q = __float2int_rz(t);
+    if (f >= 0.5f) ++q;
+    else if (f <= -0.5f) --q;
+    return q;
+}
+
+__device__ __forceinline__ float clamp127(float v) { return v > 127.0f ? 127.0f : (v < -127.0f ? -127.0f : v); }
+
+// One warp quantises one 32-element block, one element per lane.  All 32 lanes
+// must call.  Returns the block scale d; q1 is the Q8 code, q2 the fine digit.
+__device__ __forceinline__ float quantise_block_lane(float x, int& q1, int& q2) {
+    float amax = fabsf(x);
+    amax = amax > 0.0f ? amax : 0.0f;  // a NaN element never raises amax (same as the reference's compare)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, amax, o);
+        amax = other > amax ? other : amax;
+    }
+    const float d = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+    const float inv = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    q1 = round_half_away(clamp127(__fmul_rn(x, inv)));
+    const float r = __fmaf_rn(-static_cast<float>(q1), d, x);  // residual, one rounding
+    q2 = round_half_away(clamp127(__fmul_rn(r, __fmul_rn(inv, 256.0f))));
+    return d;
+}
+
+// Standalone kernel: x [tokens][K] fp32 -> q [tokens][K] int8, sc [tokens][K/32] fp32,
+// optionally q2 [tokens][K] int8 (the fine digit).  One warp per block.
+__global__ void __launch_bounds__(256) quantize_acts_kernel(const float* __restrict__ x, int8_t* __restrict__ q,
+                                                            float* __restrict__ sc, int8_t* __restrict__ q2,
+                                                            size_t total_blocks) {
+    const size_t warp = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= total_blocks) return;
+    int c1, c2;
+    const float d = quantise_block_lane(x[warp * 32 + lane], c1, c2);
+    q[warp * 32 + lane] = static_cast<int8_t>(c1);
+    if (q2) q2[warp * 32 + lane] = static_cast<int8_t>(c2);
+    if (lane == 0) sc[warp] = d;
+}
+
+}  // namespace zk

@@ -1,0 +1,70 @@
+// Upload-time re-layout of raw GGUF blocks into aligned planes.
+//
+// A GGUF tensor arrives as rows of interleaved blocks (Q8_0: 34 B, Q4_0: 18 B,
+// Q6_K: 210 B).  None of those sizes is a multiple of 16, so neither 128-bit
+// loads nor TMA copies can address the codes directly.  Like the reference's
+// GPU backends (src/backends/hip/hip_backend.hip:321-333 splits Q8_0 into
+// "quants | scales"), the device copy is split into planes, each row of each
+// plane starting on a 16-byte boundary.  Byte counts are unchanged (padding
+// aside), and the split is a pure byte move: no value is re-quantised.
+//
+//   Q8_0: codes  [rows][K]      int8      scales [rows][nbp] f16   (nbp = blocks rounded up to 8)
+//   Q4_0: nibs   [rows][K/2]    uint8     scales [rows][nbp] f16
+//   Q6_K: ql     [rows][K/2]    uint8     qh [rows][K/4] uint8
+//         sc     [rows][K/16]   int8      d  [rows][sbp] f16       (sbp = super-blocks rounded up to 8)
+#pragma once
+#include <cstdint>
+#include <cuda_fp16.h>
+
+namespace zk {
+
+__device__ __forceinline__ uint16_t ld_u16_unaligned(const uint8_t* p) { return static_cast<uint16_t>(p[0] | (p[1] << 8)); }
+
+// One thread per 32-element block.  raw: [rows][nb*34].
+__global__ void repack_q8_0_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ codes, uint16_t* __restrict__ scales,
+                                   size_t rows, uint32_t nb, uint32_t nbp) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= rows * nb) return;
+    const size_t r = i / nb;
+    const uint32_t b = static_cast<uint32_t>(i % nb);
+    const uint8_t* p = raw + i * 34;  // 2-byte aligned
+    scales[r * nbp + b] = *reinterpret_cast<const uint16_t*>(p);
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(p + 2);
+    uint16_t* dst = reinterpret_cast<uint16_t*>(codes + (r * nb + b) * 32);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) dst[k] = src[k];
+}
+
+// One thread per 32-element block.  raw: [rows][nb*18].
+__global__ void repack_q4_0_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ nibs, uint16_t* __restrict__ scales,
+                                   size_t rows, uint32_t nb, uint32_t nbp) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= rows * nb) return;
+    const size_t r = i / nb;
+    const uint32_t b = static_cast<uint32_t>(i % nb);
+    const uint8_t* p = raw + i * 18;
+    scales[r * nbp + b] = *reinterpret_cast<const uint16_t*>(p);
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(p + 2);
+    uint16_t* dst = reinterpret_cast<uint16_t*>(nibs + (r * nb + b) * 16);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) dst[k] = src[k];
+}
+
+// One thread per 256-element super-block.  raw: [rows][nsb*210].
+__global__ void repack_q6_k_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ ql, uint8_t* __restrict__ qh,
+                                   int8_t* __restrict__ sc, uint16_t* __restrict__ d, size_t rows, uint32_t nsb, uint32_t sbp) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= rows * nsb) return;
+    const size_t r = i / nsb;
+    const uint32_t b = static_cast<uint32_t>(i % nsb);
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(raw + i * 210);  // 210 is even
+    uint16_t* o_ql = reinterpret_cast<uint16_t*>(ql + (r * nsb + b) * 128);
+    uint16_t* o_qh = reinterpret_cast<uint16_t*>(qh + (r * nsb + b) * 64);
+    uint16_t* o_sc = reinterpret_cast<uint16_t*>(sc + (r * nsb + b) * 16);
+    for (int k = 0; k < 64; ++k) o_ql[k] = p[k];
+    for (int k = 0; k < 32; ++k) o_qh[k] = p[64 + k];
+    for (int k = 0; k < 8; ++k) o_sc[k] = p[96 + k];
+    d[r * sbp + b] = p[104];
+}
+
+}  // namespace zk

@@ -1,0 +1,605 @@
+// C-ABI of the backend (see include/zen_cuda.h): state, weight residency, uploads and
+// kernel launches.  Host logic only; the kernels live in the .cuh files beside it.
+//
+// The host-pointer calls keep the contract of the reference's GPU backends
+// (src/backends/hip/hip_backend.hip:937-1017): lazy latched init, one mutex, weights
+// resident by host pointer + shape, synchronous completion.  What differs is deliberate:
+// uploads stream through pinned bounce buffers and are re-laid-out on the device, not on
+// the host; activations and results cross PCIe through pinned staging; and a declined
+// call is an error, because this build has no CPU path to fall back to.
+#include "../../include/zen_cuda.h"
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "gemv_q8_0.cuh"
+#include "quantize_acts.cuh"
+#include "repack.cuh"
+
+struct zen_cuda_weights {
+    int format{};
+    size_t rows{}, cols{};
+    uint32_t nb{}, nbp{};     // blocks per row, padded to 8
+    void* plane[4]{};         // format-specific planes (see repack.cuh)
+    size_t device_bytes{};
+    size_t raw_bytes{};
+};
+
+namespace {
+
+using clock_type = std::chrono::steady_clock;
+uint64_t us_since(clock_type::time_point t0) {
+    return static_cast<uint64_t>(std::chrono::duration_cast<std::chrono::microseconds>(clock_type::now() - t0).count());
+}
+
+constexpr size_t kBounceBytes = size_t(32) << 20;  // each of the two pinned upload buffers
+
+struct ResidentKey {
+    const uint8_t* ptr; size_t rows, cols; int format;
+    bool operator==(const ResidentKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && format == o.format; }
+};
+struct ResidentKeyHash {
+    size_t operator()(const ResidentKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        h ^= std::hash<size_t>()(k.rows * 1000003u + k.cols) + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+        return h ^ static_cast<size_t>(k.format);
+    }
+};
+
+struct State {
+    std::mutex mutex;
+    bool ready{}, failed{};
+    int device{};
+    int sm_count{};
+    size_t smem_optin{};
+    cudaStream_t stream{}, copy_stream{};
+    cudaEvent_t bounce_free[2]{};
+    uint8_t* bounce[2]{};
+    zen_cuda_adapter_info adapter{};
+    zen_cuda_stats stats{};
+    std::string last_error;
+    int q8_act_mode{ZEN_CUDA_ACT_INT8};
+    std::unordered_map<ResidentKey, zen_cuda_weights*, ResidentKeyHash> resident;
+    // pinned host staging + device scratch for the host-pointer calls (grow-only)
+    float* h_stage{}; size_t h_stage_bytes{};
+    float* d_x{}; size_t d_x_bytes{};
+    float* d_y{}; size_t d_y_bytes{};
+    int* h_error{};   // mapped pinned word the kernels write on a bounded-wait timeout
+    int* d_error{};   // device alias of h_error
+};
+
+State& state() { static State s; return s; }
+
+bool set_error(State& s, const std::string& msg) {
+    s.last_error = msg;
+    ++s.stats.fallbacks;
+    return false;
+}
+#define ZC_CUDA(s, call)                                                                                  \
+    do {                                                                                                  \
+        const cudaError_t e_ = (call);                                                                    \
+        if (e_ != cudaSuccess) return set_error((s), std::string(#call) + ": " + cudaGetErrorString(e_)); \
+    } while (0)
+
+bool opted_out() {
+    static const bool out = [] {
+        if (const char* b = std::getenv("ZEN_BACKEND")) {
+            std::string n(b);
+            for (char& c : n) c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
+            if (!n.empty() && n != "cuda" && n != "gpu" && n != "b200") return true;
+        }
+        const char* f = std::getenv("ZEN_CUDA");
+        return f && f[0] == '0';
+    }();
+    return out;
+}
+
+bool init_locked(State& s) {
+    if (s.ready) return true;
+    if (s.failed) return false;
+    auto fail = [&s](const std::string& why) { s.failed = true; s.last_error = why; return false; };
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n < 1) return fail("no CUDA device");
+    int dev = 0;
+    if (const char* lr = std::getenv("LOCAL_RANK")) dev = std::atoi(lr) % n;   // one process per GPU
+    if (const char* d = std::getenv("ZEN_CUDA_DEVICE")) dev = std::atoi(d) % n;
+    if (cudaSetDevice(dev) != cudaSuccess) return fail("cudaSetDevice failed");
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return fail("cudaGetDeviceProperties failed");
+    if (prop.major != 10) return fail(std::string("device is sm_") + std::to_string(prop.major * 10 + prop.minor) + ", this build is sm_100a only");
+    s.device = dev;
+    s.sm_count = prop.multiProcessorCount;
+    s.smem_optin = prop.sharedMemPerBlockOptin;
+    std::snprintf(s.adapter.name, sizeof(s.adapter.name), "%.127s", prop.name);
+    s.adapter.dedicated_vram = prop.totalGlobalMem;
+    s.adapter.shared_memory = prop.sharedMemPerBlockOptin;
+    s.adapter.sm_count = prop.multiProcessorCount;
+    s.adapter.warp_size = prop.warpSize;
+    std::snprintf(s.adapter.arch, sizeof(s.adapter.arch), "sm_%d", prop.major * 10 + prop.minor);
+    if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess) return fail("stream create failed");
+    if (cudaStreamCreateWithFlags(&s.copy_stream, cudaStreamNonBlocking) != cudaSuccess) return fail("stream create failed");
+    for (int i = 0; i < 2; ++i) {
+        if (cudaEventCreateWithFlags(&s.bounce_free[i], cudaEventDisableTiming) != cudaSuccess) return fail("event create failed");
+        if (cudaHostAlloc(reinterpret_cast<void**>(&s.bounce[i]), kBounceBytes, cudaHostAllocDefault) != cudaSuccess) return fail("pinned alloc failed");
+    }
+    if (cudaHostAlloc(reinterpret_cast<void**>(&s.h_error), sizeof(int), cudaHostAllocMapped) != cudaSuccess) return fail("pinned alloc failed");
+    *s.h_error = 0;
+    if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.d_error), s.h_error, 0) != cudaSuccess) return fail("mapped pointer failed");
+    if (const char* m = std::getenv("ZEN_CUDA_Q8_ACT")) {
+        if (!std::strcmp(m, "fp32") || !std::strcmp(m, "2")) s.q8_act_mode = ZEN_CUDA_ACT_FP32;
+        else if (!std::strcmp(m, "int8") || !std::strcmp(m, "1")) s.q8_act_mode = ZEN_CUDA_ACT_INT8;
+    }
+    s.ready = true;
+    return true;
+}
+
+void free_weights(State& s, zen_cuda_weights* w) {
+    if (!w) return;
+    for (void* p : w->plane) if (p) cudaFree(p);
+    s.stats.weight_bytes -= std::min<uint64_t>(s.stats.weight_bytes, w->device_bytes);
+    delete w;
+}
+
+uint32_t block_elems(int fmt) { return fmt == ZEN_CUDA_Q6_K ? 256u : 32u; }
+uint32_t block_bytes(int fmt) { return fmt == ZEN_CUDA_Q8_0 ? 34u : fmt == ZEN_CUDA_Q4_0 ? 18u : fmt == ZEN_CUDA_Q6_K ? 210u : 0u; }
+
+// Streams [src, src+bytes) to `dst` on the copy stream through the two pinned bounce buffers:
+// the CPU fills one while the DMA engine drains the other.
+bool stream_to_device(State& s, void* dst, const uint8_t* src, size_t bytes) {
+    size_t off = 0;
+    int which = 0;
+    while (off < bytes) {
+        const size_t n = std::min(kBounceBytes, bytes - off);
+        ZC_CUDA(s, cudaEventSynchronize(s.bounce_free[which]));
+        const auto t0 = clock_type::now();
+        std::memcpy(s.bounce[which], src + off, n);
+        s.stats.stage_us += us_since(t0);
+        ZC_CUDA(s, cudaMemcpyAsync(static_cast<uint8_t*>(dst) + off, s.bounce[which], n, cudaMemcpyHostToDevice, s.copy_stream));
+        ZC_CUDA(s, cudaEventRecord(s.bounce_free[which], s.copy_stream));
+        off += n;
+        which ^= 1;
+    }
+    return true;
+}
+
+// Uploads rows [first_row, first_row+nrows) and re-lays them out into planes on the device.
+zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t rows_total, size_t cols, size_t first_row, size_t nrows) {
+    const uint32_t be = block_elems(fmt), bb = block_bytes(fmt);
+    if (!bb || !host || !nrows || !cols || cols % be || first_row + nrows > rows_total) {
+        set_error(s, "upload: bad shape or format");
+        return nullptr;
+    }
+    if (fmt != ZEN_CUDA_Q8_0) { set_error(s, "upload: format not built yet"); return nullptr; }
+    const auto t_all = clock_type::now();
+    auto* w = new zen_cuda_weights;
+    w->format = fmt; w->rows = nrows; w->cols = cols;
+    w->nb = static_cast<uint32_t>(cols / be);
+    w->nbp = (w->nb + 7u) & ~7u;
+    const size_t row_raw = static_cast<size_t>(w->nb) * bb;
+    w->raw_bytes = nrows * row_raw;
+    uint8_t* d_raw = nullptr;
+    auto t0 = clock_type::now();
+    bool ok = cudaMalloc(reinterpret_cast<void**>(&d_raw), w->raw_bytes + 16) == cudaSuccess;
+    size_t plane_bytes[4] = {0, 0, 0, 0};
+    plane_bytes[0] = nrows * cols + 64;                                // int8 codes (+ slack for rounded-up bulk copies)
+    plane_bytes[1] = nrows * static_cast<size_t>(w->nbp) * 2 + 64;     // f16 scales
+    for (int i = 0; ok && i < 4; ++i)
+        if (plane_bytes[i]) {
+            ok = cudaMalloc(&w->plane[i], plane_bytes[i]) == cudaSuccess;
+            if (ok) { ok = cudaMemsetAsync(w->plane[i], 0, plane_bytes[i], s.copy_stream) == cudaSuccess; w->device_bytes += plane_bytes[i]; }
+        }
+    s.stats.alloc_us += us_since(t0);
+    if (!ok) {
+        set_error(s, std::string("upload: device allocation failed: ") + cudaGetErrorString(cudaGetLastError()));
+        if (d_raw) cudaFree(d_raw);
+        for (void* p : w->plane) if (p) cudaFree(p);
+        delete w;
+        return nullptr;
+    }
+    t0 = clock_type::now();
+    ok = stream_to_device(s, d_raw, host + first_row * row_raw, w->raw_bytes);
+    s.stats.transfer_us += us_since(t0);
+    if (ok) {
+        t0 = clock_type::now();
+        const size_t nblocks = nrows * w->nb;
+        const unsigned grid = static_cast<unsigned>((nblocks + 255) / 256);
+        zk::repack_q8_0_kernel<<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]),
+                                                               static_cast<uint16_t*>(w->plane[1]), nrows, w->nb, w->nbp);
+        ++s.stats.dispatches;
+        ok = cudaGetLastError() == cudaSuccess && cudaStreamSynchronize(s.copy_stream) == cudaSuccess;
+        s.stats.repack_us += us_since(t0);
+        if (!ok) set_error(s, "upload: repack failed");
+    }
+    cudaFree(d_raw);
+    if (!ok) {
+        for (void* p : w->plane) if (p) cudaFree(p);
+        delete w;
+        return nullptr;
+    }
+    s.stats.upload_bytes += w->raw_bytes;
+    s.stats.weight_bytes += w->device_bytes;
+    s.stats.upload_us += us_since(t_all);
+    return w;
+}
+
+zen_cuda_weights* lookup_locked(State& s, int fmt, const uint8_t* host, size_t rows, size_t cols) {
+    const ResidentKey key{host, rows, cols, fmt};
+    auto it = s.resident.find(key);
+    if (it != s.resident.end()) return it->second;
+    zen_cuda_weights* w = upload_locked(s, fmt, host, rows, cols, 0, rows);
+    if (w) s.resident.emplace(key, w);
+    return w;
+}
+
+template <int kBatch, int kDigits>
+cudaError_t launch_gemv_q8_0(const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st) {
+    auto* fn = &zk::gemv_q8_0_kernel<kBatch, kDigits>;
+    static size_t configured = 0;  // per instantiation; one device per process, calls serialised by the backend mutex
+    if (smem > configured) {       // raised outside any stream capture by the first (uncaptured) launch of a shape
+        const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    fn<<<grid, zk::kGemvThreads, smem, st>>>(p);
+    return cudaGetLastError();
+}
+
+template <int kDigits>
+cudaError_t dispatch_batch(int batch, const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st) {
+    switch (batch) {
+    case 1: return launch_gemv_q8_0<1, kDigits>(p, grid, smem, st);
+    case 2: return launch_gemv_q8_0<2, kDigits>(p, grid, smem, st);
+    case 3: return launch_gemv_q8_0<3, kDigits>(p, grid, smem, st);
+    case 4: return launch_gemv_q8_0<4, kDigits>(p, grid, smem, st);
+    case 5: return launch_gemv_q8_0<5, kDigits>(p, grid, smem, st);
+    case 6: return launch_gemv_q8_0<6, kDigits>(p, grid, smem, st);
+    case 7: return launch_gemv_q8_0<7, kDigits>(p, grid, smem, st);
+    case 8: return launch_gemv_q8_0<8, kDigits>(p, grid, smem, st);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+// Enqueues one batched GEMV launch: `count` tensors (same format, same K) times `tokens` (<= 8)
+// activation rows.  Device pointers throughout.
+bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
+                  size_t tokens, int act_mode, cudaStream_t st) {
+    if (!count || count > zk::kMaxTasks || !tokens || tokens > 8 || !d_x) return set_error(s, "gemv: bad batch");
+    if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: bad activation mode");
+    zk::GemvParams p{};
+    uint32_t groups = 0;
+    for (size_t i = 0; i < count; ++i) {
+        if (!w[i] || !d_y[i] || w[i]->format != w[0]->format || w[i]->cols != w[0]->cols) return set_error(s, "gemv: tasks must share format and columns");
+        p.task[i].codes = static_cast<const uint8_t*>(w[i]->plane[0]);
+        p.task[i].scales = static_cast<const __half*>(w[i]->plane[1]);
+        p.task[i].y = d_y[i];
+        p.task[i].rows = static_cast<uint32_t>(w[i]->rows);
+        p.task[i].first_group = groups;
+        groups += static_cast<uint32_t>((w[i]->rows + zk::kGemvWarps - 1) / zk::kGemvWarps);
+    }
+    if (w[0]->format != ZEN_CUDA_Q8_0) return set_error(s, "gemv: format not built yet");
+    p.ntasks = static_cast<uint32_t>(count);
+    p.total_groups = groups;
+    p.x = d_x;
+    p.K = static_cast<uint32_t>(w[0]->cols);
+    p.nb = w[0]->nb;
+    p.nbp = w[0]->nbp;
+    p.nseg = (p.nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks;
+    p.error_word = s.d_error;
+    const int digits = act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1;
+    const size_t smem = zk::gemv_q8_0_smem_bytes(p.nseg, static_cast<int>(tokens), digits);
+    if (smem > s.smem_optin) return set_error(s, "gemv: activation rows do not fit shared memory (columns x tokens too large)");
+    const unsigned per_sm = static_cast<unsigned>(std::max<size_t>(1, std::min<size_t>(3, s.smem_optin / smem)));
+    const unsigned grid = std::min<unsigned>(groups, static_cast<unsigned>(s.sm_count) * per_sm);
+    const cudaError_t e = digits == 2 ? dispatch_batch<2>(static_cast<int>(tokens), p, grid, smem, st)
+                                      : dispatch_batch<1>(static_cast<int>(tokens), p, grid, smem, st);
+    if (e != cudaSuccess) return set_error(s, std::string("gemv launch: ") + cudaGetErrorString(e));
+    ++s.stats.dispatches;
+    return true;
+}
+
+bool ensure_scratch(State& s, size_t x_bytes, size_t y_bytes) {
+    const auto t0 = clock_type::now();
+    if (x_bytes > s.d_x_bytes) {
+        if (s.d_x) cudaFree(s.d_x);
+        s.d_x = nullptr; s.d_x_bytes = 0;
+        ZC_CUDA(s, cudaMalloc(reinterpret_cast<void**>(&s.d_x), x_bytes));
+        s.d_x_bytes = x_bytes;
+    }
+    if (y_bytes > s.d_y_bytes) {
+        if (s.d_y) cudaFree(s.d_y);
+        s.d_y = nullptr; s.d_y_bytes = 0;
+        ZC_CUDA(s, cudaMalloc(reinterpret_cast<void**>(&s.d_y), y_bytes));
+        s.d_y_bytes = y_bytes;
+    }
+    const size_t need = std::max(x_bytes, y_bytes);
+    if (need > s.h_stage_bytes) {
+        if (s.h_stage) cudaFreeHost(s.h_stage);
+        s.h_stage = nullptr; s.h_stage_bytes = 0;
+        ZC_CUDA(s, cudaHostAlloc(reinterpret_cast<void**>(&s.h_stage), need, cudaHostAllocDefault));
+        s.h_stage_bytes = need;
+    }
+    s.stats.alloc_us += us_since(t0);
+    return true;
+}
+
+bool check_error_word(State& s) {
+    if (*s.h_error == 0) return true;
+    const int code = *s.h_error;
+    *s.h_error = 0;
+    return set_error(s, "device wait timed out (code " + std::to_string(code) + ")");
+}
+
+// Host-pointer batched product: `count` tensors sharing `tokens` activation rows.
+// Outputs are token-major [tokens][rows_i] in the caller's buffers.
+bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weights, float* const* ys, const size_t* rows,
+                  size_t count, size_t tokens, size_t cols, int act_mode) {
+    if (!x || !weights || !ys || !rows || !count || count > zk::kMaxTasks || !tokens || !cols) return set_error(s, "bad arguments");
+    if (cols % block_elems(fmt)) return set_error(s, "columns are not block aligned");
+    const zen_cuda_weights* w[zk::kMaxTasks];
+    size_t total_rows = 0;
+    for (size_t i = 0; i < count; ++i) {
+        if (!weights[i] || !ys[i] || !rows[i]) return set_error(s, "bad task");
+        w[i] = lookup_locked(s, fmt, weights[i], rows[i], cols);
+        if (!w[i]) return false;
+        total_rows += rows[i];
+    }
+    const size_t x_bytes = tokens * cols * sizeof(float), y_bytes = tokens * total_rows * sizeof(float);
+    if (!ensure_scratch(s, x_bytes, y_bytes)) return false;
+    auto t0 = clock_type::now();
+    std::memcpy(s.h_stage, x, x_bytes);
+    ZC_CUDA(s, cudaMemcpyAsync(s.d_x, s.h_stage, x_bytes, cudaMemcpyHostToDevice, s.stream));
+    s.stats.transfer_us += us_since(t0);
+    t0 = clock_type::now();
+    // Token chunks of up to eight rows per launch; each task's device output is [tokens][rows_i].
+    float* d_out[zk::kMaxTasks];
+    size_t off = 0;
+    for (size_t i = 0; i < count; ++i) { d_out[i] = s.d_y + off; off += tokens * rows[i]; }
+    for (size_t t0k = 0; t0k < tokens; t0k += 8) {
+        const size_t nt = std::min<size_t>(8, tokens - t0k);
+        float* d_chunk[zk::kMaxTasks];
+        for (size_t i = 0; i < count; ++i) d_chunk[i] = d_out[i] + t0k * rows[i];
+        if (!enqueue_gemv(s, w, d_chunk, count, s.d_x + t0k * cols, nt, act_mode, s.stream)) return false;
+    }
+    s.stats.launch_us += us_since(t0);
+    t0 = clock_type::now();
+    ZC_CUDA(s, cudaMemcpyAsync(s.h_stage, s.d_y, y_bytes, cudaMemcpyDeviceToHost, s.stream));
+    ZC_CUDA(s, cudaStreamSynchronize(s.stream));
+    s.stats.wait_us += us_since(t0);
+    if (!check_error_word(s)) return false;
+    t0 = clock_type::now();
+    off = 0;
+    for (size_t i = 0; i < count; ++i) {
+        std::memcpy(ys[i], reinterpret_cast<const uint8_t*>(s.h_stage) + off * sizeof(float), tokens * rows[i] * sizeof(float));
+        off += tokens * rows[i];
+    }
+    s.stats.readback_us += us_since(t0);
+    ++s.stats.submits;
+    if (count > 1) ++s.stats.batches;
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+int zen_cuda_enabled(void) {
+    if (opted_out()) return 0;
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    return init_locked(s) ? 1 : 0;
+}
+
+int zen_cuda_init(void) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    return init_locked(s) ? 1 : 0;
+}
+
+void zen_cuda_shutdown(void) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (s.ready) {
+        cudaSetDevice(s.device);
+        cudaStreamSynchronize(s.stream);
+        cudaStreamSynchronize(s.copy_stream);
+        for (auto& kv : s.resident) free_weights(s, kv.second);
+        s.resident.clear();
+        if (s.d_x) cudaFree(s.d_x);
+        if (s.d_y) cudaFree(s.d_y);
+        if (s.h_stage) cudaFreeHost(s.h_stage);
+        if (s.h_error) cudaFreeHost(s.h_error);
+        for (int i = 0; i < 2; ++i) {
+            if (s.bounce[i]) cudaFreeHost(s.bounce[i]);
+            if (s.bounce_free[i]) cudaEventDestroy(s.bounce_free[i]);
+            s.bounce[i] = nullptr; s.bounce_free[i] = nullptr;
+        }
+        if (s.stream) cudaStreamDestroy(s.stream);
+        if (s.copy_stream) cudaStreamDestroy(s.copy_stream);
+        s.d_x = s.d_y = nullptr; s.h_stage = nullptr; s.h_error = s.d_error = nullptr;
+        s.d_x_bytes = s.d_y_bytes = s.h_stage_bytes = 0;
+        s.stream = s.copy_stream = nullptr;
+    }
+    s.ready = false;
+    s.failed = false;  // a failed init is latched only until shutdown (hip_backend.hip:921-923)
+}
+
+int zen_cuda_info(zen_cuda_adapter_info* out) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!s.ready || !out) return 0;
+    *out = s.adapter;
+    return 1;
+}
+
+void zen_cuda_get_stats(zen_cuda_stats* out) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (out) *out = s.stats;
+}
+
+const char* zen_cuda_last_error(void) {
+    static thread_local std::string copy;
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    copy = s.last_error;
+    return copy.c_str();
+}
+
+int zen_cuda_set_q8_act_mode(int mode) {
+    if (mode != ZEN_CUDA_ACT_INT8 && mode != ZEN_CUDA_ACT_FP32) return 0;
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    s.q8_act_mode = mode;
+    return 1;
+}
+int zen_cuda_get_q8_act_mode(void) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    return s.q8_act_mode;
+}
+
+int zen_cuda_gemv_q8_0(const uint8_t* weights, const float* x, float* y, size_t rows, size_t columns) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    return host_product(s, ZEN_CUDA_Q8_0, x, &weights, &y, &rows, 1, 1, columns, s.q8_act_mode) ? 1 : 0;
+}
+
+int zen_cuda_gemm_q8_0(const uint8_t* weights, const float* input, float* output, size_t tokens, size_t rows, size_t columns) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    return host_product(s, ZEN_CUDA_Q8_0, input, &weights, &output, &rows, 1, tokens, columns, s.q8_act_mode) ? 1 : 0;
+}
+
+int zen_cuda_gemv_q8_0_batch(const float* x, const zen_cuda_gemv_task* tasks, size_t count) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!tasks || !count || count > ZEN_CUDA_MAX_BATCH) return set_error(s, "gemv_q8_0_batch: bad task list") ? 1 : 0;
+    const uint8_t* w[ZEN_CUDA_MAX_BATCH]; float* y[ZEN_CUDA_MAX_BATCH]; size_t r[ZEN_CUDA_MAX_BATCH];
+    for (size_t i = 0; i < count; ++i) {
+        if (tasks[i].columns != tasks[0].columns) return set_error(s, "gemv_q8_0_batch: tasks must share columns") ? 1 : 0;
+        w[i] = tasks[i].weights; y[i] = tasks[i].y; r[i] = tasks[i].rows;
+    }
+    return host_product(s, ZEN_CUDA_Q8_0, x, w, y, r, count, 1, tasks[0].columns, s.q8_act_mode) ? 1 : 0;
+}
+
+int zen_cuda_gemm_q8_0_batch(const float* x, const zen_cuda_gemm_task* tasks, size_t count, size_t tokens, size_t columns) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!tasks || !count || count > ZEN_CUDA_MAX_BATCH) return set_error(s, "gemm_q8_0_batch: bad task list") ? 1 : 0;
+    const uint8_t* w[ZEN_CUDA_MAX_BATCH]; float* y[ZEN_CUDA_MAX_BATCH]; size_t r[ZEN_CUDA_MAX_BATCH];
+    for (size_t i = 0; i < count; ++i) { w[i] = tasks[i].weights; y[i] = tasks[i].y; r[i] = tasks[i].rows; }
+    return host_product(s, ZEN_CUDA_Q8_0, x, w, y, r, count, tokens, columns, s.q8_act_mode) ? 1 : 0;
+}
+
+int zen_cuda_gemm_q6_k(const uint8_t* weights, const float* input, float* output, size_t tokens, size_t rows, size_t columns) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    return host_product(s, ZEN_CUDA_Q6_K, input, &weights, &output, &rows, 1, tokens, columns, ZEN_CUDA_ACT_FP32) ? 1 : 0;
+}
+
+int zen_cuda_gemm_q4_0(const uint8_t* weights, const float* input, float* output, size_t tokens, size_t rows, size_t columns) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    return host_product(s, ZEN_CUDA_Q4_0, input, &weights, &output, &rows, 1, tokens, columns, ZEN_CUDA_ACT_FP32) ? 1 : 0;
+}
+
+void zen_cuda_release_weights(const uint8_t* weights) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!s.ready) return;
+    cudaStreamSynchronize(s.stream);
+    for (auto it = s.resident.begin(); it != s.resident.end();) {
+        if (it->first.ptr == weights) { free_weights(s, it->second); it = s.resident.erase(it); }
+        else ++it;
+    }
+}
+
+int zen_cuda_quantize_acts(const float* x, int8_t* codes, float* scales, size_t tokens, size_t columns) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!x || !codes || !scales || !tokens || !columns || columns % 32) return set_error(s, "quantize_acts: bad arguments") ? 1 : 0;
+    const size_t n = tokens * columns, nblk = n / 32;
+    const size_t scales_at = (n + 255) & ~size_t(255);  // scales follow the codes in the output scratch
+    if (!ensure_scratch(s, n * sizeof(float), scales_at + nblk * sizeof(float))) return 0;
+    int8_t* d_codes = reinterpret_cast<int8_t*>(s.d_y);
+    float* d_scales = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(s.d_y) + scales_at);
+    std::memcpy(s.h_stage, x, n * sizeof(float));
+    if (cudaMemcpyAsync(s.d_x, s.h_stage, n * sizeof(float), cudaMemcpyHostToDevice, s.stream) != cudaSuccess) return set_error(s, "quantize_acts: copy failed") ? 1 : 0;
+    zk::quantize_acts_kernel<<<static_cast<unsigned>((nblk + 7) / 8), 256, 0, s.stream>>>(s.d_x, d_codes, d_scales, nullptr, nblk);
+    ++s.stats.dispatches;
+    if (cudaGetLastError() != cudaSuccess) return set_error(s, "quantize_acts: launch failed") ? 1 : 0;
+    if (cudaMemcpyAsync(codes, d_codes, n, cudaMemcpyDeviceToHost, s.stream) != cudaSuccess ||
+        cudaMemcpyAsync(scales, d_scales, nblk * sizeof(float), cudaMemcpyDeviceToHost, s.stream) != cudaSuccess ||
+        cudaStreamSynchronize(s.stream) != cudaSuccess)
+        return set_error(s, "quantize_acts: readback failed") ? 1 : 0;
+    ++s.stats.submits;
+    return 1;
+}
+
+zen_cuda_weights* zen_cuda_dev_upload(int format, const uint8_t* weights, size_t rows_total, size_t columns, size_t first_row, size_t nrows) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return nullptr;
+    return upload_locked(s, format, weights, rows_total, columns, first_row, nrows);
+}
+
+void zen_cuda_dev_free(zen_cuda_weights* w) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!s.ready || !w) return;
+    cudaDeviceSynchronize();
+    free_weights(s, w);
+}
+
+size_t zen_cuda_dev_weight_bytes(const zen_cuda_weights* w) { return w ? w->device_bytes : 0; }
+
+int zen_cuda_dev_gemv(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x, size_t tokens,
+                      int act_mode, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!w || !d_y) return set_error(s, "dev_gemv: bad arguments") ? 1 : 0;
+    return enqueue_gemv(s, w, d_y, count, d_x, tokens, act_mode, stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
+}
+
+int zen_cuda_dev_quantize_acts(const float* d_x, int8_t* d_codes, float* d_scales, size_t tokens, size_t columns, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!d_x || !d_codes || !d_scales || !tokens || !columns || columns % 32) return set_error(s, "dev_quantize_acts: bad arguments") ? 1 : 0;
+    const size_t nblk = tokens * columns / 32;
+    zk::quantize_acts_kernel<<<static_cast<unsigned>((nblk + 7) / 8), 256, 0, stream ? static_cast<cudaStream_t>(stream) : s.stream>>>(
+        d_x, d_codes, d_scales, nullptr, nblk);
+    ++s.stats.dispatches;
+    if (cudaGetLastError() != cudaSuccess) return set_error(s, "dev_quantize_acts: launch failed") ? 1 : 0;
+    return 1;
+}
+
+int zen_cuda_dev_check(void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!s.ready) return 0;
+    cudaStreamSynchronize(stream ? static_cast<cudaStream_t>(stream) : s.stream);
+    const int code = *s.h_error;
+    *s.h_error = 0;
+    return code;
+}
+
+}  // extern "C"
