@@ -7,10 +7,12 @@
 // they are fp32 (kDigits == 2, two int8 digits per activation).
 //
 // Shape of the kernel
-//   * a CTA owns "row groups" of kGemvWarps consecutive weight rows, taken
-//     round-robin; every consumer warp owns one row of the group and keeps that
-//     row's accumulators in registers until the row is finished, so no partial
-//     sums ever cross warps and the result is deterministic;
+//   * one persistent CTA per SM owns a contiguous, byte-balanced slice of the
+//     launch's rows (slice i of n covers [rows*i/n, rows*(i+1)/n), the same cut the
+//     reference's ComputePool::parallel_for makes, src/compute_pool.cpp:104-106) and
+//     walks it in groups of kGemvWarps rows; every consumer warp owns one row of
+//     the group and keeps that row's accumulators in registers until the row is
+//     finished, so no partial sums ever cross warps and the result is deterministic;
 //   * one producer warp streams the group's rows through a ring of shared-memory
 //     stages with 1-D TMA bulk copies (cp.async.bulk), one K-segment of
 //     kGemvSegBlocks blocks at a time, each stage guarded by a full/empty
@@ -19,6 +21,9 @@
 //   * the activation vector is quantised once per CTA in the prologue (while the
 //     first weight stages are already in flight) into a lane-major layout, so
 //     every shared-memory read in the inner loop is a conflict-free 128-bit load;
+//   * launched with programmatic stream serialisation: the weight stream of launch
+//     n+1 starts while launch n drains (weights are constants), and only the
+//     activation read waits for the previous grid (griddepcontrol.wait);
 //   * per 32-element block: 8 dp4a per digit, one int->float conversion and one
 //     fused multiply-add with the fp16 block scale times the activation scale.
 //
@@ -33,7 +38,7 @@ namespace zk {
 
 constexpr int kGemvWarps = 8;        // consumer warps == rows per row group
 constexpr int kGemvSegBlocks = 64;   // 32-element blocks per K segment
-constexpr int kGemvStages = 4;
+constexpr int kGemvStages = 6;
 constexpr int kGemvThreads = (kGemvWarps + 1) * 32;
 constexpr int kMaxTasks = 8;         // projections sharing one input (zen::hip::kMaxBatch, include/zen/hip_backend.h:70)
 
@@ -46,13 +51,13 @@ struct GemvTask {
     const __half* scales;    // [rows][nbp]
     float* y;                // [batch][rows], token-major
     uint32_t rows;
-    uint32_t first_group;    // index of this task's first row group in the launch
+    uint32_t first_row;      // index of this task's first row in the launch's concatenated row space
 };
 
 struct GemvParams {
     GemvTask task[kMaxTasks];
     uint32_t ntasks;
-    uint32_t total_groups;
+    uint32_t total_rows;     // over all tasks
     const float* x;          // [batch][K] fp32
     uint32_t K, nb, nbp, nseg;
     int* error_word;         // set to a zk::kErr* code when a bounded wait gives up
@@ -66,8 +71,29 @@ __host__ __device__ inline size_t gemv_q8_0_smem_bytes(uint32_t nseg, int batch,
            + 2 * kGemvStages * 8 + 16;                               // barriers + abort word
 }
 
+// The slice of the launch's concatenated row space that CTA `cta` of `n` owns.
+__device__ __forceinline__ void cta_row_slice(uint32_t total_rows, uint32_t cta, uint32_t n, uint32_t& first, uint32_t& last) {
+    first = static_cast<uint32_t>(static_cast<uint64_t>(total_rows) * cta / n);
+    last = static_cast<uint32_t>(static_cast<uint64_t>(total_rows) * (cta + 1) / n);
+}
+
+// Walks a row slice in groups of at most kGemvWarps rows that never straddle two tasks.
+struct GroupWalk {
+    uint32_t r, r_end, ti;
+    __device__ GroupWalk(uint32_t first, uint32_t last) : r(first), r_end(last), ti(0) {}
+    __device__ bool done() const { return r >= r_end; }
+    // Returns the task index and fills the group's first row within that task and its row count.
+    __device__ uint32_t next(const GemvParams& p, uint32_t& row0, uint32_t& nrows) {
+        while (r >= p.task[ti].first_row + p.task[ti].rows) ++ti;
+        row0 = r - p.task[ti].first_row;
+        nrows = min(min(static_cast<uint32_t>(kGemvWarps), p.task[ti].rows - row0), r_end - r);
+        r += nrows;
+        return ti;
+    }
+};
+
 template <int kBatch, int kDigits>
-__global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 2 ? 3 : (kBatch * kDigits <= 4 ? 2 : 1)))
+__global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 4 ? 2 : 1))
     gemv_q8_0_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t kpad_blocks = p.nseg * kGemvSegBlocks;
@@ -79,6 +105,8 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 2 ? 3 : (kB
     volatile int* abort_word = reinterpret_cast<volatile int*>(empty + kGemvStages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t r_first, r_last;
+    cta_row_slice(p.total_rows, blockIdx.x, gridDim.x, r_first, r_last);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemvStages; ++s) {
@@ -89,17 +117,17 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 2 ? 3 : (kB
         mbar_fence_init();
     }
     __syncthreads();
+    // Let the next launch in the stream begin: its weight stream may overlap this grid's tail.
+    pdl_launch_dependents();
 
     if (warp == kGemvWarps) {
-        // ---------------- producer warp ----------------
+        // ---------------- producer warp: weights are constants, no need to wait for the previous grid ----------------
         uint32_t unit = 0;
         bool ok = true;
-        for (uint32_t g = blockIdx.x; g < p.total_groups && ok; g += gridDim.x) {
-            uint32_t ti = 0;
-            while (ti + 1 < p.ntasks && g >= p.task[ti + 1].first_group) ++ti;
-            const GemvTask& t = p.task[ti];
-            const uint32_t row0 = (g - t.first_group) * kGemvWarps;
-            const uint32_t nrows = min(static_cast<uint32_t>(kGemvWarps), t.rows - row0);
+        GroupWalk walk(r_first, r_last);
+        while (!walk.done() && ok) {
+            uint32_t row0, nrows;
+            const GemvTask& t = p.task[walk.next(p, row0, nrows)];
             for (uint32_t s = 0; s < p.nseg && ok; ++s, ++unit) {
                 const uint32_t stage = unit % kGemvStages;
                 if (unit >= kGemvStages) {
@@ -139,20 +167,34 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 2 ? 3 : (kB
     }
 
     // ---------------- consumer warps ----------------
+    // The activations (and the output buffers) belong to the stream's earlier work: wait for it.
+    pdl_wait();
     // Prologue: quantise the activations into the lane-major layout.  Block b = 64*s + 32*i + l is
     // read by lane l; its two 16-byte halves are stored in the order that lane loads them
     // (half ((l>>2)&1) first), which keeps both the weight and the activation loads conflict-free.
-    for (int t = 0; t < kBatch; ++t) {
-        for (uint32_t b = warp; b < p.nb; b += kGemvWarps) {
-            int q1, q2;
-            const float d = quantise_block_lane(p.x[static_cast<size_t>(t) * p.K + b * 32 + lane], q1, q2);
-            const uint32_t l = b & 31, grp = b >> 5;  // grp == 2*s + i
-            const uint32_t h0 = (l >> 2) & 1, hh = (static_cast<uint32_t>(lane) >> 4) ^ h0;
-            const size_t slot = (static_cast<size_t>(grp) * 2 + hh) * 32 + l;  // uint4 index
-            int8_t* dst = reinterpret_cast<int8_t*>(xcodes + (static_cast<size_t>(t) * kDigits) * kpad_blocks * 2 + slot) + (lane & 15);
-            *dst = static_cast<int8_t>(q1);
-            if (kDigits == 2) dst[static_cast<size_t>(kpad_blocks) * 32] = static_cast<int8_t>(q2);
-            if (lane == 0) xscale[static_cast<size_t>(t) * kpad_blocks + b] = kDigits == 2 ? d * (1.0f / 256.0f) : d;
+    // Four lanes share a block (eight consecutive elements each), so one pass of the eight warps
+    // covers 64 blocks with two 128-bit loads per lane and the whole vector in a few passes.
+    {
+        const uint32_t quad = static_cast<uint32_t>(lane) >> 2, part = static_cast<uint32_t>(lane) & 3;
+        for (int t = 0; t < kBatch; ++t) {
+            for (uint32_t b0 = warp * 8; b0 < p.nb; b0 += kGemvWarps * 8) {  // warp-uniform trip count: the quantiser shuffles
+                const uint32_t b = b0 + quad;
+                const bool live = b < p.nb;
+                const float4* src = reinterpret_cast<const float4*>(p.x + static_cast<size_t>(t) * p.K + b * 32 + part * 8);
+                const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 lo = live ? __ldg(src) : zero, hi = live ? __ldg(src + 1) : zero;
+                const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                uint2 c1, c2;
+                const float d = quantise_block_quad(v, c1, c2);
+                if (!live) continue;
+                const uint32_t l = b & 31, grp = b >> 5;  // grp == 2*s + i
+                const uint32_t hh = (part >> 1) ^ ((l >> 2) & 1);
+                const size_t slot = (static_cast<size_t>(grp) * 2 + hh) * 32 + l;  // uint4 index
+                uint2* dst = reinterpret_cast<uint2*>(xcodes + (static_cast<size_t>(t) * kDigits) * kpad_blocks * 2 + slot) + (part & 1);
+                *dst = c1;
+                if (kDigits == 2) dst[static_cast<size_t>(kpad_blocks) * 4] = c2;
+                if (part == 0) xscale[static_cast<size_t>(t) * kpad_blocks + b] = kDigits == 2 ? d * (1.0f / 256.0f) : d;
+            }
         }
     }
     // consumer-only barrier (the producer warp is already streaming)
@@ -161,12 +203,12 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 2 ? 3 : (kB
     uint32_t unit = 0;
     bool ok = true;
     const uint32_t h0 = (static_cast<uint32_t>(lane) >> 2) & 1;
-    for (uint32_t g = blockIdx.x; g < p.total_groups && ok; g += gridDim.x) {
-        uint32_t ti = 0;
-        while (ti + 1 < p.ntasks && g >= p.task[ti + 1].first_group) ++ti;
-        const GemvTask& t = p.task[ti];
-        const uint32_t row = (g - t.first_group) * kGemvWarps + warp;
-        const bool valid = row < t.rows;
+    GroupWalk walk(r_first, r_last);
+    while (!walk.done() && ok) {
+        uint32_t row0, nrows;
+        const GemvTask& t = p.task[walk.next(p, row0, nrows)];
+        const uint32_t row = row0 + warp;
+        const bool valid = static_cast<uint32_t>(warp) < nrows;
         float acc[kBatch];
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) acc[b] = 0.0f;

@@ -49,6 +49,39 @@ __device__ __forceinline__ float quantise_block_lane(float x, int& q1, int& q2) 
     return d;
 }
 
+// Four lanes quantise one 32-element block, eight consecutive elements per lane (lanes 4k..4k+3
+// of a warp form one group; all 32 lanes must call).  Same arithmetic, bit for bit, as
+// quantise_block_lane; only the reduction tree of the (order-independent) maximum differs.
+// c1/c2 receive the eight codes packed little-endian, element 0 in the low byte.
+__device__ __forceinline__ float quantise_block_quad(const float (&v)[8], uint2& c1, uint2& c2) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float a = fabsf(v[k]);
+        amax = a > amax ? a : amax;
+    }
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, amax, o);
+        amax = other > amax ? other : amax;
+    }
+    const float d = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
+    const float inv = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    const float inv256 = __fmul_rn(inv, 256.0f);
+    uint32_t w1[2] = {0, 0}, w2[2] = {0, 0};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int q1 = round_half_away(clamp127(__fmul_rn(v[k], inv)));
+        const float r = __fmaf_rn(-static_cast<float>(q1), d, v[k]);
+        const int q2 = round_half_away(clamp127(__fmul_rn(r, inv256)));
+        w1[k >> 2] |= (static_cast<uint32_t>(q1) & 0xffu) << (8 * (k & 3));
+        w2[k >> 2] |= (static_cast<uint32_t>(q2) & 0xffu) << (8 * (k & 3));
+    }
+    c1 = make_uint2(w1[0], w1[1]);
+    c2 = make_uint2(w2[0], w2[1]);
+    return d;
+}
+
 // Standalone kernel: x [tokens][K] fp32 -> q [tokens][K] int8, sc [tokens][K/32] fp32,
 // optionally q2 [tokens][K] int8 (the fine digit).  One warp per block.
 __global__ void __launch_bounds__(256) quantize_acts_kernel(const float* __restrict__ x, int8_t* __restrict__ q,

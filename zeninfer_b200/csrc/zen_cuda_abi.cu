@@ -69,6 +69,8 @@ struct State {
     zen_cuda_stats stats{};
     std::string last_error;
     int q8_act_mode{ZEN_CUDA_ACT_INT8};
+    bool pdl{true};          // programmatic dependent launch of the GEMV kernels (ZEN_CUDA_PDL=0 turns it off)
+    unsigned ctas_per_sm{1}; // persistent GEMV CTAs per SM (ZEN_CUDA_GEMV_CTAS)
     std::unordered_map<ResidentKey, zen_cuda_weights*, ResidentKeyHash> resident;
     // pinned host staging + device scratch for the host-pointer calls (grow-only)
     float* h_stage{}; size_t h_stage_bytes{};
@@ -139,6 +141,8 @@ bool init_locked(State& s) {
         if (!std::strcmp(m, "fp32") || !std::strcmp(m, "2")) s.q8_act_mode = ZEN_CUDA_ACT_FP32;
         else if (!std::strcmp(m, "int8") || !std::strcmp(m, "1")) s.q8_act_mode = ZEN_CUDA_ACT_INT8;
     }
+    if (const char* m = std::getenv("ZEN_CUDA_PDL")) s.pdl = m[0] != '0';
+    if (const char* m = std::getenv("ZEN_CUDA_GEMV_CTAS")) s.ctas_per_sm = static_cast<unsigned>(std::max(1, std::min(4, std::atoi(m))));
     s.ready = true;
     return true;
 }
@@ -242,7 +246,7 @@ zen_cuda_weights* lookup_locked(State& s, int fmt, const uint8_t* host, size_t r
 }
 
 template <int kBatch, int kDigits>
-cudaError_t launch_gemv_q8_0(const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st) {
+cudaError_t launch_gemv_q8_0(const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
     auto* fn = &zk::gemv_q8_0_kernel<kBatch, kDigits>;
     static size_t configured = 0;  // per instantiation; one device per process, calls serialised by the backend mutex
     if (smem > configured) {       // raised outside any stream capture by the first (uncaptured) launch of a shape
@@ -250,21 +254,30 @@ cudaError_t launch_gemv_q8_0(const zk::GemvParams& p, unsigned grid, size_t smem
         if (e != cudaSuccess) return e;
         configured = smem;
     }
-    fn<<<grid, zk::kGemvThreads, smem, st>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(zk::kGemvThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, fn, p);
 }
 
 template <int kDigits>
-cudaError_t dispatch_batch(int batch, const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st) {
+cudaError_t dispatch_batch(int batch, const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
     switch (batch) {
-    case 1: return launch_gemv_q8_0<1, kDigits>(p, grid, smem, st);
-    case 2: return launch_gemv_q8_0<2, kDigits>(p, grid, smem, st);
-    case 3: return launch_gemv_q8_0<3, kDigits>(p, grid, smem, st);
-    case 4: return launch_gemv_q8_0<4, kDigits>(p, grid, smem, st);
-    case 5: return launch_gemv_q8_0<5, kDigits>(p, grid, smem, st);
-    case 6: return launch_gemv_q8_0<6, kDigits>(p, grid, smem, st);
-    case 7: return launch_gemv_q8_0<7, kDigits>(p, grid, smem, st);
-    case 8: return launch_gemv_q8_0<8, kDigits>(p, grid, smem, st);
+    case 1: return launch_gemv_q8_0<1, kDigits>(p, grid, smem, st, pdl);
+    case 2: return launch_gemv_q8_0<2, kDigits>(p, grid, smem, st, pdl);
+    case 3: return launch_gemv_q8_0<3, kDigits>(p, grid, smem, st, pdl);
+    case 4: return launch_gemv_q8_0<4, kDigits>(p, grid, smem, st, pdl);
+    case 5: return launch_gemv_q8_0<5, kDigits>(p, grid, smem, st, pdl);
+    case 6: return launch_gemv_q8_0<6, kDigits>(p, grid, smem, st, pdl);
+    case 7: return launch_gemv_q8_0<7, kDigits>(p, grid, smem, st, pdl);
+    case 8: return launch_gemv_q8_0<8, kDigits>(p, grid, smem, st, pdl);
     default: return cudaErrorInvalidValue;
     }
 }
@@ -276,19 +289,19 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
     if (!count || count > zk::kMaxTasks || !tokens || tokens > 8 || !d_x) return set_error(s, "gemv: bad batch");
     if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: bad activation mode");
     zk::GemvParams p{};
-    uint32_t groups = 0;
+    uint32_t total_rows = 0;
     for (size_t i = 0; i < count; ++i) {
         if (!w[i] || !d_y[i] || w[i]->format != w[0]->format || w[i]->cols != w[0]->cols) return set_error(s, "gemv: tasks must share format and columns");
         p.task[i].codes = static_cast<const uint8_t*>(w[i]->plane[0]);
         p.task[i].scales = static_cast<const __half*>(w[i]->plane[1]);
         p.task[i].y = d_y[i];
         p.task[i].rows = static_cast<uint32_t>(w[i]->rows);
-        p.task[i].first_group = groups;
-        groups += static_cast<uint32_t>((w[i]->rows + zk::kGemvWarps - 1) / zk::kGemvWarps);
+        p.task[i].first_row = total_rows;
+        total_rows += static_cast<uint32_t>(w[i]->rows);
     }
     if (w[0]->format != ZEN_CUDA_Q8_0) return set_error(s, "gemv: format not built yet");
     p.ntasks = static_cast<uint32_t>(count);
-    p.total_groups = groups;
+    p.total_rows = total_rows;
     p.x = d_x;
     p.K = static_cast<uint32_t>(w[0]->cols);
     p.nb = w[0]->nb;
@@ -298,10 +311,10 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
     const int digits = act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1;
     const size_t smem = zk::gemv_q8_0_smem_bytes(p.nseg, static_cast<int>(tokens), digits);
     if (smem > s.smem_optin) return set_error(s, "gemv: activation rows do not fit shared memory (columns x tokens too large)");
-    const unsigned per_sm = static_cast<unsigned>(std::max<size_t>(1, std::min<size_t>(3, s.smem_optin / smem)));
-    const unsigned grid = std::min<unsigned>(groups, static_cast<unsigned>(s.sm_count) * per_sm);
-    const cudaError_t e = digits == 2 ? dispatch_batch<2>(static_cast<int>(tokens), p, grid, smem, st)
-                                      : dispatch_batch<1>(static_cast<int>(tokens), p, grid, smem, st);
+    // One persistent CTA per SM, each owning a contiguous slice of at least one row group.
+    const unsigned grid = std::max(1u, std::min<unsigned>((total_rows + zk::kGemvWarps - 1) / zk::kGemvWarps, static_cast<unsigned>(s.sm_count) * s.ctas_per_sm));
+    const cudaError_t e = digits == 2 ? dispatch_batch<2>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
+                                      : dispatch_batch<1>(static_cast<int>(tokens), p, grid, smem, st, s.pdl);
     if (e != cudaSuccess) return set_error(s, std::string("gemv launch: ") + cudaGetErrorString(e));
     ++s.stats.dispatches;
     return true;
