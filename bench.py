@@ -61,10 +61,17 @@ class ClockSampler:
 
     def __init__(self, index: int) -> None:
         self.index, self.rows, self.proc = index, [], None
+        self.window = [None, None]  # host-clock bounds of the timed region
+
+    def mark_start(self) -> None:
+        self.window[0] = time.time()
+
+    def mark_end(self) -> None:
+        self.window[1] = time.time()
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -74,7 +81,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
 
     def __exit__(self, *exc):
         if self.proc:
@@ -85,8 +92,13 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self) -> dict:
+        lo, hi = self.window
+        inside = [r for t, r in self.rows if lo is not None and hi is not None and lo <= t <= hi + 0.05]
+        scope = "timed region"
+        if not inside:  # a timed region shorter than one sampling period: use the samples taken under the same load around it
+            inside, scope = [r for _, r in self.rows], "warm-up + timed region (timed region shorter than one sample period)"
         sm, mx, reasons = [], [], set()
-        for r in self.rows:
+        for r in inside:
             try:
                 sm.append(float(r[1])); mx.append(float(r[2]))
             except Exception:
@@ -95,8 +107,8 @@ class ClockSampler:
                 if cell.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "scope": scope}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm), "scope": scope}
 
 
 def make_inputs():
@@ -162,7 +174,7 @@ def run_reference_arm(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--workload", default="q8_0_gemv")
@@ -212,22 +224,29 @@ def main() -> None:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             one_pass()
-        for _ in range(args.warmup):
-            graph.replay()
-        stream.synchronize()
-        be.dev_check(stream.cuda_stream)
-
-        # --- timed region: K graph replays, CUDA events on the launching stream ---
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local) as clocks:
+            t_warm = time.time()
+            n_warm = 0
+            while n_warm < args.warmup or time.time() - t_warm < 0.3:  # at least W steps, and long enough for the clock sampler to come up
+                graph.replay()
+                n_warm += 1
+                if n_warm % 64 == 0:
+                    stream.synchronize()
+            stream.synchronize()
+            be.dev_check(stream.cuda_stream)
+
+            # --- timed region: K graph replays, CUDA events on the launching stream ---
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            clocks.mark_start()
             e0.record(stream)
             for _ in range(args.steps):
                 graph.replay()
             e1.record(stream)
             stream.synchronize()
+            clocks.mark_end()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()

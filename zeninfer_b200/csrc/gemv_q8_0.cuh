@@ -10,17 +10,19 @@
 //   * one persistent CTA per SM owns a contiguous, byte-balanced slice of the
 //     launch's rows (slice i of n covers [rows*i/n, rows*(i+1)/n), the same cut the
 //     reference's ComputePool::parallel_for makes, src/compute_pool.cpp:104-106) and
-//     walks it in groups of kGemvWarps rows; every consumer warp owns one row of
-//     the group and keeps that row's accumulators in registers until the row is
-//     finished, so no partial sums ever cross warps and the result is deterministic;
-//   * one producer warp streams the group's rows through a ring of shared-memory
-//     stages with 1-D TMA bulk copies (cp.async.bulk), one K-segment of
-//     kGemvSegBlocks blocks at a time, each stage guarded by a full/empty
-//     mbarrier pair.  Bytes in flight are set by the ring depth, not by
-//     registers or occupancy;
+//     walks it in groups of eight rows.  Sixteen consumer warps form two teams of
+//     eight; consecutive groups go to alternate teams, and inside a team every warp
+//     owns one row and keeps that row's accumulators in registers until the row is
+//     finished.  No partial sum ever crosses a warp, so results are deterministic;
+//   * one producer warp streams the groups through a ring of shared-memory stages
+//     with 1-D TMA bulk copies (cp.async.bulk), one K-segment of up to 128 blocks
+//     at a time, each stage guarded by a full/empty mbarrier pair.  When a row is a
+//     single segment (K <= 4096) a whole group is one contiguous 32 KB copy.
+//     Bytes in flight are set by the ring depth, not by registers or occupancy;
 //   * the activation vector is quantised once per CTA in the prologue (while the
 //     first weight stages are already in flight) into a lane-major layout, so
 //     every shared-memory read in the inner loop is a conflict-free 128-bit load;
+//     for batch-1 int8 rows of at most 128 blocks it then moves into registers;
 //   * launched with programmatic stream serialisation: the weight stream of launch
 //     n+1 starts while launch n drains (weights are constants), and only the
 //     activation read waits for the previous grid (griddepcontrol.wait);
@@ -36,15 +38,22 @@
 
 namespace zk {
 
-constexpr int kGemvWarps = 8;        // consumer warps == rows per row group
-constexpr int kGemvSegBlocks = 64;   // 32-element blocks per K segment
-constexpr int kGemvStages = 6;
+constexpr int kTeamWarps = 8;                       // warps per team == rows per row group
+constexpr int kTeams = 2;
+constexpr int kGemvWarps = kTeamWarps * kTeams;     // consumer warps
+constexpr int kGemvSegBlocks = 128;                 // 32-element blocks per K segment: four per lane
+constexpr int kLaneBlocks = kGemvSegBlocks / 32;
+#ifndef ZK_GEMV_STAGES
+#define ZK_GEMV_STAGES 3
+#endif
+constexpr int kGemvStages = ZK_GEMV_STAGES;
 constexpr int kGemvThreads = (kGemvWarps + 1) * 32;
-constexpr int kMaxTasks = 8;         // projections sharing one input (zen::hip::kMaxBatch, include/zen/hip_backend.h:70)
+constexpr int kMaxTasks = 8;                        // projections sharing one input (zen::hip::kMaxBatch, include/zen/hip_backend.h:70)
 
-constexpr uint32_t kQ8StageCodeBytes = kGemvWarps * kGemvSegBlocks * 32;
-constexpr uint32_t kQ8StageScaleBytes = kGemvWarps * kGemvSegBlocks * 2;
+constexpr uint32_t kQ8StageCodeBytes = kTeamWarps * kGemvSegBlocks * 32;
+constexpr uint32_t kQ8StageScaleBytes = kTeamWarps * kGemvSegBlocks * 2;
 constexpr uint32_t kQ8StageBytes = kQ8StageCodeBytes + kQ8StageScaleBytes;
+constexpr uint32_t kL2PrefetchCap = 160 * 1024;     // bytes of the slice beyond the ring that are pulled into L2 up front
 
 struct GemvTask {
     const uint8_t* codes;    // [rows][K] int8
@@ -61,7 +70,17 @@ struct GemvParams {
     const float* x;          // [batch][K] fp32
     uint32_t K, nb, nbp, nseg;
     int* error_word;         // set to a zk::kErr* code when a bounded wait gives up
+#ifdef ZK_TRACE
+    unsigned long long* trace;  // [grid][16] phase stamps (profiling builds only)
+#endif
 };
+
+#ifdef ZK_TRACE
+__device__ __forceinline__ unsigned long long zk_globaltimer() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define ZK_STAMP(slot) do { if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + (slot)] = zk_globaltimer(); } while (0)
+#else
+#define ZK_STAMP(slot) do {} while (0)
+#endif
 
 __host__ __device__ inline size_t gemv_q8_0_smem_bytes(uint32_t nseg, int batch, int digits) {
     const size_t kpad_blocks = static_cast<size_t>(nseg) * kGemvSegBlocks;
@@ -77,23 +96,48 @@ __device__ __forceinline__ void cta_row_slice(uint32_t total_rows, uint32_t cta,
     last = static_cast<uint32_t>(static_cast<uint64_t>(total_rows) * (cta + 1) / n);
 }
 
-// Walks a row slice in groups of at most kGemvWarps rows that never straddle two tasks.
+struct RowGroup {
+    uint32_t task, row0, nrows;  // nrows == 0: no group (the odd tail of a pair)
+};
+
+// Walks a row slice in groups of at most kTeamWarps rows that never straddle two tasks.
 struct GroupWalk {
     uint32_t r, r_end, ti;
     __device__ GroupWalk(uint32_t first, uint32_t last) : r(first), r_end(last), ti(0) {}
     __device__ bool done() const { return r >= r_end; }
-    // Returns the task index and fills the group's first row within that task and its row count.
-    __device__ uint32_t next(const GemvParams& p, uint32_t& row0, uint32_t& nrows) {
+    __device__ RowGroup next(const GemvParams& p) {
+        RowGroup g{0, 0, 0};
+        if (done()) return g;
         while (r >= p.task[ti].first_row + p.task[ti].rows) ++ti;
-        row0 = r - p.task[ti].first_row;
-        nrows = min(min(static_cast<uint32_t>(kGemvWarps), p.task[ti].rows - row0), r_end - r);
-        r += nrows;
-        return ti;
+        g.task = ti;
+        g.row0 = r - p.task[ti].first_row;
+        g.nrows = min(min(static_cast<uint32_t>(kTeamWarps), p.task[ti].rows - g.row0), r_end - r);
+        r += g.nrows;
+        return g;
     }
 };
 
+__device__ __forceinline__ void l2_prefetch(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ int dot32(const uint4& wa, const uint4& wb, const uint4& xa, const uint4& xb) {
+    int s = dp4a_ss(wa.x, xa.x, 0);
+    s = dp4a_ss(wa.y, xa.y, s);
+    s = dp4a_ss(wa.z, xa.z, s);
+    s = dp4a_ss(wa.w, xa.w, s);
+    s = dp4a_ss(wb.x, xb.x, s);
+    s = dp4a_ss(wb.y, xb.y, s);
+    s = dp4a_ss(wb.z, xb.z, s);
+    s = dp4a_ss(wb.w, xb.w, s);
+    return s;
+}
+
+#ifndef ZK_GEMV_MIN_CTAS
+#define ZK_GEMV_MIN_CTAS 1
+#endif
 template <int kBatch, int kDigits>
-__global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 4 ? 2 : 1))
+__global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV_MIN_CTAS : 1))
     gemv_q8_0_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t kpad_blocks = p.nseg * kGemvSegBlocks;
@@ -105,13 +149,18 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 4 ? 2 : 1))
     volatile int* abort_word = reinterpret_cast<volatile int*>(empty + kGemvStages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    ZK_STAMP(0);
     uint32_t r_first, r_last;
     cta_row_slice(p.total_rows, blockIdx.x, gridDim.x, r_first, r_last);
+    // A group of whole single-segment rows is contiguous in both planes: one copy each.
+    const bool contiguous = p.nseg == 1 && p.nb == p.nbp;
+    const uint32_t cstride = contiguous ? p.nb * 32 : kGemvSegBlocks * 32;  // stage row pitch of the codes, bytes
+    const uint32_t sstride = contiguous ? p.nb : kGemvSegBlocks;             // stage row pitch of the scales, halves
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemvStages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kGemvWarps);
+            mbar_init(&empty[s], kTeamWarps);
         }
         *abort_word = 0;
         mbar_fence_init();
@@ -122,35 +171,68 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 4 ? 2 : 1))
 
     if (warp == kGemvWarps) {
         // ---------------- producer warp: weights are constants, no need to wait for the previous grid ----------------
+        if (lane == 0) {
+            // Pull what the ring cannot hold yet into L2, so later refills do not pay DRAM latency.
+            const uint32_t ring_rows = kGemvStages * kTeamWarps / p.nseg;
+            uint32_t budget = kL2PrefetchCap;
+            GroupWalk pre(r_first + min(ring_rows, r_last - r_first), r_last);
+            while (!pre.done() && budget) {
+                const RowGroup g = pre.next(p);
+                const GemvTask& t = p.task[g.task];
+                const uint32_t cb = min(g.nrows * p.K, budget);
+                l2_prefetch(t.codes + static_cast<size_t>(g.row0) * p.K, (cb + 15) & ~15u);
+                l2_prefetch(t.scales + static_cast<size_t>(g.row0) * p.nbp, (g.nrows * p.nbp * 2 + 15) & ~15u);
+                budget -= cb;
+            }
+        }
         uint32_t unit = 0;
         bool ok = true;
         GroupWalk walk(r_first, r_last);
         while (!walk.done() && ok) {
-            uint32_t row0, nrows;
-            const GemvTask& t = p.task[walk.next(p, row0, nrows)];
-            for (uint32_t s = 0; s < p.nseg && ok; ++s, ++unit) {
-                const uint32_t stage = unit % kGemvStages;
-                if (unit >= kGemvStages) {
-                    if (!mbar_wait(&empty[stage], ((unit / kGemvStages) - 1) & 1)) {
-                        if (lane == 0) { *abort_word = 1; atomicExch(p.error_word, kErrEmptyWaitTimeout); }
-                        ok = false;
+            RowGroup pair[kTeams];
+#pragma unroll
+            for (int m = 0; m < kTeams; ++m) pair[m] = walk.next(p);
+            for (uint32_t s = 0; s < p.nseg && ok; ++s) {
+#pragma unroll
+                for (int m = 0; m < kTeams; ++m, ++unit) {
+                    const uint32_t stage = unit % kGemvStages;
+                    if (unit >= kGemvStages) {
+                        if (!mbar_wait(&empty[stage], ((unit / kGemvStages) - 1) & 1)) {
+                            if (lane == 0) { *abort_word = 1; atomicExch(p.error_word, kErrEmptyWaitTimeout); }
+                            ok = false;
+                        }
                     }
-                }
-                if (*abort_word) ok = false;
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                const uint32_t nblk = min(static_cast<uint32_t>(kGemvSegBlocks), p.nb - s * kGemvSegBlocks);
-                const uint32_t cbytes = nblk * 32, sbytes = (nblk * 2 + 15) & ~15u;
-                uint8_t* st = ring + stage * kQ8StageBytes;
-                if (lane == 0) mbar_arrive_expect_tx(&full[stage], nrows * (cbytes + sbytes));
-                __syncwarp();
-                if (lane < static_cast<int>(nrows)) {
-                    bulk_g2s(st + lane * (kGemvSegBlocks * 32),
-                             t.codes + static_cast<size_t>(row0 + lane) * p.K + static_cast<size_t>(s) * kGemvSegBlocks * 32, cbytes, &full[stage]);
-                } else if (lane >= 16 && lane < 16 + static_cast<int>(nrows)) {
-                    const int r = lane - 16;
-                    bulk_g2s(st + kQ8StageCodeBytes + r * (kGemvSegBlocks * 2),
-                             t.scales + static_cast<size_t>(row0 + r) * p.nbp + static_cast<size_t>(s) * kGemvSegBlocks, sbytes, &full[stage]);
+                    if (*abort_word) ok = false;
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    const RowGroup g = pair[m];  // m is a compile-time index (unrolled)
+                    if (g.nrows == 0) {  // the odd tail of a pair: an empty unit keeps the ring order fixed
+                        if (lane == 0) mbar_arrive(&full[stage]);
+                        continue;
+                    }
+                    const GemvTask& t = p.task[g.task];
+                    uint8_t* st = ring + stage * kQ8StageBytes;
+                    if (contiguous) {
+                        const uint32_t cbytes = g.nrows * p.K, sbytes = g.nrows * p.nb * 2;
+                        if (lane == 0) {
+                            mbar_arrive_expect_tx(&full[stage], cbytes + sbytes);
+                            bulk_g2s(st, t.codes + static_cast<size_t>(g.row0) * p.K, cbytes, &full[stage]);
+                            bulk_g2s(st + kQ8StageCodeBytes, t.scales + static_cast<size_t>(g.row0) * p.nbp, sbytes, &full[stage]);
+                        }
+                    } else {
+                        const uint32_t nblk = min(static_cast<uint32_t>(kGemvSegBlocks), p.nb - s * kGemvSegBlocks);
+                        const uint32_t cbytes = nblk * 32, sbytes = (nblk * 2 + 15) & ~15u;
+                        if (lane == 0) mbar_arrive_expect_tx(&full[stage], g.nrows * (cbytes + sbytes));
+                        __syncwarp();
+                        if (lane < static_cast<int>(g.nrows)) {
+                            bulk_g2s(st + lane * (kGemvSegBlocks * 32),
+                                     t.codes + static_cast<size_t>(g.row0 + lane) * p.K + static_cast<size_t>(s) * kGemvSegBlocks * 32, cbytes, &full[stage]);
+                        } else if (lane >= 16 && lane < 16 + static_cast<int>(g.nrows)) {
+                            const int r = lane - 16;
+                            bulk_g2s(st + kQ8StageCodeBytes + r * (kGemvSegBlocks * 2),
+                                     t.scales + static_cast<size_t>(g.row0 + r) * p.nbp + static_cast<size_t>(s) * kGemvSegBlocks, sbytes, &full[stage]);
+                        }
+                    }
                 }
             }
         }
@@ -169,11 +251,12 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 4 ? 2 : 1))
     // ---------------- consumer warps ----------------
     // The activations (and the output buffers) belong to the stream's earlier work: wait for it.
     pdl_wait();
-    // Prologue: quantise the activations into the lane-major layout.  Block b = 64*s + 32*i + l is
-    // read by lane l; its two 16-byte halves are stored in the order that lane loads them
-    // (half ((l>>2)&1) first), which keeps both the weight and the activation loads conflict-free.
-    // Four lanes share a block (eight consecutive elements each), so one pass of the eight warps
-    // covers 64 blocks with two 128-bit loads per lane and the whole vector in a few passes.
+    ZK_STAMP(1);
+    // Prologue: quantise the activations into the lane-major layout.  Block b = 32*g + l is read by
+    // lane l; its two 16-byte halves are stored in the order that lane loads them (half ((l>>2)&1)
+    // first), which keeps both the weight and the activation loads conflict-free.
+    // Four lanes share a block (eight consecutive elements each), so one pass of the consumer warps
+    // covers 128 blocks with two 128-bit loads per lane: one pass for K = 4096.
     {
         const uint32_t quad = static_cast<uint32_t>(lane) >> 2, part = static_cast<uint32_t>(lane) & 3;
         for (int t = 0; t < kBatch; ++t) {
@@ -187,7 +270,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 4 ? 2 : 1))
                 uint2 c1, c2;
                 const float d = quantise_block_quad(v, c1, c2);
                 if (!live) continue;
-                const uint32_t l = b & 31, grp = b >> 5;  // grp == 2*s + i
+                const uint32_t l = b & 31, grp = b >> 5;
                 const uint32_t hh = (part >> 1) ^ ((l >> 2) & 1);
                 const size_t slot = (static_cast<size_t>(grp) * 2 + hh) * 32 + l;  // uint4 index
                 uint2* dst = reinterpret_cast<uint2*>(xcodes + (static_cast<size_t>(t) * kDigits) * kpad_blocks * 2 + slot) + (part & 1);
@@ -197,75 +280,108 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 4 ? 2 : 1))
             }
         }
     }
+    ZK_STAMP(2);
     // consumer-only barrier (the producer warp is already streaming)
     asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");
+    ZK_STAMP(3);
 
-    uint32_t unit = 0;
+    const int team = warp / kTeamWarps, twarp = warp % kTeamWarps;
     bool ok = true;
     const uint32_t h0 = (static_cast<uint32_t>(lane) >> 2) & 1;
+
+    // Batch-1 int8 rows of one segment (K <= 4096): a lane meets the same four activation blocks in
+    // every row, so they live in registers and the inner loop reads only weights.
+    constexpr bool kCanHoldX = (kBatch == 1 && kDigits == 1);
+    const bool x_in_regs = kCanHoldX && p.nseg == 1;
+    uint4 xra[kCanHoldX ? kLaneBlocks : 1], xrb[kCanHoldX ? kLaneBlocks : 1];
+    float xrs[kCanHoldX ? kLaneBlocks : 1];
+    if (x_in_regs) {
+#pragma unroll
+        for (int j = 0; j < kLaneBlocks; ++j) {
+            const uint32_t b = j * 32 + lane;
+            const bool live = b < p.nb;
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            xra[j] = live ? xcodes[static_cast<size_t>(j) * 64 + lane] : z;
+            xrb[j] = live ? xcodes[static_cast<size_t>(j) * 64 + 32 + lane] : z;
+            xrs[j] = live ? xscale[b] : 0.0f;
+        }
+    }
+    ZK_STAMP(4);
+
+    uint32_t pair_base = 0;  // unit index of the current pair's first unit
     GroupWalk walk(r_first, r_last);
     while (!walk.done() && ok) {
-        uint32_t row0, nrows;
-        const GemvTask& t = p.task[walk.next(p, row0, nrows)];
-        const uint32_t row = row0 + warp;
-        const bool valid = static_cast<uint32_t>(warp) < nrows;
+        RowGroup pair[kTeams];
+#pragma unroll
+        for (int m = 0; m < kTeams; ++m) pair[m] = walk.next(p);
+        const RowGroup g = team == 0 ? pair[0] : pair[1];  // no runtime-indexed local array
+        const GemvTask& t = p.task[g.task];
+        const uint32_t row = g.row0 + twarp;
+        const bool valid = static_cast<uint32_t>(twarp) < g.nrows;
         float acc[kBatch];
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) acc[b] = 0.0f;
 
-        for (uint32_t s = 0; s < p.nseg; ++s, ++unit) {
+        for (uint32_t s = 0; s < p.nseg; ++s) {
+            const uint32_t unit = pair_base + s * kTeams + team;
             const uint32_t stage = unit % kGemvStages;
             if (*abort_word || !mbar_wait(&full[stage], (unit / kGemvStages) & 1)) {
                 if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrFullWaitTimeout); }
                 ok = false;
                 break;
             }
+#ifdef ZK_TRACE
+            if (team == 0 && unit < 4) ZK_STAMP(5 + 3 * (unit >> 1));
+#endif
             if (valid) {
                 const uint8_t* st = ring + stage * kQ8StageBytes;
-                const uint4* wq = reinterpret_cast<const uint4*>(st + warp * (kGemvSegBlocks * 32));
-                const __half* ws = reinterpret_cast<const __half*>(st + kQ8StageCodeBytes + warp * (kGemvSegBlocks * 2));
+                const uint4* wq = reinterpret_cast<const uint4*>(st + twarp * cstride);
+                const __half* ws = reinterpret_cast<const __half*>(st + kQ8StageCodeBytes) + twarp * sstride;
+                if (x_in_regs) {
 #pragma unroll
-                for (int i = 0; i < kGemvSegBlocks / 32; ++i) {
-                    const uint32_t bl = i * 32 + lane;           // block within the segment
-                    const uint32_t b = s * kGemvSegBlocks + bl;  // block within the row
-                    if (b < p.nb) {
+                    for (int i = 0; i < kLaneBlocks; ++i) {
+                        const uint32_t bl = i * 32 + lane;
+                        // A lane whose block index is past the row holds zero codes; the bytes it reads are
+                        // stale but inside the stage, and its term is dropped by selection (stale scale bits
+                        // may be NaN, so it must not be multiplied away).
                         const uint4 wa = wq[bl * 2 + h0], wb = wq[bl * 2 + (h0 ^ 1)];
                         const float dw = __half2float(ws[bl]);
-                        const size_t slot = (static_cast<size_t>(b >> 5) * 2) * 32 + lane;
+                        const int isum = dot32(wa, wb, xra[i], xrb[i]);
+                        const float term = (dw * xrs[i]) * static_cast<float>(isum);
+                        acc[0] += bl < p.nb ? term : 0.0f;
+                    }
+                } else {
 #pragma unroll
-                        for (int tk = 0; tk < kBatch; ++tk) {
-                            const uint4* xc = xcodes + (static_cast<size_t>(tk) * kDigits) * kpad_blocks * 2 + slot;
-                            const uint4 xa = xc[0], xb = xc[32];
-                            int isum = dp4a_ss(wa.x, xa.x, 0);
-                            isum = dp4a_ss(wa.y, xa.y, isum);
-                            isum = dp4a_ss(wa.z, xa.z, isum);
-                            isum = dp4a_ss(wa.w, xa.w, isum);
-                            isum = dp4a_ss(wb.x, xb.x, isum);
-                            isum = dp4a_ss(wb.y, xb.y, isum);
-                            isum = dp4a_ss(wb.z, xb.z, isum);
-                            isum = dp4a_ss(wb.w, xb.w, isum);
-                            if (kDigits == 2) {
-                                const uint4 ya = xc[kpad_blocks * 2], yb = xc[kpad_blocks * 2 + 32];
-                                int lo = dp4a_ss(wa.x, ya.x, 0);
-                                lo = dp4a_ss(wa.y, ya.y, lo);
-                                lo = dp4a_ss(wa.z, ya.z, lo);
-                                lo = dp4a_ss(wa.w, ya.w, lo);
-                                lo = dp4a_ss(wb.x, yb.x, lo);
-                                lo = dp4a_ss(wb.y, yb.y, lo);
-                                lo = dp4a_ss(wb.z, yb.z, lo);
-                                lo = dp4a_ss(wb.w, yb.w, lo);
-                                isum = isum * 256 + lo;
+                    for (int i = 0; i < kLaneBlocks; ++i) {
+                        const uint32_t bl = i * 32 + lane;           // block within the segment
+                        const uint32_t b = s * kGemvSegBlocks + bl;  // block within the row
+                        if (b < p.nb) {
+                            const uint4 wa = wq[bl * 2 + h0], wb = wq[bl * 2 + (h0 ^ 1)];
+                            const float dw = __half2float(ws[bl]);
+                            const size_t slot = (static_cast<size_t>(b >> 5) * 2) * 32 + lane;
+#pragma unroll
+                            for (int tk = 0; tk < kBatch; ++tk) {
+                                const uint4* xc = xcodes + (static_cast<size_t>(tk) * kDigits) * kpad_blocks * 2 + slot;
+                                int isum = dot32(wa, wb, xc[0], xc[32]);
+                                if (kDigits == 2) isum = isum * 256 + dot32(wa, wb, xc[kpad_blocks * 2], xc[kpad_blocks * 2 + 32]);
+                                const float dx = xscale[static_cast<size_t>(tk) * kpad_blocks + b];
+                                acc[tk] = fmaf(dw * dx, static_cast<float>(isum), acc[tk]);
                             }
-                            const float dx = xscale[static_cast<size_t>(tk) * kpad_blocks + b];
-                            acc[tk] = fmaf(dw * dx, static_cast<float>(isum), acc[tk]);
                         }
                     }
                 }
             }
+#ifdef ZK_TRACE
+            if (team == 0 && unit < 4) { if (acc[0] == 123.456f) p.trace[0] = 1; ZK_STAMP(6 + 3 * (unit >> 1)); }
+#endif
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);
         }
         if (!ok) break;
+#ifdef ZK_TRACE
+        const uint32_t traced_unit = pair_base;
+#endif
+        pair_base += kTeams * p.nseg;
         if (valid) {
 #pragma unroll
             for (int tk = 0; tk < kBatch; ++tk) {
@@ -275,7 +391,11 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits <= 4 ? 2 : 1))
                 if (lane == 0) t.y[static_cast<size_t>(tk) * t.rows + row] = v;
             }
         }
+#ifdef ZK_TRACE
+        if (team == 0 && traced_unit < 4) ZK_STAMP(7 + 3 * (traced_unit >> 1));
+#endif
     }
+    ZK_STAMP(12);
 }
 
 }  // namespace zk

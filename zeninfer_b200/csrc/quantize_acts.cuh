@@ -19,14 +19,11 @@
 
 namespace zk {
 
-// Exact for |v| <= 2^23: truncation and the remainder are both representable.
+// lround() for |v| < 2^22: add half a unit with the sign of v, rounding toward zero, then
+// truncate.  Rounding the sum toward zero can never carry it across an integer (integers in
+// this range are representable), so floor(|v| + 0.5) is exact: 0.49999997 -> 0, 2.5 -> 3, -2.5 -> -3.
 __device__ __forceinline__ int round_half_away(float v) {
-    const float t = truncf(v);
-    const float f = __fsub_rn(v, t);
-    int q = __float2int_rz(t);
-    if (f >= 0.5f) ++q;
-    else if (f <= -0.5f) --q;
-    return q;
+    return __float2int_rz(__fadd_rz(v, copysignf(0.5f, v)));
 }
 
 __device__ __forceinline__ float clamp127(float v) { return v > 127.0f ? 127.0f : (v < -127.0f ? -127.0f : v); }

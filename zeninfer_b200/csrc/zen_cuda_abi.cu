@@ -245,6 +245,11 @@ zen_cuda_weights* lookup_locked(State& s, int fmt, const uint8_t* host, size_t r
     return w;
 }
 
+#ifdef ZK_TRACE
+unsigned long long* g_trace = nullptr;  // profiling builds: device buffer [launch][148][8]
+size_t g_trace_launch = 0;
+#endif
+
 template <int kBatch, int kDigits>
 cudaError_t launch_gemv_q8_0(const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
     auto* fn = &zk::gemv_q8_0_kernel<kBatch, kDigits>;
@@ -308,6 +313,9 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
     p.nbp = w[0]->nbp;
     p.nseg = (p.nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks;
     p.error_word = s.d_error;
+#ifdef ZK_TRACE
+    p.trace = g_trace ? g_trace + (g_trace_launch++) * 148 * 16 : nullptr;
+#endif
     const int digits = act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1;
     const size_t smem = zk::gemv_q8_0_smem_bytes(p.nseg, static_cast<int>(tokens), digits);
     if (smem > s.smem_optin) return set_error(s, "gemv: activation rows do not fit shared memory (columns x tokens too large)");
@@ -614,5 +622,9 @@ int zen_cuda_dev_check(void* stream) {
     *s.h_error = 0;
     return code;
 }
+
+#ifdef ZK_TRACE
+__attribute__((visibility("default"))) void zen_cuda_debug_trace(void* dev, size_t start) { g_trace = static_cast<unsigned long long*>(dev); g_trace_launch = start; }
+#endif
 
 }  // extern "C"
