@@ -50,3 +50,42 @@ def assert_parity(got, ref, tol: float = 1e-3, what: str = "") -> float:
     assert rel <= tol, f"{what}: max_abs/max_ref = {rel:.3e} > {tol}"
     assert np.all(err <= tol * np.maximum(1.0, np.abs(ref))), f"{what}: per-element gate failed, worst {err.max():.3e}"
     return rel
+
+
+class Q6KFixture:
+    """tests/q6k_gemm_tests.cpp:11-45: Q6_K blocks built from known codes and scales, one shared LCG."""
+
+    def __init__(self):
+        self.state = 0x7136A95B
+
+    def u32(self):
+        self.state = (self.state * 1664525 + 1013904223) & 0xFFFFFFFF
+        return self.state
+
+    def weights(self, rows, cols):
+        halves = [0x3400, 0xB800, 0x0001, 0x3C00]
+        factors = [np.float32(0.25), np.float32(-0.5), np.float32(2.0 ** -24), np.float32(1.0)]
+        nb = cols // 256
+        packed = np.zeros((rows, nb, 210), np.uint8)
+        expected = np.zeros((rows, cols), np.float32)
+        for r in range(rows):
+            for b in range(nb):
+                p = packed[r, b]
+                di = (r + b) % 4
+                p[208], p[209] = halves[di] & 255, halves[di] >> 8
+                scales = []
+                for i in range(16):
+                    s = (self.u32() >> 24) % 31 - 15
+                    scales.append(s)
+                    p[192 + i] = np.int8(s).view(np.uint8)
+                for half in range(2):
+                    for l in range(32):
+                        q = []
+                        for group in range(4):
+                            q.append(self.u32() >> 26)
+                            col = b * 256 + half * 128 + group * 32 + l
+                            expected[r, col] = factors[di] * np.float32(scales[half * 8 + group * 2 + l // 16]) * np.float32(q[group] - 32)
+                        p[half * 64 + l] = (q[0] & 15) | ((q[2] & 15) << 4)
+                        p[half * 64 + 32 + l] = (q[1] & 15) | ((q[3] & 15) << 4)
+                        p[128 + half * 32 + l] = (q[0] >> 4) | ((q[1] >> 4) << 2) | ((q[2] >> 4) << 4) | ((q[3] >> 4) << 6)
+        return packed, expected

@@ -1,0 +1,129 @@
+"""GPU parity for the Q4_0 and Q6_K decode paths, through the C-ABI.
+
+The reference computes both formats with fp32 activations (Q4_0: dequantise the row, then a fp32 dot,
+src/quant.cpp:1135-1162; Q6_K: gemv_q6k_avx2 / gemm_q6k_kblk_avx2), so the oracle here is always the
+fp32-activation one.  Bar: 1e-3 under both gates of helpers.assert_parity; the integer kernels land near 1e-5.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from helpers import Q6KFixture as _Q6KFixture
+from helpers import assert_parity, ref_fp32_f64, seeded_acts, seeded_weights
+from conftest import lcg_bytes
+from zeninfer_b200 import blocks
+
+pytestmark = pytest.mark.gpu
+Q4_0, Q6_K = blocks.Q4_0, blocks.Q6_K
+NAMES = {Q4_0: "Q4_0", Q6_K: "Q6_K"}
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "ref_vectors.npz")
+
+
+@pytest.fixture(scope="module")
+def be():
+    from zeninfer_b200 import Backend
+    return Backend()
+
+
+@pytest.fixture(scope="module")
+def golden():
+    with np.load(GOLDEN) as g:
+        return {k: g[k] for k in g.files}
+
+
+@pytest.mark.parametrize("fmt,key", [(Q4_0, "q4_0"), (Q6_K, "q6_k")])
+def test_against_reference_golden(be, golden, fmt, key):
+    w = np.ascontiguousarray(golden[f"{key}_w"])
+    x = golden[f"{key}_x"]
+    assert_parity(be.gemv(NAMES[fmt], w, x[0], 37, 768), golden[f"{key}_gemv_y"], what=f"golden {key} gemv")
+    assert_parity(be.gemm(NAMES[fmt], w, x, 5, 37, 768), golden[f"{key}_gemm_y"], what=f"golden {key} gemm")
+    be.release_weights(w)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 32), (3, 96), (5, 256), (67, 544), (130, 2048), (512, 4096), (1024, 4096), (64, 14336)])
+def test_q4_0_gemv_vs_oracle(be, zo, rows, cols):
+    w = seeded_weights(Q4_0, rows, cols, 110 + rows)
+    x = seeded_acts(1, cols, 120 + cols)[0]
+    rel = assert_parity(be.gemv("Q4_0", w, x, rows, cols), zo.gemv(Q4_0, w, x, rows, cols), what=f"Q4_0 gemv {rows}x{cols}")
+    assert rel < 1e-4
+    be.release_weights(w)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 256), (3, 512), (5, 768), (67, 1280), (512, 4096), (1024, 4096), (64, 14336)])
+def test_q6_k_gemv_vs_oracle(be, zo, rows, cols):
+    w = seeded_weights(Q6_K, rows, cols, 130 + rows)
+    x = seeded_acts(1, cols, 140 + cols)[0]
+    rel = assert_parity(be.gemv("Q6_K", w, x, rows, cols), zo.gemv(Q6_K, w, x, rows, cols), what=f"Q6_K gemv {rows}x{cols}")
+    assert rel < 1e-4
+    be.release_weights(w)
+
+
+@pytest.mark.parametrize("fmt", [Q4_0, Q6_K])
+@pytest.mark.parametrize("tokens", [2, 3, 5, 8, 9, 17])
+def test_small_batch_vs_oracle(be, zo, fmt, tokens):
+    rows, cols = 100, 768
+    w = seeded_weights(fmt, rows, cols, 150 + fmt)
+    x = seeded_acts(tokens, cols, 160 + tokens)
+    assert_parity(be.gemm(NAMES[fmt], w, x, tokens, rows, cols), zo.gemm(fmt, w, x, tokens, rows, cols), what=f"{NAMES[fmt]} T={tokens}")
+    be.release_weights(w)
+
+
+def test_q6_k_constructed_blocks(be):
+    # tests/q6k_gemm_tests.cpp:16-45: blocks built from known codes and scales, expected weights computed
+    # without any decoder; gate 2e-5 * max(1, sum|terms|)
+    fx = _Q6KFixture()
+    for cols in (256, 512, 1280):
+        for rows in (1, 3, 5, 35):
+            packed, expected = fx.weights(rows, cols)
+            packed = np.ascontiguousarray(packed.reshape(rows, -1))
+            for tokens in (1, 2, 5):
+                x = np.array([(float((fx.u32() >> 24) - 128) / 128.0) for _ in range(tokens * cols)], np.float32).reshape(tokens, cols)
+                terms = expected.astype(np.float64)[None, :, :] * x.astype(np.float64)[:, None, :]
+                ref, mag = terms.sum(axis=2), np.abs(terms).sum(axis=2)
+                got = be.gemm("Q6_K", packed, x, tokens, rows, cols)
+                assert np.all(np.abs(got - ref) <= 2e-5 * np.maximum(1.0, mag)), (cols, rows, tokens)
+            be.release_weights(packed)
+
+
+@pytest.mark.parametrize("fmt", [Q4_0, Q6_K])
+def test_all_format_sweep_fixture(be, zo, fmt):
+    # tests/cpu_quant_sweep_tests.cpp:12-50 over tests/support/quant_fixture.h: random block bytes (LCG 1729),
+    # every nibble / 6-bit code / int8 scale value occurs
+    for cols in (256, 768):
+        for rows in (1, 5, 67):
+            rb = blocks.row_bytes(fmt, cols)
+            w = lcg_bytes(1729, rows * rb).reshape(rows, cols // blocks.BLOCK_ELEMENTS[fmt], blocks.BLOCK_BYTES[fmt]).copy()
+            at = 208 if fmt == Q6_K else 0
+            w[..., at], w[..., at + 1] = 0, 0x30
+            w = np.ascontiguousarray(w.reshape(rows, -1))
+            decoded = zo.dequantize(fmt, w, rows * cols).reshape(rows, cols).astype(np.float64)
+            x = (((np.arange(8 * cols) * 37 + 11) % 101 - 50) / 64.0).astype(np.float32).reshape(8, cols)
+            for tokens in (1, 3, 8):
+                terms = decoded[None] * x[:tokens].astype(np.float64)[:, None, :]
+                ref, mag = terms.sum(axis=2), np.abs(terms).sum(axis=2)
+                got = be.gemm(NAMES[fmt], w, x[:tokens], tokens, rows, cols)
+                assert np.all(np.abs(got - ref) <= 2e-5 * np.maximum(1.0, mag)), (cols, rows, tokens)
+            be.release_weights(w)
+
+
+@pytest.mark.parametrize("fmt", [Q4_0, Q6_K])
+def test_layer_shapes_full_size(be, fmt):
+    # one Llama-3-8B layer (seed 4): q/o 4096x4096, k/v 1024x4096, gate/up 14336x4096, down 4096x14336
+    for i, (rows, cols) in enumerate(((4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336))):
+        w = seeded_weights(fmt, rows, cols, 4 + 10 * i)
+        x = seeded_acts(1, cols, 4 + 10 * i + 1)
+        y = be.gemv(NAMES[fmt], w, x[0], rows, cols)
+        rel = assert_parity(y, ref_fp32_f64(fmt, w, x, rows, cols)[0], what=f"{NAMES[fmt]} {rows}x{cols}")
+        assert rel < 1e-4  # max_abs/max_ref; two activation digits leave ~2e-5
+        be.release_weights(w)
+
+
+def test_int8_mode_is_q8_0_only(be):
+    from zeninfer_b200 import BackendError
+    from zeninfer_b200.backend import ACT_INT8
+    w = seeded_weights(Q4_0, 16, 256, 170)
+    h = be.dev_upload("Q4_0", w, 16, 256)
+    with pytest.raises(BackendError):
+        be.dev_gemv([h], [1], 1, 1, ACT_INT8)  # rejected on the host before any pointer is touched
+    be.dev_free(h)

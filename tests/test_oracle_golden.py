@@ -13,6 +13,7 @@ import numpy as np
 import pytest
 
 from conftest import lcg_bytes
+from helpers import Q6KFixture as _Q6KFixture
 from zeninfer_b200 import blocks
 
 Q8_0, Q4_0, Q6_K = blocks.Q8_0, blocks.Q4_0, blocks.Q6_K
@@ -128,45 +129,6 @@ def test_q8_0_kblk_sweep(zo, cols, rows):
             err = np.abs(out.astype(np.float64) - expect)
             i = np.unravel_index(err.argmax(), err.shape)
             assert err[i] <= 1.5e-3 * max(1.0, abs(expect[i]))
-
-
-class _Q6KFixture:
-    """tests/q6k_gemm_tests.cpp:11-45: Q6_K blocks built from known codes and scales, one shared LCG."""
-
-    def __init__(self):
-        self.state = 0x7136A95B
-
-    def u32(self):
-        self.state = (self.state * 1664525 + 1013904223) & 0xFFFFFFFF
-        return self.state
-
-    def weights(self, rows, cols):
-        halves = [0x3400, 0xB800, 0x0001, 0x3C00]
-        factors = [np.float32(0.25), np.float32(-0.5), np.float32(2.0 ** -24), np.float32(1.0)]
-        nb = cols // 256
-        packed = np.zeros((rows, nb, 210), np.uint8)
-        expected = np.zeros((rows, cols), np.float32)
-        for r in range(rows):
-            for b in range(nb):
-                p = packed[r, b]
-                di = (r + b) % 4
-                p[208], p[209] = halves[di] & 255, halves[di] >> 8
-                scales = []
-                for i in range(16):
-                    s = (self.u32() >> 24) % 31 - 15
-                    scales.append(s)
-                    p[192 + i] = np.int8(s).view(np.uint8)
-                for half in range(2):
-                    for l in range(32):
-                        q = []
-                        for group in range(4):
-                            q.append(self.u32() >> 26)
-                            col = b * 256 + half * 128 + group * 32 + l
-                            expected[r, col] = factors[di] * np.float32(scales[half * 8 + group * 2 + l // 16]) * np.float32(q[group] - 32)
-                        p[half * 64 + l] = (q[0] & 15) | ((q[2] & 15) << 4)
-                        p[half * 64 + 32 + l] = (q[1] & 15) | ((q[3] & 15) << 4)
-                        p[128 + half * 32 + l] = (q[0] >> 4) | ((q[1] >> 4) << 2) | ((q[2] >> 4) << 4) | ((q[3] >> 4) << 6)
-        return packed, expected
 
 
 def test_q6_k_constructed_blocks(zo):

@@ -1,0 +1,334 @@
+// Decode-time matrix-vector products for Q4_0 and Q6_K (batch 1..8).
+//
+// The reference evaluates both formats with fp32 activations: Q4_0 through its generic
+// dequantise-then-dot route (src/quant.cpp:1135-1162 over gemv_avx2, kernels/avx2.cpp:16-40) and
+// Q6_K through gemv_q6k_avx2 / gemm_q6k_kblk_avx2 (kernels/avx2.cpp:380-422, :1762-1770).  Decoding
+// every weight to fp32 costs several ALU operations per weight, more than an SM can issue at HBM
+// speed, so the dot products here stay in integers: weights are used as the small integers they
+// are, and each activation enters as two int8 digits, x ~= (d/256) * (256*q1 + q2) with an error
+// below d/512 (quantize_acts.cuh).  Results agree with the fp32-activation reference to ~1e-5.
+//
+//   Q4_0 : y += d_w * (d_x/256) * ( sum n*(256*q1+q2)  -  8 * sum(256*q1+q2) )      n = nibble 0..15
+//   Q6_K : y += d * sc_g * (d_x/256) * sum (q-32)*(256*q1+q2)                        per 16-weight group
+//
+// Same streaming skeleton as the Q8_0 kernel (gemv_q8_0.cuh): a persistent CTA per SM owns a
+// byte-balanced row slice, a producer warp feeds a ring of shared-memory stages with TMA bulk
+// copies, sixteen consumer warps in two teams own one row each.  Algorithmic traffic is the raw
+// GGUF size (18 B per Q4_0 block, 210 B per Q6_K super-block).
+#pragma once
+#include <cuda_fp16.h>
+
+#include "gemv_q8_0.cuh"
+
+namespace zk {
+
+constexpr int kKqSegElems = 4096;   // weights per row per stage segment (128 Q4_0 blocks, 16 Q6_K super-blocks)
+constexpr int kKqMaxPlanes = 4;
+
+// Per-format geometry of the planes a row is split into (repack.cuh).
+template <int kFormat> struct KqFormat;
+
+template <> struct KqFormat<2> {   // Q4_0: nibbles [K/2], f16 scales [K/32]
+    static constexpr int kPlanes = 2;
+    static constexpr int kStages = 5;
+    __host__ __device__ static constexpr uint32_t seg_bytes(int plane) { return plane == 0 ? kKqSegElems / 2 : kKqSegElems / 32 * 2; }
+    __host__ __device__ static constexpr uint32_t bytes_per_256(int plane) { return plane == 0 ? 128 : 16; }
+};
+template <> struct KqFormat<14> {  // Q6_K: ql [K/2], qh [K/4], int8 sc [K/16], f16 d [K/256]
+    static constexpr int kPlanes = 4;
+    static constexpr int kStages = 4;
+    __host__ __device__ static constexpr uint32_t seg_bytes(int plane) {
+        return plane == 0 ? kKqSegElems / 2 : plane == 1 ? kKqSegElems / 4 : plane == 2 ? kKqSegElems / 16 : kKqSegElems / 256 * 2;
+    }
+    __host__ __device__ static constexpr uint32_t bytes_per_256(int plane) { return plane == 0 ? 128 : plane == 1 ? 64 : plane == 2 ? 16 : 2; }
+};
+
+template <int kFormat> __host__ __device__ constexpr uint32_t kq_row_stage_bytes() {
+    uint32_t b = 0;
+    for (int i = 0; i < KqFormat<kFormat>::kPlanes; ++i) b += KqFormat<kFormat>::seg_bytes(i);
+    return b;
+}
+template <int kFormat> __host__ __device__ constexpr uint32_t kq_plane_offset(int plane) {  // within a stage
+    uint32_t b = 0;
+    for (int i = 0; i < plane; ++i) b += KqFormat<kFormat>::seg_bytes(i) * kTeamWarps;
+    return b;
+}
+template <int kFormat> __host__ __device__ constexpr uint32_t kq_stage_bytes() { return kq_row_stage_bytes<kFormat>() * kTeamWarps; }
+
+struct KqTask {
+    const uint8_t* plane[kKqMaxPlanes];
+    float* y;               // [batch][rows]
+    uint32_t rows;
+    uint32_t first_row;
+};
+
+struct KqParams {
+    KqTask task[kMaxTasks];
+    uint32_t ntasks, total_rows;
+    const float* x;         // [batch][K] fp32
+    uint32_t K;             // columns, a multiple of the format's block size
+    uint32_t nseg;          // ceil(K / kKqSegElems)
+    uint32_t pitch[kKqMaxPlanes];  // global row pitch of each plane, bytes
+    int* error_word;
+};
+
+template <int kFormat>
+__host__ __device__ inline size_t gemv_kq_smem_bytes(uint32_t nseg, int batch) {
+    const size_t kpad = static_cast<size_t>(nseg) * kKqSegElems;
+    return static_cast<size_t>(KqFormat<kFormat>::kStages) * kq_stage_bytes<kFormat>()
+           + static_cast<size_t>(batch) * 2 * kpad                 // two digit planes, natural order
+           + static_cast<size_t>(batch) * (kpad / 32) * 8          // per-block scale (d/256) and code sum
+           + 2 * KqFormat<kFormat>::kStages * 8 + 16;
+}
+
+struct KqWalk {  // GroupWalk over KqParams
+    uint32_t r, r_end, ti;
+    __device__ KqWalk(uint32_t first, uint32_t last) : r(first), r_end(last), ti(0) {}
+    __device__ bool done() const { return r >= r_end; }
+    __device__ RowGroup next(const KqParams& p) {
+        RowGroup g{0, 0, 0};
+        if (done()) return g;
+        while (r >= p.task[ti].first_row + p.task[ti].rows) ++ti;
+        g.task = ti;
+        g.row0 = r - p.task[ti].first_row;
+        g.nrows = min(min(static_cast<uint32_t>(kTeamWarps), p.task[ti].rows - g.row0), r_end - r);
+        r += g.nrows;
+        return g;
+    }
+};
+
+__device__ __forceinline__ int dot16(const uint4& w, const uint4& x) {
+    int s = dp4a_ss(w.x, x.x, 0);
+    s = dp4a_ss(w.y, x.y, s);
+    s = dp4a_ss(w.z, x.z, s);
+    return dp4a_ss(w.w, x.w, s);
+}
+
+// Bytes 0..63 minus 32, per byte, as signed bytes: setting the top bit first keeps the subtraction
+// from borrowing across bytes, flipping it back afterwards leaves the two's-complement difference.
+__device__ __forceinline__ uint32_t sub32_bytes(uint32_t q) { return ((q | 0x80808080u) - 0x20202020u) ^ 0x80808080u; }
+
+template <int kFormat, int kBatch>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_constant__ KqParams p) {
+    using F = KqFormat<kFormat>;
+    constexpr int kStages = F::kStages;
+    constexpr uint32_t kStageBytes = kq_stage_bytes<kFormat>();
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t kpad = p.nseg * kKqSegElems;
+    uint8_t* ring = smem;
+    uint8_t* xd = ring + kStages * kStageBytes;                                  // [batch][2][kpad] int8, natural order
+    float* xscale = reinterpret_cast<float*>(xd + static_cast<size_t>(kBatch) * 2 * kpad);   // [batch][kpad/32]  d/256
+    int* xsum = reinterpret_cast<int*>(xscale + static_cast<size_t>(kBatch) * (kpad / 32));  // [batch][kpad/32]  sum(256*q1+q2)
+    uint64_t* full = reinterpret_cast<uint64_t*>(xsum + static_cast<size_t>(kBatch) * (kpad / 32));
+    uint64_t* empty = full + kStages;
+    volatile int* abort_word = reinterpret_cast<volatile int*>(empty + kStages);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t r_first, r_last;
+    cta_row_slice(p.total_rows, blockIdx.x, gridDim.x, r_first, r_last);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kTeamWarps);
+        }
+        *abort_word = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == kGemvWarps) {
+        // ---------------- producer warp ----------------
+        uint32_t unit = 0;
+        bool ok = true;
+        KqWalk walk(r_first, r_last);
+        const int my_row = lane / F::kPlanes, my_plane = lane % F::kPlanes;  // one copy per (row, plane) of a unit
+        while (!walk.done() && ok) {
+            RowGroup pair[kTeams];
+#pragma unroll
+            for (int m = 0; m < kTeams; ++m) pair[m] = walk.next(p);
+            for (uint32_t s = 0; s < p.nseg && ok; ++s) {
+#pragma unroll
+                for (int m = 0; m < kTeams; ++m, ++unit) {
+                    const uint32_t stage = unit % kStages;
+                    if (unit >= static_cast<uint32_t>(kStages)) {
+                        if (!mbar_wait(&empty[stage], ((unit / kStages) - 1) & 1)) {
+                            if (lane == 0) { *abort_word = 1; atomicExch(p.error_word, kErrEmptyWaitTimeout); }
+                            ok = false;
+                        }
+                    }
+                    if (*abort_word) ok = false;
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    const RowGroup g = pair[m];
+                    if (g.nrows == 0) {
+                        if (lane == 0) mbar_arrive(&full[stage]);
+                        continue;
+                    }
+                    const KqTask& t = p.task[g.task];
+                    const uint32_t elems = min(static_cast<uint32_t>(kKqSegElems), p.K - s * kKqSegElems);  // multiple of the block size
+                    uint32_t row_bytes = 0;
+#pragma unroll
+                    for (int pl = 0; pl < F::kPlanes; ++pl) row_bytes += (elems / 256 * F::bytes_per_256(pl) + (elems % 256) * F::bytes_per_256(pl) / 256 + 15) & ~15u;
+                    if (lane == 0) mbar_arrive_expect_tx(&full[stage], g.nrows * row_bytes);
+                    __syncwarp();
+                    if (my_row < static_cast<int>(g.nrows) && my_row < kTeamWarps) {
+                        const uint32_t per256 = F::bytes_per_256(my_plane);
+                        const uint32_t bytes = (elems / 256 * per256 + (elems % 256) * per256 / 256 + 15) & ~15u;
+                        const uint32_t seg_off = static_cast<uint32_t>(static_cast<uint64_t>(s) * kKqSegElems / 256 * per256);
+                        uint8_t* dst = ring + stage * kStageBytes + kq_plane_offset<kFormat>(my_plane) + my_row * F::seg_bytes(my_plane);
+                        bulk_g2s(dst, t.plane[my_plane] + static_cast<size_t>(g.row0 + my_row) * p.pitch[my_plane] + seg_off, bytes, &full[stage]);
+                    }
+                }
+            }
+        }
+        if (lane == 0) {
+            const uint32_t armed = unit < static_cast<uint32_t>(kStages) ? unit : kStages;
+            for (uint32_t k = 0; k < armed; ++k) {
+                const uint32_t u = unit - 1 - k;
+                if (!mbar_wait(&full[u % kStages], (u / kStages) & 1)) atomicExch(p.error_word, kErrDrainTimeout);
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumer warps ----------------
+    pdl_wait();
+    // Prologue: two-digit quantisation of the activations, natural element order.
+    {
+        const uint32_t quad = static_cast<uint32_t>(lane) >> 2, part = static_cast<uint32_t>(lane) & 3;
+        const uint32_t nblk = p.K / 32;
+        for (int t = 0; t < kBatch; ++t) {
+            for (uint32_t b0 = warp * 8; b0 < nblk; b0 += kGemvWarps * 8) {
+                const uint32_t b = b0 + quad;
+                const bool live = b < nblk;
+                const float4* src = reinterpret_cast<const float4*>(p.x + static_cast<size_t>(t) * p.K + b * 32 + part * 8);
+                const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 lo = live ? __ldg(src) : zero, hi = live ? __ldg(src + 1) : zero;
+                const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                uint2 c1, c2;
+                const float d = quantise_block_quad(v, c1, c2);
+                // sum of the eight two-digit codes of this lane, then of the block's four lanes
+                int sum = dp4a_ss(c1.x, 0x01010101u, 0) + dp4a_ss(c1.y, 0x01010101u, 0);
+                sum = sum * 256 + dp4a_ss(c2.x, 0x01010101u, 0) + dp4a_ss(c2.y, 0x01010101u, 0);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                if (!live) continue;
+                uint8_t* base = xd + static_cast<size_t>(t) * 2 * kpad + b * 32 + part * 8;
+                *reinterpret_cast<uint2*>(base) = c1;
+                *reinterpret_cast<uint2*>(base + kpad) = c2;
+                if (part == 0) {
+                    xscale[static_cast<size_t>(t) * (kpad / 32) + b] = d * (1.0f / 256.0f);
+                    xsum[static_cast<size_t>(t) * (kpad / 32) + b] = sum;
+                }
+            }
+        }
+    }
+    asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");
+
+    const int team = warp / kTeamWarps, twarp = warp % kTeamWarps;
+    bool ok = true;
+    uint32_t pair_base = 0;
+    KqWalk walk(r_first, r_last);
+    while (!walk.done() && ok) {
+        RowGroup pair[kTeams];
+#pragma unroll
+        for (int m = 0; m < kTeams; ++m) pair[m] = walk.next(p);
+        const RowGroup g = team == 0 ? pair[0] : pair[1];
+        const KqTask& t = p.task[g.task];
+        const uint32_t row = g.row0 + twarp;
+        const bool valid = static_cast<uint32_t>(twarp) < g.nrows;
+        float acc[kBatch];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) acc[b] = 0.0f;
+
+        for (uint32_t s = 0; s < p.nseg; ++s) {
+            const uint32_t unit = pair_base + s * kTeams + team;
+            const uint32_t stage = unit % kStages;
+            if (*abort_word || !mbar_wait(&full[stage], (unit / kStages) & 1)) {
+                if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrFullWaitTimeout); }
+                ok = false;
+                break;
+            }
+            if (valid) {
+                const uint8_t* st = ring + stage * kStageBytes;
+                const uint32_t e_base = s * kKqSegElems;
+                const uint32_t elems = min(static_cast<uint32_t>(kKqSegElems), p.K - e_base);
+                if (kFormat == 2) {
+                    // ---- Q4_0: a lane owns a 32-weight block: 16 nibble bytes + one scale ----
+                    const uint4* nib = reinterpret_cast<const uint4*>(st + kq_plane_offset<kFormat>(0) + twarp * F::seg_bytes(0));
+                    const __half* ws = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(1) + twarp * F::seg_bytes(1));
+#pragma unroll
+                    for (int i = 0; i < kKqSegElems / 32 / 32; ++i) {
+                        const uint32_t bl = i * 32 + lane;
+                        if (bl * 32 < elems) {
+                            const uint4 w = nib[bl];
+                            const float dw = __half2float(ws[bl]);
+                            // low nibbles are elements 0..15, high nibbles elements 16..31 (src/quant.cpp:391-397)
+                            const uint4 lo = make_uint4(w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu);
+                            const uint4 hi = make_uint4((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, (w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu);
+                            const uint32_t b = e_base / 32 + bl;
+#pragma unroll
+                            for (int tk = 0; tk < kBatch; ++tk) {
+                                const uint4* x1 = reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + b * 32);
+                                const uint4* x2 = reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + kpad + b * 32);
+                                const int i1 = dot16(lo, x1[0]) + dot16(hi, x1[1]);
+                                const int i2 = dot16(lo, x2[0]) + dot16(hi, x2[1]);
+                                const int isum = i1 * 256 + i2 - 8 * xsum[static_cast<size_t>(tk) * (kpad / 32) + b];
+                                acc[tk] = fmaf(dw * xscale[static_cast<size_t>(tk) * (kpad / 32) + b], static_cast<float>(isum), acc[tk]);
+                            }
+                        }
+                    }
+                } else {
+                    // ---- Q6_K: a lane owns one 16-weight scale group; a warp covers two super-blocks a pass ----
+                    const uint8_t* ql = st + kq_plane_offset<kFormat>(0) + twarp * F::seg_bytes(0);
+                    const uint8_t* qh = st + kq_plane_offset<kFormat>(1) + twarp * F::seg_bytes(1);
+                    const int8_t* sc = reinterpret_cast<const int8_t*>(st + kq_plane_offset<kFormat>(2) + twarp * F::seg_bytes(2));
+                    const __half* dd = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(3) + twarp * F::seg_bytes(3));
+                    const uint32_t sg = lane & 15, half = sg >> 3, group = (sg >> 1) & 3, six = sg & 1;
+                    const uint32_t shift4 = group >= 2 ? 4u : 0u, shift2 = group * 2;
+                    // element e = half*128 + group*32 + l: ql byte half*64 + (group%2)*32 + l, qh byte half*32 + l,
+                    // scale half*8 + group*2 + l/16 == sg (src/quant.cpp:500-517)
+#pragma unroll 4
+                    for (int i = 0; i < kKqSegElems / 256 / 2; ++i) {
+                        const uint32_t sbl = i * 2 + (lane >> 4);
+                        if (sbl * 256 < elems) {
+                            const uint4 l4 = *reinterpret_cast<const uint4*>(ql + sbl * 128 + half * 64 + (group & 1) * 32 + six * 16);
+                            const uint4 h4 = *reinterpret_cast<const uint4*>(qh + sbl * 64 + half * 32 + six * 16);
+                            uint4 q;
+                            q.x = sub32_bytes(((l4.x >> shift4) & 0x0F0F0F0Fu) | (((h4.x >> shift2) & 0x03030303u) << 4));
+                            q.y = sub32_bytes(((l4.y >> shift4) & 0x0F0F0F0Fu) | (((h4.y >> shift2) & 0x03030303u) << 4));
+                            q.z = sub32_bytes(((l4.z >> shift4) & 0x0F0F0F0Fu) | (((h4.z >> shift2) & 0x03030303u) << 4));
+                            q.w = sub32_bytes(((l4.w >> shift4) & 0x0F0F0F0Fu) | (((h4.w >> shift2) & 0x03030303u) << 4));
+                            const float dsc = __half2float(dd[sbl]) * static_cast<float>(sc[sbl * 16 + sg]);  // (d * scale), the reference's order
+                            const uint32_t e0 = e_base + sbl * 256 + half * 128 + group * 32 + six * 16;
+#pragma unroll
+                            for (int tk = 0; tk < kBatch; ++tk) {
+                                const uint4 x1 = *reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + e0);
+                                const uint4 x2 = *reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + kpad + e0);
+                                const int isum = dot16(q, x1) * 256 + dot16(q, x2);
+                                acc[tk] = fmaf(dsc * xscale[static_cast<size_t>(tk) * (kpad / 32) + e0 / 32], static_cast<float>(isum), acc[tk]);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[stage]);
+        }
+        if (!ok) break;
+        pair_base += kTeams * p.nseg;
+        if (valid) {
+#pragma unroll
+            for (int tk = 0; tk < kBatch; ++tk) {
+                float v = acc[tk];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) t.y[static_cast<size_t>(tk) * t.rows + row] = v;
+            }
+        }
+    }
+}
+
+}  // namespace zk

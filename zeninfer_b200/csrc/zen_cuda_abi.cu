@@ -22,6 +22,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "gemv_kq.cuh"
 #include "gemv_q8_0.cuh"
 #include "quantize_acts.cuh"
 #include "repack.cuh"
@@ -183,7 +184,6 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
         set_error(s, "upload: bad shape or format");
         return nullptr;
     }
-    if (fmt != ZEN_CUDA_Q8_0) { set_error(s, "upload: format not built yet"); return nullptr; }
     const auto t_all = clock_type::now();
     auto* w = new zen_cuda_weights;
     w->format = fmt; w->rows = nrows; w->cols = cols;
@@ -195,8 +195,19 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
     auto t0 = clock_type::now();
     bool ok = cudaMalloc(reinterpret_cast<void**>(&d_raw), w->raw_bytes + 16) == cudaSuccess;
     size_t plane_bytes[4] = {0, 0, 0, 0};
-    plane_bytes[0] = nrows * cols + 64;                                // int8 codes (+ slack for rounded-up bulk copies)
-    plane_bytes[1] = nrows * static_cast<size_t>(w->nbp) * 2 + 64;     // f16 scales
+    // every plane gets slack for bulk copies whose size was rounded up to 16 bytes
+    if (fmt == ZEN_CUDA_Q8_0) {
+        plane_bytes[0] = nrows * cols + 64;                                // int8 codes
+        plane_bytes[1] = nrows * static_cast<size_t>(w->nbp) * 2 + 64;     // f16 scales
+    } else if (fmt == ZEN_CUDA_Q4_0) {
+        plane_bytes[0] = nrows * (cols / 2) + 64;                          // nibble bytes
+        plane_bytes[1] = nrows * static_cast<size_t>(w->nbp) * 2 + 64;     // f16 scales
+    } else {  // Q6_K: nb counts 256-weight super-blocks
+        plane_bytes[0] = nrows * (cols / 2) + 64;                          // ql
+        plane_bytes[1] = nrows * (cols / 4) + 64;                          // qh
+        plane_bytes[2] = nrows * (cols / 16) + 64;                         // int8 group scales
+        plane_bytes[3] = nrows * static_cast<size_t>(w->nbp) * 2 + 64;     // f16 super-block scales
+    }
     for (int i = 0; ok && i < 4; ++i)
         if (plane_bytes[i]) {
             ok = cudaMalloc(&w->plane[i], plane_bytes[i]) == cudaSuccess;
@@ -217,8 +228,16 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
         t0 = clock_type::now();
         const size_t nblocks = nrows * w->nb;
         const unsigned grid = static_cast<unsigned>((nblocks + 255) / 256);
-        zk::repack_q8_0_kernel<<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]),
-                                                               static_cast<uint16_t*>(w->plane[1]), nrows, w->nb, w->nbp);
+        if (fmt == ZEN_CUDA_Q8_0)
+            zk::repack_q8_0_kernel<<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]),
+                                                                   static_cast<uint16_t*>(w->plane[1]), nrows, w->nb, w->nbp);
+        else if (fmt == ZEN_CUDA_Q4_0)
+            zk::repack_q4_0_kernel<<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]),
+                                                                   static_cast<uint16_t*>(w->plane[1]), nrows, w->nb, w->nbp);
+        else
+            zk::repack_q6_k_kernel<<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]), static_cast<uint8_t*>(w->plane[1]),
+                                                                   static_cast<int8_t*>(w->plane[2]), static_cast<uint16_t*>(w->plane[3]),
+                                                                   nrows, w->nb, w->nbp);
         ++s.stats.dispatches;
         ok = cudaGetLastError() == cudaSuccess && cudaStreamSynchronize(s.copy_stream) == cudaSuccess;
         s.stats.repack_us += us_since(t0);
@@ -287,6 +306,95 @@ cudaError_t dispatch_batch(int batch, const zk::GemvParams& p, unsigned grid, si
     }
 }
 
+template <int kFormat, int kBatch>
+cudaError_t launch_gemv_kq(const zk::KqParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
+    auto* fn = &zk::gemv_kq_kernel<kFormat, kBatch>;
+    static size_t configured = 0;
+    if (smem > configured) {
+        const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(zk::kGemvThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, fn, p);
+}
+
+template <int kFormat>
+cudaError_t dispatch_kq(int batch, const zk::KqParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
+    switch (batch) {
+    case 1: return launch_gemv_kq<kFormat, 1>(p, grid, smem, st, pdl);
+    case 2: return launch_gemv_kq<kFormat, 2>(p, grid, smem, st, pdl);
+    case 3: return launch_gemv_kq<kFormat, 3>(p, grid, smem, st, pdl);
+    case 4: return launch_gemv_kq<kFormat, 4>(p, grid, smem, st, pdl);
+    case 5: return launch_gemv_kq<kFormat, 5>(p, grid, smem, st, pdl);
+    case 6: return launch_gemv_kq<kFormat, 6>(p, grid, smem, st, pdl);
+    case 7: return launch_gemv_kq<kFormat, 7>(p, grid, smem, st, pdl);
+    case 8: return launch_gemv_kq<kFormat, 8>(p, grid, smem, st, pdl);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+size_t gemv_smem_bytes(int format, size_t cols, size_t tokens, int act_mode) {
+    if (format == ZEN_CUDA_Q8_0) {
+        const uint32_t nb = static_cast<uint32_t>(cols / 32), nseg = (nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks;
+        return zk::gemv_q8_0_smem_bytes(nseg, static_cast<int>(tokens), act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1);
+    }
+    const uint32_t nseg = static_cast<uint32_t>((cols + zk::kKqSegElems - 1) / zk::kKqSegElems);
+    return format == ZEN_CUDA_Q4_0 ? zk::gemv_kq_smem_bytes<ZEN_CUDA_Q4_0>(nseg, static_cast<int>(tokens))
+                                   : zk::gemv_kq_smem_bytes<ZEN_CUDA_Q6_K>(nseg, static_cast<int>(tokens));
+}
+
+// Largest number of activation rows (<= 8) one launch can keep in shared memory beside the weight ring; 0 if not even one.
+size_t max_tokens_per_launch(const State& s, int format, size_t cols, int act_mode) {
+    for (size_t t = 8; t >= 1; --t)
+        if (gemv_smem_bytes(format, cols, t, act_mode) <= s.smem_optin) return t;
+    return 0;
+}
+
+bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
+                     size_t tokens, cudaStream_t st) {
+    zk::KqParams p{};
+    uint32_t total_rows = 0;
+    const int fmt = w[0]->format;
+    const int planes = fmt == ZEN_CUDA_Q4_0 ? 2 : 4;
+    for (size_t i = 0; i < count; ++i) {
+        for (int k = 0; k < planes; ++k) p.task[i].plane[k] = static_cast<const uint8_t*>(w[i]->plane[k]);
+        p.task[i].y = d_y[i];
+        p.task[i].rows = static_cast<uint32_t>(w[i]->rows);
+        p.task[i].first_row = total_rows;
+        total_rows += static_cast<uint32_t>(w[i]->rows);
+    }
+    p.ntasks = static_cast<uint32_t>(count);
+    p.total_rows = total_rows;
+    p.x = d_x;
+    p.K = static_cast<uint32_t>(w[0]->cols);
+    p.nseg = (p.K + zk::kKqSegElems - 1) / zk::kKqSegElems;
+    if (fmt == ZEN_CUDA_Q4_0) {
+        p.pitch[0] = p.K / 2;
+        p.pitch[1] = w[0]->nbp * 2;
+    } else {
+        p.pitch[0] = p.K / 2; p.pitch[1] = p.K / 4; p.pitch[2] = p.K / 16; p.pitch[3] = w[0]->nbp * 2;
+    }
+    p.error_word = s.d_error;
+    const size_t smem = gemv_smem_bytes(fmt, w[0]->cols, tokens, ZEN_CUDA_ACT_FP32);
+    if (smem > s.smem_optin) return set_error(s, "gemv: activation rows do not fit shared memory (columns x tokens too large)");
+    const unsigned grid = std::max(1u, std::min<unsigned>((total_rows + zk::kGemvWarps - 1) / zk::kGemvWarps, static_cast<unsigned>(s.sm_count)));
+    const cudaError_t e = fmt == ZEN_CUDA_Q4_0 ? dispatch_kq<ZEN_CUDA_Q4_0>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
+                                               : dispatch_kq<ZEN_CUDA_Q6_K>(static_cast<int>(tokens), p, grid, smem, st, s.pdl);
+    if (e != cudaSuccess) return set_error(s, std::string("gemv launch: ") + cudaGetErrorString(e));
+    ++s.stats.dispatches;
+    return true;
+}
+
 // Enqueues one batched GEMV launch: `count` tensors (same format, same K) times `tokens` (<= 8)
 // activation rows.  Device pointers throughout.
 bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
@@ -304,7 +412,10 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
         p.task[i].first_row = total_rows;
         total_rows += static_cast<uint32_t>(w[i]->rows);
     }
-    if (w[0]->format != ZEN_CUDA_Q8_0) return set_error(s, "gemv: format not built yet");
+    if (w[0]->format != ZEN_CUDA_Q8_0) {
+        if (act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: Q4_0 and Q6_K take fp32-equivalent activations only");
+        return enqueue_gemv_kq(s, w, d_y, count, d_x, tokens, st);
+    }
     p.ntasks = static_cast<uint32_t>(count);
     p.total_rows = total_rows;
     p.x = d_x;
@@ -385,8 +496,10 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     float* d_out[zk::kMaxTasks];
     size_t off = 0;
     for (size_t i = 0; i < count; ++i) { d_out[i] = s.d_y + off; off += tokens * rows[i]; }
-    for (size_t t0k = 0; t0k < tokens; t0k += 8) {
-        const size_t nt = std::min<size_t>(8, tokens - t0k);
+    const size_t chunk = max_tokens_per_launch(s, fmt, cols, act_mode);
+    if (!chunk) return set_error(s, "columns too large: one activation row does not fit shared memory");
+    for (size_t t0k = 0; t0k < tokens; t0k += chunk) {
+        const size_t nt = std::min<size_t>(chunk, tokens - t0k);
         float* d_chunk[zk::kMaxTasks];
         for (size_t i = 0; i < count; ++i) d_chunk[i] = d_out[i] + t0k * rows[i];
         if (!enqueue_gemv(s, w, d_chunk, count, s.d_x + t0k * cols, nt, act_mode, s.stream)) return false;
