@@ -22,6 +22,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "gemm_q8_0_i8.cuh"
 #include "gemv_kq.cuh"
 #include "gemv_q8_0.cuh"
 #include "quantize_acts.cuh"
@@ -77,6 +78,9 @@ struct State {
     float* h_stage{}; size_t h_stage_bytes{};
     float* d_x{}; size_t d_x_bytes{};
     float* d_y{}; size_t d_y_bytes{};
+    uint8_t* d_gemm_ws{}; size_t d_gemm_ws_bytes{};  // quantised activations of the prefill GEMM: codes, then block-major scales
+    bool use_gemm{true};     // tensor-core prefill path (ZEN_CUDA_GEMM=0 falls back to chunks of eight tokens on the decode kernel)
+    void* encode_tiled{};    // cuTensorMapEncodeTiled, resolved through the runtime
     int* h_error{};   // mapped pinned word the kernels write on a bounded-wait timeout
     int* d_error{};   // device alias of h_error
 };
@@ -143,6 +147,13 @@ bool init_locked(State& s) {
         else if (!std::strcmp(m, "int8") || !std::strcmp(m, "1")) s.q8_act_mode = ZEN_CUDA_ACT_INT8;
     }
     if (const char* m = std::getenv("ZEN_CUDA_PDL")) s.pdl = m[0] != '0';
+    if (const char* m = std::getenv("ZEN_CUDA_GEMM")) s.use_gemm = m[0] != '0';
+    {
+        cudaDriverEntryPointQueryResult qres{};
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &s.encode_tiled, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            s.encode_tiled = nullptr;
+    }
     if (const char* m = std::getenv("ZEN_CUDA_GEMV_CTAS")) s.ctas_per_sm = static_cast<unsigned>(std::max(1, std::min(4, std::atoi(m))));
     s.ready = true;
     return true;
@@ -439,6 +450,98 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
     return true;
 }
 
+
+// ---- prefill GEMM (tcgen05) -----------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+bool make_map_2d(State& s, CUtensorMap* map, CUtensorMapDataType type, size_t elem_bytes, const void* base, uint64_t inner, uint64_t outer,
+                 uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
+    if (!s.encode_tiled) return set_error(s, "gemm: cuTensorMapEncodeTiled is not available");
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    (void)elem_bytes;
+    const CUresult r = reinterpret_cast<EncodeTiledFn>(s.encode_tiled)(map, type, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                                                      CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(s, "gemm: cuTensorMapEncodeTiled failed (" + std::to_string(static_cast<int>(r)) + ")");
+    return true;
+}
+
+size_t gemm_ws_bytes(size_t tokens, size_t cols) {
+    const size_t t_ld = (tokens + 3) & ~size_t(3);
+    return ((tokens * cols + 255) & ~size_t(255)) + (cols / 32) * t_ld * sizeof(float);
+}
+
+template <int kNTile>
+cudaError_t launch_gemm(const zk::GemmParams& p, unsigned grid, cudaStream_t st) {
+    auto* fn = &zk::gemm_q8_0_i8_kernel<kNTile>;
+    const size_t smem = zk::gemm_smem_bytes(kNTile);
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    fn<<<grid, zk::kGemmThreads, smem, st>>>(p);
+    return cudaGetLastError();
+}
+
+// Quantises d_x [tokens][cols] into the workspace `ws` (gemm_ws_bytes) and enqueues one GEMM per tensor.
+// Everything is stream-ordered on `st`; `ws` must stay untouched until the work has run.
+bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x, size_t tokens,
+                       uint8_t* ws, cudaStream_t st) {
+    if (!count || !tokens || !d_x || !ws) return set_error(s, "gemm: bad arguments");
+    const size_t cols = w[0]->cols;
+    const uint32_t nb = w[0]->nb;
+    const size_t t_ld = (tokens + 3) & ~size_t(3);
+    int8_t* xq = reinterpret_cast<int8_t*>(ws);
+    float* xs_t = reinterpret_cast<float*>(ws + ((tokens * cols + 255) & ~size_t(255)));
+    const size_t nblk = tokens * nb;
+    zk::quantize_acts_gemm_kernel<<<static_cast<unsigned>((nblk + 7) / 8), 256, 0, st>>>(d_x, xq, xs_t, static_cast<uint32_t>(tokens), nb,
+                                                                                      static_cast<uint32_t>(t_ld));
+    if (cudaGetLastError() != cudaSuccess) return set_error(s, "gemm: quantise launch failed");
+    ++s.stats.dispatches;
+    const uint32_t n_tile = tokens <= 64 ? 64u : tokens <= 128 ? 128u : 256u;
+    for (size_t i = 0; i < count; ++i) {
+        if (!w[i] || !d_out[i] || w[i]->format != ZEN_CUDA_Q8_0 || w[i]->cols != cols) return set_error(s, "gemm: tasks must be Q8_0 and share columns");
+        zk::GemmParams p{};
+        if (!make_map_2d(s, &p.map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[i]->plane[0], cols, w[i]->rows, cols, zk::kGemmKTile, zk::kGemmM,
+                         CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+        if (!make_map_2d(s, &p.map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, cols, tokens, cols, zk::kGemmKTile, n_tile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+        if (!make_map_2d(s, &p.map_xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, xs_t, t_ld, nb, t_ld * sizeof(float), n_tile, zk::kGemmBlocksPerTile,
+                         CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+        p.w_scales = static_cast<const __half*>(w[i]->plane[1]);
+        p.out = d_out[i];
+        p.rows = static_cast<uint32_t>(w[i]->rows);
+        p.tokens = static_cast<uint32_t>(tokens);
+        p.nb = nb;
+        p.nbp = w[i]->nbp;
+        p.n_tile = n_tile;
+        p.m_tiles = (p.rows + zk::kGemmM - 1) / zk::kGemmM;
+        p.n_tiles = (p.tokens + n_tile - 1) / n_tile;
+        p.error_word = s.d_error;
+        const unsigned grid = std::min<unsigned>(p.m_tiles * p.n_tiles, static_cast<unsigned>(s.sm_count));
+        const cudaError_t e = n_tile == 64 ? launch_gemm<64>(p, grid, st) : n_tile == 128 ? launch_gemm<128>(p, grid, st) : launch_gemm<256>(p, grid, st);
+        if (e != cudaSuccess) return set_error(s, std::string("gemm launch: ") + cudaGetErrorString(e));
+        ++s.stats.dispatches;
+    }
+    return true;
+}
+
+bool ensure_gemm_ws(State& s, size_t bytes) {
+    if (bytes <= s.d_gemm_ws_bytes) return true;
+    if (s.d_gemm_ws) { cudaStreamSynchronize(s.stream); cudaFree(s.d_gemm_ws); }
+    s.d_gemm_ws = nullptr; s.d_gemm_ws_bytes = 0;
+    ZC_CUDA(s, cudaMalloc(reinterpret_cast<void**>(&s.d_gemm_ws), bytes));
+    s.d_gemm_ws_bytes = bytes;
+    return true;
+}
+
 bool ensure_scratch(State& s, size_t x_bytes, size_t y_bytes) {
     const auto t0 = clock_type::now();
     if (x_bytes > s.d_x_bytes) {
@@ -498,7 +601,13 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     for (size_t i = 0; i < count; ++i) { d_out[i] = s.d_y + off; off += tokens * rows[i]; }
     const size_t chunk = max_tokens_per_launch(s, fmt, cols, act_mode);
     if (!chunk) return set_error(s, "columns too large: one activation row does not fit shared memory");
-    for (size_t t0k = 0; t0k < tokens; t0k += chunk) {
+    // More than one decode launch worth of int8-activation Q8_0 tokens: the tensor-core GEMM.
+    const bool tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q8_0 && act_mode == ZEN_CUDA_ACT_INT8 && tokens > 8;
+    if (tensor_path) {
+        if (!ensure_gemm_ws(s, gemm_ws_bytes(tokens, cols))) return false;
+        if (!enqueue_gemm_q8_0(s, w, d_out, count, s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
+    }
+    for (size_t t0k = 0; !tensor_path && t0k < tokens; t0k += chunk) {
         const size_t nt = std::min<size_t>(chunk, tokens - t0k);
         float* d_chunk[zk::kMaxTasks];
         for (size_t i = 0; i < count; ++i) d_chunk[i] = d_out[i] + t0k * rows[i];
@@ -550,6 +659,8 @@ void zen_cuda_shutdown(void) {
         s.resident.clear();
         if (s.d_x) cudaFree(s.d_x);
         if (s.d_y) cudaFree(s.d_y);
+        if (s.d_gemm_ws) cudaFree(s.d_gemm_ws);
+        s.d_gemm_ws = nullptr; s.d_gemm_ws_bytes = 0;
         if (s.h_stage) cudaFreeHost(s.h_stage);
         if (s.h_error) cudaFreeHost(s.h_error);
         for (int i = 0; i < 2; ++i) {
