@@ -154,6 +154,15 @@ size_t zen_cuda_dev_weight_bytes(const zen_cuda_weights* w); /* device bytes hel
 int zen_cuda_dev_gemv(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
                       size_t tokens, int act_mode, void* stream);
 
+/* Prefill product on the tensor cores (Q8_0, int8 activations): d_out[i] = d_x * W[i]^T, token-major
+ * [tokens][rows_i].  d_x: device fp32 [tokens][columns]; `workspace` is device scratch of at least
+ * zen_cuda_gemm_workspace_bytes(tokens, columns) bytes that must stay untouched until the work has run (it
+ * receives the quantised activations: the reference's quantize_acts step, shaders/quantize_acts.hlsl, then
+ * zen::d3d12::gemm_q8_0_batch, include/zen/d3d12_backend.h:169).  Stream-ordered, no synchronisation. */
+size_t zen_cuda_gemm_workspace_bytes(size_t tokens, size_t columns);
+int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x,
+                           size_t tokens, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Device quantiser: d_x [tokens][columns] fp32 -> d_codes int8, d_scales fp32 [tokens][columns/32]. */
 int zen_cuda_dev_quantize_acts(const float* d_x, int8_t* d_codes, float* d_scales, size_t tokens, size_t columns, void* stream);
 

@@ -1,0 +1,86 @@
+"""Host logic of the multi-GPU path on CPU: the shard plan, the all-gather of output shards (gloo, world size 2 and 3)
+and the greedy pick.  The CPU oracle stands in for the kernels, so what is tested is the plumbing around them."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from zeninfer_b200 import blocks, shard
+
+
+def test_shard_plan_tiles_any_row_count():
+    for rows in (0, 1, 7, 8, 9, 264, 4096, 14336, 128256):
+        for world in (1, 2, 3, 4, 8):
+            plan = shard.shard_plan(rows, world)
+            assert plan[0][0] == 0 and plan[-1][1] == rows
+            assert all(plan[i][1] == plan[i + 1][0] for i in range(world - 1))
+            assert all(a % shard.ROW_ALIGN == 0 for a, _ in plan)
+    # the lm_head of the benchmark configuration splits evenly: 128256 / 8 = 16032 rows, a multiple of 8
+    assert shard.shard_plan(128256, 8) == [(16032 * i, 16032 * (i + 1)) for i in range(8)]
+    assert shard.raw_byte_range(16032, 32064, 3360) == (16032 * 3360, 32064 * 3360)
+
+
+def test_row_shard_matches_pool_cut_when_aligned(zo):
+    # src/compute_pool.cpp:104-106: slice i of n = [count*i/n, count*(i+1)/n)
+    for rows, world in ((4096, 4), (128256, 8), (14336, 2)):
+        for r in range(world):
+            assert shard.row_shard(rows, world, r) == zo.row_slice(rows, world, r)
+
+
+def test_greedy_pick_rule(zo):
+    rows = torch.tensor([[1.0, 3.0, 3.0, 2.0], [float("nan"), float("inf"), -5.0, -5.0],
+                         [float("nan"), float("-inf"), float("inf"), float("nan")], [-0.0, 0.0, -1.0, -2.0]])
+    got = shard.greedy_pick(rows).tolist()
+    assert got == [zo.argmax(r.numpy()) for r in rows] == [1, 2, -1, 0]
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, rows: int, cols: int, tokens: int, fmt: int, out_dir: str):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import oracle
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        zo = oracle.Oracle()
+        w = np.random.default_rng(5).standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02)
+        packed = blocks.quantize(fmt, w)
+        x = np.random.default_rng(6).standard_normal((tokens, cols), dtype=np.float32)
+        first, last = shard.row_shard(rows, world, rank)
+        lo, hi = shard.raw_byte_range(first, last, blocks.row_bytes(fmt, cols))
+        mine = np.frombuffer(packed.tobytes()[lo:hi], np.uint8)  # a rank touches only its byte range
+        local = torch.from_numpy(zo.gemm(fmt, mine, x, tokens, last - first, cols)) if last > first else torch.empty((tokens, 0))
+        if first == 0 and last > 0:
+            local[0, 0] = float("nan")  # a non-finite logit must never be picked, wherever it lives
+        full = shard.all_gather_rows(local, rows, world, rank)
+        pick_full = shard.greedy_pick(full)
+        pick_sharded = shard.sharded_greedy_pick(local, rows, world, rank)
+        torch.save({"full": full, "pick_full": pick_full, "pick_sharded": pick_sharded}, os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,rows", [(2, 264), (3, 100), (2, 8)])
+def test_all_gather_and_pick_over_gloo(zo, tmp_path, world, rows):
+    cols, tokens, fmt = 256, 3, blocks.Q6_K
+    mp.spawn(_worker, args=(world, _free_port(), rows, cols, tokens, fmt, str(tmp_path)), nprocs=world, join=True)
+    w = np.random.default_rng(5).standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02)
+    packed = blocks.quantize(fmt, w)
+    x = np.random.default_rng(6).standard_normal((tokens, cols), dtype=np.float32)
+    ref = zo.gemm(fmt, packed, x, tokens, rows, cols)
+    ref[0, 0] = np.nan
+    expect = [zo.argmax(r) for r in ref]
+    for r in range(world):
+        got = torch.load(os.path.join(tmp_path, f"r{r}.pt"))
+        assert np.array_equal(got["full"].numpy(), ref, equal_nan=True)  # shards come from the same code, bit for bit
+        assert got["pick_full"].tolist() == expect
+        assert got["pick_sharded"].tolist() == expect

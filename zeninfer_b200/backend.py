@@ -33,7 +33,7 @@ ABI_SYMBOLS = (
     "zen_cuda_gemv_q8_0", "zen_cuda_gemm_q8_0", "zen_cuda_gemv_q8_0_batch", "zen_cuda_gemm_q8_0_batch",
     "zen_cuda_gemm_q6_k", "zen_cuda_gemm_q4_0", "zen_cuda_release_weights", "zen_cuda_quantize_acts",
     "zen_cuda_dev_upload", "zen_cuda_dev_free", "zen_cuda_dev_weight_bytes", "zen_cuda_dev_gemv",
-    "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check",
+    "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_gemm_workspace_bytes", "zen_cuda_dev_gemm_q8_0",
 )
 
 
@@ -96,6 +96,9 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_dev_gemv.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, i, vp]
     lib.zen_cuda_dev_quantize_acts.argtypes = [vp, vp, vp, sz, sz, vp]
     lib.zen_cuda_dev_check.argtypes = [vp]
+    lib.zen_cuda_gemm_workspace_bytes.argtypes = [sz, sz]
+    lib.zen_cuda_gemm_workspace_bytes.restype = sz
+    lib.zen_cuda_dev_gemm_q8_0.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, vp, sz, vp]
     return lib
 
 
@@ -219,6 +222,16 @@ class Backend:
         ys = (C.c_void_p * n)(*d_y)
         if not self.lib.zen_cuda_dev_gemv(hs, ys, n, d_x, tokens, act_mode, stream):
             self._fail("dev_gemv")
+
+    def gemm_workspace_bytes(self, tokens: int, columns: int) -> int:
+        return int(self.lib.zen_cuda_gemm_workspace_bytes(tokens, columns))
+
+    def dev_gemm_q8_0(self, handles: Sequence[int], d_out: Sequence[int], d_x: int, tokens: int, workspace: int, workspace_bytes: int, stream: int = 0) -> None:
+        n = len(handles)
+        hs = (C.c_void_p * n)(*handles)
+        outs = (C.c_void_p * n)(*d_out)
+        if not self.lib.zen_cuda_dev_gemm_q8_0(hs, outs, n, d_x, tokens, workspace, workspace_bytes, stream):
+            self._fail("dev_gemm_q8_0")
 
     def dev_quantize_acts(self, d_x: int, d_codes: int, d_scales: int, tokens: int, columns: int, stream: int = 0) -> None:
         if not self.lib.zen_cuda_dev_quantize_acts(d_x, d_codes, d_scales, tokens, columns, stream):

@@ -35,7 +35,8 @@ constexpr int kGemmM = 128;            // weight rows per tile (TMEM lanes)
 constexpr int kGemmKTile = 128;        // K bytes per stage = 4 Q8_0 blocks
 constexpr int kGemmBlocksPerTile = kGemmKTile / 32;
 constexpr int kGemmStages = 4;
-constexpr int kGemmEpiWarps = 8;
+constexpr int kGemmEpiWarps = 16;       // four per TMEM lane quadrant
+constexpr int kGemmSplit = kGemmEpiWarps / 4;  // the warps of a quadrant split the token columns
 constexpr int kGemmThreads = (2 + kGemmEpiWarps) * 32;
 constexpr int kGemmMaxN = 256;         // tokens per tile, a multiple of 32
 
@@ -58,23 +59,90 @@ __host__ __device__ inline size_t gemm_smem_bytes(uint32_t n_tile) {
     return 1024 /* alignment slack */ + static_cast<size_t>(kGemmStages) * gemm_stage_bytes(n_tile) + 256 /* barriers */;
 }
 
-__device__ __forceinline__ void gemm_fma32(const uint32_t (&v)[32], float sw, const float* __restrict__ sx, float* __restrict__ acc) {
+// Packed fp32 pairs (sm_100 f32x2 arithmetic): one instruction scales or accumulates two token columns.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// Two int32 block sums -> two exact floats without the (quarter-rate) conversion unit: |v| < 2^22, so
+// adding v to the bit pattern of 1.5 * 2^23 yields the float 1.5 * 2^23 + v exactly, and subtracting
+// 1.5 * 2^23 is exact as well.  One integer add per value plus one packed fp32 add per pair.
+__device__ __forceinline__ uint64_t ints_to_float2(uint32_t v0, uint32_t v1) {
+    const uint64_t biased = pack2(__uint_as_float(v0 + 0x4B400000u), __uint_as_float(v1 + 0x4B400000u));
+    return add2(biased, pack2(-12582912.0f, -12582912.0f));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// acc[c/2] += float(v[c], v[c+1]) * (sw * sx[c], sw * sx[c+1]) for 32 token columns.
+// ZK_GEMM_VARIANT selects how: 0 = convert unit + packed fp32, 1 = magic-number convert + packed fp32,
+// 2 = convert unit + scalar fp32, 3 = magic-number convert + scalar fp32.
+#ifndef ZK_GEMM_VARIANT
+#define ZK_GEMM_VARIANT 0
+#endif
+__device__ __forceinline__ float int_to_float(uint32_t v) {
+#if ZK_GEMM_VARIANT == 1 || ZK_GEMM_VARIANT == 3
+    return __uint_as_float(v + 0x4B400000u) - 12582912.0f;
+#else
+    return static_cast<float>(static_cast<int>(v));
+#endif
+}
+__device__ __forceinline__ void gemm_fma32(const uint32_t (&v)[32], uint64_t sw2, const float* __restrict__ sx, uint64_t* __restrict__ acc) {
+#if ZK_GEMM_VARIANT >= 2
+    float sw, sw_hi;
+    unpack2(sw2, sw, sw_hi);
 #pragma unroll
     for (int c = 0; c < 32; c += 4) {
-        const float4 s4 = *reinterpret_cast<const float4*>(sx + c);  // same address in every lane: a broadcast
-        acc[c + 0] = fmaf(static_cast<float>(static_cast<int>(v[c + 0])), sw * s4.x, acc[c + 0]);
-        acc[c + 1] = fmaf(static_cast<float>(static_cast<int>(v[c + 1])), sw * s4.y, acc[c + 1]);
-        acc[c + 2] = fmaf(static_cast<float>(static_cast<int>(v[c + 2])), sw * s4.z, acc[c + 2]);
-        acc[c + 3] = fmaf(static_cast<float>(static_cast<int>(v[c + 3])), sw * s4.w, acc[c + 3]);
+        const float4 s4 = *reinterpret_cast<const float4*>(sx + c);
+        float a0, a1, a2, a3;
+        unpack2(acc[c / 2], a0, a1);
+        unpack2(acc[c / 2 + 1], a2, a3);
+        a0 = fmaf(int_to_float(v[c + 0]), sw * s4.x, a0);
+        a1 = fmaf(int_to_float(v[c + 1]), sw * s4.y, a1);
+        a2 = fmaf(int_to_float(v[c + 2]), sw * s4.z, a2);
+        a3 = fmaf(int_to_float(v[c + 3]), sw * s4.w, a3);
+        acc[c / 2] = pack2(a0, a1);
+        acc[c / 2 + 1] = pack2(a2, a3);
     }
+#else
+#pragma unroll
+    for (int c = 0; c < 32; c += 4) {
+        const ulonglong2 s4 = *reinterpret_cast<const ulonglong2*>(sx + c);  // same address in every lane: a broadcast
+#if ZK_GEMM_VARIANT == 1
+        const uint64_t f01 = ints_to_float2(v[c + 0], v[c + 1]);
+        const uint64_t f23 = ints_to_float2(v[c + 2], v[c + 3]);
+#else
+        const uint64_t f01 = pack2(int_to_float(v[c + 0]), int_to_float(v[c + 1]));
+        const uint64_t f23 = pack2(int_to_float(v[c + 2]), int_to_float(v[c + 3]));
+#endif
+        acc[c / 2] = fma2(f01, mul2(s4.x, sw2), acc[c / 2]);
+        acc[c / 2 + 1] = fma2(f23, mul2(s4.y, sw2), acc[c / 2 + 1]);
+    }
+#endif
 }
 
 // One block's int32 sums for this warp's kNHalf token columns: TMEM -> registers 32 columns at a time (the next
 // chunk is in flight while the current one is folded into the accumulators), then acc += float(sum) * (sw * sx).
 // The TMEM buffer is handed back to the MMA warp as soon as the last chunk has been read.
-template <int kNHalf>
-__device__ __forceinline__ void gemm_epilogue_block(uint32_t taddr, float sw, const float* __restrict__ sx, float (&acc)[kNHalf],
+template <int kNHalf>  // token columns per epilogue warp
+__device__ __forceinline__ void gemm_epilogue_block(uint32_t taddr, float sw_scalar, const float* __restrict__ sx, uint64_t (&acc)[kNHalf / 2],
                                                     uint64_t* tmem_empty_bar, int lane) {
+    const uint64_t sw = pack2(sw_scalar, sw_scalar);
     if constexpr (kNHalf <= 64) {
         uint32_t va[32], vb[32];
         tmem_ld_32x32(taddr, va);
@@ -84,7 +152,7 @@ __device__ __forceinline__ void gemm_epilogue_block(uint32_t taddr, float sw, co
         __syncwarp();
         if (lane == 0) mbar_arrive(tmem_empty_bar);
         gemm_fma32(va, sw, sx, acc);
-        if (kNHalf > 32) gemm_fma32(vb, sw, sx + 32, acc + 32);
+        if (kNHalf > 32) gemm_fma32(vb, sw, sx + 32, acc + 16);
     } else {
         // 128 accumulators leave room for one 32-column staging buffer only
         uint32_t v[32];
@@ -93,24 +161,24 @@ __device__ __forceinline__ void gemm_epilogue_block(uint32_t taddr, float sw, co
             tmem_ld_32x32(taddr + c, v);
             tmem_ld_wait();
             if (c + 32 >= kNHalf) { tc_fence_before_sync(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
-            gemm_fma32(v, sw, sx + c, acc + c);
+            gemm_fma32(v, sw, sx + c, acc + c / 2);
         }
     }
 }
 
 template <int kNTile>
-// Ten warps put three on one SM sub-partition (16 K registers each), so 168 registers per thread is the ceiling.
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __grid_constant__ GemmParams p) {
-    constexpr int kNHalf = kNTile / 2;
+    constexpr int kNHalf = kNTile / kGemmSplit;     // token columns per epilogue warp
+    constexpr uint32_t kBufs = 512 / kNTile > 4 ? 4 : 512 / kNTile;  // TMEM accumulator buffers
     constexpr uint32_t kStageBytes = kGemmM * kGemmKTile + kNTile * kGemmKTile + kGemmBlocksPerTile * kNTile * 4;
-    constexpr uint32_t kTmemCols = 2 * kNTile;  // two accumulator buffers; 128, 256 or 512: a power of two
+    constexpr uint32_t kTmemCols = kBufs * kNTile;  // 512: a power of two
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGemmStages * kStageBytes);
     uint64_t* empty = full + kGemmStages;
     uint64_t* tmem_full = empty + kGemmStages;
-    uint64_t* tmem_empty = tmem_full + 2;
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    uint64_t* tmem_empty = tmem_full + 4;
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 4);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -122,7 +190,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1 + kGemmEpiWarps);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < static_cast<int>(kBufs); ++b) {
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], kGemmEpiWarps);
         }
@@ -180,9 +248,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                     const uint64_t a_desc = umma_desc_k_sw128(a_addr), b_desc = umma_desc_k_sw128(a_addr + kGemmM * kGemmKTile);
                     const uint32_t nblk = min(static_cast<uint32_t>(kGemmBlocksPerTile), p.nb - kt * kGemmBlocksPerTile);
                     for (uint32_t j = 0; j < nblk; ++j, ++blk) {
-                        const uint32_t buf = blk & 1;
-                        if (blk >= 2) {
-                            if (!mbar_wait(&tmem_empty[buf], ((blk >> 1) - 1) & 1)) {
+                        const uint32_t buf = blk % kBufs;
+                        if (blk >= kBufs) {
+                            if (!mbar_wait(&tmem_empty[buf], ((blk / kBufs) - 1) & 1)) {
                                 *abort_word = 1; atomicExch(p.error_word, kErrTmemWaitTimeout); ok = false;
                                 break;
                             }
@@ -200,7 +268,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
         // ---------------- epilogue warps ----------------
         const int e = warp - 2;
         const uint32_t quad = static_cast<uint32_t>(warp) & 3;   // the TMEM lanes a warp may touch: 32 * (warp id % 4)
-        const uint32_t half = static_cast<uint32_t>(e) >> 2;      // the two warps of a quadrant split the token columns
+        const uint32_t half = static_cast<uint32_t>(e) >> 2;      // which share of the token columns this warp takes
         const uint32_t lane_addr = (quad * 32) << 16;
         uint32_t it = 0, blk = 0;
         bool ok = true;
@@ -208,9 +276,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
             const uint32_t mt = tile % p.m_tiles, nt = tile / p.m_tiles;
             const uint32_t r = mt * kGemmM + quad * 32 + lane;
             const bool row_ok = r < p.rows;
-            float acc[kNHalf];
+            uint64_t acc[kNHalf / 2];  // packed pairs of fp32 accumulators, token columns (2i, 2i+1)
 #pragma unroll
-            for (int c = 0; c < kNHalf; ++c) acc[c] = 0.0f;
+            for (int c = 0; c < kNHalf / 2; ++c) acc[c] = 0ull;
             for (uint32_t kt = 0; kt < ktiles && ok; ++kt, ++it) {
                 const uint32_t stage = it % kGemmStages;
                 // this tile's four weight scales of row r (8-byte aligned: nbp is a multiple of 8)
@@ -228,8 +296,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
 #pragma unroll
                 for (uint32_t j = 0; j < kGemmBlocksPerTile; ++j) {
                     if (j < nblk && ok) {
-                        const uint32_t buf = blk & 1;
-                        if (!mbar_wait(&tmem_full[buf], (blk >> 1) & 1)) {
+                        const uint32_t buf = blk % kBufs;
+                        if (!mbar_wait(&tmem_full[buf], (blk / kBufs) & 1)) {
                             if (lane == 0) { *abort_word = 1; atomicExch(p.error_word, kErrTmemWaitTimeout); }
                             ok = false;
                         } else {
@@ -247,9 +315,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
             if (!ok) break;
             if (row_ok) {
 #pragma unroll
-                for (int c = 0; c < kNHalf; ++c) {
+                for (int c = 0; c < kNHalf; c += 2) {
                     const uint32_t t = nt * kNTile + half * kNHalf + c;
-                    if (t < p.tokens) p.out[static_cast<size_t>(t) * p.rows + r] = acc[c];
+                    float lo, hi;
+                    unpack2(acc[c / 2], lo, hi);
+                    if (t < p.tokens) p.out[static_cast<size_t>(t) * p.rows + r] = lo;
+                    if (t + 1 < p.tokens) p.out[static_cast<size_t>(t + 1) * p.rows + r] = hi;
                 }
             }
         }

@@ -506,7 +506,8 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
                                                                                       static_cast<uint32_t>(t_ld));
     if (cudaGetLastError() != cudaSuccess) return set_error(s, "gemm: quantise launch failed");
     ++s.stats.dispatches;
-    const uint32_t n_tile = tokens <= 64 ? 64u : tokens <= 128 ? 128u : 256u;
+    uint32_t n_tile = 128u;  // tokens per tile; 256 is available but its 64 accumulators per thread leave too few registers
+    if (const char* e = std::getenv("ZEN_CUDA_GEMM_NTILE")) { const int v = std::atoi(e); if (v == 128 || v == 256) n_tile = static_cast<uint32_t>(v); }
     for (size_t i = 0; i < count; ++i) {
         if (!w[i] || !d_out[i] || w[i]->format != ZEN_CUDA_Q8_0 || w[i]->cols != cols) return set_error(s, "gemm: tasks must be Q8_0 and share columns");
         zk::GemmParams p{};
@@ -526,7 +527,7 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
         p.n_tiles = (p.tokens + n_tile - 1) / n_tile;
         p.error_word = s.d_error;
         const unsigned grid = std::min<unsigned>(p.m_tiles * p.n_tiles, static_cast<unsigned>(s.sm_count));
-        const cudaError_t e = n_tile == 64 ? launch_gemm<64>(p, grid, st) : n_tile == 128 ? launch_gemm<128>(p, grid, st) : launch_gemm<256>(p, grid, st);
+        const cudaError_t e = n_tile == 128 ? launch_gemm<128>(p, grid, st) : launch_gemm<256>(p, grid, st);
         if (e != cudaSuccess) return set_error(s, std::string("gemm launch: ") + cudaGetErrorString(e));
         ++s.stats.dispatches;
     }
@@ -822,6 +823,19 @@ int zen_cuda_dev_gemv(const zen_cuda_weights* const* w, float* const* d_y, size_
     if (!init_locked(s)) return 0;
     if (!w || !d_y) return set_error(s, "dev_gemv: bad arguments") ? 1 : 0;
     return enqueue_gemv(s, w, d_y, count, d_x, tokens, act_mode, stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
+}
+
+size_t zen_cuda_gemm_workspace_bytes(size_t tokens, size_t columns) { return gemm_ws_bytes(tokens, columns); }
+
+int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x, size_t tokens,
+                           void* workspace, size_t workspace_bytes, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!w || !d_out || !count || count > ZEN_CUDA_MAX_BATCH || !w[0]) return set_error(s, "dev_gemm: bad arguments") ? 1 : 0;
+    if (workspace_bytes < gemm_ws_bytes(tokens, w[0]->cols)) return set_error(s, "dev_gemm: workspace too small") ? 1 : 0;
+    return enqueue_gemm_q8_0(s, w, d_out, count, d_x, tokens, static_cast<uint8_t*>(workspace),
+                             stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
 }
 
 int zen_cuda_dev_quantize_acts(const float* d_x, int8_t* d_codes, float* d_scales, size_t tokens, size_t columns, void* stream) {
