@@ -506,8 +506,7 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
                                                                                       static_cast<uint32_t>(t_ld));
     if (cudaGetLastError() != cudaSuccess) return set_error(s, "gemm: quantise launch failed");
     ++s.stats.dispatches;
-    uint32_t n_tile = 128u;  // tokens per tile; 256 is available but its 64 accumulators per thread leave too few registers
-    if (const char* e = std::getenv("ZEN_CUDA_GEMM_NTILE")) { const int v = std::atoi(e); if (v == 128 || v == 256) n_tile = static_cast<uint32_t>(v); }
+    const uint32_t n_tile = 128u;  // tokens per tile: sixteen epilogue warps take 32 token columns each
     for (size_t i = 0; i < count; ++i) {
         if (!w[i] || !d_out[i] || w[i]->format != ZEN_CUDA_Q8_0 || w[i]->cols != cols) return set_error(s, "gemm: tasks must be Q8_0 and share columns");
         zk::GemmParams p{};
@@ -527,7 +526,7 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
         p.n_tiles = (p.tokens + n_tile - 1) / n_tile;
         p.error_word = s.d_error;
         const unsigned grid = std::min<unsigned>(p.m_tiles * p.n_tiles, static_cast<unsigned>(s.sm_count));
-        const cudaError_t e = n_tile == 128 ? launch_gemm<128>(p, grid, st) : launch_gemm<256>(p, grid, st);
+        const cudaError_t e = launch_gemm<128>(p, grid, st);
         if (e != cudaSuccess) return set_error(s, std::string("gemm launch: ") + cudaGetErrorString(e));
         ++s.stats.dispatches;
     }
