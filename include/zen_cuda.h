@@ -163,6 +163,25 @@ size_t zen_cuda_gemm_workspace_bytes(size_t tokens, size_t columns);
 int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x,
                            size_t tokens, void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  The same prefill product as zen_cuda_dev_gemm_q8_0 for ONE tensor, for callers
+ * that may not allocate device memory at the time of the call: a plug-in living inside a host runtime that owns all of
+ * HBM (weights, KV cache and arenas were sized at start-up and nothing is left to ask for), or a serving loop that can
+ * not afford the device-wide synchronisation an allocation or a free implies.  Such callers have no workspace to hand
+ * in, so this entry point keeps the quantised activations in a fixed scratch array that is part of the library image
+ * (ZEN_CUDA_NOALLOC_SCRATCH_BYTES of HBM on every GPU that loads the library, held until the process exits).  It calls
+ * no cudaMalloc / cudaFree and no allocating library routine, and it does not initialise the backend: the tensor must
+ * already be resident (zen_cuda_dev_upload), which is also what makes the backend ready.
+ *   - tokens * columns must not exceed ZEN_CUDA_NOALLOC_MAX_ACT_ELEMENTS; larger requests return 0 with a message.
+ *   - The first call on a device looks the scratch array's device address up (once per device); make that first call
+ *     before any stream capture begins.
+ *   - Every call uses the same array and finds the previous call's bytes in it (the part a call reads is rewritten,
+ *     and its scale area is cleared, first).  Two calls whose GPU work overlaps (different streams, or different
+ *     threads without ordering) race on it: order them on one stream or with events.
+ * d_x: device fp32 [tokens][columns]; d_out: device fp32 [tokens][rows]; stream: a cudaStream_t or NULL. */
+#define ZEN_CUDA_NOALLOC_MAX_ACT_ELEMENTS 2097152u /* e.g. 512 tokens x 4096 columns */
+#define ZEN_CUDA_NOALLOC_SCRATCH_BYTES (2097152u + 262144u)
+int zen_cuda_dev_gemm_q8_0_noalloc(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* stream);
+
 /* Device quantiser: d_x [tokens][columns] fp32 -> d_codes int8, d_scales fp32 [tokens][columns/32]. */
 int zen_cuda_dev_quantize_acts(const float* d_x, int8_t* d_codes, float* d_scales, size_t tokens, size_t columns, void* stream);
 

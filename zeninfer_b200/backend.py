@@ -34,6 +34,7 @@ ABI_SYMBOLS = (
     "zen_cuda_gemm_q6_k", "zen_cuda_gemm_q4_0", "zen_cuda_release_weights", "zen_cuda_quantize_acts",
     "zen_cuda_dev_upload", "zen_cuda_dev_free", "zen_cuda_dev_weight_bytes", "zen_cuda_dev_gemv",
     "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_gemm_workspace_bytes", "zen_cuda_dev_gemm_q8_0",
+    "zen_cuda_dev_gemm_q8_0_noalloc",
 )
 
 
@@ -99,6 +100,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_gemm_workspace_bytes.argtypes = [sz, sz]
     lib.zen_cuda_gemm_workspace_bytes.restype = sz
     lib.zen_cuda_dev_gemm_q8_0.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, vp, sz, vp]
+    lib.zen_cuda_dev_gemm_q8_0_noalloc.argtypes = [vp, vp, vp, sz, vp]
     return lib
 
 
@@ -232,6 +234,12 @@ class Backend:
         outs = (C.c_void_p * n)(*d_out)
         if not self.lib.zen_cuda_dev_gemm_q8_0(hs, outs, n, d_x, tokens, workspace, workspace_bytes, stream):
             self._fail("dev_gemm_q8_0")
+
+    def dev_gemm_q8_0_noalloc(self, handle: int, d_out: int, d_x: int, tokens: int, stream: int = 0) -> None:
+        """The prefill product for one resident tensor without any device allocation: the quantised activations live in a
+        scratch array built into the library (see zen_cuda_dev_gemm_q8_0_noalloc in include/zen_cuda.h for the limits)."""
+        if not self.lib.zen_cuda_dev_gemm_q8_0_noalloc(handle, d_out, d_x, tokens, stream):
+            self._fail("dev_gemm_q8_0_noalloc")
 
     def dev_quantize_acts(self, d_x: int, d_codes: int, d_scales: int, tokens: int, columns: int, stream: int = 0) -> None:
         if not self.lib.zen_cuda_dev_quantize_acts(d_x, d_codes, d_scales, tokens, columns, stream):

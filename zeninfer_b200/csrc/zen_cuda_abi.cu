@@ -533,6 +533,28 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
     return true;
 }
 
+// Scratch of the allocation-free GEMM entry point: part of the library image, one copy per GPU that loads it.
+// In host code this name is only a handle for the runtime; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[ZEN_CUDA_NOALLOC_SCRATCH_BYTES];
+
+// Device address of g_noalloc_scratch on the current device, looked up once per device.
+bool noalloc_scratch_address(State& s, uint8_t** out) {
+    constexpr int kMaxDevices = 64;
+    static uint8_t* by_device[kMaxDevices] = {};
+    int dev = -1;
+    ZC_CUDA(s, cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return set_error(s, "noalloc: unexpected device index");
+    if (dev != s.device) return set_error(s, "noalloc: the calling thread's current device is not the backend's device");
+    if (!by_device[dev]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) return set_error(s, std::string("noalloc: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
+        by_device[dev] = static_cast<uint8_t*>(p);
+    }
+    *out = by_device[dev];
+    return true;
+}
+
 bool ensure_gemm_ws(State& s, size_t bytes) {
     if (bytes <= s.d_gemm_ws_bytes) return true;
     if (s.d_gemm_ws) { cudaStreamSynchronize(s.stream); cudaFree(s.d_gemm_ws); }
@@ -835,6 +857,29 @@ int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out
     if (workspace_bytes < gemm_ws_bytes(tokens, w[0]->cols)) return set_error(s, "dev_gemm: workspace too small") ? 1 : 0;
     return enqueue_gemm_q8_0(s, w, d_out, count, d_x, tokens, static_cast<uint8_t*>(workspace),
                              stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
+}
+
+int zen_cuda_dev_gemm_q8_0_noalloc(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    // No lazy initialisation here: that would allocate.  A resident tensor implies a ready backend.
+    if (!s.ready) return set_error(s, "noalloc: backend not initialised; upload the tensor first") ? 1 : 0;
+    if (!w || !d_out || !d_x || !tokens) return set_error(s, "noalloc: bad arguments") ? 1 : 0;
+    if (w->format != ZEN_CUDA_Q8_0) return set_error(s, "noalloc: Q8_0 tensors only") ? 1 : 0;
+    if (tokens > ZEN_CUDA_NOALLOC_MAX_ACT_ELEMENTS / w->cols || gemm_ws_bytes(tokens, w->cols) > ZEN_CUDA_NOALLOC_SCRATCH_BYTES)
+        return set_error(s, "noalloc: tokens x columns = " + std::to_string(tokens * w->cols) + " exceeds the built-in scratch (" +
+                                std::to_string(ZEN_CUDA_NOALLOC_MAX_ACT_ELEMENTS) + " activation elements); use zen_cuda_dev_gemm_q8_0 with a caller workspace") ? 1 : 0;
+    uint8_t* scratch = nullptr;
+    if (!noalloc_scratch_address(s, &scratch)) return 0;
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : s.stream;
+    // The array still holds the previous call's bytes.  Codes of rows >= tokens are never read (the tensor map ends at
+    // `tokens`), but the padded tail of every scale row is, so the scale area starts from zero.
+    const size_t codes_bytes = (tokens * w->cols + 255) & ~size_t(255);
+    const size_t scale_bytes = gemm_ws_bytes(tokens, w->cols) - codes_bytes;
+    if (cudaMemsetAsync(scratch + codes_bytes, 0, scale_bytes, st) != cudaSuccess) return set_error(s, "noalloc: clearing the scale area failed") ? 1 : 0;
+    const zen_cuda_weights* ws[1] = {w};
+    float* outs[1] = {d_out};
+    return enqueue_gemm_q8_0(s, ws, outs, 1, d_x, tokens, scratch, st) ? 1 : 0;
 }
 
 int zen_cuda_dev_quantize_acts(const float* d_x, int8_t* d_codes, float* d_scales, size_t tokens, size_t columns, void* stream) {
