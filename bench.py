@@ -307,6 +307,9 @@ def main() -> None:
     ap.add_argument("--workload", default="q8_0_gemv")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU time for the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--min-warmup", type=int, default=1500,
+                    help="floor on the warm-up step count of the decode workload (about 0.3 s, so the clock sampler is up before "
+                         "the timed region); a profiler run lowers it so that few launches precede the captured ones")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl != "reference" else args.warmup
 
@@ -355,12 +358,11 @@ def main() -> None:
         with torch.cuda.graph(graph, stream=stream):
             one_pass()
         with ClockSampler(local) as clocks:
-            t_warm = time.time()
-            n_warm = 0
-            while n_warm < args.warmup or time.time() - t_warm < 0.3:  # at least W steps, and long enough for the clock sampler to come up
+            # At least W steps, and enough of them (about 0.3 s) for the clock sampler to come up.  The count is fixed,
+            # never time-based: every rank must replay the same number of collectives.
+            for n_warm in range(max(args.warmup, args.min_warmup)):
                 graph.replay()
-                n_warm += 1
-                if n_warm % 64 == 0:
+                if n_warm % 64 == 63:
                     stream.synchronize()
             stream.synchronize()
             be.dev_check(stream.cuda_stream)
@@ -420,9 +422,17 @@ def main() -> None:
     e2e_value = ALGO_BYTES_PER_LAUNCH * COPIES * e2e_steps * world / e2e_s / 1e9
     assert np.array_equal(y_host, y_dev), "host-pointer and device-pointer paths disagree"
 
-    if rank != 0:
+    def leave():
+        """Multi-rank exit: meet once more, then leave without tearing NCCL down under a live CUDA graph (a
+        destroy_process_group here was seen to block for ever); all results are already out."""
         if world > 1:
-            dist.destroy_process_group()
+            sys.stdout.flush()
+            torch.cuda.synchronize()
+            dist.barrier()
+            os._exit(0)
+
+    if rank != 0:
+        leave()
         return
 
     cpu = None
@@ -445,8 +455,7 @@ def main() -> None:
         "gpu_launches": launches,
     }
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    leave()
 
 
 if __name__ == "__main__":

@@ -127,3 +127,38 @@ def test_int8_mode_is_q8_0_only(be):
     with pytest.raises(BackendError):
         be.dev_gemv([h], [1], 1, 1, ACT_INT8)  # rejected on the host before any pointer is touched
     be.dev_free(h)
+
+
+@pytest.mark.parametrize("fmt", [Q4_0, Q6_K])
+def test_long_run_of_overlapped_launches_is_deterministic(be, zo, fmt):
+    """Thousands of launches back to back on one stream over several weight copies: every launch must reproduce the first
+    launch's bits and leave the error word clear (the ring protocol under overlap, as in the Q8_0 test of the same name)."""
+    import torch
+    rows = cols = 4096
+    dev = torch.device("cuda", 0)
+    copies, outs, rounds = 8, 64, 150
+    w = seeded_weights(fmt, rows, cols, 60)
+    handles = [be.dev_upload(NAMES[fmt], w, rows, cols) for _ in range(copies)]
+    x = seeded_acts(1, cols, 61)
+    d_x = torch.from_numpy(x).to(dev)
+    d_y = torch.zeros((outs, rows), dtype=torch.float32, device=dev)
+    ptrs = [d_y[i].data_ptr() for i in range(outs)]
+    stream = torch.cuda.Stream(device=dev)
+    bad = torch.zeros((), dtype=torch.int64, device=dev)
+    with torch.cuda.stream(stream):
+        be.dev_gemv([handles[0]], [ptrs[0]], d_x.data_ptr(), 1, 2, stream.cuda_stream)
+        stream.synchronize()
+        first = d_y[0].clone()
+        for rnd in range(rounds):
+            for i in range(outs):
+                be.dev_gemv([handles[(rnd + i) % copies]], [ptrs[i]], d_x.data_ptr(), 1, 2, stream.cuda_stream)
+            bad += (d_y != first[None, :]).sum()
+            d_y.zero_()
+            if rnd % 16 == 15:
+                stream.synchronize()
+        stream.synchronize()
+    be.dev_check(stream.cuda_stream)
+    assert int(bad.item()) == 0
+    assert_parity(first.cpu().numpy(), zo.gemv(fmt, w, x[0], rows, cols), what=f"{NAMES[fmt]} first launch vs oracle")
+    for h in handles:
+        be.dev_free(h)

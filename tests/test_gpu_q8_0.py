@@ -154,6 +154,43 @@ def test_config0_full_size_int8(be, zo):
     be.set_q8_act_mode(ACT_INT8)
 
 
+def test_long_run_of_overlapped_launches_is_deterministic(be, zo):
+    """Tens of thousands of launches back to back on one stream, each overlapping the tail of the one before
+    (programmatic dependent launch), over several weight copies so the stream comes from HBM.  Every launch must give
+    the first launch's bits, the error word must stay clear and the first result must match the oracle.  A ring protocol
+    that lets a consumer team run ahead of a copy still in flight shows up here (about one launch in 10^4) and nowhere
+    in a single-launch test."""
+    import torch
+    rows = cols = 4096
+    dev = torch.device("cuda", 0)
+    copies, outs, rounds = 8, 64, 400
+    ws = [seeded_weights(Q8_0, rows, cols, 40)] * 1
+    handles = [be.dev_upload("Q8_0", ws[0], rows, cols) for _ in range(copies)]
+    x = seeded_acts(1, cols, 41)
+    d_x = torch.from_numpy(x).to(dev)
+    d_y = torch.zeros((outs, rows), dtype=torch.float32, device=dev)
+    stream = torch.cuda.Stream(device=dev)
+    ptrs = [d_y[i].data_ptr() for i in range(outs)]
+    bad = torch.zeros((), dtype=torch.int64, device=dev)
+    with torch.cuda.stream(stream):
+        be.dev_gemv([handles[0]], [ptrs[0]], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream)
+        stream.synchronize()
+        first = d_y[0].clone()
+        for rnd in range(rounds):
+            for i in range(outs):
+                be.dev_gemv([handles[(rnd + i) % copies]], [ptrs[i]], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream)
+            bad += (d_y != first[None, :]).sum()
+            d_y.zero_()
+            if rnd % 16 == 15:
+                stream.synchronize()
+        stream.synchronize()
+    be.dev_check(stream.cuda_stream)
+    assert int(bad.item()) == 0, f"{int(bad.item())} output elements differed from the first launch over {rounds * outs} launches"
+    assert_parity(first.cpu().numpy(), zo.gemv(Q8_0, ws[0], x[0], rows, cols, int8_acts=True), what="first launch vs oracle")
+    for h in handles:
+        be.dev_free(h)
+
+
 def test_ffn_shapes_full_size(be, zo):
     # gate/up 14336x4096 and down 4096x14336 of config 2, checked through size-independent float64 references
     be.set_q8_act_mode(ACT_INT8)

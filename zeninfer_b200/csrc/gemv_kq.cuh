@@ -30,7 +30,7 @@ template <int kFormat> struct KqFormat;
 
 template <> struct KqFormat<2> {   // Q4_0: nibbles [K/2], f16 scales [K/32]
     static constexpr int kPlanes = 2;
-    static constexpr int kStages = 5;
+    static constexpr int kStages = 6;   // a multiple of the team count, see kGemvStages
     __host__ __device__ static constexpr uint32_t seg_bytes(int plane) { return plane == 0 ? kKqSegElems / 2 : kKqSegElems / 32 * 2; }
     __host__ __device__ static constexpr uint32_t bytes_per_256(int plane) { return plane == 0 ? 128 : 16; }
 };
@@ -112,6 +112,7 @@ template <int kFormat, int kBatch>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_constant__ KqParams p) {
     using F = KqFormat<kFormat>;
     constexpr int kStages = F::kStages;
+    static_assert(kStages % kTeams == 0, "ring depth must be a multiple of the number of consumer teams");
     constexpr uint32_t kStageBytes = kq_stage_bytes<kFormat>();
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t kpad = p.nseg * kKqSegElems;

@@ -44,9 +44,15 @@ constexpr int kGemvWarps = kTeamWarps * kTeams;     // consumer warps
 constexpr int kGemvSegBlocks = 128;                 // 32-element blocks per K segment: four per lane
 constexpr int kLaneBlocks = kGemvSegBlocks / 32;
 #ifndef ZK_GEMV_STAGES
-#define ZK_GEMV_STAGES 3
+#define ZK_GEMV_STAGES 4
 #endif
 constexpr int kGemvStages = ZK_GEMV_STAGES;
+// A parity wait is only meaningful to a waiter that has seen the barrier's previous phase complete: on a barrier still
+// one phase behind, the test for the next phase's parity passes at once.  Units go to teams in turn, so the ring depth
+// must be a multiple of the team count: then a stage always serves the same team, and that team observes every phase of
+// the stage's barrier in order.  (With an odd depth a team met a stage whose previous phase belonged to the other team,
+// could read it while its copy was still in flight and hand it back early.)
+static_assert(kGemvStages % kTeams == 0, "ring depth must be a multiple of the number of consumer teams");
 constexpr int kGemvThreads = (kGemvWarps + 1) * 32;
 constexpr int kMaxTasks = 8;                        // projections sharing one input (zen::hip::kMaxBatch, include/zen/hip_backend.h:70)
 
