@@ -312,6 +312,9 @@ def main() -> None:
     ap.add_argument("--workload", default="q8_0_gemv")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU time for the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: how the output shards are all-gathered after each product -- by the product kernel itself "
+                         "(peer stores over NVLink, the default) or by an NCCL all-gather launched after it")
     ap.add_argument("--min-warmup", type=int, default=1500,
                     help="floor on the warm-up step count of the decode workload (about 0.3 s, so the clock sampler is up before "
                          "the timed region); a profiler run lowers it so that few launches precede the captured ones")
@@ -349,9 +352,18 @@ def main() -> None:
     d_y = torch.zeros(ROWS, dtype=torch.float32, device=dev)
     d_all = torch.zeros(ROWS * world, dtype=torch.float32, device=dev) if world > 1 else None
     stream = torch.cuda.Stream(device=dev)
+    fused = world > 1 and args.gather == "fused"
+    pg = None
+    if fused:
+        from zeninfer_b200.shard import PeerGather
+        pg = PeerGather(be, world, rank, ROWS)  # collective: IPC handles travel through torch.distributed, once
 
     def one_pass():
         for h in handles:
+            if fused:   # the product kernel stores its outputs into every rank's gather region and publishes the launch;
+                        # the next launch waits on the device until all ranks have published: no collective launch
+                pg.gemv([h], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream, d_y=[d_y.data_ptr()])
+                continue
             be.dev_gemv([h], [d_y.data_ptr()], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream)
             if world > 1:
                 dist.all_gather_into_tensor(d_all, d_y)
@@ -403,6 +415,13 @@ def main() -> None:
 
     # --- correctness of what was timed (not part of the timed region) ---
     y_dev = d_y.cpu().numpy()
+    if world > 1:
+        if fused:
+            pg.fetch(d_all.data_ptr(), stream.cuda_stream)
+            stream.synchronize()
+            be.dev_check(stream.cuda_stream)
+        # every rank holds the same weights and input here, so every gathered shard must equal the local product
+        assert bool((d_all.view(world, ROWS) == d_y[None, :]).all().item()), "gathered shards differ from the local product"
 
     # --- e2e: the host-pointer call, host buffers, copies inside the timed region ---
     e2e_copies = [packed.copy() for _ in range(COPIES)]  # distinct host addresses => distinct resident tensors
@@ -450,7 +469,9 @@ def main() -> None:
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "rows_per_gpu": ROWS, "columns": COLS, "batch": 1, "activations": "int8 (bit-exact reference codes)",
                    "l2": f"inputs larger than L2: {COPIES} weight copies, {COPIES * ALGO_BYTES_PER_LAUNCH / 1e6:.0f} MB per pass",
-                   "launch": "CUDA graph replay, one kernel per copy" + ("; NCCL all-gather of output shards after each" if world > 1 else "")},
+                   "launch": "CUDA graph replay, one kernel per copy" + (
+                       "" if world == 1 else "; output shards all-gathered by the product kernel itself (peer stores over NVLink, device-side epoch flags)"
+                       if fused else "; NCCL all-gather of output shards after each")},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "traffic": GEMV_NCU_TRAFFIC_BYTES, "launch_us": per_launch_us, "algorithmic_bytes_per_launch": ALGO_BYTES_PER_LAUNCH},
         "cpu_baseline": cpu,

@@ -185,6 +185,41 @@ int zen_cuda_dev_gemm_q8_0_noalloc(const zen_cuda_weights* w, float* d_out, cons
 /* Device quantiser: d_x [tokens][columns] fp32 -> d_codes int8, d_scales fp32 [tokens][columns/32]. */
 int zen_cuda_dev_quantize_acts(const float* d_x, int8_t* d_codes, float* d_scales, size_t tokens, size_t columns, void* stream);
 
+/* ---- row-sharded products across GPUs: the output all-gather fused into the decode kernel ------------------------
+ * No counterpart in the reference, which drives one device; the row cut is its worker cut (ComputePool::parallel_for,
+ * src/compute_pool.cpp:104-106).  One process per GPU.  Every rank allocates a gather region, the ranks exchange the
+ * 64-byte IPC handles through whatever channel the host has (the tests and the benchmark use torch.distributed), open
+ * each other's regions and bind them into a gather object.  zen_cuda_dev_gemv_gather then runs the rank's shard of the
+ * product and stores every output into the rank's slot of EVERY rank's region from inside the product kernel (peer
+ * stores over NVLink); the grid's last CTA publishes the launch to all ranks.  A later launch on any rank that
+ * consumes the gathered vector waits on the device, with a time limit of about a second, until all ranks have published
+ * it; on expiry the error word is set (zen_cuda_dev_check) and nothing hangs.
+ *   - All ranks must enqueue the same sequence of gather launches on a gather object.
+ *   - A slot holds [tokens][sum of the launch's rows] floats and must fit slot_floats.
+ *   - The gathered vector of launch n, [world][slot_floats], stays intact until launch n+2 starts writing.
+ *   - Before zen_cuda_gather_destroy / zen_cuda_ipc_free the host must make sure (a barrier after a stream
+ *     synchronise) that no rank still has a launch in flight that writes here. */
+#define ZEN_CUDA_MAX_PEERS 8
+#define ZEN_CUDA_IPC_HANDLE_BYTES 64
+typedef struct zen_cuda_gather zen_cuda_gather;
+size_t zen_cuda_gather_region_bytes(size_t world, size_t slot_floats);
+/* cudaMalloc'd, zero-filled device memory whose IPC handle is written to handle_out; NULL on failure. */
+void* zen_cuda_ipc_alloc(size_t bytes, unsigned char handle_out[ZEN_CUDA_IPC_HANDLE_BYTES]);
+void* zen_cuda_ipc_open(const unsigned char handle[ZEN_CUDA_IPC_HANDLE_BYTES]); /* a peer's region, mapped here */
+void zen_cuda_ipc_close(void* peer_region);
+void zen_cuda_ipc_free(void* own_region);
+/* regions[r] = rank r's region as addressed from this process (regions[rank] = the own allocation). */
+zen_cuda_gather* zen_cuda_gather_create(size_t world, size_t rank, size_t slot_floats, void* const* regions);
+void zen_cuda_gather_destroy(zen_cuda_gather* g);
+/* The shard product of zen_cuda_dev_gemv with the gather fused in.  d_x == NULL: the input is the vector gathered by
+ * the previous launch on this object (columns must equal world * slot_floats, tokens 1).  d_y may be NULL (or hold
+ * NULL entries) when only the gathered copy is wanted. */
+int zen_cuda_dev_gemv_gather(zen_cuda_gather* g, const zen_cuda_weights* const* w, float* const* d_y, size_t count,
+                             const float* d_x, size_t tokens, int act_mode, void* stream);
+/* Waits (on the device, bounded) until the latest launch of every rank has landed here and copies the gathered
+ * vector, [world][slot_floats] floats, to d_out (NULL: wait only). */
+int zen_cuda_dev_gather_fetch(zen_cuda_gather* g, float* d_out, void* stream);
+
 /* Reads and clears the device-side error word the kernels set when a bounded wait gives up
  * (0 = none).  Synchronises `stream`. */
 int zen_cuda_dev_check(void* stream);

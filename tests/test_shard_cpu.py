@@ -84,3 +84,62 @@ def test_all_gather_and_pick_over_gloo(zo, tmp_path, world, rows):
         assert np.array_equal(got["full"].numpy(), ref, equal_nan=True)  # shards come from the same code, bit for bit
         assert got["pick_full"].tolist() == expect
         assert got["pick_sharded"].tolist() == expect
+
+
+class _FakeBackend:
+    """Stands in for the CUDA library in the collective set-up of PeerGather: hands out fake addresses and records calls."""
+
+    def __init__(self, rank):
+        self.rank, self.calls = rank, []
+
+    def gather_region_bytes(self, world, slot):
+        return 2 * world * slot * 4 + 64
+
+    def ipc_alloc(self, nbytes):
+        self.calls.append(("alloc", nbytes))
+        return 0x1000 * (self.rank + 1), bytes([self.rank]) * 64
+
+    def ipc_open(self, handle):
+        assert len(handle) == 64 and len(set(handle)) == 1
+        self.calls.append(("open", handle[0]))
+        return 0x100000 + handle[0]
+
+    def gather_create(self, world, rank, slot, regions):
+        self.calls.append(("create", world, rank, slot, tuple(regions)))
+        return 77
+
+    def gather_destroy(self, g):
+        self.calls.append(("destroy", g))
+
+    def ipc_close(self, p):
+        self.calls.append(("close", p))
+
+    def ipc_free(self, p):
+        self.calls.append(("free", p))
+
+
+def _gather_worker(rank: int, world: int, port: int, out_dir: str):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        be = _FakeBackend(rank)
+        pg = shard.PeerGather(be, world, rank, 4096)
+        pg.close()
+        pg.close()  # idempotent
+        torch.save(be.calls, os.path.join(out_dir, f"g{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_gather_setup_exchanges_handles_over_gloo(tmp_path):
+    world = 3
+    mp.spawn(_gather_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        calls = torch.load(os.path.join(tmp_path, f"g{r}.pt"))
+        own = 0x1000 * (r + 1)
+        expect_regions = tuple(own if q == r else 0x100000 + q for q in range(world))
+        assert calls[0] == ("alloc", 2 * world * 4096 * 4 + 64)
+        assert [c for c in calls if c[0] == "open"] == [("open", q) for q in range(world) if q != r]  # each peer once, never itself
+        assert ("create", world, r, 4096, expect_regions) in calls
+        assert calls[-1] == ("free", own) and calls.count(("destroy", 77)) == 1
+        assert sorted(c[1] for c in calls if c[0] == "close") == sorted(p for q, p in enumerate(expect_regions) if q != r)

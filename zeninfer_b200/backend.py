@@ -35,6 +35,8 @@ ABI_SYMBOLS = (
     "zen_cuda_dev_upload", "zen_cuda_dev_free", "zen_cuda_dev_weight_bytes", "zen_cuda_dev_gemv",
     "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_gemm_workspace_bytes", "zen_cuda_dev_gemm_q8_0",
     "zen_cuda_dev_gemm_q8_0_noalloc",
+    "zen_cuda_gather_region_bytes", "zen_cuda_ipc_alloc", "zen_cuda_ipc_open", "zen_cuda_ipc_close", "zen_cuda_ipc_free",
+    "zen_cuda_gather_create", "zen_cuda_gather_destroy", "zen_cuda_dev_gemv_gather", "zen_cuda_dev_gather_fetch",
 )
 
 
@@ -101,6 +103,22 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_gemm_workspace_bytes.restype = sz
     lib.zen_cuda_dev_gemm_q8_0.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, vp, sz, vp]
     lib.zen_cuda_dev_gemm_q8_0_noalloc.argtypes = [vp, vp, vp, sz, vp]
+    lib.zen_cuda_gather_region_bytes.argtypes = [sz, sz]
+    lib.zen_cuda_gather_region_bytes.restype = sz
+    lib.zen_cuda_ipc_alloc.argtypes = [sz, vp]
+    lib.zen_cuda_ipc_alloc.restype = vp
+    lib.zen_cuda_ipc_open.argtypes = [vp]
+    lib.zen_cuda_ipc_open.restype = vp
+    lib.zen_cuda_ipc_close.argtypes = [vp]
+    lib.zen_cuda_ipc_close.restype = None
+    lib.zen_cuda_ipc_free.argtypes = [vp]
+    lib.zen_cuda_ipc_free.restype = None
+    lib.zen_cuda_gather_create.argtypes = [sz, sz, sz, C.POINTER(vp)]
+    lib.zen_cuda_gather_create.restype = vp
+    lib.zen_cuda_gather_destroy.argtypes = [vp]
+    lib.zen_cuda_gather_destroy.restype = None
+    lib.zen_cuda_dev_gemv_gather.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), sz, vp, sz, i, vp]
+    lib.zen_cuda_dev_gather_fetch.argtypes = [vp, vp, vp]
     return lib
 
 
@@ -240,6 +258,57 @@ class Backend:
         scratch array built into the library (see zen_cuda_dev_gemm_q8_0_noalloc in include/zen_cuda.h for the limits)."""
         if not self.lib.zen_cuda_dev_gemm_q8_0_noalloc(handle, d_out, d_x, tokens, stream):
             self._fail("dev_gemm_q8_0_noalloc")
+
+    # ---- row-sharded products with the output all-gather fused into the kernel (one process per GPU) ----
+    IPC_HANDLE_BYTES = 64
+
+    def gather_region_bytes(self, world: int, slot_floats: int) -> int:
+        return int(self.lib.zen_cuda_gather_region_bytes(world, slot_floats))
+
+    def ipc_alloc(self, nbytes: int) -> tuple[int, bytes]:
+        """Zero-filled device memory other processes can map: (device pointer, 64-byte handle to send them)."""
+        handle = (C.c_ubyte * self.IPC_HANDLE_BYTES)()
+        p = self.lib.zen_cuda_ipc_alloc(nbytes, handle)
+        if not p:
+            self._fail("ipc_alloc")
+        return int(p), bytes(handle)
+
+    def ipc_open(self, handle: bytes) -> int:
+        buf = (C.c_ubyte * self.IPC_HANDLE_BYTES).from_buffer_copy(handle)
+        p = self.lib.zen_cuda_ipc_open(buf)
+        if not p:
+            self._fail("ipc_open")
+        return int(p)
+
+    def ipc_close(self, peer_region: int) -> None:
+        self.lib.zen_cuda_ipc_close(peer_region)
+
+    def ipc_free(self, own_region: int) -> None:
+        self.lib.zen_cuda_ipc_free(own_region)
+
+    def gather_create(self, world: int, rank: int, slot_floats: int, regions: Sequence[int]) -> int:
+        arr = (C.c_void_p * world)(*regions)
+        g = self.lib.zen_cuda_gather_create(world, rank, slot_floats, arr)
+        if not g:
+            self._fail("gather_create")
+        return int(g)
+
+    def gather_destroy(self, gather: int) -> None:
+        self.lib.zen_cuda_gather_destroy(gather)
+
+    def dev_gemv_gather(self, gather: int, handles: Sequence[int], d_y: Sequence[int] | None, d_x: int | None, tokens: int,
+                        act_mode: int, stream: int = 0) -> None:
+        """The shard product with every output also stored into each rank's gather region by the kernel itself.
+        d_x None: the input is what the previous launch on this gather object gathered."""
+        n = len(handles)
+        hs = (C.c_void_p * n)(*handles)
+        ys = (C.c_void_p * n)(*d_y) if d_y is not None else None
+        if not self.lib.zen_cuda_dev_gemv_gather(gather, hs, ys, n, d_x, tokens, act_mode, stream):
+            self._fail("dev_gemv_gather")
+
+    def dev_gather_fetch(self, gather: int, d_out: int | None, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_gather_fetch(gather, d_out, stream):
+            self._fail("dev_gather_fetch")
 
     def dev_quantize_acts(self, d_x: int, d_codes: int, d_scales: int, tokens: int, columns: int, stream: int = 0) -> None:
         if not self.lib.zen_cuda_dev_quantize_acts(d_x, d_codes, d_scales, tokens, columns, stream):

@@ -65,11 +65,12 @@ struct KqTask {
 struct KqParams {
     KqTask task[kMaxTasks];
     uint32_t ntasks, total_rows;
-    const float* x;         // [batch][K] fp32
+    const float* x;         // [batch][K] fp32; null with a gather: the vector gathered by the previous launch
     uint32_t K;             // columns, a multiple of the format's block size
     uint32_t nseg;          // ceil(K / kKqSegElems)
     uint32_t pitch[kKqMaxPlanes];  // global row pitch of each plane, bytes
     int* error_word;
+    PeerGather gather;      // world == 0: outputs go to task[].y only
 };
 
 template <int kFormat>
@@ -123,10 +124,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
     uint64_t* full = reinterpret_cast<uint64_t*>(xsum + static_cast<size_t>(kBatch) * (kpad / 32));
     uint64_t* empty = full + kStages;
     volatile int* abort_word = reinterpret_cast<volatile int*>(empty + kStages);
+    float* stash = reinterpret_cast<float*>(empty + kStages + 2);   // gather only: [batch][rows of this CTA's slice]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint32_t r_first, r_last;
     cta_row_slice(p.total_rows, blockIdx.x, gridDim.x, r_first, r_last);
+    const uint32_t n_mine = r_last - r_first;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -196,6 +199,15 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
 
     // ---------------- consumer warps ----------------
     pdl_wait();
+    // Row-sharded launch (peer_gather.cuh): wait for every rank's previous launch; a null x means "what it gathered".
+    unsigned long long epoch = 0;
+    const float* x_src = p.x;
+    if (p.gather.world) {
+        if (!gather_begin(p.gather, lane, epoch)) {
+            if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrPeerWaitTimeout); }
+        }
+        if (!x_src) x_src = gather_previous(p.gather, epoch);
+    }
     // Prologue: two-digit quantisation of the activations, natural element order.
     {
         const uint32_t quad = static_cast<uint32_t>(lane) >> 2, part = static_cast<uint32_t>(lane) & 3;
@@ -204,9 +216,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
             for (uint32_t b0 = warp * 8; b0 < nblk; b0 += kGemvWarps * 8) {
                 const uint32_t b = b0 + quad;
                 const bool live = b < nblk;
-                const float4* src = reinterpret_cast<const float4*>(p.x + static_cast<size_t>(t) * p.K + b * 32 + part * 8);
+                const float4* src = reinterpret_cast<const float4*>(x_src + static_cast<size_t>(t) * p.K + b * 32 + part * 8);
                 const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-                const float4 lo = live ? __ldg(src) : zero, hi = live ? __ldg(src + 1) : zero;
+                const float4 lo = live ? __ldcg(src) : zero, hi = live ? __ldcg(src + 1) : zero;  // L2: coherent with peers' stores
                 const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
                 uint2 c1, c2;
                 const float d = quantise_block_quad(v, c1, c2);
@@ -229,14 +241,15 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
     asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");
 
     const int team = warp / kTeamWarps, twarp = warp % kTeamWarps;
-    bool ok = true;
+    bool ok = *abort_word == 0;
     uint32_t pair_base = 0;
     KqWalk walk(r_first, r_last);
     while (!walk.done() && ok) {
         RowGroup pair[kTeams];
 #pragma unroll
         for (int m = 0; m < kTeams; ++m) pair[m] = walk.next(p);
-        const RowGroup g = team == 0 ? pair[0] : pair[1];
+        RowGroup g = pair[0];
+        if constexpr (kTeams > 1) { if (team == 1) g = pair[kTeams - 1]; }
         const KqTask& t = p.task[g.task];
         const uint32_t row = g.row0 + twarp;
         const bool valid = static_cast<uint32_t>(twarp) < g.nrows;
@@ -326,9 +339,16 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                 float v = acc[tk];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0) t.y[static_cast<size_t>(tk) * t.rows + row] = v;
+                if (lane == 0 && t.y) t.y[static_cast<size_t>(tk) * t.rows + row] = v;
+                if (lane == 0 && p.gather.world) stash[static_cast<size_t>(tk) * n_mine + (t.first_row + row - r_first)] = v;
             }
         }
+    }
+    if (p.gather.world) {
+        asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");
+        gather_push(p.gather, epoch, stash, n_mine, r_first, p.total_rows, kBatch, warp, kGemvWarps, lane);
+        asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");
+        if (threadIdx.x == 0) gather_finish(p.gather, epoch);
     }
 }
 

@@ -29,17 +29,25 @@
 //   * per 32-element block: 8 dp4a per digit, one int->float conversion and one
 //     fused multiply-add with the fp16 block scale times the activation scale.
 //
+//   * with a peer gather attached (row-sharded tensor, one GPU per shard) the finishing warp
+//     also stores each output into every rank's gather region and the grid's last CTA
+//     publishes the launch (peer_gather.cuh): the all-gather costs no launch of its own.
+//
 // Algorithmic traffic is the raw GGUF size: 34 bytes per block.
 #pragma once
 #include <cuda_fp16.h>
 
+#include "peer_gather.cuh"
 #include "quantize_acts.cuh"
 #include "zk_ptx.cuh"
 
 namespace zk {
 
 constexpr int kTeamWarps = 8;                       // warps per team == rows per row group
-constexpr int kTeams = 2;
+#ifndef ZK_GEMV_TEAMS
+#define ZK_GEMV_TEAMS 2
+#endif
+constexpr int kTeams = ZK_GEMV_TEAMS;               // 1 or 2
 constexpr int kGemvWarps = kTeamWarps * kTeams;     // consumer warps
 constexpr int kGemvSegBlocks = 128;                 // 32-element blocks per K segment: four per lane
 constexpr int kLaneBlocks = kGemvSegBlocks / 32;
@@ -69,13 +77,19 @@ struct GemvTask {
     uint32_t first_row;      // index of this task's first row in the launch's concatenated row space
 };
 
+// Kernel parameters live in constant memory that is cold on every SM at the start of every launch, and a warp stalls
+// on each line it misses (about half a microsecond, one after the other).  So everything a single-tensor launch needs
+// sits in the first 64 bytes (the scalars and task[0]; blocks per row, padded pitch and segment count are derived from
+// K), and the consumer warps touch the remaining lines, one line per warp, while they wait for the previous grid.
 struct GemvParams {
-    GemvTask task[kMaxTasks];
-    uint32_t ntasks;
-    uint32_t total_rows;     // over all tasks
-    const float* x;          // [batch][K] fp32
-    uint32_t K, nb, nbp, nseg;
+    const float* x;          // [batch][K] fp32; null with a gather: the vector gathered by the previous launch
     int* error_word;         // set to a zk::kErr* code when a bounded wait gives up
+    uint32_t total_rows;     // over all tasks
+    uint32_t ntasks;
+    uint32_t K;              // columns; nb = K / 32 blocks per row, scale pitch nb rounded up to 8, nseg = ceil(nb / 128)
+    uint32_t pad;
+    GemvTask task[kMaxTasks];
+    PeerGather gather;       // world == 0: outputs go to task[].y only
 #ifdef ZK_TRACE
     unsigned long long* trace;  // [grid][16] phase stamps (profiling builds only)
 #endif
@@ -83,10 +97,15 @@ struct GemvParams {
 
 #ifdef ZK_TRACE
 __device__ __forceinline__ unsigned long long zk_globaltimer() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define ZK_STAMP(slot) do { if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + (slot)] = zk_globaltimer(); } while (0)
+#define ZK_STAMP(slot) do { if (trace_base && threadIdx.x == 0) trace_base[blockIdx.x * 16 + (slot)] = zk_globaltimer(); } while (0)
 #else
 #define ZK_STAMP(slot) do {} while (0)
 #endif
+
+// Shared memory a launch with a peer gather adds: one float per (token, row of the largest CTA slice).
+__host__ __device__ inline size_t gather_stash_bytes(uint32_t total_rows, uint32_t grid, int batch) {
+    return static_cast<size_t>(batch) * ((total_rows + grid - 1) / grid) * sizeof(float);
+}
 
 __host__ __device__ inline size_t gemv_q8_0_smem_bytes(uint32_t nseg, int batch, int digits) {
     const size_t kpad_blocks = static_cast<size_t>(nseg) * kGemvSegBlocks;
@@ -146,22 +165,31 @@ template <int kBatch, int kDigits>
 __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV_MIN_CTAS : 1))
     gemv_q8_0_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    const uint32_t kpad_blocks = p.nseg * kGemvSegBlocks;
+    const uint32_t nb = p.K >> 5, nbp = (nb + 7) & ~7u, nseg = (nb + kGemvSegBlocks - 1) / kGemvSegBlocks;
+    const uint32_t kpad_blocks = nseg * kGemvSegBlocks;
     uint8_t* ring = smem;
     uint4* xcodes = reinterpret_cast<uint4*>(ring + kGemvStages * kQ8StageBytes);           // [batch][digit][kpad_blocks*2]
     float* xscale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xcodes) + static_cast<size_t>(kBatch) * kDigits * kpad_blocks * 32);
     uint64_t* full = reinterpret_cast<uint64_t*>(xscale + static_cast<size_t>(kBatch) * kpad_blocks);
     uint64_t* empty = full + kGemvStages;
     volatile int* abort_word = reinterpret_cast<volatile int*>(empty + kGemvStages);
+    float* stash = reinterpret_cast<float*>(empty + kGemvStages + 2);   // gather only: [batch][rows of this CTA's slice]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef ZK_TRACE
+    unsigned long long* const trace_base = p.trace;
+#endif
     ZK_STAMP(0);
+#ifdef ZK_TRACE
+    if (trace_base && threadIdx.x == 0) { unsigned sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); trace_base[blockIdx.x * 16 + 13] = sm; }
+#endif
     uint32_t r_first, r_last;
     cta_row_slice(p.total_rows, blockIdx.x, gridDim.x, r_first, r_last);
+    const uint32_t n_mine = r_last - r_first;
     // A group of whole single-segment rows is contiguous in both planes: one copy each.
-    const bool contiguous = p.nseg == 1 && p.nb == p.nbp;
-    const uint32_t cstride = contiguous ? p.nb * 32 : kGemvSegBlocks * 32;  // stage row pitch of the codes, bytes
-    const uint32_t sstride = contiguous ? p.nb : kGemvSegBlocks;             // stage row pitch of the scales, halves
+    const bool contiguous = nseg == 1 && nb == nbp;
+    const uint32_t cstride = contiguous ? nb * 32 : kGemvSegBlocks * 32;  // stage row pitch of the codes, bytes
+    const uint32_t sstride = contiguous ? nb : kGemvSegBlocks;             // stage row pitch of the scales, halves
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemvStages; ++s) {
@@ -177,20 +205,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
 
     if (warp == kGemvWarps) {
         // ---------------- producer warp: weights are constants, no need to wait for the previous grid ----------------
-        if (lane == 0) {
-            // Pull what the ring cannot hold yet into L2, so later refills do not pay DRAM latency.
-            const uint32_t ring_rows = kGemvStages * kTeamWarps / p.nseg;
-            uint32_t budget = kL2PrefetchCap;
-            GroupWalk pre(r_first + min(ring_rows, r_last - r_first), r_last);
-            while (!pre.done() && budget) {
-                const RowGroup g = pre.next(p);
-                const GemvTask& t = p.task[g.task];
-                const uint32_t cb = min(g.nrows * p.K, budget);
-                l2_prefetch(t.codes + static_cast<size_t>(g.row0) * p.K, (cb + 15) & ~15u);
-                l2_prefetch(t.scales + static_cast<size_t>(g.row0) * p.nbp, (g.nrows * p.nbp * 2 + 15) & ~15u);
-                budget -= cb;
-            }
-        }
+        bool met = false;   // has the L2 prefetch of the rows beyond the ring's first fill been issued yet
         uint32_t unit = 0;
         bool ok = true;
         GroupWalk walk(r_first, r_last);
@@ -198,10 +213,27 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
             RowGroup pair[kTeams];
 #pragma unroll
             for (int m = 0; m < kTeams; ++m) pair[m] = walk.next(p);
-            for (uint32_t s = 0; s < p.nseg && ok; ++s) {
+            for (uint32_t s = 0; s < nseg && ok; ++s) {
 #pragma unroll
                 for (int m = 0; m < kTeams; ++m, ++unit) {
                     const uint32_t stage = unit % kGemvStages;
+                    if (unit >= kGemvStages && !met) {
+                        met = true;
+                        if (lane == 0) {
+                            // Pull what the ring cannot hold yet into L2, so later refills do not pay DRAM latency.
+                            uint32_t budget = kL2PrefetchCap;
+                            GroupWalk pre(r_first + min(static_cast<uint32_t>(kGemvStages * kTeamWarps) / nseg, n_mine), r_last);
+                            while (!pre.done() && budget) {
+                                const RowGroup g = pre.next(p);
+                                const GemvTask& t = p.task[g.task];
+                                const uint32_t cb = min(g.nrows * p.K, budget);
+                                l2_prefetch(t.codes + static_cast<size_t>(g.row0) * p.K, (cb + 15) & ~15u);
+                                l2_prefetch(t.scales + static_cast<size_t>(g.row0) * nbp, (g.nrows * nbp * 2 + 15) & ~15u);
+                                budget -= cb;
+                            }
+                        }
+                        __syncwarp();
+                    }
                     if (unit >= kGemvStages) {
                         if (!mbar_wait(&empty[stage], ((unit / kGemvStages) - 1) & 1)) {
                             if (lane == 0) { *abort_word = 1; atomicExch(p.error_word, kErrEmptyWaitTimeout); }
@@ -219,14 +251,17 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
                     const GemvTask& t = p.task[g.task];
                     uint8_t* st = ring + stage * kQ8StageBytes;
                     if (contiguous) {
-                        const uint32_t cbytes = g.nrows * p.K, sbytes = g.nrows * p.nb * 2;
+                        const uint32_t cbytes = g.nrows * p.K, sbytes = g.nrows * nb * 2;
                         if (lane == 0) {
                             mbar_arrive_expect_tx(&full[stage], cbytes + sbytes);
                             bulk_g2s(st, t.codes + static_cast<size_t>(g.row0) * p.K, cbytes, &full[stage]);
-                            bulk_g2s(st + kQ8StageCodeBytes, t.scales + static_cast<size_t>(g.row0) * p.nbp, sbytes, &full[stage]);
+                            bulk_g2s(st + kQ8StageCodeBytes, t.scales + static_cast<size_t>(g.row0) * nbp, sbytes, &full[stage]);
+#ifdef ZK_TRACE
+                            if (trace_base && unit == 0) trace_base[blockIdx.x * 16 + 11] = zk_globaltimer();
+#endif
                         }
                     } else {
-                        const uint32_t nblk = min(static_cast<uint32_t>(kGemvSegBlocks), p.nb - s * kGemvSegBlocks);
+                        const uint32_t nblk = min(static_cast<uint32_t>(kGemvSegBlocks), nb - s * kGemvSegBlocks);
                         const uint32_t cbytes = nblk * 32, sbytes = (nblk * 2 + 15) & ~15u;
                         if (lane == 0) mbar_arrive_expect_tx(&full[stage], g.nrows * (cbytes + sbytes));
                         __syncwarp();
@@ -236,7 +271,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
                         } else if (lane >= 16 && lane < 16 + static_cast<int>(g.nrows)) {
                             const int r = lane - 16;
                             bulk_g2s(st + kQ8StageCodeBytes + r * (kGemvSegBlocks * 2),
-                                     t.scales + static_cast<size_t>(g.row0 + r) * p.nbp + static_cast<size_t>(s) * kGemvSegBlocks, sbytes, &full[stage]);
+                                     t.scales + static_cast<size_t>(g.row0 + r) * nbp + static_cast<size_t>(s) * kGemvSegBlocks, sbytes, &full[stage]);
                         }
                     }
                 }
@@ -255,9 +290,35 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
     }
 
     // ---------------- consumer warps ----------------
+    // While the previous grid drains: pull the parameter lines needed later into the constant cache, a different
+    // 64-byte line per warp so the misses overlap (line 0, the scalars and task[0], is warm already).
+    {
+        uint32_t touched = 0;
+        switch (warp & 7) {
+        case 0: touched = p.task[1].rows; break;                                                   // bytes  64..127
+        case 1: touched = p.task[3].rows; break;                                                   // bytes 128..191
+        case 2: touched = p.task[5].rows; break;                                                   // bytes 192..255
+        case 3: touched = p.task[7].rows; break;                                                   // bytes 256..319
+        case 4: touched = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.gather.region[4])); break;   // 320..383
+        case 5: touched = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.gather.flags[4])); break;    // 384..447
+        case 6: touched = p.gather.world; break;                                                   // 448..
+        default: break;
+        }
+        asm volatile("" ::"r"(touched));
+    }
     // The activations (and the output buffers) belong to the stream's earlier work: wait for it.
     pdl_wait();
     ZK_STAMP(1);
+    // Row-sharded launch: every rank must have published the launch before this one (its outputs are this launch's
+    // input when x is null, and the slot parity written now was last read during that launch).
+    unsigned long long epoch = 0;
+    const float* x_src = p.x;
+    if (p.gather.world) {
+        if (!gather_begin(p.gather, lane, epoch)) {
+            if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrPeerWaitTimeout); }
+        }
+        if (!x_src) x_src = gather_previous(p.gather, epoch);
+    }
     // Prologue: quantise the activations into the lane-major layout.  Block b = 32*g + l is read by
     // lane l; its two 16-byte halves are stored in the order that lane loads them (half ((l>>2)&1)
     // first), which keeps both the weight and the activation loads conflict-free.
@@ -266,12 +327,13 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
     {
         const uint32_t quad = static_cast<uint32_t>(lane) >> 2, part = static_cast<uint32_t>(lane) & 3;
         for (int t = 0; t < kBatch; ++t) {
-            for (uint32_t b0 = warp * 8; b0 < p.nb; b0 += kGemvWarps * 8) {  // warp-uniform trip count: the quantiser shuffles
+            for (uint32_t b0 = warp * 8; b0 < nb; b0 += kGemvWarps * 8) {  // warp-uniform trip count: the quantiser shuffles
                 const uint32_t b = b0 + quad;
-                const bool live = b < p.nb;
-                const float4* src = reinterpret_cast<const float4*>(p.x + static_cast<size_t>(t) * p.K + b * 32 + part * 8);
+                const bool live = b < nb;
+                const float4* src = reinterpret_cast<const float4*>(x_src + static_cast<size_t>(t) * p.K + b * 32 + part * 8);
                 const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-                const float4 lo = live ? __ldg(src) : zero, hi = live ? __ldg(src + 1) : zero;
+                // L2 is the point of coherence for what earlier kernels and peers wrote: bypass L1
+                const float4 lo = live ? __ldcg(src) : zero, hi = live ? __ldcg(src + 1) : zero;
                 const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
                 uint2 c1, c2;
                 const float d = quantise_block_quad(v, c1, c2);
@@ -292,20 +354,20 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
     ZK_STAMP(3);
 
     const int team = warp / kTeamWarps, twarp = warp % kTeamWarps;
-    bool ok = true;
+    bool ok = *abort_word == 0;
     const uint32_t h0 = (static_cast<uint32_t>(lane) >> 2) & 1;
 
     // Batch-1 int8 rows of one segment (K <= 4096): a lane meets the same four activation blocks in
     // every row, so they live in registers and the inner loop reads only weights.
     constexpr bool kCanHoldX = (kBatch == 1 && kDigits == 1);
-    const bool x_in_regs = kCanHoldX && p.nseg == 1;
+    const bool x_in_regs = kCanHoldX && nseg == 1;
     uint4 xra[kCanHoldX ? kLaneBlocks : 1], xrb[kCanHoldX ? kLaneBlocks : 1];
     float xrs[kCanHoldX ? kLaneBlocks : 1];
     if (x_in_regs) {
 #pragma unroll
         for (int j = 0; j < kLaneBlocks; ++j) {
             const uint32_t b = j * 32 + lane;
-            const bool live = b < p.nb;
+            const bool live = b < nb;
             const uint4 z = make_uint4(0, 0, 0, 0);
             xra[j] = live ? xcodes[static_cast<size_t>(j) * 64 + lane] : z;
             xrb[j] = live ? xcodes[static_cast<size_t>(j) * 64 + 32 + lane] : z;
@@ -320,7 +382,8 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
         RowGroup pair[kTeams];
 #pragma unroll
         for (int m = 0; m < kTeams; ++m) pair[m] = walk.next(p);
-        const RowGroup g = team == 0 ? pair[0] : pair[1];  // no runtime-indexed local array
+        RowGroup g = pair[0];
+        if constexpr (kTeams > 1) { if (team == 1) g = pair[kTeams - 1]; }  // no runtime-indexed local array
         const GemvTask& t = p.task[g.task];
         const uint32_t row = g.row0 + twarp;
         const bool valid = static_cast<uint32_t>(twarp) < g.nrows;
@@ -328,7 +391,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) acc[b] = 0.0f;
 
-        for (uint32_t s = 0; s < p.nseg; ++s) {
+        for (uint32_t s = 0; s < nseg; ++s) {
             const uint32_t unit = pair_base + s * kTeams + team;
             const uint32_t stage = unit % kGemvStages;
             if (*abort_word || !mbar_wait(&full[stage], (unit / kGemvStages) & 1)) {
@@ -354,14 +417,14 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
                         const float dw = __half2float(ws[bl]);
                         const int isum = dot32(wa, wb, xra[i], xrb[i]);
                         const float term = (dw * xrs[i]) * static_cast<float>(isum);
-                        acc[0] += bl < p.nb ? term : 0.0f;
+                        acc[0] += bl < nb ? term : 0.0f;
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < kLaneBlocks; ++i) {
                         const uint32_t bl = i * 32 + lane;           // block within the segment
                         const uint32_t b = s * kGemvSegBlocks + bl;  // block within the row
-                        if (b < p.nb) {
+                        if (b < nb) {
                             const uint4 wa = wq[bl * 2 + h0], wb = wq[bl * 2 + (h0 ^ 1)];
                             const float dw = __half2float(ws[bl]);
                             const size_t slot = (static_cast<size_t>(b >> 5) * 2) * 32 + lane;
@@ -378,7 +441,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
                 }
             }
 #ifdef ZK_TRACE
-            if (team == 0 && unit < 4) { if (acc[0] == 123.456f) p.trace[0] = 1; ZK_STAMP(6 + 3 * (unit >> 1)); }
+            if (team == 0 && unit < 4) { if (acc[0] == 123.456f) trace_base[0] = 1; ZK_STAMP(6 + 3 * (unit >> 1)); }
 #endif
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);
@@ -387,14 +450,15 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
 #ifdef ZK_TRACE
         const uint32_t traced_unit = pair_base;
 #endif
-        pair_base += kTeams * p.nseg;
+        pair_base += kTeams * nseg;
         if (valid) {
 #pragma unroll
             for (int tk = 0; tk < kBatch; ++tk) {
                 float v = acc[tk];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0) t.y[static_cast<size_t>(tk) * t.rows + row] = v;
+                if (lane == 0 && t.y) t.y[static_cast<size_t>(tk) * t.rows + row] = v;
+                if (lane == 0 && p.gather.world) stash[static_cast<size_t>(tk) * n_mine + (t.first_row + row - r_first)] = v;
             }
         }
 #ifdef ZK_TRACE
@@ -402,6 +466,12 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
 #endif
     }
     ZK_STAMP(12);
+    if (p.gather.world) {
+        asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");   // the slice's outputs are all in the stash
+        gather_push(p.gather, epoch, stash, n_mine, r_first, p.total_rows, kBatch, warp, kGemvWarps, lane);
+        asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");
+        if (threadIdx.x == 0) gather_finish(p.gather, epoch);
+    }
 }
 
 }  // namespace zk

@@ -1,0 +1,138 @@
+// Output all-gather fused into the decode kernels, over peer memory (NVLink / NVSwitch).
+//
+// A projection is sharded by output rows, one shard per GPU (one process per GPU).  Instead of
+// running the product and then a separate collective, the product kernel itself delivers its
+// outputs: a CTA collects the outputs of its row slice in shared memory and, when the slice is
+// done, copies the run into the same slot of every rank's gather region with coalesced peer
+// stores; the last CTA of the grid to finish then publishes the launch's number into every
+// rank's flag array.  A kernel that consumes the gathered vector (the next launch in the chain,
+// or gather_fetch_kernel) waits, with a clock budget, until all ranks' flags have reached the
+// number it needs.  No host round trip, no extra launch, and the next launch's weight stream
+// overlaps the link latency.  The reference drives one device and has no counterpart of this
+// file; the row cut it mirrors is ComputePool::parallel_for's (src/compute_pool.cpp:104-106).
+//
+// Region layout in each rank's memory (allocated once, zero-filled, shared through CUDA IPC):
+//     float  data[2][world][slot_floats]      two parities: launch L writes parity L & 1
+//     u64    flags[kMaxPeers]                 flags[r] = number of launches rank r has published here
+// Launch L (1-based) of a rank may only start writing once every rank has published L-1, so a
+// rank is never more than one launch ahead of any other and the parity it overwrites (that of
+// launch L-2) is no longer being read by anyone.
+//
+// Ordering, and why it looks the way it does: a fence at system scope costs this GPU tens of
+// nanoseconds that do not overlap with other such fences, so a launch may afford one, not one per
+// CTA or per warp (148 of them were measured at about 10 us per launch).  Writers of a CTA meet
+// at a CTA barrier after their peer stores; one thread then fences at GPU scope and counts the
+// CTA in with an atomic; the thread that completes the count fences ONCE at system scope --
+// fences are cumulative, so this covers the stores of every CTA it has synchronised with -- and
+// stores the flags.  Readers poll their own (local) flags with relaxed system-scope loads and
+// read the data through L2 (never L1), the point where peer stores to local memory land.
+// Only loads of local memory ever spin.
+#pragma once
+#include <cstdint>
+
+#include "zk_ptx.cuh"
+
+namespace zk {
+
+constexpr int kMaxPeers = 8;
+enum : int { kErrPeerWaitTimeout = 5 };
+
+struct PeerGather {
+    float* region[kMaxPeers];                 // data base of every rank's region (own entry = local memory)
+    unsigned long long* flags[kMaxPeers];     // flag array of every rank's region
+    float* local_region;
+    const unsigned long long* local_flags;
+    unsigned long long* epoch;                // local: launches this rank has completed
+    unsigned int* arrive;                     // local: CTAs of the running launch that have finished
+    uint32_t world, rank, slot_floats;        // world == 0: no gather, the kernel writes its ordinary outputs only
+    uint32_t grid;                            // CTAs of every gather launch on this object, the same on all ranks
+};
+
+__host__ __device__ inline size_t peer_region_data_bytes(size_t world, size_t slot_floats) { return 2 * world * slot_floats * sizeof(float); }
+__host__ __device__ inline size_t peer_region_flag_offset(size_t world, size_t slot_floats) {
+    return ((peer_region_data_bytes(world, slot_floats) + 255) / 256) * 256;
+}
+__host__ __device__ inline size_t peer_region_bytes(size_t world, size_t slot_floats) {
+    return peer_region_flag_offset(world, slot_floats) + static_cast<size_t>(kMaxPeers) * sizeof(unsigned long long);
+}
+
+__device__ __forceinline__ unsigned long long ld_relaxed_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_relaxed_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
+// Warp-wide; every consumer warp of a CTA calls it after the previous grid in the stream has completed.  Returns
+// the number of launches this rank has completed so far (this launch is number epoch + 1) and waits until every rank
+// has published that many; false (warp-uniform) when the clock budget ran out first.
+__device__ __forceinline__ bool gather_begin(const PeerGather& g, int lane, unsigned long long& epoch) {
+    epoch = *reinterpret_cast<volatile unsigned long long*>(g.epoch);
+    bool ok = true;
+    if (lane < static_cast<int>(g.world)) {
+        const unsigned long long* f = g.local_flags + lane;
+        if (ld_relaxed_sys(f) < epoch) {
+            const long long t0 = clock64();
+            while (ld_relaxed_sys(f) < epoch)
+                if (clock64() - t0 > kWaitBudgetCycles) { ok = false; break; }
+        }
+    }
+    __threadfence();   // GPU scope: nothing that follows is satisfied from before the flags were seen
+    return __all_sync(0xffffffffu, ok);
+}
+
+// Where launch (epoch + 1) of this rank puts element `off` of its slot, in rank `peer`'s region.
+__device__ __forceinline__ float* gather_slot(const PeerGather& g, unsigned long long epoch, uint32_t peer, uint32_t off) {
+    const size_t parity = static_cast<size_t>((epoch + 1) & 1);
+    return g.region[peer] + (parity * g.world + g.rank) * g.slot_floats + off;
+}
+// The vector gathered by the launch before this one (what a chained launch reads as its input), in local memory.
+__device__ __forceinline__ const float* gather_previous(const PeerGather& g, unsigned long long epoch) {
+    return g.local_region + static_cast<size_t>(epoch & 1) * g.world * g.slot_floats;
+}
+
+// Copies a CTA's finished outputs -- stash[token][n_mine], rows [r_first, r_first + n_mine) of the launch's row space
+// -- into every rank's region.  Jobs (rank, token) are dealt to warps; a warp stores 32 consecutive floats at a time.
+__device__ __forceinline__ void gather_push(const PeerGather& g, unsigned long long epoch, const float* stash, uint32_t n_mine,
+                                            uint32_t r_first, uint32_t total_rows, uint32_t tokens, int warp, int nwarps, int lane) {
+    for (uint32_t job = warp; job < g.world * tokens; job += nwarps) {
+        const uint32_t peer = job % g.world, tk = job / g.world;
+        float* dst = gather_slot(g, epoch, peer, tk * total_rows + r_first);
+        const float* src = stash + static_cast<size_t>(tk) * n_mine;
+        for (uint32_t i = lane; i < n_mine; i += 32) dst[i] = src[i];
+    }
+}
+
+// One thread per CTA, after every writer of the CTA has passed a CTA barrier: count the CTA in; the thread that
+// completes the count publishes the launch to every rank and advances the rank's own launch counter.
+__device__ __forceinline__ void gather_finish(const PeerGather& g, unsigned long long epoch) {
+    __threadfence();
+    const unsigned int prev = atomicAdd(g.arrive, 1u);
+    if (prev == gridDim.x - 1) {
+        fence_acq_rel_sys();   // the one system-scope fence of the launch
+        for (uint32_t p = 0; p < g.world; ++p) st_relaxed_sys(g.flags[p] + g.rank, epoch + 1);
+        *reinterpret_cast<volatile unsigned int*>(g.arrive) = 0;  // the next launch counts again only after this grid has ended
+        *reinterpret_cast<volatile unsigned long long*>(g.epoch) = epoch + 1;
+    }
+}
+
+// Waits until the latest launch of every rank has landed here, then copies the gathered vector
+// ([world][slot_floats], the parity of the latest launch) to `out`.  One CTA per 1024 floats.
+__global__ void __launch_bounds__(256) gather_fetch_kernel(const PeerGather g, float* __restrict__ out, int* error_word) {
+    const int lane = threadIdx.x & 31;
+    unsigned long long epoch;
+    if (!gather_begin(g, lane, epoch)) {
+        if (threadIdx.x == 0) atomicExch(error_word, kErrPeerWaitTimeout);
+        return;
+    }
+    if (!out) return;
+    const float* src = gather_previous(g, epoch);
+    const size_t n = static_cast<size_t>(g.world) * g.slot_floats;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        out[i] = __ldcv(src + i);   // written by peers: never through a stale non-coherent line
+}
+
+}  // namespace zk

@@ -28,6 +28,11 @@
 #include "quantize_acts.cuh"
 #include "repack.cuh"
 
+struct zen_cuda_gather {
+    zk::PeerGather dev{};     // what the kernels receive
+    void* counters{};         // local device words: epoch (u64) and CTA arrival count (u32)
+};
+
 struct zen_cuda_weights {
     int format{};
     size_t rows{}, cols{};
@@ -285,7 +290,10 @@ cudaError_t launch_gemv_q8_0(const zk::GemvParams& p, unsigned grid, size_t smem
     auto* fn = &zk::gemv_q8_0_kernel<kBatch, kDigits>;
     static size_t configured = 0;  // per instantiation; one device per process, calls serialised by the backend mutex
     if (smem > configured) {       // raised outside any stream capture by the first (uncaptured) launch of a shape
-        const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        // The kernels stream through shared memory and barely use L1: give shared memory the whole array, so that a
+        // CTA of the next launch can become resident beside one of this launch whenever two fit.
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return e;
         configured = smem;
     }
@@ -322,7 +330,10 @@ cudaError_t launch_gemv_kq(const zk::KqParams& p, unsigned grid, size_t smem, cu
     auto* fn = &zk::gemv_kq_kernel<kFormat, kBatch>;
     static size_t configured = 0;
     if (smem > configured) {
-        const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        // The kernels stream through shared memory and barely use L1: give shared memory the whole array, so that a
+        // CTA of the next launch can become resident beside one of this launch whenever two fit.
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return e;
         configured = smem;
     }
@@ -372,14 +383,15 @@ size_t max_tokens_per_launch(const State& s, int format, size_t cols, int act_mo
 }
 
 bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
-                     size_t tokens, cudaStream_t st) {
+                     size_t tokens, cudaStream_t st, const zk::PeerGather* gather) {
     zk::KqParams p{};
+    if (gather) p.gather = *gather;
     uint32_t total_rows = 0;
     const int fmt = w[0]->format;
     const int planes = fmt == ZEN_CUDA_Q4_0 ? 2 : 4;
     for (size_t i = 0; i < count; ++i) {
         for (int k = 0; k < planes; ++k) p.task[i].plane[k] = static_cast<const uint8_t*>(w[i]->plane[k]);
-        p.task[i].y = d_y[i];
+        p.task[i].y = d_y ? d_y[i] : nullptr;
         p.task[i].rows = static_cast<uint32_t>(w[i]->rows);
         p.task[i].first_row = total_rows;
         total_rows += static_cast<uint32_t>(w[i]->rows);
@@ -396,9 +408,11 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
         p.pitch[0] = p.K / 2; p.pitch[1] = p.K / 4; p.pitch[2] = p.K / 16; p.pitch[3] = w[0]->nbp * 2;
     }
     p.error_word = s.d_error;
-    const size_t smem = gemv_smem_bytes(fmt, w[0]->cols, tokens, ZEN_CUDA_ACT_FP32);
+    const unsigned grid = gather ? gather->grid
+                                 : std::max(1u, std::min<unsigned>((total_rows + zk::kGemvWarps - 1) / zk::kGemvWarps, static_cast<unsigned>(s.sm_count)));
+    const size_t smem = gemv_smem_bytes(fmt, w[0]->cols, tokens, ZEN_CUDA_ACT_FP32)
+                        + (gather ? zk::gather_stash_bytes(total_rows, grid, static_cast<int>(tokens)) : 0);
     if (smem > s.smem_optin) return set_error(s, "gemv: activation rows do not fit shared memory (columns x tokens too large)");
-    const unsigned grid = std::max(1u, std::min<unsigned>((total_rows + zk::kGemvWarps - 1) / zk::kGemvWarps, static_cast<unsigned>(s.sm_count)));
     const cudaError_t e = fmt == ZEN_CUDA_Q4_0 ? dispatch_kq<ZEN_CUDA_Q4_0>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
                                                : dispatch_kq<ZEN_CUDA_Q6_K>(static_cast<int>(tokens), p, grid, smem, st, s.pdl);
     if (e != cudaSuccess) return set_error(s, std::string("gemv launch: ") + cudaGetErrorString(e));
@@ -409,40 +423,48 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
 // Enqueues one batched GEMV launch: `count` tensors (same format, same K) times `tokens` (<= 8)
 // activation rows.  Device pointers throughout.
 bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
-                  size_t tokens, int act_mode, cudaStream_t st) {
-    if (!count || count > zk::kMaxTasks || !tokens || tokens > 8 || !d_x) return set_error(s, "gemv: bad batch");
+                  size_t tokens, int act_mode, cudaStream_t st, const zk::PeerGather* gather = nullptr) {
+    if (!count || count > zk::kMaxTasks || !tokens || tokens > 8 || (!d_x && !gather)) return set_error(s, "gemv: bad batch");
     if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: bad activation mode");
     zk::GemvParams p{};
     uint32_t total_rows = 0;
     for (size_t i = 0; i < count; ++i) {
-        if (!w[i] || !d_y[i] || w[i]->format != w[0]->format || w[i]->cols != w[0]->cols) return set_error(s, "gemv: tasks must share format and columns");
+        const bool has_y = d_y && d_y[i];
+        if (!w[i] || (!has_y && !gather) || w[i]->format != w[0]->format || w[i]->cols != w[0]->cols) return set_error(s, "gemv: tasks must share format and columns");
         p.task[i].codes = static_cast<const uint8_t*>(w[i]->plane[0]);
         p.task[i].scales = static_cast<const __half*>(w[i]->plane[1]);
-        p.task[i].y = d_y[i];
+        p.task[i].y = has_y ? d_y[i] : nullptr;
         p.task[i].rows = static_cast<uint32_t>(w[i]->rows);
         p.task[i].first_row = total_rows;
         total_rows += static_cast<uint32_t>(w[i]->rows);
     }
+    if (gather) {
+        if (tokens * total_rows > gather->slot_floats) return set_error(s, "gemv gather: tokens x rows exceed the gather slot");
+        if (!d_x && (tokens != 1 || w[0]->cols != static_cast<size_t>(gather->world) * gather->slot_floats))
+            return set_error(s, "gemv gather: a chained input needs one token and columns == world x slot_floats");
+        p.gather = *gather;
+    }
     if (w[0]->format != ZEN_CUDA_Q8_0) {
         if (act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: Q4_0 and Q6_K take fp32-equivalent activations only");
-        return enqueue_gemv_kq(s, w, d_y, count, d_x, tokens, st);
+        return enqueue_gemv_kq(s, w, d_y, count, d_x, tokens, st, gather);
     }
     p.ntasks = static_cast<uint32_t>(count);
     p.total_rows = total_rows;
     p.x = d_x;
     p.K = static_cast<uint32_t>(w[0]->cols);
-    p.nb = w[0]->nb;
-    p.nbp = w[0]->nbp;
-    p.nseg = (p.nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks;
+    const uint32_t nb = p.K / 32, nseg = (nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks;
+    if (w[0]->nb != nb || w[0]->nbp != ((nb + 7) & ~7u)) return set_error(s, "gemv: resident tensor has an unexpected scale pitch");
     p.error_word = s.d_error;
 #ifdef ZK_TRACE
     p.trace = g_trace ? g_trace + (g_trace_launch++) * 148 * 16 : nullptr;
 #endif
     const int digits = act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1;
-    const size_t smem = zk::gemv_q8_0_smem_bytes(p.nseg, static_cast<int>(tokens), digits);
-    if (smem > s.smem_optin) return set_error(s, "gemv: activation rows do not fit shared memory (columns x tokens too large)");
     // One persistent CTA per SM, each owning a contiguous slice of at least one row group.
-    const unsigned grid = std::max(1u, std::min<unsigned>((total_rows + zk::kGemvWarps - 1) / zk::kGemvWarps, static_cast<unsigned>(s.sm_count) * s.ctas_per_sm));
+    const unsigned grid = gather ? gather->grid
+                                 : std::max(1u, std::min<unsigned>((total_rows + zk::kGemvWarps - 1) / zk::kGemvWarps, static_cast<unsigned>(s.sm_count) * s.ctas_per_sm));
+    const size_t smem = zk::gemv_q8_0_smem_bytes(nseg, static_cast<int>(tokens), digits)
+                        + (gather ? zk::gather_stash_bytes(total_rows, grid, static_cast<int>(tokens)) : 0);
+    if (smem > s.smem_optin) return set_error(s, "gemv: activation rows do not fit shared memory (columns x tokens too large)");
     const cudaError_t e = digits == 2 ? dispatch_batch<2>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
                                       : dispatch_batch<1>(static_cast<int>(tokens), p, grid, smem, st, s.pdl);
     if (e != cudaSuccess) return set_error(s, std::string("gemv launch: ") + cudaGetErrorString(e));
@@ -892,6 +914,120 @@ int zen_cuda_dev_quantize_acts(const float* d_x, int8_t* d_codes, float* d_scale
         d_x, d_codes, d_scales, nullptr, nblk);
     ++s.stats.dispatches;
     if (cudaGetLastError() != cudaSuccess) return set_error(s, "dev_quantize_acts: launch failed") ? 1 : 0;
+    return 1;
+}
+
+// ---- row-sharded products: gather regions shared between processes through CUDA IPC ------------------------------
+
+size_t zen_cuda_gather_region_bytes(size_t world, size_t slot_floats) {
+    if (!world || world > zk::kMaxPeers || !slot_floats) return 0;
+    return zk::peer_region_bytes(world, slot_floats);
+}
+
+void* zen_cuda_ipc_alloc(size_t bytes, unsigned char handle_out[ZEN_CUDA_IPC_HANDLE_BYTES]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == ZEN_CUDA_IPC_HANDLE_BYTES, "IPC handle size");
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return nullptr;
+    if (!bytes || !handle_out) { set_error(s, "ipc_alloc: bad arguments"); return nullptr; }
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h{};
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        if (p) cudaFree(p);
+        set_error(s, std::string("ipc_alloc: ") + cudaGetErrorString(e));
+        return nullptr;
+    }
+    std::memcpy(handle_out, &h, sizeof h);
+    return p;
+}
+
+void* zen_cuda_ipc_open(const unsigned char handle[ZEN_CUDA_IPC_HANDLE_BYTES]) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return nullptr;
+    if (!handle) { set_error(s, "ipc_open: bad arguments"); return nullptr; }
+    cudaIpcMemHandle_t h{};
+    std::memcpy(&h, handle, sizeof h);
+    void* p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) { set_error(s, std::string("ipc_open: ") + cudaGetErrorString(e)); return nullptr; }
+    return p;
+}
+
+void zen_cuda_ipc_close(void* peer_region) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (s.ready && peer_region) cudaIpcCloseMemHandle(peer_region);
+}
+
+void zen_cuda_ipc_free(void* own_region) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (s.ready && own_region) { cudaDeviceSynchronize(); cudaFree(own_region); }
+}
+
+zen_cuda_gather* zen_cuda_gather_create(size_t world, size_t rank, size_t slot_floats, void* const* regions) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return nullptr;
+    if (!world || world > zk::kMaxPeers || rank >= world || !slot_floats || !regions) { set_error(s, "gather_create: bad arguments"); return nullptr; }
+    for (size_t r = 0; r < world; ++r)
+        if (!regions[r]) { set_error(s, "gather_create: a region is missing"); return nullptr; }
+    auto* g = new zen_cuda_gather();
+    if (cudaMalloc(&g->counters, 16) != cudaSuccess || cudaMemset(g->counters, 0, 16) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+        if (g->counters) cudaFree(g->counters);
+        delete g;
+        set_error(s, "gather_create: out of device memory");
+        return nullptr;
+    }
+    const size_t flag_offset = zk::peer_region_flag_offset(world, slot_floats);
+    for (size_t r = 0; r < world; ++r) {
+        g->dev.region[r] = static_cast<float*>(regions[r]);
+        g->dev.flags[r] = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(regions[r]) + flag_offset);
+    }
+    g->dev.local_region = g->dev.region[rank];
+    g->dev.local_flags = g->dev.flags[rank];
+    g->dev.epoch = static_cast<unsigned long long*>(g->counters);
+    g->dev.arrive = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(g->counters) + 8);
+    g->dev.world = static_cast<uint32_t>(world);
+    g->dev.rank = static_cast<uint32_t>(rank);
+    g->dev.slot_floats = static_cast<uint32_t>(slot_floats);
+    // The grid of every launch on this object: a function of the slot size alone, so all ranks agree whatever their shards.
+    g->dev.grid = static_cast<uint32_t>(std::max<size_t>(1, std::min<size_t>((slot_floats + zk::kGemvWarps - 1) / zk::kGemvWarps, static_cast<size_t>(s.sm_count))));
+    return g;
+}
+
+void zen_cuda_gather_destroy(zen_cuda_gather* g) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!g) return;
+    if (s.ready) { cudaDeviceSynchronize(); cudaFree(g->counters); }
+    delete g;
+}
+
+int zen_cuda_dev_gemv_gather(zen_cuda_gather* g, const zen_cuda_weights* const* w, float* const* d_y, size_t count,
+                             const float* d_x, size_t tokens, int act_mode, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!g || !w) return set_error(s, "dev_gemv_gather: bad arguments") ? 1 : 0;
+    return enqueue_gemv(s, w, d_y, count, d_x, tokens, act_mode, stream ? static_cast<cudaStream_t>(stream) : s.stream, &g->dev) ? 1 : 0;
+}
+
+int zen_cuda_dev_gather_fetch(zen_cuda_gather* g, float* d_out, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!g) return set_error(s, "dev_gather_fetch: bad arguments") ? 1 : 0;
+    const size_t n = static_cast<size_t>(g->dev.world) * g->dev.slot_floats;
+    const unsigned grid = static_cast<unsigned>(std::max<size_t>(1, std::min<size_t>((n + 1023) / 1024, static_cast<size_t>(s.sm_count))));
+    zk::gather_fetch_kernel<<<grid, 256, 0, stream ? static_cast<cudaStream_t>(stream) : s.stream>>>(g->dev, d_out, s.d_error);
+    ++s.stats.dispatches;
+    if (cudaGetLastError() != cudaSuccess) return set_error(s, "dev_gather_fetch: launch failed") ? 1 : 0;
     return 1;
 }
 

@@ -94,3 +94,51 @@ def sharded_greedy_pick(local: torch.Tensor, rows: int, world: int, rank: int, g
     cand = torch.where((vals == best) & (idxs >= 0), idxs, torch.full_like(idxs, float("inf")))
     pick = cand.min(dim=0).values
     return torch.where(torch.isfinite(pick), pick, torch.full_like(pick, -1.0)).long()
+
+
+class PeerGather:
+    """One rank's end of the all-gather that the decode kernels perform themselves (zen_cuda_dev_gemv_gather).
+
+    Construction is collective: every rank allocates its gather region, the 64-byte IPC handles travel through
+    torch.distributed (any backend: they are host bytes), every rank opens the others' regions and binds them.  After
+    that no collective library is on the data path: a launch stores its outputs into every rank's region over NVLink
+    and publishes an epoch; consumers wait on the device.  `slot_floats` is the capacity of one rank's slot,
+    tokens x shard rows at most.  close() is collective too (no rank may free memory a peer can still write to).
+    """
+
+    def __init__(self, backend, world: int, rank: int, slot_floats: int, group=None):
+        self.be, self.world, self.rank, self.slot_floats, self.group = backend, world, rank, slot_floats, group
+        nbytes = backend.gather_region_bytes(world, slot_floats)
+        if nbytes == 0:
+            raise ValueError("bad gather geometry")
+        self.own, handle = backend.ipc_alloc(nbytes)
+        handles: list = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, handle, group=group)
+        else:
+            handles[0] = handle
+        self.regions = [self.own if r == rank else backend.ipc_open(handles[r]) for r in range(world)]
+        self.handle = backend.gather_create(world, rank, slot_floats, self.regions)
+        if world > 1:
+            dist.barrier(group=group)  # nobody launches before every rank has mapped every region
+
+    def gemv(self, weights, d_x, tokens: int, act_mode: int, stream: int = 0, d_y=None) -> None:
+        self.be.dev_gemv_gather(self.handle, weights, d_y, d_x, tokens, act_mode, stream)
+
+    def fetch(self, d_out, stream: int = 0) -> None:
+        """Device-side wait for every rank's latest launch, then a copy of the gathered [world][slot_floats] floats."""
+        self.be.dev_gather_fetch(self.handle, d_out, stream)
+
+    def close(self) -> None:
+        if self.handle is None:
+            return
+        if self.world > 1:
+            dist.barrier(group=self.group)  # callers synchronise their streams first; then nobody writes any more
+        self.be.gather_destroy(self.handle)
+        for r, p in enumerate(self.regions):
+            if r != self.rank:
+                self.be.ipc_close(p)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # every mapping of the own region is gone before it is freed
+        self.be.ipc_free(self.own)
+        self.handle = None
