@@ -146,6 +146,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
         // ---------------- producer warp ----------------
         uint32_t unit = 0;
         bool ok = true;
+        bool announce = p.gather.world != 0 && blockIdx.x == 0;   // see gemv_q8_0_kernel
         KqWalk walk(r_first, r_last);
         const int my_row = lane / F::kPlanes, my_plane = lane % F::kPlanes;  // one copy per (row, plane) of a unit
         while (!walk.done() && ok) {
@@ -156,6 +157,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
 #pragma unroll
                 for (int m = 0; m < kTeams; ++m, ++unit) {
                     const uint32_t stage = unit % kStages;
+                    if (unit >= static_cast<uint32_t>(kStages) && announce) {
+                        announce = false;
+                        if (lane == 0) { pdl_wait(); gather_publish_pending(p.gather); }
+                        __syncwarp();
+                    }
                     if (unit >= static_cast<uint32_t>(kStages)) {
                         if (!mbar_wait(&empty[stage], ((unit / kStages) - 1) & 1)) {
                             if (lane == 0) { *abort_word = 1; atomicExch(p.error_word, kErrEmptyWaitTimeout); }
@@ -187,6 +193,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                 }
             }
         }
+        if (announce && lane == 0) { pdl_wait(); gather_publish_pending(p.gather); }
         if (lane == 0) {
             const uint32_t armed = unit < static_cast<uint32_t>(kStages) ? unit : kStages;
             for (uint32_t k = 0; k < armed; ++k) {
@@ -203,10 +210,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
     unsigned long long epoch = 0;
     const float* x_src = p.x;
     if (p.gather.world) {
-        if (!gather_begin(p.gather, lane, epoch)) {
-            if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrPeerWaitTimeout); }
+        epoch = gather_epoch(p.gather);
+        if (!x_src) {   // chained: the other ranks' previous outputs are this launch's input, so they are needed now
+            if (!gather_wait(p.gather, lane, epoch)) {
+                if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrPeerWaitTimeout); }
+            }
+            x_src = gather_previous(p.gather, epoch);
         }
-        if (!x_src) x_src = gather_previous(p.gather, epoch);
     }
     // Prologue: two-digit quantisation of the activations, natural element order.
     {
@@ -346,7 +356,14 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
     }
     if (p.gather.world) {
         asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");
-        gather_push(p.gather, epoch, stash, n_mine, r_first, p.total_rows, kBatch, warp, kGemvWarps, lane);
+        // With an input of its own the launch needs the other ranks only now: they must have finished the previous
+        // launch (whose reads used the parity about to be overwritten) before anything is stored into their regions.
+        bool may_push = true;
+        if (p.x && !gather_wait(p.gather, lane, epoch)) {
+            if (lane == 0) atomicExch(p.error_word, kErrPeerWaitTimeout);
+            may_push = false;
+        }
+        if (may_push) gather_push(p.gather, epoch, stash, n_mine, r_first, p.total_rows, kBatch, warp, kGemvWarps, lane);
         asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");
         if (threadIdx.x == 0) gather_finish(p.gather, epoch);
     }

@@ -206,6 +206,8 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
     if (warp == kGemvWarps) {
         // ---------------- producer warp: weights are constants, no need to wait for the previous grid ----------------
         bool met = false;   // has the L2 prefetch of the rows beyond the ring's first fill been issued yet
+        // CTA 0's producer also announces the previous launch to the other ranks, once its own first copies are out
+        bool announce = p.gather.world != 0 && blockIdx.x == 0;
         uint32_t unit = 0;
         bool ok = true;
         GroupWalk walk(r_first, r_last);
@@ -217,6 +219,11 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
 #pragma unroll
                 for (int m = 0; m < kTeams; ++m, ++unit) {
                     const uint32_t stage = unit % kGemvStages;
+                    if (unit >= kGemvStages && announce) {
+                        announce = false;
+                        if (lane == 0) { pdl_wait(); gather_publish_pending(p.gather); }
+                        __syncwarp();
+                    }
                     if (unit >= kGemvStages && !met) {
                         met = true;
                         if (lane == 0) {
@@ -277,6 +284,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
                 }
             }
         }
+        if (announce && lane == 0) { pdl_wait(); gather_publish_pending(p.gather); }
         // Nothing may still be landing in shared memory when the CTA exits: wait (bounded) for
         // the most recent phase of every stage that was armed.
         if (lane == 0) {
@@ -314,10 +322,13 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
     unsigned long long epoch = 0;
     const float* x_src = p.x;
     if (p.gather.world) {
-        if (!gather_begin(p.gather, lane, epoch)) {
-            if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrPeerWaitTimeout); }
+        epoch = gather_epoch(p.gather);
+        if (!x_src) {   // chained: the other ranks' previous outputs are this launch's input, so they are needed now
+            if (!gather_wait(p.gather, lane, epoch)) {
+                if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrPeerWaitTimeout); }
+            }
+            x_src = gather_previous(p.gather, epoch);
         }
-        if (!x_src) x_src = gather_previous(p.gather, epoch);
     }
     // Prologue: quantise the activations into the lane-major layout.  Block b = 32*g + l is read by
     // lane l; its two 16-byte halves are stored in the order that lane loads them (half ((l>>2)&1)
@@ -468,7 +479,14 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
     ZK_STAMP(12);
     if (p.gather.world) {
         asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");   // the slice's outputs are all in the stash
-        gather_push(p.gather, epoch, stash, n_mine, r_first, p.total_rows, kBatch, warp, kGemvWarps, lane);
+        // With an input of its own the launch needs the other ranks only now: they must have finished the previous
+        // launch (whose reads used the parity about to be overwritten) before anything is stored into their regions.
+        bool may_push = true;
+        if (p.x && !gather_wait(p.gather, lane, epoch)) {
+            if (lane == 0) atomicExch(p.error_word, kErrPeerWaitTimeout);
+            may_push = false;
+        }
+        if (may_push) gather_push(p.gather, epoch, stash, n_mine, r_first, p.total_rows, kBatch, warp, kGemvWarps, lane);
         asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");
         if (threadIdx.x == 0) gather_finish(p.gather, epoch);
     }

@@ -4,9 +4,10 @@
 // running the product and then a separate collective, the product kernel itself delivers its
 // outputs: a CTA collects the outputs of its row slice in shared memory and, when the slice is
 // done, copies the run into the same slot of every rank's gather region with coalesced peer
-// stores; the last CTA of the grid to finish then publishes the launch's number into every
-// rank's flag array.  A kernel that consumes the gathered vector (the next launch in the chain,
-// or gather_fetch_kernel) waits, with a clock budget, until all ranks' flags have reached the
+// stores.  The launch's number is published into every rank's flag array by the NEXT kernel on
+// the gather object (one idle thread of it, as soon as the launch has ended), off every critical
+// path.  A kernel that consumes the gathered vector (the next launch in the chain, or
+// gather_fetch_kernel) waits, with a clock budget, until all ranks' flags have reached the
 // number it needs.  No host round trip, no extra launch, and the next launch's weight stream
 // overlaps the link latency.  The reference drives one device and has no counterpart of this
 // file; the row cut it mirrors is ComputePool::parallel_for's (src/compute_pool.cpp:104-106).
@@ -21,10 +22,12 @@
 // Ordering, and why it looks the way it does: a fence at system scope costs this GPU tens of
 // nanoseconds that do not overlap with other such fences, so a launch may afford one, not one per
 // CTA or per warp (148 of them were measured at about 10 us per launch).  Writers of a CTA meet
-// at a CTA barrier after their peer stores; one thread then fences at GPU scope and counts the
-// CTA in with an atomic; the thread that completes the count fences ONCE at system scope --
-// fences are cumulative, so this covers the stores of every CTA it has synchronised with -- and
-// stores the flags.  Readers poll their own (local) flags with relaxed system-scope loads and
+// at a CTA barrier after their peer stores; one thread then counts the CTA in with an atomic, and
+// the thread that completes the count advances the rank's launch counter (no fence: see below).
+// The publishing thread of the next kernel starts after that grid has completed, fences ONCE at
+// system scope -- fences are cumulative, so this covers every store of the completed grid, and
+// by then their acknowledgements are mostly in, so the fence is short -- and stores the flags.
+// Readers poll their own (local) flags with relaxed system-scope loads and
 // read the data through L2 (never L1), the point where peer stores to local memory land.
 // Only loads of local memory ever spin.
 #pragma once
@@ -44,6 +47,7 @@ struct PeerGather {
     const unsigned long long* local_flags;
     unsigned long long* epoch;                // local: launches this rank has completed
     unsigned int* arrive;                     // local: CTAs of the running launch that have finished
+    unsigned long long* published;            // local: launches whose number has been stored into the ranks' flags
     uint32_t world, rank, slot_floats;        // world == 0: no gather, the kernel writes its ordinary outputs only
     uint32_t grid;                            // CTAs of every gather launch on this object, the same on all ranks
 };
@@ -66,13 +70,17 @@ __device__ __forceinline__ void st_relaxed_sys(unsigned long long* p, unsigned l
 }
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 
-// Warp-wide; every consumer warp of a CTA calls it after the previous grid in the stream has completed.  Returns
-// the number of launches this rank has completed so far (this launch is number epoch + 1) and waits until every rank
-// has published that many; false (warp-uniform) when the clock budget ran out first.
-__device__ __forceinline__ bool gather_begin(const PeerGather& g, int lane, unsigned long long& epoch) {
-    epoch = *reinterpret_cast<volatile unsigned long long*>(g.epoch);
+// The number of launches this rank has completed so far (the running launch is number epoch + 1).  Valid once the
+// previous grid in the stream has completed.
+__device__ __forceinline__ unsigned long long gather_epoch(const PeerGather& g) {
+    return *reinterpret_cast<volatile unsigned long long*>(g.epoch);
+}
+
+// Warp-wide: waits until every rank has published `epoch` launches; false (warp-uniform) when the clock budget ran out
+// first.  A launch calls it before it reads gathered data and, at the latest, before it stores into other ranks' regions.
+__device__ __forceinline__ bool gather_wait(const PeerGather& g, int lane, unsigned long long epoch) {
     bool ok = true;
-    if (lane < static_cast<int>(g.world)) {
+    if (lane < static_cast<int>(g.world) && lane != static_cast<int>(g.rank)) {   // own outputs are local and complete
         const unsigned long long* f = g.local_flags + lane;
         if (ld_relaxed_sys(f) < epoch) {
             const long long t0 = clock64();
@@ -107,15 +115,26 @@ __device__ __forceinline__ void gather_push(const PeerGather& g, unsigned long l
 }
 
 // One thread per CTA, after every writer of the CTA has passed a CTA barrier: count the CTA in; the thread that
-// completes the count publishes the launch to every rank and advances the rank's own launch counter.
+// completes the count advances the rank's own launch counter.
 __device__ __forceinline__ void gather_finish(const PeerGather& g, unsigned long long epoch) {
-    __threadfence();
+    // No fence here: the counter only numbers the launches.  What orders the peer stores before the flags is the end of
+    // this grid followed by the publishing thread's fence; a fence in every CTA would keep the CTA resident until its
+    // peer stores are acknowledged and hold back the next launch's weight stream on this SM.
     const unsigned int prev = atomicAdd(g.arrive, 1u);
     if (prev == gridDim.x - 1) {
-        fence_acq_rel_sys();   // the one system-scope fence of the launch
-        for (uint32_t p = 0; p < g.world; ++p) st_relaxed_sys(g.flags[p] + g.rank, epoch + 1);
         *reinterpret_cast<volatile unsigned int*>(g.arrive) = 0;  // the next launch counts again only after this grid has ended
         *reinterpret_cast<volatile unsigned long long*>(g.epoch) = epoch + 1;
+    }
+}
+
+// One thread of a kernel, once the previous grid in the stream has completed: tell every rank about the launches this
+// rank has finished but not announced yet.  This holds the one system-scope fence a launch costs.
+__device__ __forceinline__ void gather_publish_pending(const PeerGather& g) {
+    const unsigned long long done = *reinterpret_cast<volatile unsigned long long*>(g.epoch);
+    if (*reinterpret_cast<volatile unsigned long long*>(g.published) < done) {
+        fence_acq_rel_sys();
+        for (uint32_t p = 0; p < g.world; ++p) st_relaxed_sys(g.flags[p] + g.rank, done);
+        *reinterpret_cast<volatile unsigned long long*>(g.published) = done;
     }
 }
 
@@ -123,8 +142,9 @@ __device__ __forceinline__ void gather_finish(const PeerGather& g, unsigned long
 // ([world][slot_floats], the parity of the latest launch) to `out`.  One CTA per 1024 floats.
 __global__ void __launch_bounds__(256) gather_fetch_kernel(const PeerGather g, float* __restrict__ out, int* error_word) {
     const int lane = threadIdx.x & 31;
-    unsigned long long epoch;
-    if (!gather_begin(g, lane, epoch)) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) gather_publish_pending(g);   // the last launch has no successor to do it
+    const unsigned long long epoch = gather_epoch(g);
+    if (!gather_wait(g, lane, epoch)) {
         if (threadIdx.x == 0) atomicExch(error_word, kErrPeerWaitTimeout);
         return;
     }

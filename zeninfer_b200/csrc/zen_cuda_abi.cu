@@ -30,7 +30,7 @@
 
 struct zen_cuda_gather {
     zk::PeerGather dev{};     // what the kernels receive
-    void* counters{};         // local device words: epoch (u64) and CTA arrival count (u32)
+    void* counters{};         // local device words: epoch (u64), CTA arrival count (u32), published (u64)
 };
 
 struct zen_cuda_weights {
@@ -978,7 +978,7 @@ zen_cuda_gather* zen_cuda_gather_create(size_t world, size_t rank, size_t slot_f
     for (size_t r = 0; r < world; ++r)
         if (!regions[r]) { set_error(s, "gather_create: a region is missing"); return nullptr; }
     auto* g = new zen_cuda_gather();
-    if (cudaMalloc(&g->counters, 16) != cudaSuccess || cudaMemset(g->counters, 0, 16) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+    if (cudaMalloc(&g->counters, 32) != cudaSuccess || cudaMemset(g->counters, 0, 32) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
         if (g->counters) cudaFree(g->counters);
         delete g;
         set_error(s, "gather_create: out of device memory");
@@ -993,6 +993,7 @@ zen_cuda_gather* zen_cuda_gather_create(size_t world, size_t rank, size_t slot_f
     g->dev.local_flags = g->dev.flags[rank];
     g->dev.epoch = static_cast<unsigned long long*>(g->counters);
     g->dev.arrive = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(g->counters) + 8);
+    g->dev.published = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(g->counters) + 16);
     g->dev.world = static_cast<uint32_t>(world);
     g->dev.rank = static_cast<uint32_t>(rank);
     g->dev.slot_floats = static_cast<uint32_t>(slot_floats);
