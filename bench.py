@@ -303,6 +303,344 @@ def run_gemm_workload(args) -> None:
     }))
 
 
+# ---- workload layer_sweep: mixed-format decode GEMV sweep over one Llama-3-8B layer (third benchmark configuration) ----
+LAYER_TENSORS = (("q", 4096, 4096), ("k", 1024, 4096), ("v", 1024, 4096), ("o", 4096, 4096),
+                 ("gate", 14336, 4096), ("up", 14336, 4096), ("down", 4096, 14336))
+# what a decode step launches: projections that share an input go out as one launch (zen::quant::gemv_batch)
+LAYER_LAUNCHES = (("qkv", ("q", "k", "v")), ("o", ("o",)), ("gate_up", ("gate", "up")), ("down", ("down",)))
+FORMAT_BLOCK = {"Q4_0": (32, 18), "Q8_0": (32, 34), "Q6_K": (256, 210)}
+SWEEP_MIN_BYTES = 300e6   # bytes a timing loop sweeps before it meets an address again: well past the 126 MB L2
+
+
+def tensor_bytes(fmt: str, rows: int, cols: int) -> int:
+    elems, nbytes = FORMAT_BLOCK[fmt]
+    return rows * (cols // elems) * nbytes
+
+
+def run_layer_sweep(args) -> None:
+    """All seven projections of one layer (weights N(0, 0.02), inputs N(0, 1), one generator seeded 4) in Q4_0, Q8_0 and
+    Q6_K, batch 1.  Every launch kind is timed on its own over enough rotating weight copies to exceed L2, and the
+    whole layer (four launches) is timed as a sequence over rotating layer copies.  value = the Q8_0 layer."""
+    import torch
+    from zeninfer_b200 import Backend, blocks
+    from zeninfer_b200.backend import ACT_FP32, ACT_INT8, FORMAT_IDS
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1 or args.gpus != 1:
+        raise SystemExit("workload layer_sweep is a single-GPU workload")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    be = Backend()
+    rng = np.random.default_rng(4)
+    dense = {name: rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02) for name, rows, cols in LAYER_TENSORS}
+    shape = {name: (rows, cols) for name, rows, cols in LAYER_TENSORS}
+    x_host = {4096: rng.standard_normal(4096, dtype=np.float32), 14336: rng.standard_normal(14336, dtype=np.float32)}
+    d_x = {k: torch.from_numpy(v).to(dev) for k, v in x_host.items()}
+    d_y = {name: torch.zeros(rows, dtype=torch.float32, device=dev) for name, rows, _ in LAYER_TENSORS}
+    stream = torch.cuda.Stream(device=dev)
+    peak, peak_kind = peaks()
+    reps = max(3, args.steps // 100)
+
+    def time_graph(enqueue, launches_per_replay):
+        with torch.cuda.stream(stream):
+            enqueue()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                enqueue()
+            for _ in range(max(3, args.warmup)):
+                graph.replay()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+        be.dev_check(stream.cuda_stream)
+        return e0.elapsed_time(e1) * 1e3 / (reps * launches_per_replay)  # microseconds per launch
+
+    detail, packed_q8, launches_total = {}, None, 0
+    with ClockSampler(0) as clocks:
+        clocks.mark_start()
+        for fmt in ("Q8_0", "Q4_0", "Q6_K"):
+            mode = ACT_INT8 if fmt == "Q8_0" else ACT_FP32
+            packed = {name: np.ascontiguousarray(blocks.quantize(FORMAT_IDS[fmt], dense[name])) for name in dense}
+            if fmt == "Q8_0":
+                packed_q8 = packed
+            layer_bytes = sum(tensor_bytes(fmt, *shape[n]) for n in shape)
+            layer_copies = int(SWEEP_MIN_BYTES // layer_bytes) + 1
+            per_kind, copies = {}, {}
+            for kind, names in LAYER_LAUNCHES:
+                nbytes = sum(tensor_bytes(fmt, *shape[n]) for n in names)
+                ncopy = max(layer_copies, int(SWEEP_MIN_BYTES // nbytes) + 1)
+                copies[kind] = [[be.dev_upload(fmt, packed[n], *shape[n]) for n in names] for _ in range(ncopy)]
+                cols = shape[names[0]][1]
+                algo = nbytes + 4 * cols + 4 * sum(shape[n][0] for n in names)
+
+                def enqueue(kind=kind, names=names, cols=cols):
+                    for hs in copies[kind]:
+                        be.dev_gemv(hs, [d_y[n].data_ptr() for n in names], d_x[cols].data_ptr(), 1, mode, stream.cuda_stream)
+
+                us = time_graph(enqueue, ncopy)
+                launches_total += (reps + max(3, args.warmup) + 2) * ncopy
+                per_kind[kind] = {"rows": [shape[n][0] for n in names], "columns": cols, "algorithmic_bytes": algo, "copies": ncopy,
+                                  "us": us, "gbs": algo / us / 1e3, "frac": algo / us / 1e3 / peak}
+
+            def enqueue_layer():
+                for c in range(layer_copies):
+                    for kind, names in LAYER_LAUNCHES:
+                        cols = shape[names[0]][1]
+                        be.dev_gemv(copies[kind][c], [d_y[n].data_ptr() for n in names], d_x[cols].data_ptr(), 1, mode, stream.cuda_stream)
+
+            layer_us = time_graph(enqueue_layer, layer_copies)
+            launches_total += (reps + max(3, args.warmup) + 2) * layer_copies * len(LAYER_LAUNCHES)
+            layer_algo = sum(v["algorithmic_bytes"] for v in per_kind.values())
+            per_kind["layer"] = {"algorithmic_bytes": layer_algo, "copies": layer_copies, "us": layer_us, "gbs": layer_algo / layer_us / 1e3,
+                                 "frac": layer_algo / layer_us / 1e3 / peak, "launches": len(LAYER_LAUNCHES)}
+            detail[fmt] = per_kind
+            for kind in copies:
+                for hs in copies[kind]:
+                    for h in hs:
+                        be.dev_free(h)
+        clocks.mark_end()
+
+    # e2e: the Q8_0 layer through the host-pointer calls (zen_cuda_gemv_q8_0_batch / zen_cuda_gemv_q8_0), host buffers
+    hosts = [{n: (packed_q8[n] if c == 0 else packed_q8[n].copy()) for n in packed_q8} for c in range(2)]
+
+    def host_layer(hc):
+        for kind, names in LAYER_LAUNCHES:
+            cols = shape[names[0]][1]
+            if len(names) > 1:
+                be.gemv_batch("Q8_0", [hc[n] for n in names], x_host[cols], [shape[n][0] for n in names], cols)
+            else:
+                be.gemv("Q8_0", hc[names[0]], x_host[cols], shape[names[0]][0], cols)
+
+    for hc in hosts:
+        host_layer(hc)
+    e2e_steps, t0 = 10, time.perf_counter()
+    for i in range(e2e_steps):
+        host_layer(hosts[i % 2])
+    e2e_s = time.perf_counter() - t0
+    q8 = detail["Q8_0"]
+    e2e_value = q8["layer"]["algorithmic_bytes"] * e2e_steps / e2e_s / 1e9
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        import oracle
+        os.environ.setdefault("ZEN_CPU_Q8_ACT", "1")
+        if oracle.reference_available():
+            zr = oracle.Reference()
+            run = lambda n: zr.gemv(oracle.Q8_0, packed_q8[n], x_host[shape[n][1]], shape[n][0], shape[n][1], workers=0)
+            kind, cores = "reference", min(zr.pool_workers(), os.cpu_count() or 1)
+        else:
+            zo = oracle.Oracle()
+            run = lambda n: zo.gemv(oracle.Q8_0, packed_q8[n], x_host[shape[n][1]], shape[n][0], shape[n][1], int8_acts=True)
+            kind, cores = "port", 1
+        t0, n = time.perf_counter(), 0
+        while n == 0 or time.perf_counter() - t0 < args.cpu_budget:
+            for name in shape:
+                run(name)
+            n += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": q8["layer"]["algorithmic_bytes"] * n / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+               "sample": f"{n} passes over the seven Q8_0 projections of the layer in {dt:.1f} s, one call per projection, int8 activations"}
+
+    dom = q8["gate_up"]
+    print(json.dumps({
+        "metric": "layer_decode_gemv_hbm_gbs", "value": q8["layer"]["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": max(3, args.warmup),
+        "ms_per_step": q8["layer"]["us"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "decode GEMV sweep over one Llama-3-8B layer, batch 1, Q8_0 / Q4_0 / Q6_K (config 2); value = the Q8_0 layer, "
+                               "four launches (q|k|v, o, gate|up, down)",
+                   "l2": f"inputs larger than L2: every timing loop sweeps at least {SWEEP_MIN_BYTES / 1e6:.0f} MB of distinct weight copies",
+                   "launch": "CUDA graph replay"},
+        "roofline": {"bound": "hbm", "achieved": dom["gbs"], "peak": peak, "unit": "GB/s", "frac": dom["frac"], "peak_kind": peak_kind, "traffic": None,
+                     "kernel": "gemv_q8_0_kernel<1,1> on gate|up (2 x 14336 x 4096)", "launch_us": dom["us"],
+                     "algorithmic_bytes_per_launch": dom["algorithmic_bytes"]},
+        "detail": detail, "cpu_baseline": cpu, "clocks": clocks.summary(),
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * (3 * 4096 + 14336), "d2h_bytes_per_step": 4 * sum(r for _, r, _ in LAYER_TENSORS),
+                "api": "zen_cuda_gemv_q8_0_batch + zen_cuda_gemv_q8_0 (host pointers)", "steps": e2e_steps},
+        "gpu_launches": launches_total,
+    }))
+
+
+# ---- workload lm_head: row-sharded Q6_K lm_head, fused all-gather of the logits, greedy pick (fourth configuration) ----
+LM_ROWS, LM_COLS = 128256, 4096
+
+
+def lm_head_shard(first: int, last: int) -> np.ndarray:
+    """Rows [first, last) of W 128256 x 4096 ~ N(0, 0.02) from the generator seeded 5, packed to Q6_K.  The stream is
+    drawn in row chunks from the start so that every rank sees the same matrix; only the own rows are packed."""
+    from zeninfer_b200 import blocks
+    rng = np.random.default_rng(5)
+    out, chunk = [], 8016
+    for r0 in range(0, LM_ROWS, chunk):
+        r1 = min(LM_ROWS, r0 + chunk)
+        if r0 >= last:
+            break
+        w = rng.standard_normal((r1 - r0, LM_COLS), dtype=np.float32)
+        a, b = max(first, r0), min(last, r1)
+        if a < b:
+            out.append(blocks.quantize_q6_k(w[a - r0:b - r0] * np.float32(0.02)))
+    return np.ascontiguousarray(np.concatenate(out, axis=0))
+
+
+def run_lm_head(args) -> None:
+    """Q6_K lm_head 128256 x 4096 at batch 1 (value) and batch 8, rows sharded over the ranks.  A step on every rank: the
+    shard product with the all-gather fused in (or followed by an NCCL all-gather), then the greedy pick over the
+    gathered logits.  Total work is fixed as N grows: strong scaling."""
+    import torch
+    import torch.distributed as dist
+    from zeninfer_b200 import Backend, shard
+    from zeninfer_b200.backend import ACT_FP32
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    be = Backend()
+    plan = shard.shard_plan(LM_ROWS, world)
+    first, last = plan[rank]
+    my_rows, widest = last - first, max(b - a for a, b in plan)
+    packed = lm_head_shard(first, last)
+    shard_bytes = tensor_bytes("Q6_K", my_rows, LM_COLS)
+    ncopy = int(SWEEP_MIN_BYTES // shard_bytes) + 1
+    handles = [be.dev_upload("Q6_K", packed, my_rows, LM_COLS) for _ in range(ncopy)]
+    hidden = np.random.default_rng([5, 1]).standard_normal((8, LM_COLS), dtype=np.float32)
+    d_h = torch.from_numpy(hidden).to(dev)
+    stream = torch.cuda.Stream(device=dev)
+    fused = world > 1 and args.gather == "fused"
+    peak, peak_kind = peaks()
+    results = {}
+
+    with ClockSampler(local) as clocks:
+        for tokens in (1, 8):
+            d_local = torch.zeros((tokens, my_rows), dtype=torch.float32, device=dev)
+            d_all = torch.zeros((world, tokens * widest), dtype=torch.float32, device=dev)
+            d_pick = torch.full((tokens,), -7, dtype=torch.int64, device=dev)
+            pg = shard.PeerGather(be, world, rank, tokens * widest) if fused else None
+            segs = [(d_all.data_ptr() + 4 * r * tokens * widest, b - a, a, b - a) for r, (a, b) in enumerate(plan)]
+            if world == 1:
+                segs = [(d_local.data_ptr(), LM_ROWS, 0, LM_ROWS)]
+
+            def one_pass():
+                for h in handles:
+                    if fused:
+                        pg.gemv([h], d_h.data_ptr(), tokens, ACT_FP32, stream.cuda_stream, d_y=[d_local.data_ptr()])
+                        pg.fetch(d_all.data_ptr(), stream.cuda_stream)
+                    else:
+                        be.dev_gemv([h], [d_local.data_ptr()], d_h.data_ptr(), tokens, ACT_FP32, stream.cuda_stream)
+                        if world > 1:
+                            send = d_local if my_rows == widest else torch.nn.functional.pad(d_local, (0, widest - my_rows))
+                            dist.all_gather_into_tensor(d_all.view(world * tokens, widest), send.contiguous())
+                    be.dev_greedy_pick(segs, tokens, d_pick.data_ptr(), stream.cuda_stream)
+
+            with torch.cuda.stream(stream):
+                one_pass()
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    one_pass()
+                for _ in range(max(3, args.warmup)):
+                    graph.replay()
+                stream.synchronize()
+                be.dev_check(stream.cuda_stream)
+                replays = max(1, args.steps // ncopy)
+                if world > 1:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                if tokens == 1:
+                    clocks.mark_start()
+                e0.record(stream)
+                for _ in range(replays):
+                    graph.replay()
+                e1.record(stream)
+                stream.synchronize()
+                if tokens == 1:
+                    clocks.mark_end()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            ms = e0.elapsed_time(e1)
+            be.dev_check(stream.cuda_stream)
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            steps = replays * ncopy
+            # what was timed is right: the pick equals the first maximum of the gathered logits, and the own shard of the
+            # gathered logits equals the local product
+            if world > 1:
+                mine = d_all[rank, : tokens * my_rows].view(tokens, my_rows)
+                assert bool((mine == d_local).all().item()), "gathered shard differs from the local product"
+                full = torch.cat([d_all[r, : tokens * (b - a)].view(tokens, b - a) for r, (a, b) in enumerate(plan)], dim=1)
+            else:
+                full = d_local
+            assert bool((shard.greedy_pick(full) == d_pick).all().item()), "device pick differs from the first maximum of the logits"
+            algo = tensor_bytes("Q6_K", LM_ROWS, LM_COLS) + tokens * 4 * (LM_COLS + LM_ROWS)
+            results[tokens] = {"us_per_step": ms * 1e3 / steps, "gbs": algo / (ms * 1e-3 / steps) / 1e9, "steps": steps,
+                               "algorithmic_bytes": algo, "picks_per_s": tokens * steps / (ms * 1e-3)}
+            if pg is not None:
+                stream.synchronize()
+                pg.close()
+
+    def leave():
+        if world > 1:
+            sys.stdout.flush()
+            torch.cuda.synchronize()
+            dist.barrier()
+            os._exit(0)
+
+    # e2e (single GPU): the host-pointer Q6_K call, hidden state host->device and all logits device->host per step
+    e2e = None
+    if world == 1:
+        be.gemm("Q6_K", packed, hidden[:1], 1, LM_ROWS, LM_COLS)
+        e2e_steps, t0 = 10, time.perf_counter()
+        for _ in range(e2e_steps):
+            y = be.gemm("Q6_K", packed, hidden[:1], 1, LM_ROWS, LM_COLS)
+        e2e_s = time.perf_counter() - t0
+        e2e = {"value": results[1]["algorithmic_bytes"] * e2e_steps / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * LM_COLS,
+               "d2h_bytes_per_step": 4 * LM_ROWS, "api": "zen_cuda_gemm_q6_k (host pointers, tokens = 1)", "steps": e2e_steps}
+    if rank != 0:
+        leave()
+        return
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        import oracle
+        if oracle.reference_available():
+            zr = oracle.Reference()
+            run, kind, cores = (lambda: zr.gemv(oracle.Q6_K, packed, hidden[0], LM_ROWS, LM_COLS, workers=0)), "reference", min(zr.pool_workers(), os.cpu_count() or 1)
+        else:
+            zo = oracle.Oracle()
+            run, kind, cores = (lambda: zo.gemv(oracle.Q6_K, packed, hidden[0], LM_ROWS, LM_COLS)), "port", 1
+        run()
+        t0, n = time.perf_counter(), 0
+        while n == 0 or time.perf_counter() - t0 < args.cpu_budget:
+            run(); n += 1
+        dt = time.perf_counter() - t0
+        cpu = {"value": results[1]["algorithmic_bytes"] * n / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+               "sample": f"{n} full lm_head products (batch 1) in {dt:.1f} s, the reference's Q6_K kernel, its own worker policy"}
+    r1 = results[1]
+    per_gpu = r1["gbs"] / world
+    print(json.dumps({
+        "metric": "lm_head_q6_k_hbm_gbs", "value": r1["gbs"], "unit": "GB/s", "n_gpus": world, "steps": r1["steps"], "warmup": max(3, args.warmup),
+        "ms_per_step": r1["us_per_step"] / 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "Q6_K lm_head 128256 x 4096 (config 3), batch 1 (value) and batch 8, rows sharded over the GPUs, logits all-gathered, greedy pick",
+                   "gather": ("none (one GPU)" if world == 1 else "fused into the product kernel (peer stores over NVLink)" if fused else "NCCL all-gather"),
+                   "l2": f"inputs larger than L2: {ncopy} rotating copies of the {shard_bytes / 1e6:.0f} MB shard per GPU", "launch": "CUDA graph replay"},
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak, "peak_kind": peak_kind, "traffic": None,
+                     "kernel": "gemv_kq_kernel<Q6_K, 1> (per GPU; step time includes the gather wait and the pick)", "launch_us": r1["us_per_step"],
+                     "algorithmic_bytes_per_launch": r1["algorithmic_bytes"] // world},
+        "detail": {"batch1": r1, "batch8": results[8]}, "cpu_baseline": cpu, "clocks": clocks.summary(), "e2e": e2e,
+        "gpu_launches": sum(r["steps"] for r in results.values()) * (4 if fused else 3),
+    }))
+    leave()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -323,6 +661,12 @@ def main() -> None:
 
     if args.workload == "q8_0_gemm" and args.impl != "reference":
         run_gemm_workload(args)
+        return
+    if args.workload == "layer_sweep" and args.impl != "reference":
+        run_layer_sweep(args)
+        return
+    if args.workload == "lm_head" and args.impl != "reference":
+        run_lm_head(args)
         return
     if args.impl == "reference":
         run_reference_arm(args)

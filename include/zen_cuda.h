@@ -220,6 +220,22 @@ int zen_cuda_dev_gemv_gather(zen_cuda_gather* g, const zen_cuda_weights* const* 
  * vector, [world][slot_floats] floats, to d_out (NULL: wait only). */
 int zen_cuda_dev_gather_fetch(zen_cuda_gather* g, float* d_out, void* stream);
 
+/* Greedy token pick on the device: for every token row, the index of the first maximum among the finite logits,
+ * -1 when the row has none.  The greedy branch of the reference's sampler (sample_logits,
+ * src/adapters/dense_transformer_runtime.cpp:391-418): the lowest index wins ties, non-finite logits never win.
+ * A row may be given in up to ZEN_CUDA_MAX_PEERS segments, which is the layout a row-sharded lm_head leaves behind
+ * ([rank][token][shard rows], zen_cuda_dev_gather_fetch): segment i covers row entries
+ * [first_index, first_index + len) and token t of it starts at base + t * token_stride.  d_pick: device int64
+ * [tokens].  Stream-ordered, no synchronisation. */
+typedef struct zen_cuda_pick_segment {
+    const float* base;
+    uint32_t len;
+    uint32_t first_index;
+    uint32_t token_stride;
+    uint32_t reserved;
+} zen_cuda_pick_segment;
+int zen_cuda_dev_greedy_pick(const zen_cuda_pick_segment* segments, size_t count, size_t tokens, int64_t* d_pick, void* stream);
+
 /* Reads and clears the device-side error word the kernels set when a bounded wait gives up
  * (0 = none).  Synchronises `stream`. */
 int zen_cuda_dev_check(void* stream);

@@ -37,6 +37,7 @@ ABI_SYMBOLS = (
     "zen_cuda_dev_gemm_q8_0_noalloc",
     "zen_cuda_gather_region_bytes", "zen_cuda_ipc_alloc", "zen_cuda_ipc_open", "zen_cuda_ipc_close", "zen_cuda_ipc_free",
     "zen_cuda_gather_create", "zen_cuda_gather_destroy", "zen_cuda_dev_gemv_gather", "zen_cuda_dev_gather_fetch",
+    "zen_cuda_dev_greedy_pick",
 )
 
 
@@ -64,6 +65,10 @@ class GemvTask(C.Structure):
 
 class GemmTask(C.Structure):
     _fields_ = [("weights", C.c_void_p), ("y", C.c_void_p), ("rows", C.c_size_t)]
+
+
+class PickSegment(C.Structure):
+    _fields_ = [("base", C.c_void_p), ("len", C.c_uint32), ("first_index", C.c_uint32), ("token_stride", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 def load_library(path: str | None = None) -> C.CDLL:
@@ -119,6 +124,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_gather_destroy.restype = None
     lib.zen_cuda_dev_gemv_gather.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), sz, vp, sz, i, vp]
     lib.zen_cuda_dev_gather_fetch.argtypes = [vp, vp, vp]
+    lib.zen_cuda_dev_greedy_pick.argtypes = [C.POINTER(PickSegment), sz, sz, vp, vp]
     return lib
 
 
@@ -313,6 +319,14 @@ class Backend:
     def dev_quantize_acts(self, d_x: int, d_codes: int, d_scales: int, tokens: int, columns: int, stream: int = 0) -> None:
         if not self.lib.zen_cuda_dev_quantize_acts(d_x, d_codes, d_scales, tokens, columns, stream):
             self._fail("dev_quantize_acts")
+
+    def dev_greedy_pick(self, segments: Sequence[tuple[int, int, int, int]], tokens: int, d_pick: int, stream: int = 0) -> None:
+        """Greedy token pick (first maximum among finite logits, -1 if none) into device int64 [tokens].  A segment is
+        (device address of token 0's first entry, entries per token, index of the first entry, floats between tokens)."""
+        n = len(segments)
+        segs = (PickSegment * n)(*[PickSegment(b, ln, first, stride, 0) for b, ln, first, stride in segments])
+        if not self.lib.zen_cuda_dev_greedy_pick(segs, n, tokens, d_pick, stream):
+            self._fail("dev_greedy_pick")
 
     def dev_check(self, stream: int = 0) -> None:
         code = self.lib.zen_cuda_dev_check(stream)

@@ -29,9 +29,11 @@ def row_bytes(fmt: int, columns: int) -> int:
 
 
 def _round_half_away(v: np.ndarray) -> np.ndarray:
-    """C ``lround`` on float32 input, evaluated exactly (no float32 re-rounding of v +/- 0.5)."""
-    v64 = v.astype(np.float64)
-    return np.where(v64 >= 0, np.floor(v64 + 0.5), np.ceil(v64 - 0.5))
+    """C ``lround`` on float32 input, evaluated exactly: truncation and the fractional part are exact in
+    float32, so no step re-rounds (v +/- 0.5 computed in float32 would, just below a tie)."""
+    v = np.asarray(v, np.float32)
+    t = np.trunc(v)
+    return t + np.where(np.abs(v - t) >= np.float32(0.5), np.sign(v), np.float32(0)).astype(np.float32)
 
 
 def quantize_q8_0(w: np.ndarray) -> np.ndarray:

@@ -25,6 +25,7 @@
 #include "gemm_q8_0_i8.cuh"
 #include "gemv_kq.cuh"
 #include "gemv_q8_0.cuh"
+#include "greedy_pick.cuh"
 #include "quantize_acts.cuh"
 #include "repack.cuh"
 
@@ -1029,6 +1030,33 @@ int zen_cuda_dev_gather_fetch(zen_cuda_gather* g, float* d_out, void* stream) {
     zk::gather_fetch_kernel<<<grid, 256, 0, stream ? static_cast<cudaStream_t>(stream) : s.stream>>>(g->dev, d_out, s.d_error);
     ++s.stats.dispatches;
     if (cudaGetLastError() != cudaSuccess) return set_error(s, "dev_gather_fetch: launch failed") ? 1 : 0;
+    return 1;
+}
+
+int zen_cuda_dev_greedy_pick(const zen_cuda_pick_segment* segments, size_t count, size_t tokens, int64_t* d_pick, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!segments || !count || count > zk::kPickMaxSegments || !tokens || tokens > 65535 || !d_pick) return set_error(s, "dev_greedy_pick: bad arguments") ? 1 : 0;
+    zk::PickParams p{};
+    size_t longest = 0;
+    for (size_t i = 0; i < count; ++i) {
+        if (!segments[i].base && segments[i].len) return set_error(s, "dev_greedy_pick: null segment") ? 1 : 0;
+        if (static_cast<uint64_t>(segments[i].first_index) + segments[i].len > 0xffffffffull) return set_error(s, "dev_greedy_pick: index range too large") ? 1 : 0;
+        p.seg[i] = zk::PickSegment{segments[i].base, segments[i].len, segments[i].first_index, segments[i].token_stride, 0};
+        longest = std::max<size_t>(longest, segments[i].len);
+    }
+    p.nseg = static_cast<uint32_t>(count);
+    // enough CTAs to fill the machine once, at least 2048 entries each
+    const size_t want = std::max<size_t>(1, static_cast<size_t>(s.sm_count) * 2 / (count * tokens));
+    p.ctas_per_segment = static_cast<uint32_t>(std::max<size_t>(1, std::min(want, (longest + 2047) / 2048)));
+    p.keys = reinterpret_cast<unsigned long long*>(d_pick);
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : s.stream;
+    ZC_CUDA(s, cudaMemsetAsync(d_pick, 0, tokens * sizeof(int64_t), st));
+    zk::pick_scan_kernel<<<dim3(p.nseg * p.ctas_per_segment, static_cast<unsigned>(tokens)), zk::kPickThreads, 0, st>>>(p);
+    zk::pick_finish_kernel<<<static_cast<unsigned>((tokens + 63) / 64), 64, 0, st>>>(p.keys, static_cast<uint32_t>(tokens));
+    s.stats.dispatches += 2;
+    if (cudaGetLastError() != cudaSuccess) return set_error(s, "dev_greedy_pick: launch failed") ? 1 : 0;
     return 1;
 }
 
