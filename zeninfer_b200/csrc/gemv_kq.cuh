@@ -24,6 +24,7 @@ namespace zk {
 
 constexpr int kKqSegElems = 4096;   // weights per row per stage segment (128 Q4_0 blocks, 16 Q6_K super-blocks)
 constexpr int kKqMaxPlanes = 4;
+constexpr int kKqPartialFloats = kTeams * 2 * kTeamWarps * kTeamWarps;   // [team][unit parity][K slice][row]
 
 // Per-format geometry of the planes a row is split into (repack.cuh).
 template <int kFormat> struct KqFormat;
@@ -79,7 +80,8 @@ __host__ __device__ inline size_t gemv_kq_smem_bytes(uint32_t nseg, int batch) {
     return static_cast<size_t>(KqFormat<kFormat>::kStages) * kq_stage_bytes<kFormat>()
            + static_cast<size_t>(batch) * 2 * kpad                 // two digit planes, natural order
            + static_cast<size_t>(batch) * (kpad / 32) * 8          // per-block scale (d/256) and code sum
-           + 2 * KqFormat<kFormat>::kStages * 8 + 16;
+           + 2 * KqFormat<kFormat>::kStages * 8 + 16
+           + kKqPartialFloats * sizeof(float);                      // batch 1: per-warp partial row sums
 }
 
 struct KqWalk {  // GroupWalk over KqParams
@@ -109,6 +111,56 @@ __device__ __forceinline__ int dot16(const uint4& w, const uint4& x) {
 // from borrowing across bytes, flipping it back afterwards leaves the two's-complement difference.
 __device__ __forceinline__ uint32_t sub32_bytes(uint32_t q) { return ((q | 0x80808080u) - 0x20202020u) ^ 0x80808080u; }
 
+// Sum of `v` over the lanes of a warp for R rows at once.  Each exchange step halves the number of rows a lane still
+// carries, so R rows cost R - 1 + (5 - log2 R) shuffles instead of 5 R.  On return every lane holds the complete sum
+// of row `row` (lanes that share the low bits hold the same row); the order of additions is fixed.
+template <int R>
+__device__ __forceinline__ float kq_reduce_rows(const float (&acc)[R], int lane, uint32_t& row) {
+    static_assert(R == 4 || R == 8, "four or eight rows per warp");
+    float a4[4];
+    if constexpr (R == 8) {
+        const bool up = lane & 16;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float send = up ? acc[i] : acc[i + 4], keep = up ? acc[i + 4] : acc[i];
+            a4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) a4[i] = acc[i];
+    }
+    constexpr int o2 = R == 8 ? 8 : 16, o1 = R == 8 ? 4 : 8;
+    float a2[2];
+    {
+        const bool up = lane & o2;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float send = up ? a4[i] : a4[i + 2], keep = up ? a4[i + 2] : a4[i];
+            a2[i] = keep + __shfl_xor_sync(0xffffffffu, send, o2);
+        }
+    }
+    float a1;
+    {
+        const bool up = lane & o1;
+        const float send = up ? a2[0] : a2[1], keep = up ? a2[1] : a2[0];
+        a1 = keep + __shfl_xor_sync(0xffffffffu, send, o1);
+    }
+#pragma unroll
+    for (int o = o1 >> 1; o > 0; o >>= 1) a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+    if constexpr (R == 8) row = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    else row = ((lane >> 4) & 1) * 2 + ((lane >> 3) & 1);
+    return a1;
+}
+
+// Team-wide barrier that also agrees on failure: true when any of the team's threads passed `failed`.
+__device__ __forceinline__ bool team_barrier_any(int team, bool failed) {
+    uint32_t any;
+    asm volatile(
+        "{ .reg .pred p, q; setp.ne.u32 q, %3, 0; barrier.red.or.pred p, %1, %2, q; selp.u32 %0, 1, 0, p; }"
+        : "=r"(any) : "r"(2 + team), "r"(kTeamWarps * 32), "r"(static_cast<uint32_t>(failed)) : "memory");
+    return any != 0;
+}
+
 template <int kFormat, int kBatch>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_constant__ KqParams p) {
     using F = KqFormat<kFormat>;
@@ -124,7 +176,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
     uint64_t* full = reinterpret_cast<uint64_t*>(xsum + static_cast<size_t>(kBatch) * (kpad / 32));
     uint64_t* empty = full + kStages;
     volatile int* abort_word = reinterpret_cast<volatile int*>(empty + kStages);
-    float* stash = reinterpret_cast<float*>(empty + kStages + 2);   // gather only: [batch][rows of this CTA's slice]
+    float* partial = reinterpret_cast<float*>(empty + kStages + 2);   // batch 1: [team][unit parity][K slice][row]
+    float* stash = partial + kKqPartialFloats;                        // gather only: [batch][rows of this CTA's slice]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint32_t r_first, r_last;
@@ -149,6 +202,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
         bool announce = p.gather.world != 0 && blockIdx.x == 0;   // see gemv_q8_0_kernel
         KqWalk walk(r_first, r_last);
         const int my_row = lane / F::kPlanes, my_plane = lane % F::kPlanes;  // one copy per (row, plane) of a unit
+        bool contiguous = p.nseg == 1 && p.K == static_cast<uint32_t>(kKqSegElems);
+#pragma unroll
+        for (int pl = 0; pl < F::kPlanes; ++pl) contiguous = contiguous && p.pitch[pl] == F::seg_bytes(pl);
         while (!walk.done() && ok) {
             RowGroup pair[kTeams];
 #pragma unroll
@@ -183,7 +239,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                     for (int pl = 0; pl < F::kPlanes; ++pl) row_bytes += (elems / 256 * F::bytes_per_256(pl) + (elems % 256) * F::bytes_per_256(pl) / 256 + 15) & ~15u;
                     if (lane == 0) mbar_arrive_expect_tx(&full[stage], g.nrows * row_bytes);
                     __syncwarp();
-                    if (my_row < static_cast<int>(g.nrows) && my_row < kTeamWarps) {
+                    if (contiguous) {
+                        // rows of one full segment follow each other in every plane: one copy per plane for the whole group
+                        if (lane < F::kPlanes) {
+                            bulk_g2s(ring + stage * kStageBytes + kq_plane_offset<kFormat>(lane),
+                                     t.plane[lane] + static_cast<size_t>(g.row0) * p.pitch[lane], g.nrows * F::seg_bytes(lane), &full[stage]);
+                        }
+                    } else if (my_row < static_cast<int>(g.nrows) && my_row < kTeamWarps) {
                         const uint32_t per256 = F::bytes_per_256(my_plane);
                         const uint32_t bytes = (elems / 256 * per256 + (elems % 256) * per256 / 256 + 15) & ~15u;
                         const uint32_t seg_off = static_cast<uint32_t>(static_cast<uint64_t>(s) * kKqSegElems / 256 * per256);
@@ -252,105 +314,240 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
 
     const int team = warp / kTeamWarps, twarp = warp % kTeamWarps;
     bool ok = *abort_word == 0;
-    uint32_t pair_base = 0;
-    KqWalk walk(r_first, r_last);
-    while (!walk.done() && ok) {
-        RowGroup pair[kTeams];
-#pragma unroll
-        for (int m = 0; m < kTeams; ++m) pair[m] = walk.next(p);
-        RowGroup g = pair[0];
-        if constexpr (kTeams > 1) { if (team == 1) g = pair[kTeams - 1]; }
-        const KqTask& t = p.task[g.task];
-        const uint32_t row = g.row0 + twarp;
-        const bool valid = static_cast<uint32_t>(twarp) < g.nrows;
-        float acc[kBatch];
-#pragma unroll
-        for (int b = 0; b < kBatch; ++b) acc[b] = 0.0f;
+    if constexpr (kBatch == 1) {
+        // ---- batch 1: a warp owns a slice of K and walks every row of the unit with its activations in registers ----
+        // Shared memory is then read for weights only (reading two activation digits per weight from it costs several
+        // times the weight bytes in wavefronts and capped the kernel at a third of the HBM rate).
+        //   Q4_0: warp = (K slice of 32 blocks, half of the eight rows); a lane owns one 32-weight block
+        //   Q6_K: warp = K slice of two super-blocks, all eight rows;     a lane owns one 16-weight scale group
+        constexpr int kR = kFormat == 2 ? 4 : 8;                       // rows per warp
+        constexpr int kSlices = kFormat == 2 ? 4 : 8;                  // K slices per segment
+        const uint32_t kslice = static_cast<uint32_t>(twarp) % kSlices;
+        const uint32_t rowbase = kFormat == 2 ? (static_cast<uint32_t>(twarp) / kSlices) * kR : 0u;
+        // Q6_K lane geometry (src/quant.cpp:500-517): element e = half*128 + group*32 + l lives in ql byte
+        // half*64 + (group%2)*32 + l (low nibble for group < 2), qh byte half*32 + l bits 2*group.., scale half*8 + group*2 + l/16
+        const uint32_t sg = lane & 15, qhalf = sg >> 3, group = (sg >> 1) & 3, six = sg & 1;
+        const uint32_t shift4 = group >= 2 ? 4u : 0u, shift2 = group * 2;
+        const uint32_t sbl = kslice * 2 + (static_cast<uint32_t>(lane) >> 4);   // super-block within the segment
 
-        for (uint32_t s = 0; s < p.nseg; ++s) {
-            const uint32_t unit = pair_base + s * kTeams + team;
-            const uint32_t stage = unit % kStages;
-            if (*abort_word || !mbar_wait(&full[stage], (unit / kStages) & 1)) {
-                if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrFullWaitTimeout); }
-                ok = false;
-                break;
+        uint4 xa = make_uint4(0, 0, 0, 0), xb = xa, xc = xa, xd4 = xa;   // Q4_0: digit 1 lo/hi halves, digit 2 lo/hi; Q6_K: digit 1, digit 2
+        float xs = 0.0f;     // activation scale of the lane's block, with the digit weight folded in
+        int bias = 0;        // minus (zero point x sum of the lane's activation codes), the dp4a chain's starting value
+        bool live = false;
+        auto load_x = [&](uint32_t seg) {
+            if (kFormat == 2) {
+                const uint32_t b = seg * (kKqSegElems / 32) + kslice * 32 + lane;
+                live = b * 32 < p.K;
+                if (live) {
+                    const uint4* x1 = reinterpret_cast<const uint4*>(xd + b * 32);
+                    const uint4* x2 = reinterpret_cast<const uint4*>(xd + kpad + b * 32);
+                    xa = x1[0]; xb = x1[1]; xc = x2[0]; xd4 = x2[1];
+                    xs = xscale[b] * (1.0f / 16.0f);   // high nibbles enter sixteen-fold, so every sum is sixteen-fold
+                    bias = -128 * xsum[b];             // -8 * sum, sixteen-fold
+                }
+            } else {
+                const uint32_t e0 = seg * kKqSegElems + sbl * 256 + qhalf * 128 + group * 32 + six * 16;
+                live = e0 < p.K;
+                if (live) {
+                    xa = *reinterpret_cast<const uint4*>(xd + e0);
+                    xc = *reinterpret_cast<const uint4*>(xd + kpad + e0);
+                    xs = xscale[e0 / 32];
+                    const uint4 ones = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+                    bias = -32 * (dot16(ones, xa) * 256 + dot16(ones, xc));
+                }
             }
-            if (valid) {
+        };
+        if (p.nseg == 1) load_x(0);
+
+        uint32_t pair_index = 0;
+        KqWalk walk(r_first, r_last);
+        while (!walk.done()) {
+            RowGroup pair[kTeams];
+#pragma unroll
+            for (int m = 0; m < kTeams; ++m) pair[m] = walk.next(p);
+            RowGroup g = pair[0];
+            if constexpr (kTeams > 1) { if (team == 1) g = pair[kTeams - 1]; }
+            const KqTask& t = p.task[g.task];
+            float acc[kR];
+#pragma unroll
+            for (int r = 0; r < kR; ++r) acc[r] = 0.0f;
+            bool failed = false;
+            for (uint32_t s = 0; s < p.nseg; ++s) {
+                const uint32_t unit = (pair_index * p.nseg + s) * kTeams + team;
+                const uint32_t stage = unit % kStages;
+                if (*abort_word || !mbar_wait(&full[stage], (unit / kStages) & 1)) {
+                    if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrFullWaitTimeout); }
+                    failed = true;
+                    break;
+                }
+                if (p.nseg > 1) load_x(s);
                 const uint8_t* st = ring + stage * kStageBytes;
-                const uint32_t e_base = s * kKqSegElems;
-                const uint32_t elems = min(static_cast<uint32_t>(kKqSegElems), p.K - e_base);
                 if (kFormat == 2) {
-                    // ---- Q4_0: a lane owns a 32-weight block: 16 nibble bytes + one scale ----
-                    const uint4* nib = reinterpret_cast<const uint4*>(st + kq_plane_offset<kFormat>(0) + twarp * F::seg_bytes(0));
-                    const __half* ws = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(1) + twarp * F::seg_bytes(1));
+                    const uint32_t bl = kslice * 32 + lane;
 #pragma unroll
-                    for (int i = 0; i < kKqSegElems / 32 / 32; ++i) {
-                        const uint32_t bl = i * 32 + lane;
-                        if (bl * 32 < elems) {
-                            const uint4 w = nib[bl];
-                            const float dw = __half2float(ws[bl]);
-                            // low nibbles are elements 0..15, high nibbles elements 16..31 (src/quant.cpp:391-397)
-                            const uint4 lo = make_uint4(w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu);
-                            const uint4 hi = make_uint4((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, (w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu);
-                            const uint32_t b = e_base / 32 + bl;
-#pragma unroll
-                            for (int tk = 0; tk < kBatch; ++tk) {
-                                const uint4* x1 = reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + b * 32);
-                                const uint4* x2 = reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + kpad + b * 32);
-                                const int i1 = dot16(lo, x1[0]) + dot16(hi, x1[1]);
-                                const int i2 = dot16(lo, x2[0]) + dot16(hi, x2[1]);
-                                const int isum = i1 * 256 + i2 - 8 * xsum[static_cast<size_t>(tk) * (kpad / 32) + b];
-                                acc[tk] = fmaf(dw * xscale[static_cast<size_t>(tk) * (kpad / 32) + b], static_cast<float>(isum), acc[tk]);
-                            }
+                    for (int r = 0; r < kR; ++r) {
+                        const uint32_t row = rowbase + r;
+                        if (row < g.nrows) {
+                            const uint4 w = *reinterpret_cast<const uint4*>(st + kq_plane_offset<kFormat>(0) + row * F::seg_bytes(0) + bl * 16);
+                            const float dw = __half2float(*reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(1) + row * F::seg_bytes(1) + bl * 2));
+                            // low nibbles are elements 0..15, high nibbles elements 16..31 (src/quant.cpp:391-397); the high
+                            // nibbles stay in place (value x 16, an unsigned byte), which saves the shifts
+                            const uint32_t m = 0x0F0F0F0Fu;
+                            int a = dp4a_us(w.x & m, xa.x, 0), b = dp4a_us(w.x & ~m, xb.x, 0), c = dp4a_us(w.x & m, xc.x, 0), d = dp4a_us(w.x & ~m, xd4.x, bias);
+                            a = dp4a_us(w.y & m, xa.y, a); b = dp4a_us(w.y & ~m, xb.y, b); c = dp4a_us(w.y & m, xc.y, c); d = dp4a_us(w.y & ~m, xd4.y, d);
+                            a = dp4a_us(w.z & m, xa.z, a); b = dp4a_us(w.z & ~m, xb.z, b); c = dp4a_us(w.z & m, xc.z, c); d = dp4a_us(w.z & ~m, xd4.z, d);
+                            a = dp4a_us(w.w & m, xa.w, a); b = dp4a_us(w.w & ~m, xb.w, b); c = dp4a_us(w.w & m, xc.w, c); d = dp4a_us(w.w & ~m, xd4.w, d);
+                            // 16 * (256 * (lo.q1 + hi.q1) + (lo.q2 + hi.q2) - 8 * sum) = 4096 a + 256 b + 16 c + d
+                            const int isum = ((a * 16 + b) * 16 + c) * 16 + d;
+                            const float term = (dw * xs) * static_cast<float>(isum);
+                            acc[r] += live ? term : 0.0f;   // a lane past the row holds stale scale bits: select, do not multiply
                         }
                     }
                 } else {
-                    // ---- Q6_K: a lane owns one 16-weight scale group; a warp covers two super-blocks a pass ----
-                    const uint8_t* ql = st + kq_plane_offset<kFormat>(0) + twarp * F::seg_bytes(0);
-                    const uint8_t* qh = st + kq_plane_offset<kFormat>(1) + twarp * F::seg_bytes(1);
-                    const int8_t* sc = reinterpret_cast<const int8_t*>(st + kq_plane_offset<kFormat>(2) + twarp * F::seg_bytes(2));
-                    const __half* dd = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(3) + twarp * F::seg_bytes(3));
-                    const uint32_t sg = lane & 15, half = sg >> 3, group = (sg >> 1) & 3, six = sg & 1;
-                    const uint32_t shift4 = group >= 2 ? 4u : 0u, shift2 = group * 2;
-                    // element e = half*128 + group*32 + l: ql byte half*64 + (group%2)*32 + l, qh byte half*32 + l,
-                    // scale half*8 + group*2 + l/16 == sg (src/quant.cpp:500-517)
-#pragma unroll 4
-                    for (int i = 0; i < kKqSegElems / 256 / 2; ++i) {
-                        const uint32_t sbl = i * 2 + (lane >> 4);
-                        if (sbl * 256 < elems) {
-                            const uint4 l4 = *reinterpret_cast<const uint4*>(ql + sbl * 128 + half * 64 + (group & 1) * 32 + six * 16);
-                            const uint4 h4 = *reinterpret_cast<const uint4*>(qh + sbl * 64 + half * 32 + six * 16);
-                            uint4 q;
-                            q.x = sub32_bytes(((l4.x >> shift4) & 0x0F0F0F0Fu) | (((h4.x >> shift2) & 0x03030303u) << 4));
-                            q.y = sub32_bytes(((l4.y >> shift4) & 0x0F0F0F0Fu) | (((h4.y >> shift2) & 0x03030303u) << 4));
-                            q.z = sub32_bytes(((l4.z >> shift4) & 0x0F0F0F0Fu) | (((h4.z >> shift2) & 0x03030303u) << 4));
-                            q.w = sub32_bytes(((l4.w >> shift4) & 0x0F0F0F0Fu) | (((h4.w >> shift2) & 0x03030303u) << 4));
-                            const float dsc = __half2float(dd[sbl]) * static_cast<float>(sc[sbl * 16 + sg]);  // (d * scale), the reference's order
-                            const uint32_t e0 = e_base + sbl * 256 + half * 128 + group * 32 + six * 16;
+                    const uint8_t* ql = st + kq_plane_offset<kFormat>(0) + sbl * 128 + qhalf * 64 + (group & 1) * 32 + six * 16;
+                    const uint8_t* qh = st + kq_plane_offset<kFormat>(1) + sbl * 64 + qhalf * 32 + six * 16;
+                    const int8_t* sc = reinterpret_cast<const int8_t*>(st + kq_plane_offset<kFormat>(2)) + sbl * 16 + sg;
+                    const __half* dd = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(3)) + sbl;
 #pragma unroll
-                            for (int tk = 0; tk < kBatch; ++tk) {
-                                const uint4 x1 = *reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + e0);
-                                const uint4 x2 = *reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + kpad + e0);
-                                const int isum = dot16(q, x1) * 256 + dot16(q, x2);
-                                acc[tk] = fmaf(dsc * xscale[static_cast<size_t>(tk) * (kpad / 32) + e0 / 32], static_cast<float>(isum), acc[tk]);
+                    for (int r = 0; r < kR; ++r) {
+                        if (static_cast<uint32_t>(r) < g.nrows) {
+                            const uint4 l4 = *reinterpret_cast<const uint4*>(ql + r * F::seg_bytes(0));
+                            const uint4 h4 = *reinterpret_cast<const uint4*>(qh + r * F::seg_bytes(1));
+                            // codes stay 0..63; the zero point 32 is in `bias`
+                            const uint32_t q0 = ((l4.x >> shift4) & 0x0F0F0F0Fu) | (((h4.x >> shift2) & 0x03030303u) << 4);
+                            const uint32_t q1 = ((l4.y >> shift4) & 0x0F0F0F0Fu) | (((h4.y >> shift2) & 0x03030303u) << 4);
+                            const uint32_t q2 = ((l4.z >> shift4) & 0x0F0F0F0Fu) | (((h4.z >> shift2) & 0x03030303u) << 4);
+                            const uint32_t q3 = ((l4.w >> shift4) & 0x0F0F0F0Fu) | (((h4.w >> shift2) & 0x03030303u) << 4);
+                            int a = dp4a_us(q0, xa.x, 0), c = dp4a_us(q0, xc.x, bias);
+                            a = dp4a_us(q1, xa.y, a); c = dp4a_us(q1, xc.y, c);
+                            a = dp4a_us(q2, xa.z, a); c = dp4a_us(q2, xc.z, c);
+                            a = dp4a_us(q3, xa.w, a); c = dp4a_us(q3, xc.w, c);
+                            const float dsc = __half2float(dd[r * (F::seg_bytes(3) / 2)]) * static_cast<float>(sc[r * F::seg_bytes(2)]);  // (d * scale), the reference's order
+                            const float term = (dsc * xs) * static_cast<float>(a * 256 + c);
+                            acc[r] += live ? term : 0.0f;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[stage]);
+            }
+            // rows of the unit: sum over the warp's lanes, then over the K slices through shared memory
+            uint32_t prow;
+            const float psum = kq_reduce_rows<kR>(acc, lane, prow);
+            float* part = partial + (team * 2 + (pair_index & 1)) * (kTeamWarps * kTeamWarps);
+            if ((lane & (kR == 8 ? 3 : 7)) == 0) part[kslice * kTeamWarps + rowbase + prow] = psum;
+            if (team_barrier_any(team, failed)) { ok = false; break; }
+            if (twarp == 0 && static_cast<uint32_t>(lane) < g.nrows) {
+                float v = part[lane];
+#pragma unroll
+                for (int k = 1; k < kSlices; ++k) v += part[k * kTeamWarps + lane];
+                const uint32_t row = g.row0 + lane;
+                if (t.y) t.y[row] = v;
+                if (p.gather.world) stash[t.first_row + row - r_first] = v;
+            }
+            ++pair_index;
+        }
+    } else {
+        uint32_t pair_base = 0;
+        KqWalk walk(r_first, r_last);
+        while (!walk.done() && ok) {
+            RowGroup pair[kTeams];
+    #pragma unroll
+            for (int m = 0; m < kTeams; ++m) pair[m] = walk.next(p);
+            RowGroup g = pair[0];
+            if constexpr (kTeams > 1) { if (team == 1) g = pair[kTeams - 1]; }
+            const KqTask& t = p.task[g.task];
+            const uint32_t row = g.row0 + twarp;
+            const bool valid = static_cast<uint32_t>(twarp) < g.nrows;
+            float acc[kBatch];
+    #pragma unroll
+            for (int b = 0; b < kBatch; ++b) acc[b] = 0.0f;
+
+            for (uint32_t s = 0; s < p.nseg; ++s) {
+                const uint32_t unit = pair_base + s * kTeams + team;
+                const uint32_t stage = unit % kStages;
+                if (*abort_word || !mbar_wait(&full[stage], (unit / kStages) & 1)) {
+                    if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrFullWaitTimeout); }
+                    ok = false;
+                    break;
+                }
+                if (valid) {
+                    const uint8_t* st = ring + stage * kStageBytes;
+                    const uint32_t e_base = s * kKqSegElems;
+                    const uint32_t elems = min(static_cast<uint32_t>(kKqSegElems), p.K - e_base);
+                    if (kFormat == 2) {
+                        // ---- Q4_0: a lane owns a 32-weight block: 16 nibble bytes + one scale ----
+                        const uint4* nib = reinterpret_cast<const uint4*>(st + kq_plane_offset<kFormat>(0) + twarp * F::seg_bytes(0));
+                        const __half* ws = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(1) + twarp * F::seg_bytes(1));
+    #pragma unroll
+                        for (int i = 0; i < kKqSegElems / 32 / 32; ++i) {
+                            const uint32_t bl = i * 32 + lane;
+                            if (bl * 32 < elems) {
+                                const uint4 w = nib[bl];
+                                const float dw = __half2float(ws[bl]);
+                                // low nibbles are elements 0..15, high nibbles elements 16..31 (src/quant.cpp:391-397)
+                                const uint4 lo = make_uint4(w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu);
+                                const uint4 hi = make_uint4((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, (w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu);
+                                const uint32_t b = e_base / 32 + bl;
+    #pragma unroll
+                                for (int tk = 0; tk < kBatch; ++tk) {
+                                    const uint4* x1 = reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + b * 32);
+                                    const uint4* x2 = reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + kpad + b * 32);
+                                    const int i1 = dot16(lo, x1[0]) + dot16(hi, x1[1]);
+                                    const int i2 = dot16(lo, x2[0]) + dot16(hi, x2[1]);
+                                    const int isum = i1 * 256 + i2 - 8 * xsum[static_cast<size_t>(tk) * (kpad / 32) + b];
+                                    acc[tk] = fmaf(dw * xscale[static_cast<size_t>(tk) * (kpad / 32) + b], static_cast<float>(isum), acc[tk]);
+                                }
+                            }
+                        }
+                    } else {
+                        // ---- Q6_K: a lane owns one 16-weight scale group; a warp covers two super-blocks a pass ----
+                        const uint8_t* ql = st + kq_plane_offset<kFormat>(0) + twarp * F::seg_bytes(0);
+                        const uint8_t* qh = st + kq_plane_offset<kFormat>(1) + twarp * F::seg_bytes(1);
+                        const int8_t* sc = reinterpret_cast<const int8_t*>(st + kq_plane_offset<kFormat>(2) + twarp * F::seg_bytes(2));
+                        const __half* dd = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(3) + twarp * F::seg_bytes(3));
+                        const uint32_t sg = lane & 15, half = sg >> 3, group = (sg >> 1) & 3, six = sg & 1;
+                        const uint32_t shift4 = group >= 2 ? 4u : 0u, shift2 = group * 2;
+                        // element e = half*128 + group*32 + l: ql byte half*64 + (group%2)*32 + l, qh byte half*32 + l,
+                        // scale half*8 + group*2 + l/16 == sg (src/quant.cpp:500-517)
+    #pragma unroll 4
+                        for (int i = 0; i < kKqSegElems / 256 / 2; ++i) {
+                            const uint32_t sbl = i * 2 + (lane >> 4);
+                            if (sbl * 256 < elems) {
+                                const uint4 l4 = *reinterpret_cast<const uint4*>(ql + sbl * 128 + half * 64 + (group & 1) * 32 + six * 16);
+                                const uint4 h4 = *reinterpret_cast<const uint4*>(qh + sbl * 64 + half * 32 + six * 16);
+                                uint4 q;
+                                q.x = sub32_bytes(((l4.x >> shift4) & 0x0F0F0F0Fu) | (((h4.x >> shift2) & 0x03030303u) << 4));
+                                q.y = sub32_bytes(((l4.y >> shift4) & 0x0F0F0F0Fu) | (((h4.y >> shift2) & 0x03030303u) << 4));
+                                q.z = sub32_bytes(((l4.z >> shift4) & 0x0F0F0F0Fu) | (((h4.z >> shift2) & 0x03030303u) << 4));
+                                q.w = sub32_bytes(((l4.w >> shift4) & 0x0F0F0F0Fu) | (((h4.w >> shift2) & 0x03030303u) << 4));
+                                const float dsc = __half2float(dd[sbl]) * static_cast<float>(sc[sbl * 16 + sg]);  // (d * scale), the reference's order
+                                const uint32_t e0 = e_base + sbl * 256 + half * 128 + group * 32 + six * 16;
+    #pragma unroll
+                                for (int tk = 0; tk < kBatch; ++tk) {
+                                    const uint4 x1 = *reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + e0);
+                                    const uint4 x2 = *reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + kpad + e0);
+                                    const int isum = dot16(q, x1) * 256 + dot16(q, x2);
+                                    acc[tk] = fmaf(dsc * xscale[static_cast<size_t>(tk) * (kpad / 32) + e0 / 32], static_cast<float>(isum), acc[tk]);
+                                }
                             }
                         }
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[stage]);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[stage]);
-        }
-        if (!ok) break;
-        pair_base += kTeams * p.nseg;
-        if (valid) {
-#pragma unroll
-            for (int tk = 0; tk < kBatch; ++tk) {
-                float v = acc[tk];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0 && t.y) t.y[static_cast<size_t>(tk) * t.rows + row] = v;
-                if (lane == 0 && p.gather.world) stash[static_cast<size_t>(tk) * n_mine + (t.first_row + row - r_first)] = v;
+            if (!ok) break;
+            pair_base += kTeams * p.nseg;
+            if (valid) {
+    #pragma unroll
+                for (int tk = 0; tk < kBatch; ++tk) {
+                    float v = acc[tk];
+    #pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                    if (lane == 0 && t.y) t.y[static_cast<size_t>(tk) * t.rows + row] = v;
+                    if (lane == 0 && p.gather.world) stash[static_cast<size_t>(tk) * n_mine + (t.first_row + row - r_first)] = v;
+                }
             }
         }
     }

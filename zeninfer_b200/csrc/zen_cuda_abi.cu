@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -89,6 +90,10 @@ struct State {
     void* encode_tiled{};    // cuTensorMapEncodeTiled, resolved through the runtime
     int* h_error{};   // mapped pinned word the kernels write on a bounded-wait timeout
     int* d_error{};   // device alias of h_error
+    // Small results skip the copy engine: the kernels store them straight into mapped pinned memory, a one-thread
+    // kernel behind them raises a sequence number there, and the calling thread polls it.
+    float* h_result{}; float* d_result{}; size_t h_result_bytes{};
+    volatile unsigned* h_done{}; unsigned* d_done{}; unsigned done_seq{};
 };
 
 State& state() { static State s; return s; }
@@ -612,6 +617,51 @@ bool ensure_scratch(State& s, size_t x_bytes, size_t y_bytes) {
     return true;
 }
 
+constexpr size_t kDirectResultBytes = size_t(1) << 20;  // results up to this size are written to host memory by the kernel itself
+
+__global__ void publish_done_kernel(volatile unsigned* done, unsigned seq) {
+    __threadfence_system();  // the grid before this one has finished; its stores to host memory are ordered before the flag
+    *done = seq;
+}
+
+bool ensure_direct_result(State& s, size_t bytes) {
+    if (!s.h_done) {
+        unsigned* h = nullptr;
+        ZC_CUDA(s, cudaHostAlloc(reinterpret_cast<void**>(&h), 64, cudaHostAllocMapped));
+        *h = 0;
+        s.h_done = h;
+        ZC_CUDA(s, cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.d_done), h, 0));
+    }
+    if (bytes > s.h_result_bytes) {
+        if (s.h_result) { cudaStreamSynchronize(s.stream); cudaFreeHost(s.h_result); }
+        s.h_result = nullptr; s.d_result = nullptr; s.h_result_bytes = 0;
+        const size_t cap = std::max(bytes, size_t(64) << 10);
+        ZC_CUDA(s, cudaHostAlloc(reinterpret_cast<void**>(&s.h_result), cap, cudaHostAllocMapped));
+        ZC_CUDA(s, cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.d_result), s.h_result, 0));
+        s.h_result_bytes = cap;
+    }
+    return true;
+}
+
+// Waits for publish_done_kernel(seq): polls the mapped word for a while, then falls back to a stream synchronise
+// (which also surfaces a failed launch or a device fault as an error instead of an endless poll).
+bool wait_done(State& s, unsigned seq) {
+    const auto t0 = clock_type::now();
+    unsigned spins = 0;
+    while (*s.h_done != seq) {
+        if ((++spins & 1023u) == 0 && us_since(t0) > 2000) {
+            ZC_CUDA(s, cudaStreamSynchronize(s.stream));
+            if (*s.h_done != seq) return set_error(s, "result flag was not raised");
+            break;
+        }
+#if defined(__x86_64__) || defined(__i386__)
+        __builtin_ia32_pause();
+#endif
+    }
+    std::atomic_thread_fence(std::memory_order_acquire);
+    return true;
+}
+
 bool check_error_word(State& s) {
     if (*s.h_error == 0) return true;
     const int code = *s.h_error;
@@ -634,7 +684,11 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
         total_rows += rows[i];
     }
     const size_t x_bytes = tokens * cols * sizeof(float), y_bytes = tokens * total_rows * sizeof(float);
-    if (!ensure_scratch(s, x_bytes, y_bytes)) return false;
+    const bool direct = y_bytes <= kDirectResultBytes;
+    if (!ensure_scratch(s, x_bytes, direct ? 0 : y_bytes)) return false;
+    if (direct && !ensure_direct_result(s, y_bytes)) return false;
+    float* const d_result = direct ? s.d_result : s.d_y;
+    const float* const h_result = direct ? s.h_result : s.h_stage;
     auto t0 = clock_type::now();
     std::memcpy(s.h_stage, x, x_bytes);
     ZC_CUDA(s, cudaMemcpyAsync(s.d_x, s.h_stage, x_bytes, cudaMemcpyHostToDevice, s.stream));
@@ -643,7 +697,7 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     // Token chunks of up to eight rows per launch; each task's device output is [tokens][rows_i].
     float* d_out[zk::kMaxTasks];
     size_t off = 0;
-    for (size_t i = 0; i < count; ++i) { d_out[i] = s.d_y + off; off += tokens * rows[i]; }
+    for (size_t i = 0; i < count; ++i) { d_out[i] = d_result + off; off += tokens * rows[i]; }
     const size_t chunk = max_tokens_per_launch(s, fmt, cols, act_mode);
     if (!chunk) return set_error(s, "columns too large: one activation row does not fit shared memory");
     // More than one decode launch worth of int8-activation Q8_0 tokens: the tensor-core GEMM.
@@ -660,14 +714,22 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     }
     s.stats.launch_us += us_since(t0);
     t0 = clock_type::now();
-    ZC_CUDA(s, cudaMemcpyAsync(s.h_stage, s.d_y, y_bytes, cudaMemcpyDeviceToHost, s.stream));
-    ZC_CUDA(s, cudaStreamSynchronize(s.stream));
+    if (direct) {
+        const unsigned seq = ++s.done_seq;
+        publish_done_kernel<<<1, 1, 0, s.stream>>>(s.d_done, seq);
+        ++s.stats.dispatches;
+        if (cudaGetLastError() != cudaSuccess) return set_error(s, "result flag launch failed");
+        if (!wait_done(s, seq)) return false;
+    } else {
+        ZC_CUDA(s, cudaMemcpyAsync(s.h_stage, s.d_y, y_bytes, cudaMemcpyDeviceToHost, s.stream));
+        ZC_CUDA(s, cudaStreamSynchronize(s.stream));
+    }
     s.stats.wait_us += us_since(t0);
     if (!check_error_word(s)) return false;
     t0 = clock_type::now();
     off = 0;
     for (size_t i = 0; i < count; ++i) {
-        std::memcpy(ys[i], reinterpret_cast<const uint8_t*>(s.h_stage) + off * sizeof(float), tokens * rows[i] * sizeof(float));
+        std::memcpy(ys[i], reinterpret_cast<const uint8_t*>(h_result) + off * sizeof(float), tokens * rows[i] * sizeof(float));
         off += tokens * rows[i];
     }
     s.stats.readback_us += us_since(t0);
@@ -708,6 +770,10 @@ void zen_cuda_shutdown(void) {
         s.d_gemm_ws = nullptr; s.d_gemm_ws_bytes = 0;
         if (s.h_stage) cudaFreeHost(s.h_stage);
         if (s.h_error) cudaFreeHost(s.h_error);
+        if (s.h_result) cudaFreeHost(s.h_result);
+        if (s.h_done) cudaFreeHost(const_cast<unsigned*>(s.h_done));
+        s.h_result = s.d_result = nullptr; s.h_result_bytes = 0;
+        s.h_done = nullptr; s.d_done = nullptr;
         for (int i = 0; i < 2; ++i) {
             if (s.bounce[i]) cudaFreeHost(s.bounce[i]);
             if (s.bounce_free[i]) cudaEventDestroy(s.bounce_free[i]);
