@@ -641,6 +641,145 @@ def run_lm_head(args) -> None:
     leave()
 
 
+# ---- workload decode: full greedy decode of a random-init Llama-3-8B-shaped Q8_0 model (fifth configuration) ----------
+def torch_q8_0_pack(w):
+    """fp32 [rows, K] on the GPU -> uint8 [rows, K/32*34] raw GGUF Q8_0 blocks, the packer of zeninfer_b200.blocks
+    (scale = amax/127 stored as fp16, codes from the unrounded scale, round half away from zero) on torch, because
+    packing eight billion weights with numpy would take minutes of box time.  Benchmark input preparation only."""
+    import torch
+    rows, k = w.shape
+    blk = w.view(rows, k // 32, 32)
+    scale = blk.abs().amax(dim=2) / 127.0
+    inv = torch.where(scale > 0, 1.0 / scale, torch.zeros_like(scale))
+    v = blk * inv[..., None]
+    t = torch.trunc(v)
+    q = (t + torch.where((v - t).abs() >= 0.5, torch.sign(v), torch.zeros_like(v))).clamp_(-127, 127).to(torch.int8)
+    out = torch.empty((rows, k // 32, 34), dtype=torch.uint8, device=w.device)
+    out[..., 0:2] = scale.to(torch.float16).view(torch.uint8).view(rows, k // 32, 2)
+    out[..., 2:] = q.view(torch.uint8)
+    return out.view(rows, -1)
+
+
+def run_decode(args) -> None:
+    """Config: 32 layers, d 4096, 32 query / 8 KV heads of 128, SwiGLU 14336, vocab 128256, eps 1e-5, theta 500000,
+    weights N(0, 0.02) seed 6, a prompt of 512 uniform-random ids, then greedy decode steps.  A step is one decoded
+    token: 290 launches replayed from two CUDA graphs.  The prompt is consumed token by token through the same step
+    and is not timed."""
+    import torch
+    from zeninfer_b200 import Backend
+    from zeninfer_b200.backend import ACT_INT8
+    from zeninfer_b200.llama import LlamaConfig, LlamaDecoder, tensor_plan
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1 or args.gpus != 1:
+        raise SystemExit("workload decode runs on one GPU in this build")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    be = Backend()
+    cfg = LlamaConfig()
+    prompt_len = 512
+    steps = args.steps if args.steps != 2000 else 125      # the default run: 3 warm-up + 125 timed = the 128 greedy steps
+    warm = max(3, args.warmup)
+
+    def tensors():
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(6)
+        for name, shape, is_matrix in tensor_plan(cfg):
+            if is_matrix:
+                w = torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) * 0.02
+                yield name, torch_q8_0_pack(w).cpu().numpy(), True
+            else:
+                yield name, (1.0 + 0.02 * torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)).cpu().numpy(), False
+
+    t0 = time.perf_counter()
+    dec = LlamaDecoder(be, cfg, tensors(), act_mode=ACT_INT8, max_positions=1024)
+    load_s = time.perf_counter() - t0
+    dec.capture()
+    prompt = np.random.default_rng(6).integers(0, cfg.vocab, size=prompt_len, dtype=np.int64)
+    ids = torch.from_numpy(prompt).to(dev)
+    stream = dec.stream
+    with ClockSampler(0) as clocks:
+        with torch.cuda.stream(stream):
+            dec.reset()
+            for i in range(prompt_len):
+                dec.token.copy_(ids[i:i + 1])
+                dec.step(want_token=(i + 1 == prompt_len))
+            for _ in range(warm):
+                dec.step(want_token=True)
+            stream.synchronize()
+            be.dev_check(stream.cuda_stream)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            clocks.mark_start()
+            e0.record(stream)
+            for _ in range(steps):
+                dec.step(want_token=True)
+            e1.record(stream)
+            stream.synchronize()
+            clocks.mark_end()
+        ms = e0.elapsed_time(e1)
+    be.dev_check(stream.cuda_stream)
+    last_pos = int(dec.pos.item())
+    assert last_pos == prompt_len + warm + steps, "position counter out of step"
+    assert bool(torch.isfinite(dec.logits).all().item()), "non-finite logits"
+    tok_s = steps / (ms * 1e-3)
+    layer_bytes = sum(tensor_bytes("Q8_0", r, c) for _, r, c in LAYER_TENSORS)
+    weight_bytes = cfg.layers * layer_bytes + tensor_bytes("Q8_0", cfg.vocab, cfg.embedding)
+    mean_pos = prompt_len + warm + steps / 2
+    kv_bytes = int(cfg.layers * 2 * cfg.kv_width * 4 * mean_pos)
+    algo = weight_bytes + kv_bytes
+    peak, peak_kind = peaks()
+    achieved = algo / (ms * 1e-3 / steps) / 1e9
+
+    # e2e: the public generate() call; every picked token is read back to the host as it is produced
+    stamps = []
+    e2e_new = 33
+    dec.generate(prompt.tolist(), e2e_new, on_token=lambda _t: stamps.append(time.perf_counter()))
+    e2e_tok_s = (e2e_new - 1) / (stamps[-1] - stamps[0])
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        import oracle
+        from zeninfer_b200 import blocks
+        os.environ.setdefault("ZEN_CPU_Q8_ACT", "1")
+        if oracle.reference_available():
+            zr = oracle.Reference()
+            rng = np.random.default_rng(6)
+            mats = {(r, c): np.ascontiguousarray(blocks.quantize_q8_0(rng.standard_normal((r, c), dtype=np.float32) * np.float32(0.02)))
+                    for r, c in {(r, c) for _, r, c in LAYER_TENSORS}}
+            xs = {c: rng.standard_normal(c, dtype=np.float32) for c in (4096, 14336)}
+            def one_layer():
+                for _, r, c in LAYER_TENSORS:
+                    zr.gemv(oracle.Q8_0, mats[(r, c)], xs[c], r, c, workers=0)
+            one_layer()
+            t0, n = time.perf_counter(), 0
+            while n == 0 or time.perf_counter() - t0 < args.cpu_budget:
+                one_layer(); n += 1
+            dt = time.perf_counter() - t0
+            per_token = dt / n * (cfg.layers + tensor_bytes("Q8_0", cfg.vocab, cfg.embedding) / layer_bytes)
+            cpu = {"value": 1.0 / per_token, "unit": "tokens/s", "cores": min(zr.pool_workers(), os.cpu_count() or 1), "kind": "reference",
+                   "sample": f"{n} passes over the seven Q8_0 projections of one layer in {dt:.1f} s (reference kernels, int8 activations, its own "
+                             f"worker policy), scaled to 32 layers + lm_head by bytes; attention, norms and sampling not included, so an upper bound "
+                             f"for the reference's decode rate on these cores"}
+
+    launches_per_step = 2 + 9 * cfg.layers + 1 + 1 + 3
+    print(json.dumps({
+        "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "greedy decode, random-init Llama-3-8B shape in Q8_0 (config 4): 32 layers, d 4096, 32/8 heads of 128, ffn 14336, "
+                               f"vocab 128256; prompt of {prompt_len} random ids (consumed token by token, untimed), then {warm} + {steps} decode steps",
+                   "activations": "int8 (bit-exact reference codes)", "l2": "inputs larger than L2: 8.5 GB of weights stream per token",
+                   "launch": f"two CUDA graphs per token, {launches_per_step} kernel launches", "weights": "torch.randn on the device, seed 6, N(0, 0.02)",
+                   "load_s": load_s},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
+                     "kernel": "whole token step (projections through gemv_q8_0_kernel<1,1>)", "launch_us": ms * 1e3 / steps,
+                     "algorithmic_bytes_per_launch": algo, "weight_bytes": weight_bytes, "kv_bytes": kv_bytes},
+        "cpu_baseline": cpu, "clocks": clocks.summary(),
+        "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8,
+                "api": "LlamaDecoder.generate: each picked token id is read back to the host, and fed to the next step from pinned host memory, "
+                       "as the reference's generate loop does", "steps": e2e_new - 1},
+        "gpu_launches": steps * launches_per_step,
+    }))
+    dec.close()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -667,6 +806,9 @@ def main() -> None:
         return
     if args.workload == "lm_head" and args.impl != "reference":
         run_lm_head(args)
+        return
+    if args.workload == "decode" and args.impl != "reference":
+        run_decode(args)
         return
     if args.impl == "reference":
         run_reference_arm(args)

@@ -236,6 +236,37 @@ typedef struct zen_cuda_pick_segment {
 } zen_cuda_pick_segment;
 int zen_cuda_dev_greedy_pick(const zen_cuda_pick_segment* segments, size_t count, size_t tokens, int64_t* d_pick, void* stream);
 
+/* ---- the decode-step operators between the projections (device pointers, stream-ordered, no synchronisation) -----
+ * With these a whole token step of a dense Llama-style layer stays in HBM on one stream.  They answer the reference's
+ * host loop in DenseTransformerRuntime::forward (src/adapters/dense_transformer_runtime.cpp:3670-4600) and the
+ * per-operator submissions its D3D12 backend offers for the same steps (include/zen/d3d12_backend.h:176 rms_norm,
+ * :192 rope_apply, :231 kv_cache_append, :247 attention_block, :370 silu_mul).  The position of the token in flight
+ * is read from device memory (d_pos), so a captured launch sequence can be replayed for every step. */
+
+/* d_out[columns] = row *d_token of a resident Q8_0 tensor, decoded to fp32 (the embedding fetch,
+ * src/adapters/dense_transformer_runtime.cpp:3692 over src/quant.cpp:410-416).  d_token: device int64. */
+int zen_cuda_dev_embed_q8_0(const zen_cuda_weights* w, const int64_t* d_token, float* d_out, void* stream);
+/* Per row of n floats: if d_delta is given, x += delta in place first (the residual add); then, if d_weight is given,
+ * y = x * inv * weight with inv = 1 / sqrt(float(sum x^2 / n) + eps), the sum taken in double
+ * (rms_norm, src/adapters/dense_transformer_runtime.cpp:117-125). */
+int zen_cuda_dev_rms_norm(float* d_x, const float* d_delta, const float* d_weight, float* d_y, size_t n, size_t rows, float eps, void* stream);
+/* Rotary embedding of q [heads][head_dim] and k [kv_heads][head_dim] in place with row *d_pos of the HOST-BUILT tables
+ * d_cos / d_sin [positions][pairs] (the table contract of rope_table, src/adapters/dense_transformer_runtime.cpp:264-276:
+ * the device computes no angle), pairs (x[2i], x[2i+1]) when adjacent != 0, else (x[i], x[i+pairs]); then k and v are
+ * appended to the layer's fp32 caches [max_positions][kv_heads * head_dim] at *d_pos. */
+int zen_cuda_dev_rope_kv_append(float* d_q, float* d_k, const float* d_v, const float* d_cos, const float* d_sin, const int* d_pos,
+                                size_t heads, size_t kv_heads, size_t head_dim, size_t pairs, int adjacent, float* d_k_cache, float* d_v_cache,
+                                size_t max_positions, void* stream);
+/* Grouped-query attention of one new token over positions [first, *d_pos] of the layer's caches, first = 0 or the
+ * sliding-window start; query head h reads kv head h / (heads / kv_heads)
+ * (src/adapters/dense_transformer_runtime.cpp:4284-4337).  scale 0 means 1 / sqrt(head_dim).  d_out [heads][head_dim]. */
+int zen_cuda_dev_attention(const float* d_q, const float* d_k_cache, const float* d_v_cache, const int* d_pos, float* d_out, size_t heads,
+                           size_t kv_heads, size_t head_dim, float scale, size_t window, size_t max_positions, void* stream);
+/* d_out = silu(gate) * up (silu_mul, src/adapters/dense_transformer_runtime.cpp:193-199). */
+int zen_cuda_dev_silu_mul(const float* d_gate, const float* d_up, float* d_out, size_t count, void* stream);
+/* *d_pos += delta, in stream order (a step's last launch). */
+int zen_cuda_dev_advance_position(int* d_pos, int delta, void* stream);
+
 /* Reads and clears the device-side error word the kernels set when a bounded wait gives up
  * (0 = none).  Synchronises `stream`. */
 int zen_cuda_dev_check(void* stream);

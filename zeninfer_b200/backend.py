@@ -38,6 +38,8 @@ ABI_SYMBOLS = (
     "zen_cuda_gather_region_bytes", "zen_cuda_ipc_alloc", "zen_cuda_ipc_open", "zen_cuda_ipc_close", "zen_cuda_ipc_free",
     "zen_cuda_gather_create", "zen_cuda_gather_destroy", "zen_cuda_dev_gemv_gather", "zen_cuda_dev_gather_fetch",
     "zen_cuda_dev_greedy_pick",
+    "zen_cuda_dev_embed_q8_0", "zen_cuda_dev_rms_norm", "zen_cuda_dev_rope_kv_append", "zen_cuda_dev_attention", "zen_cuda_dev_silu_mul",
+    "zen_cuda_dev_advance_position",
 )
 
 
@@ -125,6 +127,12 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_dev_gemv_gather.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), sz, vp, sz, i, vp]
     lib.zen_cuda_dev_gather_fetch.argtypes = [vp, vp, vp]
     lib.zen_cuda_dev_greedy_pick.argtypes = [C.POINTER(PickSegment), sz, sz, vp, vp]
+    lib.zen_cuda_dev_embed_q8_0.argtypes = [vp, vp, vp, vp]
+    lib.zen_cuda_dev_rms_norm.argtypes = [vp, vp, vp, vp, sz, sz, C.c_float, vp]
+    lib.zen_cuda_dev_rope_kv_append.argtypes = [vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, i, vp, vp, sz, vp]
+    lib.zen_cuda_dev_attention.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz, C.c_float, sz, sz, vp]
+    lib.zen_cuda_dev_silu_mul.argtypes = [vp, vp, vp, sz, vp]
+    lib.zen_cuda_dev_advance_position.argtypes = [vp, i, vp]
     return lib
 
 
@@ -327,6 +335,34 @@ class Backend:
         segs = (PickSegment * n)(*[PickSegment(b, ln, first, stride, 0) for b, ln, first, stride in segments])
         if not self.lib.zen_cuda_dev_greedy_pick(segs, n, tokens, d_pick, stream):
             self._fail("dev_greedy_pick")
+
+    # ---- decode-step operators between the projections ----
+    def dev_embed_q8_0(self, handle: int, d_token: int, d_out: int, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_embed_q8_0(handle, d_token, d_out, stream):
+            self._fail("dev_embed_q8_0")
+
+    def dev_rms_norm(self, d_x: int, d_delta: int | None, d_weight: int | None, d_y: int | None, n: int, rows: int, eps: float, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_rms_norm(d_x, d_delta, d_weight, d_y, n, rows, eps, stream):
+            self._fail("dev_rms_norm")
+
+    def dev_rope_kv_append(self, d_q: int, d_k: int, d_v: int, d_cos: int, d_sin: int, d_pos: int, heads: int, kv_heads: int, head_dim: int,
+                           pairs: int, adjacent: bool, d_k_cache: int, d_v_cache: int, max_positions: int, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_rope_kv_append(d_q, d_k, d_v, d_cos, d_sin, d_pos, heads, kv_heads, head_dim, pairs, int(adjacent), d_k_cache,
+                                                    d_v_cache, max_positions, stream):
+            self._fail("dev_rope_kv_append")
+
+    def dev_attention(self, d_q: int, d_k_cache: int, d_v_cache: int, d_pos: int, d_out: int, heads: int, kv_heads: int, head_dim: int,
+                      max_positions: int, scale: float = 0.0, window: int = 0, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_attention(d_q, d_k_cache, d_v_cache, d_pos, d_out, heads, kv_heads, head_dim, scale, window, max_positions, stream):
+            self._fail("dev_attention")
+
+    def dev_silu_mul(self, d_gate: int, d_up: int, d_out: int, count: int, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_silu_mul(d_gate, d_up, d_out, count, stream):
+            self._fail("dev_silu_mul")
+
+    def dev_advance_position(self, d_pos: int, delta: int = 1, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_advance_position(d_pos, delta, stream):
+            self._fail("dev_advance_position")
 
     def dev_check(self, stream: int = 0) -> None:
         code = self.lib.zen_cuda_dev_check(stream)

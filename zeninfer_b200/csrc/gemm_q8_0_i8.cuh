@@ -49,6 +49,7 @@ struct GemmParams {
     uint32_t rows, tokens, nb, nbp;
     uint32_t n_tile;                   // tokens per tile: 32, 64, 128 or 256
     uint32_t m_tiles, n_tiles;
+    uint32_t stream_k;                 // 1: CTAs share the (tile, K tile) units evenly (see GemmWork); 0: whole tiles in turn
     int* error_word;
 };
 
@@ -71,107 +72,95 @@ __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-    uint64_t r;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-// Two int32 block sums -> two exact floats without the (quarter-rate) conversion unit: |v| < 2^22, so
-// adding v to the bit pattern of 1.5 * 2^23 yields the float 1.5 * 2^23 + v exactly, and subtracting
-// 1.5 * 2^23 is exact as well.  One integer add per value plus one packed fp32 add per pair.
-__device__ __forceinline__ uint64_t ints_to_float2(uint32_t v0, uint32_t v1) {
-    const uint64_t biased = pack2(__uint_as_float(v0 + 0x4B400000u), __uint_as_float(v1 + 0x4B400000u));
-    return add2(biased, pack2(-12582912.0f, -12582912.0f));
-}
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t r;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
     return r;
 }
 
-// acc[c/2] += float(v[c], v[c+1]) * (sw * sx[c], sw * sx[c+1]) for 32 token columns.
-// ZK_GEMM_VARIANT selects how: 0 = convert unit + packed fp32, 1 = magic-number convert + packed fp32,
-// 2 = convert unit + scalar fp32, 3 = magic-number convert + scalar fp32.
-#ifndef ZK_GEMM_VARIANT
-#define ZK_GEMM_VARIANT 0
-#endif
-__device__ __forceinline__ float int_to_float(uint32_t v) {
-#if ZK_GEMM_VARIANT == 1 || ZK_GEMM_VARIANT == 3
-    return __uint_as_float(v + 0x4B400000u) - 12582912.0f;
-#else
-    return static_cast<float>(static_cast<int>(v));
-#endif
+// acc[c/2] += float(v[c], v[c+1]) * (sw * sx[c], sw * sx[c+1]) for 32 token columns: one conversion per sum (exact:
+// |sum| < 2^24), one packed multiply and one packed multiply-add per pair of token columns.
+__device__ __forceinline__ float int_to_float(uint32_t v) { return static_cast<float>(static_cast<int>(v)); }
+// Four consecutive activation scales from the stage, by shared-memory address: the same address in every lane (a
+// broadcast), and a 32-bit shared-space address with an immediate offset costs no address arithmetic, where a generic
+// pointer costs a 64-bit add per load and a slower load.
+#define ZK_LDS128(v, addr, byte_off) \
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4+" #byte_off "];" : "=r"((v).x), "=r"((v).y), "=r"((v).z), "=r"((v).w) : "r"(addr))
+
+__device__ __forceinline__ void gemm_fma4(const uint32_t* v, uint64_t sw2, const uint4& s4, uint64_t* acc) {
+    uint64_t s01, s23;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(s01) : "r"(s4.x), "r"(s4.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(s23) : "r"(s4.z), "r"(s4.w));
+    const uint64_t f01 = pack2(int_to_float(v[0]), int_to_float(v[1]));
+    const uint64_t f23 = pack2(int_to_float(v[2]), int_to_float(v[3]));
+    acc[0] = fma2(f01, mul2(s01, sw2), acc[0]);
+    acc[1] = fma2(f23, mul2(s23, sw2), acc[1]);
 }
-__device__ __forceinline__ void gemm_fma32(const uint32_t (&v)[32], uint64_t sw2, const float* __restrict__ sx, uint64_t* __restrict__ acc) {
-#if ZK_GEMM_VARIANT >= 2
-    float sw, sw_hi;
-    unpack2(sw2, sw, sw_hi);
-#pragma unroll
-    for (int c = 0; c < 32; c += 4) {
-        const float4 s4 = *reinterpret_cast<const float4*>(sx + c);
-        float a0, a1, a2, a3;
-        unpack2(acc[c / 2], a0, a1);
-        unpack2(acc[c / 2 + 1], a2, a3);
-        a0 = fmaf(int_to_float(v[c + 0]), sw * s4.x, a0);
-        a1 = fmaf(int_to_float(v[c + 1]), sw * s4.y, a1);
-        a2 = fmaf(int_to_float(v[c + 2]), sw * s4.z, a2);
-        a3 = fmaf(int_to_float(v[c + 3]), sw * s4.w, a3);
-        acc[c / 2] = pack2(a0, a1);
-        acc[c / 2 + 1] = pack2(a2, a3);
-    }
-#else
-#pragma unroll
-    for (int c = 0; c < 32; c += 4) {
-        const ulonglong2 s4 = *reinterpret_cast<const ulonglong2*>(sx + c);  // same address in every lane: a broadcast
-#if ZK_GEMM_VARIANT == 1
-        const uint64_t f01 = ints_to_float2(v[c + 0], v[c + 1]);
-        const uint64_t f23 = ints_to_float2(v[c + 2], v[c + 3]);
-#else
-        const uint64_t f01 = pack2(int_to_float(v[c + 0]), int_to_float(v[c + 1]));
-        const uint64_t f23 = pack2(int_to_float(v[c + 2]), int_to_float(v[c + 3]));
-#endif
-        acc[c / 2] = fma2(f01, mul2(s4.x, sw2), acc[c / 2]);
-        acc[c / 2 + 1] = fma2(f23, mul2(s4.y, sw2), acc[c / 2 + 1]);
-    }
-#endif
+__device__ __forceinline__ void gemm_fma32(const uint32_t (&v)[32], uint64_t sw2, uint32_t sx_addr, uint64_t* __restrict__ acc) {
+    uint4 s;
+    ZK_LDS128(s, sx_addr, 0);   gemm_fma4(v + 0, sw2, s, acc + 0);
+    ZK_LDS128(s, sx_addr, 16);  gemm_fma4(v + 4, sw2, s, acc + 2);
+    ZK_LDS128(s, sx_addr, 32);  gemm_fma4(v + 8, sw2, s, acc + 4);
+    ZK_LDS128(s, sx_addr, 48);  gemm_fma4(v + 12, sw2, s, acc + 6);
+    ZK_LDS128(s, sx_addr, 64);  gemm_fma4(v + 16, sw2, s, acc + 8);
+    ZK_LDS128(s, sx_addr, 80);  gemm_fma4(v + 20, sw2, s, acc + 10);
+    ZK_LDS128(s, sx_addr, 96);  gemm_fma4(v + 24, sw2, s, acc + 12);
+    ZK_LDS128(s, sx_addr, 112); gemm_fma4(v + 28, sw2, s, acc + 14);
 }
 
-// One block's int32 sums for this warp's kNHalf token columns: TMEM -> registers 32 columns at a time (the next
-// chunk is in flight while the current one is folded into the accumulators), then acc += float(sum) * (sw * sx).
-// The TMEM buffer is handed back to the MMA warp as soon as the last chunk has been read.
-template <int kNHalf>  // token columns per epilogue warp
-__device__ __forceinline__ void gemm_epilogue_block(uint32_t taddr, float sw_scalar, const float* __restrict__ sx, uint64_t (&acc)[kNHalf / 2],
-                                                    uint64_t* tmem_empty_bar, int lane) {
-    const uint64_t sw = pack2(sw_scalar, sw_scalar);
-    if constexpr (kNHalf <= 64) {
-        uint32_t va[32], vb[32];
-        tmem_ld_32x32(taddr, va);
-        if (kNHalf > 32) tmem_ld_32x32(taddr + 32, vb);
-        tmem_ld_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tmem_empty_bar);
-        gemm_fma32(va, sw, sx, acc);
-        if (kNHalf > 32) gemm_fma32(vb, sw, sx + 32, acc + 16);
-    } else {
-        // 128 accumulators leave room for one 32-column staging buffer only
-        uint32_t v[32];
-#pragma unroll
-        for (int c = 0; c < kNHalf; c += 32) {
-            tmem_ld_32x32(taddr + c, v);
-            tmem_ld_wait();
-            if (c + 32 >= kNHalf) { tc_fence_before_sync(); __syncwarp(); if (lane == 0) mbar_arrive(tmem_empty_bar); }
-            gemm_fma32(v, sw, sx + c, acc + c / 2);
+// The work of one CTA.  With `stream_k` the (tile, K tile) units of the whole product, tile-major, are cut into
+// gridDim.x equal contiguous ranges, so every SM gets the same number of K tiles even when the tile count is not a
+// multiple of the SM count (448 tiles on 148 SMs would otherwise take four rounds for 3.03 rounds of work).  A
+// range is at least one tile long, so a tile is shared by at most two CTAs; both add their partial sums to an
+// output that gemm_zero_split_tiles_kernel cleared, and the sum of two floats does not depend on their order.
+// Without it, CTAs take whole tiles in turn.
+struct GemmWork {
+    uint32_t u, u_end, ktiles, stride;   // stride != 0: whole tiles, `u` counts tiles
+    __device__ GemmWork(const GemmParams& p, uint32_t ktiles_) : ktiles(ktiles_) {
+        const uint32_t tiles = p.m_tiles * p.n_tiles;
+        if (p.stream_k) {
+            const uint64_t total = static_cast<uint64_t>(tiles) * ktiles;
+            u = static_cast<uint32_t>(total * blockIdx.x / gridDim.x);
+            u_end = static_cast<uint32_t>(total * (blockIdx.x + 1) / gridDim.x);
+            stride = 0;
+        } else {
+            u = blockIdx.x; u_end = tiles; stride = gridDim.x;
         }
     }
+    __device__ bool next(uint32_t& tile, uint32_t& kt0, uint32_t& kt1) {
+        if (u >= u_end) return false;
+        if (stride) { tile = u; kt0 = 0; kt1 = ktiles; u += stride; return true; }
+        tile = u / ktiles; kt0 = u % ktiles;
+        kt1 = min(ktiles, kt0 + (u_end - u));
+        u += kt1 - kt0;
+        return true;
+    }
+};
+
+// Clears the output tiles that two CTAs of a stream-K launch share (launched right before it, same grid).
+__global__ void gemm_zero_split_tiles_kernel(float* __restrict__ out, uint32_t rows, uint32_t tokens, uint32_t m_tiles, uint32_t n_tiles,
+                                             uint32_t n_tile, uint32_t ktiles) {
+    if (blockIdx.x == 0) return;
+    const uint64_t total = static_cast<uint64_t>(m_tiles) * n_tiles * ktiles;
+    const uint32_t cut = static_cast<uint32_t>(total * blockIdx.x / gridDim.x);
+    if (cut % ktiles == 0) return;   // the boundary falls between two tiles
+    const uint32_t tile = cut / ktiles, mt = tile % m_tiles, nt = tile / m_tiles;
+    for (uint32_t i = threadIdx.x; i < n_tile * kGemmM; i += blockDim.x) {
+        const uint32_t t = nt * n_tile + i / kGemmM, r = mt * kGemmM + i % kGemmM;
+        if (t < tokens && r < rows) out[static_cast<size_t>(t) * rows + r] = 0.0f;
+    }
 }
 
+// Eighteen warps put five on one of the SM's four register files (16384 registers each), so 96 registers per thread is
+// the ceiling: 5 x 32 x 96 = 15360.
 template <int kNTile>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __grid_constant__ GemmParams p) {
     constexpr int kNHalf = kNTile / kGemmSplit;     // token columns per epilogue warp
-    constexpr uint32_t kBufs = 512 / kNTile > 4 ? 4 : 512 / kNTile;  // TMEM accumulator buffers
+    static_assert(kNHalf == 32, "an epilogue warp takes 32 token columns");
+    constexpr uint32_t kPairs = 2;                   // TMEM accumulator buffers come in pairs: one hand-off per two blocks
     constexpr uint32_t kStageBytes = kGemmM * kGemmKTile + kNTile * kGemmKTile + kGemmBlocksPerTile * kNTile * 4;
-    constexpr uint32_t kTmemCols = kBufs * kNTile;  // 512: a power of two
+    constexpr uint32_t kTmemCols = 2 * kPairs * kNTile;  // 512: a power of two
+    static_assert(kTmemCols == 512, "four accumulator buffers of 128 columns");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGemmStages * kStageBytes);
@@ -183,14 +172,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t ktiles = (p.nb + kGemmBlocksPerTile - 1) / kGemmBlocksPerTile;
-    const uint32_t total_tiles = p.m_tiles * p.n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1 + kGemmEpiWarps);
         }
-        for (int b = 0; b < static_cast<int>(kBufs); ++b) {
+        for (int b = 0; b < static_cast<int>(kPairs); ++b) {
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], kGemmEpiWarps);
         }
@@ -209,11 +197,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t it = 0, tile, kt0, kt1;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            GemmWork work(p, ktiles);
+            while (ok && work.next(tile, kt0, kt1)) {
                 const uint32_t mt = tile % p.m_tiles, nt = tile / p.m_tiles;
-                for (uint32_t kt = 0; kt < ktiles; ++kt, ++it) {
+                for (uint32_t kt = kt0; kt < kt1; ++kt, ++it) {
                     const uint32_t stage = it % kGemmStages;
                     if (it >= kGemmStages && !mbar_wait(&empty[stage], ((it / kGemmStages) - 1) & 1)) {
                         *abort_word = 1; atomicExch(p.error_word, kErrEmptyWaitTimeout); ok = false;
@@ -233,10 +222,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_i8(kGemmM, kNTile);
-            uint32_t it = 0, blk = 0;
+            uint32_t it = 0, pair = 0, tile, kt0, kt1;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                for (uint32_t kt = 0; kt < ktiles && ok; ++kt, ++it) {
+            GemmWork work(p, ktiles);
+            while (ok && work.next(tile, kt0, kt1)) {
+                for (uint32_t kt = kt0; kt < kt1 && ok; ++kt, ++it) {
                     const uint32_t stage = it % kGemmStages;
                     if (*abort_word || !mbar_wait(&full[stage], (it / kGemmStages) & 1)) {
                         if (!*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrFullWaitTimeout); }
@@ -247,18 +237,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                     const uint32_t a_addr = smem_u32(smem + stage * kStageBytes);
                     const uint64_t a_desc = umma_desc_k_sw128(a_addr), b_desc = umma_desc_k_sw128(a_addr + kGemmM * kGemmKTile);
                     const uint32_t nblk = min(static_cast<uint32_t>(kGemmBlocksPerTile), p.nb - kt * kGemmBlocksPerTile);
-                    for (uint32_t j = 0; j < nblk; ++j, ++blk) {
-                        const uint32_t buf = blk % kBufs;
-                        if (blk >= kBufs) {
-                            if (!mbar_wait(&tmem_empty[buf], ((blk / kBufs) - 1) & 1)) {
+                    for (uint32_t j0 = 0; j0 < nblk; j0 += 2, ++pair) {
+                        const uint32_t pr = pair % kPairs;
+                        if (pair >= kPairs) {
+                            if (!mbar_wait(&tmem_empty[pr], ((pair / kPairs) - 1) & 1)) {
                                 *abort_word = 1; atomicExch(p.error_word, kErrTmemWaitTimeout); ok = false;
                                 break;
                             }
                             tc_fence_after_sync();
                         }
-                        // one Q8_0 block: 32 bytes of K = two 16-byte units further into the swizzle atom
-                        tc_mma_i8(tmem_base + buf * kNTile, a_desc + 2 * j, b_desc + 2 * j, idesc, 0u);
-                        tc_commit(&tmem_full[buf]);
+                        // one Q8_0 block per instruction: 32 bytes of K = two 16-byte units further into the swizzle atom
+                        tc_mma_i8(tmem_base + (2 * pr) * kNTile, a_desc + 2 * j0, b_desc + 2 * j0, idesc, 0u);
+                        if (j0 + 1 < nblk) tc_mma_i8(tmem_base + (2 * pr + 1) * kNTile, a_desc + 2 * (j0 + 1), b_desc + 2 * (j0 + 1), idesc, 0u);
+                        tc_commit(&tmem_full[pr]);
                     }
                     if (ok) tc_commit(&empty[stage]);  // the stage is free once its MMAs have read it
                 }
@@ -269,42 +260,57 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
         const int e = warp - 2;
         const uint32_t quad = static_cast<uint32_t>(warp) & 3;   // the TMEM lanes a warp may touch: 32 * (warp id % 4)
         const uint32_t half = static_cast<uint32_t>(e) >> 2;      // which share of the token columns this warp takes
-        const uint32_t lane_addr = (quad * 32) << 16;
-        uint32_t it = 0, blk = 0;
+        const uint32_t taddr0 = tmem_base + ((quad * 32) << 16) + half * kNHalf;
+        uint32_t it = 0, pair = 0, tile, kt0, kt1;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        GemmWork work(p, ktiles);
+        while (ok && work.next(tile, kt0, kt1)) {
             const uint32_t mt = tile % p.m_tiles, nt = tile / p.m_tiles;
             const uint32_t r = mt * kGemmM + quad * 32 + lane;
             const bool row_ok = r < p.rows;
             uint64_t acc[kNHalf / 2];  // packed pairs of fp32 accumulators, token columns (2i, 2i+1)
 #pragma unroll
             for (int c = 0; c < kNHalf / 2; ++c) acc[c] = 0ull;
-            for (uint32_t kt = 0; kt < ktiles && ok; ++kt, ++it) {
+            // the four weight scales of row r per K tile (8-byte aligned: nbp is a multiple of 8), fetched one K tile ahead
+            const uint2* sw_row = reinterpret_cast<const uint2*>(p.w_scales + static_cast<size_t>(row_ok ? r : 0) * p.nbp);
+            uint2 sw_next = __ldg(sw_row + kt0);
+            for (uint32_t kt = kt0; kt < kt1 && ok; ++kt, ++it) {
                 const uint32_t stage = it % kGemmStages;
-                // this tile's four weight scales of row r (8-byte aligned: nbp is a multiple of 8)
-                uint2 sw4 = make_uint2(0, 0);
-                if (row_ok) sw4 = __ldg(reinterpret_cast<const uint2*>(p.w_scales + static_cast<size_t>(r) * p.nbp + kt * kGemmBlocksPerTile));
+                const uint2 sw4 = sw_next;
+                if (kt + 1 < kt1) sw_next = __ldg(sw_row + kt + 1);
                 if (*abort_word || !mbar_wait(&full[stage], (it / kGemmStages) & 1)) {
                     if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrFullWaitTimeout); }
                     ok = false;
                     break;
                 }
-                const float* sxs = reinterpret_cast<const float*>(smem + stage * kStageBytes + kGemmM * kGemmKTile + kNTile * kGemmKTile);
+                const uint32_t sxs = smem_u32(smem + stage * kStageBytes + kGemmM * kGemmKTile + kNTile * kGemmKTile) + half * kNHalf * 4;
                 const __half2 h01 = *reinterpret_cast<const __half2*>(&sw4.x), h23 = *reinterpret_cast<const __half2*>(&sw4.y);
                 const float swf[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
                 const uint32_t nblk = min(static_cast<uint32_t>(kGemmBlocksPerTile), p.nb - kt * kGemmBlocksPerTile);
 #pragma unroll
-                for (uint32_t j = 0; j < kGemmBlocksPerTile; ++j) {
-                    if (j < nblk && ok) {
-                        const uint32_t buf = blk % kBufs;
-                        if (!mbar_wait(&tmem_full[buf], (blk / kBufs) & 1)) {
+                for (uint32_t j0 = 0; j0 < kGemmBlocksPerTile; j0 += 2) {
+                    if (j0 < nblk && ok) {
+                        const uint32_t pr = pair % kPairs;
+                        if (!mbar_wait(&tmem_full[pr], (pair / kPairs) & 1)) {
                             if (lane == 0) { *abort_word = 1; atomicExch(p.error_word, kErrTmemWaitTimeout); }
                             ok = false;
                         } else {
                             tc_fence_after_sync();
-                            gemm_epilogue_block<kNHalf>(tmem_base + lane_addr + buf * kNTile + half * kNHalf, swf[j],
-                                                        sxs + j * kNTile + half * kNHalf, acc, &tmem_empty[buf], lane);
-                            ++blk;
+                            const bool two = j0 + 1 < nblk;
+                            uint32_t v[32];
+                            tmem_ld_32x32(taddr0 + (2 * pr) * kNTile, v);
+                            tmem_ld_wait();
+                            if (!two) { tc_fence_before_sync(); __syncwarp(); if (lane == 0) mbar_arrive(&tmem_empty[pr]); }
+                            gemm_fma32(v, pack2(swf[j0], swf[j0]), sxs + j0 * kNTile * 4, acc);
+                            if (two) {
+                                tmem_ld_32x32(taddr0 + (2 * pr + 1) * kNTile, v);
+                                tmem_ld_wait();
+                                tc_fence_before_sync();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&tmem_empty[pr]);   // both buffers of the pair have been read
+                                gemm_fma32(v, pack2(swf[j0 + 1], swf[j0 + 1]), sxs + (j0 + 1) * kNTile * 4, acc);
+                            }
+                            ++pair;
                         }
                     }
                 }
@@ -314,13 +320,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
             }
             if (!ok) break;
             if (row_ok) {
+                const bool whole = kt0 == 0 && kt1 == ktiles;   // otherwise another CTA holds the rest of this tile's K range
 #pragma unroll
                 for (int c = 0; c < kNHalf; c += 2) {
                     const uint32_t t = nt * kNTile + half * kNHalf + c;
                     float lo, hi;
                     unpack2(acc[c / 2], lo, hi);
-                    if (t < p.tokens) p.out[static_cast<size_t>(t) * p.rows + r] = lo;
-                    if (t + 1 < p.tokens) p.out[static_cast<size_t>(t + 1) * p.rows + r] = hi;
+                    float* o = p.out + static_cast<size_t>(t) * p.rows + r;
+                    if (whole) {
+                        if (t < p.tokens) o[0] = lo;
+                        if (t + 1 < p.tokens) o[p.rows] = hi;
+                    } else {
+                        if (t < p.tokens) atomicAdd(o, lo);
+                        if (t + 1 < p.tokens) atomicAdd(o + p.rows, hi);
+                    }
                 }
             }
         }

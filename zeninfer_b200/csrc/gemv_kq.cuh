@@ -333,28 +333,29 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
         uint4 xa = make_uint4(0, 0, 0, 0), xb = xa, xc = xa, xd4 = xa;   // Q4_0: digit 1 lo/hi halves, digit 2 lo/hi; Q6_K: digit 1, digit 2
         float xs = 0.0f;     // activation scale of the lane's block, with the digit weight folded in
         int bias = 0;        // minus (zero point x sum of the lane's activation codes), the dp4a chain's starting value
-        bool live = false;
+        // A lane whose block lies past the end of the row reads the segment's first block instead (valid bytes, so a
+        // finite scale) with zero activations and a zero scale: its terms are exactly zero and need no select.
+        uint32_t wofs = 0;   // byte offset of the lane's weights within a row of plane 0 (Q4_0) / super-block index (Q6_K)
         auto load_x = [&](uint32_t seg) {
+            const uint4 zero = make_uint4(0, 0, 0, 0);
             if (kFormat == 2) {
                 const uint32_t b = seg * (kKqSegElems / 32) + kslice * 32 + lane;
-                live = b * 32 < p.K;
-                if (live) {
-                    const uint4* x1 = reinterpret_cast<const uint4*>(xd + b * 32);
-                    const uint4* x2 = reinterpret_cast<const uint4*>(xd + kpad + b * 32);
-                    xa = x1[0]; xb = x1[1]; xc = x2[0]; xd4 = x2[1];
-                    xs = xscale[b] * (1.0f / 16.0f);   // high nibbles enter sixteen-fold, so every sum is sixteen-fold
-                    bias = -128 * xsum[b];             // -8 * sum, sixteen-fold
-                }
+                const bool live = b * 32 < p.K;
+                const uint4* x1 = reinterpret_cast<const uint4*>(xd + b * 32);
+                const uint4* x2 = reinterpret_cast<const uint4*>(xd + kpad + b * 32);
+                xa = live ? x1[0] : zero; xb = live ? x1[1] : zero; xc = live ? x2[0] : zero; xd4 = live ? x2[1] : zero;
+                xs = live ? xscale[b] * (1.0f / 16.0f) : 0.0f;   // high nibbles enter sixteen-fold, so every sum is sixteen-fold
+                bias = live ? -128 * xsum[b] : 0;                 // -8 * sum, sixteen-fold
+                wofs = live ? kslice * 32 + lane : 0u;
             } else {
                 const uint32_t e0 = seg * kKqSegElems + sbl * 256 + qhalf * 128 + group * 32 + six * 16;
-                live = e0 < p.K;
-                if (live) {
-                    xa = *reinterpret_cast<const uint4*>(xd + e0);
-                    xc = *reinterpret_cast<const uint4*>(xd + kpad + e0);
-                    xs = xscale[e0 / 32];
-                    const uint4 ones = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
-                    bias = -32 * (dot16(ones, xa) * 256 + dot16(ones, xc));
-                }
+                const bool live = e0 < p.K;
+                xa = live ? *reinterpret_cast<const uint4*>(xd + e0) : zero;
+                xc = live ? *reinterpret_cast<const uint4*>(xd + kpad + e0) : zero;
+                xs = live ? xscale[e0 / 32] : 0.0f;
+                const uint4 ones = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+                bias = -32 * (dot16(ones, xa) * 256 + dot16(ones, xc));
+                wofs = live ? sbl : 0u;
             }
         };
         if (p.nseg == 1) load_x(0);
@@ -382,51 +383,56 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                 }
                 if (p.nseg > 1) load_x(s);
                 const uint8_t* st = ring + stage * kStageBytes;
+                const uint8_t* w0;   // the lane's weights in row 0 of the stage
+                const uint8_t* w1;
+                const int8_t* sc = nullptr;
+                const __half* dd = nullptr;
                 if (kFormat == 2) {
-                    const uint32_t bl = kslice * 32 + lane;
-#pragma unroll
-                    for (int r = 0; r < kR; ++r) {
-                        const uint32_t row = rowbase + r;
-                        if (row < g.nrows) {
-                            const uint4 w = *reinterpret_cast<const uint4*>(st + kq_plane_offset<kFormat>(0) + row * F::seg_bytes(0) + bl * 16);
-                            const float dw = __half2float(*reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(1) + row * F::seg_bytes(1) + bl * 2));
-                            // low nibbles are elements 0..15, high nibbles elements 16..31 (src/quant.cpp:391-397); the high
-                            // nibbles stay in place (value x 16, an unsigned byte), which saves the shifts
-                            const uint32_t m = 0x0F0F0F0Fu;
-                            int a = dp4a_us(w.x & m, xa.x, 0), b = dp4a_us(w.x & ~m, xb.x, 0), c = dp4a_us(w.x & m, xc.x, 0), d = dp4a_us(w.x & ~m, xd4.x, bias);
-                            a = dp4a_us(w.y & m, xa.y, a); b = dp4a_us(w.y & ~m, xb.y, b); c = dp4a_us(w.y & m, xc.y, c); d = dp4a_us(w.y & ~m, xd4.y, d);
-                            a = dp4a_us(w.z & m, xa.z, a); b = dp4a_us(w.z & ~m, xb.z, b); c = dp4a_us(w.z & m, xc.z, c); d = dp4a_us(w.z & ~m, xd4.z, d);
-                            a = dp4a_us(w.w & m, xa.w, a); b = dp4a_us(w.w & ~m, xb.w, b); c = dp4a_us(w.w & m, xc.w, c); d = dp4a_us(w.w & ~m, xd4.w, d);
-                            // 16 * (256 * (lo.q1 + hi.q1) + (lo.q2 + hi.q2) - 8 * sum) = 4096 a + 256 b + 16 c + d
-                            const int isum = ((a * 16 + b) * 16 + c) * 16 + d;
-                            const float term = (dw * xs) * static_cast<float>(isum);
-                            acc[r] += live ? term : 0.0f;   // a lane past the row holds stale scale bits: select, do not multiply
-                        }
-                    }
+                    w0 = st + kq_plane_offset<kFormat>(0) + rowbase * F::seg_bytes(0) + wofs * 16;   // nibbles
+                    w1 = st + kq_plane_offset<kFormat>(1) + rowbase * F::seg_bytes(1) + wofs * 2;    // scale
                 } else {
-                    const uint8_t* ql = st + kq_plane_offset<kFormat>(0) + sbl * 128 + qhalf * 64 + (group & 1) * 32 + six * 16;
-                    const uint8_t* qh = st + kq_plane_offset<kFormat>(1) + sbl * 64 + qhalf * 32 + six * 16;
-                    const int8_t* sc = reinterpret_cast<const int8_t*>(st + kq_plane_offset<kFormat>(2)) + sbl * 16 + sg;
-                    const __half* dd = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(3)) + sbl;
-#pragma unroll
-                    for (int r = 0; r < kR; ++r) {
-                        if (static_cast<uint32_t>(r) < g.nrows) {
-                            const uint4 l4 = *reinterpret_cast<const uint4*>(ql + r * F::seg_bytes(0));
-                            const uint4 h4 = *reinterpret_cast<const uint4*>(qh + r * F::seg_bytes(1));
-                            // codes stay 0..63; the zero point 32 is in `bias`
-                            const uint32_t q0 = ((l4.x >> shift4) & 0x0F0F0F0Fu) | (((h4.x >> shift2) & 0x03030303u) << 4);
-                            const uint32_t q1 = ((l4.y >> shift4) & 0x0F0F0F0Fu) | (((h4.y >> shift2) & 0x03030303u) << 4);
-                            const uint32_t q2 = ((l4.z >> shift4) & 0x0F0F0F0Fu) | (((h4.z >> shift2) & 0x03030303u) << 4);
-                            const uint32_t q3 = ((l4.w >> shift4) & 0x0F0F0F0Fu) | (((h4.w >> shift2) & 0x03030303u) << 4);
-                            int a = dp4a_us(q0, xa.x, 0), c = dp4a_us(q0, xc.x, bias);
-                            a = dp4a_us(q1, xa.y, a); c = dp4a_us(q1, xc.y, c);
-                            a = dp4a_us(q2, xa.z, a); c = dp4a_us(q2, xc.z, c);
-                            a = dp4a_us(q3, xa.w, a); c = dp4a_us(q3, xc.w, c);
-                            const float dsc = __half2float(dd[r * (F::seg_bytes(3) / 2)]) * static_cast<float>(sc[r * F::seg_bytes(2)]);  // (d * scale), the reference's order
-                            const float term = (dsc * xs) * static_cast<float>(a * 256 + c);
-                            acc[r] += live ? term : 0.0f;
-                        }
+                    w0 = st + kq_plane_offset<kFormat>(0) + wofs * 128 + qhalf * 64 + (group & 1) * 32 + six * 16;   // ql
+                    w1 = st + kq_plane_offset<kFormat>(1) + wofs * 64 + qhalf * 32 + six * 16;                       // qh
+                    sc = reinterpret_cast<const int8_t*>(st + kq_plane_offset<kFormat>(2)) + wofs * 16 + sg;
+                    dd = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(3)) + wofs;
+                }
+                auto row_body = [&](int r) {
+                    if (kFormat == 2) {
+                        const uint4 w = *reinterpret_cast<const uint4*>(w0 + r * F::seg_bytes(0));
+                        const float dw = __half2float(*reinterpret_cast<const __half*>(w1 + r * F::seg_bytes(1)));
+                        // low nibbles are elements 0..15, high nibbles elements 16..31 (src/quant.cpp:391-397); the high
+                        // nibbles stay in place (value x 16, an unsigned byte), which saves the shifts
+                        const uint32_t m = 0x0F0F0F0Fu;
+                        int a = dp4a_us(w.x & m, xa.x, 0), b = dp4a_us(w.x & ~m, xb.x, 0), c = dp4a_us(w.x & m, xc.x, 0), d = dp4a_us(w.x & ~m, xd4.x, bias);
+                        a = dp4a_us(w.y & m, xa.y, a); b = dp4a_us(w.y & ~m, xb.y, b); c = dp4a_us(w.y & m, xc.y, c); d = dp4a_us(w.y & ~m, xd4.y, d);
+                        a = dp4a_us(w.z & m, xa.z, a); b = dp4a_us(w.z & ~m, xb.z, b); c = dp4a_us(w.z & m, xc.z, c); d = dp4a_us(w.z & ~m, xd4.z, d);
+                        a = dp4a_us(w.w & m, xa.w, a); b = dp4a_us(w.w & ~m, xb.w, b); c = dp4a_us(w.w & m, xc.w, c); d = dp4a_us(w.w & ~m, xd4.w, d);
+                        // 16 * (256 * (lo.q1 + hi.q1) + (lo.q2 + hi.q2) - 8 * sum) = 4096 a + 256 b + 16 c + d
+                        const int isum = ((a * 16 + b) * 16 + c) * 16 + d;
+                        acc[r] = fmaf(dw * xs, static_cast<float>(isum), acc[r]);
+                    } else {
+                        const uint4 l4 = *reinterpret_cast<const uint4*>(w0 + r * F::seg_bytes(0));
+                        const uint4 h4 = *reinterpret_cast<const uint4*>(w1 + r * F::seg_bytes(1));
+                        // codes stay 0..63; the zero point 32 is in `bias`
+                        const uint32_t q0 = ((l4.x >> shift4) & 0x0F0F0F0Fu) | (((h4.x >> shift2) & 0x03030303u) << 4);
+                        const uint32_t q1 = ((l4.y >> shift4) & 0x0F0F0F0Fu) | (((h4.y >> shift2) & 0x03030303u) << 4);
+                        const uint32_t q2 = ((l4.z >> shift4) & 0x0F0F0F0Fu) | (((h4.z >> shift2) & 0x03030303u) << 4);
+                        const uint32_t q3 = ((l4.w >> shift4) & 0x0F0F0F0Fu) | (((h4.w >> shift2) & 0x03030303u) << 4);
+                        int a = dp4a_us(q0, xa.x, 0), c = dp4a_us(q0, xc.x, bias);
+                        a = dp4a_us(q1, xa.y, a); c = dp4a_us(q1, xc.y, c);
+                        a = dp4a_us(q2, xa.z, a); c = dp4a_us(q2, xc.z, c);
+                        a = dp4a_us(q3, xa.w, a); c = dp4a_us(q3, xc.w, c);
+                        const float dsc = __half2float(dd[r * (F::seg_bytes(3) / 2)]) * static_cast<float>(sc[r * F::seg_bytes(2)]);  // (d * scale), the reference's order
+                        acc[r] = fmaf(dsc * xs, static_cast<float>(a * 256 + c), acc[r]);
                     }
+                };
+                if (g.nrows == static_cast<uint32_t>(kTeamWarps)) {   // the common case: no per-row test
+#pragma unroll
+                    for (int r = 0; r < kR; ++r) row_body(r);
+                } else {
+#pragma unroll
+                    for (int r = 0; r < kR; ++r)
+                        if (rowbase + r < g.nrows) row_body(r);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&empty[stage]);

@@ -15,6 +15,8 @@
 #pragma once
 #include <cstdint>
 
+#include "zk_ptx.cuh"
+
 namespace zk {
 
 constexpr int kPickMaxSegments = 8;
@@ -45,6 +47,8 @@ __device__ __forceinline__ unsigned long long pick_key(float v, uint32_t index) 
 
 // grid = (nseg * ctas_per_segment, tokens)
 __global__ void __launch_bounds__(kPickThreads) pick_scan_kernel(const __grid_constant__ PickParams p) {
+    pdl_launch_dependents();
+    pdl_wait();   // the logits, and the cleared keys, come from earlier launches
     const uint32_t s = blockIdx.x / p.ctas_per_segment, part = blockIdx.x % p.ctas_per_segment;
     const PickSegment& sg = p.seg[s];
     const float* row = sg.base + static_cast<size_t>(blockIdx.y) * sg.token_stride;
@@ -70,6 +74,8 @@ __global__ void __launch_bounds__(kPickThreads) pick_scan_kernel(const __grid_co
 
 // keys[t] -> picked index as a signed 64-bit integer, in place.
 __global__ void pick_finish_kernel(unsigned long long* keys, uint32_t tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= tokens) return;
     const unsigned long long k = keys[t];

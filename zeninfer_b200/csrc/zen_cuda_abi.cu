@@ -15,6 +15,7 @@
 #include <algorithm>
 #include <atomic>
 #include <chrono>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -23,6 +24,7 @@
 #include <unordered_map>
 #include <vector>
 
+#include "decode_ops.cuh"
 #include "gemm_q8_0_i8.cuh"
 #include "gemv_kq.cuh"
 #include "gemv_q8_0.cuh"
@@ -86,6 +88,7 @@ struct State {
     float* d_x{}; size_t d_x_bytes{};
     float* d_y{}; size_t d_y_bytes{};
     uint8_t* d_gemm_ws{}; size_t d_gemm_ws_bytes{};  // quantised activations of the prefill GEMM: codes, then block-major scales
+    bool gemm_stream_k{true}; // prefill GEMM: even K-tile shares when tiles do not divide the SMs (ZEN_CUDA_GEMM_STREAMK=0 turns it off)
     bool use_gemm{true};     // tensor-core prefill path (ZEN_CUDA_GEMM=0 falls back to chunks of eight tokens on the decode kernel)
     void* encode_tiled{};    // cuTensorMapEncodeTiled, resolved through the runtime
     int* h_error{};   // mapped pinned word the kernels write on a bounded-wait timeout
@@ -93,6 +96,7 @@ struct State {
     // Small results skip the copy engine: the kernels store them straight into mapped pinned memory, a one-thread
     // kernel behind them raises a sequence number there, and the calling thread polls it.
     float* h_result{}; float* d_result{}; size_t h_result_bytes{};
+    float* h_input{}; float* d_input{};   // mapped pinned staging for small activations, read by stage_in_kernel
     volatile unsigned* h_done{}; unsigned* d_done{}; unsigned done_seq{};
 };
 
@@ -159,6 +163,7 @@ bool init_locked(State& s) {
     }
     if (const char* m = std::getenv("ZEN_CUDA_PDL")) s.pdl = m[0] != '0';
     if (const char* m = std::getenv("ZEN_CUDA_GEMM")) s.use_gemm = m[0] != '0';
+    if (const char* m = std::getenv("ZEN_CUDA_GEMM_STREAMK")) s.gemm_stream_k = m[0] != '0';
     {
         cudaDriverEntryPointQueryResult qres{};
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &s.encode_tiled, cudaEnableDefault, &qres) != cudaSuccess ||
@@ -553,7 +558,15 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
         p.m_tiles = (p.rows + zk::kGemmM - 1) / zk::kGemmM;
         p.n_tiles = (p.tokens + n_tile - 1) / n_tile;
         p.error_word = s.d_error;
-        const unsigned grid = std::min<unsigned>(p.m_tiles * p.n_tiles, static_cast<unsigned>(s.sm_count));
+        const unsigned tiles = p.m_tiles * p.n_tiles, ktiles = (nb + zk::kGemmBlocksPerTile - 1) / zk::kGemmBlocksPerTile;
+        const unsigned grid = std::min<unsigned>(tiles, static_cast<unsigned>(s.sm_count));
+        // Uneven tile counts: share the K tiles evenly instead (every CTA's range must span at least one tile's worth,
+        // so that no tile is cut more than once).
+        p.stream_k = (s.gemm_stream_k && tiles % grid != 0 && static_cast<uint64_t>(tiles) * ktiles / grid >= ktiles) ? 1u : 0u;
+        if (p.stream_k) {
+            zk::gemm_zero_split_tiles_kernel<<<grid, 256, 0, st>>>(p.out, p.rows, p.tokens, p.m_tiles, p.n_tiles, n_tile, ktiles);
+            ++s.stats.dispatches;
+        }
         const cudaError_t e = launch_gemm<128>(p, grid, st);
         if (e != cudaSuccess) return set_error(s, std::string("gemm launch: ") + cudaGetErrorString(e));
         ++s.stats.dispatches;
@@ -603,7 +616,7 @@ bool ensure_scratch(State& s, size_t x_bytes, size_t y_bytes) {
     if (y_bytes > s.d_y_bytes) {
         if (s.d_y) cudaFree(s.d_y);
         s.d_y = nullptr; s.d_y_bytes = 0;
-        ZC_CUDA(s, cudaMalloc(reinterpret_cast<void**>(&s.d_y), y_bytes));
+        ZC_CUDA(s, cudaMalloc(reinterpret_cast<void**>(&s.d_y), (y_bytes + 255) & ~size_t(255)));
         s.d_y_bytes = y_bytes;
     }
     const size_t need = std::max(x_bytes, y_bytes);
@@ -619,12 +632,35 @@ bool ensure_scratch(State& s, size_t x_bytes, size_t y_bytes) {
 
 constexpr size_t kDirectResultBytes = size_t(1) << 20;  // results up to this size are written to host memory by the kernel itself
 
-__global__ void publish_done_kernel(volatile unsigned* done, unsigned seq) {
-    __threadfence_system();  // the grid before this one has finished; its stores to host memory are ordered before the flag
-    *done = seq;
+constexpr size_t kDirectInputBytes = size_t(256) << 10;  // activations up to this size are fetched from host memory by a kernel
+
+// Launched with programmatic stream serialisation right behind the product: resident early, it sleeps until the
+// product grid has completed, copies the result from HBM to mapped host memory in full lines (the product kernels
+// write one float per row from different warps, which would cross PCIe as thousands of 4-byte writes), and then
+// raises the sequence number.  One CTA.
+__global__ void __launch_bounds__(1024) copy_out_publish_kernel(float4* __restrict__ host_dst, const float4* __restrict__ src, size_t n16,
+                                                                volatile unsigned* done, unsigned seq) {
+    zk::pdl_wait();
+    for (size_t i = threadIdx.x; i < n16; i += blockDim.x) host_dst[i] = __ldcg(src + i);
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) *done = seq;
+}
+
+// Fetches the activations from mapped host memory into HBM.  It lets the next launch start at once: the product
+// kernels stream their weights (which do not depend on the activations) while this copy crosses PCIe, and only their
+// activation read waits for it (griddepcontrol.wait).
+__global__ void stage_in_kernel(float4* __restrict__ dst, const float4* __restrict__ src, size_t n) {
+    zk::pdl_launch_dependents();
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        dst[i] = src[i];
 }
 
 bool ensure_direct_result(State& s, size_t bytes) {
+    if (!s.h_input) {
+        ZC_CUDA(s, cudaHostAlloc(reinterpret_cast<void**>(&s.h_input), kDirectInputBytes, cudaHostAllocMapped));
+        ZC_CUDA(s, cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.d_input), s.h_input, 0));
+    }
     if (!s.h_done) {
         unsigned* h = nullptr;
         ZC_CUDA(s, cudaHostAlloc(reinterpret_cast<void**>(&h), 64, cudaHostAllocMapped));
@@ -635,7 +671,7 @@ bool ensure_direct_result(State& s, size_t bytes) {
     if (bytes > s.h_result_bytes) {
         if (s.h_result) { cudaStreamSynchronize(s.stream); cudaFreeHost(s.h_result); }
         s.h_result = nullptr; s.d_result = nullptr; s.h_result_bytes = 0;
-        const size_t cap = std::max(bytes, size_t(64) << 10);
+        const size_t cap = (std::max(bytes, size_t(64) << 10) + 255) & ~size_t(255);   // the copy-out kernel moves whole 16-byte words
         ZC_CUDA(s, cudaHostAlloc(reinterpret_cast<void**>(&s.h_result), cap, cudaHostAllocMapped));
         ZC_CUDA(s, cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.d_result), s.h_result, 0));
         s.h_result_bytes = cap;
@@ -662,6 +698,22 @@ bool wait_done(State& s, unsigned seq) {
     return true;
 }
 
+// Launch with programmatic stream serialisation (the kernel calls griddepcontrol.wait before it touches memory).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(State& s, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = s.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 bool check_error_word(State& s) {
     if (*s.h_error == 0) return true;
     const int code = *s.h_error;
@@ -685,13 +737,22 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     }
     const size_t x_bytes = tokens * cols * sizeof(float), y_bytes = tokens * total_rows * sizeof(float);
     const bool direct = y_bytes <= kDirectResultBytes;
-    if (!ensure_scratch(s, x_bytes, direct ? 0 : y_bytes)) return false;
+    if (!ensure_scratch(s, x_bytes, y_bytes)) return false;
     if (direct && !ensure_direct_result(s, y_bytes)) return false;
-    float* const d_result = direct ? s.d_result : s.d_y;
+    float* const d_result = s.d_y;
     const float* const h_result = direct ? s.h_result : s.h_stage;
     auto t0 = clock_type::now();
-    std::memcpy(s.h_stage, x, x_bytes);
-    ZC_CUDA(s, cudaMemcpyAsync(s.d_x, s.h_stage, x_bytes, cudaMemcpyHostToDevice, s.stream));
+    if (direct && x_bytes <= kDirectInputBytes) {
+        std::memcpy(s.h_input, x, x_bytes);
+        const size_t n16 = x_bytes / sizeof(float4);
+        stage_in_kernel<<<static_cast<unsigned>(std::min<size_t>((n16 + 255) / 256, 32)), 256, 0, s.stream>>>(
+            reinterpret_cast<float4*>(s.d_x), reinterpret_cast<const float4*>(s.d_input), n16);
+        ++s.stats.dispatches;
+        if (cudaGetLastError() != cudaSuccess) return set_error(s, "activation fetch launch failed");
+    } else {
+        std::memcpy(s.h_stage, x, x_bytes);
+        ZC_CUDA(s, cudaMemcpyAsync(s.d_x, s.h_stage, x_bytes, cudaMemcpyHostToDevice, s.stream));
+    }
     s.stats.transfer_us += us_since(t0);
     t0 = clock_type::now();
     // Token chunks of up to eight rows per launch; each task's device output is [tokens][rows_i].
@@ -716,9 +777,19 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     t0 = clock_type::now();
     if (direct) {
         const unsigned seq = ++s.done_seq;
-        publish_done_kernel<<<1, 1, 0, s.stream>>>(s.d_done, seq);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(1);
+        cfg.blockDim = dim3(1024);
+        cfg.stream = s.stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = s.pdl ? 1 : 0;
         ++s.stats.dispatches;
-        if (cudaGetLastError() != cudaSuccess) return set_error(s, "result flag launch failed");
+        if (cudaLaunchKernelEx(&cfg, copy_out_publish_kernel, reinterpret_cast<float4*>(s.d_result), reinterpret_cast<const float4*>(s.d_y),
+                               (y_bytes + 15) / 16, s.d_done, seq) != cudaSuccess)
+            return set_error(s, "result copy launch failed");
         if (!wait_done(s, seq)) return false;
     } else {
         ZC_CUDA(s, cudaMemcpyAsync(s.h_stage, s.d_y, y_bytes, cudaMemcpyDeviceToHost, s.stream));
@@ -771,6 +842,8 @@ void zen_cuda_shutdown(void) {
         if (s.h_stage) cudaFreeHost(s.h_stage);
         if (s.h_error) cudaFreeHost(s.h_error);
         if (s.h_result) cudaFreeHost(s.h_result);
+        if (s.h_input) cudaFreeHost(s.h_input);
+        s.h_input = s.d_input = nullptr;
         if (s.h_done) cudaFreeHost(const_cast<unsigned*>(s.h_done));
         s.h_result = s.d_result = nullptr; s.h_result_bytes = 0;
         s.h_done = nullptr; s.d_done = nullptr;
@@ -1119,11 +1192,93 @@ int zen_cuda_dev_greedy_pick(const zen_cuda_pick_segment* segments, size_t count
     p.keys = reinterpret_cast<unsigned long long*>(d_pick);
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : s.stream;
     ZC_CUDA(s, cudaMemsetAsync(d_pick, 0, tokens * sizeof(int64_t), st));
-    zk::pick_scan_kernel<<<dim3(p.nseg * p.ctas_per_segment, static_cast<unsigned>(tokens)), zk::kPickThreads, 0, st>>>(p);
-    zk::pick_finish_kernel<<<static_cast<unsigned>((tokens + 63) / 64), 64, 0, st>>>(p.keys, static_cast<uint32_t>(tokens));
+    cudaError_t e = launch_pdl(s, zk::pick_scan_kernel, dim3(p.nseg * p.ctas_per_segment, static_cast<unsigned>(tokens)), dim3(zk::kPickThreads), 0, st, p);
+    if (e == cudaSuccess)
+        e = launch_pdl(s, zk::pick_finish_kernel, dim3(static_cast<unsigned>((tokens + 63) / 64)), dim3(64), 0, st, p.keys, static_cast<uint32_t>(tokens));
     s.stats.dispatches += 2;
-    if (cudaGetLastError() != cudaSuccess) return set_error(s, "dev_greedy_pick: launch failed") ? 1 : 0;
+    if (e != cudaSuccess) return set_error(s, "dev_greedy_pick: launch failed") ? 1 : 0;
     return 1;
+}
+
+// ---- decode-step operators ------------------------------------------------------------------------------------------
+
+#define ZC_DEV_ENTER(name)                                   \
+    State& s = state();                                      \
+    std::lock_guard<std::mutex> lock(s.mutex);               \
+    if (!init_locked(s)) return 0;                           \
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : s.stream; \
+    const char* const entry_name = name;                     \
+    (void)entry_name
+#define ZC_DEV_LEAVE(launch_result)                                                                            \
+    ++s.stats.dispatches;                                                                                      \
+    if ((launch_result) != cudaSuccess) return set_error(s, std::string(entry_name) + ": launch failed") ? 1 : 0; \
+    return 1
+
+int zen_cuda_dev_embed_q8_0(const zen_cuda_weights* w, const int64_t* d_token, float* d_out, void* stream) {
+    ZC_DEV_ENTER("dev_embed_q8_0");
+    if (!w || !d_token || !d_out || w->format != ZEN_CUDA_Q8_0) return set_error(s, "dev_embed_q8_0: bad arguments") ? 1 : 0;
+    const cudaError_t e = launch_pdl(s, zk::embed_row_q8_0_kernel, dim3(static_cast<unsigned>((w->cols + 255) / 256)), dim3(256), 0, st,
+        static_cast<const int8_t*>(w->plane[0]), static_cast<const __half*>(w->plane[1]), static_cast<uint32_t>(w->rows), static_cast<uint32_t>(w->cols),
+        w->nbp, reinterpret_cast<const long long*>(d_token), d_out, s.d_error);
+    ZC_DEV_LEAVE(e);
+}
+
+int zen_cuda_dev_rms_norm(float* d_x, const float* d_delta, const float* d_weight, float* d_y, size_t n, size_t rows, float eps, void* stream) {
+    ZC_DEV_ENTER("dev_rms_norm");
+    if (!d_x || !n || !rows || rows > 65535 || (d_weight && !d_y) || (!d_weight && !d_delta)) return set_error(s, "dev_rms_norm: bad arguments") ? 1 : 0;
+    const cudaError_t e = launch_pdl(s, zk::residual_rms_norm_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, st, d_x, d_delta, d_weight, d_y,
+                                     static_cast<uint32_t>(n), eps);
+    ZC_DEV_LEAVE(e);
+}
+
+int zen_cuda_dev_rope_kv_append(float* d_q, float* d_k, const float* d_v, const float* d_cos, const float* d_sin, const int* d_pos,
+                                size_t heads, size_t kv_heads, size_t head_dim, size_t pairs, int adjacent, float* d_k_cache, float* d_v_cache,
+                                size_t max_positions, void* stream) {
+    ZC_DEV_ENTER("dev_rope_kv_append");
+    if (!d_q || !d_k || !d_v || !d_cos || !d_sin || !d_pos || !d_k_cache || !d_v_cache || !heads || !kv_heads || !head_dim || 2 * pairs > head_dim ||
+        !max_positions)
+        return set_error(s, "dev_rope_kv_append: bad arguments") ? 1 : 0;
+    const cudaError_t e = launch_pdl(s, zk::rope_kv_append_kernel, dim3(1), dim3(1024), 0, st, d_q, d_k, d_v, d_cos, d_sin, d_pos,
+                                     static_cast<uint32_t>(heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(head_dim),
+                                     static_cast<uint32_t>(pairs), adjacent, d_k_cache, d_v_cache, static_cast<uint32_t>(max_positions), s.d_error);
+    ZC_DEV_LEAVE(e);
+}
+
+int zen_cuda_dev_attention(const float* d_q, const float* d_k_cache, const float* d_v_cache, const int* d_pos, float* d_out, size_t heads,
+                           size_t kv_heads, size_t head_dim, float scale, size_t window, size_t max_positions, void* stream) {
+    ZC_DEV_ENTER("dev_attention");
+    if (!d_q || !d_k_cache || !d_v_cache || !d_pos || !d_out || !heads || !kv_heads || heads % kv_heads || !head_dim || head_dim % 4 || head_dim > 256 ||
+        !max_positions)
+        return set_error(s, "dev_attention: bad arguments") ? 1 : 0;
+    const size_t span = window ? std::min(window, max_positions) : max_positions;
+    const size_t smem = span * sizeof(float);
+    if (smem + 1024 > s.smem_optin) return set_error(s, "dev_attention: the attended span does not fit shared memory") ? 1 : 0;
+    static size_t configured = 48 * 1024;
+    if (smem > configured) {
+        if (cudaFuncSetAttribute(zk::attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+            return set_error(s, "dev_attention: shared memory opt-in failed") ? 1 : 0;
+        configured = smem;
+    }
+    if (scale == 0.0f) scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+    const cudaError_t e = launch_pdl(s, zk::attention_decode_kernel, dim3(static_cast<unsigned>(heads)), dim3(zk::kAttnThreads), smem, st,
+        d_q, d_k_cache, d_v_cache, d_pos, d_out, static_cast<uint32_t>(heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(head_dim), scale,
+        static_cast<uint32_t>(window), static_cast<uint32_t>(max_positions), s.d_error);
+    ZC_DEV_LEAVE(e);
+}
+
+int zen_cuda_dev_silu_mul(const float* d_gate, const float* d_up, float* d_out, size_t count, void* stream) {
+    ZC_DEV_ENTER("dev_silu_mul");
+    if (!d_gate || !d_up || !d_out || !count) return set_error(s, "dev_silu_mul: bad arguments") ? 1 : 0;
+    const cudaError_t e = launch_pdl(s, zk::silu_mul_kernel, dim3(static_cast<unsigned>(std::min<size_t>((count + 255) / 256, 4 * static_cast<size_t>(s.sm_count)))),
+                                     dim3(256), 0, st, d_gate, d_up, d_out, count);
+    ZC_DEV_LEAVE(e);
+}
+
+int zen_cuda_dev_advance_position(int* d_pos, int delta, void* stream) {
+    ZC_DEV_ENTER("dev_advance_position");
+    if (!d_pos) return set_error(s, "dev_advance_position: bad arguments") ? 1 : 0;
+    const cudaError_t e = launch_pdl(s, zk::advance_position_kernel, dim3(1), dim3(1), 0, st, d_pos, delta);
+    ZC_DEV_LEAVE(e);
 }
 
 int zen_cuda_dev_check(void* stream) {

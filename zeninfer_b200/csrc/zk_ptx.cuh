@@ -12,7 +12,9 @@ namespace zk {
 constexpr long long kWaitBudgetCycles = 2000000000LL;
 
 // Error codes written to the kernel's error word (0 = success).
-enum : int { kErrNone = 0, kErrFullWaitTimeout = 1, kErrEmptyWaitTimeout = 2, kErrDrainTimeout = 3, kErrTmemWaitTimeout = 4 };
+enum : int { kErrNone = 0, kErrFullWaitTimeout = 1, kErrEmptyWaitTimeout = 2, kErrDrainTimeout = 3, kErrTmemWaitTimeout = 4,
+             /* 5: a peer did not publish in time (peer_gather.cuh) */
+             kErrBadToken = 6, kErrBadPosition = 7, kErrNonFinite = 8 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 

@@ -1,0 +1,226 @@
+"""A dense Llama-style decoder whose every token step runs on the device through the C-ABI.
+
+Host-side mirror of the reference's ModelRuntime::generate for a `general.architecture = llama` model
+(src/adapters/dense_transformer_runtime.cpp:4660-4820 over forward() :3670-4600): embedding fetch, per layer
+RMSNorm -> q|k|v -> adjacent-pair RoPE + KV append -> grouped-query attention -> o -> residual -> RMSNorm ->
+gate|up -> SwiGLU -> down -> residual, final RMSNorm, lm_head, greedy pick.  All projections and the lm_head go
+through the quantised product kernels (zen_cuda_dev_gemv); the operators between them are the decode-step entry
+points of include/zen_cuda.h.  Nothing here computes on the host: Python only orders launches and builds the RoPE
+cos/sin tables (the reference's table contract, rope_table :264-276).
+
+The prompt is consumed one token at a time through the same step (the reference prefills in batches; the
+arithmetic per token is the same).  A step is captured once into two CUDA graphs (layers; lm_head + pick), because
+the position and the token are read from device memory.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import blocks
+from .backend import ACT_FP32, ACT_INT8, Backend
+
+
+@dataclass(frozen=True)
+class LlamaConfig:
+    embedding: int = 4096
+    layers: int = 32
+    heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    ffn: int = 14336
+    vocab: int = 128256
+    rope_base: float = 500000.0
+    rms_eps: float = 1e-5
+    context: int = 1024
+
+    @property
+    def q_width(self) -> int:
+        return self.heads * self.head_dim
+
+    @property
+    def kv_width(self) -> int:
+        return self.kv_heads * self.head_dim
+
+
+MATRIX_SHAPES = {  # GGUF tensor name suffix -> (rows, columns) as functions of the config
+    "attn_q.weight": lambda c: (c.q_width, c.embedding), "attn_k.weight": lambda c: (c.kv_width, c.embedding),
+    "attn_v.weight": lambda c: (c.kv_width, c.embedding), "attn_output.weight": lambda c: (c.embedding, c.q_width),
+    "ffn_gate.weight": lambda c: (c.ffn, c.embedding), "ffn_up.weight": lambda c: (c.ffn, c.embedding),
+    "ffn_down.weight": lambda c: (c.embedding, c.ffn),
+}
+
+
+def tensor_plan(cfg: LlamaConfig) -> list[tuple[str, tuple[int, ...], bool]]:
+    """(name, shape, is_matrix) in file order; matrices are [rows, columns] and stored quantised."""
+    plan = [("token_embd.weight", (cfg.vocab, cfg.embedding), True), ("output_norm.weight", (cfg.embedding,), False),
+            ("output.weight", (cfg.vocab, cfg.embedding), True)]
+    for layer in range(cfg.layers):
+        p = f"blk.{layer}."
+        plan.append((p + "attn_norm.weight", (cfg.embedding,), False))
+        for suffix in ("attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight"):
+            plan.append((p + suffix, MATRIX_SHAPES[suffix](cfg), True))
+        plan.append((p + "ffn_norm.weight", (cfg.embedding,), False))
+        for suffix in ("ffn_gate.weight", "ffn_up.weight", "ffn_down.weight"):
+            plan.append((p + suffix, MATRIX_SHAPES[suffix](cfg), True))
+    return plan
+
+
+def synthetic_tensors(cfg: LlamaConfig, seed: int, weight_std: float = 0.02):
+    """Random-init model, one generator: matrices N(0, weight_std) packed to Q8_0 (raw GGUF blocks), norm weights
+    1 + N(0, weight_std) in fp32.  Yields (name, array, is_matrix) in tensor_plan order, one tensor at a time."""
+    rng = np.random.default_rng(seed)
+    for name, shape, is_matrix in tensor_plan(cfg):
+        if is_matrix:
+            w = rng.standard_normal(shape, dtype=np.float32) * np.float32(weight_std)
+            yield name, np.ascontiguousarray(blocks.quantize_q8_0(w)), True
+        else:
+            yield name, (np.float32(1.0) + rng.standard_normal(shape, dtype=np.float32) * np.float32(weight_std)).astype(np.float32), False
+
+
+def rope_tables(cfg: LlamaConfig, positions: int) -> tuple[np.ndarray, np.ndarray]:
+    """cos/sin [positions][head_dim / 2] in fp32, the arithmetic of rope_table (no scaling):
+    freq_i = base^(-2 i / rotary_dim), angle = float(pos) * freq_i, all in single precision."""
+    half = cfg.head_dim // 2
+    i = np.arange(half, dtype=np.float32)
+    freq = np.power(np.float32(cfg.rope_base), (np.float32(-2.0) * i / np.float32(cfg.head_dim)).astype(np.float32)).astype(np.float32)
+    angle = (np.arange(positions, dtype=np.float32)[:, None] * freq[None, :]).astype(np.float32)
+    return np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
+
+
+class LlamaDecoder:
+    """Holds the resident model and the step's device buffers.  `tensors` yields (name, array, is_matrix) as
+    synthetic_tensors does; matrices must be Q8_0 raw blocks [rows, row_bytes]."""
+
+    def __init__(self, backend: Backend, cfg: LlamaConfig, tensors, act_mode: int = ACT_INT8, max_positions: int | None = None, device=None):
+        import torch
+        self.torch, self.be, self.cfg, self.act_mode = torch, backend, cfg, act_mode
+        self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.max_positions = max_positions or cfg.context
+        self.stream = torch.cuda.Stream(device=self.dev)
+        self.h: dict[str, int] = {}        # matrix name -> resident handle
+        self.norm: dict[str, "torch.Tensor"] = {}
+        shapes = {name: shape for name, shape, _ in tensor_plan(cfg)}
+        for name, arr, is_matrix in tensors:
+            if is_matrix:
+                rows, cols = shapes[name]
+                self.h[name] = backend.dev_upload("Q8_0", arr, rows, cols)
+            else:
+                self.norm[name] = torch.from_numpy(np.ascontiguousarray(arr, np.float32)).to(self.dev)
+        missing = [n for n, _, m in tensor_plan(cfg) if (m and n not in self.h) or (not m and n not in self.norm)]
+        if missing:
+            raise ValueError(f"model is missing tensors: {missing[:4]}...")
+        f32 = dict(dtype=torch.float32, device=self.dev)
+        E, QW, KW, F, V = cfg.embedding, cfg.q_width, cfg.kv_width, cfg.ffn, cfg.vocab
+        self.x, self.xn, self.tmp = torch.zeros(E, **f32), torch.zeros(E, **f32), torch.zeros(E, **f32)
+        self.q, self.k, self.v, self.att = torch.zeros(QW, **f32), torch.zeros(KW, **f32), torch.zeros(KW, **f32), torch.zeros(QW, **f32)
+        self.gate, self.up, self.hid = torch.zeros(F, **f32), torch.zeros(F, **f32), torch.zeros(F, **f32)
+        self.logits = torch.zeros(V, **f32)
+        self.k_cache = torch.zeros((cfg.layers, self.max_positions, KW), **f32)
+        self.v_cache = torch.zeros((cfg.layers, self.max_positions, KW), **f32)
+        cos, sin = rope_tables(cfg, self.max_positions)
+        self.cos, self.sin = torch.from_numpy(cos).to(self.dev), torch.from_numpy(sin).to(self.dev)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.token = torch.zeros(1, dtype=torch.int64, device=self.dev)
+        self.host_token = torch.zeros(1, dtype=torch.int64).pin_memory()   # generate() feeds every step from the host, as the reference does
+        self.graph_layers = self.graph_head = None
+
+    # ---- one token step, as launches on self.stream ----
+    def _enqueue_layers(self) -> None:
+        be, cfg, st, mode = self.be, self.cfg, self.stream.cuda_stream, self.act_mode
+        P = lambda t: t.data_ptr()
+        be.dev_embed_q8_0(self.h["token_embd.weight"], P(self.token), P(self.x), st)
+        be.dev_rms_norm(P(self.x), None, P(self.norm["blk.0.attn_norm.weight"]), P(self.xn), cfg.embedding, 1, cfg.rms_eps, st)
+        for layer in range(cfg.layers):
+            p = f"blk.{layer}."
+            be.dev_gemv([self.h[p + "attn_q.weight"], self.h[p + "attn_k.weight"], self.h[p + "attn_v.weight"]],
+                        [P(self.q), P(self.k), P(self.v)], P(self.xn), 1, mode, st)
+            be.dev_rope_kv_append(P(self.q), P(self.k), P(self.v), P(self.cos), P(self.sin), P(self.pos), cfg.heads, cfg.kv_heads, cfg.head_dim,
+                                  cfg.head_dim // 2, True, P(self.k_cache[layer]), P(self.v_cache[layer]), self.max_positions, st)
+            be.dev_attention(P(self.q), P(self.k_cache[layer]), P(self.v_cache[layer]), P(self.pos), P(self.att), cfg.heads, cfg.kv_heads,
+                             cfg.head_dim, self.max_positions, 0.0, 0, st)
+            be.dev_gemv([self.h[p + "attn_output.weight"]], [P(self.tmp)], P(self.att), 1, mode, st)
+            be.dev_rms_norm(P(self.x), P(self.tmp), P(self.norm[p + "ffn_norm.weight"]), P(self.xn), cfg.embedding, 1, cfg.rms_eps, st)
+            be.dev_gemv([self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]], [P(self.gate), P(self.up)], P(self.xn), 1, mode, st)
+            be.dev_silu_mul(P(self.gate), P(self.up), P(self.hid), cfg.ffn, st)
+            be.dev_gemv([self.h[p + "ffn_down.weight"]], [P(self.tmp)], P(self.hid), 1, mode, st)
+            nxt = self.norm[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < cfg.layers else self.norm["output_norm.weight"]
+            be.dev_rms_norm(P(self.x), P(self.tmp), P(nxt), P(self.xn), cfg.embedding, 1, cfg.rms_eps, st)
+        be.dev_advance_position(P(self.pos), 1, st)
+
+    def _enqueue_head(self) -> None:
+        be, st = self.be, self.stream.cuda_stream
+        be.dev_gemv([self.h["output.weight"]], [self.logits.data_ptr()], self.xn.data_ptr(), 1, self.act_mode, st)
+        be.dev_greedy_pick([(self.logits.data_ptr(), self.cfg.vocab, 0, self.cfg.vocab)], 1, self.token.data_ptr(), st)
+
+    def capture(self) -> None:
+        """Runs one throw-away step (kernel attributes are set on first launch), then captures the two graphs."""
+        torch = self.torch
+        with torch.cuda.stream(self.stream):
+            self.reset()
+            self._enqueue_layers()
+            self._enqueue_head()
+            self.stream.synchronize()
+            self.graph_layers, self.graph_head = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph_layers, stream=self.stream):
+                self._enqueue_layers()
+            with torch.cuda.graph(self.graph_head, stream=self.stream):
+                self._enqueue_head()
+            self.stream.synchronize()
+        self.reset()
+
+    def reset(self) -> None:
+        with self.torch.cuda.stream(self.stream):
+            self.pos.zero_()
+            self.token.zero_()
+        self.stream.synchronize()
+
+    def step(self, want_token: bool) -> None:
+        """Consumes the token in self.token at position self.pos; with want_token the pick replaces self.token."""
+        with self.torch.cuda.stream(self.stream):
+            if self.graph_layers is not None:
+                self.graph_layers.replay()
+                if want_token:
+                    self.graph_head.replay()
+            else:
+                self._enqueue_layers()
+                if want_token:
+                    self._enqueue_head()
+
+    def generate(self, prompt: list[int], max_new: int, on_token=None) -> list[int]:
+        """Greedy generation: the prompt token by token, then max_new picks (each read back, as the reference's
+        per-token callback does).  Raises when the context would overflow."""
+        torch = self.torch
+        if not prompt or len(prompt) + max_new > self.max_positions:
+            raise ValueError("prompt + max_new exceeds the configured positions")
+        self.reset()
+        ids = torch.tensor(prompt, dtype=torch.int64).pin_memory()
+        out: list[int] = []
+        with torch.cuda.stream(self.stream):
+            for i in range(len(prompt)):
+                self.token.copy_(ids[i:i + 1], non_blocking=True)
+                self.step(want_token=(i + 1 == len(prompt)))
+            for n in range(max_new):
+                tok = int(self.token.item())      # device -> host read of the step's result
+                out.append(tok)
+                if on_token:
+                    on_token(tok)
+                if n + 1 < max_new:
+                    self.host_token[0] = tok      # host -> device: the next step's input comes from the caller's side
+                    self.token.copy_(self.host_token, non_blocking=True)
+                    self.step(want_token=True)
+        self.be.dev_check(self.stream.cuda_stream)
+        return out
+
+    def last_logits(self) -> np.ndarray:
+        self.stream.synchronize()
+        return self.logits.cpu().numpy()
+
+    def close(self) -> None:
+        for h in self.h.values():
+            self.be.dev_free(h)
+        self.h.clear()
+
+
+__all__ = ["LlamaConfig", "LlamaDecoder", "synthetic_tensors", "tensor_plan", "rope_tables", "ACT_FP32", "ACT_INT8"]
