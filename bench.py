@@ -663,7 +663,7 @@ def torch_q8_0_pack(w):
 def run_decode(args) -> None:
     """Config: 32 layers, d 4096, 32 query / 8 KV heads of 128, SwiGLU 14336, vocab 128256, eps 1e-5, theta 500000,
     weights N(0, 0.02) seed 6, a prompt of 512 uniform-random ids, then greedy decode steps.  A step is one decoded
-    token: 290 launches replayed from two CUDA graphs.  The prompt is consumed token by token through the same step
+    token: 165 launches replayed from two CUDA graphs (norms, SwiGLU and residual adds are folded into the projections).  The prompt is consumed token by token through the same step
     and is not timed."""
     import torch
     from zeninfer_b200 import Backend
@@ -675,7 +675,7 @@ def run_decode(args) -> None:
     torch.cuda.set_device(0)
     be = Backend()
     cfg = LlamaConfig()
-    prompt_len = 512
+    prompt_len = args.prompt_len
     steps = args.steps if args.steps != 2000 else 125      # the default run: 3 warm-up + 125 timed = the 128 greedy steps
     warm = max(3, args.warmup)
 
@@ -759,7 +759,7 @@ def run_decode(args) -> None:
                              f"worker policy), scaled to 32 layers + lm_head by bytes; attention, norms and sampling not included, so an upper bound "
                              f"for the reference's decode rate on these cores"}
 
-    launches_per_step = 2 + 9 * cfg.layers + 1 + 1 + 3
+    launches_per_step = 1 + 5 * cfg.layers + 1 + 1 + 2   # embed, per layer q|k|v + attention block + o + gate|up + down, advance, lm_head, pick (2)
     print(json.dumps({
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
@@ -792,6 +792,7 @@ def main() -> None:
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: how the output shards are all-gathered after each product -- by the product kernel itself "
                          "(peer stores over NVLink, the default) or by an NCCL all-gather launched after it")
+    ap.add_argument("--prompt-len", type=int, default=512, help="workload decode: prompt tokens consumed before the timed steps")
     ap.add_argument("--min-warmup", type=int, default=1500,
                     help="floor on the warm-up step count of the decode workload (about 0.3 s, so the clock sampler is up before "
                          "the timed region); a profiler run lowers it so that few launches precede the captured ones")

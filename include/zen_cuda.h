@@ -154,6 +154,29 @@ size_t zen_cuda_dev_weight_bytes(const zen_cuda_weights* w); /* device bytes hel
 int zen_cuda_dev_gemv(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
                       size_t tokens, int act_mode, void* stream);
 
+/* zen_cuda_dev_gemv for Q8_0 tensors whose input is the SwiGLU hidden state: x = silu(gate) * up is formed while the
+ * activations are loaded for quantisation, so the down projection needs no separate activation launch
+ * (zen::quant::ffn_gemv / the D3D12 gemv_q8_0_ffn submission, src/quant.cpp:1566-1571; silu_mul,
+ * src/adapters/dense_transformer_runtime.cpp:193-199).  d_gate, d_up: device fp32 [tokens][columns]. */
+int zen_cuda_dev_gemv_swiglu(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_gate, const float* d_up,
+                             size_t tokens, int act_mode, void* stream);
+
+/* zen_cuda_dev_gemv for Q8_0 tensors with the layer's small operators folded into the product launch, which is what the
+ * reference's fused D3D12 submissions do (ffn_residual_fused and LayerDecodeParams, include/zen/d3d12_backend.h:289-352,
+ * zen::quant::ffn_residual_fused, src/quant.cpp:1566-1611):
+ *   norm_weight != NULL : the input is RMSNorm(x) * norm_weight, eps = norm_eps (rms_norm, :117-125), formed per CTA in the
+ *                         prologue; x itself is left untouched;
+ *   gate != NULL        : the input is silu(gate) * x (as zen_cuda_dev_gemv_swiglu); not together with norm_weight;
+ *   accumulate != 0     : y += W x instead of y = W x: with y the residual stream this is the layer's residual add. */
+typedef struct zen_cuda_gemv_fusion {
+    const float* norm_weight;
+    float norm_eps;
+    int accumulate;
+    const float* gate;
+} zen_cuda_gemv_fusion;
+int zen_cuda_dev_gemv_fused(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x, size_t tokens, int act_mode,
+                            const zen_cuda_gemv_fusion* fusion, void* stream);
+
 /* Prefill product on the tensor cores (Q8_0, int8 activations): d_out[i] = d_x * W[i]^T, token-major
  * [tokens][rows_i].  d_x: device fp32 [tokens][columns]; `workspace` is device scratch of at least
  * zen_cuda_gemm_workspace_bytes(tokens, columns) bytes that must stay untouched until the work has run (it
@@ -262,6 +285,13 @@ int zen_cuda_dev_rope_kv_append(float* d_q, float* d_k, const float* d_v, const 
  * (src/adapters/dense_transformer_runtime.cpp:4284-4337).  scale 0 means 1 / sqrt(head_dim).  d_out [heads][head_dim]. */
 int zen_cuda_dev_attention(const float* d_q, const float* d_k_cache, const float* d_v_cache, const int* d_pos, float* d_out, size_t heads,
                            size_t kv_heads, size_t head_dim, float scale, size_t window, size_t max_positions, void* stream);
+/* The attention block of one new token in one launch (zen::d3d12::attention_block, include/zen/d3d12_backend.h:247): q, k, v
+ * are the raw projections; the adjacent-pair rotary embedding (row *d_pos of the host-built tables, `pairs` pairs per head)
+ * is applied to q and k inside the kernel, k and v are appended to the caches at *d_pos, and the attention of
+ * zen_cuda_dev_attention runs over [first, *d_pos].  d_q and d_k are left untouched. */
+int zen_cuda_dev_attention_block(const float* d_q, const float* d_k, const float* d_v, const float* d_cos, const float* d_sin, size_t pairs,
+                                 const int* d_pos, float* d_k_cache, float* d_v_cache, float* d_out, size_t heads, size_t kv_heads, size_t head_dim,
+                                 float scale, size_t window, size_t max_positions, void* stream);
 /* d_out = silu(gate) * up (silu_mul, src/adapters/dense_transformer_runtime.cpp:193-199). */
 int zen_cuda_dev_silu_mul(const float* d_gate, const float* d_up, float* d_out, size_t count, void* stream);
 /* *d_pos += delta, in stream order (a step's last launch). */

@@ -43,10 +43,13 @@ def test_embed_row(be):
     h = be.dev_upload("Q8_0", packed, rows, cols)
     out = torch.zeros(cols, device="cuda")
     for tok in (0, 17, rows - 1):
-        be.dev_embed_q8_0(h, dev(np.array([tok], np.int64)).data_ptr(), out.data_ptr(), 0)
+        d_tok = dev(np.array([tok], np.int64))   # device inputs stay referenced until the launch has run
+        be.dev_embed_q8_0(h, d_tok.data_ptr(), out.data_ptr(), 0)
         torch.cuda.synchronize()
         assert np.array_equal(out.cpu().numpy(), blocks.dequantize(blocks.Q8_0, packed, rows, cols)[tok])
-    be.dev_embed_q8_0(h, dev(np.array([rows], np.int64)).data_ptr(), out.data_ptr(), 0)   # out of range: zero row + error word
+    d_tok = dev(np.array([rows], np.int64))
+    be.dev_embed_q8_0(h, d_tok.data_ptr(), out.data_ptr(), 0)   # out of range: zero row + error word
+    torch.cuda.synchronize()
     with pytest.raises(Exception):
         be.dev_check(0)
     assert float(out.abs().sum()) == 0.0
@@ -59,8 +62,9 @@ def test_rms_norm_with_residual(be, n, rows):
     rng = np.random.default_rng(n + rows)
     x, delta = rng.standard_normal((rows, n), dtype=np.float32), rng.standard_normal((rows, n), dtype=np.float32) * np.float32(0.1)
     w = (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
-    dx, dy = dev(x), torch.zeros((rows, n), device="cuda")
-    be.dev_rms_norm(dx.data_ptr(), dev(delta).data_ptr(), dev(w).data_ptr(), dy.data_ptr(), n, rows, 1e-5, 0)
+    dx, dd, dw, dy = dev(x), dev(delta), dev(w), torch.zeros((rows, n), device="cuda")
+    torch.cuda.synchronize()
+    be.dev_rms_norm(dx.data_ptr(), dd.data_ptr(), dw.data_ptr(), dy.data_ptr(), n, rows, 1e-5, 0)
     torch.cuda.synchronize()
     xs = x + delta
     assert np.array_equal(dx.cpu().numpy(), xs)                                    # the residual add is exact
@@ -78,9 +82,10 @@ def test_rope_and_kv_append(be, adjacent):
     rng = np.random.default_rng(3)
     q, k, v = (rng.standard_normal(n, dtype=np.float32) for n in (H * D, KH * D, KH * D))
     pos = 7
-    dq, dk, dv = dev(q), dev(k), dev(v)
+    dq, dk, dv, dcos, dsin, dpos = dev(q), dev(k), dev(v), dev(cos), dev(sin), dev(np.array([pos], np.int32))
     kc, vc = torch.zeros((P, KH * D), device="cuda"), torch.zeros((P, KH * D), device="cuda")
-    be.dev_rope_kv_append(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dev(cos).data_ptr(), dev(sin).data_ptr(), dev(np.array([pos], np.int32)).data_ptr(),
+    torch.cuda.synchronize()
+    be.dev_rope_kv_append(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dcos.data_ptr(), dsin.data_ptr(), dpos.data_ptr(),
                           H, KH, D, D // 2, adjacent, kc.data_ptr(), vc.data_ptr(), P, 0)
     torch.cuda.synchronize()
     be.dev_check(0)
@@ -101,7 +106,8 @@ def test_rope_and_kv_append(be, adjacent):
     assert float(kc.abs().sum() - kc[pos].abs().sum()) == 0.0                     # no other position touched
 
 
-@pytest.mark.parametrize("H,KH,D,pos,window", [(4, 2, 64, 0, 0), (4, 2, 64, 37, 0), (32, 8, 128, 300, 0), (8, 8, 128, 50, 16)])
+@pytest.mark.parametrize("H,KH,D,pos,window", [(4, 2, 64, 0, 0), (4, 2, 64, 2, 0), (4, 2, 64, 37, 0), (32, 8, 128, 300, 0), (32, 8, 128, 511, 0),
+                                               (8, 8, 128, 50, 16), (2, 1, 256, 9, 0)])
 def test_attention(be, H, KH, D, pos, window):
     import torch
     P = 512
@@ -109,8 +115,9 @@ def test_attention(be, H, KH, D, pos, window):
     q = rng.standard_normal(H * D, dtype=np.float32)
     kc, vc = rng.standard_normal((P, KH * D), dtype=np.float32), rng.standard_normal((P, KH * D), dtype=np.float32)
     out = torch.zeros(H * D, device="cuda")
-    be.dev_attention(dev(q).data_ptr(), dev(kc).data_ptr(), dev(vc).data_ptr(), dev(np.array([pos], np.int32)).data_ptr(), out.data_ptr(), H, KH, D, P,
-                     0.0, window, 0)
+    dq, dkc, dvc, dpos = dev(q), dev(kc), dev(vc), dev(np.array([pos], np.int32))
+    torch.cuda.synchronize()
+    be.dev_attention(dq.data_ptr(), dkc.data_ptr(), dvc.data_ptr(), dpos.data_ptr(), out.data_ptr(), H, KH, D, P, 0.0, window, 0)
     torch.cuda.synchronize()
     be.dev_check(0)
     first = pos + 1 - window if window and pos + 1 > window else 0
@@ -127,16 +134,18 @@ def test_silu_mul(be):
     import torch
     rng = np.random.default_rng(9)
     g, u = rng.standard_normal(14336, dtype=np.float32) * 3, rng.standard_normal(14336, dtype=np.float32)
-    out = torch.zeros(14336, device="cuda")
-    be.dev_silu_mul(dev(g).data_ptr(), dev(u).data_ptr(), out.data_ptr(), 14336, 0)
+    out, dg, du = torch.zeros(14336, device="cuda"), dev(g), dev(u)
+    torch.cuda.synchronize()
+    be.dev_silu_mul(dg.data_ptr(), du.data_ptr(), out.data_ptr(), 14336, 0)
     torch.cuda.synchronize()
     assert_parity(out.cpu().numpy(), (g.astype(np.float64) / (1 + np.exp(-g.astype(np.float64)))) * u, 1e-6, "silu_mul")
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("graphs", [False, True])
-def test_generation_matches_the_reference(be, golden, graphs):
+def test_generation_matches_the_reference(be, golden, graphs, fused):
     cfg, meta, prompt, ids, logits = golden
-    dec = LlamaDecoder(be, cfg, synthetic_tensors(cfg, meta["seed"], meta["weight_std"]), act_mode=ACT_FP32)
+    dec = LlamaDecoder(be, cfg, synthetic_tensors(cfg, meta["seed"], meta["weight_std"]), act_mode=ACT_FP32, fused=fused)
     try:
         if graphs:
             dec.capture()
@@ -173,3 +182,92 @@ def test_context_overflow_is_an_error(be, golden):
             dec.generate(prompt.tolist(), 8)
     finally:
         dec.close()
+
+
+@pytest.mark.parametrize("mode,int8", [(ACT_INT8, True), (ACT_FP32, False)])
+def test_gemv_with_fused_swiglu_input(be, zo, mode, int8):
+    import oracle
+    import torch
+    rows, cols = 512, 14336   # the down projection's shape class: several K segments
+    w = np.random.default_rng(21).standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02)
+    packed = np.ascontiguousarray(blocks.quantize_q8_0(w))
+    rng = np.random.default_rng(22)
+    g, u = rng.standard_normal(cols, dtype=np.float32) * 2, rng.standard_normal(cols, dtype=np.float32)
+    h = be.dev_upload("Q8_0", packed, rows, cols)
+    dg, du, y = dev(g), dev(u), torch.zeros(rows, device="cuda")
+    torch.cuda.synchronize()
+    be.dev_gemv_swiglu([h], [y.data_ptr()], dg.data_ptr(), du.data_ptr(), 1, mode, 0)
+    torch.cuda.synchronize()
+    be.dev_check(0)
+    x = ((g / (np.float32(1.0) + np.exp(-g))) * u).astype(np.float32)
+    ref = zo.gemv(oracle.Q8_0, packed, x, rows, cols, int8_acts=int8)
+    assert_parity(y.cpu().numpy(), ref, 1e-3, "swiglu-fused gemv")
+    be.dev_free(h)
+
+
+@pytest.mark.parametrize("H,KH,D,pos", [(4, 2, 64, 0), (4, 2, 64, 5), (32, 8, 128, 130), (2, 1, 256, 9)])
+def test_attention_block_fuses_rope_append_and_attention(be, H, KH, D, pos):
+    import torch
+    P = 256
+    cfg = LlamaConfig(heads=H, kv_heads=KH, head_dim=D, rope_base=500000.0)
+    cos, sin = rope_tables(cfg, P)
+    rng = np.random.default_rng(H * 100 + pos)
+    q, k, v = (rng.standard_normal(n, dtype=np.float32) for n in (H * D, KH * D, KH * D))
+    kc, vc = rng.standard_normal((P, KH * D), dtype=np.float32), rng.standard_normal((P, KH * D), dtype=np.float32)
+    kc[pos:], vc[pos:] = 7.0, -7.0          # whatever the cache holds at and past the position must not matter
+    dq, dk, dv, dcos, dsin, dpos = dev(q), dev(k), dev(v), dev(cos), dev(sin), dev(np.array([pos], np.int32))
+    dkc, dvc, out = dev(kc), dev(vc), torch.zeros(H * D, device="cuda")
+    torch.cuda.synchronize()
+    be.dev_attention_block(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dcos.data_ptr(), dsin.data_ptr(), D // 2, dpos.data_ptr(), dkc.data_ptr(),
+                           dvc.data_ptr(), out.data_ptr(), H, KH, D, P, 0.0, 0, 0)
+    torch.cuda.synchronize()
+    be.dev_check(0)
+
+    def rot(vec, heads):
+        t = vec.reshape(heads, D).astype(np.float64)
+        a, b = t[:, 0::2].copy(), t[:, 1::2].copy()
+        t[:, 0::2], t[:, 1::2] = a * cos[pos] - b * sin[pos], a * sin[pos] + b * cos[pos]
+        return t.reshape(-1)
+
+    qr, kr = rot(q, H), rot(k, KH)
+    keys = np.concatenate([kc[:pos].astype(np.float64), kr[None]], 0)
+    vals = np.concatenate([vc[:pos].astype(np.float64), v[None].astype(np.float64)], 0)
+    ref = np.zeros(H * D)
+    for h in range(H):
+        kh = h // (H // KH)
+        sc = keys[:, kh * D:(kh + 1) * D] @ qr[h * D:(h + 1) * D] / np.sqrt(D)
+        a = np.exp(sc - sc.max())
+        ref[h * D:(h + 1) * D] = (a / a.sum()) @ vals[:, kh * D:(kh + 1) * D]
+    assert_parity(out.cpu().numpy(), ref, 1e-5, "attention block")
+    got_kc, got_vc = dkc.cpu().numpy(), dvc.cpu().numpy()
+    assert_parity(got_kc[pos], kr, 1e-6, "appended key")
+    assert np.array_equal(got_vc[pos], v)
+    assert np.array_equal(got_kc[:pos], kc[:pos]) and np.array_equal(got_kc[pos + 1:], kc[pos + 1:])   # nothing else written
+    assert np.array_equal(dq.cpu().numpy(), q) and np.array_equal(dk.cpu().numpy(), k)                   # inputs untouched
+
+
+@pytest.mark.parametrize("mode,int8", [(ACT_INT8, True), (ACT_FP32, False)])
+@pytest.mark.parametrize("tokens", [1, 3])
+def test_gemv_with_fused_rms_norm_and_accumulate(be, zo, mode, int8, tokens):
+    import oracle
+    import torch
+    rows, cols = 384, 4096
+    w = np.random.default_rng(31).standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02)
+    packed = np.ascontiguousarray(blocks.quantize_q8_0(w))
+    rng = np.random.default_rng(32)
+    x = rng.standard_normal((tokens, cols), dtype=np.float32) * np.float32(1.7)
+    nw = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    y0 = rng.standard_normal((tokens, rows), dtype=np.float32)
+    h = be.dev_upload("Q8_0", packed, rows, cols)
+    dx, dw, y = dev(x), dev(nw), dev(y0)
+    torch.cuda.synchronize()
+    be.dev_gemv_fused([h], [y.data_ptr()], dx.data_ptr(), tokens, mode, 0, norm_weight=dw.data_ptr(), norm_eps=1e-5, accumulate=True)
+    torch.cuda.synchronize()
+    be.dev_check(0)
+    ss = (x.astype(np.float64) ** 2).sum(axis=1, keepdims=True)
+    inv = (np.float32(1.0) / np.sqrt((ss / cols).astype(np.float32) + np.float32(1e-5))).astype(np.float32)
+    xn = (x * inv * nw).astype(np.float32)
+    ref = y0 + zo.gemm(oracle.Q8_0, packed, xn, tokens, rows, cols, int8_acts=int8)
+    assert_parity(y.cpu().numpy(), ref, 1e-3, "norm-fused accumulating gemv")
+    assert np.array_equal(dx.cpu().numpy(), x)      # the input row itself is not normalised in place
+    be.dev_free(h)

@@ -39,7 +39,7 @@ ABI_SYMBOLS = (
     "zen_cuda_gather_create", "zen_cuda_gather_destroy", "zen_cuda_dev_gemv_gather", "zen_cuda_dev_gather_fetch",
     "zen_cuda_dev_greedy_pick",
     "zen_cuda_dev_embed_q8_0", "zen_cuda_dev_rms_norm", "zen_cuda_dev_rope_kv_append", "zen_cuda_dev_attention", "zen_cuda_dev_silu_mul",
-    "zen_cuda_dev_advance_position",
+    "zen_cuda_dev_advance_position", "zen_cuda_dev_gemv_swiglu", "zen_cuda_dev_attention_block", "zen_cuda_dev_gemv_fused",
 )
 
 
@@ -69,13 +69,17 @@ class GemmTask(C.Structure):
     _fields_ = [("weights", C.c_void_p), ("y", C.c_void_p), ("rows", C.c_size_t)]
 
 
+class GemvFusion(C.Structure):
+    _fields_ = [("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("accumulate", C.c_int), ("gate", C.c_void_p)]
+
+
 class PickSegment(C.Structure):
     _fields_ = [("base", C.c_void_p), ("len", C.c_uint32), ("first_index", C.c_uint32), ("token_stride", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 def load_library(path: str | None = None) -> C.CDLL:
     """dlopen the backend.  Raises BackendError when it has not been built: there is no fallback."""
-    path = path or _LIB_PATH
+    path = path or os.environ.get("ZEN_CUDA_LIB") or _LIB_PATH   # ZEN_CUDA_LIB: an alternative build of the library
     if not os.path.exists(path):
         raise BackendError(f"{path} is missing: build it with `python -m zeninfer_b200.build` (needs nvcc)")
     lib = C.CDLL(path)
@@ -105,6 +109,8 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_dev_weight_bytes.restype = sz
     lib.zen_cuda_dev_gemv.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, i, vp]
     lib.zen_cuda_dev_quantize_acts.argtypes = [vp, vp, vp, sz, sz, vp]
+    lib.zen_cuda_dev_gemv_swiglu.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, vp, sz, i, vp]
+    lib.zen_cuda_dev_gemv_fused.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, i, C.POINTER(GemvFusion), vp]
     lib.zen_cuda_dev_check.argtypes = [vp]
     lib.zen_cuda_gemm_workspace_bytes.argtypes = [sz, sz]
     lib.zen_cuda_gemm_workspace_bytes.restype = sz
@@ -132,6 +138,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_dev_rope_kv_append.argtypes = [vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, i, vp, vp, sz, vp]
     lib.zen_cuda_dev_attention.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz, C.c_float, sz, sz, vp]
     lib.zen_cuda_dev_silu_mul.argtypes = [vp, vp, vp, sz, vp]
+    lib.zen_cuda_dev_attention_block.argtypes = [vp, vp, vp, vp, vp, sz, vp, vp, vp, vp, sz, sz, sz, C.c_float, sz, sz, vp]
     lib.zen_cuda_dev_advance_position.argtypes = [vp, i, vp]
     return lib
 
@@ -257,6 +264,24 @@ class Backend:
         if not self.lib.zen_cuda_dev_gemv(hs, ys, n, d_x, tokens, act_mode, stream):
             self._fail("dev_gemv")
 
+    def dev_gemv_swiglu(self, handles: Sequence[int], d_y: Sequence[int], d_gate: int, d_up: int, tokens: int, act_mode: int, stream: int = 0) -> None:
+        """dev_gemv whose input is silu(gate) * up, formed inside the product kernel (Q8_0 only)."""
+        n = len(handles)
+        hs = (C.c_void_p * n)(*handles)
+        ys = (C.c_void_p * n)(*d_y)
+        if not self.lib.zen_cuda_dev_gemv_swiglu(hs, ys, n, d_gate, d_up, tokens, act_mode, stream):
+            self._fail("dev_gemv_swiglu")
+
+    def dev_gemv_fused(self, handles: Sequence[int], d_y: Sequence[int], d_x: int, tokens: int, act_mode: int, stream: int = 0, *,
+                       norm_weight: int | None = None, norm_eps: float = 0.0, gate: int | None = None, accumulate: bool = False) -> None:
+        """dev_gemv (Q8_0) with RMSNorm or SwiGLU applied to the input inside the launch and/or y += W x."""
+        n = len(handles)
+        hs = (C.c_void_p * n)(*handles)
+        ys = (C.c_void_p * n)(*d_y)
+        f = GemvFusion(norm_weight, norm_eps, int(accumulate), gate)
+        if not self.lib.zen_cuda_dev_gemv_fused(hs, ys, n, d_x, tokens, act_mode, C.byref(f), stream):
+            self._fail("dev_gemv_fused")
+
     def gemm_workspace_bytes(self, tokens: int, columns: int) -> int:
         return int(self.lib.zen_cuda_gemm_workspace_bytes(tokens, columns))
 
@@ -355,6 +380,14 @@ class Backend:
                       max_positions: int, scale: float = 0.0, window: int = 0, stream: int = 0) -> None:
         if not self.lib.zen_cuda_dev_attention(d_q, d_k_cache, d_v_cache, d_pos, d_out, heads, kv_heads, head_dim, scale, window, max_positions, stream):
             self._fail("dev_attention")
+
+    def dev_attention_block(self, d_q: int, d_k: int, d_v: int, d_cos: int, d_sin: int, pairs: int, d_pos: int, d_k_cache: int, d_v_cache: int,
+                            d_out: int, heads: int, kv_heads: int, head_dim: int, max_positions: int, scale: float = 0.0, window: int = 0,
+                            stream: int = 0) -> None:
+        """Adjacent-pair RoPE + KV append + attention of one new token in one launch."""
+        if not self.lib.zen_cuda_dev_attention_block(d_q, d_k, d_v, d_cos, d_sin, pairs, d_pos, d_k_cache, d_v_cache, d_out, heads, kv_heads, head_dim,
+                                                     scale, window, max_positions, stream):
+            self._fail("dev_attention_block")
 
     def dev_silu_mul(self, d_gate: int, d_up: int, d_out: int, count: int, stream: int = 0) -> None:
         if not self.lib.zen_cuda_dev_silu_mul(d_gate, d_up, d_out, count, stream):

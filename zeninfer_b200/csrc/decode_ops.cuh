@@ -14,6 +14,7 @@
 // before it touches memory.  Each grid waits for its predecessor before it can finish, so completion is transitive
 // along the stream.
 #pragma once
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 
 #include <cstdint>
@@ -53,25 +54,47 @@ __device__ __forceinline__ double block_sum_double(double v, double* scratch) {
 
 // One CTA per row.  If `delta` is given the row is first updated in place, x += delta (the residual add that
 // precedes every norm but the first), then y = x * inv * weight with inv = 1 / sqrt(float(sum x^2 / n) + eps).
-// weight == nullptr: only the residual add.
-__global__ void __launch_bounds__(256) residual_rms_norm_kernel(float* __restrict__ x, const float* __restrict__ delta, const float* __restrict__ weight,
-                                                                float* __restrict__ y, uint32_t n, float eps) {
-    __shared__ double scratch[8];
+// weight == nullptr: only the residual add.  Rows whose length is a multiple of four move as 16-byte words, one or a
+// few per thread, so a 4096-wide row is two short round trips to L2.
+constexpr int kNormThreads = 1024;
+__global__ void __launch_bounds__(kNormThreads) residual_rms_norm_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                                                         const float* __restrict__ weight, float* __restrict__ y, uint32_t n, float eps) {
+    __shared__ double scratch[kNormThreads / 32];
     pdl_launch_dependents();
     pdl_wait();
     float* xr = x + static_cast<size_t>(blockIdx.x) * n;
     const float* dr = delta ? delta + static_cast<size_t>(blockIdx.x) * n : nullptr;
     float* yr = y ? y + static_cast<size_t>(blockIdx.x) * n : nullptr;
+    const bool vec = (n & 3u) == 0;
     double ss = 0.0;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = xr[i];
-        if (dr) { v += dr[i]; xr[i] = v; }
-        ss += static_cast<double>(v) * v;
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < n / 4; i += blockDim.x) {
+            float4 v = reinterpret_cast<const float4*>(xr)[i];
+            if (dr) {
+                const float4 dl = reinterpret_cast<const float4*>(dr)[i];
+                v.x += dl.x; v.y += dl.y; v.z += dl.z; v.w += dl.w;
+                reinterpret_cast<float4*>(xr)[i] = v;
+            }
+            ss += static_cast<double>(v.x) * v.x + static_cast<double>(v.y) * v.y + static_cast<double>(v.z) * v.z + static_cast<double>(v.w) * v.w;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+            float v = xr[i];
+            if (dr) { v += dr[i]; xr[i] = v; }
+            ss += static_cast<double>(v) * v;
+        }
     }
     if (!weight) return;
     const double total = block_sum_double(ss, scratch);
     const float inv = 1.0f / sqrtf(static_cast<float>(total / n) + eps);
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) yr[i] = xr[i] * inv * weight[i];
+    if (vec) {
+        for (uint32_t i = threadIdx.x; i < n / 4; i += blockDim.x) {   // a thread re-reads what it wrote itself
+            const float4 v = reinterpret_cast<const float4*>(xr)[i], w = reinterpret_cast<const float4*>(weight)[i];
+            reinterpret_cast<float4*>(yr)[i] = make_float4(v.x * inv * w.x, v.y * inv * w.y, v.z * inv * w.z, v.w * inv * w.w);
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) yr[i] = xr[i] * inv * weight[i];
+    }
 }
 
 // Rotates q (heads x D) and k (kv_heads x D) in place with the cos/sin row of the current position, then appends k
@@ -109,75 +132,191 @@ __global__ void __launch_bounds__(1024) rope_kv_append_kernel(float* __restrict_
     }
 }
 
-// Grouped-query attention for one new token: one CTA per query head (four warps).  Warps take positions in turn
-// and compute q . k[t] with four dimensions per lane; scores wait in shared memory; after the max and the
-// denominator (double) thread d accumulates out[d] = sum_t a[t] * v[t][d] over coalesced rows of V.
-// D must be a multiple of 4 and at most 4 * 32 * 2; scores for up to `max_positions` fit the dynamic shared memory.
-constexpr int kAttnThreads = 128;
-__global__ void __launch_bounds__(kAttnThreads) attention_decode_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
-                                                                          const float* __restrict__ v_cache, const int* __restrict__ pos_ptr,
-                                                                          float* __restrict__ out, uint32_t heads, uint32_t kv_heads, uint32_t D, float scale,
-                                                                          uint32_t window, uint32_t max_positions, int* error_word) {
-    extern __shared__ float scores[];
+// Grouped-query attention for one new token.  A cluster of kAttnSplit CTAs serves one query head: CTA `rank` takes
+// positions first + rank, first + rank + kAttnSplit, ... (the KV rows of a step are read by 4 x heads CTAs at once,
+// with several rows in flight per warp: at a few hundred positions the kernel is bound by memory latency, not
+// bandwidth).  Each CTA computes its scores q . k[t] * scale (a warp per position, four dimensions per lane), its
+// own maximum, exp(score - maximum), their sum in double and its share of sum_t e[t] * v[t]; rank 0 then reads the
+// other CTAs' (maximum, sum, partial output) through distributed shared memory and combines them:
+// out = sum_r w_r out_r / sum_r w_r s_r with w_r = exp(max_r - max), which is exp(score - max) / denominator applied
+// to v, the reference's formula.  D must be a multiple of 4, at most 256 and a divisor of kAttnThreads.
+constexpr int kAttnThreads = 256;
+constexpr int kAttnSplit = 4;
+constexpr int kAttnMaxD = 256;
+
+struct AttnShare {          // one CTA's contribution, read by rank 0 of the cluster
+    float out[kAttnMaxD];
+    float max_score;
+    double sum;
+};
+
+// One rotation of an adjacent pair, with every product and the sum rounded on its own as in the reference's scalar
+// loop (a fused multiply-add here would make a cached key differ in the last bit from the one used in its own step).
+__device__ __forceinline__ void rope_pair(float& a, float& b, float c, float s) {
+    const float ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)), rb = __fadd_rn(__fmul_rn(a, s), __fmul_rn(b, c));
+    a = ra; b = rb;
+}
+// dimensions base .. base+3 of a head vector: pairs base/2 and base/2 + 1 (adjacent pairing)
+__device__ __forceinline__ void rope_quad(float4& v, uint32_t base, uint32_t pairs, const float* __restrict__ c, const float* __restrict__ s) {
+    const uint32_t pr = base >> 1;
+    if (pr < pairs) rope_pair(v.x, v.y, c[pr], s[pr]);
+    if (pr + 1 < pairs) rope_pair(v.z, v.w, c[pr + 1], s[pr + 1]);
+}
+
+// kFused: q, k_new, v_new are the raw projections of the token in flight; the kernel applies the adjacent-pair rotary
+// embedding (host-built table rows of *pos_ptr) to q and k_new in registers, attends to the cache for earlier
+// positions and to k_new / v_new for the current one, and the cluster of each KV group's first query head appends the
+// rotated key and the value to the caches.  This is the reference's attention_block contract
+// (include/zen/d3d12_backend.h:247).  Other clusters never read the cache at the current position, so the append
+// races with nothing.
+template <bool kFused>
+__global__ void __cluster_dims__(kAttnSplit, 1, 1) __launch_bounds__(kAttnThreads)
+    attention_decode_kernel(const float* __restrict__ q, const float* __restrict__ k_cache_in, const float* __restrict__ v_cache_in,
+                            const int* __restrict__ pos_ptr, float* __restrict__ out, uint32_t heads, uint32_t kv_heads, uint32_t D, float scale,
+                            uint32_t window, uint32_t max_positions, int* error_word, const float* __restrict__ k_new, const float* __restrict__ v_new,
+                            const float* __restrict__ cos_t, const float* __restrict__ sin_t, uint32_t pairs, float* k_cache_out, float* v_cache_out) {
+    const float* k_cache = kFused ? k_cache_out : k_cache_in;   // fused: the caches are also written here, so no read-only promise
+    const float* v_cache = kFused ? v_cache_out : v_cache_in;
+    namespace cg = cooperative_groups;
+    extern __shared__ float scores[];                 // this CTA's positions
+    __shared__ AttnShare share;
+    __shared__ float partial[kAttnThreads];          // [position group][dimension]
     __shared__ float red[kAttnThreads / 32];
     __shared__ double scratch[8];
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t rank = cluster.block_rank();
     pdl_launch_dependents();
     pdl_wait();
     const int pos = *pos_ptr;
-    if (pos < 0 || static_cast<uint32_t>(pos) >= max_positions) {
-        if (threadIdx.x == 0 && blockIdx.x == 0) atomicExch(error_word, kErrBadPosition);
-        return;
-    }
-    const uint32_t h = blockIdx.x, kh = h / (heads / kv_heads), kw = kv_heads * D;
+    const bool bad = pos < 0 || static_cast<uint32_t>(pos) >= max_positions;
+    if (bad && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicExch(error_word, kErrBadPosition);
+    const uint32_t h = blockIdx.y, kh = h / (heads / kv_heads), kw = kv_heads * D;
     const uint32_t first = (window && static_cast<uint32_t>(pos) + 1 > window) ? static_cast<uint32_t>(pos) + 1 - window : 0u;
+    const uint32_t count = bad ? 0u : static_cast<uint32_t>(pos) + 1 - first;                 // positions attended by the head
+    const uint32_t mine = count > rank ? (count - rank + kAttnSplit - 1) / kAttnSplit : 0u;   // ... by this CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float* qh = q + static_cast<size_t>(h) * D;
+    const float* kbase = k_cache + static_cast<size_t>(first + rank) * kw + static_cast<size_t>(kh) * D;
+    const float* vbase = v_cache + static_cast<size_t>(first + rank) * kw + static_cast<size_t>(kh) * D;
+    const size_t step = static_cast<size_t>(kAttnSplit) * kw;     // floats between this CTA's consecutive positions
     // q for this lane: dimensions 4 * lane + {0..3} (+ 128 when D > 128)
+    const bool lo_on = 4u * lane < D, hi_on = 128u + 4u * lane < D;
     float4 q0 = make_float4(0.f, 0.f, 0.f, 0.f), q1 = q0;
-    if (4u * lane < D) q0 = *reinterpret_cast<const float4*>(qh + 4 * lane);
-    if (128u + 4u * lane < D) q1 = *reinterpret_cast<const float4*>(qh + 128 + 4 * lane);
-    float local_max = -INFINITY;
-    for (uint32_t t = first + warp; t <= static_cast<uint32_t>(pos); t += kAttnThreads / 32) {
-        const float* kt = k_cache + static_cast<size_t>(t) * kw + static_cast<size_t>(kh) * D;
-        float acc = 0.0f;
-        if (4u * lane < D) {
-            const float4 kk = *reinterpret_cast<const float4*>(kt + 4 * lane);
-            acc = q0.x * kk.x + q0.y * kk.y + q0.z * kk.z + q0.w * kk.w;
+    if (lo_on) q0 = *reinterpret_cast<const float4*>(qh + 4 * lane);
+    if (hi_on) q1 = *reinterpret_cast<const float4*>(qh + 128 + 4 * lane);
+    const float* cs = nullptr;
+    const float* sn = nullptr;
+    const float* knew = nullptr;
+    const float* vnew = nullptr;
+    const uint32_t last = count ? count - 1 : 0;                  // index of the current position among the attended ones
+    if (kFused && !bad) {
+        cs = cos_t + static_cast<size_t>(pos) * pairs;
+        sn = sin_t + static_cast<size_t>(pos) * pairs;
+        knew = k_new + static_cast<size_t>(kh) * D;
+        vnew = v_new + static_cast<size_t>(kh) * D;
+        if (lo_on) rope_quad(q0, 4u * lane, pairs, cs, sn);
+        if (hi_on) rope_quad(q1, 128u + 4u * lane, pairs, cs, sn);
+        // append: the cluster of the KV group's first query head, the CTA that owns the current position
+        if (h % (heads / kv_heads) == 0 && rank == last % kAttnSplit && threadIdx.x < D) {
+            const uint32_t dd = threadIdx.x, pr = dd >> 1;
+            float a = knew[dd & ~1u], b = knew[dd | 1u];
+            if (pr < pairs) rope_pair(a, b, cs[pr], sn[pr]);
+            k_cache_out[static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D + dd] = (dd & 1u) ? b : a;
+            v_cache_out[static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D + dd] = vnew[dd];
         }
-        if (128u + 4u * lane < D) {
-            const float4 kk = *reinterpret_cast<const float4*>(kt + 128 + 4 * lane);
-            acc += q1.x * kk.x + q1.y * kk.y + q1.z * kk.z + q1.w * kk.w;
+    }
+    float local_max = -INFINITY;
+    constexpr int kWarps = kAttnThreads / 32, kUnroll = 4;
+    for (uint32_t i0 = warp; i0 < mine; i0 += kWarps * kUnroll) {
+        float4 ka[kUnroll], kb[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {          // all loads first: several rows in flight per warp
+            const uint32_t i = i0 + u * kWarps;
+            ka[u] = kb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < mine) {
+                const bool fresh = kFused && rank + i * kAttnSplit == last;     // the token in flight: not in the cache yet
+                const float* kt = fresh ? knew : kbase + static_cast<size_t>(i) * step;
+                if (lo_on) ka[u] = __ldcg(reinterpret_cast<const float4*>(kt + 4 * lane));
+                if (hi_on) kb[u] = __ldcg(reinterpret_cast<const float4*>(kt + 128 + 4 * lane));
+                if (fresh) {
+                    if (lo_on) rope_quad(ka[u], 4u * lane, pairs, cs, sn);
+                    if (hi_on) rope_quad(kb[u], 128u + 4u * lane, pairs, cs, sn);
+                }
+            }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        const float sc = acc * scale;
-        if (lane == 0) scores[t - first] = sc;
-        local_max = fmaxf(local_max, sc);
+        for (int u = 0; u < kUnroll; ++u) {
+            const uint32_t i = i0 + u * kWarps;
+            float acc = q0.x * ka[u].x + q0.y * ka[u].y + q0.z * ka[u].z + q0.w * ka[u].w + q1.x * kb[u].x + q1.y * kb[u].y + q1.z * kb[u].z + q1.w * kb[u].w;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (i < mine) {
+                const float sc = acc * scale;
+                if (lane == 0) scores[i] = sc;
+                local_max = fmaxf(local_max, sc);
+            }
+        }
     }
     if (lane == 0) red[warp] = local_max;
     __syncthreads();
     float max_score = red[0];
 #pragma unroll
-    for (int w = 1; w < kAttnThreads / 32; ++w) max_score = fmaxf(max_score, red[w]);
-    const uint32_t count = static_cast<uint32_t>(pos) + 1 - first;
+    for (int w = 1; w < kWarps; ++w) max_score = fmaxf(max_score, red[w]);
     double part = 0.0;
-    for (uint32_t i = threadIdx.x; i < count; i += kAttnThreads) {
+    for (uint32_t i = threadIdx.x; i < mine; i += kAttnThreads) {
         const float e = expf(scores[i] - max_score);
         scores[i] = e;
         part += e;
     }
-    const double denom = block_sum_double(part, scratch);   // also orders the score writes before the reads below
-    if (!(denom > 0.0) || !isfinite(denom)) {
-        if (threadIdx.x == 0) atomicExch(error_word, kErrNonFinite);
-        return;
+    const double sum = block_sum_double(part, scratch);   // also orders the score writes before the reads below
+    // this CTA's share of sum_t e[t] * v[t]: thread = (position group, dimension)
+    const uint32_t groups = kAttnThreads / D, d = threadIdx.x % D, g = threadIdx.x / D;
+    float acc = 0.0f;
+    if (g < groups) {
+        for (uint32_t i0 = g; i0 < mine; i0 += groups * kUnroll) {
+            float vv[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const uint32_t i = i0 + u * groups;
+                const bool fresh = kFused && rank + i * kAttnSplit == last;
+                vv[u] = i < mine ? __ldcg(fresh ? vnew + d : vbase + static_cast<size_t>(i) * step + d) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const uint32_t i = i0 + u * groups;
+                if (i < mine) acc += scores[i] * vv[u];
+            }
+        }
     }
-    const float inv = 1.0f / static_cast<float>(denom);
-    for (uint32_t d = threadIdx.x; d < D; d += kAttnThreads) {
-        const float* vcol = v_cache + static_cast<size_t>(first) * kw + static_cast<size_t>(kh) * D + d;
-        float acc = 0.0f;
-        for (uint32_t i = 0; i < count; ++i) acc += (scores[i] * inv) * vcol[static_cast<size_t>(i) * kw];
-        out[static_cast<size_t>(h) * D + d] = acc;
+    partial[threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.x < D) {
+        float total = 0.0f;
+        for (uint32_t gg = 0; gg < groups; ++gg) total += partial[gg * D + threadIdx.x];
+        share.out[threadIdx.x] = total;
     }
+    if (threadIdx.x == 0) { share.max_score = max_score; share.sum = sum; }
+    cluster.sync();                                   // every CTA's share is complete and visible
+    if (rank == 0 && !bad) {
+        float m = -INFINITY;
+        for (uint32_t r = 0; r < kAttnSplit; ++r) m = fmaxf(m, cluster.map_shared_rank(&share, r)->max_score);
+        double denom = 0.0;
+        float w[kAttnSplit];
+        for (uint32_t r = 0; r < kAttnSplit; ++r) {
+            const AttnShare* sh = cluster.map_shared_rank(&share, r);
+            w[r] = sh->max_score == -INFINITY ? 0.0f : expf(sh->max_score - m);   // a CTA without positions contributes nothing
+            denom += static_cast<double>(w[r]) * sh->sum;
+        }
+        if (!(denom > 0.0) || !isfinite(denom)) {
+            if (threadIdx.x == 0) atomicExch(error_word, kErrNonFinite);
+        } else if (threadIdx.x < D) {
+            const float inv = 1.0f / static_cast<float>(denom);
+            float total = 0.0f;
+            for (uint32_t r = 0; r < kAttnSplit; ++r) total += w[r] * cluster.map_shared_rank(&share, r)->out[threadIdx.x];
+            out[static_cast<size_t>(h) * D + threadIdx.x] = total * inv;
+        }
+    }
+    cluster.sync();                                   // nobody leaves while rank 0 still reads its shared memory
 }
 
 // out = silu(gate) * up, silu(z) = z / (1 + exp(-z)).

@@ -35,7 +35,10 @@ constexpr int kGemmM = 128;            // weight rows per tile (TMEM lanes)
 constexpr int kGemmKTile = 128;        // K bytes per stage = 4 Q8_0 blocks
 constexpr int kGemmBlocksPerTile = kGemmKTile / 32;
 constexpr int kGemmStages = 4;
-constexpr int kGemmEpiWarps = 16;       // four per TMEM lane quadrant
+#ifndef ZK_GEMM_EPI_WARPS
+#define ZK_GEMM_EPI_WARPS 16
+#endif
+constexpr int kGemmEpiWarps = ZK_GEMM_EPI_WARPS;   // four (or two) per TMEM lane quadrant
 constexpr int kGemmSplit = kGemmEpiWarps / 4;  // the warps of a quadrant split the token columns
 constexpr int kGemmThreads = (2 + kGemmEpiWarps) * 32;
 constexpr int kGemmMaxN = 256;         // tokens per tile, a multiple of 32
@@ -156,7 +159,7 @@ __global__ void gemm_zero_split_tiles_kernel(float* __restrict__ out, uint32_t r
 template <int kNTile>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __grid_constant__ GemmParams p) {
     constexpr int kNHalf = kNTile / kGemmSplit;     // token columns per epilogue warp
-    static_assert(kNHalf == 32, "an epilogue warp takes 32 token columns");
+    static_assert(kNHalf % 32 == 0, "an epilogue warp takes whole 32-column chunks");
     constexpr uint32_t kPairs = 2;                   // TMEM accumulator buffers come in pairs: one hand-off per two blocks
     constexpr uint32_t kStageBytes = kGemmM * kGemmKTile + kNTile * kGemmKTile + kGemmBlocksPerTile * kNTile * 4;
     constexpr uint32_t kTmemCols = 2 * kPairs * kNTile;  // 512: a power of two
@@ -298,17 +301,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                             tc_fence_after_sync();
                             const bool two = j0 + 1 < nblk;
                             uint32_t v[32];
-                            tmem_ld_32x32(taddr0 + (2 * pr) * kNTile, v);
-                            tmem_ld_wait();
-                            if (!two) { tc_fence_before_sync(); __syncwarp(); if (lane == 0) mbar_arrive(&tmem_empty[pr]); }
-                            gemm_fma32(v, pack2(swf[j0], swf[j0]), sxs + j0 * kNTile * 4, acc);
-                            if (two) {
-                                tmem_ld_32x32(taddr0 + (2 * pr + 1) * kNTile, v);
+#pragma unroll
+                            for (int c = 0; c < kNHalf; c += 32) {
+                                tmem_ld_32x32(taddr0 + (2 * pr) * kNTile + c, v);
                                 tmem_ld_wait();
-                                tc_fence_before_sync();
-                                __syncwarp();
-                                if (lane == 0) mbar_arrive(&tmem_empty[pr]);   // both buffers of the pair have been read
-                                gemm_fma32(v, pack2(swf[j0 + 1], swf[j0 + 1]), sxs + (j0 + 1) * kNTile * 4, acc);
+                                if (!two && c + 32 == kNHalf) { tc_fence_before_sync(); __syncwarp(); if (lane == 0) mbar_arrive(&tmem_empty[pr]); }
+                                gemm_fma32(v, pack2(swf[j0], swf[j0]), sxs + (j0 * kNTile + c) * 4, acc + c / 2);
+                            }
+                            if (two) {
+#pragma unroll
+                                for (int c = 0; c < kNHalf; c += 32) {
+                                    tmem_ld_32x32(taddr0 + (2 * pr + 1) * kNTile + c, v);
+                                    tmem_ld_wait();
+                                    if (c + 32 == kNHalf) {   // both buffers of the pair have been read
+                                        tc_fence_before_sync();
+                                        __syncwarp();
+                                        if (lane == 0) mbar_arrive(&tmem_empty[pr]);
+                                    }
+                                    gemm_fma32(v, pack2(swf[j0 + 1], swf[j0 + 1]), sxs + ((j0 + 1) * kNTile + c) * 4, acc + c / 2);
+                                }
                             }
                             ++pair;
                         }

@@ -69,6 +69,10 @@ constexpr uint32_t kQ8StageScaleBytes = kTeamWarps * kGemvSegBlocks * 2;
 constexpr uint32_t kQ8StageBytes = kQ8StageCodeBytes + kQ8StageScaleBytes;
 constexpr uint32_t kL2PrefetchCap = 160 * 1024;     // bytes of the slice beyond the ring that are pulled into L2 up front
 
+constexpr uint32_t kGemvFlagSwiglu = 1u;      // input = silu(x_gate) * x
+constexpr uint32_t kGemvFlagNorm = 2u;        // input = RMSNorm(x) * norm_weight, formed in the prologue
+constexpr uint32_t kGemvFlagAccumulate = 4u;  // y += W x instead of y = W x (the residual add)
+
 struct GemvTask {
     const uint8_t* codes;    // [rows][K] int8
     const __half* scales;    // [rows][nbp]
@@ -87,9 +91,12 @@ struct GemvParams {
     uint32_t total_rows;     // over all tasks
     uint32_t ntasks;
     uint32_t K;              // columns; nb = K / 32 blocks per row, scale pitch nb rounded up to 8, nseg = ceil(nb / 128)
-    uint32_t pad;
+    uint32_t flags;          // kGemvFlag*: what happens to the input while it is quantised, and whether y accumulates
     GemvTask task[kMaxTasks];
     PeerGather gather;       // world == 0: outputs go to task[].y only
+    const float* x_gate;     // [batch][K] fp32, read only with kGemvFlagSwiglu (a cold parameter line, touched by fused launches only)
+    const float* norm_weight;  // [K] fp32, read only with kGemvFlagNorm
+    float norm_eps;
 #ifdef ZK_TRACE
     unsigned long long* trace;  // [grid][16] phase stamps (profiling builds only)
 #endif
@@ -112,7 +119,8 @@ __host__ __device__ inline size_t gemv_q8_0_smem_bytes(uint32_t nseg, int batch,
     return static_cast<size_t>(kGemvStages) * kQ8StageBytes        // weight ring
            + static_cast<size_t>(batch) * digits * kpad_blocks * 32  // activation codes
            + static_cast<size_t>(batch) * kpad_blocks * 4            // activation scales
-           + 2 * kGemvStages * 8 + 16;                               // barriers + abort word
+           + 2 * kGemvStages * 8 + 16                                // barriers + abort word
+           + kMaxTasks * kGemvWarps * sizeof(double);                // per-warp sums of squares of a fused RMSNorm
 }
 
 // The slice of the launch's concatenated row space that CTA `cta` of `n` owns.
@@ -173,7 +181,8 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
     uint64_t* full = reinterpret_cast<uint64_t*>(xscale + static_cast<size_t>(kBatch) * kpad_blocks);
     uint64_t* empty = full + kGemvStages;
     volatile int* abort_word = reinterpret_cast<volatile int*>(empty + kGemvStages);
-    float* stash = reinterpret_cast<float*>(empty + kGemvStages + 2);   // gather only: [batch][rows of this CTA's slice]
+    double* norm_part = reinterpret_cast<double*>(empty + kGemvStages + 2);   // fused RMSNorm: [batch][consumer warp]
+    float* stash = reinterpret_cast<float*>(norm_part + kMaxTasks * kGemvWarps);   // gather only: [batch][rows of this CTA's slice]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef ZK_TRACE
@@ -337,7 +346,34 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
     // covers 128 blocks with two 128-bit loads per lane: one pass for K = 4096.
     {
         const uint32_t quad = static_cast<uint32_t>(lane) >> 2, part = static_cast<uint32_t>(lane) & 3;
+        // Fused RMSNorm (rms_norm, src/adapters/dense_transformer_runtime.cpp:117-125): a first pass over the row sums the
+        // squares in double, warp by warp and then across the consumer warps in a fixed order; the quantising pass below
+        // scales what it loads by inv * weight.  Every CTA repeats this for itself: the row is 16 KB in L2.
+        if (p.flags & kGemvFlagNorm) {
+            for (int t = 0; t < kBatch; ++t) {
+                double ss = 0.0;
+                for (uint32_t b0 = warp * 8; b0 < nb; b0 += kGemvWarps * 8) {
+                    const uint32_t b = b0 + quad;
+                    if (b < nb) {
+                        const float4* src = reinterpret_cast<const float4*>(x_src + static_cast<size_t>(t) * p.K + b * 32 + part * 8);
+                        const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
+                        ss += static_cast<double>(lo.x) * lo.x + static_cast<double>(lo.y) * lo.y + static_cast<double>(lo.z) * lo.z + static_cast<double>(lo.w) * lo.w
+                            + static_cast<double>(hi.x) * hi.x + static_cast<double>(hi.y) * hi.y + static_cast<double>(hi.z) * hi.z + static_cast<double>(hi.w) * hi.w;
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) norm_part[t * kGemvWarps + warp] = ss;
+            }
+            asm volatile("bar.sync 1, %0;" ::"r"(kGemvWarps * 32) : "memory");
+        }
         for (int t = 0; t < kBatch; ++t) {
+            float inv_norm = 1.0f;
+            if (p.flags & kGemvFlagNorm) {
+                double total = 0.0;
+                for (int w = 0; w < kGemvWarps; ++w) total += norm_part[t * kGemvWarps + w];
+                inv_norm = 1.0f / sqrtf(static_cast<float>(total / p.K) + p.norm_eps);
+            }
             for (uint32_t b0 = warp * 8; b0 < nb; b0 += kGemvWarps * 8) {  // warp-uniform trip count: the quantiser shuffles
                 const uint32_t b = b0 + quad;
                 const bool live = b < nb;
@@ -345,7 +381,23 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
                 const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
                 // L2 is the point of coherence for what earlier kernels and peers wrote: bypass L1
                 const float4 lo = live ? __ldcg(src) : zero, hi = live ? __ldcg(src + 1) : zero;
-                const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+                if (p.flags & kGemvFlagNorm) {
+                    const float4* wsrc = reinterpret_cast<const float4*>(p.norm_weight + b * 32 + part * 8);
+                    const float4 wlo = live ? __ldg(wsrc) : zero, whi = live ? __ldg(wsrc + 1) : zero;
+                    const float nw[8] = {wlo.x, wlo.y, wlo.z, wlo.w, whi.x, whi.y, whi.z, whi.w};
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = v[e] * inv_norm * nw[e];   // x * inv * weight, the reference's order
+                }
+                if (p.flags & kGemvFlagSwiglu) {
+                    // SwiGLU fused into the load: silu(gate) * up, silu(z) = z / (1 + exp(-z))
+                    // (silu_mul, src/adapters/dense_transformer_runtime.cpp:193-199)
+                    const float4* gsrc = reinterpret_cast<const float4*>(p.x_gate + static_cast<size_t>(t) * p.K + b * 32 + part * 8);
+                    const float4 glo = live ? __ldcg(gsrc) : zero, ghi = live ? __ldcg(gsrc + 1) : zero;
+                    const float g[8] = {glo.x, glo.y, glo.z, glo.w, ghi.x, ghi.y, ghi.z, ghi.w};
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = (g[e] / (1.0f + expf(-g[e]))) * v[e];
+                }
                 uint2 c1, c2;
                 const float d = quantise_block_quad(v, c1, c2);
                 if (!live) continue;
@@ -468,7 +520,10 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
                 float v = acc[tk];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0 && t.y) t.y[static_cast<size_t>(tk) * t.rows + row] = v;
+                if (lane == 0 && t.y) {
+                    float* dst = t.y + static_cast<size_t>(tk) * t.rows + row;
+                    *dst = (p.flags & kGemvFlagAccumulate) ? *dst + v : v;
+                }
                 if (lane == 0 && p.gather.world) stash[static_cast<size_t>(tk) * n_mine + (t.first_row + row - r_first)] = v;
             }
         }

@@ -434,7 +434,8 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
 // Enqueues one batched GEMV launch: `count` tensors (same format, same K) times `tokens` (<= 8)
 // activation rows.  Device pointers throughout.
 bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
-                  size_t tokens, int act_mode, cudaStream_t st, const zk::PeerGather* gather = nullptr) {
+                  size_t tokens, int act_mode, cudaStream_t st, const zk::PeerGather* gather = nullptr, const float* d_gate = nullptr,
+                  const float* d_norm_weight = nullptr, float norm_eps = 0.0f, bool accumulate = false) {
     if (!count || count > zk::kMaxTasks || !tokens || tokens > 8 || (!d_x && !gather)) return set_error(s, "gemv: bad batch");
     if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: bad activation mode");
     zk::GemvParams p{};
@@ -457,8 +458,13 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
     }
     if (w[0]->format != ZEN_CUDA_Q8_0) {
         if (act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: Q4_0 and Q6_K take fp32-equivalent activations only");
+        if (d_gate || d_norm_weight || accumulate) return set_error(s, "gemv: fused inputs and accumulation are Q8_0 paths");
         return enqueue_gemv_kq(s, w, d_y, count, d_x, tokens, st, gather);
     }
+    if (d_gate && d_norm_weight) return set_error(s, "gemv: a fused input is either SwiGLU or RMSNorm");
+    if (d_gate) { p.flags |= zk::kGemvFlagSwiglu; p.x_gate = d_gate; }
+    if (d_norm_weight) { p.flags |= zk::kGemvFlagNorm; p.norm_weight = d_norm_weight; p.norm_eps = norm_eps; }
+    if (accumulate) p.flags |= zk::kGemvFlagAccumulate;
     p.ntasks = static_cast<uint32_t>(count);
     p.total_rows = total_rows;
     p.x = d_x;
@@ -1008,6 +1014,25 @@ int zen_cuda_dev_gemv(const zen_cuda_weights* const* w, float* const* d_y, size_
     return enqueue_gemv(s, w, d_y, count, d_x, tokens, act_mode, stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
 }
 
+int zen_cuda_dev_gemv_swiglu(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_gate, const float* d_up,
+                             size_t tokens, int act_mode, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!w || !d_y || !d_gate || !d_up) return set_error(s, "dev_gemv_swiglu: bad arguments") ? 1 : 0;
+    return enqueue_gemv(s, w, d_y, count, d_up, tokens, act_mode, stream ? static_cast<cudaStream_t>(stream) : s.stream, nullptr, d_gate) ? 1 : 0;
+}
+
+int zen_cuda_dev_gemv_fused(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x, size_t tokens, int act_mode,
+                            const zen_cuda_gemv_fusion* fusion, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!w || !d_y || !d_x || !fusion) return set_error(s, "dev_gemv_fused: bad arguments") ? 1 : 0;
+    return enqueue_gemv(s, w, d_y, count, d_x, tokens, act_mode, stream ? static_cast<cudaStream_t>(stream) : s.stream, nullptr, fusion->gate,
+                        fusion->norm_weight, fusion->norm_eps, fusion->accumulate != 0) ? 1 : 0;
+}
+
 size_t zen_cuda_gemm_workspace_bytes(size_t tokens, size_t columns) { return gemm_ws_bytes(tokens, columns); }
 
 int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x, size_t tokens,
@@ -1226,7 +1251,7 @@ int zen_cuda_dev_embed_q8_0(const zen_cuda_weights* w, const int64_t* d_token, f
 int zen_cuda_dev_rms_norm(float* d_x, const float* d_delta, const float* d_weight, float* d_y, size_t n, size_t rows, float eps, void* stream) {
     ZC_DEV_ENTER("dev_rms_norm");
     if (!d_x || !n || !rows || rows > 65535 || (d_weight && !d_y) || (!d_weight && !d_delta)) return set_error(s, "dev_rms_norm: bad arguments") ? 1 : 0;
-    const cudaError_t e = launch_pdl(s, zk::residual_rms_norm_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, st, d_x, d_delta, d_weight, d_y,
+    const cudaError_t e = launch_pdl(s, zk::residual_rms_norm_kernel, dim3(static_cast<unsigned>(rows)), dim3(zk::kNormThreads), 0, st, d_x, d_delta, d_weight, d_y,
                                      static_cast<uint32_t>(n), eps);
     ZC_DEV_LEAVE(e);
 }
@@ -1244,26 +1269,56 @@ int zen_cuda_dev_rope_kv_append(float* d_q, float* d_k, const float* d_v, const 
     ZC_DEV_LEAVE(e);
 }
 
+namespace {
+// Shared by the two attention entry points.  fused: q/k/v are the raw projections, rope and the cache append happen inside.
+bool enqueue_attention(State& s, cudaStream_t st, bool fused, const float* d_q, const float* d_k, const float* d_v, const float* d_cos, const float* d_sin,
+                       size_t pairs, const int* d_pos, float* d_k_cache, float* d_v_cache, float* d_out, size_t heads, size_t kv_heads, size_t head_dim,
+                       float scale, size_t window, size_t max_positions) {
+    if (!d_q || !d_k_cache || !d_v_cache || !d_pos || !d_out || !heads || !kv_heads || heads % kv_heads || !head_dim || head_dim % 4 || head_dim > 256 ||
+        !max_positions || (fused && (!d_k || !d_v || !d_cos || !d_sin || 2 * pairs > head_dim)))
+        return set_error(s, "attention: bad arguments");
+    if (zk::kAttnThreads % head_dim) return set_error(s, "attention: head_dim must divide 256");
+    const size_t span = window ? std::min(window, max_positions) : max_positions;
+    const size_t smem = ((span + zk::kAttnSplit - 1) / zk::kAttnSplit) * sizeof(float);   // a CTA of the cluster holds its own positions' scores
+    if (smem + 4096 > s.smem_optin) return set_error(s, "attention: the attended span does not fit shared memory");
+    static size_t configured[2] = {40 * 1024, 40 * 1024};
+    if (smem > configured[fused]) {
+        const cudaError_t ea = fused ? cudaFuncSetAttribute(zk::attention_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))
+                                     : cudaFuncSetAttribute(zk::attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (ea != cudaSuccess) return set_error(s, "attention: shared memory opt-in failed");
+        configured[fused] = smem;
+    }
+    if (scale == 0.0f) scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+    const dim3 grid(zk::kAttnSplit, static_cast<unsigned>(heads)), block(zk::kAttnThreads);
+    const cudaError_t e =
+        fused ? launch_pdl(s, zk::attention_decode_kernel<true>, grid, block, smem, st, d_q, static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
+                           d_pos, d_out, static_cast<uint32_t>(heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(head_dim), scale,
+                           static_cast<uint32_t>(window), static_cast<uint32_t>(max_positions), s.d_error, d_k, d_v, d_cos, d_sin, static_cast<uint32_t>(pairs),
+                           d_k_cache, d_v_cache)
+              : launch_pdl(s, zk::attention_decode_kernel<false>, grid, block, smem, st, d_q, static_cast<const float*>(d_k_cache),
+                           static_cast<const float*>(d_v_cache), d_pos, d_out, static_cast<uint32_t>(heads), static_cast<uint32_t>(kv_heads),
+                           static_cast<uint32_t>(head_dim), scale, static_cast<uint32_t>(window), static_cast<uint32_t>(max_positions), s.d_error,
+                           static_cast<const float*>(nullptr), static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
+                           static_cast<const float*>(nullptr), 0u, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+    ++s.stats.dispatches;
+    if (e != cudaSuccess) return set_error(s, "attention: launch failed");
+    return true;
+}
+}  // namespace
+
 int zen_cuda_dev_attention(const float* d_q, const float* d_k_cache, const float* d_v_cache, const int* d_pos, float* d_out, size_t heads,
                            size_t kv_heads, size_t head_dim, float scale, size_t window, size_t max_positions, void* stream) {
     ZC_DEV_ENTER("dev_attention");
-    if (!d_q || !d_k_cache || !d_v_cache || !d_pos || !d_out || !heads || !kv_heads || heads % kv_heads || !head_dim || head_dim % 4 || head_dim > 256 ||
-        !max_positions)
-        return set_error(s, "dev_attention: bad arguments") ? 1 : 0;
-    const size_t span = window ? std::min(window, max_positions) : max_positions;
-    const size_t smem = span * sizeof(float);
-    if (smem + 1024 > s.smem_optin) return set_error(s, "dev_attention: the attended span does not fit shared memory") ? 1 : 0;
-    static size_t configured = 48 * 1024;
-    if (smem > configured) {
-        if (cudaFuncSetAttribute(zk::attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
-            return set_error(s, "dev_attention: shared memory opt-in failed") ? 1 : 0;
-        configured = smem;
-    }
-    if (scale == 0.0f) scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
-    const cudaError_t e = launch_pdl(s, zk::attention_decode_kernel, dim3(static_cast<unsigned>(heads)), dim3(zk::kAttnThreads), smem, st,
-        d_q, d_k_cache, d_v_cache, d_pos, d_out, static_cast<uint32_t>(heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(head_dim), scale,
-        static_cast<uint32_t>(window), static_cast<uint32_t>(max_positions), s.d_error);
-    ZC_DEV_LEAVE(e);
+    return enqueue_attention(s, st, false, d_q, nullptr, nullptr, nullptr, nullptr, 0, d_pos, const_cast<float*>(d_k_cache), const_cast<float*>(d_v_cache), d_out,
+                             heads, kv_heads, head_dim, scale, window, max_positions) ? 1 : 0;
+}
+
+int zen_cuda_dev_attention_block(const float* d_q, const float* d_k, const float* d_v, const float* d_cos, const float* d_sin, size_t pairs, const int* d_pos,
+                                 float* d_k_cache, float* d_v_cache, float* d_out, size_t heads, size_t kv_heads, size_t head_dim, float scale, size_t window,
+                                 size_t max_positions, void* stream) {
+    ZC_DEV_ENTER("dev_attention_block");
+    return enqueue_attention(s, st, true, d_q, d_k, d_v, d_cos, d_sin, pairs, d_pos, d_k_cache, d_v_cache, d_out, heads, kv_heads, head_dim, scale, window,
+                             max_positions) ? 1 : 0;
 }
 
 int zen_cuda_dev_silu_mul(const float* d_gate, const float* d_up, float* d_out, size_t count, void* stream) {

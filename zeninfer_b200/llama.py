@@ -93,9 +93,12 @@ class LlamaDecoder:
     """Holds the resident model and the step's device buffers.  `tensors` yields (name, array, is_matrix) as
     synthetic_tensors does; matrices must be Q8_0 raw blocks [rows, row_bytes]."""
 
-    def __init__(self, backend: Backend, cfg: LlamaConfig, tensors, act_mode: int = ACT_INT8, max_positions: int | None = None, device=None):
+    def __init__(self, backend: Backend, cfg: LlamaConfig, tensors, act_mode: int = ACT_INT8, max_positions: int | None = None, device=None,
+                 fused: bool = True):
+        """fused: fold RMSNorm, SwiGLU and the residual adds into the projection launches (5 launches per layer);
+        otherwise every operator is its own launch (9 per layer).  Same arithmetic either way."""
         import torch
-        self.torch, self.be, self.cfg, self.act_mode = torch, backend, cfg, act_mode
+        self.torch, self.be, self.cfg, self.act_mode, self.fused = torch, backend, cfg, act_mode, fused
         self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.max_positions = max_positions or cfg.context
         self.stream = torch.cuda.Stream(device=self.dev)
@@ -130,28 +133,42 @@ class LlamaDecoder:
     def _enqueue_layers(self) -> None:
         be, cfg, st, mode = self.be, self.cfg, self.stream.cuda_stream, self.act_mode
         P = lambda t: t.data_ptr()
+        E, eps = cfg.embedding, cfg.rms_eps
         be.dev_embed_q8_0(self.h["token_embd.weight"], P(self.token), P(self.x), st)
-        be.dev_rms_norm(P(self.x), None, P(self.norm["blk.0.attn_norm.weight"]), P(self.xn), cfg.embedding, 1, cfg.rms_eps, st)
+        if not self.fused:
+            be.dev_rms_norm(P(self.x), None, P(self.norm["blk.0.attn_norm.weight"]), P(self.xn), E, 1, eps, st)
         for layer in range(cfg.layers):
             p = f"blk.{layer}."
-            be.dev_gemv([self.h[p + "attn_q.weight"], self.h[p + "attn_k.weight"], self.h[p + "attn_v.weight"]],
-                        [P(self.q), P(self.k), P(self.v)], P(self.xn), 1, mode, st)
-            be.dev_rope_kv_append(P(self.q), P(self.k), P(self.v), P(self.cos), P(self.sin), P(self.pos), cfg.heads, cfg.kv_heads, cfg.head_dim,
-                                  cfg.head_dim // 2, True, P(self.k_cache[layer]), P(self.v_cache[layer]), self.max_positions, st)
-            be.dev_attention(P(self.q), P(self.k_cache[layer]), P(self.v_cache[layer]), P(self.pos), P(self.att), cfg.heads, cfg.kv_heads,
-                             cfg.head_dim, self.max_positions, 0.0, 0, st)
-            be.dev_gemv([self.h[p + "attn_output.weight"]], [P(self.tmp)], P(self.att), 1, mode, st)
-            be.dev_rms_norm(P(self.x), P(self.tmp), P(self.norm[p + "ffn_norm.weight"]), P(self.xn), cfg.embedding, 1, cfg.rms_eps, st)
-            be.dev_gemv([self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]], [P(self.gate), P(self.up)], P(self.xn), 1, mode, st)
-            be.dev_silu_mul(P(self.gate), P(self.up), P(self.hid), cfg.ffn, st)
-            be.dev_gemv([self.h[p + "ffn_down.weight"]], [P(self.tmp)], P(self.hid), 1, mode, st)
-            nxt = self.norm[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < cfg.layers else self.norm["output_norm.weight"]
-            be.dev_rms_norm(P(self.x), P(self.tmp), P(nxt), P(self.xn), cfg.embedding, 1, cfg.rms_eps, st)
+            qkv = [self.h[p + "attn_q.weight"], self.h[p + "attn_k.weight"], self.h[p + "attn_v.weight"]]
+            qkv_out = [P(self.q), P(self.k), P(self.v)]
+            if self.fused:
+                be.dev_gemv_fused(qkv, qkv_out, P(self.x), 1, mode, st, norm_weight=P(self.norm[p + "attn_norm.weight"]), norm_eps=eps)
+            else:
+                be.dev_gemv(qkv, qkv_out, P(self.xn), 1, mode, st)
+            be.dev_attention_block(P(self.q), P(self.k), P(self.v), P(self.cos), P(self.sin), cfg.head_dim // 2, P(self.pos), P(self.k_cache[layer]),
+                                   P(self.v_cache[layer]), P(self.att), cfg.heads, cfg.kv_heads, cfg.head_dim, self.max_positions, 0.0, 0, st)
+            gate_up = [self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]]
+            if self.fused:
+                be.dev_gemv_fused([self.h[p + "attn_output.weight"]], [P(self.x)], P(self.att), 1, mode, st, accumulate=True)         # x += o(att)
+                be.dev_gemv_fused(gate_up, [P(self.gate), P(self.up)], P(self.x), 1, mode, st, norm_weight=P(self.norm[p + "ffn_norm.weight"]), norm_eps=eps)
+                be.dev_gemv_fused([self.h[p + "ffn_down.weight"]], [P(self.x)], P(self.up), 1, mode, st, gate=P(self.gate), accumulate=True)  # x += down(silu(gate) * up)
+            else:
+                be.dev_gemv([self.h[p + "attn_output.weight"]], [P(self.tmp)], P(self.att), 1, mode, st)
+                be.dev_rms_norm(P(self.x), P(self.tmp), P(self.norm[p + "ffn_norm.weight"]), P(self.xn), E, 1, eps, st)
+                be.dev_gemv(gate_up, [P(self.gate), P(self.up)], P(self.xn), 1, mode, st)
+                be.dev_silu_mul(P(self.gate), P(self.up), P(self.hid), cfg.ffn, st)
+                be.dev_gemv([self.h[p + "ffn_down.weight"]], [P(self.tmp)], P(self.hid), 1, mode, st)
+                nxt = self.norm[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < cfg.layers else self.norm["output_norm.weight"]
+                be.dev_rms_norm(P(self.x), P(self.tmp), P(nxt), P(self.xn), E, 1, eps, st)
         be.dev_advance_position(P(self.pos), 1, st)
 
     def _enqueue_head(self) -> None:
         be, st = self.be, self.stream.cuda_stream
-        be.dev_gemv([self.h["output.weight"]], [self.logits.data_ptr()], self.xn.data_ptr(), 1, self.act_mode, st)
+        if self.fused:
+            be.dev_gemv_fused([self.h["output.weight"]], [self.logits.data_ptr()], self.x.data_ptr(), 1, self.act_mode, st,
+                              norm_weight=self.norm["output_norm.weight"].data_ptr(), norm_eps=self.cfg.rms_eps)
+        else:
+            be.dev_gemv([self.h["output.weight"]], [self.logits.data_ptr()], self.xn.data_ptr(), 1, self.act_mode, st)
         be.dev_greedy_pick([(self.logits.data_ptr(), self.cfg.vocab, 0, self.cfg.vocab)], 1, self.token.data_ptr(), st)
 
     def capture(self) -> None:
