@@ -690,7 +690,7 @@ def run_decode(args) -> None:
                 yield name, (1.0 + 0.02 * torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)).cpu().numpy(), False
 
     t0 = time.perf_counter()
-    dec = LlamaDecoder(be, cfg, tensors(), act_mode=ACT_INT8, max_positions=1024)
+    dec = LlamaDecoder(be, cfg, tensors(), act_mode=ACT_INT8, max_positions=1024, fused=args.fuse)
     load_s = time.perf_counter() - t0
     dec.capture()
     prompt = np.random.default_rng(6).integers(0, cfg.vocab, size=prompt_len, dtype=np.int64)
@@ -759,14 +759,16 @@ def run_decode(args) -> None:
                              f"worker policy), scaled to 32 layers + lm_head by bytes; attention, norms and sampling not included, so an upper bound "
                              f"for the reference's decode rate on these cores"}
 
-    launches_per_step = 1 + 5 * cfg.layers + 1 + 1 + 2   # embed, per layer q|k|v + attention block + o + gate|up + down, advance, lm_head, pick (2)
+    fn, fs, fr = ("n" in dec.fuse), ("s" in dec.fuse), ("r" in dec.fuse)
+    per_layer = 5 + (0 if (fn and fr) else 2) + (0 if fs else 1)   # q|k|v, attention block, o, gate|up, down + norm / residual / SwiGLU launches
+    launches_per_step = 1 + (0 if fn else 1) + per_layer * cfg.layers + 1 + 1 + 2   # embed, layers, advance, lm_head, pick (2)
     print(json.dumps({
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": "greedy decode, random-init Llama-3-8B shape in Q8_0 (config 4): 32 layers, d 4096, 32/8 heads of 128, ffn 14336, "
                                f"vocab 128256; prompt of {prompt_len} random ids (consumed token by token, untimed), then {warm} + {steps} decode steps",
                    "activations": "int8 (bit-exact reference codes)", "l2": "inputs larger than L2: 8.5 GB of weights stream per token",
-                   "launch": f"two CUDA graphs per token, {launches_per_step} kernel launches", "weights": "torch.randn on the device, seed 6, N(0, 0.02)",
+                   "launch": f"two CUDA graphs per token, {launches_per_step} kernel launches (folded into the projections: '{dec.fuse}')", "weights": "torch.randn on the device, seed 6, N(0, 0.02)",
                    "load_s": load_s},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
                      "kernel": "whole token step (projections through gemv_q8_0_kernel<1,1>)", "launch_us": ms * 1e3 / steps,
@@ -792,6 +794,7 @@ def main() -> None:
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: how the output shards are all-gathered after each product -- by the product kernel itself "
                          "(peer stores over NVLink, the default) or by an NCCL all-gather launched after it")
+    ap.add_argument("--fuse", default="nr", help="workload decode: operators folded into the projection launches (letters n, s, r; see LlamaDecoder)")
     ap.add_argument("--prompt-len", type=int, default=512, help="workload decode: prompt tokens consumed before the timed steps")
     ap.add_argument("--min-warmup", type=int, default=1500,
                     help="floor on the warm-up step count of the decode workload (about 0.3 s, so the clock sampler is up before "

@@ -141,7 +141,7 @@ def test_silu_mul(be):
     assert_parity(out.cpu().numpy(), (g.astype(np.float64) / (1 + np.exp(-g.astype(np.float64)))) * u, 1e-6, "silu_mul")
 
 
-@pytest.mark.parametrize("fused", [False, True])
+@pytest.mark.parametrize("fused", [False, True, "r", "nr", "s"])
 @pytest.mark.parametrize("graphs", [False, True])
 def test_generation_matches_the_reference(be, golden, graphs, fused):
     cfg, meta, prompt, ids, logits = golden
@@ -271,3 +271,19 @@ def test_gemv_with_fused_rms_norm_and_accumulate(be, zo, mode, int8, tokens):
     assert_parity(y.cpu().numpy(), ref, 1e-3, "norm-fused accumulating gemv")
     assert np.array_equal(dx.cpu().numpy(), x)      # the input row itself is not normalised in place
     be.dev_free(h)
+
+
+def test_decoder_loaded_from_a_gguf_file(be, golden, tmp_path):
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+    from make_llama_golden import write_gguf
+    cfg, meta, prompt, ids, logits = golden
+    path = str(tmp_path / "tiny.gguf")
+    write_gguf(path, cfg, synthetic_tensors(cfg, meta["seed"], meta["weight_std"]))
+    dec = LlamaDecoder.from_gguf(be, path, act_mode=ACT_FP32)      # tensors stream from the file mapping to the device
+    try:
+        assert dec.cfg.layers == cfg.layers and dec.cfg.vocab == cfg.vocab
+        assert dec.generate(prompt.tolist(), meta["max_new"]) == ids.tolist()
+        assert_parity(dec.last_logits(), logits, 1e-3, "last logits")
+    finally:
+        dec.close()

@@ -133,15 +133,15 @@ __global__ void __launch_bounds__(1024) rope_kv_append_kernel(float* __restrict_
 }
 
 // Grouped-query attention for one new token.  A cluster of kAttnSplit CTAs serves one query head: CTA `rank` takes
-// positions first + rank, first + rank + kAttnSplit, ... (the KV rows of a step are read by 4 x heads CTAs at once,
-// with several rows in flight per warp: at a few hundred positions the kernel is bound by memory latency, not
-// bandwidth).  Each CTA computes its scores q . k[t] * scale (a warp per position, four dimensions per lane), its
+// positions first + rank, first + rank + kAttnSplit, ... (the KV rows of a step are read by 8 x heads CTAs at once,
+// with several rows in flight per warp, and the value rows are pulled into L2 while the scores are computed: at a few
+// hundred positions the kernel is bound by memory latency, not bandwidth).  Each CTA computes its scores q . k[t] * scale (a warp per position, four dimensions per lane), its
 // own maximum, exp(score - maximum), their sum in double and its share of sum_t e[t] * v[t]; rank 0 then reads the
 // other CTAs' (maximum, sum, partial output) through distributed shared memory and combines them:
 // out = sum_r w_r out_r / sum_r w_r s_r with w_r = exp(max_r - max), which is exp(score - max) / denominator applied
-// to v, the reference's formula.  D must be a multiple of 4, at most 256 and a divisor of kAttnThreads.
+// to v, the reference's formula.  D must be a multiple of 4 and at most 256.
 constexpr int kAttnThreads = 256;
-constexpr int kAttnSplit = 4;
+constexpr int kAttnSplit = 8;
 constexpr int kAttnMaxD = 256;
 
 struct AttnShare {          // one CTA's contribution, read by rank 0 of the cluster
@@ -180,7 +180,7 @@ __global__ void __cluster_dims__(kAttnSplit, 1, 1) __launch_bounds__(kAttnThread
     namespace cg = cooperative_groups;
     extern __shared__ float scores[];                 // this CTA's positions
     __shared__ AttnShare share;
-    __shared__ float partial[kAttnThreads];          // [position group][dimension]
+    __shared__ __align__(16) float partial[(kAttnThreads / 32) * kAttnMaxD];   // [warp][dimension]
     __shared__ float red[kAttnThreads / 32];
     __shared__ double scratch[8];
     cg::cluster_group cluster = cg::this_cluster();
@@ -238,6 +238,8 @@ __global__ void __cluster_dims__(kAttnSplit, 1, 1) __launch_bounds__(kAttnThread
                 const float* kt = fresh ? knew : kbase + static_cast<size_t>(i) * step;
                 if (lo_on) ka[u] = __ldcg(reinterpret_cast<const float4*>(kt + 4 * lane));
                 if (hi_on) kb[u] = __ldcg(reinterpret_cast<const float4*>(kt + 128 + 4 * lane));
+                if (!fresh && lane * 32u < D)    // one lane per 128-byte line of the position's value row
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(vbase + static_cast<size_t>(i) * step + lane * 32));
                 if (fresh) {
                     if (lo_on) rope_quad(ka[u], 4u * lane, pairs, cs, sn);
                     if (hi_on) rope_quad(kb[u], 128u + 4u * lane, pairs, cs, sn);
@@ -269,30 +271,36 @@ __global__ void __cluster_dims__(kAttnSplit, 1, 1) __launch_bounds__(kAttnThread
         part += e;
     }
     const double sum = block_sum_double(part, scratch);   // also orders the score writes before the reads below
-    // this CTA's share of sum_t e[t] * v[t]: thread = (position group, dimension)
-    const uint32_t groups = kAttnThreads / D, d = threadIdx.x % D, g = threadIdx.x / D;
-    float acc = 0.0f;
-    if (g < groups) {
-        for (uint32_t i0 = g; i0 < mine; i0 += groups * kUnroll) {
-            float vv[kUnroll];
+    // this CTA's share of sum_t e[t] * v[t]: a warp per position (in turn), four dimensions per lane as for the keys
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    for (uint32_t i0 = warp; i0 < mine; i0 += kWarps * kUnroll) {
+        float4 va[kUnroll], vb[kUnroll];
 #pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                const uint32_t i = i0 + u * groups;
+        for (int u = 0; u < kUnroll; ++u) {
+            const uint32_t i = i0 + u * kWarps;
+            va[u] = vb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < mine) {
                 const bool fresh = kFused && rank + i * kAttnSplit == last;
-                vv[u] = i < mine ? __ldcg(fresh ? vnew + d : vbase + static_cast<size_t>(i) * step + d) : 0.0f;
-            }
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                const uint32_t i = i0 + u * groups;
-                if (i < mine) acc += scores[i] * vv[u];
+                const float* vt = fresh ? vnew : vbase + static_cast<size_t>(i) * step;
+                if (lo_on) va[u] = __ldcg(reinterpret_cast<const float4*>(vt + 4 * lane));
+                if (hi_on) vb[u] = __ldcg(reinterpret_cast<const float4*>(vt + 128 + 4 * lane));
             }
         }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const uint32_t i = i0 + u * kWarps;
+            const float e = i < mine ? scores[i] : 0.0f;
+            a0.x += e * va[u].x; a0.y += e * va[u].y; a0.z += e * va[u].z; a0.w += e * va[u].w;
+            a1.x += e * vb[u].x; a1.y += e * vb[u].y; a1.z += e * vb[u].z; a1.w += e * vb[u].w;
+        }
     }
-    partial[threadIdx.x] = acc;
+    if (lo_on) *reinterpret_cast<float4*>(&partial[warp * kAttnMaxD + 4 * lane]) = a0;
+    if (hi_on) *reinterpret_cast<float4*>(&partial[warp * kAttnMaxD + 128 + 4 * lane]) = a1;
     __syncthreads();
     if (threadIdx.x < D) {
         float total = 0.0f;
-        for (uint32_t gg = 0; gg < groups; ++gg) total += partial[gg * D + threadIdx.x];
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) total += partial[w * kAttnMaxD + threadIdx.x];
         share.out[threadIdx.x] = total;
     }
     if (threadIdx.x == 0) { share.max_score = max_score; share.sum = sum; }

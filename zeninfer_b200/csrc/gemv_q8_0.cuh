@@ -453,6 +453,11 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
         float acc[kBatch];
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) acc[b] = 0.0f;
+        // y += W x: fetch the old outputs now, so that their latency hides behind the row's dot products
+        float y_old[kBatch];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b)
+            y_old[b] = ((p.flags & kGemvFlagAccumulate) && valid && lane == 0 && t.y) ? __ldcg(t.y + static_cast<size_t>(b) * t.rows + row) : 0.0f;
 
         for (uint32_t s = 0; s < nseg; ++s) {
             const uint32_t unit = pair_base + s * kTeams + team;
@@ -520,10 +525,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
                 float v = acc[tk];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0 && t.y) {
-                    float* dst = t.y + static_cast<size_t>(tk) * t.rows + row;
-                    *dst = (p.flags & kGemvFlagAccumulate) ? *dst + v : v;
-                }
+                if (lane == 0 && t.y) t.y[static_cast<size_t>(tk) * t.rows + row] = y_old[tk] + v;   // y_old is zero unless accumulating
                 if (lane == 0 && p.gather.world) stash[static_cast<size_t>(tk) * n_mine + (t.first_row + row - r_first)] = v;
             }
         }

@@ -1277,11 +1277,10 @@ bool enqueue_attention(State& s, cudaStream_t st, bool fused, const float* d_q, 
     if (!d_q || !d_k_cache || !d_v_cache || !d_pos || !d_out || !heads || !kv_heads || heads % kv_heads || !head_dim || head_dim % 4 || head_dim > 256 ||
         !max_positions || (fused && (!d_k || !d_v || !d_cos || !d_sin || 2 * pairs > head_dim)))
         return set_error(s, "attention: bad arguments");
-    if (zk::kAttnThreads % head_dim) return set_error(s, "attention: head_dim must divide 256");
     const size_t span = window ? std::min(window, max_positions) : max_positions;
     const size_t smem = ((span + zk::kAttnSplit - 1) / zk::kAttnSplit) * sizeof(float);   // a CTA of the cluster holds its own positions' scores
-    if (smem + 4096 > s.smem_optin) return set_error(s, "attention: the attended span does not fit shared memory");
-    static size_t configured[2] = {40 * 1024, 40 * 1024};
+    if (smem + 12288 > s.smem_optin) return set_error(s, "attention: the attended span does not fit shared memory");
+    static size_t configured[2] = {36 * 1024, 36 * 1024};
     if (smem > configured[fused]) {
         const cudaError_t ea = fused ? cudaFuncSetAttribute(zk::attention_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))
                                      : cudaFuncSetAttribute(zk::attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

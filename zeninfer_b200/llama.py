@@ -94,11 +94,15 @@ class LlamaDecoder:
     synthetic_tensors does; matrices must be Q8_0 raw blocks [rows, row_bytes]."""
 
     def __init__(self, backend: Backend, cfg: LlamaConfig, tensors, act_mode: int = ACT_INT8, max_positions: int | None = None, device=None,
-                 fused: bool = True):
-        """fused: fold RMSNorm, SwiGLU and the residual adds into the projection launches (5 launches per layer);
-        otherwise every operator is its own launch (9 per layer).  Same arithmetic either way."""
+                 fused: bool | str = "nr"):
+        """fused: which of the layer's small operators are folded into the projection launches, as a string of letters:
+        'n' RMSNorm into the q|k|v, gate|up and lm_head prologues, 's' SwiGLU into the down projection's prologue,
+        'r' the residual adds into the o and down projections' stores.  True = all (5 launches per layer), False =
+        none (8 per layer); the default folds what pays: the norm costs a CTA one extra pass over a 16 KB row, SwiGLU would
+        cost every CTA 14336 exponentials.  Same arithmetic either way."""
         import torch
-        self.torch, self.be, self.cfg, self.act_mode, self.fused = torch, backend, cfg, act_mode, fused
+        self.torch, self.be, self.cfg, self.act_mode = torch, backend, cfg, act_mode
+        self.fuse = "nsr" if fused is True else "" if fused is False else str(fused)
         self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.max_positions = max_positions or cfg.context
         self.stream = torch.cuda.Stream(device=self.dev)
@@ -129,42 +133,68 @@ class LlamaDecoder:
         self.host_token = torch.zeros(1, dtype=torch.int64).pin_memory()   # generate() feeds every step from the host, as the reference does
         self.graph_layers = self.graph_head = None
 
+    @classmethod
+    def from_gguf(cls, backend: Backend, path: str, **kwargs) -> "LlamaDecoder":
+        """Loads a `general.architecture = llama` GGUF file with Q8_0 matrices: the tensors are uploaded straight from
+        the file mapping (no host copy of the model), as the reference's loader hands its backends pointers into the
+        mapping (src/adapters/dense_transformer_runtime.cpp:993-1004)."""
+        from . import gguf
+        with gguf.GgufFile(path) as g:
+            cfg = gguf.llama_config(g)
+            return cls(backend, cfg, gguf.llama_tensors(g, cfg), **kwargs)   # uploads complete before the mapping closes
+
     # ---- one token step, as launches on self.stream ----
     def _enqueue_layers(self) -> None:
         be, cfg, st, mode = self.be, self.cfg, self.stream.cuda_stream, self.act_mode
         P = lambda t: t.data_ptr()
         E, eps = cfg.embedding, cfg.rms_eps
+        fn, fs, fr = "n" in self.fuse, "s" in self.fuse, "r" in self.fuse
+        # the residual stream is self.x; a projection's input is x itself (norm folded in) or its normalised copy self.xn
         be.dev_embed_q8_0(self.h["token_embd.weight"], P(self.token), P(self.x), st)
-        if not self.fused:
+        if not fn:
             be.dev_rms_norm(P(self.x), None, P(self.norm["blk.0.attn_norm.weight"]), P(self.xn), E, 1, eps, st)
         for layer in range(cfg.layers):
             p = f"blk.{layer}."
             qkv = [self.h[p + "attn_q.weight"], self.h[p + "attn_k.weight"], self.h[p + "attn_v.weight"]]
             qkv_out = [P(self.q), P(self.k), P(self.v)]
-            if self.fused:
+            if fn:
                 be.dev_gemv_fused(qkv, qkv_out, P(self.x), 1, mode, st, norm_weight=P(self.norm[p + "attn_norm.weight"]), norm_eps=eps)
             else:
                 be.dev_gemv(qkv, qkv_out, P(self.xn), 1, mode, st)
             be.dev_attention_block(P(self.q), P(self.k), P(self.v), P(self.cos), P(self.sin), cfg.head_dim // 2, P(self.pos), P(self.k_cache[layer]),
                                    P(self.v_cache[layer]), P(self.att), cfg.heads, cfg.kv_heads, cfg.head_dim, self.max_positions, 0.0, 0, st)
-            gate_up = [self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]]
-            if self.fused:
-                be.dev_gemv_fused([self.h[p + "attn_output.weight"]], [P(self.x)], P(self.att), 1, mode, st, accumulate=True)         # x += o(att)
-                be.dev_gemv_fused(gate_up, [P(self.gate), P(self.up)], P(self.x), 1, mode, st, norm_weight=P(self.norm[p + "ffn_norm.weight"]), norm_eps=eps)
-                be.dev_gemv_fused([self.h[p + "ffn_down.weight"]], [P(self.x)], P(self.up), 1, mode, st, gate=P(self.gate), accumulate=True)  # x += down(silu(gate) * up)
+            # attention output projection and its residual add
+            o = [self.h[p + "attn_output.weight"]]
+            if fr:
+                be.dev_gemv_fused(o, [P(self.x)], P(self.att), 1, mode, st, accumulate=True)                     # x += o(att)
             else:
-                be.dev_gemv([self.h[p + "attn_output.weight"]], [P(self.tmp)], P(self.att), 1, mode, st)
-                be.dev_rms_norm(P(self.x), P(self.tmp), P(self.norm[p + "ffn_norm.weight"]), P(self.xn), E, 1, eps, st)
+                be.dev_gemv(o, [P(self.tmp)], P(self.att), 1, mode, st)
+            # ffn norm (with the residual add when it was not folded into the store)
+            if not fn:
+                be.dev_rms_norm(P(self.x), None if fr else P(self.tmp), P(self.norm[p + "ffn_norm.weight"]), P(self.xn), E, 1, eps, st)
+            elif not fr:
+                be.dev_rms_norm(P(self.x), P(self.tmp), None, None, E, 1, eps, st)                                 # x += tmp only
+            gate_up = [self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]]
+            if fn:
+                be.dev_gemv_fused(gate_up, [P(self.gate), P(self.up)], P(self.x), 1, mode, st, norm_weight=P(self.norm[p + "ffn_norm.weight"]), norm_eps=eps)
+            else:
                 be.dev_gemv(gate_up, [P(self.gate), P(self.up)], P(self.xn), 1, mode, st)
+            down = [self.h[p + "ffn_down.weight"]]
+            if not fs:
                 be.dev_silu_mul(P(self.gate), P(self.up), P(self.hid), cfg.ffn, st)
-                be.dev_gemv([self.h[p + "ffn_down.weight"]], [P(self.tmp)], P(self.hid), 1, mode, st)
-                nxt = self.norm[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < cfg.layers else self.norm["output_norm.weight"]
-                be.dev_rms_norm(P(self.x), P(self.tmp), P(nxt), P(self.xn), E, 1, eps, st)
+            be.dev_gemv_fused(down, [P(self.x) if fr else P(self.tmp)], P(self.up) if fs else P(self.hid), 1, mode, st,
+                              gate=P(self.gate) if fs else None, accumulate=fr)                                   # (x +=) down(silu(gate) * up)
+            # the next norm: the next layer's attention norm, or the output norm
+            nxt = self.norm[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < cfg.layers else self.norm["output_norm.weight"]
+            if not fn:
+                be.dev_rms_norm(P(self.x), None if fr else P(self.tmp), P(nxt), P(self.xn), E, 1, eps, st)
+            elif not fr:
+                be.dev_rms_norm(P(self.x), P(self.tmp), None, None, E, 1, eps, st)
         be.dev_advance_position(P(self.pos), 1, st)
 
     def _enqueue_head(self) -> None:
         be, st = self.be, self.stream.cuda_stream
-        if self.fused:
+        if "n" in self.fuse:
             be.dev_gemv_fused([self.h["output.weight"]], [self.logits.data_ptr()], self.x.data_ptr(), 1, self.act_mode, st,
                               norm_weight=self.norm["output_norm.weight"].data_ptr(), norm_eps=self.cfg.rms_eps)
         else:
