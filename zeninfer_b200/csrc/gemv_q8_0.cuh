@@ -169,9 +169,12 @@ __device__ __forceinline__ int dot32(const uint4& wa, const uint4& wb, const uin
 #ifndef ZK_GEMV_MIN_CTAS
 #define ZK_GEMV_MIN_CTAS 1
 #endif
-template <int kBatch, int kDigits>
+// kFuse: the launch may carry kGemvFlag* work (fused RMSNorm / SwiGLU input, accumulating store).  It is a template
+// parameter because even untaken flag tests in the prologue and the store cost the plain 4096 x 4096 product 5 %.
+template <int kBatch, int kDigits, bool kFuse = false>
 __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV_MIN_CTAS : 1))
     gemv_q8_0_kernel(const __grid_constant__ GemvParams p) {
+    const uint32_t flags = kFuse ? p.flags : 0u;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t nb = p.K >> 5, nbp = (nb + 7) & ~7u, nseg = (nb + kGemvSegBlocks - 1) / kGemvSegBlocks;
     const uint32_t kpad_blocks = nseg * kGemvSegBlocks;
@@ -349,7 +352,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
         // Fused RMSNorm (rms_norm, src/adapters/dense_transformer_runtime.cpp:117-125): a first pass over the row sums the
         // squares in double, warp by warp and then across the consumer warps in a fixed order; the quantising pass below
         // scales what it loads by inv * weight.  Every CTA repeats this for itself: the row is 16 KB in L2.
-        if (p.flags & kGemvFlagNorm) {
+        if (kFuse && (flags & kGemvFlagNorm)) {
             for (int t = 0; t < kBatch; ++t) {
                 double ss = 0.0;
                 for (uint32_t b0 = warp * 8; b0 < nb; b0 += kGemvWarps * 8) {
@@ -369,7 +372,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
         }
         for (int t = 0; t < kBatch; ++t) {
             float inv_norm = 1.0f;
-            if (p.flags & kGemvFlagNorm) {
+            if (kFuse && (flags & kGemvFlagNorm)) {
                 double total = 0.0;
                 for (int w = 0; w < kGemvWarps; ++w) total += norm_part[t * kGemvWarps + w];
                 inv_norm = 1.0f / sqrtf(static_cast<float>(total / p.K) + p.norm_eps);
@@ -382,14 +385,14 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
                 // L2 is the point of coherence for what earlier kernels and peers wrote: bypass L1
                 const float4 lo = live ? __ldcg(src) : zero, hi = live ? __ldcg(src + 1) : zero;
                 float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-                if (p.flags & kGemvFlagNorm) {
+                if (kFuse && (flags & kGemvFlagNorm)) {
                     const float4* wsrc = reinterpret_cast<const float4*>(p.norm_weight + b * 32 + part * 8);
                     const float4 wlo = live ? __ldg(wsrc) : zero, whi = live ? __ldg(wsrc + 1) : zero;
                     const float nw[8] = {wlo.x, wlo.y, wlo.z, wlo.w, whi.x, whi.y, whi.z, whi.w};
 #pragma unroll
                     for (int e = 0; e < 8; ++e) v[e] = v[e] * inv_norm * nw[e];   // x * inv * weight, the reference's order
                 }
-                if (p.flags & kGemvFlagSwiglu) {
+                if (kFuse && (flags & kGemvFlagSwiglu)) {
                     // SwiGLU fused into the load: silu(gate) * up, silu(z) = z / (1 + exp(-z))
                     // (silu_mul, src/adapters/dense_transformer_runtime.cpp:193-199)
                     const float4* gsrc = reinterpret_cast<const float4*>(p.x_gate + static_cast<size_t>(t) * p.K + b * 32 + part * 8);
@@ -457,7 +460,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
         float y_old[kBatch];
 #pragma unroll
         for (int b = 0; b < kBatch; ++b)
-            y_old[b] = ((p.flags & kGemvFlagAccumulate) && valid && lane == 0 && t.y) ? __ldcg(t.y + static_cast<size_t>(b) * t.rows + row) : 0.0f;
+            y_old[b] = (kFuse && (flags & kGemvFlagAccumulate) && valid && lane == 0 && t.y) ? __ldcg(t.y + static_cast<size_t>(b) * t.rows + row) : 0.0f;
 
         for (uint32_t s = 0; s < nseg; ++s) {
             const uint32_t unit = pair_base + s * kTeams + team;
@@ -525,7 +528,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
                 float v = acc[tk];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0 && t.y) t.y[static_cast<size_t>(tk) * t.rows + row] = y_old[tk] + v;   // y_old is zero unless accumulating
+                if (lane == 0 && t.y) t.y[static_cast<size_t>(tk) * t.rows + row] = kFuse ? y_old[tk] + v : v;   // y_old is zero unless accumulating
                 if (lane == 0 && p.gather.world) stash[static_cast<size_t>(tk) * n_mine + (t.first_row + row - r_first)] = v;
             }
         }

@@ -296,9 +296,9 @@ unsigned long long* g_trace = nullptr;  // profiling builds: device buffer [laun
 size_t g_trace_launch = 0;
 #endif
 
-template <int kBatch, int kDigits>
+template <int kBatch, int kDigits, bool kFuse>
 cudaError_t launch_gemv_q8_0(const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
-    auto* fn = &zk::gemv_q8_0_kernel<kBatch, kDigits>;
+    auto* fn = &zk::gemv_q8_0_kernel<kBatch, kDigits, kFuse>;
     static size_t configured = 0;  // per instantiation; one device per process, calls serialised by the backend mutex
     if (smem > configured) {       // raised outside any stream capture by the first (uncaptured) launch of a shape
         cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -321,19 +321,24 @@ cudaError_t launch_gemv_q8_0(const zk::GemvParams& p, unsigned grid, size_t smem
     return cudaLaunchKernelEx(&cfg, fn, p);
 }
 
-template <int kDigits>
-cudaError_t dispatch_batch(int batch, const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
+template <int kDigits, bool kFuse>
+cudaError_t dispatch_batch_fuse(int batch, const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
     switch (batch) {
-    case 1: return launch_gemv_q8_0<1, kDigits>(p, grid, smem, st, pdl);
-    case 2: return launch_gemv_q8_0<2, kDigits>(p, grid, smem, st, pdl);
-    case 3: return launch_gemv_q8_0<3, kDigits>(p, grid, smem, st, pdl);
-    case 4: return launch_gemv_q8_0<4, kDigits>(p, grid, smem, st, pdl);
-    case 5: return launch_gemv_q8_0<5, kDigits>(p, grid, smem, st, pdl);
-    case 6: return launch_gemv_q8_0<6, kDigits>(p, grid, smem, st, pdl);
-    case 7: return launch_gemv_q8_0<7, kDigits>(p, grid, smem, st, pdl);
-    case 8: return launch_gemv_q8_0<8, kDigits>(p, grid, smem, st, pdl);
+    case 1: return launch_gemv_q8_0<1, kDigits, kFuse>(p, grid, smem, st, pdl);
+    case 2: return launch_gemv_q8_0<2, kDigits, kFuse>(p, grid, smem, st, pdl);
+    case 3: return launch_gemv_q8_0<3, kDigits, kFuse>(p, grid, smem, st, pdl);
+    case 4: return launch_gemv_q8_0<4, kDigits, kFuse>(p, grid, smem, st, pdl);
+    case 5: return launch_gemv_q8_0<5, kDigits, kFuse>(p, grid, smem, st, pdl);
+    case 6: return launch_gemv_q8_0<6, kDigits, kFuse>(p, grid, smem, st, pdl);
+    case 7: return launch_gemv_q8_0<7, kDigits, kFuse>(p, grid, smem, st, pdl);
+    case 8: return launch_gemv_q8_0<8, kDigits, kFuse>(p, grid, smem, st, pdl);
     default: return cudaErrorInvalidValue;
     }
+}
+// Launches that carry fused work (p.flags) take the kFuse instantiation; plain products keep the lean one.
+template <int kDigits>
+cudaError_t dispatch_batch(int batch, const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
+    return p.flags ? dispatch_batch_fuse<kDigits, true>(batch, p, grid, smem, st, pdl) : dispatch_batch_fuse<kDigits, false>(batch, p, grid, smem, st, pdl);
 }
 
 template <int kFormat, int kBatch>
