@@ -369,6 +369,11 @@ def run_layer_sweep(args) -> None:
             layer_bytes = sum(tensor_bytes(fmt, *shape[n]) for n in shape)
             layer_copies = int(SWEEP_MIN_BYTES // layer_bytes) + 1
             per_kind, copies = {}, {}
+
+            def launch(hs, names, cols, next_handle, fmt=fmt, mode=mode):
+                """One product launch; it also hints the tensor the next launch reads to L2 (no result changes)."""
+                be.dev_gemv_fused(hs, [d_y[n].data_ptr() for n in names], d_x[cols].data_ptr(), 1, mode, stream.cuda_stream, warm_next=next_handle)
+
             for kind, names in LAYER_LAUNCHES:
                 nbytes = sum(tensor_bytes(fmt, *shape[n]) for n in names)
                 ncopy = max(layer_copies, int(SWEEP_MIN_BYTES // nbytes) + 1)
@@ -377,8 +382,8 @@ def run_layer_sweep(args) -> None:
                 algo = nbytes + 4 * cols + 4 * sum(shape[n][0] for n in names)
 
                 def enqueue(kind=kind, names=names, cols=cols):
-                    for hs in copies[kind]:
-                        be.dev_gemv(hs, [d_y[n].data_ptr() for n in names], d_x[cols].data_ptr(), 1, mode, stream.cuda_stream)
+                    for c, hs in enumerate(copies[kind]):
+                        launch(hs, names, cols, copies[kind][(c + 1) % len(copies[kind])][0])
 
                 us = time_graph(enqueue, ncopy)
                 launches_total += (reps + max(3, args.warmup) + 2) * ncopy
@@ -386,10 +391,10 @@ def run_layer_sweep(args) -> None:
                                   "us": us, "gbs": algo / us / 1e3, "frac": algo / us / 1e3 / peak}
 
             def enqueue_layer():
-                for c in range(layer_copies):
-                    for kind, names in LAYER_LAUNCHES:
-                        cols = shape[names[0]][1]
-                        be.dev_gemv(copies[kind][c], [d_y[n].data_ptr() for n in names], d_x[cols].data_ptr(), 1, mode, stream.cuda_stream)
+                order = [(c, kind, names) for c in range(layer_copies) for kind, names in LAYER_LAUNCHES]
+                for i, (c, kind, names) in enumerate(order):
+                    nc, nkind, _ = order[(i + 1) % len(order)]
+                    launch(copies[kind][c], names, shape[names[0]][1], copies[nkind][nc][0])
 
             layer_us = time_graph(enqueue_layer, layer_copies)
             launches_total += (reps + max(3, args.warmup) + 2) * layer_copies * len(LAYER_LAUNCHES)
@@ -662,7 +667,7 @@ def torch_q8_0_pack(w):
 
 def run_decode(args) -> None:
     """Config: 32 layers, d 4096, 32 query / 8 KV heads of 128, SwiGLU 14336, vocab 128256, eps 1e-5, theta 500000,
-    weights N(0, 0.02) seed 6, a prompt of 512 uniform-random ids, then greedy decode steps.  A step is one decoded
+    weights N(0, 0.02) seed 6, a prompt of 512 uniform-random ids (consumed as tensor-core blocks, timed separately), then greedy decode steps.  A step is one decoded
     token: 165 launches replayed from two CUDA graphs (norms, SwiGLU and residual adds are folded into the projections).  The prompt is consumed token by token through the same step
     and is not timed."""
     import torch
@@ -694,14 +699,19 @@ def run_decode(args) -> None:
     load_s = time.perf_counter() - t0
     dec.capture()
     prompt = np.random.default_rng(6).integers(0, cfg.vocab, size=prompt_len, dtype=np.int64)
-    ids = torch.from_numpy(prompt).to(dev)
     stream = dec.stream
     with ClockSampler(0) as clocks:
         with torch.cuda.stream(stream):
             dec.reset()
-            for i in range(prompt_len):
-                dec.token.copy_(ids[i:i + 1])
-                dec.step(want_token=(i + 1 == prompt_len))
+            dec.feed_prompt(prompt.tolist(), batched_prefill=not args.token_prefill)      # first run: kernel attributes, workspace allocation
+            stream.synchronize()
+            dec.reset()
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            p0.record(stream)
+            dec.feed_prompt(prompt.tolist(), batched_prefill=not args.token_prefill)      # the prompt as tensor-core blocks (or token by token), then the first pick
+            p1.record(stream)
+            stream.synchronize()
+            prefill_ms = p0.elapsed_time(p1)
             for _ in range(warm):
                 dec.step(want_token=True)
             stream.synchronize()
@@ -766,10 +776,11 @@ def run_decode(args) -> None:
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": "greedy decode, random-init Llama-3-8B shape in Q8_0 (config 4): 32 layers, d 4096, 32/8 heads of 128, ffn 14336, "
-                               f"vocab 128256; prompt of {prompt_len} random ids (consumed token by token, untimed), then {warm} + {steps} decode steps",
+                               f"vocab 128256; prompt of {prompt_len} random ids (untimed here, see prefill_ms), then {warm} + {steps} decode steps",
                    "activations": "int8 (bit-exact reference codes)", "l2": "inputs larger than L2: 8.5 GB of weights stream per token",
                    "launch": f"two CUDA graphs per token, {launches_per_step} kernel launches (folded into the projections: '{dec.fuse}')", "weights": "torch.randn on the device, seed 6, N(0, 0.02)",
-                   "load_s": load_s},
+                   "load_s": load_s, "prefill": ("token by token" if args.token_prefill else "blocks of up to 512 tokens through the tcgen05 GEMM + causal block attention"),
+                   "prefill_ms": prefill_ms, "prefill_tokens_per_s": prompt_len / (prefill_ms * 1e-3)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
                      "kernel": "whole token step (projections through gemv_q8_0_kernel<1,1>)", "launch_us": ms * 1e3 / steps,
                      "algorithmic_bytes_per_launch": algo, "weight_bytes": weight_bytes, "kv_bytes": kv_bytes},
@@ -795,6 +806,7 @@ def main() -> None:
                     help="N > 1: how the output shards are all-gathered after each product -- by the product kernel itself "
                          "(peer stores over NVLink, the default) or by an NCCL all-gather launched after it")
     ap.add_argument("--fuse", default="nr", help="workload decode: operators folded into the projection launches (letters n, s, r; see LlamaDecoder)")
+    ap.add_argument("--token-prefill", action="store_true", help="workload decode: consume the prompt token by token instead of in tensor-core blocks")
     ap.add_argument("--prompt-len", type=int, default=512, help="workload decode: prompt tokens consumed before the timed steps")
     ap.add_argument("--min-warmup", type=int, default=1500,
                     help="floor on the warm-up step count of the decode workload (about 0.3 s, so the clock sampler is up before "
@@ -849,14 +861,16 @@ def main() -> None:
         pg = PeerGather(be, world, rank, ROWS)  # collective: IPC handles travel through torch.distributed, once
 
     def one_pass():
-        for h in handles:
+        for i, h in enumerate(handles):
             if fused:   # the product kernel stores its outputs into every rank's gather region and publishes the launch;
                         # the next launch waits on the device until all ranks have published: no collective launch
                 pg.gemv([h], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream, d_y=[d_y.data_ptr()])
                 continue
+            if world == 1:   # the launch also asks L2 for the start of the tensor the next launch reads (a hint, no result changes)
+                be.dev_gemv_fused([h], [d_y.data_ptr()], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream, warm_next=handles[(i + 1) % COPIES])
+                continue
             be.dev_gemv([h], [d_y.data_ptr()], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream)
-            if world > 1:
-                dist.all_gather_into_tensor(d_all, d_y)
+            dist.all_gather_into_tensor(d_all, d_y)
 
     with torch.cuda.stream(stream):
         one_pass()  # first launch sets function attributes; keep it out of the capture
@@ -960,7 +974,7 @@ def main() -> None:
         "config": {"workload": WORKLOAD, "rows_per_gpu": ROWS, "columns": COLS, "batch": 1, "activations": "int8 (bit-exact reference codes)",
                    "l2": f"inputs larger than L2: {COPIES} weight copies, {COPIES * ALGO_BYTES_PER_LAUNCH / 1e6:.0f} MB per pass",
                    "launch": "CUDA graph replay, one kernel per copy" + (
-                       "" if world == 1 else "; output shards all-gathered by the product kernel itself (peer stores over NVLink, device-side epoch flags)"
+                       "; each launch hints the next launch's tensor to L2 (zen_cuda_gemv_fusion.warm_next)" if world == 1 else "; output shards all-gathered by the product kernel itself (peer stores over NVLink, device-side epoch flags)"
                        if fused else "; NCCL all-gather of output shards after each")},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "traffic": GEMV_NCU_TRAFFIC_BYTES, "launch_us": per_launch_us, "algorithmic_bytes_per_launch": ALGO_BYTES_PER_LAUNCH},

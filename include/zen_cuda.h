@@ -161,18 +161,24 @@ int zen_cuda_dev_gemv(const zen_cuda_weights* const* w, float* const* d_y, size_
 int zen_cuda_dev_gemv_swiglu(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_gate, const float* d_up,
                              size_t tokens, int act_mode, void* stream);
 
-/* zen_cuda_dev_gemv for Q8_0 tensors with the layer's small operators folded into the product launch, which is what the
+/* zen_cuda_dev_gemv for Q8_0 tensors with the layer's small operators folded into the product launch (for Q4_0 and
+ * Q6_K tensors only the warm_next field may be set, and it is ignored), which is what the
  * reference's fused D3D12 submissions do (ffn_residual_fused and LayerDecodeParams, include/zen/d3d12_backend.h:289-352,
  * zen::quant::ffn_residual_fused, src/quant.cpp:1566-1611):
  *   norm_weight != NULL : the input is RMSNorm(x) * norm_weight, eps = norm_eps (rms_norm, :117-125), formed per CTA in the
  *                         prologue; x itself is left untouched;
  *   gate != NULL        : the input is silu(gate) * x (as zen_cuda_dev_gemv_swiglu); not together with norm_weight;
- *   accumulate != 0     : y += W x instead of y = W x: with y the residual stream this is the layer's residual add. */
+ *   accumulate != 0     : y += W x instead of y = W x: with y the residual stream this is the layer's residual add;
+ *   warm_next != NULL   : a hint, the resident Q8_0 tensor the stream's next product will read: once its own copies are
+ *                         issued the launch asks L2 for the start of that tensor (up to 192 KB per CTA), so the next launch
+ *                         does not begin with a DRAM round trip.  Honoured for launches of at most 32 MB of weights (a larger
+ *                         one keeps HBM busy by itself).  Changes no result; any field combination is allowed. */
 typedef struct zen_cuda_gemv_fusion {
     const float* norm_weight;
     float norm_eps;
     int accumulate;
     const float* gate;
+    const zen_cuda_weights* warm_next;
 } zen_cuda_gemv_fusion;
 int zen_cuda_dev_gemv_fused(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x, size_t tokens, int act_mode,
                             const zen_cuda_gemv_fusion* fusion, void* stream);
@@ -292,6 +298,19 @@ int zen_cuda_dev_attention(const float* d_q, const float* d_k_cache, const float
 int zen_cuda_dev_attention_block(const float* d_q, const float* d_k, const float* d_v, const float* d_cos, const float* d_sin, size_t pairs,
                                  const int* d_pos, float* d_k_cache, float* d_v_cache, float* d_out, size_t heads, size_t kv_heads, size_t head_dim,
                                  float scale, size_t window, size_t max_positions, void* stream);
+/* ---- the same operators over a block of `tokens` new tokens at positions *d_pos .. *d_pos + tokens - 1 (prefill and
+ * speculative verify: DenseTransformerRuntime::forward_batch, src/adapters/dense_transformer_runtime.cpp:2296-3664; the
+ * D3D12 counterparts are rope_apply_prefill, kv_cache_append_batched and the flash-attention submissions,
+ * include/zen/d3d12_backend.h:207,235).  Buffers are token-major: q [tokens][heads * head_dim] and so on; the projections
+ * between them are zen_cuda_dev_gemm_q8_0, the norms zen_cuda_dev_rms_norm with rows = tokens. */
+int zen_cuda_dev_embed_rows_q8_0(const zen_cuda_weights* w, const int64_t* d_tokens, size_t tokens, float* d_out, void* stream);
+int zen_cuda_dev_rope_kv_append_rows(float* d_q, float* d_k, const float* d_v, size_t tokens, const float* d_cos, const float* d_sin, const int* d_pos,
+                                     size_t heads, size_t kv_heads, size_t head_dim, size_t pairs, int adjacent, float* d_k_cache, float* d_v_cache,
+                                     size_t max_positions, void* stream);
+/* Causal attention: token t attends positions [first, *d_pos + t] of the caches (which already hold the block's keys
+ * and values).  head_dim 64, 128 or 256. */
+int zen_cuda_dev_attention_prefill(const float* d_q, const float* d_k_cache, const float* d_v_cache, const int* d_pos, float* d_out, size_t tokens,
+                                   size_t heads, size_t kv_heads, size_t head_dim, float scale, size_t window, size_t max_positions, void* stream);
 /* d_out = silu(gate) * up (silu_mul, src/adapters/dense_transformer_runtime.cpp:193-199). */
 int zen_cuda_dev_silu_mul(const float* d_gate, const float* d_up, float* d_out, size_t count, void* stream);
 /* *d_pos += delta, in stream order (a step's last launch). */

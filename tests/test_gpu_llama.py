@@ -287,3 +287,100 @@ def test_decoder_loaded_from_a_gguf_file(be, golden, tmp_path):
         assert_parity(dec.last_logits(), logits, 1e-3, "last logits")
     finally:
         dec.close()
+
+
+def test_warm_next_hint_changes_no_result(be, zo):
+    import torch
+    rows, cols = 4096, 4096
+    w = np.ascontiguousarray(blocks.quantize_q8_0(np.random.default_rng(41).standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02)))
+    other = np.ascontiguousarray(blocks.quantize_q8_0(np.random.default_rng(42).standard_normal((1000, 14336), dtype=np.float32) * np.float32(0.02)))
+    q6 = np.ascontiguousarray(blocks.quantize_q6_k(np.random.default_rng(43).standard_normal((64, 1024), dtype=np.float32)))
+    h, h_other, h_q6 = be.dev_upload("Q8_0", w, rows, cols), be.dev_upload("Q8_0", other, 1000, 14336), be.dev_upload("Q6_K", q6, 64, 1024)
+    x = dev(np.random.default_rng(44).standard_normal(cols, dtype=np.float32))
+    outs = []
+    torch.cuda.synchronize()
+    for warm in (None, h, h_other, h_q6):       # itself, a tensor of another shape, a format that is not warmed
+        y = torch.zeros(rows, device="cuda")
+        torch.cuda.synchronize()
+        be.dev_gemv_fused([h], [y.data_ptr()], x.data_ptr(), 1, ACT_INT8, 0, warm_next=warm)
+        torch.cuda.synchronize()
+        be.dev_check(0)
+        outs.append(y.cpu().numpy())
+    assert all(np.array_equal(outs[0], o) for o in outs[1:])
+    for hh in (h, h_other, h_q6):
+        be.dev_free(hh)
+
+
+@pytest.mark.parametrize("H,KH,D,T,pos0,window", [(4, 2, 64, 37, 5, 0), (8, 8, 128, 16, 0, 0), (32, 8, 128, 70, 100, 0), (4, 1, 64, 33, 3, 12), (2, 1, 256, 20, 7, 0)])
+def test_attention_prefill_block(be, H, KH, D, T, pos0, window):
+    import torch
+    P = 256
+    rng = np.random.default_rng(H * 7 + T)
+    q = rng.standard_normal((T, H * D), dtype=np.float32)
+    kc, vc = rng.standard_normal((P, KH * D), dtype=np.float32), rng.standard_normal((P, KH * D), dtype=np.float32)
+    dq, dkc, dvc, dpos, out = dev(q), dev(kc), dev(vc), dev(np.array([pos0], np.int32)), torch.zeros((T, H * D), device="cuda")
+    torch.cuda.synchronize()
+    be.dev_attention_prefill(dq.data_ptr(), dkc.data_ptr(), dvc.data_ptr(), dpos.data_ptr(), out.data_ptr(), T, H, KH, D, P, 0.0, window, 0)
+    torch.cuda.synchronize()
+    be.dev_check(0)
+    ref = np.zeros((T, H * D))
+    for t in range(T):
+        last = pos0 + t
+        first = last + 1 - window if window and last + 1 > window else 0
+        for h in range(H):
+            kh = h // (H // KH)
+            sc = kc[first:last + 1, kh * D:(kh + 1) * D].astype(np.float64) @ q[t, h * D:(h + 1) * D].astype(np.float64) / np.sqrt(D)
+            a = np.exp(sc - sc.max())
+            ref[t, h * D:(h + 1) * D] = (a / a.sum()) @ vc[first:last + 1, kh * D:(kh + 1) * D].astype(np.float64)
+    assert_parity(out.cpu().numpy(), ref, 1e-5, "prefill attention")
+
+
+def test_embed_and_rope_rows(be):
+    import torch
+    rows, cols, T = 300, 256, 19
+    w = np.random.default_rng(1).standard_normal((rows, cols), dtype=np.float32) * np.float32(0.05)
+    packed = np.ascontiguousarray(blocks.quantize_q8_0(w))
+    h = be.dev_upload("Q8_0", packed, rows, cols)
+    toks = np.random.default_rng(2).integers(0, rows, size=T, dtype=np.int64)
+    dt, out = dev(toks), torch.zeros((T, cols), device="cuda")
+    torch.cuda.synchronize()
+    be.dev_embed_rows_q8_0(h, dt.data_ptr(), T, out.data_ptr(), 0)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), blocks.dequantize(blocks.Q8_0, packed, rows, cols)[toks])
+    be.dev_free(h)
+
+    H, KH, D, P, pos0 = 4, 2, 64, 64, 9
+    cos, sin = rope_tables(LlamaConfig(heads=H, kv_heads=KH, head_dim=D, rope_base=500000.0), P)
+    rng = np.random.default_rng(3)
+    q, k, v = (rng.standard_normal((T, n), dtype=np.float32) for n in (H * D, KH * D, KH * D))
+    dq, dk, dv, dcos, dsin, dpos = dev(q), dev(k), dev(v), dev(cos), dev(sin), dev(np.array([pos0], np.int32))
+    kc, vc = torch.zeros((P, KH * D), device="cuda"), torch.zeros((P, KH * D), device="cuda")
+    torch.cuda.synchronize()
+    be.dev_rope_kv_append_rows(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), T, dcos.data_ptr(), dsin.data_ptr(), dpos.data_ptr(), H, KH, D, D // 2, True,
+                               kc.data_ptr(), vc.data_ptr(), P, 0)
+    torch.cuda.synchronize()
+    be.dev_check(0)
+    for t in (0, 7, T - 1):
+        tv = k[t].reshape(KH, D).astype(np.float64)
+        a, b = tv[:, 0::2].copy(), tv[:, 1::2].copy()
+        tv[:, 0::2], tv[:, 1::2] = a * cos[pos0 + t] - b * sin[pos0 + t], a * sin[pos0 + t] + b * cos[pos0 + t]
+        assert_parity(kc.cpu().numpy()[pos0 + t], tv.reshape(-1), 1e-6, "appended key row")
+        assert np.array_equal(vc.cpu().numpy()[pos0 + t], v[t])
+    assert float(kc[:pos0].abs().sum()) == 0.0 and float(kc[pos0 + T:].abs().sum()) == 0.0
+
+
+def test_batched_prefill_matches_token_by_token(be, golden):
+    cfg, meta, _, _, _ = golden
+    prompt = np.random.default_rng(77).integers(3, cfg.vocab, size=45).tolist()      # 45 = 2 x 16 + 13: two blocks and a tail... see PREFILL_CHUNK
+    dec = LlamaDecoder(be, cfg, synthetic_tensors(cfg, meta["seed"], meta["weight_std"]), act_mode=ACT_INT8)
+    try:
+        dec.PREFILL_CHUNK = 32           # forces a 32-token block, then 13 tokens one by one
+        dec._pf = None
+        a = dec.generate(prompt, 10, batched_prefill=False)
+        la = dec.last_logits()
+        b = dec.generate(prompt, 10, batched_prefill=True)
+        lb = dec.last_logits()
+        assert a == b
+        assert_parity(lb, la, 1e-3, "logits after a batched prefill vs token by token")
+    finally:
+        dec.close()

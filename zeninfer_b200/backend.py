@@ -40,6 +40,7 @@ ABI_SYMBOLS = (
     "zen_cuda_dev_greedy_pick",
     "zen_cuda_dev_embed_q8_0", "zen_cuda_dev_rms_norm", "zen_cuda_dev_rope_kv_append", "zen_cuda_dev_attention", "zen_cuda_dev_silu_mul",
     "zen_cuda_dev_advance_position", "zen_cuda_dev_gemv_swiglu", "zen_cuda_dev_attention_block", "zen_cuda_dev_gemv_fused",
+    "zen_cuda_dev_embed_rows_q8_0", "zen_cuda_dev_rope_kv_append_rows", "zen_cuda_dev_attention_prefill",
 )
 
 
@@ -70,7 +71,7 @@ class GemmTask(C.Structure):
 
 
 class GemvFusion(C.Structure):
-    _fields_ = [("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("accumulate", C.c_int), ("gate", C.c_void_p)]
+    _fields_ = [("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("accumulate", C.c_int), ("gate", C.c_void_p), ("warm_next", C.c_void_p)]
 
 
 class PickSegment(C.Structure):
@@ -138,6 +139,9 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_dev_rope_kv_append.argtypes = [vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, i, vp, vp, sz, vp]
     lib.zen_cuda_dev_attention.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz, C.c_float, sz, sz, vp]
     lib.zen_cuda_dev_silu_mul.argtypes = [vp, vp, vp, sz, vp]
+    lib.zen_cuda_dev_embed_rows_q8_0.argtypes = [vp, vp, sz, vp, vp]
+    lib.zen_cuda_dev_rope_kv_append_rows.argtypes = [vp, vp, vp, sz, vp, vp, vp, sz, sz, sz, sz, i, vp, vp, sz, vp]
+    lib.zen_cuda_dev_attention_prefill.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz, sz, C.c_float, sz, sz, vp]
     lib.zen_cuda_dev_attention_block.argtypes = [vp, vp, vp, vp, vp, sz, vp, vp, vp, vp, sz, sz, sz, C.c_float, sz, sz, vp]
     lib.zen_cuda_dev_advance_position.argtypes = [vp, i, vp]
     return lib
@@ -273,12 +277,14 @@ class Backend:
             self._fail("dev_gemv_swiglu")
 
     def dev_gemv_fused(self, handles: Sequence[int], d_y: Sequence[int], d_x: int, tokens: int, act_mode: int, stream: int = 0, *,
-                       norm_weight: int | None = None, norm_eps: float = 0.0, gate: int | None = None, accumulate: bool = False) -> None:
-        """dev_gemv (Q8_0) with RMSNorm or SwiGLU applied to the input inside the launch and/or y += W x."""
+                       norm_weight: int | None = None, norm_eps: float = 0.0, gate: int | None = None, accumulate: bool = False,
+                       warm_next: int | None = None) -> None:
+        """dev_gemv (Q8_0) with RMSNorm or SwiGLU applied to the input inside the launch and/or y += W x; warm_next
+        names the tensor the stream's next product reads, whose start this launch pulls into L2."""
         n = len(handles)
         hs = (C.c_void_p * n)(*handles)
         ys = (C.c_void_p * n)(*d_y)
-        f = GemvFusion(norm_weight, norm_eps, int(accumulate), gate)
+        f = GemvFusion(norm_weight, norm_eps, int(accumulate), gate, warm_next)
         if not self.lib.zen_cuda_dev_gemv_fused(hs, ys, n, d_x, tokens, act_mode, C.byref(f), stream):
             self._fail("dev_gemv_fused")
 
@@ -388,6 +394,23 @@ class Backend:
         if not self.lib.zen_cuda_dev_attention_block(d_q, d_k, d_v, d_cos, d_sin, pairs, d_pos, d_k_cache, d_v_cache, d_out, heads, kv_heads, head_dim,
                                                      scale, window, max_positions, stream):
             self._fail("dev_attention_block")
+
+    # ---- the block (prefill) forms ----
+    def dev_embed_rows_q8_0(self, handle: int, d_tokens: int, tokens: int, d_out: int, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_embed_rows_q8_0(handle, d_tokens, tokens, d_out, stream):
+            self._fail("dev_embed_rows_q8_0")
+
+    def dev_rope_kv_append_rows(self, d_q: int, d_k: int, d_v: int, tokens: int, d_cos: int, d_sin: int, d_pos: int, heads: int, kv_heads: int,
+                                head_dim: int, pairs: int, adjacent: bool, d_k_cache: int, d_v_cache: int, max_positions: int, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_rope_kv_append_rows(d_q, d_k, d_v, tokens, d_cos, d_sin, d_pos, heads, kv_heads, head_dim, pairs, int(adjacent),
+                                                         d_k_cache, d_v_cache, max_positions, stream):
+            self._fail("dev_rope_kv_append_rows")
+
+    def dev_attention_prefill(self, d_q: int, d_k_cache: int, d_v_cache: int, d_pos: int, d_out: int, tokens: int, heads: int, kv_heads: int,
+                              head_dim: int, max_positions: int, scale: float = 0.0, window: int = 0, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_attention_prefill(d_q, d_k_cache, d_v_cache, d_pos, d_out, tokens, heads, kv_heads, head_dim, scale, window,
+                                                       max_positions, stream):
+            self._fail("dev_attention_prefill")
 
     def dev_silu_mul(self, d_gate: int, d_up: int, d_out: int, count: int, stream: int = 0) -> None:
         if not self.lib.zen_cuda_dev_silu_mul(d_gate, d_up, d_out, count, stream):

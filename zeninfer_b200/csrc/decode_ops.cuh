@@ -327,6 +327,155 @@ __global__ void __cluster_dims__(kAttnSplit, 1, 1) __launch_bounds__(kAttnThread
     cluster.sync();                                   // nobody leaves while rank 0 still reads its shared memory
 }
 
+// ---- prefill: the same operators over a block of T tokens at positions pos0 .. pos0 + T - 1 ------------------------------
+// (DenseTransformerRuntime::forward_batch, src/adapters/dense_transformer_runtime.cpp:2296-3664: embedding gather
+// :2315-2319, rope tables once :2380-2398, then per layer norm rows, batched projections, rope, attention, FFN.)
+
+// out[t][e] = row tokens[t] of a resident Q8_0 tensor; grid (ceil(K / 256), T).
+__global__ void embed_rows_q8_0_kernel(const int8_t* __restrict__ codes, const __half* __restrict__ scales, uint32_t rows, uint32_t K, uint32_t nbp,
+                                       const long long* __restrict__ tokens, float* __restrict__ out, int* error_word) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long id = tokens[blockIdx.y];
+    const bool ok = id >= 0 && id < static_cast<long long>(rows);
+    if (!ok && threadIdx.x == 0 && blockIdx.x == 0) atomicExch(error_word, kErrBadToken);
+    const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= K) return;
+    float v = 0.0f;
+    if (ok) v = static_cast<float>(codes[static_cast<size_t>(id) * K + e]) * __half2float(scales[static_cast<size_t>(id) * nbp + (e >> 5)]);
+    out[static_cast<size_t>(blockIdx.y) * K + e] = v;
+}
+
+// One CTA per token: rotate q [T][heads*D] and k [T][kv_heads*D] in place (adjacent pairs, or half-split) with the
+// table row of position *pos_ptr + t, then append k and v to the caches there.
+__global__ void __launch_bounds__(1024) rope_kv_append_rows_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v,
+                                                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                                                   const int* __restrict__ pos_ptr, uint32_t heads, uint32_t kv_heads, uint32_t D,
+                                                                   uint32_t pairs, int adjacent, float* __restrict__ k_cache, float* __restrict__ v_cache,
+                                                                   uint32_t max_positions, int* error_word) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long pos = static_cast<long long>(*pos_ptr) + blockIdx.x;
+    if (pos < 0 || pos >= static_cast<long long>(max_positions)) {
+        if (threadIdx.x == 0) atomicExch(error_word, kErrBadPosition);
+        return;
+    }
+    const uint32_t kw = kv_heads * D, qw = heads * D;
+    float* qt = q + static_cast<size_t>(blockIdx.x) * qw;
+    float* kt = k + static_cast<size_t>(blockIdx.x) * kw;
+    const float* vt = v + static_cast<size_t>(blockIdx.x) * kw;
+    const float* c = cos_t + static_cast<size_t>(pos) * pairs;
+    const float* s = sin_t + static_cast<size_t>(pos) * pairs;
+    for (uint32_t i = threadIdx.x; i < (heads + kv_heads) * pairs; i += blockDim.x) {
+        const uint32_t h = i / pairs, pr = i % pairs;
+        float* vec = h < heads ? qt + static_cast<size_t>(h) * D : kt + static_cast<size_t>(h - heads) * D;
+        const uint32_t ia = adjacent ? 2 * pr : pr, ib = adjacent ? 2 * pr + 1 : pr + pairs;
+        float a = vec[ia], b = vec[ib];
+        rope_pair(a, b, c[pr], s[pr]);
+        vec[ia] = a;
+        vec[ib] = b;
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < kw; i += blockDim.x) {
+        k_cache[static_cast<size_t>(pos) * kw + i] = kt[i];
+        v_cache[static_cast<size_t>(pos) * kw + i] = vt[i];
+    }
+}
+
+// Causal grouped-query attention for a block of T new tokens whose keys and values are already in the caches.
+// Grid (ceil(T / kPfTokens), kv_heads): a CTA takes kPfTokens consecutive tokens and all query heads of one KV head,
+// so that a key/value row staged in shared memory serves every query row of the group.  A query row (token, head) is
+// held by kPfLanes threads, D / kPfLanes dimensions each; keys and values come through shared memory in blocks of
+// kPfBlock positions; the softmax is the running-maximum form (out and denominator rescaled when the maximum moves),
+// which equals the reference's two-pass form up to rounding (attention rows of forward_batch, :3041-3570).
+// Token t attends positions [first, pos0 + t], first = the sliding-window start or 0.
+constexpr int kPfTokens = 16, kPfLanes = 4, kPfBlock = 32, kPfThreads = 256;
+template <int D>   // head dimension: 64, 128 or 256 (a compile-time constant keeps the row's registers registers)
+__global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
+                                                                        const float* __restrict__ v_cache, const int* __restrict__ pos_ptr,
+                                                                        float* __restrict__ out, uint32_t tokens, uint32_t heads, uint32_t kv_heads,
+                                                                        float scale, uint32_t window, uint32_t max_positions, int* error_word) {
+    extern __shared__ __align__(16) float kv_smem[];      // [2][kPfBlock][D]: keys, then values
+    pdl_launch_dependents();
+    pdl_wait();
+    const int pos0 = *pos_ptr;
+    if (pos0 < 0 || static_cast<uint32_t>(pos0) + tokens > max_positions) {
+        if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicExch(error_word, kErrBadPosition);
+        return;
+    }
+    const uint32_t group = heads / kv_heads, kh = blockIdx.y, kw = kv_heads * D, qw = heads * D;
+    const uint32_t rows_per_cta = kPfTokens * group;                 // query rows: (token, head of the group)
+    constexpr int per = D / kPfLanes;                                 // dimensions per thread
+    float* ks = kv_smem;
+    float* vs = kv_smem + kPfBlock * D;
+    const uint32_t t0 = blockIdx.x * kPfTokens;
+    const uint32_t t_end = min(tokens, t0 + kPfTokens);
+    // the span of positions any row of this CTA attends
+    const uint32_t last_pos = static_cast<uint32_t>(pos0) + t_end - 1;
+    const uint32_t first_any = (window && static_cast<uint32_t>(pos0) + t0 + 1 > window) ? static_cast<uint32_t>(pos0) + t0 + 1 - window : 0u;
+    for (uint32_t r0 = 0; r0 < rows_per_cta; r0 += kPfThreads / kPfLanes) {   // passes when the group has more rows than row slots
+        const uint32_t r = r0 + threadIdx.x / kPfLanes, part = threadIdx.x % kPfLanes;
+        const uint32_t t = t0 + r / group, h = kh * group + r % group;
+        const bool live = r < rows_per_cta && t < t_end;
+        const uint32_t my_last = static_cast<uint32_t>(pos0) + t;
+        const uint32_t my_first = (window && my_last + 1 > window) ? my_last + 1 - window : 0u;
+        float qv[per], acc[per];
+        float m = -INFINITY;
+        double l = 0.0;
+#pragma unroll
+        for (int i = 0; i < per; ++i) { qv[i] = 0.0f; acc[i] = 0.0f; }
+        if (live) {
+#pragma unroll
+            for (int i = 0; i < per; ++i) qv[i] = q[static_cast<size_t>(t) * qw + static_cast<size_t>(h) * D + part * per + i];
+        }
+        for (uint32_t p0 = first_any; p0 <= last_pos; p0 += kPfBlock) {
+            __syncthreads();                                            // the previous block's rows are no longer read
+            for (uint32_t i = threadIdx.x; i < kPfBlock * D / 4; i += kPfThreads) {
+                const uint32_t row = i / (D / 4), col = i % (D / 4), pos = p0 + row;
+                float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+                if (pos <= last_pos) {
+                    kk = __ldcg(reinterpret_cast<const float4*>(k_cache + static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D) + col);
+                    vv = __ldcg(reinterpret_cast<const float4*>(v_cache + static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D) + col);
+                }
+                reinterpret_cast<float4*>(ks)[i] = kk;
+                reinterpret_cast<float4*>(vs)[i] = vv;
+            }
+            __syncthreads();
+            for (uint32_t j = 0; j < kPfBlock; ++j) {
+                const uint32_t pos = p0 + j;
+                float dot = 0.0f;
+#pragma unroll
+                for (int i = 0; i < per; ++i) dot += qv[i] * ks[j * D + part * per + i];
+#pragma unroll
+                for (int o = kPfLanes / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                if (live && pos >= my_first && pos <= my_last) {        // uniform over the row's kPfLanes threads
+                    const float sc = dot * scale;
+                    if (sc > m) {                                       // the maximum moves: rescale what has been summed
+                        const float f = expf(m - sc);                   // exp(-inf) = 0 on the first position
+                        l *= f;
+#pragma unroll
+                        for (int i = 0; i < per; ++i) acc[i] *= f;
+                        m = sc;
+                    }
+                    const float e = expf(sc - m);
+                    l += e;
+#pragma unroll
+                    for (int i = 0; i < per; ++i) acc[i] += e * vs[j * D + part * per + i];
+                }
+            }
+        }
+        if (live) {
+            if (!(l > 0.0) || !isfinite(l)) {
+                if (part == 0) atomicExch(error_word, kErrNonFinite);
+            } else {
+                const float inv = 1.0f / static_cast<float>(l);
+#pragma unroll
+                for (int i = 0; i < per; ++i) out[static_cast<size_t>(t) * qw + static_cast<size_t>(h) * D + part * per + i] = acc[i] * inv;
+            }
+        }
+    }
+}
+
 // out = silu(gate) * up, silu(z) = z / (1 + exp(-z)).
 __global__ void silu_mul_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out, size_t n) {
     pdl_launch_dependents();

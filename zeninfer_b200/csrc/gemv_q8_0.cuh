@@ -72,6 +72,8 @@ constexpr uint32_t kL2PrefetchCap = 160 * 1024;     // bytes of the slice beyond
 constexpr uint32_t kGemvFlagSwiglu = 1u;      // input = silu(x_gate) * x
 constexpr uint32_t kGemvFlagNorm = 2u;        // input = RMSNorm(x) * norm_weight, formed in the prologue
 constexpr uint32_t kGemvFlagAccumulate = 4u;  // y += W x instead of y = W x (the residual add)
+constexpr uint32_t kGemvFlagWarm = 8u;        // pull the start of the next launch's tensor into L2 (producer warp only)
+constexpr uint32_t kWarmCapBytes = 192 * 1024;   // per CTA
 
 struct GemvTask {
     const uint8_t* codes;    // [rows][K] int8
@@ -97,6 +99,12 @@ struct GemvParams {
     const float* x_gate;     // [batch][K] fp32, read only with kGemvFlagSwiglu (a cold parameter line, touched by fused launches only)
     const float* norm_weight;  // [K] fp32, read only with kGemvFlagNorm
     float norm_eps;
+    // kGemvFlagWarm: the tensor the stream's next product will read.  Its rows are cut like this launch's rows, and
+    // every CTA's producer asks L2 for its cut once its own copies are out: the next launch then finds its first
+    // stages in L2 instead of waiting a DRAM round trip for them, which is most of a small product's time.
+    uint32_t warm_rows, warm_K, warm_nbp;
+    const uint8_t* warm_codes;
+    const __half* warm_scales;
 #ifdef ZK_TRACE
     unsigned long long* trace;  // [grid][16] phase stamps (profiling builds only)
 #endif
@@ -297,6 +305,16 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
             }
         }
         if (announce && lane == 0) { pdl_wait(); gather_publish_pending(p.gather); }
+        if ((p.flags & kGemvFlagWarm) && ok && lane == 0) {
+            uint32_t w_first, w_last;
+            cta_row_slice(p.warm_rows, blockIdx.x, gridDim.x, w_first, w_last);
+            const size_t code_bytes = min(static_cast<size_t>(w_last - w_first) * p.warm_K, static_cast<size_t>(kWarmCapBytes));
+            const uint8_t* src = p.warm_codes + static_cast<size_t>(w_first) * p.warm_K;   // K is a multiple of 32: 16-byte aligned
+            for (size_t off = 0; off < code_bytes; off += 32768)
+                l2_prefetch(src + off, static_cast<uint32_t>((min(code_bytes - off, static_cast<size_t>(32768)) + 15) & ~static_cast<size_t>(15)));
+            const uint32_t scale_rows = static_cast<uint32_t>(code_bytes / p.warm_K);
+            if (scale_rows) l2_prefetch(p.warm_scales + static_cast<size_t>(w_first) * p.warm_nbp, (scale_rows * p.warm_nbp * 2 + 15) & ~15u);
+        }
         // Nothing may still be landing in shared memory when the CTA exits: wait (bounded) for
         // the most recent phase of every stage that was armed.
         if (lane == 0) {

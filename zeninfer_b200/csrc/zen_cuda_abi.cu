@@ -88,6 +88,7 @@ struct State {
     float* d_x{}; size_t d_x_bytes{};
     float* d_y{}; size_t d_y_bytes{};
     uint8_t* d_gemm_ws{}; size_t d_gemm_ws_bytes{};  // quantised activations of the prefill GEMM: codes, then block-major scales
+    bool warm_hints{true};    // honour zen_cuda_gemv_fusion.warm_next (ZEN_CUDA_WARM=0 ignores the hints)
     bool gemm_stream_k{true}; // prefill GEMM: even K-tile shares when tiles do not divide the SMs (ZEN_CUDA_GEMM_STREAMK=0 turns it off)
     bool use_gemm{true};     // tensor-core prefill path (ZEN_CUDA_GEMM=0 falls back to chunks of eight tokens on the decode kernel)
     void* encode_tiled{};    // cuTensorMapEncodeTiled, resolved through the runtime
@@ -164,6 +165,7 @@ bool init_locked(State& s) {
     if (const char* m = std::getenv("ZEN_CUDA_PDL")) s.pdl = m[0] != '0';
     if (const char* m = std::getenv("ZEN_CUDA_GEMM")) s.use_gemm = m[0] != '0';
     if (const char* m = std::getenv("ZEN_CUDA_GEMM_STREAMK")) s.gemm_stream_k = m[0] != '0';
+    if (const char* m = std::getenv("ZEN_CUDA_WARM")) s.warm_hints = m[0] != '0';
     {
         cudaDriverEntryPointQueryResult qres{};
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &s.encode_tiled, cudaEnableDefault, &qres) != cudaSuccess ||
@@ -338,7 +340,8 @@ cudaError_t dispatch_batch_fuse(int batch, const zk::GemvParams& p, unsigned gri
 // Launches that carry fused work (p.flags) take the kFuse instantiation; plain products keep the lean one.
 template <int kDigits>
 cudaError_t dispatch_batch(int batch, const zk::GemvParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
-    return p.flags ? dispatch_batch_fuse<kDigits, true>(batch, p, grid, smem, st, pdl) : dispatch_batch_fuse<kDigits, false>(batch, p, grid, smem, st, pdl);
+    return (p.flags & ~zk::kGemvFlagWarm) ? dispatch_batch_fuse<kDigits, true>(batch, p, grid, smem, st, pdl)
+                                          : dispatch_batch_fuse<kDigits, false>(batch, p, grid, smem, st, pdl);
 }
 
 template <int kFormat, int kBatch>
@@ -440,7 +443,7 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
 // activation rows.  Device pointers throughout.
 bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
                   size_t tokens, int act_mode, cudaStream_t st, const zk::PeerGather* gather = nullptr, const float* d_gate = nullptr,
-                  const float* d_norm_weight = nullptr, float norm_eps = 0.0f, bool accumulate = false) {
+                  const float* d_norm_weight = nullptr, float norm_eps = 0.0f, bool accumulate = false, const zen_cuda_weights* warm_next = nullptr) {
     if (!count || count > zk::kMaxTasks || !tokens || tokens > 8 || (!d_x && !gather)) return set_error(s, "gemv: bad batch");
     if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: bad activation mode");
     zk::GemvParams p{};
@@ -464,12 +467,23 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
     if (w[0]->format != ZEN_CUDA_Q8_0) {
         if (act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: Q4_0 and Q6_K take fp32-equivalent activations only");
         if (d_gate || d_norm_weight || accumulate) return set_error(s, "gemv: fused inputs and accumulation are Q8_0 paths");
-        return enqueue_gemv_kq(s, w, d_y, count, d_x, tokens, st, gather);
+        return enqueue_gemv_kq(s, w, d_y, count, d_x, tokens, st, gather);   // a warm_next hint is not used by these kernels (measured: no gain)
     }
     if (d_gate && d_norm_weight) return set_error(s, "gemv: a fused input is either SwiGLU or RMSNorm");
     if (d_gate) { p.flags |= zk::kGemvFlagSwiglu; p.x_gate = d_gate; }
     if (d_norm_weight) { p.flags |= zk::kGemvFlagNorm; p.norm_weight = d_norm_weight; p.norm_eps = norm_eps; }
     if (accumulate) p.flags |= zk::kGemvFlagAccumulate;
+    // A hint, honoured where it pays: a launch that streams more than kWarmMaxLaunchBytes keeps HBM busy by itself, and a
+    // prefetch for its successor then only competes with it (measured: -0.5 us for a 26.8 MB launch, +1.2 us for 62 MB).
+    constexpr size_t kWarmMaxLaunchBytes = size_t(32) << 20;
+    if (s.warm_hints && warm_next && warm_next->format == ZEN_CUDA_Q8_0 && static_cast<size_t>(total_rows) * w[0]->cols <= kWarmMaxLaunchBytes) {
+        p.flags |= zk::kGemvFlagWarm;
+        p.warm_codes = static_cast<const uint8_t*>(warm_next->plane[0]);
+        p.warm_scales = static_cast<const __half*>(warm_next->plane[1]);
+        p.warm_rows = static_cast<uint32_t>(warm_next->rows);
+        p.warm_K = static_cast<uint32_t>(warm_next->cols);
+        p.warm_nbp = warm_next->nbp;
+    }
     p.ntasks = static_cast<uint32_t>(count);
     p.total_rows = total_rows;
     p.x = d_x;
@@ -1035,7 +1049,7 @@ int zen_cuda_dev_gemv_fused(const zen_cuda_weights* const* w, float* const* d_y,
     if (!init_locked(s)) return 0;
     if (!w || !d_y || !d_x || !fusion) return set_error(s, "dev_gemv_fused: bad arguments") ? 1 : 0;
     return enqueue_gemv(s, w, d_y, count, d_x, tokens, act_mode, stream ? static_cast<cudaStream_t>(stream) : s.stream, nullptr, fusion->gate,
-                        fusion->norm_weight, fusion->norm_eps, fusion->accumulate != 0) ? 1 : 0;
+                        fusion->norm_weight, fusion->norm_eps, fusion->accumulate != 0, fusion->warm_next) ? 1 : 0;
 }
 
 size_t zen_cuda_gemm_workspace_bytes(size_t tokens, size_t columns) { return gemm_ws_bytes(tokens, columns); }
@@ -1323,6 +1337,51 @@ int zen_cuda_dev_attention_block(const float* d_q, const float* d_k, const float
     ZC_DEV_ENTER("dev_attention_block");
     return enqueue_attention(s, st, true, d_q, d_k, d_v, d_cos, d_sin, pairs, d_pos, d_k_cache, d_v_cache, d_out, heads, kv_heads, head_dim, scale, window,
                              max_positions) ? 1 : 0;
+}
+
+int zen_cuda_dev_embed_rows_q8_0(const zen_cuda_weights* w, const int64_t* d_tokens, size_t tokens, float* d_out, void* stream) {
+    ZC_DEV_ENTER("dev_embed_rows_q8_0");
+    if (!w || !d_tokens || !tokens || tokens > 65535 || !d_out || w->format != ZEN_CUDA_Q8_0) return set_error(s, "dev_embed_rows_q8_0: bad arguments") ? 1 : 0;
+    const cudaError_t e = launch_pdl(s, zk::embed_rows_q8_0_kernel, dim3(static_cast<unsigned>((w->cols + 255) / 256), static_cast<unsigned>(tokens)), dim3(256), 0, st,
+        static_cast<const int8_t*>(w->plane[0]), static_cast<const __half*>(w->plane[1]), static_cast<uint32_t>(w->rows), static_cast<uint32_t>(w->cols),
+        w->nbp, reinterpret_cast<const long long*>(d_tokens), d_out, s.d_error);
+    ZC_DEV_LEAVE(e);
+}
+
+int zen_cuda_dev_rope_kv_append_rows(float* d_q, float* d_k, const float* d_v, size_t tokens, const float* d_cos, const float* d_sin, const int* d_pos,
+                                     size_t heads, size_t kv_heads, size_t head_dim, size_t pairs, int adjacent, float* d_k_cache, float* d_v_cache,
+                                     size_t max_positions, void* stream) {
+    ZC_DEV_ENTER("dev_rope_kv_append_rows");
+    if (!d_q || !d_k || !d_v || !tokens || tokens > 65535 || !d_cos || !d_sin || !d_pos || !d_k_cache || !d_v_cache || !heads || !kv_heads || !head_dim ||
+        2 * pairs > head_dim || !max_positions)
+        return set_error(s, "dev_rope_kv_append_rows: bad arguments") ? 1 : 0;
+    const cudaError_t e = launch_pdl(s, zk::rope_kv_append_rows_kernel, dim3(static_cast<unsigned>(tokens)), dim3(1024), 0, st, d_q, d_k, d_v, d_cos, d_sin, d_pos,
+                                     static_cast<uint32_t>(heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(head_dim),
+                                     static_cast<uint32_t>(pairs), adjacent, d_k_cache, d_v_cache, static_cast<uint32_t>(max_positions), s.d_error);
+    ZC_DEV_LEAVE(e);
+}
+
+int zen_cuda_dev_attention_prefill(const float* d_q, const float* d_k_cache, const float* d_v_cache, const int* d_pos, float* d_out, size_t tokens,
+                                   size_t heads, size_t kv_heads, size_t head_dim, float scale, size_t window, size_t max_positions, void* stream) {
+    ZC_DEV_ENTER("dev_attention_prefill");
+    if (!d_q || !d_k_cache || !d_v_cache || !d_pos || !d_out || !tokens || !heads || !kv_heads || heads % kv_heads || kv_heads > 65535 || !max_positions ||
+        (head_dim != 64 && head_dim != 128 && head_dim != 256))
+        return set_error(s, "dev_attention_prefill: bad arguments (head_dim 64, 128 or 256)") ? 1 : 0;
+    if (scale == 0.0f) scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
+    const dim3 grid(static_cast<unsigned>((tokens + zk::kPfTokens - 1) / zk::kPfTokens), static_cast<unsigned>(kv_heads)), block(zk::kPfThreads);
+    const size_t smem = 2 * zk::kPfBlock * head_dim * sizeof(float);
+    auto launch = [&](auto kernel) {
+        static bool configured = false;   // one static per instantiation of this lambda's call operator
+        if (!configured && smem > 48 * 1024) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return cudaErrorInvalidValue;
+            configured = true;
+        }
+        return launch_pdl(s, kernel, grid, block, smem, st, d_q, d_k_cache, d_v_cache, d_pos, d_out, static_cast<uint32_t>(tokens), static_cast<uint32_t>(heads),
+                          static_cast<uint32_t>(kv_heads), scale, static_cast<uint32_t>(window), static_cast<uint32_t>(max_positions), s.d_error);
+    };
+    const cudaError_t e = head_dim == 64 ? launch(zk::attention_prefill_kernel<64>) : head_dim == 128 ? launch(zk::attention_prefill_kernel<128>)
+                                                                                                      : launch(zk::attention_prefill_kernel<256>);
+    ZC_DEV_LEAVE(e);
 }
 
 int zen_cuda_dev_silu_mul(const float* d_gate, const float* d_up, float* d_out, size_t count, void* stream) {

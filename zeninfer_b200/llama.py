@@ -114,7 +114,7 @@ class LlamaDecoder:
                 rows, cols = shapes[name]
                 self.h[name] = backend.dev_upload("Q8_0", arr, rows, cols)
             else:
-                self.norm[name] = torch.from_numpy(np.ascontiguousarray(arr, np.float32)).to(self.dev)
+                self.norm[name] = torch.from_numpy(np.array(arr, np.float32)).to(self.dev)   # a copy: the source may be a read-only file mapping
         missing = [n for n, _, m in tensor_plan(cfg) if (m and n not in self.h) or (not m and n not in self.norm)]
         if missing:
             raise ValueError(f"model is missing tensors: {missing[:4]}...")
@@ -144,8 +144,13 @@ class LlamaDecoder:
             return cls(backend, cfg, gguf.llama_tensors(g, cfg), **kwargs)   # uploads complete before the mapping closes
 
     # ---- one token step, as launches on self.stream ----
+    def _gemv(self, handles, outs, x, *, norm=None, gate=None, acc=False, warm=None) -> None:
+        """One product launch on the decoder's stream; `warm` is the tensor the next product launch will read."""
+        self.be.dev_gemv_fused(handles, outs, x, 1, self.act_mode, self.stream.cuda_stream, norm_weight=norm, norm_eps=self.cfg.rms_eps if norm else 0.0,
+                               gate=gate, accumulate=acc, warm_next=warm)
+
     def _enqueue_layers(self) -> None:
-        be, cfg, st, mode = self.be, self.cfg, self.stream.cuda_stream, self.act_mode
+        be, cfg, st = self.be, self.cfg, self.stream.cuda_stream
         P = lambda t: t.data_ptr()
         E, eps = cfg.embedding, cfg.rms_eps
         fn, fs, fr = "n" in self.fuse, "s" in self.fuse, "r" in self.fuse
@@ -155,35 +160,25 @@ class LlamaDecoder:
             be.dev_rms_norm(P(self.x), None, P(self.norm["blk.0.attn_norm.weight"]), P(self.xn), E, 1, eps, st)
         for layer in range(cfg.layers):
             p = f"blk.{layer}."
+            nxt_q = self.h[f"blk.{layer + 1}.attn_q.weight"] if layer + 1 < cfg.layers else self.h["output.weight"]
             qkv = [self.h[p + "attn_q.weight"], self.h[p + "attn_k.weight"], self.h[p + "attn_v.weight"]]
-            qkv_out = [P(self.q), P(self.k), P(self.v)]
-            if fn:
-                be.dev_gemv_fused(qkv, qkv_out, P(self.x), 1, mode, st, norm_weight=P(self.norm[p + "attn_norm.weight"]), norm_eps=eps)
-            else:
-                be.dev_gemv(qkv, qkv_out, P(self.xn), 1, mode, st)
+            self._gemv(qkv, [P(self.q), P(self.k), P(self.v)], P(self.x) if fn else P(self.xn),
+                       norm=P(self.norm[p + "attn_norm.weight"]) if fn else None, warm=self.h[p + "attn_output.weight"])
             be.dev_attention_block(P(self.q), P(self.k), P(self.v), P(self.cos), P(self.sin), cfg.head_dim // 2, P(self.pos), P(self.k_cache[layer]),
                                    P(self.v_cache[layer]), P(self.att), cfg.heads, cfg.kv_heads, cfg.head_dim, self.max_positions, 0.0, 0, st)
-            # attention output projection and its residual add
-            o = [self.h[p + "attn_output.weight"]]
-            if fr:
-                be.dev_gemv_fused(o, [P(self.x)], P(self.att), 1, mode, st, accumulate=True)                     # x += o(att)
-            else:
-                be.dev_gemv(o, [P(self.tmp)], P(self.att), 1, mode, st)
+            # attention output projection and its residual add (x += o(att))
+            self._gemv([self.h[p + "attn_output.weight"]], [P(self.x) if fr else P(self.tmp)], P(self.att), acc=fr, warm=self.h[p + "ffn_gate.weight"])
             # ffn norm (with the residual add when it was not folded into the store)
             if not fn:
                 be.dev_rms_norm(P(self.x), None if fr else P(self.tmp), P(self.norm[p + "ffn_norm.weight"]), P(self.xn), E, 1, eps, st)
             elif not fr:
                 be.dev_rms_norm(P(self.x), P(self.tmp), None, None, E, 1, eps, st)                                 # x += tmp only
-            gate_up = [self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]]
-            if fn:
-                be.dev_gemv_fused(gate_up, [P(self.gate), P(self.up)], P(self.x), 1, mode, st, norm_weight=P(self.norm[p + "ffn_norm.weight"]), norm_eps=eps)
-            else:
-                be.dev_gemv(gate_up, [P(self.gate), P(self.up)], P(self.xn), 1, mode, st)
-            down = [self.h[p + "ffn_down.weight"]]
+            self._gemv([self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]], [P(self.gate), P(self.up)], P(self.x) if fn else P(self.xn),
+                       norm=P(self.norm[p + "ffn_norm.weight"]) if fn else None, warm=self.h[p + "ffn_down.weight"])
             if not fs:
                 be.dev_silu_mul(P(self.gate), P(self.up), P(self.hid), cfg.ffn, st)
-            be.dev_gemv_fused(down, [P(self.x) if fr else P(self.tmp)], P(self.up) if fs else P(self.hid), 1, mode, st,
-                              gate=P(self.gate) if fs else None, accumulate=fr)                                   # (x +=) down(silu(gate) * up)
+            self._gemv([self.h[p + "ffn_down.weight"]], [P(self.x) if fr else P(self.tmp)], P(self.up) if fs else P(self.hid),
+                       gate=P(self.gate) if fs else None, acc=fr, warm=nxt_q)                                      # (x +=) down(silu(gate) * up)
             # the next norm: the next layer's attention norm, or the output norm
             nxt = self.norm[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < cfg.layers else self.norm["output_norm.weight"]
             if not fn:
@@ -193,13 +188,10 @@ class LlamaDecoder:
         be.dev_advance_position(P(self.pos), 1, st)
 
     def _enqueue_head(self) -> None:
-        be, st = self.be, self.stream.cuda_stream
-        if "n" in self.fuse:
-            be.dev_gemv_fused([self.h["output.weight"]], [self.logits.data_ptr()], self.x.data_ptr(), 1, self.act_mode, st,
-                              norm_weight=self.norm["output_norm.weight"].data_ptr(), norm_eps=self.cfg.rms_eps)
-        else:
-            be.dev_gemv([self.h["output.weight"]], [self.logits.data_ptr()], self.xn.data_ptr(), 1, self.act_mode, st)
-        be.dev_greedy_pick([(self.logits.data_ptr(), self.cfg.vocab, 0, self.cfg.vocab)], 1, self.token.data_ptr(), st)
+        fn = "n" in self.fuse
+        self._gemv([self.h["output.weight"]], [self.logits.data_ptr()], self.x.data_ptr() if fn else self.xn.data_ptr(),
+                   norm=self.norm["output_norm.weight"].data_ptr() if fn else None, warm=self.h["blk.0.attn_q.weight"])
+        self.be.dev_greedy_pick([(self.logits.data_ptr(), self.cfg.vocab, 0, self.cfg.vocab)], 1, self.token.data_ptr(), self.stream.cuda_stream)
 
     def capture(self) -> None:
         """Runs one throw-away step (kernel attributes are set on first launch), then captures the two graphs."""
@@ -235,19 +227,85 @@ class LlamaDecoder:
                 if want_token:
                     self._enqueue_head()
 
-    def generate(self, prompt: list[int], max_new: int, on_token=None) -> list[int]:
-        """Greedy generation: the prompt token by token, then max_new picks (each read back, as the reference's
-        per-token callback does).  Raises when the context would overflow."""
+    # ---- prefill: a block of prompt tokens through the tensor-core products ----
+    PREFILL_CHUNK = 512     # tokens per block (buffers are sized for it)
+    PREFILL_MIN = 16        # shorter blocks go token by token
+
+    def _prefill_buffers(self):
+        if getattr(self, "_pf", None) is None:
+            torch, cfg, T = self.torch, self.cfg, self.PREFILL_CHUNK
+            f32 = dict(dtype=torch.float32, device=self.dev)
+            ws_bytes = max(self.be.gemm_workspace_bytes(T, cfg.embedding), self.be.gemm_workspace_bytes(T, cfg.ffn), self.be.gemm_workspace_bytes(T, cfg.q_width))
+            self._pf = dict(x=torch.zeros((T, cfg.embedding), **f32), xn=torch.zeros((T, cfg.embedding), **f32), tmp=torch.zeros((T, cfg.embedding), **f32),
+                            q=torch.zeros((T, cfg.q_width), **f32), k=torch.zeros((T, cfg.kv_width), **f32), v=torch.zeros((T, cfg.kv_width), **f32),
+                            att=torch.zeros((T, cfg.q_width), **f32), gate=torch.zeros((T, cfg.ffn), **f32), up=torch.zeros((T, cfg.ffn), **f32),
+                            hid=torch.zeros((T, cfg.ffn), **f32), ws=torch.zeros(ws_bytes, dtype=torch.uint8, device=self.dev), ws_bytes=ws_bytes)
+        return self._pf
+
+    def prefill(self, d_tokens, count: int) -> None:
+        """Consumes `count` tokens (device int64) at positions pos .. pos + count - 1 as one block: the projections run
+        as tcgen05 GEMMs (int8 activations), the attention as the causal block kernel; afterwards the residual stream and
+        its normalised copy of the LAST token are in self.x / self.xn, ready for the lm_head, and pos has advanced."""
+        be, cfg, st = self.be, self.cfg, self.stream.cuda_stream
+        b = self._prefill_buffers()
+        P = lambda t: t.data_ptr()
+        T, E, eps = count, cfg.embedding, cfg.rms_eps
+        gemm = lambda hs, outs, x: be.dev_gemm_q8_0(hs, [P(o) for o in outs], P(x), T, P(b["ws"]), b["ws_bytes"], st)
+        be.dev_embed_rows_q8_0(self.h["token_embd.weight"], P(d_tokens), T, P(b["x"]), st)
+        be.dev_rms_norm(P(b["x"]), None, P(self.norm["blk.0.attn_norm.weight"]), P(b["xn"]), E, T, eps, st)
+        for layer in range(cfg.layers):
+            p = f"blk.{layer}."
+            gemm([self.h[p + "attn_q.weight"], self.h[p + "attn_k.weight"], self.h[p + "attn_v.weight"]], [b["q"], b["k"], b["v"]], b["xn"])
+            be.dev_rope_kv_append_rows(P(b["q"]), P(b["k"]), P(b["v"]), T, P(self.cos), P(self.sin), P(self.pos), cfg.heads, cfg.kv_heads, cfg.head_dim,
+                                       cfg.head_dim // 2, True, P(self.k_cache[layer]), P(self.v_cache[layer]), self.max_positions, st)
+            be.dev_attention_prefill(P(b["q"]), P(self.k_cache[layer]), P(self.v_cache[layer]), P(self.pos), P(b["att"]), T, cfg.heads, cfg.kv_heads,
+                                     cfg.head_dim, self.max_positions, 0.0, 0, st)
+            gemm([self.h[p + "attn_output.weight"]], [b["tmp"]], b["att"])
+            be.dev_rms_norm(P(b["x"]), P(b["tmp"]), P(self.norm[p + "ffn_norm.weight"]), P(b["xn"]), E, T, eps, st)          # x += o; xn = norm(x)
+            gemm([self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]], [b["gate"], b["up"]], b["xn"])
+            be.dev_silu_mul(P(b["gate"]), P(b["up"]), P(b["hid"]), T * cfg.ffn, st)
+            gemm([self.h[p + "ffn_down.weight"]], [b["tmp"]], b["hid"])
+            nxt = self.norm[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < cfg.layers else self.norm["output_norm.weight"]
+            be.dev_rms_norm(P(b["x"]), P(b["tmp"]), P(nxt), P(b["xn"]), E, T, eps, st)                                       # x += down; xn = next norm
+        be.dev_advance_position(P(self.pos), T, st)
+        with self.torch.cuda.stream(self.stream):
+            self.x.copy_(b["x"][T - 1])
+            self.xn.copy_(b["xn"][T - 1])
+
+    def feed_prompt(self, prompt: list[int], batched_prefill: bool | None = None) -> None:
+        """Enqueues the whole prompt from position self.pos on, ending with the first pick (left in self.token).  Blocks of
+        at least PREFILL_MIN tokens go through prefill() when batched_prefill (default: when the decoder computes with
+        int8 activations), the rest token by token."""
+        torch = self.torch
+        ids = torch.tensor(prompt, dtype=torch.int64).pin_memory()
+        if batched_prefill is None:
+            batched_prefill = self.act_mode == ACT_INT8
+        with torch.cuda.stream(self.stream):
+            done = 0
+            if batched_prefill and len(prompt) >= self.PREFILL_MIN:
+                d_ids = ids.to(self.dev, non_blocking=True)
+                while len(prompt) - done >= self.PREFILL_MIN:
+                    n = min(self.PREFILL_CHUNK, len(prompt) - done)
+                    self.prefill(d_ids[done:done + n], n)
+                    done += n
+                if done == len(prompt):
+                    self._enqueue_head()      # the first pick, from the last prompt token's hidden state
+            for i in range(done, len(prompt)):
+                self.token.copy_(ids[i:i + 1], non_blocking=True)
+                self.step(want_token=(i + 1 == len(prompt)))
+
+    def generate(self, prompt: list[int], max_new: int, on_token=None, batched_prefill: bool | None = None) -> list[int]:
+        """Greedy generation: the prompt, then max_new picks (each read back, as the reference's per-token callback
+        does).  The prompt goes through prefill() in blocks when the decoder computes with int8 activations (the
+        tensor-core product has no fp32-equivalent mode), token by token otherwise; batched_prefill overrides the choice.
+        Raises when the context would overflow."""
         torch = self.torch
         if not prompt or len(prompt) + max_new > self.max_positions:
             raise ValueError("prompt + max_new exceeds the configured positions")
         self.reset()
-        ids = torch.tensor(prompt, dtype=torch.int64).pin_memory()
         out: list[int] = []
         with torch.cuda.stream(self.stream):
-            for i in range(len(prompt)):
-                self.token.copy_(ids[i:i + 1], non_blocking=True)
-                self.step(want_token=(i + 1 == len(prompt)))
+            self.feed_prompt(prompt, batched_prefill)
             for n in range(max_new):
                 tok = int(self.token.item())      # device -> host read of the step's result
                 out.append(tok)
