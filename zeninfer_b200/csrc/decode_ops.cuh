@@ -385,11 +385,31 @@ __global__ void __launch_bounds__(1024) rope_kv_append_rows_kernel(float* __rest
 // Causal grouped-query attention for a block of T new tokens whose keys and values are already in the caches.
 // Grid (ceil(T / kPfTokens), kv_heads): a CTA takes kPfTokens consecutive tokens and all query heads of one KV head,
 // so that a key/value row staged in shared memory serves every query row of the group.  A query row (token, head) is
-// held by kPfLanes threads, D / kPfLanes dimensions each; keys and values come through shared memory in blocks of
-// kPfBlock positions; the softmax is the running-maximum form (out and denominator rescaled when the maximum moves),
-// which equals the reference's two-pass form up to rounding (attention rows of forward_batch, :3041-3570).
+// held by kPfLanes threads; thread `part` of a row owns the float4 columns part, part + kPfLanes, ... of the head, so
+// that the row's threads read consecutive 16-byte words of a staged key or value row (no bank conflict; the rows of a
+// warp read the same words, a broadcast).  Products and accumulations are packed fp32 pairs (fma.rn.f32x2: each half
+// is an IEEE fused multiply-add).  Keys and values come through shared memory in blocks of kPfBlock positions; the
+// softmax is the running-maximum form (out and denominator rescaled when the maximum moves), which equals the
+// reference's two-pass form up to rounding (attention rows of forward_batch, :3041-3570).
 // Token t attends positions [first, pos0 + t], first = the sliding-window start or 0.
+// Heavy tiles (late tokens, long key ranges) take the low block indices so that they are scheduled first.
 constexpr int kPfTokens = 16, kPfLanes = 4, kPfBlock = 32, kPfThreads = 256;
+__device__ __forceinline__ uint64_t pf_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void pf_unpack(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t pf_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t pf_mul(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
 template <int D>   // head dimension: 64, 128 or 256 (a compile-time constant keeps the row's registers registers)
 __global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                                         const float* __restrict__ v_cache, const int* __restrict__ pos_ptr,
@@ -405,10 +425,10 @@ __global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(const flo
     }
     const uint32_t group = heads / kv_heads, kh = blockIdx.y, kw = kv_heads * D, qw = heads * D;
     const uint32_t rows_per_cta = kPfTokens * group;                 // query rows: (token, head of the group)
-    constexpr int per = D / kPfLanes;                                 // dimensions per thread
+    constexpr int per4 = D / (4 * kPfLanes);                          // float4 columns per thread
     float* ks = kv_smem;
     float* vs = kv_smem + kPfBlock * D;
-    const uint32_t t0 = blockIdx.x * kPfTokens;
+    const uint32_t t0 = (gridDim.x - 1 - blockIdx.x) * kPfTokens;    // the last tokens first
     const uint32_t t_end = min(tokens, t0 + kPfTokens);
     // the span of positions any row of this CTA attends
     const uint32_t last_pos = static_cast<uint32_t>(pos0) + t_end - 1;
@@ -419,14 +439,19 @@ __global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(const flo
         const bool live = r < rows_per_cta && t < t_end;
         const uint32_t my_last = static_cast<uint32_t>(pos0) + t;
         const uint32_t my_first = (window && my_last + 1 > window) ? my_last + 1 - window : 0u;
-        float qv[per], acc[per];
+        uint64_t q01[per4], q23[per4], a01[per4], a23[per4];
         float m = -INFINITY;
         double l = 0.0;
 #pragma unroll
-        for (int i = 0; i < per; ++i) { qv[i] = 0.0f; acc[i] = 0.0f; }
+        for (int i = 0; i < per4; ++i) { q01[i] = q23[i] = a01[i] = a23[i] = pf_pack(0.0f, 0.0f); }
         if (live) {
+            const float4* qrow = reinterpret_cast<const float4*>(q + static_cast<size_t>(t) * qw + static_cast<size_t>(h) * D) + part;
 #pragma unroll
-            for (int i = 0; i < per; ++i) qv[i] = q[static_cast<size_t>(t) * qw + static_cast<size_t>(h) * D + part * per + i];
+            for (int i = 0; i < per4; ++i) {
+                const float4 v = qrow[i * kPfLanes];
+                q01[i] = pf_pack(v.x, v.y);
+                q23[i] = pf_pack(v.z, v.w);
+            }
         }
         for (uint32_t p0 = first_any; p0 <= last_pos; p0 += kPfBlock) {
             __syncthreads();                                            // the previous block's rows are no longer read
@@ -441,26 +466,43 @@ __global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(const flo
                 reinterpret_cast<float4*>(vs)[i] = vv;
             }
             __syncthreads();
-            for (uint32_t j = 0; j < kPfBlock; ++j) {
+            const uint32_t j_end = min(static_cast<uint32_t>(kPfBlock), last_pos - p0 + 1);
+            for (uint32_t j = 0; j < j_end; ++j) {
                 const uint32_t pos = p0 + j;
-                float dot = 0.0f;
+                const float4* krow = reinterpret_cast<const float4*>(ks + j * D) + part;
+                uint64_t d01 = pf_pack(0.0f, 0.0f), d23 = d01;
 #pragma unroll
-                for (int i = 0; i < per; ++i) dot += qv[i] * ks[j * D + part * per + i];
+                for (int i = 0; i < per4; ++i) {
+                    const float4 kk = krow[i * kPfLanes];
+                    d01 = pf_fma(q01[i], pf_pack(kk.x, kk.y), d01);
+                    d23 = pf_fma(q23[i], pf_pack(kk.z, kk.w), d23);
+                }
+                float d0, d1, d2, d3;
+                pf_unpack(d01, d0, d1);
+                pf_unpack(d23, d2, d3);
+                float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
                 for (int o = kPfLanes / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
                 if (live && pos >= my_first && pos <= my_last) {        // uniform over the row's kPfLanes threads
                     const float sc = dot * scale;
                     if (sc > m) {                                       // the maximum moves: rescale what has been summed
                         const float f = expf(m - sc);                   // exp(-inf) = 0 on the first position
+                        const uint64_t f2 = pf_pack(f, f);
                         l *= f;
 #pragma unroll
-                        for (int i = 0; i < per; ++i) acc[i] *= f;
+                        for (int i = 0; i < per4; ++i) { a01[i] = pf_mul(a01[i], f2); a23[i] = pf_mul(a23[i], f2); }
                         m = sc;
                     }
                     const float e = expf(sc - m);
+                    const uint64_t e2 = pf_pack(e, e);
                     l += e;
+                    const float4* vrow = reinterpret_cast<const float4*>(vs + j * D) + part;
 #pragma unroll
-                    for (int i = 0; i < per; ++i) acc[i] += e * vs[j * D + part * per + i];
+                    for (int i = 0; i < per4; ++i) {
+                        const float4 vv = vrow[i * kPfLanes];
+                        a01[i] = pf_fma(e2, pf_pack(vv.x, vv.y), a01[i]);
+                        a23[i] = pf_fma(e2, pf_pack(vv.z, vv.w), a23[i]);
+                    }
                 }
             }
         }
@@ -469,8 +511,15 @@ __global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(const flo
                 if (part == 0) atomicExch(error_word, kErrNonFinite);
             } else {
                 const float inv = 1.0f / static_cast<float>(l);
+                float4* orow = reinterpret_cast<float4*>(out + static_cast<size_t>(t) * qw + static_cast<size_t>(h) * D) + part;
 #pragma unroll
-                for (int i = 0; i < per; ++i) out[static_cast<size_t>(t) * qw + static_cast<size_t>(h) * D + part * per + i] = acc[i] * inv;
+                for (int i = 0; i < per4; ++i) {
+                    float4 o;
+                    pf_unpack(a01[i], o.x, o.y);
+                    pf_unpack(a23[i], o.z, o.w);
+                    o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
+                    orow[i * kPfLanes] = o;
+                }
             }
         }
     }
