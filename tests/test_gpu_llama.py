@@ -311,7 +311,8 @@ def test_warm_next_hint_changes_no_result(be, zo):
         be.dev_free(hh)
 
 
-@pytest.mark.parametrize("H,KH,D,T,pos0,window", [(4, 2, 64, 37, 5, 0), (8, 8, 128, 16, 0, 0), (32, 8, 128, 70, 100, 0), (4, 1, 64, 33, 3, 12), (2, 1, 256, 20, 7, 0)])
+@pytest.mark.parametrize("H,KH,D,T,pos0,window", [(4, 2, 64, 37, 5, 0), (8, 8, 128, 16, 0, 0), (32, 8, 128, 70, 100, 0), (4, 1, 64, 33, 3, 12), (2, 1, 256, 20, 7, 0),
+                                                  (3, 1, 64, 21, 2, 0), (12, 2, 128, 40, 9, 0), (4, 1, 256, 18, 0, 0)])
 def test_attention_prefill_block(be, H, KH, D, T, pos0, window):
     import torch
     P = 256

@@ -383,17 +383,29 @@ __global__ void __launch_bounds__(1024) rope_kv_append_rows_kernel(float* __rest
 }
 
 // Causal grouped-query attention for a block of T new tokens whose keys and values are already in the caches.
-// Grid (ceil(T / kPfTokens), kv_heads): a CTA takes kPfTokens consecutive tokens and all query heads of one KV head,
-// so that a key/value row staged in shared memory serves every query row of the group.  A query row (token, head) is
-// held by kPfLanes threads; thread `part` of a row owns the float4 columns part, part + kPfLanes, ... of the head, so
-// that the row's threads read consecutive 16-byte words of a staged key or value row (no bank conflict; the rows of a
-// warp read the same words, a broadcast).  Products and accumulations are packed fp32 pairs (fma.rn.f32x2: each half
-// is an IEEE fused multiply-add).  Keys and values come through shared memory in blocks of kPfBlock positions; the
-// softmax is the running-maximum form (out and denominator rescaled when the maximum moves), which equals the
-// reference's two-pass form up to rounding (attention rows of forward_batch, :3041-3570).
-// Token t attends positions [first, pos0 + t], first = the sliding-window start or 0.
-// Heavy tiles (late tokens, long key ranges) take the low block indices so that they are scheduled first.
-constexpr int kPfTokens = 16, kPfLanes = 4, kPfBlock = 32, kPfThreads = 256;
+// A CTA takes kPfTokens consecutive tokens, one KV head and R query heads of that KV head's group (R = 4, 2 or 1, the
+// largest that divides the group and keeps the rows in registers).  A token is held by kPfLanes threads; thread `part`
+// owns the float4 columns part, part + kPfLanes, ... of the head and keeps them for all R heads, so a key or value word
+// read from shared memory feeds R multiply-adds (shared-memory bandwidth, 128 bytes per clock per SM, bounds this
+// kernel otherwise) and the token's threads read consecutive 16-byte words (no bank conflict).  Products and
+// accumulations are packed fp32 pairs (fma.rn.f32x2: each half is an IEEE fused multiply-add).  Keys and values come
+// through shared memory in blocks of kPfBlock positions; the softmax is the running-maximum form (out and denominator
+// rescaled when the maximum moves), which equals the reference's two-pass form up to rounding (attention rows of
+// forward_batch, :3041-3570).  Token t attends positions [first, pos0 + t], first = the sliding-window start or 0.
+// The grid is one-dimensional and ordered by work: the tiles of the last tokens (the longest key ranges) take the low
+// block indices and start first.
+#ifndef ZK_PF_STEP
+#define ZK_PF_STEP 4
+#endif
+constexpr int kPfTokens = 16, kPfLanes = 8, kPfBlock = 32, kPfThreads = kPfTokens * kPfLanes, kPfStep = ZK_PF_STEP;
+static_assert(kPfBlock % kPfStep == 0, "a round of positions must not straddle two staged blocks");
+// 16-byte asynchronous copy global -> shared (bypassing L1); `bytes` = 16, or 0 for a zero fill.
+__device__ __forceinline__ void cp_async_16(float* smem_dst, const float* gmem_src, uint32_t bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
 __device__ __forceinline__ uint64_t pf_pack(float lo, float hi) {
     uint64_t r;
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
@@ -410,116 +422,206 @@ __device__ __forceinline__ uint64_t pf_mul(uint64_t a, uint64_t b) {
     asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
-template <int D>   // head dimension: 64, 128 or 256 (a compile-time constant keeps the row's registers registers)
+// The lane (within a token's kPfLanes) that ends the score reduction with head r's sum and keeps that row's softmax state.
+template <int R>
+__device__ __forceinline__ constexpr int pf_owner(int r) { return R == 4 ? ((r >> 1) * 4 + (r & 1) * 2) : R == 2 ? r * 4 : 0; }
+template <int D, int R>   // head dimension (64, 128 or 256) and query heads per thread: compile-time, so the rows stay in registers
 __global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(const float* __restrict__ q, const float* __restrict__ k_cache,
                                                                         const float* __restrict__ v_cache, const int* __restrict__ pos_ptr,
                                                                         float* __restrict__ out, uint32_t tokens, uint32_t heads, uint32_t kv_heads,
                                                                         float scale, uint32_t window, uint32_t max_positions, int* error_word) {
-    extern __shared__ __align__(16) float kv_smem[];      // [2][kPfBlock][D]: keys, then values
+    extern __shared__ __align__(16) float kv_smem[];      // two buffers of [2][kPfBlock][D]: keys, then values
     pdl_launch_dependents();
     pdl_wait();
     const int pos0 = *pos_ptr;
     if (pos0 < 0 || static_cast<uint32_t>(pos0) + tokens > max_positions) {
-        if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicExch(error_word, kErrBadPosition);
+        if (threadIdx.x == 0 && blockIdx.x == 0) atomicExch(error_word, kErrBadPosition);
         return;
     }
-    const uint32_t group = heads / kv_heads, kh = blockIdx.y, kw = kv_heads * D, qw = heads * D;
-    const uint32_t rows_per_cta = kPfTokens * group;                 // query rows: (token, head of the group)
-    constexpr int per4 = D / (4 * kPfLanes);                          // float4 columns per thread
-    float* ks = kv_smem;
-    float* vs = kv_smem + kPfBlock * D;
-    const uint32_t t0 = (gridDim.x - 1 - blockIdx.x) * kPfTokens;    // the last tokens first
+    const uint32_t group = heads / kv_heads, passes = group / R, kw = kv_heads * D, qw = heads * D;
+    const uint32_t per_tile = kv_heads * passes, n_tiles = gridDim.x / per_tile;
+    const uint32_t tile = n_tiles - 1 - blockIdx.x / per_tile, rem = blockIdx.x % per_tile;
+    const uint32_t kh = rem / passes, h0 = kh * group + (rem % passes) * R;      // this CTA's heads: h0 .. h0 + R - 1
+    constexpr int per4 = D / (4 * kPfLanes);                          // float4 columns per thread and head
+    const uint32_t t0 = tile * kPfTokens;
     const uint32_t t_end = min(tokens, t0 + kPfTokens);
-    // the span of positions any row of this CTA attends
+    // the span of positions any token of this CTA attends
     const uint32_t last_pos = static_cast<uint32_t>(pos0) + t_end - 1;
     const uint32_t first_any = (window && static_cast<uint32_t>(pos0) + t0 + 1 > window) ? static_cast<uint32_t>(pos0) + t0 + 1 - window : 0u;
-    for (uint32_t r0 = 0; r0 < rows_per_cta; r0 += kPfThreads / kPfLanes) {   // passes when the group has more rows than row slots
-        const uint32_t r = r0 + threadIdx.x / kPfLanes, part = threadIdx.x % kPfLanes;
-        const uint32_t t = t0 + r / group, h = kh * group + r % group;
-        const bool live = r < rows_per_cta && t < t_end;
-        const uint32_t my_last = static_cast<uint32_t>(pos0) + t;
-        const uint32_t my_first = (window && my_last + 1 > window) ? my_last + 1 - window : 0u;
-        uint64_t q01[per4], q23[per4], a01[per4], a23[per4];
-        float m = -INFINITY;
-        double l = 0.0;
+    const uint32_t t = t0 + threadIdx.x / kPfLanes, part = threadIdx.x % kPfLanes;
+    const bool live = t < t_end;
+    const uint32_t my_last = static_cast<uint32_t>(pos0) + t;
+    const uint32_t my_first = (window && my_last + 1 > window) ? my_last + 1 - window : 0u;
+    uint64_t q01[R][per4], q23[R][per4], a01[R][per4], a23[R][per4];
+    // The softmax state of a row lives in one lane: the score reduction below leaves the token's lane `part` with the
+    // full sum of head my_row, and that lane keeps the row's running maximum and denominator.
+    const uint32_t my_row = R == 4 ? ((part >> 2) << 1 | ((part >> 1) & 1)) : R == 2 ? (part >> 2) : 0u;
+    float m = -INFINITY;
+    double l = 0.0;
 #pragma unroll
-        for (int i = 0; i < per4; ++i) { q01[i] = q23[i] = a01[i] = a23[i] = pf_pack(0.0f, 0.0f); }
-        if (live) {
-            const float4* qrow = reinterpret_cast<const float4*>(q + static_cast<size_t>(t) * qw + static_cast<size_t>(h) * D) + part;
+    for (int r = 0; r < R; ++r) {
+#pragma unroll
+        for (int i = 0; i < per4; ++i) { q01[r][i] = q23[r][i] = a01[r][i] = a23[r][i] = pf_pack(0.0f, 0.0f); }
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float4* qrow = reinterpret_cast<const float4*>(q + static_cast<size_t>(t) * qw + static_cast<size_t>(h0 + r) * D) + part;
 #pragma unroll
             for (int i = 0; i < per4; ++i) {
                 const float4 v = qrow[i * kPfLanes];
-                q01[i] = pf_pack(v.x, v.y);
-                q23[i] = pf_pack(v.z, v.w);
+                q01[r][i] = pf_pack(v.x, v.y);
+                q23[r][i] = pf_pack(v.z, v.w);
             }
         }
-        for (uint32_t p0 = first_any; p0 <= last_pos; p0 += kPfBlock) {
-            __syncthreads();                                            // the previous block's rows are no longer read
-            for (uint32_t i = threadIdx.x; i < kPfBlock * D / 4; i += kPfThreads) {
-                const uint32_t row = i / (D / 4), col = i % (D / 4), pos = p0 + row;
-                float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
-                if (pos <= last_pos) {
-                    kk = __ldcg(reinterpret_cast<const float4*>(k_cache + static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D) + col);
-                    vv = __ldcg(reinterpret_cast<const float4*>(v_cache + static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D) + col);
-                }
-                reinterpret_cast<float4*>(ks)[i] = kk;
-                reinterpret_cast<float4*>(vs)[i] = vv;
+    }
+    // Blocks of kPfBlock positions go through two shared-memory buffers: the asynchronous copies of block b + 1 are in
+    // flight while block b is consumed.  Rows past last_pos are filled with zeros (a copy of source size 0).
+    auto stage = [&](uint32_t p0, uint32_t buf) {
+        float* kd = kv_smem + buf * (2 * kPfBlock * D);
+        float* vd = kd + kPfBlock * D;
+#pragma unroll 4
+        for (uint32_t i = threadIdx.x; i < kPfBlock * D / 4; i += kPfThreads) {
+            const uint32_t row = i / (D / 4), col = i % (D / 4), pos = min(p0 + row, last_pos);
+            const uint32_t bytes = p0 + row <= last_pos ? 16u : 0u;
+            const size_t off = static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D + col * 4;
+            cp_async_16(kd + i * 4, k_cache + off, bytes);
+            cp_async_16(vd + i * 4, v_cache + off, bytes);
+        }
+        cp_async_commit();
+    };
+    stage(first_any, 0);
+    uint32_t buf = 0;
+    for (uint32_t p0 = first_any; p0 <= last_pos; p0 += kPfBlock, buf ^= 1u) {
+        const bool more = p0 + kPfBlock <= last_pos;
+        if (more) stage(p0 + kPfBlock, buf ^ 1u);       // its buffer was read during the previous block, which ended with a barrier
+        if (more) cp_async_wait<1>(); else cp_async_wait<0>();
+        __syncthreads();
+        const float* ks = kv_smem + buf * (2 * kPfBlock * D);
+        const float* vs = ks + kPfBlock * D;
+        const uint32_t j_end = min(static_cast<uint32_t>(kPfBlock), last_pos - p0 + 1);
+        // kPfStep positions per round: their score chains, reductions and exponentials are independent of one another, which
+        // is what hides the arithmetic and shuffle latencies at the two or three warps per scheduler the row registers allow.
+        // Rows of the staged block past last_pos are zeros and fall outside every token's range.
+        for (uint32_t j = 0; j < j_end; j += kPfStep) {
+            bool in_range[kPfStep];
+            bool any = false;
+#pragma unroll
+            for (int u = 0; u < kPfStep; ++u) {
+                const uint32_t pos = p0 + j + u;
+                in_range[u] = live && pos >= my_first && pos <= my_last;      // uniform over the token's kPfLanes threads
+                any |= in_range[u];
             }
-            __syncthreads();
-            const uint32_t j_end = min(static_cast<uint32_t>(kPfBlock), last_pos - p0 + 1);
-            for (uint32_t j = 0; j < j_end; ++j) {
-                const uint32_t pos = p0 + j;
-                const float4* krow = reinterpret_cast<const float4*>(ks + j * D) + part;
-                uint64_t d01 = pf_pack(0.0f, 0.0f), d23 = d01;
+            if (!__any_sync(0xffffffffu, any)) continue;                          // none of this warp's tokens attends these positions
+            const float4* krow = reinterpret_cast<const float4*>(ks + j * D) + part;
+            uint64_t d[kPfStep][R];
 #pragma unroll
-                for (int i = 0; i < per4; ++i) {
-                    const float4 kk = krow[i * kPfLanes];
-                    d01 = pf_fma(q01[i], pf_pack(kk.x, kk.y), d01);
-                    d23 = pf_fma(q23[i], pf_pack(kk.z, kk.w), d23);
+            for (int u = 0; u < kPfStep; ++u) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) d[u][r] = pf_pack(0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int i = 0; i < per4; ++i) {
+#pragma unroll
+                for (int u = 0; u < kPfStep; ++u) {
+                    const float4 kk = krow[u * (D / 4) + i * kPfLanes];
+                    const uint64_t k01 = pf_pack(kk.x, kk.y), k23 = pf_pack(kk.z, kk.w);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) d[u][r] = pf_fma(q23[r][i], k23, pf_fma(q01[r][i], k01, d[u][r]));
                 }
-                float d0, d1, d2, d3;
-                pf_unpack(d01, d0, d1);
-                pf_unpack(d23, d2, d3);
-                float dot = (d0 + d1) + (d2 + d3);
+            }
+            // Sum over the token's eight lanes, halving the rows a lane carries at each exchange: lane `part` ends with
+            // the full score of head my_row (R + 1 or 3 shuffles, where one reduction per row would take 3 R).
+            float sc[kPfStep];
 #pragma unroll
-                for (int o = kPfLanes / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                if (live && pos >= my_first && pos <= my_last) {        // uniform over the row's kPfLanes threads
-                    const float sc = dot * scale;
-                    if (sc > m) {                                       // the maximum moves: rescale what has been summed
-                        const float f = expf(m - sc);                   // exp(-inf) = 0 on the first position
-                        const uint64_t f2 = pf_pack(f, f);
-                        l *= f;
+            for (int u = 0; u < kPfStep; ++u) {
+                float dot[R];
 #pragma unroll
-                        for (int i = 0; i < per4; ++i) { a01[i] = pf_mul(a01[i], f2); a23[i] = pf_mul(a23[i], f2); }
-                        m = sc;
-                    }
-                    const float e = expf(sc - m);
-                    const uint64_t e2 = pf_pack(e, e);
-                    l += e;
-                    const float4* vrow = reinterpret_cast<const float4*>(vs + j * D) + part;
+                for (int r = 0; r < R; ++r) {
+                    float d0, d1;
+                    pf_unpack(d[u][r], d0, d1);
+                    dot[r] = d0 + d1;
+                }
+                float red;
+                if constexpr (R == 4) {
+                    const bool hi = part & 4, hi2 = part & 2;
+                    float k0 = hi ? dot[2] : dot[0], k1 = hi ? dot[3] : dot[1];
+                    k0 += __shfl_xor_sync(0xffffffffu, hi ? dot[0] : dot[2], 4);
+                    k1 += __shfl_xor_sync(0xffffffffu, hi ? dot[1] : dot[3], 4);
+                    red = (hi2 ? k1 : k0) + __shfl_xor_sync(0xffffffffu, hi2 ? k0 : k1, 2);
+                } else if constexpr (R == 2) {
+                    const bool hi = part & 4;
+                    red = (hi ? dot[1] : dot[0]) + __shfl_xor_sync(0xffffffffu, hi ? dot[0] : dot[1], 4);
+                    red += __shfl_xor_sync(0xffffffffu, red, 2);
+                } else {
+                    red = dot[0] + __shfl_xor_sync(0xffffffffu, dot[0], 4);
+                    red += __shfl_xor_sync(0xffffffffu, red, 2);
+                }
+                red += __shfl_xor_sync(0xffffffffu, red, 1);
+                sc[u] = red * scale;
+            }
+            float m_new = m;
 #pragma unroll
-                    for (int i = 0; i < per4; ++i) {
-                        const float4 vv = vrow[i * kPfLanes];
-                        a01[i] = pf_fma(e2, pf_pack(vv.x, vv.y), a01[i]);
-                        a23[i] = pf_fma(e2, pf_pack(vv.z, vv.w), a23[i]);
+            for (int u = 0; u < kPfStep; ++u) m_new = in_range[u] ? fmaxf(m_new, sc[u]) : m_new;
+            const bool moved = m_new > m;
+            if (__any_sync(0xffffffffu, moved)) {                   // a maximum moves: rescale what has been summed (rare after the first positions)
+                const float f = moved ? expf(m - m_new) : 1.0f;     // exp(-inf) = 0 on the first position
+                l *= f;
+                m = m_new;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float fr = __shfl_sync(0xffffffffu, f, pf_owner<R>(r), kPfLanes);
+                    const uint64_t f2 = pf_pack(fr, fr);
+#pragma unroll
+                    for (int i = 0; i < per4; ++i) { a01[r][i] = pf_mul(a01[r][i], f2); a23[r][i] = pf_mul(a23[r][i], f2); }
+                }
+            }
+            uint64_t e2[kPfStep][R];
+            float e_sum = 0.0f;                                         // the round's terms in fp32, one double addition per round
+#pragma unroll
+            for (int u = 0; u < kPfStep; ++u) {
+                const float e = in_range[u] ? expf(sc[u] - m) : 0.0f;   // a token that does not attend the position adds 0 x value
+                e_sum += e;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float er = __shfl_sync(0xffffffffu, e, pf_owner<R>(r), kPfLanes);
+                    e2[u][r] = pf_pack(er, er);
+                }
+            }
+            l += e_sum;
+            const float4* vrow = reinterpret_cast<const float4*>(vs + j * D) + part;
+#pragma unroll
+            for (int i = 0; i < per4; ++i) {
+#pragma unroll
+                for (int u = 0; u < kPfStep; ++u) {
+                    const float4 vv = vrow[u * (D / 4) + i * kPfLanes];
+                    const uint64_t v01 = pf_pack(vv.x, vv.y), v23 = pf_pack(vv.z, vv.w);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        a01[r][i] = pf_fma(e2[u][r], v01, a01[r][i]);
+                        a23[r][i] = pf_fma(e2[u][r], v23, a23[r][i]);
                     }
                 }
             }
         }
-        if (live) {
-            if (!(l > 0.0) || !isfinite(l)) {
-                if (part == 0) atomicExch(error_word, kErrNonFinite);
-            } else {
-                const float inv = 1.0f / static_cast<float>(l);
-                float4* orow = reinterpret_cast<float4*>(out + static_cast<size_t>(t) * qw + static_cast<size_t>(h) * D) + part;
+        __syncthreads();                                    // the block's rows are no longer read: the next copies may land in this buffer
+    }
+    // every lane of the warp takes part in the exchanges below; only live tokens store
+    const bool bad = live && (!(l > 0.0) || !isfinite(l));
+    const float inv_mine = (live && !bad) ? 1.0f / static_cast<float>(l) : 0.0f;
+    if (bad) atomicExch(error_word, kErrNonFinite);
 #pragma unroll
-                for (int i = 0; i < per4; ++i) {
-                    float4 o;
-                    pf_unpack(a01[i], o.x, o.y);
-                    pf_unpack(a23[i], o.z, o.w);
-                    o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
-                    orow[i * kPfLanes] = o;
-                }
+    for (int r = 0; r < R; ++r) {
+        const float inv = __shfl_sync(0xffffffffu, inv_mine, pf_owner<R>(r), kPfLanes);
+        if (live && inv != 0.0f) {
+            float4* orow = reinterpret_cast<float4*>(out + static_cast<size_t>(t) * qw + static_cast<size_t>(h0 + r) * D) + part;
+#pragma unroll
+            for (int i = 0; i < per4; ++i) {
+                float4 o;
+                pf_unpack(a01[r][i], o.x, o.y);
+                pf_unpack(a23[r][i], o.z, o.w);
+                o.x *= inv; o.y *= inv; o.z *= inv; o.w *= inv;
+                orow[i * kPfLanes] = o;
             }
         }
     }

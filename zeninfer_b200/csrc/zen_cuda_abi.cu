@@ -21,6 +21,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <type_traits>
 #include <unordered_map>
 #include <vector>
 
@@ -1368,19 +1369,34 @@ int zen_cuda_dev_attention_prefill(const float* d_q, const float* d_k_cache, con
         (head_dim != 64 && head_dim != 128 && head_dim != 256))
         return set_error(s, "dev_attention_prefill: bad arguments (head_dim 64, 128 or 256)") ? 1 : 0;
     if (scale == 0.0f) scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
-    const dim3 grid(static_cast<unsigned>((tokens + zk::kPfTokens - 1) / zk::kPfTokens), static_cast<unsigned>(kv_heads)), block(zk::kPfThreads);
-    const size_t smem = 2 * zk::kPfBlock * head_dim * sizeof(float);
+    // query heads per thread: the largest of 4, 2, 1 that divides the group and keeps 2 * R * head_dim / 8 row values in registers
+    const size_t group = heads / kv_heads;
+    const int cap = head_dim == 256 ? 2 : 4;
+    const int r_heads = (cap >= 4 && group % 4 == 0) ? 4 : (group % 2 == 0) ? 2 : 1;
+    const size_t n_tiles = (tokens + zk::kPfTokens - 1) / zk::kPfTokens, n_ctas = n_tiles * kv_heads * (group / r_heads);
+    if (n_ctas > 0x7fffffffu) return set_error(s, "dev_attention_prefill: too many tiles") ? 1 : 0;
+    const dim3 grid(static_cast<unsigned>(n_ctas)), block(zk::kPfThreads);
+    const size_t smem = 2 * 2 * zk::kPfBlock * head_dim * sizeof(float);   // two buffers of keys + values
     auto launch = [&](auto kernel) {
-        static bool configured = false;   // one static per instantiation of this lambda's call operator
-        if (!configured && smem > 48 * 1024) {
+        // the instantiations share one function-pointer type, so the opt-in flags are keyed by (head_dim, heads per thread)
+        static bool configured[3][3] = {};
+        bool& done = configured[head_dim == 64 ? 0 : head_dim == 128 ? 1 : 2][r_heads == 4 ? 2 : r_heads == 2 ? 1 : 0];
+        if (!done && smem > 48 * 1024) {
             if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) return cudaErrorInvalidValue;
-            configured = true;
+            done = true;
         }
         return launch_pdl(s, kernel, grid, block, smem, st, d_q, d_k_cache, d_v_cache, d_pos, d_out, static_cast<uint32_t>(tokens), static_cast<uint32_t>(heads),
                           static_cast<uint32_t>(kv_heads), scale, static_cast<uint32_t>(window), static_cast<uint32_t>(max_positions), s.d_error);
     };
-    const cudaError_t e = head_dim == 64 ? launch(zk::attention_prefill_kernel<64>) : head_dim == 128 ? launch(zk::attention_prefill_kernel<128>)
-                                                                                                      : launch(zk::attention_prefill_kernel<256>);
+    auto by_heads = [&](auto dim) {
+        constexpr int kD = decltype(dim)::value;
+        if constexpr (kD < 256) {
+            if (r_heads == 4) return launch(zk::attention_prefill_kernel<kD, 4>);
+        }
+        return r_heads == 2 ? launch(zk::attention_prefill_kernel<kD, 2>) : launch(zk::attention_prefill_kernel<kD, 1>);
+    };
+    const cudaError_t e = head_dim == 64 ? by_heads(std::integral_constant<int, 64>{}) : head_dim == 128 ? by_heads(std::integral_constant<int, 128>{})
+                                                                                                          : by_heads(std::integral_constant<int, 256>{});
     ZC_DEV_LEAVE(e);
 }
 
