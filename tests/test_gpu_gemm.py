@@ -78,6 +78,18 @@ def test_gemm_batch_shares_input(be, zo):
         be.release_weights(w)
 
 
+def test_gemm_batch_numbers_row_tiles_through_the_tensors(be, zo):
+    # 100 + 25 + 25 = 150 row tiles in one launch on 148 SMs: the K tiles are shared evenly and the cuts fall inside tiles of
+    # different tensors; the second tensor ends in a ragged tile; the fourth tensor goes into a second launch
+    cols, rows, tokens = 1024, [12800, 3190, 3200, 130], 40
+    ws = [seeded_weights(Q8_0, r, cols, 430 + i) for i, r in enumerate(rows)]
+    x = seeded_acts(tokens, cols, 440)
+    outs = be.gemm_batch("Q8_0", ws, x, rows, tokens, cols)
+    for w, r, o in zip(ws, rows, outs):
+        assert_parity(o, zo.gemm(Q8_0, w, x, tokens, r, cols, int8_acts=True), what=f"batched gemm rows={r}")
+        be.release_weights(w)
+
+
 def test_config1_full_size(be, zo):
     # BASELINE config 1: activations 512 x 4096 N(0,1) seed 2, W 14336 x 4096 N(0,.02) seed 3 -> Q8_0
     tokens, rows, cols = 512, 14336, 4096

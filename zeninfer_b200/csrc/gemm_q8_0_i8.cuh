@@ -43,15 +43,19 @@ constexpr int kGemmSplit = kGemmEpiWarps / 4;  // the warps of a quadrant split 
 constexpr int kGemmThreads = (2 + kGemmEpiWarps) * 32;
 constexpr int kGemmMaxN = 256;         // tokens per tile, a multiple of 32
 
+constexpr int kGemmMaxTensors = 3;     // weight tensors of one launch (they share the activation block): q|k|v, gate|up
+
 struct GemmParams {
-    CUtensorMap map_w;                 // weight codes  [rows][K] int8, box 128 B x 128 rows, SWIZZLE_128B
+    CUtensorMap map_w[kGemmMaxTensors];  // weight codes  [rows][K] int8, box 128 B x 128 rows, SWIZZLE_128B
     CUtensorMap map_x;                 // act codes     [tokens_padded][K] int8, box 128 B x n_tile rows, SWIZZLE_128B
     CUtensorMap map_xs;                // act scales    [nb][t_ld] fp32 (block-major), box n_tile x 4
-    const __half* w_scales;            // [rows][nbp]
-    float* out;                        // [tokens][rows]
-    uint32_t rows, tokens, nb, nbp;
+    const __half* w_scales[kGemmMaxTensors];   // [rows][nbp]
+    float* out[kGemmMaxTensors];               // [tokens][rows]
+    uint32_t rows[kGemmMaxTensors];
+    uint32_t m_start[kGemmMaxTensors];         // first row tile of each tensor in the launch's row-tile numbering (0xffffffff: unused)
+    uint32_t tensors, tokens, nb, nbp;
     uint32_t n_tile;                   // tokens per tile: 32, 64, 128 or 256
-    uint32_t m_tiles, n_tiles;
+    uint32_t m_tiles, n_tiles;         // m_tiles: row tiles of all the tensors together
     uint32_t stream_k;                 // 1: CTAs share the (tile, K tile) units evenly (see GemmWork); 0: whole tiles in turn
     int* error_word;
 };
@@ -111,6 +115,12 @@ __device__ __forceinline__ void gemm_fma32(const uint32_t (&v)[32], uint64_t sw2
     ZK_LDS128(s, sx_addr, 112); gemm_fma4(v + 28, sw2, s, acc + 14);
 }
 
+// Which tensor a row tile of the launch belongs to, and its index there.
+__device__ __forceinline__ void gemm_locate(const GemmParams& p, uint32_t mt_all, uint32_t& ti, uint32_t& mt) {
+    ti = (mt_all >= p.m_start[1] ? 1u : 0u) + (mt_all >= p.m_start[2] ? 1u : 0u);
+    mt = mt_all - p.m_start[ti];
+}
+
 // The work of one CTA.  With `stream_k` the (tile, K tile) units of the whole product, tile-major, are cut into
 // gridDim.x equal contiguous ranges, so every SM gets the same number of K tiles even when the tile count is not a
 // multiple of the SM count (448 tiles on 148 SMs would otherwise take four rounds for 3.03 rounds of work).  A
@@ -141,16 +151,19 @@ struct GemmWork {
 };
 
 // Clears the output tiles that two CTAs of a stream-K launch share (launched right before it, same grid).
-__global__ void gemm_zero_split_tiles_kernel(float* __restrict__ out, uint32_t rows, uint32_t tokens, uint32_t m_tiles, uint32_t n_tiles,
-                                             uint32_t n_tile, uint32_t ktiles) {
+__global__ void gemm_zero_split_tiles_kernel(const __grid_constant__ GemmParams p, uint32_t ktiles) {
     if (blockIdx.x == 0) return;
-    const uint64_t total = static_cast<uint64_t>(m_tiles) * n_tiles * ktiles;
+    const uint64_t total = static_cast<uint64_t>(p.m_tiles) * p.n_tiles * ktiles;
     const uint32_t cut = static_cast<uint32_t>(total * blockIdx.x / gridDim.x);
     if (cut % ktiles == 0) return;   // the boundary falls between two tiles
-    const uint32_t tile = cut / ktiles, mt = tile % m_tiles, nt = tile / m_tiles;
-    for (uint32_t i = threadIdx.x; i < n_tile * kGemmM; i += blockDim.x) {
-        const uint32_t t = nt * n_tile + i / kGemmM, r = mt * kGemmM + i % kGemmM;
-        if (t < tokens && r < rows) out[static_cast<size_t>(t) * rows + r] = 0.0f;
+    const uint32_t tile = cut / ktiles, nt = tile / p.m_tiles;
+    uint32_t ti, mt;
+    gemm_locate(p, tile % p.m_tiles, ti, mt);
+    float* out = p.out[ti];
+    const uint32_t rows = p.rows[ti];
+    for (uint32_t i = threadIdx.x; i < p.n_tile * kGemmM; i += blockDim.x) {
+        const uint32_t t = nt * p.n_tile + i / kGemmM, r = mt * kGemmM + i % kGemmM;
+        if (t < p.tokens && r < rows) out[static_cast<size_t>(t) * rows + r] = 0.0f;
     }
 }
 
@@ -187,7 +200,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
         }
         *abort_word = 0;
         mbar_fence_init();
-        tma_prefetch_descriptor(&p.map_w);
+        for (uint32_t i = 0; i < p.tensors; ++i) tma_prefetch_descriptor(&p.map_w[i]);
         tma_prefetch_descriptor(&p.map_x);
         tma_prefetch_descriptor(&p.map_xs);
     }
@@ -204,7 +217,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
             bool ok = true;
             GemmWork work(p, ktiles);
             while (ok && work.next(tile, kt0, kt1)) {
-                const uint32_t mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+                const uint32_t nt = tile / p.m_tiles;
+                uint32_t ti, mt;
+                gemm_locate(p, tile % p.m_tiles, ti, mt);
+                const CUtensorMap* map_w = &p.map_w[ti];
                 for (uint32_t kt = kt0; kt < kt1; ++kt, ++it) {
                     const uint32_t stage = it % kGemmStages;
                     if (it >= kGemmStages && !mbar_wait(&empty[stage], ((it / kGemmStages) - 1) & 1)) {
@@ -214,7 +230,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                     if (!ok) break;
                     uint8_t* st = smem + stage * kStageBytes;
                     mbar_arrive_expect_tx(&full[stage], kStageBytes);
-                    tma_load_2d(st, &p.map_w, static_cast<int>(kt * kGemmKTile), static_cast<int>(mt * kGemmM), &full[stage]);
+                    tma_load_2d(st, map_w, static_cast<int>(kt * kGemmKTile), static_cast<int>(mt * kGemmM), &full[stage]);
                     tma_load_2d(st + kGemmM * kGemmKTile, &p.map_x, static_cast<int>(kt * kGemmKTile), static_cast<int>(nt * kNTile), &full[stage]);
                     tma_load_2d(st + kGemmM * kGemmKTile + kNTile * kGemmKTile, &p.map_xs, static_cast<int>(nt * kNTile),
                                 static_cast<int>(kt * kGemmBlocksPerTile), &full[stage]);
@@ -268,14 +284,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
         bool ok = true;
         GemmWork work(p, ktiles);
         while (ok && work.next(tile, kt0, kt1)) {
-            const uint32_t mt = tile % p.m_tiles, nt = tile / p.m_tiles;
-            const uint32_t r = mt * kGemmM + quad * 32 + lane;
-            const bool row_ok = r < p.rows;
+            const uint32_t nt = tile / p.m_tiles;
+            uint32_t ti, mt;
+            gemm_locate(p, tile % p.m_tiles, ti, mt);
+            const uint32_t r = mt * kGemmM + quad * 32 + lane, rows = p.rows[ti];
+            const bool row_ok = r < rows;
             uint64_t acc[kNHalf / 2];  // packed pairs of fp32 accumulators, token columns (2i, 2i+1)
 #pragma unroll
             for (int c = 0; c < kNHalf / 2; ++c) acc[c] = 0ull;
             // the four weight scales of row r per K tile (8-byte aligned: nbp is a multiple of 8), fetched one K tile ahead
-            const uint2* sw_row = reinterpret_cast<const uint2*>(p.w_scales + static_cast<size_t>(row_ok ? r : 0) * p.nbp);
+            const uint2* sw_row = reinterpret_cast<const uint2*>(p.w_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nbp);
             uint2 sw_next = __ldg(sw_row + kt0);
             for (uint32_t kt = kt0; kt < kt1 && ok; ++kt, ++it) {
                 const uint32_t stage = it % kGemmStages;
@@ -332,18 +350,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
             if (!ok) break;
             if (row_ok) {
                 const bool whole = kt0 == 0 && kt1 == ktiles;   // otherwise another CTA holds the rest of this tile's K range
+                float* out_t = p.out[ti];
 #pragma unroll
                 for (int c = 0; c < kNHalf; c += 2) {
                     const uint32_t t = nt * kNTile + half * kNHalf + c;
                     float lo, hi;
                     unpack2(acc[c / 2], lo, hi);
-                    float* o = p.out + static_cast<size_t>(t) * p.rows + r;
+                    float* o = out_t + static_cast<size_t>(t) * rows + r;
                     if (whole) {
                         if (t < p.tokens) o[0] = lo;
-                        if (t + 1 < p.tokens) o[p.rows] = hi;
+                        if (t + 1 < p.tokens) o[rows] = hi;
                     } else {
                         if (t < p.tokens) atomicAdd(o, lo);
-                        if (t + 1 < p.tokens) atomicAdd(o + p.rows, hi);
+                        if (t + 1 < p.tokens) atomicAdd(o + rows, hi);
                     }
                 }
             }

@@ -566,22 +566,35 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
     if (cudaGetLastError() != cudaSuccess) return set_error(s, "gemm: quantise launch failed");
     ++s.stats.dispatches;
     const uint32_t n_tile = 128u;  // tokens per tile: sixteen epilogue warps take 32 token columns each
-    for (size_t i = 0; i < count; ++i) {
-        if (!w[i] || !d_out[i] || w[i]->format != ZEN_CUDA_Q8_0 || w[i]->cols != cols) return set_error(s, "gemm: tasks must be Q8_0 and share columns");
+    for (size_t i = 0; i < count; ++i)
+        if (!w[i] || !d_out[i] || w[i]->format != ZEN_CUDA_Q8_0 || w[i]->cols != cols || w[i]->nbp != w[0]->nbp)
+            return set_error(s, "gemm: tasks must be Q8_0 and share columns");
+    // Up to kGemmMaxTensors tensors per launch: their row tiles are numbered through, so that q|k|v or gate|up fill the
+    // SMs together (a 1024-row tensor alone is 32 tiles for 148 SMs).
+    for (size_t i0 = 0; i0 < count; i0 += zk::kGemmMaxTensors) {
+        const size_t n = std::min<size_t>(zk::kGemmMaxTensors, count - i0);
         zk::GemmParams p{};
-        if (!make_map_2d(s, &p.map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w[i]->plane[0], cols, w[i]->rows, cols, zk::kGemmKTile, zk::kGemmM,
-                         CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+        uint32_t m_tiles = 0;
+        for (size_t j = 0; j < static_cast<size_t>(zk::kGemmMaxTensors); ++j) {
+            if (j >= n) { p.m_start[j] = 0xffffffffu; continue; }
+            const zen_cuda_weights* wt = w[i0 + j];
+            if (!make_map_2d(s, &p.map_w[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wt->plane[0], cols, wt->rows, cols, zk::kGemmKTile, zk::kGemmM,
+                             CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+            p.w_scales[j] = static_cast<const __half*>(wt->plane[1]);
+            p.out[j] = d_out[i0 + j];
+            p.rows[j] = static_cast<uint32_t>(wt->rows);
+            p.m_start[j] = m_tiles;
+            m_tiles += (p.rows[j] + zk::kGemmM - 1) / zk::kGemmM;
+        }
         if (!make_map_2d(s, &p.map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, cols, tokens, cols, zk::kGemmKTile, n_tile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
         if (!make_map_2d(s, &p.map_xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, xs_t, t_ld, nb, t_ld * sizeof(float), n_tile, zk::kGemmBlocksPerTile,
                          CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
-        p.w_scales = static_cast<const __half*>(w[i]->plane[1]);
-        p.out = d_out[i];
-        p.rows = static_cast<uint32_t>(w[i]->rows);
+        p.tensors = static_cast<uint32_t>(n);
         p.tokens = static_cast<uint32_t>(tokens);
         p.nb = nb;
-        p.nbp = w[i]->nbp;
+        p.nbp = w[0]->nbp;
         p.n_tile = n_tile;
-        p.m_tiles = (p.rows + zk::kGemmM - 1) / zk::kGemmM;
+        p.m_tiles = m_tiles;
         p.n_tiles = (p.tokens + n_tile - 1) / n_tile;
         p.error_word = s.d_error;
         const unsigned tiles = p.m_tiles * p.n_tiles, ktiles = (nb + zk::kGemmBlocksPerTile - 1) / zk::kGemmBlocksPerTile;
@@ -590,7 +603,7 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
         // so that no tile is cut more than once).
         p.stream_k = (s.gemm_stream_k && tiles % grid != 0 && static_cast<uint64_t>(tiles) * ktiles / grid >= ktiles) ? 1u : 0u;
         if (p.stream_k) {
-            zk::gemm_zero_split_tiles_kernel<<<grid, 256, 0, st>>>(p.out, p.rows, p.tokens, p.m_tiles, p.n_tiles, n_tile, ktiles);
+            zk::gemm_zero_split_tiles_kernel<<<grid, 256, 0, st>>>(p, ktiles);
             ++s.stats.dispatches;
         }
         const cudaError_t e = launch_gemm<128>(p, grid, st);
