@@ -674,10 +674,16 @@ def run_decode(args) -> None:
     from zeninfer_b200 import Backend
     from zeninfer_b200.backend import ACT_INT8
     from zeninfer_b200.llama import LlamaConfig, LlamaDecoder, tensor_plan
-    if int(os.environ.get("WORLD_SIZE", "1")) != 1 or args.gpus != 1:
-        raise SystemExit("workload decode runs on one GPU in this build")
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(0)
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     be = Backend()
     cfg = LlamaConfig()
     prompt_len = args.prompt_len
@@ -695,20 +701,21 @@ def run_decode(args) -> None:
                 yield name, (1.0 + 0.02 * torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)).cpu().numpy(), False
 
     t0 = time.perf_counter()
-    dec = LlamaDecoder(be, cfg, tensors(), act_mode=ACT_INT8, max_positions=1024, fused=args.fuse)
+    dec = LlamaDecoder(be, cfg, tensors(), act_mode=ACT_INT8, max_positions=1024, fused=args.fuse, rank=rank, world=world)
     load_s = time.perf_counter() - t0
     dec.capture()
+    token_prefill = args.token_prefill or world > 1     # the block prefill is not sharded
     prompt = np.random.default_rng(6).integers(0, cfg.vocab, size=prompt_len, dtype=np.int64)
     stream = dec.stream
-    with ClockSampler(0) as clocks:
+    with ClockSampler(local) as clocks:
         with torch.cuda.stream(stream):
             dec.reset()
-            dec.feed_prompt(prompt.tolist(), batched_prefill=not args.token_prefill)      # first run: kernel attributes, workspace allocation
+            dec.feed_prompt(prompt.tolist(), batched_prefill=not token_prefill)      # first run: kernel attributes, workspace allocation
             stream.synchronize()
             dec.reset()
             p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             p0.record(stream)
-            dec.feed_prompt(prompt.tolist(), batched_prefill=not args.token_prefill)      # the prompt as tensor-core blocks (or token by token), then the first pick
+            dec.feed_prompt(prompt.tolist(), batched_prefill=not token_prefill)      # the prompt as tensor-core blocks (or token by token), then the first pick
             p1.record(stream)
             stream.synchronize()
             prefill_ms = p0.elapsed_time(p1)
@@ -716,6 +723,9 @@ def run_decode(args) -> None:
                 dec.step(want_token=True)
             stream.synchronize()
             be.dev_check(stream.cuda_stream)
+            if world > 1:
+                torch.cuda.synchronize()
+                dist.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             clocks.mark_start()
             e0.record(stream)
@@ -724,7 +734,14 @@ def run_decode(args) -> None:
             e1.record(stream)
             stream.synchronize()
             clocks.mark_end()
+            if world > 1:
+                torch.cuda.synchronize()
+                dist.barrier()
         ms = e0.elapsed_time(e1)
+        if world > 1:       # the step's time is the slowest rank's
+            t = torch.tensor([ms, prefill_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms, prefill_ms = float(t[0].item()), float(t[1].item())
     be.dev_check(stream.cuda_stream)
     last_pos = int(dec.pos.item())
     assert last_pos == prompt_len + warm + steps, "position counter out of step"
@@ -736,16 +753,32 @@ def run_decode(args) -> None:
     kv_bytes = int(cfg.layers * 2 * cfg.kv_width * 4 * mean_pos)
     algo = weight_bytes + kv_bytes
     peak, peak_kind = peaks()
+    peak *= world
     achieved = algo / (ms * 1e-3 / steps) / 1e9
 
     # e2e: the public generate() call; every picked token is read back to the host as it is produced
     stamps = []
     e2e_new = 33
-    dec.generate(prompt.tolist(), e2e_new, on_token=lambda _t: stamps.append(time.perf_counter()))
+    picked = dec.generate(prompt.tolist() if world == 1 else prompt[:32].tolist(), e2e_new, on_token=lambda _t: stamps.append(time.perf_counter()))
     e2e_tok_s = (e2e_new - 1) / (stamps[-1] - stamps[0])
+    if world > 1:           # every rank picked the same tokens; the rate is the slowest rank's
+        ids = torch.tensor(picked, device=dev)
+        lo, hi = ids.clone(), ids.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        assert bool((lo == hi).all().item()), "the ranks picked different tokens"
+        t = torch.tensor([e2e_tok_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        e2e_tok_s = float(t.item())
+    if rank != 0:
+        dec.close()
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        dist.barrier()
+        os._exit(0)
 
     cpu = None
-    if not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline:
         import oracle
         from zeninfer_b200 import blocks
         os.environ.setdefault("ZEN_CPU_Q8_ACT", "1")
@@ -771,15 +804,18 @@ def run_decode(args) -> None:
 
     fn, fs, fr = ("n" in dec.fuse), ("s" in dec.fuse), ("r" in dec.fuse)
     per_layer = 5 + (0 if (fn and fr) else 2) + (0 if fs else 1)   # q|k|v, attention block, o, gate|up, down + norm / residual / SwiGLU launches
-    launches_per_step = 1 + (0 if fn else 1) + per_layer * cfg.layers + 1 + 1 + 2   # embed, layers, advance, lm_head, pick (2)
+    launches_per_step = 1 + (0 if fn else 1) + per_layer * cfg.layers + 1 + 1 + 2   # embed, layers, advance, lm_head, pick (2): per rank
+    gathers = (4 * cfg.layers + 1) if world > 1 else 0
     print(json.dumps({
-        "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
+        "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": "greedy decode, random-init Llama-3-8B shape in Q8_0 (config 4): 32 layers, d 4096, 32/8 heads of 128, ffn 14336, "
                                f"vocab 128256; prompt of {prompt_len} random ids (untimed here, see prefill_ms), then {warm} + {steps} decode steps",
                    "activations": "int8 (bit-exact reference codes)", "l2": "inputs larger than L2: 8.5 GB of weights stream per token",
                    "launch": f"two CUDA graphs per token, {launches_per_step} kernel launches (folded into the projections: '{dec.fuse}')", "weights": "torch.randn on the device, seed 6, N(0, 0.02)",
-                   "load_s": load_s, "prefill": ("token by token" if args.token_prefill else "blocks of up to 512 tokens through the tcgen05 GEMM + causal block attention"),
+                   "sharding": ("none (one GPU)" if world == 1 else f"output rows of every matrix over {world} GPUs, rank-local heads and KV cache, "
+                                f"{gathers} NCCL all-gathers per token inside the step graphs (attention output, o, SwiGLU activation, down; logits)"),
+                   "load_s": load_s, "prefill": ("token by token" if token_prefill else "blocks of up to 512 tokens through the tcgen05 GEMM + causal block attention"),
                    "prefill_ms": prefill_ms, "prefill_tokens_per_s": prompt_len / (prefill_ms * 1e-3)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
                      "kernel": "whole token step (projections through gemv_q8_0_kernel<1,1>)", "launch_us": ms * 1e3 / steps,
@@ -788,9 +824,14 @@ def run_decode(args) -> None:
         "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8,
                 "api": "LlamaDecoder.generate: each picked token id is read back to the host, and fed to the next step from pinned host memory, "
                        "as the reference's generate loop does", "steps": e2e_new - 1},
-        "gpu_launches": steps * launches_per_step,
+        "gpu_launches": steps * launches_per_step * world,
     }))
     dec.close()
+    if world > 1:
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        dist.barrier()
+        os._exit(0)
 
 
 def main() -> None:

@@ -27,12 +27,26 @@ def _rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
     return (x * inv * w).astype(np.float32)
 
 
-def generate(cfg, tensors: dict, shapes: dict, prompt, max_new: int):
+def generate(cfg, tensors: dict, shapes: dict, prompt, max_new: int, rank: int = 0, world: int = 1, gather=None):
     """tensors: name -> array (Q8_0 raw blocks for matrices, fp32 for norms); shapes: name -> (rows, cols).
-    Returns (ids, last_logits)."""
+    Returns (ids, last_logits).
+
+    world > 1 restates the row-sharded decoder: every matrix but the embedding table keeps rows
+    [rank * rows / world, (rank + 1) * rows / world), attention runs on the rank's heads, and `gather(piece)` returns the
+    concatenation of all ranks' pieces in rank order (four per layer: attention output, o projection, SwiGLU activation,
+    down projection; one for the logits).  Rows are independent, so the result equals the unsharded one."""
+    if gather is None:
+        if world != 1:
+            raise ValueError("a sharded run needs a gather")
+        gather = lambda piece: piece
     W = {n: _dequant_q8_0(a, *shapes[n]) for n, a in tensors.items() if len(shapes[n]) == 2}
+    if world > 1:
+        for n in W:
+            if n != "token_embd.weight":
+                per = W[n].shape[0] // world
+                W[n] = W[n][rank * per:(rank + 1) * per]
     N = {n: np.asarray(a, np.float32) for n, a in tensors.items() if len(shapes[n]) == 1}
-    E, H, KH, D = cfg.embedding, cfg.heads, cfg.kv_heads, cfg.head_dim
+    E, H, KH, D = cfg.embedding, cfg.heads // world, cfg.kv_heads // world, cfg.head_dim      # H, KH: this rank's heads
     half = D // 2
     kc = [np.zeros((0, KH * D), np.float32) for _ in range(cfg.layers)]
     vc = [np.zeros((0, KH * D), np.float32) for _ in range(cfg.layers)]
@@ -64,11 +78,11 @@ def generate(cfg, tensors: dict, shapes: dict, prompt, max_new: int):
                 e = np.exp(sc - sc.max()).astype(np.float32)
                 a = e * np.float32(1.0 / float(e.astype(np.float64).sum()))
                 att[h * D:(h + 1) * D] = a @ vc[l][:, kh * D:(kh + 1) * D]
-            x = x + W[p + "attn_output.weight"] @ att
+            x = x + gather(W[p + "attn_output.weight"] @ gather(att))
             xn = _rms_norm(x, N[p + "ffn_norm.weight"], cfg.rms_eps)
             g, u = W[p + "ffn_gate.weight"] @ xn, W[p + "ffn_up.weight"] @ xn
-            x = x + W[p + "ffn_down.weight"] @ ((g / (np.float32(1.0) + np.exp(-g))) * u).astype(np.float32)
-        return W["output.weight"] @ _rms_norm(x, N["output_norm.weight"], cfg.rms_eps)
+            x = x + gather(W[p + "ffn_down.weight"] @ gather(((g / (np.float32(1.0) + np.exp(-g))) * u).astype(np.float32)))
+        return gather(W["output.weight"] @ _rms_norm(x, N["output_norm.weight"], cfg.rms_eps))
 
     def pick(logits: np.ndarray) -> int:
         finite = np.isfinite(logits)

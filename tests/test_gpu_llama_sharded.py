@@ -1,0 +1,90 @@
+"""The row-sharded decoder on two or more GPUs, one process per GPU (spawned here), NCCL gathers on the decoder's stream.
+
+Bars: every rank generates the golden ids of the unmodified reference (tests/golden/llama_tiny.npz) with logits within
+1e-3, with and without the captured step graphs; and, rows being independent, the sharded logits equal the logits of an
+unsharded decoder on the same GPU bit for bit (fp32 and int8 activations)."""
+import json
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from helpers import assert_parity
+from zeninfer_b200.backend import ACT_FP32, ACT_INT8
+from zeninfer_b200.llama import LlamaConfig, LlamaDecoder, synthetic_tensors
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "llama_tiny.npz")
+
+
+def _golden():
+    with np.load(GOLDEN) as g:
+        meta = json.loads(str(g["meta"]))
+        return LlamaConfig(**meta["config"]), meta, g["prompt"].copy(), g["ids"].copy(), g["last_logits"].copy()
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank: int, world: int, port: int, out_dir: str):
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), LOCAL_RANK=str(rank), ZEN_CUDA_DEVICE=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank), timeout=datetime.timedelta(seconds=60))
+    from zeninfer_b200 import Backend
+    be = Backend()
+    cfg, meta, prompt, _, _ = _golden()
+    result = {}
+    try:
+        for mode, tag in ((ACT_FP32, "fp32"), (ACT_INT8, "int8")):
+            model = lambda: synthetic_tensors(cfg, meta["seed"], meta["weight_std"])
+            dec = LlamaDecoder(be, cfg, model(), act_mode=mode, rank=rank, world=world)
+            whole = LlamaDecoder(be, cfg, model(), act_mode=mode)
+            try:
+                result[tag + "_ids_eager"] = dec.generate(prompt.tolist(), meta["max_new"])
+                result[tag + "_logits_eager"] = dec.last_logits()
+                dec.capture()
+                result[tag + "_ids_graph"] = dec.generate(prompt.tolist(), meta["max_new"])
+                result[tag + "_logits_graph"] = dec.last_logits()
+                result[tag + "_ids_whole"] = whole.generate(prompt.tolist(), meta["max_new"], batched_prefill=False)
+                result[tag + "_logits_whole"] = whole.last_logits()
+            finally:
+                dist.barrier()
+                dec.close()
+                whole.close()
+        with pytest.raises(ValueError):
+            LlamaDecoder(be, cfg, (), rank=rank, world=world, fused="n")
+        torch.save(result, os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        # leave as the benchmark's ranks do: no collective in flight, a barrier, then straight out (tearing the NCCL group
+        # down after its collectives were captured into graphs did not return)
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
+
+
+def test_row_sharded_generation_matches_the_reference_and_the_unsharded_decoder(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    world = 2 if torch.cuda.device_count() >= 2 else 0
+    if not world:
+        pytest.skip("needs at least two GPUs")
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    _, _, _, ids, logits = _golden()
+    for r in range(world):
+        got = torch.load(os.path.join(tmp_path, f"rank{r}.pt"), weights_only=False)
+        for how in ("eager", "graph"):
+            assert got[f"fp32_ids_{how}"] == ids.tolist(), f"rank {r} {how}"
+            assert_parity(got[f"fp32_logits_{how}"], logits, 1e-3, f"rank {r} {how} logits vs the reference")
+            for tag in ("fp32", "int8"):
+                assert got[f"{tag}_ids_{how}"] == got[f"{tag}_ids_whole"]
+                assert np.array_equal(got[f"{tag}_logits_{how}"], got[f"{tag}_logits_whole"]), f"rank {r} {tag} {how}: sharded != unsharded"

@@ -8,9 +8,17 @@ through the quantised product kernels (zen_cuda_dev_gemv); the operators between
 points of include/zen_cuda.h.  Nothing here computes on the host: Python only orders launches and builds the RoPE
 cos/sin tables (the reference's table contract, rope_table :264-276).
 
-The prompt is consumed one token at a time through the same step (the reference prefills in batches; the
-arithmetic per token is the same).  A step is captured once into two CUDA graphs (layers; lm_head + pick), because
-the position and the token are read from device memory.
+A step is captured once into two CUDA graphs (layers; lm_head + pick), because the position and the token are read
+from device memory.  The prompt goes through prefill() in blocks (tensor-core products) or token by token.
+
+Several GPUs (one process per GPU, `rank` of `world`): every matrix but the embedding table is cut by output rows, a
+rank uploads only its rows, and the vector a row-cut product leaves in pieces is put together by an all-gather before
+the next operator needs it whole: the attention output (heads are cut with the q|k|v rows, so attention and the KV
+cache are rank-local), the o projection's residual stream, the SwiGLU activation, the down projection's residual
+stream, and the logits.  Four gathers per layer and one for the lm_head, as NCCL collectives on the decoder's stream
+(they are captured into the step graphs).  Rows are independent, so every rank holds the same residual stream bit for
+bit and picks the same token.  The reference drives one device; the row cut is its worker cut (ComputePool::parallel_for,
+src/compute_pool.cpp:104-106).
 """
 from __future__ import annotations
 
@@ -94,15 +102,27 @@ class LlamaDecoder:
     synthetic_tensors does; matrices must be Q8_0 raw blocks [rows, row_bytes]."""
 
     def __init__(self, backend: Backend, cfg: LlamaConfig, tensors, act_mode: int = ACT_INT8, max_positions: int | None = None, device=None,
-                 fused: bool | str = "nr"):
+                 fused: bool | str = "nr", rank: int = 0, world: int = 1, group=None):
         """fused: which of the layer's small operators are folded into the projection launches, as a string of letters:
         'n' RMSNorm into the q|k|v, gate|up and lm_head prologues, 's' SwiGLU into the down projection's prologue,
         'r' the residual adds into the o and down projections' stores.  True = all (5 launches per layer), False =
         none (8 per layer); the default folds what pays: the norm costs a CTA one extra pass over a 16 KB row, SwiGLU would
-        cost every CTA 14336 exponentials.  Same arithmetic either way."""
+        cost every CTA 14336 exponentials.  Same arithmetic either way.
+        rank, world, group: this process's share of a row-sharded model and the torch.distributed group (NCCL) of the
+        ranks; world must divide the KV heads, the embedding, the ffn width and the vocabulary, and fused must be "nr"."""
         import torch
         self.torch, self.be, self.cfg, self.act_mode = torch, backend, cfg, act_mode
         self.fuse = "nsr" if fused is True else "" if fused is False else str(fused)
+        self.rank, self.world, self.group = int(rank), int(world), group
+        if not 0 <= self.rank < self.world:
+            raise ValueError(f"rank {rank} of {world}")
+        if self.world > 1:
+            for what, n in (("kv_heads", cfg.kv_heads), ("embedding", cfg.embedding), ("ffn", cfg.ffn), ("vocab", cfg.vocab)):
+                if n % self.world:
+                    raise ValueError(f"{what} = {n} does not split over {self.world} ranks")
+            if set(self.fuse) != set("nr"):
+                raise ValueError('a row-sharded decoder runs with fused="nr"')
+            import torch.distributed  # noqa: F401  (the collectives of _gather)
         self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.max_positions = max_positions or cfg.context
         self.stream = torch.cuda.Stream(device=self.dev)
@@ -112,20 +132,27 @@ class LlamaDecoder:
         for name, arr, is_matrix in tensors:
             if is_matrix:
                 rows, cols = shapes[name]
-                self.h[name] = backend.dev_upload("Q8_0", arr, rows, cols)
+                if self.world > 1 and name != "token_embd.weight":     # this rank's rows only; every rank fetches embeddings itself
+                    per = rows // self.world
+                    self.h[name] = backend.dev_upload("Q8_0", arr, rows, cols, self.rank * per, per)
+                else:
+                    self.h[name] = backend.dev_upload("Q8_0", arr, rows, cols)
             else:
                 self.norm[name] = torch.from_numpy(np.array(arr, np.float32)).to(self.dev)   # a copy: the source may be a read-only file mapping
         missing = [n for n, _, m in tensor_plan(cfg) if (m and n not in self.h) or (not m and n not in self.norm)]
         if missing:
             raise ValueError(f"model is missing tensors: {missing[:4]}...")
         f32 = dict(dtype=torch.float32, device=self.dev)
-        E, QW, KW, F, V = cfg.embedding, cfg.q_width, cfg.kv_width, cfg.ffn, cfg.vocab
+        E, QW, KW, F, V, w = cfg.embedding, cfg.q_width, cfg.kv_width, cfg.ffn, cfg.vocab, self.world
+        # whole vectors (x, att, hid, logits: every rank holds all of them) and rank-local ones (q, k, v, gate, up, the caches)
         self.x, self.xn, self.tmp = torch.zeros(E, **f32), torch.zeros(E, **f32), torch.zeros(E, **f32)
-        self.q, self.k, self.v, self.att = torch.zeros(QW, **f32), torch.zeros(KW, **f32), torch.zeros(KW, **f32), torch.zeros(QW, **f32)
-        self.gate, self.up, self.hid = torch.zeros(F, **f32), torch.zeros(F, **f32), torch.zeros(F, **f32)
+        self.q, self.k, self.v, self.att = torch.zeros(QW // w, **f32), torch.zeros(KW // w, **f32), torch.zeros(KW // w, **f32), torch.zeros(QW, **f32)
+        self.gate, self.up, self.hid = torch.zeros(F // w, **f32), torch.zeros(F // w, **f32), torch.zeros(F, **f32)
         self.logits = torch.zeros(V, **f32)
-        self.k_cache = torch.zeros((cfg.layers, self.max_positions, KW), **f32)
-        self.v_cache = torch.zeros((cfg.layers, self.max_positions, KW), **f32)
+        self.k_cache = torch.zeros((cfg.layers, self.max_positions, KW // w), **f32)
+        self.v_cache = torch.zeros((cfg.layers, self.max_positions, KW // w), **f32)
+        mine = lambda t: t[self.rank * (t.numel() // w):(self.rank + 1) * (t.numel() // w)]     # the piece this rank's rows produce
+        self.x_mine, self.att_mine, self.hid_mine, self.logits_mine = mine(self.x), mine(self.att), mine(self.hid), mine(self.logits)
         cos, sin = rope_tables(cfg, self.max_positions)
         self.cos, self.sin = torch.from_numpy(cos).to(self.dev), torch.from_numpy(sin).to(self.dev)
         self.pos = torch.zeros(1, dtype=torch.int32, device=self.dev)
@@ -149,6 +176,12 @@ class LlamaDecoder:
         self.be.dev_gemv_fused(handles, outs, x, 1, self.act_mode, self.stream.cuda_stream, norm_weight=norm, norm_eps=self.cfg.rms_eps if norm else 0.0,
                                gate=gate, accumulate=acc, warm_next=warm)
 
+    def _gather(self, whole, piece) -> None:
+        """Every rank's piece into every rank's whole vector, in place (piece is this rank's slice of whole), ordered on
+        the decoder's stream: the caller is inside `with torch.cuda.stream(self.stream)`."""
+        if self.world > 1:
+            self.torch.distributed.all_gather_into_tensor(whole, piece, group=self.group)
+
     def _enqueue_layers(self) -> None:
         be, cfg, st = self.be, self.cfg, self.stream.cuda_stream
         P = lambda t: t.data_ptr()
@@ -165,9 +198,12 @@ class LlamaDecoder:
             self._gemv(qkv, [P(self.q), P(self.k), P(self.v)], P(self.x) if fn else P(self.xn),
                        norm=P(self.norm[p + "attn_norm.weight"]) if fn else None, warm=self.h[p + "attn_output.weight"])
             be.dev_attention_block(P(self.q), P(self.k), P(self.v), P(self.cos), P(self.sin), cfg.head_dim // 2, P(self.pos), P(self.k_cache[layer]),
-                                   P(self.v_cache[layer]), P(self.att), cfg.heads, cfg.kv_heads, cfg.head_dim, self.max_positions, 0.0, 0, st)
+                                   P(self.v_cache[layer]), P(self.att_mine), cfg.heads // self.world, cfg.kv_heads // self.world, cfg.head_dim,
+                                   self.max_positions, 0.0, 0, st)
+            self._gather(self.att, self.att_mine)
             # attention output projection and its residual add (x += o(att))
-            self._gemv([self.h[p + "attn_output.weight"]], [P(self.x) if fr else P(self.tmp)], P(self.att), acc=fr, warm=self.h[p + "ffn_gate.weight"])
+            self._gemv([self.h[p + "attn_output.weight"]], [P(self.x_mine) if fr else P(self.tmp)], P(self.att), acc=fr, warm=self.h[p + "ffn_gate.weight"])
+            self._gather(self.x, self.x_mine)
             # ffn norm (with the residual add when it was not folded into the store)
             if not fn:
                 be.dev_rms_norm(P(self.x), None if fr else P(self.tmp), P(self.norm[p + "ffn_norm.weight"]), P(self.xn), E, 1, eps, st)
@@ -176,9 +212,11 @@ class LlamaDecoder:
             self._gemv([self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]], [P(self.gate), P(self.up)], P(self.x) if fn else P(self.xn),
                        norm=P(self.norm[p + "ffn_norm.weight"]) if fn else None, warm=self.h[p + "ffn_down.weight"])
             if not fs:
-                be.dev_silu_mul(P(self.gate), P(self.up), P(self.hid), cfg.ffn, st)
-            self._gemv([self.h[p + "ffn_down.weight"]], [P(self.x) if fr else P(self.tmp)], P(self.up) if fs else P(self.hid),
+                be.dev_silu_mul(P(self.gate), P(self.up), P(self.hid_mine), cfg.ffn // self.world, st)
+                self._gather(self.hid, self.hid_mine)
+            self._gemv([self.h[p + "ffn_down.weight"]], [P(self.x_mine) if fr else P(self.tmp)], P(self.up) if fs else P(self.hid),
                        gate=P(self.gate) if fs else None, acc=fr, warm=nxt_q)                                      # (x +=) down(silu(gate) * up)
+            self._gather(self.x, self.x_mine)
             # the next norm: the next layer's attention norm, or the output norm
             nxt = self.norm[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < cfg.layers else self.norm["output_norm.weight"]
             if not fn:
@@ -189,8 +227,9 @@ class LlamaDecoder:
 
     def _enqueue_head(self) -> None:
         fn = "n" in self.fuse
-        self._gemv([self.h["output.weight"]], [self.logits.data_ptr()], self.x.data_ptr() if fn else self.xn.data_ptr(),
+        self._gemv([self.h["output.weight"]], [self.logits_mine.data_ptr()], self.x.data_ptr() if fn else self.xn.data_ptr(),
                    norm=self.norm["output_norm.weight"].data_ptr() if fn else None, warm=self.h["blk.0.attn_q.weight"])
+        self._gather(self.logits, self.logits_mine)
         self.be.dev_greedy_pick([(self.logits.data_ptr(), self.cfg.vocab, 0, self.cfg.vocab)], 1, self.token.data_ptr(), self.stream.cuda_stream)
 
     def capture(self) -> None:
@@ -202,9 +241,12 @@ class LlamaDecoder:
             self._enqueue_head()
             self.stream.synchronize()
             self.graph_layers, self.graph_head = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph_layers, stream=self.stream):
+            # with collectives in the graph, other threads of the process (the collective library's watchdog) may call
+            # the runtime during the capture: only this thread's calls belong to it
+            mode = dict(capture_error_mode="thread_local") if self.world > 1 else {}
+            with torch.cuda.graph(self.graph_layers, stream=self.stream, **mode):
                 self._enqueue_layers()
-            with torch.cuda.graph(self.graph_head, stream=self.stream):
+            with torch.cuda.graph(self.graph_head, stream=self.stream, **mode):
                 self._enqueue_head()
             self.stream.synchronize()
         self.reset()
@@ -246,6 +288,8 @@ class LlamaDecoder:
         """Consumes `count` tokens (device int64) at positions pos .. pos + count - 1 as one block: the projections run
         as tcgen05 GEMMs (int8 activations), the attention as the causal block kernel; afterwards the residual stream and
         its normalised copy of the LAST token are in self.x / self.xn, ready for the lm_head, and pos has advanced."""
+        if self.world > 1:
+            raise ValueError("the block prefill is not sharded: a row-sharded decoder takes its prompt token by token")
         be, cfg, st = self.be, self.cfg, self.stream.cuda_stream
         b = self._prefill_buffers()
         P = lambda t: t.data_ptr()
@@ -279,7 +323,7 @@ class LlamaDecoder:
         torch = self.torch
         ids = torch.tensor(prompt, dtype=torch.int64).pin_memory()
         if batched_prefill is None:
-            batched_prefill = self.act_mode == ACT_INT8
+            batched_prefill = self.act_mode == ACT_INT8 and self.world == 1
         with torch.cuda.stream(self.stream):
             done = 0
             if batched_prefill and len(prompt) >= self.PREFILL_MIN:
@@ -323,6 +367,8 @@ class LlamaDecoder:
         return self.logits.cpu().numpy()
 
     def close(self) -> None:
+        self.stream.synchronize()
+        self.graph_layers = self.graph_head = None     # captured collectives hold on to the communicator: release them before the group goes
         for h in self.h.values():
             self.be.dev_free(h)
         self.h.clear()
