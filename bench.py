@@ -701,7 +701,8 @@ def run_decode(args) -> None:
                 yield name, (1.0 + 0.02 * torch.randn(shape, generator=gen, device=dev, dtype=torch.float32)).cpu().numpy(), False
 
     t0 = time.perf_counter()
-    dec = LlamaDecoder(be, cfg, tensors(), act_mode=ACT_INT8, max_positions=1024, fused=args.fuse, rank=rank, world=world)
+    dec = LlamaDecoder(be, cfg, tensors(), act_mode=ACT_INT8, max_positions=1024, fused=args.fuse, rank=rank, world=world,
+                       gather="nccl" if args.gather == "nccl" else "peer")
     load_s = time.perf_counter() - t0
     dec.capture()
     token_prefill = args.token_prefill or world > 1     # the block prefill is not sharded
@@ -814,7 +815,8 @@ def run_decode(args) -> None:
                    "activations": "int8 (bit-exact reference codes)", "l2": "inputs larger than L2: 8.5 GB of weights stream per token",
                    "launch": f"two CUDA graphs per token, {launches_per_step} kernel launches (folded into the projections: '{dec.fuse}')", "weights": "torch.randn on the device, seed 6, N(0, 0.02)",
                    "sharding": ("none (one GPU)" if world == 1 else f"output rows of every matrix over {world} GPUs, rank-local heads and KV cache, "
-                                f"{gathers} NCCL all-gathers per token inside the step graphs (attention output, o, SwiGLU activation, down; logits)"),
+                                f"{gathers} all-gathers per token inside the step graphs (attention output, o, SwiGLU activation, down; logits), "
+                                + ("NCCL collectives" if args.gather == "nccl" else "each one launch of the peer-store all-gather kernel over NVLink")),
                    "load_s": load_s, "prefill": ("token by token" if token_prefill else "blocks of up to 512 tokens through the tcgen05 GEMM + causal block attention"),
                    "prefill_ms": prefill_ms, "prefill_tokens_per_s": prompt_len / (prefill_ms * 1e-3)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,

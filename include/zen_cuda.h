@@ -248,6 +248,13 @@ int zen_cuda_dev_gemv_gather(zen_cuda_gather* g, const zen_cuda_weights* const* 
 /* Waits (on the device, bounded) until the latest launch of every rank has landed here and copies the gathered
  * vector, [world][slot_floats] floats, to d_out (NULL: wait only). */
 int zen_cuda_dev_gather_fetch(zen_cuda_gather* g, float* d_out, void* stream);
+/* A plain all-gather of device vectors over a gather object's regions (peer stores over NVLink, flags, a bounded device
+ * wait; one launch, no collective library): rank r's d_piece (count floats, a multiple of 4, at most slot_floats, 16-byte
+ * aligned) lands in every rank's d_whole at [r * count, (r + 1) * count); d_piece may be this rank's slice of d_whole.
+ * For the vectors between the row-sharded projections of a decode step (attention output, residual stream, SwiGLU
+ * activation, logits).  All ranks enqueue the same sequence of these calls on the object; an object used here must not
+ * also be used by zen_cuda_dev_gemv_gather.  No counterpart in the reference (one device). */
+int zen_cuda_dev_allgather(zen_cuda_gather* g, const float* d_piece, size_t count, float* d_whole, void* stream);
 
 /* Greedy token pick on the device: for every token row, the index of the first maximum among the finite logits,
  * -1 when the row has none.  The greedy branch of the reference's sampler (sample_logits,

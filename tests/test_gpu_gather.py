@@ -82,6 +82,33 @@ def test_single_rank_chain_reads_previous_gather(be):
     be.dev_free(h)
 
 
+def test_single_rank_allgather(be):
+    """zen_cuda_dev_allgather with one rank: the piece goes through the rank's own slot (both parities, several launches,
+    two sizes on one object) and lands in the whole vector; in place when the piece is the whole vector's slice."""
+    import torch
+    from zeninfer_b200 import BackendError
+    dev = torch.device("cuda", 0)
+    pg = shard.PeerGather(be, 1, 0, 4096)
+    stream = torch.cuda.Stream(device=dev)
+    for launch, n in enumerate((4096, 128, 4096, 2048, 4)):
+        piece = torch.from_numpy(seeded_acts(1, n, 340 + launch)[0]).to(dev)
+        whole = torch.zeros(n, dtype=torch.float32, device=dev)
+        pg.allgather(piece.data_ptr(), n, whole.data_ptr(), stream.cuda_stream)
+        keep = piece.clone()
+        pg.allgather(piece.data_ptr(), n, piece.data_ptr(), stream.cuda_stream)      # in place
+        stream.synchronize()
+        be.dev_check(stream.cuda_stream)
+        assert torch.equal(whole, keep) and torch.equal(piece, keep)
+    buf = torch.zeros(8192, dtype=torch.float32, device=dev)
+    with pytest.raises(BackendError, match="dev_allgather"):
+        pg.allgather(buf.data_ptr(), 6, buf.data_ptr())               # not a multiple of 4 floats
+    with pytest.raises(BackendError, match="dev_allgather"):
+        pg.allgather(buf.data_ptr(), 8192, buf.data_ptr())            # larger than the slot
+    with pytest.raises(BackendError, match="dev_allgather"):
+        pg.allgather(buf.data_ptr() + 4, 8, buf.data_ptr())           # not 16-byte aligned
+    pg.close()
+
+
 def test_gather_rejects_bad_geometry(be):
     from zeninfer_b200 import BackendError
     rows, cols = 64, 256

@@ -1,4 +1,5 @@
-"""The row-sharded decoder on two or more GPUs, one process per GPU (spawned here), NCCL gathers on the decoder's stream.
+"""The row-sharded decoder on two GPUs, one process per GPU (spawned here); the gathers between the projections are the
+library's peer-store all-gather kernel (fp32 and int8 activations) or NCCL collectives (fp32) on the decoder's stream.
 
 Bars: every rank generates the golden ids of the unmodified reference (tests/golden/llama_tiny.npz) with logits within
 1e-3, with and without the captured step graphs; and, rows being independent, the sharded logits equal the logits of an
@@ -44,9 +45,9 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str):
     cfg, meta, prompt, _, _ = _golden()
     result = {}
     try:
-        for mode, tag in ((ACT_FP32, "fp32"), (ACT_INT8, "int8")):
+        for mode, tag, kind in ((ACT_FP32, "fp32", "peer"), (ACT_INT8, "int8", "peer"), (ACT_FP32, "nccl", "nccl")):
             model = lambda: synthetic_tensors(cfg, meta["seed"], meta["weight_std"])
-            dec = LlamaDecoder(be, cfg, model(), act_mode=mode, rank=rank, world=world)
+            dec = LlamaDecoder(be, cfg, model(), act_mode=mode, rank=rank, world=world, gather=kind)
             whole = LlamaDecoder(be, cfg, model(), act_mode=mode)
             try:
                 result[tag + "_ids_eager"] = dec.generate(prompt.tolist(), meta["max_new"])
@@ -83,8 +84,9 @@ def test_row_sharded_generation_matches_the_reference_and_the_unsharded_decoder(
     for r in range(world):
         got = torch.load(os.path.join(tmp_path, f"rank{r}.pt"), weights_only=False)
         for how in ("eager", "graph"):
-            assert got[f"fp32_ids_{how}"] == ids.tolist(), f"rank {r} {how}"
-            assert_parity(got[f"fp32_logits_{how}"], logits, 1e-3, f"rank {r} {how} logits vs the reference")
-            for tag in ("fp32", "int8"):
+            for tag in ("fp32", "nccl"):
+                assert got[f"{tag}_ids_{how}"] == ids.tolist(), f"rank {r} {tag} {how}"
+                assert_parity(got[f"{tag}_logits_{how}"], logits, 1e-3, f"rank {r} {tag} {how} logits vs the reference")
+            for tag in ("fp32", "int8", "nccl"):
                 assert got[f"{tag}_ids_{how}"] == got[f"{tag}_ids_whole"]
                 assert np.array_equal(got[f"{tag}_logits_{how}"], got[f"{tag}_logits_whole"]), f"rank {r} {tag} {how}: sharded != unsharded"

@@ -155,4 +155,53 @@ __global__ void __launch_bounds__(256) gather_fetch_kernel(const PeerGather g, f
         out[i] = __ldcv(src + i);   // written by peers: never through a stale non-coherent line
 }
 
+// A plain all-gather of device vectors over the same regions and flags, for the vectors no product kernel produces
+// (attention output, SwiGLU activation) or whose producer also folds other work in: every rank's `piece` (n floats, a
+// multiple of 4) ends up in every rank's `whole` at [rank * n, (rank + 1) * n).  One CTA: it copies the piece into its
+// slot of every rank's region (peer stores), meets at a CTA barrier, one thread fences once at system scope and raises
+// this launch's number in every rank's flags; warp 0 then waits (bounded) for all ranks' flags and the CTA copies the
+// other ranks' slots from the local region to `whole`.  The launch number is a device counter, so a captured launch can
+// be replayed.  A rank starts launch L only after its launch L-1 has seen every rank's L-1, i.e. after every rank has
+// finished reading launch L-2, whose parity launch L overwrites.  An object used by this kernel is not used by the
+// product kernels' fused gather (they number launches differently).
+__global__ void __launch_bounds__(1024) allgather_kernel(const PeerGather g, const float* __restrict__ piece, uint32_t n, float* __restrict__ whole,
+                                                         int* error_word) {
+    __shared__ int wait_ok;
+    pdl_launch_dependents();     // the next launch may stream its weights meanwhile; it reads `whole` only after its own wait
+    pdl_wait();
+    const unsigned long long launch = gather_epoch(g) + 1;
+    const uint32_t n4 = n / 4;
+    for (uint32_t peer = 0; peer < g.world; ++peer) {
+        float4* dst = reinterpret_cast<float4*>(gather_slot(g, launch - 1, peer, 0));
+        const float4* src = reinterpret_cast<const float4*>(piece);
+        for (uint32_t i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = src[i];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        fence_acq_rel_sys();
+        for (uint32_t p = 0; p < g.world; ++p) st_relaxed_sys(g.flags[p] + g.rank, launch);
+    }
+    if (threadIdx.x < 32) {
+        const bool ok = gather_wait(g, static_cast<int>(threadIdx.x), launch);
+        if (threadIdx.x == 0) wait_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned long long*>(g.epoch) = launch;   // counted even when the wait gave up
+    if (!wait_ok) {
+        if (threadIdx.x == 0) atomicExch(error_word, kErrPeerWaitTimeout);
+        return;
+    }
+    const float* local = gather_previous(g, launch);    // the parity launch `launch` wrote
+    for (uint32_t r = 0; r < g.world; ++r) {
+        float4* dst = reinterpret_cast<float4*>(whole + static_cast<size_t>(r) * n);
+        if (r == g.rank) {
+            if (reinterpret_cast<const float*>(dst) != piece)
+                for (uint32_t i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = reinterpret_cast<const float4*>(piece)[i];
+            continue;
+        }
+        const float4* src = reinterpret_cast<const float4*>(local + static_cast<size_t>(r) * g.slot_floats);
+        for (uint32_t i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = __ldcv(src + i);   // written by a peer: never through a stale line
+    }
+}
+
 }  // namespace zk

@@ -1230,6 +1230,20 @@ int zen_cuda_dev_gather_fetch(zen_cuda_gather* g, float* d_out, void* stream) {
     return 1;
 }
 
+int zen_cuda_dev_allgather(zen_cuda_gather* g, const float* d_piece, size_t count, float* d_whole, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!g || !d_piece || !d_whole || !count || count % 4 || g->dev.slot_floats % 4 || count > g->dev.slot_floats ||
+        (reinterpret_cast<uintptr_t>(d_piece) | reinterpret_cast<uintptr_t>(d_whole)) % 16)
+        return set_error(s, "dev_allgather: bad arguments (count and slot: multiples of 4 floats, count <= slot, 16-byte aligned vectors)") ? 1 : 0;
+    const cudaError_t e = launch_pdl(s, zk::allgather_kernel, dim3(1), dim3(1024), 0, stream ? static_cast<cudaStream_t>(stream) : s.stream, g->dev, d_piece,
+                                     static_cast<uint32_t>(count), d_whole, s.d_error);
+    ++s.stats.dispatches;
+    if (e != cudaSuccess) return set_error(s, std::string("dev_allgather: launch failed: ") + cudaGetErrorString(e)) ? 1 : 0;
+    return 1;
+}
+
 int zen_cuda_dev_greedy_pick(const zen_cuda_pick_segment* segments, size_t count, size_t tokens, int64_t* d_pick, void* stream) {
     State& s = state();
     std::lock_guard<std::mutex> lock(s.mutex);

@@ -15,8 +15,9 @@ Several GPUs (one process per GPU, `rank` of `world`): every matrix but the embe
 rank uploads only its rows, and the vector a row-cut product leaves in pieces is put together by an all-gather before
 the next operator needs it whole: the attention output (heads are cut with the q|k|v rows, so attention and the KV
 cache are rank-local), the o projection's residual stream, the SwiGLU activation, the down projection's residual
-stream, and the logits.  Four gathers per layer and one for the lm_head, as NCCL collectives on the decoder's stream
-(they are captured into the step graphs).  Rows are independent, so every rank holds the same residual stream bit for
+stream, and the logits.  Four gathers per layer and one for the lm_head, each one launch of the peer-store all-gather
+kernel (zen_cuda_dev_allgather; default) or an NCCL collective on the decoder's stream; either way they are captured
+into the step graphs.  Rows are independent, so every rank holds the same residual stream bit for
 bit and picks the same token.  The reference drives one device; the row cut is its worker cut (ComputePool::parallel_for,
 src/compute_pool.cpp:104-106).
 """
@@ -102,14 +103,16 @@ class LlamaDecoder:
     synthetic_tensors does; matrices must be Q8_0 raw blocks [rows, row_bytes]."""
 
     def __init__(self, backend: Backend, cfg: LlamaConfig, tensors, act_mode: int = ACT_INT8, max_positions: int | None = None, device=None,
-                 fused: bool | str = "nr", rank: int = 0, world: int = 1, group=None):
+                 fused: bool | str = "nr", rank: int = 0, world: int = 1, group=None, gather: str = "peer"):
         """fused: which of the layer's small operators are folded into the projection launches, as a string of letters:
         'n' RMSNorm into the q|k|v, gate|up and lm_head prologues, 's' SwiGLU into the down projection's prologue,
         'r' the residual adds into the o and down projections' stores.  True = all (5 launches per layer), False =
         none (8 per layer); the default folds what pays: the norm costs a CTA one extra pass over a 16 KB row, SwiGLU would
         cost every CTA 14336 exponentials.  Same arithmetic either way.
-        rank, world, group: this process's share of a row-sharded model and the torch.distributed group (NCCL) of the
-        ranks; world must divide the KV heads, the embedding, the ffn width and the vocabulary, and fused must be "nr"."""
+        rank, world, group: this process's share of a row-sharded model and the torch.distributed group of the ranks; world
+        must divide the KV heads, the embedding, the ffn width and the vocabulary, and fused must be "nr".
+        gather: "peer" = the library's own all-gather kernel over NVLink peer memory (the group only carries the IPC
+        handles and host barriers, any backend), "nccl" = all_gather_into_tensor (the group must be NCCL)."""
         import torch
         self.torch, self.be, self.cfg, self.act_mode = torch, backend, cfg, act_mode
         self.fuse = "nsr" if fused is True else "" if fused is False else str(fused)
@@ -122,7 +125,10 @@ class LlamaDecoder:
                     raise ValueError(f"{what} = {n} does not split over {self.world} ranks")
             if set(self.fuse) != set("nr"):
                 raise ValueError('a row-sharded decoder runs with fused="nr"')
-            import torch.distributed  # noqa: F401  (the collectives of _gather)
+            import torch.distributed  # noqa: F401  (the collectives of _gather, handle exchange, host barriers)
+            if gather not in ("peer", "nccl"):
+                raise ValueError(f"gather = {gather!r}")
+        self.gather_kind, self.peer = gather if self.world > 1 else "none", None
         self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.max_positions = max_positions or cfg.context
         self.stream = torch.cuda.Stream(device=self.dev)
@@ -153,6 +159,10 @@ class LlamaDecoder:
         self.v_cache = torch.zeros((cfg.layers, self.max_positions, KW // w), **f32)
         mine = lambda t: t[self.rank * (t.numel() // w):(self.rank + 1) * (t.numel() // w)]     # the piece this rank's rows produce
         self.x_mine, self.att_mine, self.hid_mine, self.logits_mine = mine(self.x), mine(self.att), mine(self.hid), mine(self.logits)
+        if self.gather_kind == "peer":
+            from . import shard
+            slot = max(E, QW, F, V) // w
+            self.peer = shard.PeerGather(backend, w, self.rank, (slot + 3) & ~3, group=group)     # collective: handles travel through the group
         cos, sin = rope_tables(cfg, self.max_positions)
         self.cos, self.sin = torch.from_numpy(cos).to(self.dev), torch.from_numpy(sin).to(self.dev)
         self.pos = torch.zeros(1, dtype=torch.int32, device=self.dev)
@@ -179,8 +189,17 @@ class LlamaDecoder:
     def _gather(self, whole, piece) -> None:
         """Every rank's piece into every rank's whole vector, in place (piece is this rank's slice of whole), ordered on
         the decoder's stream: the caller is inside `with torch.cuda.stream(self.stream)`."""
-        if self.world > 1:
+        if self.peer is not None:
+            self.peer.allgather(piece.data_ptr(), piece.numel(), whole.data_ptr(), self.stream.cuda_stream)
+        elif self.world > 1:
             self.torch.distributed.all_gather_into_tensor(whole, piece, group=self.group)
+
+    def sync_ranks(self) -> None:
+        """Host barrier after draining the own stream: the peer all-gather waits about a second for the other ranks on
+        the device, so the ranks begin a sequence of steps together."""
+        if self.world > 1:
+            self.stream.synchronize()
+            self.torch.distributed.barrier(group=self.group)
 
     def _enqueue_layers(self) -> None:
         be, cfg, st = self.be, self.cfg, self.stream.cuda_stream
@@ -235,6 +254,7 @@ class LlamaDecoder:
     def capture(self) -> None:
         """Runs one throw-away step (kernel attributes are set on first launch), then captures the two graphs."""
         torch = self.torch
+        self.sync_ranks()
         with torch.cuda.stream(self.stream):
             self.reset()
             self._enqueue_layers()
@@ -347,6 +367,7 @@ class LlamaDecoder:
         if not prompt or len(prompt) + max_new > self.max_positions:
             raise ValueError("prompt + max_new exceeds the configured positions")
         self.reset()
+        self.sync_ranks()
         out: list[int] = []
         with torch.cuda.stream(self.stream):
             self.feed_prompt(prompt, batched_prefill)
@@ -369,6 +390,9 @@ class LlamaDecoder:
     def close(self) -> None:
         self.stream.synchronize()
         self.graph_layers = self.graph_head = None     # captured collectives hold on to the communicator: release them before the group goes
+        if self.peer is not None:
+            self.peer.close()                          # collective: every rank closes its decoder
+            self.peer = None
         for h in self.h.values():
             self.be.dev_free(h)
         self.h.clear()

@@ -129,6 +129,11 @@ class PeerGather:
         """Device-side wait for every rank's latest launch, then a copy of the gathered [world][slot_floats] floats."""
         self.be.dev_gather_fetch(self.handle, d_out, stream)
 
+    def allgather(self, d_piece: int, count: int, d_whole: int, stream: int = 0) -> None:
+        """Plain all-gather of device vectors over this object's regions (zen_cuda_dev_allgather): rank r's `count` floats
+        land at d_whole[r * count : (r + 1) * count] on every rank.  Not to be mixed with gemv() on one object."""
+        self.be.dev_allgather(self.handle, d_piece, count, d_whole, stream)
+
     def close(self) -> None:
         if self.handle is None:
             return
