@@ -702,7 +702,7 @@ def run_decode(args) -> None:
 
     t0 = time.perf_counter()
     dec = LlamaDecoder(be, cfg, tensors(), act_mode=ACT_INT8, max_positions=1024, fused=args.fuse, rank=rank, world=world,
-                       gather="nccl" if args.gather == "nccl" else "peer")
+                       gather="nccl" if args.gather == "nccl" else "peer", cut=args.cut)
     load_s = time.perf_counter() - t0
     dec.capture()
     token_prefill = args.token_prefill or world > 1     # the block prefill is not sharded
@@ -760,7 +760,7 @@ def run_decode(args) -> None:
     # e2e: the public generate() call; every picked token is read back to the host as it is produced
     stamps = []
     e2e_new = 33
-    picked = dec.generate(prompt.tolist() if world == 1 else prompt[:32].tolist(), e2e_new, on_token=lambda _t: stamps.append(time.perf_counter()))
+    picked = dec.generate(prompt.tolist(), e2e_new, on_token=lambda _t: stamps.append(time.perf_counter()))
     e2e_tok_s = (e2e_new - 1) / (stamps[-1] - stamps[0])
     if world > 1:           # every rank picked the same tokens; the rate is the slowest rank's
         ids = torch.tensor(picked, device=dev)
@@ -806,7 +806,7 @@ def run_decode(args) -> None:
     fn, fs, fr = ("n" in dec.fuse), ("s" in dec.fuse), ("r" in dec.fuse)
     per_layer = 5 + (0 if (fn and fr) else 2) + (0 if fs else 1)   # q|k|v, attention block, o, gate|up, down + norm / residual / SwiGLU launches
     launches_per_step = 1 + (0 if fn else 1) + per_layer * cfg.layers + 1 + 1 + 2   # embed, layers, advance, lm_head, pick (2): per rank
-    gathers = (4 * cfg.layers + 1) if world > 1 else 0
+    gathers = ((2 if dec.col_cut else 4) * cfg.layers + 1) if world > 1 else 0
     print(json.dumps({
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
         "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
@@ -815,8 +815,10 @@ def run_decode(args) -> None:
                    "activations": "int8 (bit-exact reference codes)", "l2": "inputs larger than L2: 8.5 GB of weights stream per token",
                    "launch": f"two CUDA graphs per token, {launches_per_step} kernel launches (folded into the projections: '{dec.fuse}')", "weights": "torch.randn on the device, seed 6, N(0, 0.02)",
                    "sharding": ("none (one GPU)" if world == 1 else f"output rows of every matrix over {world} GPUs, rank-local heads and KV cache, "
-                                f"{gathers} all-gathers per token inside the step graphs (attention output, o, SwiGLU activation, down; logits), "
-                                + ("NCCL collectives" if args.gather == "nccl" else "each one launch of the peer-store all-gather kernel over NVLink")),
+                                f"{gathers} exchanges per token inside the step graphs "
+                                + ("(o and down cut by columns, their partial products all-reduced into the residual stream; logits gathered), "
+                                   if dec.col_cut else "(all-gathers of attention output, o, SwiGLU activation, down; logits), ")
+                                + ("NCCL collectives" if args.gather == "nccl" else "each one launch of a peer-store kernel over NVLink")),
                    "load_s": load_s, "prefill": ("token by token" if token_prefill else "blocks of up to 512 tokens through the tcgen05 GEMM + causal block attention"),
                    "prefill_ms": prefill_ms, "prefill_tokens_per_s": prompt_len / (prefill_ms * 1e-3)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
@@ -826,7 +828,7 @@ def run_decode(args) -> None:
         "e2e": {"value": e2e_tok_s, "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 8,
                 "api": "LlamaDecoder.generate: each picked token id is read back to the host, and fed to the next step from pinned host memory, "
                        "as the reference's generate loop does", "steps": e2e_new - 1},
-        "gpu_launches": steps * launches_per_step * world,
+        "gpu_launches": steps * (launches_per_step + (gathers if dec.peer is not None else 0)) * world,
     }))
     dec.close()
     if world > 1:
@@ -845,6 +847,9 @@ def main() -> None:
     ap.add_argument("--workload", default="q8_0_gemv")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU time for the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cut", default="rows+cols", choices=["rows", "rows+cols"],
+                    help="workload decode, N > 1: every matrix by output rows (four gathers per layer), or o and down by columns "
+                         "(two all-reduces per layer)")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: how the output shards are all-gathered after each product -- by the product kernel itself "
                          "(peer stores over NVLink, the default) or by an NCCL all-gather launched after it")

@@ -255,6 +255,10 @@ int zen_cuda_dev_gather_fetch(zen_cuda_gather* g, float* d_out, void* stream);
  * activation, logits).  All ranks enqueue the same sequence of these calls on the object; an object used here must not
  * also be used by zen_cuda_dev_gemv_gather.  No counterpart in the reference (one device). */
 int zen_cuda_dev_allgather(zen_cuda_gather* g, const float* d_piece, size_t count, float* d_whole, void* stream);
+/* The all-reduce that goes with a projection cut by columns: d_inout[i] += sum over ranks of that rank's d_partial[i]
+ * (count floats, same rules as above), added in rank order on every rank, so all ranks end with identical values.
+ * Shares the object's launch numbering with zen_cuda_dev_allgather: the two may alternate on one object. */
+int zen_cuda_dev_allreduce_add(zen_cuda_gather* g, const float* d_partial, size_t count, float* d_inout, void* stream);
 
 /* Greedy token pick on the device: for every token row, the index of the first maximum among the finite logits,
  * -1 when the row has none.  The greedy branch of the reference's sampler (sample_logits,

@@ -27,14 +27,17 @@ def _rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
     return (x * inv * w).astype(np.float32)
 
 
-def generate(cfg, tensors: dict, shapes: dict, prompt, max_new: int, rank: int = 0, world: int = 1, gather=None):
+def generate(cfg, tensors: dict, shapes: dict, prompt, max_new: int, rank: int = 0, world: int = 1, gather=None, cut: str = "rows"):
     """tensors: name -> array (Q8_0 raw blocks for matrices, fp32 for norms); shapes: name -> (rows, cols).
     Returns (ids, last_logits).
 
     world > 1 restates the row-sharded decoder: every matrix but the embedding table keeps rows
     [rank * rows / world, (rank + 1) * rows / world), attention runs on the rank's heads, and `gather(piece)` returns the
     concatenation of all ranks' pieces in rank order (four per layer: attention output, o projection, SwiGLU activation,
-    down projection; one for the logits).  Rows are independent, so the result equals the unsharded one."""
+    down projection; one for the logits).  Rows are independent, so the result equals the unsharded one.
+    cut = "rows+cols": the o and down projections keep columns [rank * cols / world, ...) instead, multiply the rank's own
+    attention output / SwiGLU activation, and the ranks' partial products are added in rank order (two exchanges per
+    layer); equal to the unsharded result up to fp32 rounding."""
     if gather is None:
         if world != 1:
             raise ValueError("a sharded run needs a gather")
@@ -42,10 +45,19 @@ def generate(cfg, tensors: dict, shapes: dict, prompt, max_new: int, rank: int =
     W = {n: _dequant_q8_0(a, *shapes[n]) for n, a in tensors.items() if len(shapes[n]) == 2}
     if world > 1:
         for n in W:
-            if n != "token_embd.weight":
+            if cut == "rows+cols" and n.endswith(("attn_output.weight", "ffn_down.weight")):
+                per = W[n].shape[1] // world
+                W[n] = W[n][:, rank * per:(rank + 1) * per]
+            elif n != "token_embd.weight":
                 per = W[n].shape[0] // world
                 W[n] = W[n][rank * per:(rank + 1) * per]
     N = {n: np.asarray(a, np.float32) for n, a in tensors.items() if len(shapes[n]) == 1}
+
+    def add_partials(x: np.ndarray, partial: np.ndarray) -> np.ndarray:
+        for piece in gather(partial).reshape(world, -1):     # x + p0 + p1 + ..., the same order on every rank
+            x = x + piece
+        return x
+
     E, H, KH, D = cfg.embedding, cfg.heads // world, cfg.kv_heads // world, cfg.head_dim      # H, KH: this rank's heads
     half = D // 2
     kc = [np.zeros((0, KH * D), np.float32) for _ in range(cfg.layers)]
@@ -78,10 +90,11 @@ def generate(cfg, tensors: dict, shapes: dict, prompt, max_new: int, rank: int =
                 e = np.exp(sc - sc.max()).astype(np.float32)
                 a = e * np.float32(1.0 / float(e.astype(np.float64).sum()))
                 att[h * D:(h + 1) * D] = a @ vc[l][:, kh * D:(kh + 1) * D]
-            x = x + gather(W[p + "attn_output.weight"] @ gather(att))
+            x = add_partials(x, W[p + "attn_output.weight"] @ att) if cut == "rows+cols" else x + gather(W[p + "attn_output.weight"] @ gather(att))
             xn = _rms_norm(x, N[p + "ffn_norm.weight"], cfg.rms_eps)
             g, u = W[p + "ffn_gate.weight"] @ xn, W[p + "ffn_up.weight"] @ xn
-            x = x + gather(W[p + "ffn_down.weight"] @ gather(((g / (np.float32(1.0) + np.exp(-g))) * u).astype(np.float32)))
+            hid = ((g / (np.float32(1.0) + np.exp(-g))) * u).astype(np.float32)
+            x = add_partials(x, W[p + "ffn_down.weight"] @ hid) if cut == "rows+cols" else x + gather(W[p + "ffn_down.weight"] @ gather(hid))
         return gather(W["output.weight"] @ _rms_norm(x, N["output_norm.weight"], cfg.rms_eps))
 
     def pick(logits: np.ndarray) -> int:

@@ -99,6 +99,16 @@ def test_single_rank_allgather(be):
         stream.synchronize()
         be.dev_check(stream.cuda_stream)
         assert torch.equal(whole, keep) and torch.equal(piece, keep)
+    # the all-reduce on the same object (the launch numbering is shared): with one rank, inout += partial
+    part = torch.from_numpy(seeded_acts(1, 1024, 350)[0]).to(dev)
+    acc = torch.from_numpy(seeded_acts(1, 1024, 351)[0]).to(dev)
+    want = acc + part
+    pg.allreduce_add(part.data_ptr(), 1024, acc.data_ptr(), stream.cuda_stream)
+    stream.synchronize()
+    be.dev_check(stream.cuda_stream)
+    assert torch.equal(acc, want)
+    with pytest.raises(BackendError, match="dev_allreduce_add"):
+        pg.allreduce_add(acc.data_ptr(), 1024, acc.data_ptr())       # in place is not a sum
     buf = torch.zeros(8192, dtype=torch.float32, device=dev)
     with pytest.raises(BackendError, match="dev_allgather"):
         pg.allgather(buf.data_ptr(), 6, buf.data_ptr())               # not a multiple of 4 floats

@@ -2,8 +2,9 @@
 library's peer-store all-gather kernel (fp32 and int8 activations) or NCCL collectives (fp32) on the decoder's stream.
 
 Bars: every rank generates the golden ids of the unmodified reference (tests/golden/llama_tiny.npz) with logits within
-1e-3, with and without the captured step graphs; and, rows being independent, the sharded logits equal the logits of an
-unsharded decoder on the same GPU bit for bit (fp32 and int8 activations)."""
+1e-3, with and without the captured step graphs; rows being independent, the row-sharded logits equal the logits of an
+unsharded decoder on the same GPU bit for bit (fp32 and int8 activations); with o and down cut by columns the logits stay
+within 1e-3 of the unsharded ones and are identical on all ranks."""
 import json
 import os
 import socket
@@ -45,9 +46,10 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str):
     cfg, meta, prompt, _, _ = _golden()
     result = {}
     try:
-        for mode, tag, kind in ((ACT_FP32, "fp32", "peer"), (ACT_INT8, "int8", "peer"), (ACT_FP32, "nccl", "nccl")):
+        for mode, tag, kind, cut in ((ACT_FP32, "fp32", "peer", "rows"), (ACT_INT8, "int8", "peer", "rows"), (ACT_FP32, "nccl", "nccl", "rows"),
+                                     (ACT_FP32, "cols", "peer", "rows+cols"), (ACT_INT8, "cols8", "peer", "rows+cols")):
             model = lambda: synthetic_tensors(cfg, meta["seed"], meta["weight_std"])
-            dec = LlamaDecoder(be, cfg, model(), act_mode=mode, rank=rank, world=world, gather=kind)
+            dec = LlamaDecoder(be, cfg, model(), act_mode=mode, rank=rank, world=world, gather=kind, cut=cut)
             whole = LlamaDecoder(be, cfg, model(), act_mode=mode)
             try:
                 result[tag + "_ids_eager"] = dec.generate(prompt.tolist(), meta["max_new"])
@@ -84,9 +86,14 @@ def test_row_sharded_generation_matches_the_reference_and_the_unsharded_decoder(
     for r in range(world):
         got = torch.load(os.path.join(tmp_path, f"rank{r}.pt"), weights_only=False)
         for how in ("eager", "graph"):
-            for tag in ("fp32", "nccl"):
+            for tag in ("fp32", "nccl", "cols"):
                 assert got[f"{tag}_ids_{how}"] == ids.tolist(), f"rank {r} {tag} {how}"
                 assert_parity(got[f"{tag}_logits_{how}"], logits, 1e-3, f"rank {r} {tag} {how} logits vs the reference")
             for tag in ("fp32", "int8", "nccl"):
                 assert got[f"{tag}_ids_{how}"] == got[f"{tag}_ids_whole"]
                 assert np.array_equal(got[f"{tag}_logits_{how}"], got[f"{tag}_logits_whole"]), f"rank {r} {tag} {how}: sharded != unsharded"
+            # the column cut reorders the block sums of o and down: close to the unsharded logits, and identical on all ranks
+            assert_parity(got[f"cols8_logits_{how}"], got["cols8_logits_whole"], 1e-3, f"rank {r} column cut, int8 activations, {how}")
+            first = torch.load(os.path.join(tmp_path, "rank0.pt"), weights_only=False)
+            for tag in ("cols", "cols8"):
+                assert np.array_equal(got[f"{tag}_logits_{how}"], first[f"{tag}_logits_{how}"]), f"rank {r} and rank 0 differ ({tag}, {how})"

@@ -4,6 +4,7 @@ import json
 import os
 
 import numpy as np
+import pytest
 
 from zeninfer_b200.llama import LlamaConfig, rope_tables, synthetic_tensors, tensor_plan
 
@@ -43,7 +44,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _sharded_rank(rank: int, world: int, port: int, out_dir: str):
+def _sharded_rank(rank: int, world: int, port: int, out_dir: str, cut: str):
     import sys
     sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     import torch
@@ -64,20 +65,22 @@ def _sharded_rank(rank: int, world: int, port: int, out_dir: str):
             gathers[0] += 1
             return whole.numpy()
 
-        ids, logits = ol.generate(cfg, tensors, shapes, prompt, meta["max_new"], rank=rank, world=world, gather=gather)
+        ids, logits = ol.generate(cfg, tensors, shapes, prompt, meta["max_new"], rank=rank, world=world, gather=gather, cut=cut)
         steps = len(prompt) + meta["max_new"] - 1
-        assert gathers[0] == steps * (4 * cfg.layers + 1)
+        assert gathers[0] == steps * ((4 if cut == "rows" else 2) * cfg.layers + 1)
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), ids=np.asarray(ids), logits=logits)
     finally:
         dist.destroy_process_group()
 
 
-def test_row_sharded_decode_with_gloo_gathers_reproduces_the_reference(tmp_path):
-    """The sharding scheme of the multi-GPU decoder (rows of every matrix cut over the ranks, rank-local heads, four
-    gathers per layer and one for the logits) restated in numpy with real collectives: two processes, gloo."""
+@pytest.mark.parametrize("cut", ["rows", "rows+cols"])
+def test_sharded_decode_with_gloo_exchanges_reproduces_the_reference(tmp_path, cut):
+    """The sharding schemes of the multi-GPU decoder restated in numpy with real collectives (two processes, gloo): rows
+    of every matrix cut over the ranks, rank-local heads, four gathers per layer and one for the logits; or o and down
+    cut by columns, their partial products added in rank order (two exchanges per layer)."""
     import torch.multiprocessing as mp
     world = 2
-    mp.spawn(_sharded_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_sharded_rank, args=(world, _free_port(), str(tmp_path), cut), nprocs=world, join=True)
     _, _, _, ids, logits = load_golden()
     for r in range(world):
         with np.load(os.path.join(tmp_path, f"rank{r}.npz")) as got:

@@ -36,7 +36,7 @@ ABI_SYMBOLS = (
     "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_gemm_workspace_bytes", "zen_cuda_dev_gemm_q8_0",
     "zen_cuda_dev_gemm_q8_0_noalloc",
     "zen_cuda_gather_region_bytes", "zen_cuda_ipc_alloc", "zen_cuda_ipc_open", "zen_cuda_ipc_close", "zen_cuda_ipc_free",
-    "zen_cuda_gather_create", "zen_cuda_gather_destroy", "zen_cuda_dev_gemv_gather", "zen_cuda_dev_gather_fetch", "zen_cuda_dev_allgather",
+    "zen_cuda_gather_create", "zen_cuda_gather_destroy", "zen_cuda_dev_gemv_gather", "zen_cuda_dev_gather_fetch", "zen_cuda_dev_allgather", "zen_cuda_dev_allreduce_add",
     "zen_cuda_dev_greedy_pick",
     "zen_cuda_dev_embed_q8_0", "zen_cuda_dev_rms_norm", "zen_cuda_dev_rope_kv_append", "zen_cuda_dev_attention", "zen_cuda_dev_silu_mul",
     "zen_cuda_dev_advance_position", "zen_cuda_dev_gemv_swiglu", "zen_cuda_dev_attention_block", "zen_cuda_dev_gemv_fused",
@@ -134,6 +134,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_dev_gemv_gather.argtypes = [vp, C.POINTER(vp), C.POINTER(vp), sz, vp, sz, i, vp]
     lib.zen_cuda_dev_gather_fetch.argtypes = [vp, vp, vp]
     lib.zen_cuda_dev_allgather.argtypes = [vp, vp, sz, vp, vp]
+    lib.zen_cuda_dev_allreduce_add.argtypes = [vp, vp, sz, vp, vp]
     lib.zen_cuda_dev_greedy_pick.argtypes = [C.POINTER(PickSegment), sz, sz, vp, vp]
     lib.zen_cuda_dev_embed_q8_0.argtypes = [vp, vp, vp, vp]
     lib.zen_cuda_dev_rms_norm.argtypes = [vp, vp, vp, vp, sz, sz, C.c_float, vp]
@@ -360,6 +361,11 @@ class Backend:
         """Every rank's d_piece (count floats) into every rank's d_whole, by peer stores and a bounded device wait."""
         if not self.lib.zen_cuda_dev_allgather(gather, d_piece, count, d_whole, stream):
             self._fail("dev_allgather")
+
+    def dev_allreduce_add(self, gather: int, d_partial: int, count: int, d_inout: int, stream: int = 0) -> None:
+        """d_inout += the ranks' d_partial vectors, added in rank order on every rank."""
+        if not self.lib.zen_cuda_dev_allreduce_add(gather, d_partial, count, d_inout, stream):
+            self._fail("dev_allreduce_add")
 
     def dev_quantize_acts(self, d_x: int, d_codes: int, d_scales: int, tokens: int, columns: int, stream: int = 0) -> None:
         if not self.lib.zen_cuda_dev_quantize_acts(d_x, d_codes, d_scales, tokens, columns, stream):

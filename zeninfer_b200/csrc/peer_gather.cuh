@@ -204,4 +204,48 @@ __global__ void __launch_bounds__(1024) allgather_kernel(const PeerGather g, con
     }
 }
 
+// The all-reduce that goes with a column cut: inout[i] += partial_0[i] + partial_1[i] + ... , the ranks' partial products
+// added in rank order on every rank, so that all ranks hold the same sums bit for bit.  Same regions, flags, launch
+// counter and parities as allgather_kernel (the two may alternate on one object); a rank's own partial is read from
+// `partial` and not sent to itself.
+__global__ void __launch_bounds__(1024) allreduce_add_kernel(const PeerGather g, const float* __restrict__ partial, uint32_t n, float* __restrict__ inout,
+                                                             int* error_word) {
+    __shared__ int wait_ok;
+    pdl_launch_dependents();
+    pdl_wait();
+    const unsigned long long launch = gather_epoch(g) + 1;
+    const uint32_t n4 = n / 4;
+    const float4* mine = reinterpret_cast<const float4*>(partial);
+    for (uint32_t peer = 0; peer < g.world; ++peer) {
+        if (peer == g.rank) continue;
+        float4* dst = reinterpret_cast<float4*>(gather_slot(g, launch - 1, peer, 0));
+        for (uint32_t i = threadIdx.x; i < n4; i += blockDim.x) dst[i] = mine[i];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        fence_acq_rel_sys();
+        for (uint32_t p = 0; p < g.world; ++p) st_relaxed_sys(g.flags[p] + g.rank, launch);
+    }
+    if (threadIdx.x < 32) {
+        const bool ok = gather_wait(g, static_cast<int>(threadIdx.x), launch);
+        if (threadIdx.x == 0) wait_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *reinterpret_cast<volatile unsigned long long*>(g.epoch) = launch;
+    if (!wait_ok) {
+        if (threadIdx.x == 0) atomicExch(error_word, kErrPeerWaitTimeout);
+        return;
+    }
+    const float* local = gather_previous(g, launch);
+    float4* io = reinterpret_cast<float4*>(inout);
+    for (uint32_t i = threadIdx.x; i < n4; i += blockDim.x) {
+        float4 acc = io[i];
+        for (uint32_t r = 0; r < g.world; ++r) {
+            const float4 v = r == g.rank ? mine[i] : __ldcv(reinterpret_cast<const float4*>(local + static_cast<size_t>(r) * g.slot_floats) + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        io[i] = acc;
+    }
+}
+
 }  // namespace zk

@@ -1244,6 +1244,20 @@ int zen_cuda_dev_allgather(zen_cuda_gather* g, const float* d_piece, size_t coun
     return 1;
 }
 
+int zen_cuda_dev_allreduce_add(zen_cuda_gather* g, const float* d_partial, size_t count, float* d_inout, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!g || !d_partial || !d_inout || d_partial == d_inout || !count || count % 4 || g->dev.slot_floats % 4 || count > g->dev.slot_floats ||
+        (reinterpret_cast<uintptr_t>(d_partial) | reinterpret_cast<uintptr_t>(d_inout)) % 16)
+        return set_error(s, "dev_allreduce_add: bad arguments (count and slot: multiples of 4 floats, count <= slot, 16-byte aligned distinct vectors)") ? 1 : 0;
+    const cudaError_t e = launch_pdl(s, zk::allreduce_add_kernel, dim3(1), dim3(1024), 0, stream ? static_cast<cudaStream_t>(stream) : s.stream, g->dev,
+                                     d_partial, static_cast<uint32_t>(count), d_inout, s.d_error);
+    ++s.stats.dispatches;
+    if (e != cudaSuccess) return set_error(s, std::string("dev_allreduce_add: launch failed: ") + cudaGetErrorString(e)) ? 1 : 0;
+    return 1;
+}
+
 int zen_cuda_dev_greedy_pick(const zen_cuda_pick_segment* segments, size_t count, size_t tokens, int64_t* d_pick, void* stream) {
     State& s = state();
     std::lock_guard<std::mutex> lock(s.mutex);

@@ -17,7 +17,11 @@ the next operator needs it whole: the attention output (heads are cut with the q
 cache are rank-local), the o projection's residual stream, the SwiGLU activation, the down projection's residual
 stream, and the logits.  Four gathers per layer and one for the lm_head, each one launch of the peer-store all-gather
 kernel (zen_cuda_dev_allgather; default) or an NCCL collective on the decoder's stream; either way they are captured
-into the step graphs.  Rows are independent, so every rank holds the same residual stream bit for
+into the step graphs.  With cut="rows+cols" the o and down projections are cut by columns instead (a rank multiplies
+its own heads' attention output, or its own slice of the SwiGLU activation, by the matching columns): their partial
+products are summed into the residual stream by one all-reduce each (zen_cuda_dev_allreduce_add, rank order, identical
+on every rank), which leaves two exchanges per layer instead of four; the sums then differ from the unsharded
+decoder's by fp32 rounding (the order of the block sums changes), not by more.  Rows are independent, so every rank holds the same residual stream bit for
 bit and picks the same token.  The reference drives one device; the row cut is its worker cut (ComputePool::parallel_for,
 src/compute_pool.cpp:104-106).
 """
@@ -103,7 +107,7 @@ class LlamaDecoder:
     synthetic_tensors does; matrices must be Q8_0 raw blocks [rows, row_bytes]."""
 
     def __init__(self, backend: Backend, cfg: LlamaConfig, tensors, act_mode: int = ACT_INT8, max_positions: int | None = None, device=None,
-                 fused: bool | str = "nr", rank: int = 0, world: int = 1, group=None, gather: str = "peer"):
+                 fused: bool | str = "nr", rank: int = 0, world: int = 1, group=None, gather: str = "peer", cut: str = "rows+cols"):
         """fused: which of the layer's small operators are folded into the projection launches, as a string of letters:
         'n' RMSNorm into the q|k|v, gate|up and lm_head prologues, 's' SwiGLU into the down projection's prologue,
         'r' the residual adds into the o and down projections' stores.  True = all (5 launches per layer), False =
@@ -112,7 +116,9 @@ class LlamaDecoder:
         rank, world, group: this process's share of a row-sharded model and the torch.distributed group of the ranks; world
         must divide the KV heads, the embedding, the ffn width and the vocabulary, and fused must be "nr".
         gather: "peer" = the library's own all-gather kernel over NVLink peer memory (the group only carries the IPC
-        handles and host barriers, any backend), "nccl" = all_gather_into_tensor (the group must be NCCL)."""
+        handles and host barriers, any backend), "nccl" = all_gather_into_tensor (the group must be NCCL).
+        cut: "rows" = every matrix by output rows (four gathers per layer); "rows+cols" (default) = o and down by columns,
+        summed by an all-reduce (two exchanges per layer; with gather="nccl" the row cut is used)."""
         import torch
         self.torch, self.be, self.cfg, self.act_mode = torch, backend, cfg, act_mode
         self.fuse = "nsr" if fused is True else "" if fused is False else str(fused)
@@ -128,6 +134,11 @@ class LlamaDecoder:
             import torch.distributed  # noqa: F401  (the collectives of _gather, handle exchange, host barriers)
             if gather not in ("peer", "nccl"):
                 raise ValueError(f"gather = {gather!r}")
+            if gather == "nccl" and cut == "rows+cols":
+                cut = "rows"                               # the all-reduce in rank order is the peer kernel's
+            if cut not in ("rows", "rows+cols"):
+                raise ValueError(f"cut = {cut!r}")
+        self.col_cut = self.world > 1 and cut == "rows+cols"
         self.gather_kind, self.peer = gather if self.world > 1 else "none", None
         self.dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.max_positions = max_positions or cfg.context
@@ -138,7 +149,12 @@ class LlamaDecoder:
         for name, arr, is_matrix in tensors:
             if is_matrix:
                 rows, cols = shapes[name]
-                if self.world > 1 and name != "token_embd.weight":     # this rank's rows only; every rank fetches embeddings itself
+                if self.col_cut and name.endswith(("attn_output.weight", "ffn_down.weight")):
+                    # this rank's columns: whole 34-byte blocks [b0, b1) of every row, copied out of the source
+                    nb = cols // 32 // self.world
+                    part = np.ascontiguousarray(np.asarray(arr).reshape(rows, cols // 32, 34)[:, self.rank * nb:(self.rank + 1) * nb]).reshape(rows, nb * 34)
+                    self.h[name] = backend.dev_upload("Q8_0", part, rows, nb * 32)
+                elif self.world > 1 and name != "token_embd.weight":   # this rank's rows only; every rank fetches embeddings itself
                     per = rows // self.world
                     self.h[name] = backend.dev_upload("Q8_0", arr, rows, cols, self.rank * per, per)
                 else:
@@ -219,10 +235,14 @@ class LlamaDecoder:
             be.dev_attention_block(P(self.q), P(self.k), P(self.v), P(self.cos), P(self.sin), cfg.head_dim // 2, P(self.pos), P(self.k_cache[layer]),
                                    P(self.v_cache[layer]), P(self.att_mine), cfg.heads // self.world, cfg.kv_heads // self.world, cfg.head_dim,
                                    self.max_positions, 0.0, 0, st)
-            self._gather(self.att, self.att_mine)
             # attention output projection and its residual add (x += o(att))
-            self._gemv([self.h[p + "attn_output.weight"]], [P(self.x_mine) if fr else P(self.tmp)], P(self.att), acc=fr, warm=self.h[p + "ffn_gate.weight"])
-            self._gather(self.x, self.x_mine)
+            if self.col_cut:      # this rank's heads times their columns of o: a partial product of every output, summed over the ranks into x
+                self._gemv([self.h[p + "attn_output.weight"]], [P(self.tmp)], P(self.att_mine), warm=self.h[p + "ffn_gate.weight"])
+                self.peer.allreduce_add(P(self.tmp), E, P(self.x), st)
+            else:
+                self._gather(self.att, self.att_mine)
+                self._gemv([self.h[p + "attn_output.weight"]], [P(self.x_mine) if fr else P(self.tmp)], P(self.att), acc=fr, warm=self.h[p + "ffn_gate.weight"])
+                self._gather(self.x, self.x_mine)
             # ffn norm (with the residual add when it was not folded into the store)
             if not fn:
                 be.dev_rms_norm(P(self.x), None if fr else P(self.tmp), P(self.norm[p + "ffn_norm.weight"]), P(self.xn), E, 1, eps, st)
@@ -232,10 +252,15 @@ class LlamaDecoder:
                        norm=P(self.norm[p + "ffn_norm.weight"]) if fn else None, warm=self.h[p + "ffn_down.weight"])
             if not fs:
                 be.dev_silu_mul(P(self.gate), P(self.up), P(self.hid_mine), cfg.ffn // self.world, st)
-                self._gather(self.hid, self.hid_mine)
-            self._gemv([self.h[p + "ffn_down.weight"]], [P(self.x_mine) if fr else P(self.tmp)], P(self.up) if fs else P(self.hid),
-                       gate=P(self.gate) if fs else None, acc=fr, warm=nxt_q)                                      # (x +=) down(silu(gate) * up)
-            self._gather(self.x, self.x_mine)
+            if self.col_cut:
+                self._gemv([self.h[p + "ffn_down.weight"]], [P(self.tmp)], P(self.hid_mine), warm=nxt_q)
+                self.peer.allreduce_add(P(self.tmp), E, P(self.x), st)
+            else:
+                if not fs:
+                    self._gather(self.hid, self.hid_mine)
+                self._gemv([self.h[p + "ffn_down.weight"]], [P(self.x_mine) if fr else P(self.tmp)], P(self.up) if fs else P(self.hid),
+                           gate=P(self.gate) if fs else None, acc=fr, warm=nxt_q)                                  # (x +=) down(silu(gate) * up)
+                self._gather(self.x, self.x_mine)
             # the next norm: the next layer's attention norm, or the output norm
             nxt = self.norm[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < cfg.layers else self.norm["output_norm.weight"]
             if not fn:

@@ -134,6 +134,10 @@ class PeerGather:
         land at d_whole[r * count : (r + 1) * count] on every rank.  Not to be mixed with gemv() on one object."""
         self.be.dev_allgather(self.handle, d_piece, count, d_whole, stream)
 
+    def allreduce_add(self, d_partial: int, count: int, d_inout: int, stream: int = 0) -> None:
+        """d_inout += sum of every rank's d_partial, in rank order (zen_cuda_dev_allreduce_add)."""
+        self.be.dev_allreduce_add(self.handle, d_partial, count, d_inout, stream)
+
     def close(self) -> None:
         if self.handle is None:
             return
