@@ -17,7 +17,7 @@ import subprocess
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-Q8_0, Q4_0, Q6_K = 8, 2, 14  # GGML type ids, as in the GGUF tensor directory
+Q8_0, Q4_0, Q6_K, Q4_K, Q5_K = 8, 2, 14, 12, 13  # GGML type ids, as in the GGUF tensor directory
 
 _u8p = C.POINTER(C.c_uint8)
 _i8p = C.POINTER(C.c_int8)

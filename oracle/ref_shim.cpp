@@ -20,6 +20,8 @@ const zen::quant::Format* format_for(int ggml_type) {
     case 8: return zen::quant::find("Q8_0");
     case 2: return zen::quant::find("Q4_0");
     case 14: return zen::quant::find("Q6_K");
+    case 12: return zen::quant::find("Q4_K");
+    case 13: return zen::quant::find("Q5_K");
     default: return nullptr;
     }
 }

@@ -25,7 +25,7 @@
 
 #define ZO_API __attribute__((visibility("default")))
 
-enum { ZO_Q8_0 = 8, ZO_Q4_0 = 2, ZO_Q6_K = 14 }; /* GGML type ids */
+enum { ZO_Q8_0 = 8, ZO_Q4_0 = 2, ZO_Q6_K = 14, ZO_Q4_K = 12, ZO_Q5_K = 13 }; /* GGML type ids */
 
 /* ---- binary16 <-> binary32: src/quant.cpp:80-122 ------------------------ */
 
@@ -82,8 +82,24 @@ static inline uint16_t rd16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] <
 
 /* ---- format table rows: src/quant.cpp:253,257,259 and :894-943 ---------- */
 
-ZO_API size_t zo_block_elements(int fmt) { return fmt == ZO_Q6_K ? 256 : (fmt == ZO_Q8_0 || fmt == ZO_Q4_0) ? 32 : 0; }
-ZO_API size_t zo_block_bytes(int fmt) { return fmt == ZO_Q8_0 ? 34 : fmt == ZO_Q4_0 ? 18 : fmt == ZO_Q6_K ? 210 : 0; }
+ZO_API size_t zo_block_elements(int fmt) {
+    return (fmt == ZO_Q6_K || fmt == ZO_Q4_K || fmt == ZO_Q5_K) ? 256 : (fmt == ZO_Q8_0 || fmt == ZO_Q4_0) ? 32 : 0;
+}
+ZO_API size_t zo_block_bytes(int fmt) {   /* Q4_K, Q5_K: src/quant.cpp:273-274 */
+    return fmt == ZO_Q8_0 ? 34 : fmt == ZO_Q4_0 ? 18 : fmt == ZO_Q6_K ? 210 : fmt == ZO_Q4_K ? 144 : fmt == ZO_Q5_K ? 176 : 0;
+}
+
+/* The 6-bit scale and minimum of sub-block j (0..7) of a Q4_K / Q5_K super-block, from its 12 packed bytes:
+ * src/quant.cpp:133-141. */
+static inline void k_scale_min(unsigned j, const uint8_t* q, unsigned* scale, unsigned* min) {
+    if (j < 4) {
+        *scale = q[j] & 63u;
+        *min = q[j + 4] & 63u;
+    } else {
+        *scale = (q[j + 4] & 15u) | ((unsigned)(q[j - 4] >> 6) << 4);
+        *min = (unsigned)(q[j + 4] >> 4) | ((unsigned)(q[j] >> 6) << 4);
+    }
+}
 ZO_API size_t zo_row_bytes(int fmt, size_t columns) {
     const size_t be = zo_block_elements(fmt);
     if (!be || columns % be) return 0;
@@ -111,6 +127,28 @@ ZO_API int zo_dequantize(int fmt, const uint8_t* src, size_t n, float* dst) {
                 const uint8_t q = p[2 + j];
                 dst[b * 32 + j] = (float)((int)(q & 15) - 8) * d;
                 dst[b * 32 + j + 16] = (float)((int)(q >> 4) - 8) * d;
+            }
+        }
+        return 1;
+    }
+    if (fmt == ZO_Q4_K || fmt == ZO_Q5_K) {   /* src/quant.cpp:439-457 and :458-476: y = (d * sc) * q - dmin * m */
+        const int q5 = fmt == ZO_Q5_K;
+        if (n % 256) return 0;
+        for (size_t b = 0; b < n / 256; ++b) {
+            const uint8_t* p = src + b * (q5 ? 176 : 144);
+            const float d = zo_half_to_float(rd16(p)), dmin = zo_half_to_float(rd16(p + 2));
+            const uint8_t* scales = p + 4; const uint8_t* qh = p + 16; const uint8_t* ql = p + (q5 ? 48 : 16);
+            size_t out = b * 256;
+            for (unsigned pair = 0; pair < 4; ++pair) {     /* 64 values: low nibbles, then high nibbles, of 32 bytes */
+                unsigned sc, m;
+                k_scale_min(2 * pair, scales, &sc, &m);
+                const float d1 = d * (float)sc, m1 = dmin * (float)m;
+                k_scale_min(2 * pair + 1, scales, &sc, &m);
+                const float d2 = d * (float)sc, m2 = dmin * (float)m;
+                const unsigned u1 = 1u << (2 * pair), u2 = 2u << (2 * pair);
+                for (unsigned l = 0; l < 32; ++l) dst[out++] = d1 * (float)((ql[l] & 15u) + ((q5 && (qh[l] & u1)) ? 16u : 0u)) - m1;
+                for (unsigned l = 0; l < 32; ++l) dst[out++] = d2 * (float)((unsigned)(ql[l] >> 4) + ((q5 && (qh[l] & u2)) ? 16u : 0u)) - m2;
+                ql += 32;
             }
         }
         return 1;
@@ -323,6 +361,43 @@ ZO_API int zo_gemv_q6k_f32(const uint8_t* weights, const float* x, float* y, siz
     return 1;
 }
 
+/* ---- Q4_K / Q5_K GEMV, fp32 activations: kernels/avx2.cpp:329-378 (route src/quant.cpp:1020-1031, columns % 256 == 0).
+ *      Per sub-block of 32: ds = d * sc, ms = dmin * m; chunk c (8 lanes) of the sub-block goes to accumulator c:
+ *      w = ds * float(q) - ms (a multiply, then a subtract), acc[c] = fma(w, x, acc[c]); the four accumulators are added
+ *      pairwise and summed across lanes at the end of the row. ----------------------------------------------------- */
+
+ZO_API int zo_gemv_q4k_q5k_f32(const uint8_t* weights, const float* x, float* y, size_t rows, size_t columns, int q5) {
+    if (!weights || !x || !y || !rows || !columns || columns % 256) return 0;
+    const size_t block_bytes = q5 ? 176 : 144, blocks = columns / 256;
+    for (size_t r = 0; r < rows; ++r) {
+        float acc[4][8] = {{0}};
+        for (size_t b = 0; b < blocks; ++b) {
+            const uint8_t* p = weights + (r * blocks + b) * block_bytes;
+            const float d = zo_half_to_float(rd16(p)), dm = zo_half_to_float(rd16(p + 2));
+            const uint8_t* scales = p + 4; const uint8_t* qh = p + 16; const uint8_t* ql = p + (q5 ? 48 : 16);
+            for (unsigned group = 0; group < 8; ++group) {
+                unsigned sc, mn;
+                k_scale_min(group, scales, &sc, &mn);
+                const float ds = d * (float)sc, ms = dm * (float)mn;
+                const unsigned shift = (group & 1u) * 4;
+                for (unsigned chunk = 0; chunk < 4; ++chunk)
+                    for (unsigned j = 0; j < 8; ++j) {
+                        const unsigned l = chunk * 8 + j;
+                        unsigned q = ((unsigned)ql[(group / 2) * 32 + l] >> shift) & 15u;
+                        if (q5) q |= (((unsigned)qh[l] >> group) & 1u) << 4;
+                        const float prod = ds * (float)q;       /* rounded before the subtraction, as mul_ps then sub_ps */
+                        const float w = prod - ms;
+                        acc[chunk][j] = fmaf(w, x[b * 256 + group * 32 + l], acc[chunk][j]);
+                    }
+            }
+        }
+        float t[8];
+        for (unsigned j = 0; j < 8; ++j) t[j] = (acc[0][j] + acc[1][j]) + (acc[2][j] + acc[3][j]);
+        y[r] = hsum8(t);
+    }
+    return 1;
+}
+
 /* ---- batched kernels.  Main block of kernels/avx2.cpp:772-840 (Q8_0, two
  *      rows x four tokens) and of gemm_kblk_impl :1470-1545 (Q6_K, Kc=256):
  *      the row is dequantised to fp32, one 8-lane FMA chain runs over
@@ -435,6 +510,7 @@ ZO_API int zo_gemv(int fmt, const uint8_t* w, const float* x, float* y, size_t r
     if (fmt == ZO_Q8_0) return q8_int8_acts ? zo_gemv_q8_0_i8(w, x, y, rows, columns) : zo_gemv_q8_0_f32(w, x, y, rows, columns);
     if (fmt == ZO_Q6_K) return zo_gemv_q6k_f32(w, x, y, rows, columns);
     if (fmt == ZO_Q4_0) return zo_gemm_generic(fmt, w, x, y, 1, rows, columns);
+    if (fmt == ZO_Q4_K || fmt == ZO_Q5_K) return zo_gemv_q4k_q5k_f32(w, x, y, rows, columns, fmt == ZO_Q5_K);
     return 0;
 }
 

@@ -11,15 +11,20 @@ Block layouts (little endian):
   Q4_0  18 B / 32 el : f16 d | 16 B, low nibble = el j, high = el j+16
                                                                  w = (q - 8) * d
   Q6_K 210 B / 256 el: ql[128] | qh[64] | int8 sc[16] | f16 d    w = d * sc * (q - 32)
+  Q4_K 144 B / 256 el: f16 d | f16 dmin | 12 B of 6-bit (scale, min) x 8 | 128 B nibbles
+                                                                 w = (d * sc_j) * q - dmin * m_j, j = element / 32
+  Q5_K 176 B / 256 el: Q4_K with a 32-byte plane of fifth bits between the scales and the nibbles (src/quant.cpp:439-476)
+
+Q4_K and Q5_K are known here by size and decoder only (host side and CPU checker); the device library does not take them yet.
 """
 from __future__ import annotations
 
 import numpy as np
 
-Q8_0, Q4_0, Q6_K = 8, 2, 14  # GGML type ids
-BLOCK_ELEMENTS = {Q8_0: 32, Q4_0: 32, Q6_K: 256}
-BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q6_K: 210}
-NAMES = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q6_K: "Q6_K"}
+Q8_0, Q4_0, Q6_K, Q4_K, Q5_K = 8, 2, 14, 12, 13  # GGML type ids
+BLOCK_ELEMENTS = {Q8_0: 32, Q4_0: 32, Q6_K: 256, Q4_K: 256, Q5_K: 256}
+BLOCK_BYTES = {Q8_0: 34, Q4_0: 18, Q6_K: 210, Q4_K: 144, Q5_K: 176}
+NAMES = {Q8_0: "Q8_0", Q4_0: "Q4_0", Q6_K: "Q6_K", Q4_K: "Q4_K", Q5_K: "Q5_K"}
 
 
 def row_bytes(fmt: int, columns: int) -> int:
@@ -132,6 +137,27 @@ def quantize(fmt: int, w: np.ndarray) -> np.ndarray:
     return {Q8_0: quantize_q8_0, Q4_0: quantize_q4_0, Q6_K: quantize_q6_k}[fmt](w)
 
 
+def random_k_blocks(fmt: int, rows: int, columns: int, seed: int) -> np.ndarray:
+    """Valid Q4_K / Q5_K rows with random content (uint8 [rows, row_bytes]): every code, 6-bit scale and minimum is
+    uniform, d and dmin are small positive normal halves, so decoded weights are of the order of 0.02."""
+    if fmt not in (Q4_K, Q5_K) or columns % 256:
+        raise ValueError("Q4_K / Q5_K rows of whole super-blocks")
+    rng = np.random.default_rng(seed)
+    n = rows * (columns // 256)
+    b = rng.integers(0, 256, size=(n, BLOCK_BYTES[fmt]), dtype=np.uint8)
+    b[:, 0:2] = (rng.uniform(6.2e-5, 1.5e-4, size=n).astype(np.float16)).view(np.uint8).reshape(n, 2)
+    b[:, 2:4] = (rng.uniform(6.2e-5, 1.5e-4, size=n).astype(np.float16)).view(np.uint8).reshape(n, 2)
+    return np.ascontiguousarray(b.reshape(rows, -1))
+
+
+def _k_scales_mins(s: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """The eight 6-bit (scale, minimum) pairs of a super-block from its 12 packed bytes [n, 12] (src/quant.cpp:133-141)."""
+    s = s.astype(np.uint32)
+    sc = np.concatenate([s[:, 0:4] & 63, (s[:, 8:12] & 15) | ((s[:, 0:4] >> 6) << 4)], axis=1)
+    mn = np.concatenate([s[:, 4:8] & 63, (s[:, 8:12] >> 4) | ((s[:, 4:8] >> 6) << 4)], axis=1)
+    return sc.astype(np.float32), mn.astype(np.float32)
+
+
 def dequantize(fmt: int, packed: np.ndarray, rows: int, columns: int) -> np.ndarray:
     """Vectorised decoder with the reference's operation order; uint8 [rows, row_bytes] -> fp32 [rows, K]."""
     p = np.ascontiguousarray(packed, np.uint8).reshape(rows, -1)
@@ -157,4 +183,18 @@ def dequantize(fmt: int, packed: np.ndarray, rows: int, columns: int) -> np.ndar
         d = b[:, 208:210].copy().view(np.float16).astype(np.float32).reshape(n, 1, 1, 1)
         ds = (d * sc)[..., None]  # [n, half, group, 2, 1]
         return (ds * q.reshape(n, 2, 4, 2, 16).astype(np.float32)).reshape(rows, columns)
+    if fmt in (Q4_K, Q5_K):
+        n = rows * (columns // 256)
+        b = p.reshape(n, BLOCK_BYTES[fmt])
+        d = b[:, 0:2].copy().view(np.float16).astype(np.float32)            # [n, 1]
+        dmin = b[:, 2:4].copy().view(np.float16).astype(np.float32)
+        sc, mn = _k_scales_mins(b[:, 4:16])                                 # [n, 8]
+        ql = b[:, (48 if fmt == Q5_K else 16):].reshape(n, 4, 32)           # 32 bytes serve sub-blocks 2p (low nibbles) and 2p + 1 (high)
+        q = np.stack([ql & 15, ql >> 4], axis=2).reshape(n, 8, 32).astype(np.uint32)
+        if fmt == Q5_K:
+            qh = b[:, 16:48].astype(np.uint32)                              # bit j of byte l: the fifth bit of element l of sub-block j
+            q = q | (((qh[:, None, :] >> np.arange(8, dtype=np.uint32).reshape(1, 8, 1)) & 1) << 4)
+        ds = (d * sc)[..., None]
+        ms = (dmin * mn)[..., None]
+        return (ds * q.astype(np.float32) - ms).reshape(rows, columns)
     raise ValueError(fmt)

@@ -9,7 +9,8 @@ Backend.dev_upload streams the bytes from the page cache through the pinned boun
 intermediate copy of the model in host memory.
 
 Only what the decode path needs is understood: scalar and string metadata, arrays (skipped or kept as lists), and the
-tensor types F32, Q4_0, Q8_0 and Q6_K.
+tensor types F32, Q4_0, Q8_0 and Q6_K, plus Q4_K and Q5_K by size (their bytes can be read; the device library does not
+take them yet).
 """
 from __future__ import annotations
 
