@@ -38,7 +38,7 @@ extern "C" {
 #endif
 
 /* GGML tensor type ids of the three formats on the path (GGUF tensor directory). */
-enum { ZEN_CUDA_Q4_0 = 2, ZEN_CUDA_Q8_0 = 8, ZEN_CUDA_Q6_K = 14 };
+enum { ZEN_CUDA_Q4_0 = 2, ZEN_CUDA_Q8_0 = 8, ZEN_CUDA_Q6_K = 14, ZEN_CUDA_Q4_K = 12, ZEN_CUDA_Q5_K = 13 };
 
 /* How activations enter the integer dot products.
  *   ZEN_CUDA_ACT_INT8 : one int8 code per element, bit-identical to the reference's
@@ -125,6 +125,11 @@ int zen_cuda_gemm_q6_k(const uint8_t* weights, const float* input, float* output
 /* Q4_0 has no GPU entry point in the reference (its CPU generic route, src/quant.cpp:1135-1162,
  * is the only implementation); same contract as gemm_q6_k. */
 int zen_cuda_gemm_q4_0(const uint8_t* weights, const float* input, float* output, size_t tokens, size_t rows, size_t columns);
+/* zen::d3d12::gemm_kquant, include/zen/d3d12_backend.h:75-77 (hook sites src/quant.cpp:970-976 for one token, :1619 for a
+ * batch): raw Q4_K (q5 == 0) or Q5_K (q5 != 0) super-blocks, fp32 activations, columns a multiple of 256.  The device
+ * pointer calls take these formats too (zen_cuda_dev_upload / zen_cuda_dev_gemv with ZEN_CUDA_Q4_K / ZEN_CUDA_Q5_K;
+ * no fused input, accumulation or gather).  A first, untuned kernel. */
+int zen_cuda_gemm_kquant(const uint8_t* weights, const float* input, float* output, size_t tokens, size_t rows, size_t columns, int q5);
 
 /* zen::d3d12::release_q8_0_weights / release_kquant_weights, include/zen/d3d12_backend.h:80,88.
  * Call before unmapping or reusing a weight address; drops every resident shape at that address. */

@@ -1,0 +1,71 @@
+"""GPU parity for the Q4_K and Q5_K decode products, through the C-ABI (zen_cuda_gemm_kquant, the device-pointer calls).
+
+The reference computes both with fp32 activations (gemv_q4k_q5k_avx2, kernels/avx2.cpp:329-378); the checker is its C
+restatement, pinned bit for bit to the compiled reference (tests/test_kquant_q4k_q5k_cpu.py), and the vectors the
+unmodified reference produced.  Bar: 1e-3 under both gates of helpers.assert_parity; only the summation order differs, so
+results land near 1e-6."""
+import os
+
+import numpy as np
+import pytest
+
+from helpers import assert_parity, seeded_acts
+from zeninfer_b200 import blocks
+
+pytestmark = pytest.mark.gpu
+FORMATS = [(blocks.Q4_K, "Q4_K", "q4_k"), (blocks.Q5_K, "Q5_K", "q5_k")]
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "kquant_vectors.npz")
+
+
+@pytest.fixture(scope="module")
+def be():
+    from zeninfer_b200 import Backend
+    return Backend()
+
+
+@pytest.mark.parametrize("fmt,name,tag", FORMATS)
+def test_against_the_reference_vectors(be, fmt, name, tag):
+    with np.load(GOLDEN) as g:
+        w, x, y = np.ascontiguousarray(g[tag + "_w"]), g[tag + "_x"], g[tag + "_y"]
+    rel = assert_parity(be.gemv(name, w, x, w.shape[0], x.size), y, what=f"{name} gemv vs the reference's vector")
+    assert rel < 1e-4
+    be.release_weights(w)
+
+
+@pytest.mark.parametrize("fmt,name,tag", FORMATS)
+@pytest.mark.parametrize("rows,cols,tokens", [(1, 256, 1), (5, 512, 1), (67, 1280, 3), (130, 2048, 8), (1024, 4096, 1), (64, 14336, 2), (300, 768, 11)])
+def test_host_pointer_product_vs_oracle(be, zo, fmt, name, tag, rows, cols, tokens):
+    w = blocks.random_k_blocks(fmt, rows, cols, 500 + rows)
+    x = seeded_acts(tokens, cols, 510 + cols)
+    got = be.gemm(name, w, x, tokens, rows, cols)       # more than 8 tokens: several launches
+    ref = np.stack([zo.gemv(fmt, w, x[t], rows, cols) for t in range(tokens)])
+    rel = assert_parity(got, ref, what=f"{name} {tokens}x{rows}x{cols}")
+    assert rel < 1e-4
+    be.release_weights(w)
+
+
+@pytest.mark.parametrize("fmt,name,tag", FORMATS)
+def test_device_pointer_calls(be, zo, fmt, name, tag):
+    import torch
+    from zeninfer_b200 import BackendError
+    from zeninfer_b200.backend import ACT_FP32, ACT_INT8
+    rows, cols, tokens = [96, 40], 1024, 3
+    ws = [blocks.random_k_blocks(fmt, r, cols, 520 + r) for r in rows]
+    hs = [be.dev_upload(name, w, r, cols) for w, r in zip(ws, rows)]
+    part = be.dev_upload(name, ws[0], rows[0], cols, 32, 48)            # rows 32..79 of the first tensor
+    x = seeded_acts(tokens, cols, 530)
+    d_x = torch.from_numpy(x).cuda()
+    outs = [torch.zeros((tokens, r), dtype=torch.float32, device="cuda") for r in rows + [48]]
+    stream = torch.cuda.Stream()
+    be.dev_gemv(hs, [o.data_ptr() for o in outs[:2]], d_x.data_ptr(), tokens, ACT_FP32, stream.cuda_stream)
+    be.dev_gemv([part], [outs[2].data_ptr()], d_x.data_ptr(), tokens, ACT_FP32, stream.cuda_stream)
+    stream.synchronize()
+    be.dev_check(stream.cuda_stream)
+    for w, r, o in zip(ws, rows, outs):
+        ref = np.stack([zo.gemv(fmt, w, x[t], r, cols) for t in range(tokens)])
+        assert_parity(o.cpu().numpy(), ref, what=f"{name} device-pointer product rows={r}")
+    assert torch.equal(outs[2], outs[0][:, 32:80])
+    with pytest.raises(BackendError):
+        be.dev_gemv(hs[:1], [outs[0].data_ptr()], d_x.data_ptr(), tokens, ACT_INT8, stream.cuda_stream)   # fp32-equivalent activations only
+    for h in hs + [part]:
+        be.dev_free(h)

@@ -24,14 +24,14 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_PKG, "lib", "libzen_cuda.so")
 
 ACT_INT8, ACT_FP32 = 1, 2
-FORMAT_IDS = {"Q8_0": blocks.Q8_0, "Q4_0": blocks.Q4_0, "Q6_K": blocks.Q6_K}
+FORMAT_IDS = {"Q8_0": blocks.Q8_0, "Q4_0": blocks.Q4_0, "Q6_K": blocks.Q6_K, "Q4_K": blocks.Q4_K, "Q5_K": blocks.Q5_K}
 
 # every symbol include/zen_cuda.h declares; the CPU test-suite checks the library exports them all
 ABI_SYMBOLS = (
     "zen_cuda_enabled", "zen_cuda_init", "zen_cuda_shutdown", "zen_cuda_info", "zen_cuda_get_stats",
     "zen_cuda_last_error", "zen_cuda_set_q8_act_mode", "zen_cuda_get_q8_act_mode",
     "zen_cuda_gemv_q8_0", "zen_cuda_gemm_q8_0", "zen_cuda_gemv_q8_0_batch", "zen_cuda_gemm_q8_0_batch",
-    "zen_cuda_gemm_q6_k", "zen_cuda_gemm_q4_0", "zen_cuda_release_weights", "zen_cuda_quantize_acts",
+    "zen_cuda_gemm_q6_k", "zen_cuda_gemm_q4_0", "zen_cuda_gemm_kquant", "zen_cuda_release_weights", "zen_cuda_quantize_acts",
     "zen_cuda_dev_upload", "zen_cuda_dev_free", "zen_cuda_dev_weight_bytes", "zen_cuda_dev_gemv",
     "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_gemm_workspace_bytes", "zen_cuda_dev_gemm_q8_0",
     "zen_cuda_dev_gemm_q8_0_noalloc",
@@ -99,6 +99,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_gemm_q8_0_batch.argtypes = [vp, C.POINTER(GemmTask), sz, sz, sz]
     lib.zen_cuda_gemm_q6_k.argtypes = [vp, vp, vp, sz, sz, sz]
     lib.zen_cuda_gemm_q4_0.argtypes = [vp, vp, vp, sz, sz, sz]
+    lib.zen_cuda_gemm_kquant.argtypes = [vp, vp, vp, sz, sz, sz, C.c_int]
     lib.zen_cuda_release_weights.argtypes = [vp]
     lib.zen_cuda_release_weights.restype = None
     lib.zen_cuda_quantize_acts.argtypes = [vp, vp, vp, sz, sz]
@@ -211,6 +212,8 @@ class Backend:
             ok = self.lib.zen_cuda_gemm_q6_k(_addr(w), _addr(x), _addr(out), tokens, rows, columns)
         elif fmt == "Q4_0":
             ok = self.lib.zen_cuda_gemm_q4_0(_addr(w), _addr(x), _addr(out), tokens, rows, columns)
+        elif fmt in ("Q4_K", "Q5_K"):
+            ok = self.lib.zen_cuda_gemm_kquant(_addr(w), _addr(x), _addr(out), tokens, rows, columns, int(fmt == "Q5_K"))
         else:
             raise BackendError(f"format {fmt} is not on this path")
         if not ok:

@@ -27,6 +27,7 @@
 
 #include "decode_ops.cuh"
 #include "gemm_q8_0_i8.cuh"
+#include "gemv_k45.cuh"
 #include "gemv_kq.cuh"
 #include "gemv_q8_0.cuh"
 #include "greedy_pick.cuh"
@@ -185,8 +186,11 @@ void free_weights(State& s, zen_cuda_weights* w) {
     delete w;
 }
 
-uint32_t block_elems(int fmt) { return fmt == ZEN_CUDA_Q6_K ? 256u : 32u; }
-uint32_t block_bytes(int fmt) { return fmt == ZEN_CUDA_Q8_0 ? 34u : fmt == ZEN_CUDA_Q4_0 ? 18u : fmt == ZEN_CUDA_Q6_K ? 210u : 0u; }
+bool raw_layout(int fmt) { return fmt == ZEN_CUDA_Q4_K || fmt == ZEN_CUDA_Q5_K; }   // kept as GGUF super-blocks on the device
+uint32_t block_elems(int fmt) { return (fmt == ZEN_CUDA_Q6_K || raw_layout(fmt)) ? 256u : 32u; }
+uint32_t block_bytes(int fmt) {
+    return fmt == ZEN_CUDA_Q8_0 ? 34u : fmt == ZEN_CUDA_Q4_0 ? 18u : fmt == ZEN_CUDA_Q6_K ? 210u : fmt == ZEN_CUDA_Q4_K ? 144u : fmt == ZEN_CUDA_Q5_K ? 176u : 0u;
+}
 
 // Streams [src, src+bytes) to `dst` on the copy stream through the two pinned bounce buffers:
 // the CPU fills one while the DMA engine drains the other.
@@ -223,10 +227,13 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
     w->raw_bytes = nrows * row_raw;
     uint8_t* d_raw = nullptr;
     auto t0 = clock_type::now();
-    bool ok = cudaMalloc(reinterpret_cast<void**>(&d_raw), w->raw_bytes + 16) == cudaSuccess;
+    const bool raw = raw_layout(fmt);
+    bool ok = raw || cudaMalloc(reinterpret_cast<void**>(&d_raw), w->raw_bytes + 16) == cudaSuccess;
     size_t plane_bytes[4] = {0, 0, 0, 0};
     // every plane gets slack for bulk copies whose size was rounded up to 16 bytes
-    if (fmt == ZEN_CUDA_Q8_0) {
+    if (raw) {
+        plane_bytes[0] = w->raw_bytes + 64;                                // the super-blocks as they are in the file
+    } else if (fmt == ZEN_CUDA_Q8_0) {
         plane_bytes[0] = nrows * cols + 64;                                // int8 codes
         plane_bytes[1] = nrows * static_cast<size_t>(w->nbp) * 2 + 64;     // f16 scales
     } else if (fmt == ZEN_CUDA_Q4_0) {
@@ -252,9 +259,12 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
         return nullptr;
     }
     t0 = clock_type::now();
-    ok = stream_to_device(s, d_raw, host + first_row * row_raw, w->raw_bytes);
+    ok = stream_to_device(s, raw ? w->plane[0] : d_raw, host + first_row * row_raw, w->raw_bytes);
     s.stats.transfer_us += us_since(t0);
-    if (ok) {
+    if (ok && raw) {
+        ok = cudaStreamSynchronize(s.copy_stream) == cudaSuccess;
+        if (!ok) set_error(s, "upload: copy failed");
+    } else if (ok) {
         t0 = clock_type::now();
         const size_t nblocks = nrows * w->nb;
         const unsigned grid = static_cast<unsigned>((nblocks + 255) / 256);
@@ -273,7 +283,7 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
         s.stats.repack_us += us_since(t0);
         if (!ok) set_error(s, "upload: repack failed");
     }
-    cudaFree(d_raw);
+    if (d_raw) cudaFree(d_raw);
     if (!ok) {
         for (void* p : w->plane) if (p) cudaFree(p);
         delete w;
@@ -386,6 +396,7 @@ cudaError_t dispatch_kq(int batch, const zk::KqParams& p, unsigned grid, size_t 
 }
 
 size_t gemv_smem_bytes(int format, size_t cols, size_t tokens, int act_mode) {
+    if (raw_layout(format)) return 0;   // the Q4_K / Q5_K kernel stages nothing
     if (format == ZEN_CUDA_Q8_0) {
         const uint32_t nb = static_cast<uint32_t>(cols / 32), nseg = (nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks;
         return zk::gemv_q8_0_smem_bytes(nseg, static_cast<int>(tokens), act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1);
@@ -442,6 +453,23 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
 
 // Enqueues one batched GEMV launch: `count` tensors (same format, same K) times `tokens` (<= 8)
 // activation rows.  Device pointers throughout.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(State& s, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args);   // defined below
+
+// Q4_K / Q5_K: one launch per tensor, a warp per row, straight from the raw super-blocks.
+bool enqueue_gemv_k45(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x, size_t tokens, cudaStream_t st) {
+    for (size_t i = 0; i < count; ++i) {
+        const unsigned grid = static_cast<unsigned>((w[i]->rows + zk::kK45Warps - 1) / zk::kK45Warps);
+        const cudaError_t e = w[i]->format == ZEN_CUDA_Q5_K
+            ? launch_pdl(s, zk::gemv_k45_kernel<true>, dim3(grid), dim3(zk::kK45Warps * 32), 0, st, static_cast<const uint8_t*>(w[i]->plane[0]), d_x, d_y[i],
+                         static_cast<uint32_t>(w[i]->rows), w[i]->nb, static_cast<uint32_t>(tokens))
+            : launch_pdl(s, zk::gemv_k45_kernel<false>, dim3(grid), dim3(zk::kK45Warps * 32), 0, st, static_cast<const uint8_t*>(w[i]->plane[0]), d_x, d_y[i],
+                         static_cast<uint32_t>(w[i]->rows), w[i]->nb, static_cast<uint32_t>(tokens));
+        if (e != cudaSuccess) return set_error(s, std::string("gemv launch: ") + cudaGetErrorString(e));
+        ++s.stats.dispatches;
+    }
+    return true;
+}
 bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
                   size_t tokens, int act_mode, cudaStream_t st, const zk::PeerGather* gather = nullptr, const float* d_gate = nullptr,
                   const float* d_norm_weight = nullptr, float norm_eps = 0.0f, bool accumulate = false, const zen_cuda_weights* warm_next = nullptr) {
@@ -468,6 +496,10 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
     if (w[0]->format != ZEN_CUDA_Q8_0) {
         if (act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: Q4_0 and Q6_K take fp32-equivalent activations only");
         if (d_gate || d_norm_weight || accumulate) return set_error(s, "gemv: fused inputs and accumulation are Q8_0 paths");
+        if (raw_layout(w[0]->format)) {
+            if (gather || !d_x || (reinterpret_cast<uintptr_t>(d_x) % 16)) return set_error(s, "gemv: Q4_K / Q5_K take a 16-byte aligned input and no gather");
+            return enqueue_gemv_k45(s, w, d_y, count, d_x, tokens, st);
+        }
         return enqueue_gemv_kq(s, w, d_y, count, d_x, tokens, st, gather);   // a warm_next hint is not used by these kernels (measured: no gain)
     }
     if (d_gate && d_norm_weight) return set_error(s, "gemv: a fused input is either SwiGLU or RMSNorm");
@@ -985,6 +1017,13 @@ int zen_cuda_gemm_q4_0(const uint8_t* weights, const float* input, float* output
     std::lock_guard<std::mutex> lock(s.mutex);
     if (!init_locked(s)) return 0;
     return host_product(s, ZEN_CUDA_Q4_0, input, &weights, &output, &rows, 1, tokens, columns, ZEN_CUDA_ACT_FP32) ? 1 : 0;
+}
+
+int zen_cuda_gemm_kquant(const uint8_t* weights, const float* input, float* output, size_t tokens, size_t rows, size_t columns, int q5) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    return host_product(s, q5 ? ZEN_CUDA_Q5_K : ZEN_CUDA_Q4_K, input, &weights, &output, &rows, 1, tokens, columns, ZEN_CUDA_ACT_FP32) ? 1 : 0;
 }
 
 void zen_cuda_release_weights(const uint8_t* weights) {
