@@ -143,3 +143,25 @@ def test_peer_gather_setup_exchanges_handles_over_gloo(tmp_path):
         assert ("create", world, r, 4096, expect_regions) in calls
         assert calls[-1] == ("free", own) and calls.count(("destroy", 77)) == 1
         assert sorted(c[1] for c in calls if c[0] == "close") == sorted(p for q, p in enumerate(expect_regions) if q != r)
+
+
+def test_column_shard_partial_products_add_up():
+    """The column cut of the sharded decoder's o and down projections: every rank's blocks times its slice of the input,
+    summed over the ranks, is the whole product (same decoded weights, same codes and scales)."""
+    rows, cols = 24, 1024
+    for fmt in (blocks.Q8_0, blocks.Q4_0, blocks.Q6_K):
+        w = np.random.default_rng(9).standard_normal((rows, cols), dtype=np.float32) * np.float32(0.02)
+        packed = blocks.quantize(fmt, w)
+        x = np.random.default_rng(10).standard_normal(cols, dtype=np.float32)
+        whole = blocks.dequantize(fmt, packed, rows, cols).astype(np.float64) @ x.astype(np.float64)
+        for world in (1, 2, 4):
+            total = np.zeros(rows)
+            for rank in range(world):
+                part, kept = shard.column_shard(packed, fmt, rows, cols, world, rank)
+                assert kept == cols // world and part.shape == (rows, blocks.row_bytes(fmt, kept)) and part.flags["C_CONTIGUOUS"]
+                dec = blocks.dequantize(fmt, part, rows, kept)
+                assert np.array_equal(dec, blocks.dequantize(fmt, packed, rows, cols)[:, rank * kept:(rank + 1) * kept])
+                total += dec.astype(np.float64) @ x[rank * kept:(rank + 1) * kept].astype(np.float64)
+            assert np.allclose(total, whole, rtol=0, atol=1e-9 * np.abs(whole).max())
+    with pytest.raises(ValueError):
+        shard.column_shard(blocks.quantize(blocks.Q6_K, np.zeros((2, 768), np.float32)), blocks.Q6_K, 2, 768, 2, 0)   # three super-blocks over two ranks

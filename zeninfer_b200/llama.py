@@ -150,10 +150,10 @@ class LlamaDecoder:
             if is_matrix:
                 rows, cols = shapes[name]
                 if self.col_cut and name.endswith(("attn_output.weight", "ffn_down.weight")):
-                    # this rank's columns: whole 34-byte blocks [b0, b1) of every row, copied out of the source
-                    nb = cols // 32 // self.world
-                    part = np.ascontiguousarray(np.asarray(arr).reshape(rows, cols // 32, 34)[:, self.rank * nb:(self.rank + 1) * nb]).reshape(rows, nb * 34)
-                    self.h[name] = backend.dev_upload("Q8_0", part, rows, nb * 32)
+                    # this rank's columns: whole 34-byte blocks of every row, copied out of the source
+                    from . import shard
+                    part, kept = shard.column_shard(arr, blocks.Q8_0, rows, cols, self.world, self.rank)
+                    self.h[name] = backend.dev_upload("Q8_0", part, rows, kept)
                 elif self.world > 1 and name != "token_embd.weight":   # this rank's rows only; every rank fetches embeddings itself
                     per = rows // self.world
                     self.h[name] = backend.dev_upload("Q8_0", arr, rows, cols, self.rank * per, per)

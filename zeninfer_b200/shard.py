@@ -10,8 +10,11 @@ win (sample_logits, src/adapters/dense_transformer_runtime.cpp:407-415).
 """
 from __future__ import annotations
 
+import numpy as np
 import torch
 import torch.distributed as dist
+
+from . import blocks
 
 ROW_ALIGN = 8  # rows per group in the decode kernels
 
@@ -59,6 +62,19 @@ def all_gather_rows(local: torch.Tensor, rows: int, world: int, rank: int, group
     for r, (a, b) in enumerate(plan):
         full[:, a:b] = gathered[r, :, : b - a]
     return full
+
+
+def column_shard(packed: np.ndarray, fmt: int, rows: int, columns: int, world: int, rank: int) -> tuple[np.ndarray, int]:
+    """The column cut that goes with an all-reduce: rank r keeps blocks [r * nb / world, (r + 1) * nb / world) of every
+    row (whole quantisation blocks, so the codes and scales are untouched) as a contiguous [rows, bytes] copy, and
+    multiplies them with the matching slice of the input.  Returns (rows of raw blocks, columns kept)."""
+    be, bb = blocks.BLOCK_ELEMENTS[fmt], blocks.BLOCK_BYTES[fmt]
+    nb = columns // be
+    if columns % be or nb % world:
+        raise ValueError(f"{columns} columns do not split into {world} runs of whole blocks")
+    per = nb // world
+    raw = np.asarray(packed).reshape(rows, nb, bb)[:, rank * per:(rank + 1) * per]
+    return np.ascontiguousarray(raw).reshape(rows, per * bb), per * be
 
 
 def greedy_pick(logits: torch.Tensor) -> torch.Tensor:
