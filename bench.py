@@ -19,8 +19,13 @@ copies with one launch per copy, replayed from a CUDA graph.
              the same workload, bounded sample, on this box's host cores.
 
 With --gpus N (under torchrun) every rank owns one 4096-row shard of a (4096*N) x 4096 matrix per copy
-(weak scaling); each launch is followed by the path's one exchange step, an NCCL all-gather of the
-output shards.
+(weak scaling); the path's one exchange step, the all-gather of the output shards, is fused into the
+product kernel as peer stores (--gather nccl: an NCCL all-gather after each launch instead).
+
+Other workloads (--workload): q8_0_gemm (config 1, the tcgen05 prefill product), layer_sweep (config 2, the
+seven projections of a layer in Q8_0 / Q4_0 / Q6_K), lm_head (config 3, Q6_K 128256 x 4096, --gpus N shards the
+rows), decode (config 4, greedy decode of the Llama-3-8B shape; --gpus N runs the sharded decoder, --cut chooses
+its cut).
 """
 from __future__ import annotations
 
