@@ -506,6 +506,28 @@ ZO_API int zo_gemm_q6k_f32(const uint8_t* weights, const float* input, float* ou
  *      takes for each of the three formats.  q8_int8_acts selects the
  *      ZEN_CPU_Q8_ACT=1 arithmetic for Q8_0. ------------------------------ */
 
+/* Q4_K / Q5_K batched: gemm_q4k_kblk_avx2 / gemm_q5k_kblk_avx2 (kernels/avx2.cpp:1605-1628) are gemm_kblk_impl
+ * (:1470-1545) over panel dequantisers whose values equal zo_dequantize's (multiply, then subtract: :1352-1366,
+ * :1410-1432); the panel width does not enter the arithmetic (the lane accumulators live across panels).  So, as for
+ * Q6_K: the decoded row, one 8-lane FMA chain over the columns for rows in whole groups of four, dot_f32 for the
+ * remaining rows. */
+ZO_API int zo_gemm_q4k_q5k_f32(int fmt, const uint8_t* weights, const float* input, float* output,
+                               size_t tokens, size_t rows, size_t columns) {
+    if ((fmt != ZO_Q4_K && fmt != ZO_Q5_K) || !weights || !input || !output || !tokens || !rows || !columns || columns % 256) return 0;
+    const size_t rb = zo_row_bytes(fmt, columns), rows_main = (rows / 4) * 4;
+    float* w = (float*)malloc(columns * sizeof(float));
+    if (!w) return 0;
+    for (size_t r = 0; r < rows; ++r) {
+        zo_dequantize(fmt, weights + r * rb, columns, w);
+        for (size_t t = 0; t < tokens; ++t) {
+            const float* x = input + t * columns;
+            output[t * rows + r] = r < rows_main ? dot_lane_chain(w, x, columns) : dot_f32(w, x, columns);
+        }
+    }
+    free(w);
+    return 1;
+}
+
 ZO_API int zo_gemv(int fmt, const uint8_t* w, const float* x, float* y, size_t rows, size_t columns, int q8_int8_acts) {
     if (fmt == ZO_Q8_0) return q8_int8_acts ? zo_gemv_q8_0_i8(w, x, y, rows, columns) : zo_gemv_q8_0_f32(w, x, y, rows, columns);
     if (fmt == ZO_Q6_K) return zo_gemv_q6k_f32(w, x, y, rows, columns);
@@ -526,6 +548,7 @@ ZO_API int zo_gemm(int fmt, const uint8_t* w, const float* in, float* out, size_
     }
     if (fmt == ZO_Q6_K) return zo_gemm_q6k_f32(w, in, out, tokens, rows, columns);
     if (fmt == ZO_Q4_0) return zo_gemm_generic(fmt, w, in, out, tokens, rows, columns);
+    if (fmt == ZO_Q4_K || fmt == ZO_Q5_K) return zo_gemm_q4k_q5k_f32(fmt, w, in, out, tokens, rows, columns);
     return 0;
 }
 
