@@ -129,6 +129,26 @@ def make_inputs():
     return packed, x
 
 
+def cpu_description() -> dict:
+    """Model name and core counts of the host the CPU baseline runs on (every CPU figure is quoted with them)."""
+    model = "unknown"
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.lower().startswith("model name"):
+                    model = line.split(":", 1)[1].strip()
+                    break
+    except OSError:
+        pass
+    physical = None
+    try:
+        import psutil
+        physical = psutil.cpu_count(logical=False)
+    except Exception:
+        pass
+    return {"cpu_model": model, "logical_cpus": os.cpu_count(), "physical_cores": physical}
+
+
 class CpuReference:
     """The reference's own CPU path (zen::quant::gemv through oracle/_ref) on the workload; the plain-C
     restatement stands in only where the compiled reference did not travel with the tree."""
@@ -143,10 +163,12 @@ class CpuReference:
             zr = oracle.Reference()
             self.cores = min(zr.pool_workers(), os.cpu_count() or 1)
             self.run = lambda w: zr.gemv(oracle.Q8_0, w, x, ROWS, COLS, workers=0)  # workers=0: the reference's own policy
+            self.run_with = lambda w, n: zr.gemv(oracle.Q8_0, w, x, ROWS, COLS, workers=n)
         else:
             zo = oracle.Oracle()
             self.cores = 1
             self.run = lambda w: zo.gemv(oracle.Q8_0, w, x, ROWS, COLS, int8_acts=True)
+            self.run_with = None
         self.run(self.ws[0])
 
     def sample(self, budget_s: float) -> dict:
@@ -159,11 +181,31 @@ class CpuReference:
                 break
         dt = time.perf_counter() - t0
         return {"value": ALGO_BYTES_PER_LAUNCH * n / dt / 1e9, "unit": "GB/s", "cores": self.cores, "kind": self.kind,
-                "sample": f"{n} GEMV calls over {self.copies} weight copies in {dt:.2f} s, int8 activations (ZEN_CPU_Q8_ACT=1), reference worker policy"}
+                "sample": f"{n} GEMV calls over {self.copies} weight copies in {dt:.2f} s, int8 activations (ZEN_CPU_Q8_ACT=1), reference worker policy",
+                "workers": "0 (the reference's planner default; its pool is capped at 32 threads)", **cpu_description()}
+
+    def worker_sweep(self, budget_each_s: float) -> dict:
+        """GB/s with an explicit worker count: 1, the physical cores, min(32, logical CPUs)."""
+        if self.run_with is None:
+            return {}
+        desc = cpu_description()
+        counts = sorted({1, desc["physical_cores"] or 1, min(32, desc["logical_cpus"] or 1)})
+        out = {}
+        for workers in counts:
+            self.run_with(self.ws[0], workers)
+            t0, n = time.perf_counter(), 0
+            while n == 0 or time.perf_counter() - t0 < budget_each_s:
+                self.run_with(self.ws[n % self.copies], workers)
+                n += 1
+            out[str(workers)] = ALGO_BYTES_PER_LAUNCH * n / (time.perf_counter() - t0) / 1e9
+        return out
 
 
 def cpu_reference_leg(packed: np.ndarray, x: np.ndarray, budget_s: float, copies: int) -> dict:
-    return CpuReference(packed, x, copies).sample(budget_s)
+    ref = CpuReference(packed, x, copies)
+    leg = ref.sample(budget_s)
+    leg["gbs_by_workers"] = ref.worker_sweep(min(2.0, budget_s / 6))
+    return leg
 
 
 def run_reference_arm(args) -> None:
