@@ -332,7 +332,7 @@ def run_gemm_workload(args) -> None:
             run(); n += 1
         dt = time.perf_counter() - t0
         frac = 1.0 if kind == "reference" else 256 / GEMM_ROWS
-        cpu = {"value": GEMM_OPS * frac * n / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": kind,
+        cpu = {**cpu_description(), "value": GEMM_OPS * frac * n / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": kind,
                "sample": f"{n} full products in {dt:.1f} s, the reference's default fp32-activation K-blocked kernel (it has no int8 GEMM), its own worker policy"}
 
     print(json.dumps({
@@ -493,7 +493,7 @@ def run_layer_sweep(args) -> None:
                 run(name)
             n += 1
         dt = time.perf_counter() - t0
-        cpu = {"value": q8["layer"]["algorithmic_bytes"] * n / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+        cpu = {**cpu_description(), "value": q8["layer"]["algorithmic_bytes"] * n / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
                "sample": f"{n} passes over the seven Q8_0 projections of the layer in {dt:.1f} s, one call per projection, int8 activations"}
 
     dom = q8["gate_up"]
@@ -674,7 +674,7 @@ def run_lm_head(args) -> None:
         while n == 0 or time.perf_counter() - t0 < args.cpu_budget:
             run(); n += 1
         dt = time.perf_counter() - t0
-        cpu = {"value": results[1]["algorithmic_bytes"] * n / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
+        cpu = {**cpu_description(), "value": results[1]["algorithmic_bytes"] * n / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind,
                "sample": f"{n} full lm_head products (batch 1) in {dt:.1f} s, the reference's Q6_K kernel, its own worker policy"}
     r1 = results[1]
     per_gpu = r1["gbs"] / world
@@ -845,7 +845,7 @@ def run_decode(args) -> None:
                 one_layer(); n += 1
             dt = time.perf_counter() - t0
             per_token = dt / n * (cfg.layers + tensor_bytes("Q8_0", cfg.vocab, cfg.embedding) / layer_bytes)
-            cpu = {"value": 1.0 / per_token, "unit": "tokens/s", "cores": min(zr.pool_workers(), os.cpu_count() or 1), "kind": "reference",
+            cpu = {**cpu_description(), "value": 1.0 / per_token, "unit": "tokens/s", "cores": min(zr.pool_workers(), os.cpu_count() or 1), "kind": "reference",
                    "sample": f"{n} passes over the seven Q8_0 projections of one layer in {dt:.1f} s (reference kernels, int8 activations, its own "
                              f"worker policy), scaled to 32 layers + lm_head by bytes; attention, norms and sampling not included, so an upper bound "
                              f"for the reference's decode rate on these cores"}
