@@ -1067,6 +1067,7 @@ def main() -> None:
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "rows_per_gpu": ROWS, "columns": COLS, "batch": 1, "activations": "int8 (bit-exact reference codes)",
+                   "generator": "numpy.random.default_rng(seed).standard_normal(float32): W seed 0 x 0.02 packed to Q8_0, x seed 1",
                    "l2": f"inputs larger than L2: {COPIES} weight copies, {COPIES * ALGO_BYTES_PER_LAUNCH / 1e6:.0f} MB per pass",
                    "launch": "CUDA graph replay, one kernel per copy" + (
                        "; each launch hints the next launch's tensor to L2 (zen_cuda_gemv_fusion.warm_next)" if world == 1 else "; output shards all-gathered by the product kernel itself (peer stores over NVLink, device-side epoch flags)"
