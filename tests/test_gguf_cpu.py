@@ -62,3 +62,45 @@ def test_wrong_architecture_or_type_is_refused(model_path, tmp_path):
         f.write(data)
     with gguf.GgufFile(p) as g, pytest.raises(gguf.GgufError):
         gguf.llama_config(g)
+
+
+def test_k_quant_tensors_are_sized_and_readable(tmp_path):
+    """Q4_K (type 12) and Q5_K (type 13) tensors: the directory sizes them by their super-blocks and hands out their raw
+    bytes; an unknown type is listed but not readable; a Q4_K tensor whose columns are not whole super-blocks is refused."""
+    from zeninfer_b200 import blocks
+
+    def s(text: str) -> bytes:
+        b = text.encode()
+        return struct.pack("<Q", len(b)) + b
+
+    def build(entries) -> bytes:
+        out = bytearray(b"GGUF" + struct.pack("<IQQ", 3, len(entries), 0))
+        off, datas = 0, []
+        for name, dims, ggml_type, data in entries:
+            off = (off + 31) & ~31
+            out += s(name) + struct.pack("<I", len(dims)) + struct.pack("<" + "Q" * len(dims), *dims) + struct.pack("<IQ", ggml_type, off)
+            datas.append((off, data))
+            off += len(data)
+        out += bytes((-len(out)) % 32)
+        start = len(out)
+        for o, data in datas:
+            out += bytes(start + o - len(out)) + data
+        return bytes(out)
+
+    w4 = blocks.random_k_blocks(blocks.Q4_K, 4, 512, 1)
+    w5 = blocks.random_k_blocks(blocks.Q5_K, 3, 256, 2)
+    p = str(tmp_path / "k.gguf")
+    with open(p, "wb") as f:
+        f.write(build([("a.weight", [512, 4], 12, w4.tobytes()), ("b.weight", [256, 3], 13, w5.tobytes()), ("c.weight", [32, 2], 99, bytes(64))]))
+    with gguf.GgufFile(p) as g:
+        assert g.tensors["a.weight"].shape == (4, 512) and g.tensors["a.weight"].nbytes == 4 * 2 * 144
+        assert g.tensors["b.weight"].nbytes == 3 * 176
+        assert np.array_equal(g.array("a.weight"), w4) and np.array_equal(g.array("b.weight"), w5)
+        assert np.array_equal(blocks.dequantize(blocks.Q5_K, np.array(g.array("b.weight")), 3, 256), blocks.dequantize(blocks.Q5_K, w5, 3, 256))
+        with pytest.raises(gguf.GgufError):
+            g.array("c.weight")
+    bad = str(tmp_path / "bad.gguf")
+    with open(bad, "wb") as f:
+        f.write(build([("a.weight", [128, 4], 12, bytes(4 * 72))]))
+    with pytest.raises(gguf.GgufError):
+        gguf.GgufFile(bad)
