@@ -205,9 +205,13 @@ int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out
  * (ZEN_CUDA_NOALLOC_SCRATCH_BYTES of HBM on every GPU that loads the library, held until the process exits).  It calls
  * no cudaMalloc / cudaFree and no allocating library routine, and it does not initialise the backend: the tensor must
  * already be resident (zen_cuda_dev_upload), which is also what makes the backend ready.
- *   - tokens * columns must not exceed ZEN_CUDA_NOALLOC_MAX_ACT_ELEMENTS; larger requests return 0 with a message.
- *   - The first call on a device looks the scratch array's device address up (once per device); make that first call
- *     before any stream capture begins.
+ *   - tokens * columns must not exceed ZEN_CUDA_NOALLOC_MAX_ACT_ELEMENTS, and the quantised activations with their
+ *     scale rows (zen_cuda_gemm_workspace_bytes) must fit ZEN_CUDA_NOALLOC_SCRATCH_BYTES; larger requests return 0
+ *     with a message.
+ *   - What CUDA itself allocates lazily on first use -- the array when its address is first looked up, the code of the
+ *     kernels, the GEMM's shared-memory opt-in -- is done when the backend starts (zen_cuda_init or the first upload,
+ *     where allocating is allowed), once per device and with that device current, so this call finds all of it in
+ *     place.  Start the backend before any stream capture begins.
  *   - Every call uses the same array and finds the previous call's bytes in it (the part a call reads is rewritten,
  *     and its scale area is cleared, first).  Two calls whose GPU work overlaps (different streams, or different
  *     threads without ordering) race on it: order them on one stream or with events.
@@ -332,9 +336,25 @@ int zen_cuda_dev_silu_mul(const float* d_gate, const float* d_up, float* d_out, 
 /* *d_pos += delta, in stream order (a step's last launch). */
 int zen_cuda_dev_advance_position(int* d_pos, int delta, void* stream);
 
-/* Reads and clears the device-side error word the kernels set when a bounded wait gives up
- * (0 = none).  Synchronises `stream`. */
+/* The device-side error channel.  Synchronises `stream` (NULL: the backend's own), then reads and clears the error word
+ * the kernels set.  Returns
+ *    0      nothing to report;
+ *    1..4   a bounded wait inside a product kernel gave up (weight stage full / empty, drain at exit, tensor memory);
+ *    5      a peer GPU did not publish its outputs within the wait budget;
+ *    6, 7   a token id outside the embedding table / a position outside the KV cache (the kernel wrote zeros);
+ *    8      a non-finite value met in attention;
+ *    9      a work-list item's input was not produced within the wait budget;
+ *    < 0    the synchronise itself or an earlier launch failed in the CUDA runtime (-(cudaError_t) - 1), or the backend
+ *           is not initialised (-1): zen_cuda_last_error() has the text.
+ * The kernels never spin for ever: every device-side wait is bounded by the wait budget below, after which the kernel
+ * sets the word and returns, and the context stays usable.  (The reference reports GPU failures as a `false` return of
+ * the submitting call, src/backends/hip/hip_backend.hip:947-950; stream-ordered calls have no such moment.) */
 int zen_cuda_dev_check(void* stream);
+const char* zen_cuda_error_name(int code); /* a static string for a zen_cuda_dev_check code */
+/* The wait budget of every bounded device-side wait, in milliseconds of the top SM clock (default about one second;
+ * 0 restores the default; ZEN_CUDA_WAIT_MS sets it at start-up).  Drains the backend's own stream first; kernels
+ * already enqueued on other streams may see either value.  No counterpart in the reference. */
+int zen_cuda_set_wait_budget_ms(unsigned milliseconds);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

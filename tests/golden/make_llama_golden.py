@@ -8,6 +8,10 @@ generated Llama-layout GGUF model (Q8_0 matrices, fp32 norms).
 The model is zeninfer_b200.llama.synthetic_tensors(TINY, seed) written as a GGUF v3 file; the reference loads it
 with load_model_runtime and generates greedily (ModelRuntime::generate, include/zen/model_runtime.h:26-28).  The GPU
 test rebuilds the same tensors from the same seed and must reproduce the ids exactly and the logits within 1e-3.
+A second generation comes from a child process with ZEN_CPU_Q8_ACT=1 (the reference latches that switch on its first
+Q8_0 call, so it needs a process of its own): there the reference quantises the activations of every single-token
+product to int8 (src/quant.cpp:1088-1123) while the prompt block still goes through its fp32-activation GEMM
+(src/quant.cpp:1667-1680, tokens >= 2).  Stored as ids_int8 / last_logits_int8.
 Needs the reference tree; the committed .npz is what travels.
 """
 from __future__ import annotations
@@ -16,6 +20,7 @@ import ctypes as C
 import json
 import os
 import struct
+import subprocess
 import sys
 import tempfile
 
@@ -101,15 +106,31 @@ def reference_generate(gguf_path: str, prompt: np.ndarray, max_new: int, vocab: 
     return ids[:n], logits
 
 
+def child(gguf_path: str, out_path: str) -> None:
+    """Runs in a process whose environment already carries ZEN_CPU_Q8_ACT=1."""
+    prompt = np.random.default_rng([SEED, 1]).integers(3, TINY.vocab, size=PROMPT_LEN, dtype=np.int64)
+    ids, logits = reference_generate(gguf_path, prompt, MAX_NEW, TINY.vocab)
+    np.savez(out_path, ids=ids.astype(np.int64), last_logits=logits)
+
+
 def main() -> None:
     os.environ["ZEN_BACKEND"] = "cpu"
+    if len(sys.argv) == 4 and sys.argv[1] == "--child":
+        child(sys.argv[2], sys.argv[3])
+        return
     prompt = np.random.default_rng([SEED, 1]).integers(3, TINY.vocab, size=PROMPT_LEN, dtype=np.int64)
     with tempfile.TemporaryDirectory() as tmp:
         path = os.path.join(tmp, "llama_tiny.gguf")
         write_gguf(path, TINY, synthetic_tensors(TINY, SEED, WEIGHT_STD))
         ids, logits = reference_generate(path, prompt, MAX_NEW, TINY.vocab)
+        side = os.path.join(tmp, "int8.npz")
+        subprocess.run([sys.executable, os.path.abspath(__file__), "--child", path, side], check=True,
+                       env={**os.environ, "ZEN_CPU_Q8_ACT": "1", "ZEN_BACKEND": "cpu"})
+        with np.load(side) as g:
+            ids_int8, logits_int8 = g["ids"].copy(), g["last_logits"].copy()
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "llama_tiny.npz")
-    np.savez_compressed(out, prompt=prompt, ids=ids.astype(np.int64), last_logits=logits,
+    print("int8-activation ids:", ids_int8.tolist(), "max |logit diff| to the fp32 run:", float(np.abs(logits_int8 - logits).max()))
+    np.savez_compressed(out, prompt=prompt, ids=ids.astype(np.int64), last_logits=logits, ids_int8=ids_int8, last_logits_int8=logits_int8,
                         meta=json.dumps({"config": TINY.__dict__, "seed": SEED, "weight_std": WEIGHT_STD, "max_new": MAX_NEW}))
     print("reference ids:", ids.tolist())
     print("logits: max", float(logits.max()), "top-2 gap", float(np.sort(logits)[-1] - np.sort(logits)[-2]))

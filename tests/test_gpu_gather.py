@@ -207,9 +207,15 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str):
         dist.barrier()
         pg.close()
         torch.save(result, os.path.join(out_dir, f"rank{rank}.pt"))
-    finally:
-        dist.barrier()
-        dist.destroy_process_group()
+    except BaseException:
+        # no barrier on the error path (the other ranks may never reach it): leave a traceback for the parent and a
+        # failing exit status, on which the spawner ends the remaining ranks
+        import traceback
+        with open(os.path.join(out_dir, f"rank{rank}.err"), "w") as f:
+            traceback.print_exc(file=f)
+        os._exit(1)
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 def test_two_or_more_gpus_gather_matches_oracle(zo, tmp_path):
@@ -218,7 +224,11 @@ def test_two_or_more_gpus_gather_matches_oracle(zo, tmp_path):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
-    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    try:
+        mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    finally:
+        errors = {f: open(os.path.join(tmp_path, f)).read() for f in sorted(os.listdir(tmp_path)) if f.endswith(".err")}
+        assert not errors, "\n".join(f"{f}:\n{t}" for f, t in errors.items())
     rows, cols, tokens = 1000, 1024, 3
     w = seeded_weights(blocks.Q6_K, rows, cols, 400)
     x = seeded_acts(tokens, cols, 401)

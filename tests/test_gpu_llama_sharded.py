@@ -45,6 +45,7 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str):
     be = Backend()
     cfg, meta, prompt, _, _ = _golden()
     result = {}
+    failed = False
     try:
         for mode, tag, kind, cut in ((ACT_FP32, "fp32", "peer", "rows"), (ACT_INT8, "int8", "peer", "rows"), (ACT_FP32, "nccl", "nccl", "rows"),
                                      (ACT_FP32, "cols", "peer", "rows+cols"), (ACT_INT8, "cols8", "peer", "rows+cols")):
@@ -59,20 +60,30 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str):
                 result[tag + "_logits_graph"] = dec.last_logits()
                 result[tag + "_ids_whole"] = whole.generate(prompt.tolist(), meta["max_new"], batched_prefill=False)
                 result[tag + "_logits_whole"] = whole.last_logits()
+            except BaseException:
+                failed = True          # no barrier on the way out: the other rank may never reach it
+                raise
             finally:
-                dist.barrier()
-                dec.close()
-                whole.close()
+                if not failed:
+                    dist.barrier()
+                    dec.close()
+                    whole.close()
         with pytest.raises(ValueError):
             LlamaDecoder(be, cfg, (), rank=rank, world=world, fused="n")
         torch.save(result, os.path.join(out_dir, f"rank{rank}.pt"))
-    finally:
-        # leave as the benchmark's ranks do: no collective in flight, a barrier, then straight out (tearing the NCCL group
-        # down after its collectives were captured into graphs did not return)
-        torch.cuda.synchronize()
-        dist.barrier()
+    except BaseException:
+        # the parent reads the traceback from this file; the exit status says the rank failed
+        import traceback
+        with open(os.path.join(out_dir, f"rank{rank}.err"), "w") as f:
+            traceback.print_exc(file=f)
         sys.stdout.flush()
-        os._exit(0)
+        os._exit(1)
+    # leave as the benchmark's ranks do: no collective in flight, a barrier, then straight out (tearing the NCCL group
+    # down after its collectives were captured into graphs did not return)
+    torch.cuda.synchronize()
+    dist.barrier()
+    sys.stdout.flush()
+    os._exit(0)
 
 
 def test_row_sharded_generation_matches_the_reference_and_the_unsharded_decoder(tmp_path):
@@ -81,7 +92,11 @@ def test_row_sharded_generation_matches_the_reference_and_the_unsharded_decoder(
     world = 2 if torch.cuda.device_count() >= 2 else 0
     if not world:
         pytest.skip("needs at least two GPUs")
-    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    try:
+        mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    finally:
+        errors = {f: open(os.path.join(tmp_path, f)).read() for f in sorted(os.listdir(tmp_path)) if f.endswith(".err")}
+        assert not errors, "\n".join(f"{f}:\n{t}" for f, t in errors.items())
     _, _, _, ids, logits = _golden()
     for r in range(world):
         got = torch.load(os.path.join(tmp_path, f"rank{r}.pt"), weights_only=False)

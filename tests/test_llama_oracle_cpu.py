@@ -27,6 +27,21 @@ def test_numpy_decode_reproduces_the_reference():
     assert np.abs(got_logits - logits).max() <= 1e-4 * np.abs(logits).max()
 
 
+def test_numpy_decode_reproduces_the_reference_with_int8_single_token_products():
+    """The reference run with ZEN_CPU_Q8_ACT=1 (prompt block through the fp32 GEMM, every single-token product with int8
+    activations): ids_int8 / last_logits_int8 of the golden file."""
+    from oracle import llama as ol
+    cfg, meta, prompt, ids_fp32, _ = load_golden()
+    with np.load(GOLDEN) as g:
+        ids, logits = g["ids_int8"].copy(), g["last_logits_int8"].copy()
+    assert ids.tolist() != ids_fp32.tolist()      # the two arithmetics part ways on this model, so the pin tells them apart
+    tensors = {n: a for n, a, _ in synthetic_tensors(cfg, meta["seed"], meta["weight_std"])}
+    shapes = {n: s for n, s, _ in tensor_plan(cfg)}
+    got_ids, got_logits = ol.generate(cfg, tensors, shapes, prompt, meta["max_new"], int8_single_token=True)
+    assert got_ids == ids.tolist()
+    assert np.abs(got_logits - logits).max() <= 1e-4 * np.abs(logits).max()
+
+
 def test_tensor_plan_and_tables():
     cfg = LlamaConfig()
     plan = tensor_plan(cfg)
@@ -67,7 +82,7 @@ def _sharded_rank(rank: int, world: int, port: int, out_dir: str, cut: str):
 
         ids, logits = ol.generate(cfg, tensors, shapes, prompt, meta["max_new"], rank=rank, world=world, gather=gather, cut=cut)
         steps = len(prompt) + meta["max_new"] - 1
-        assert gathers[0] == steps * ((4 if cut == "rows" else 2) * cfg.layers + 1)
+        assert gathers[0] == steps * (4 if cut == "rows" else 2) * cfg.layers + meta["max_new"]     # logits only where a token is picked
         np.savez(os.path.join(out_dir, f"rank{rank}.npz"), ids=np.asarray(ids), logits=logits)
     finally:
         dist.destroy_process_group()

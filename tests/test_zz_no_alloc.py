@@ -6,7 +6,9 @@ allocation implies -- so they have no workspace to pass.  For them the quantised
 built into the library.  This test drives that entry point through the C-ABI twice in a row, with different shapes, so
 the second call meets the first call's bytes in the shared scratch, and compares each result with
 zen_cuda_dev_gemm_q8_0 given an ordinary caller workspace.  Both run the same kernels on the same codes, so the bar is
-the suite's parity bar (1e-3) and the results are in fact expected to be identical.
+the suite's parity bar (1e-3) and the results are in fact expected to be identical.  Each result is also held against
+the CPU oracle's int8-activation product, so the test stands on its own, and the free device memory reported by the
+driver must be the same before and after the calls.
 
 The file name makes pytest collect it last: if it fails, a run that stops at the first failure has already run
 everything else.  It builds its own inputs, so it also passes when run alone in a fresh process.
@@ -20,7 +22,7 @@ from zeninfer_b200 import blocks
 pytestmark = pytest.mark.gpu
 
 
-def test_noalloc_matches_workspace_entry_twice():
+def test_noalloc_matches_workspace_entry_twice(zo):
     import torch
     from zeninfer_b200 import Backend, BackendError
 
@@ -40,16 +42,28 @@ def test_noalloc_matches_workspace_entry_twice():
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         torch.cuda.synchronize()
         be.dev_gemm_q8_0([handle], [out_ref.data_ptr()], x.data_ptr(), tokens, ws.data_ptr(), ws_bytes, stream.cuda_stream)
+        stream.synchronize()
+        free_before = torch.cuda.mem_get_info(dev)[0]          # cudaMemGetInfo: what the driver still has to give
         be.dev_gemm_q8_0_noalloc(handle, out_new.data_ptr(), x.data_ptr(), tokens, stream.cuda_stream)
         stream.synchronize()
+        assert torch.cuda.mem_get_info(dev)[0] == free_before, "the allocation-free entry point changed the free device memory"
         be.dev_check(stream.cuda_stream)
         got, ref = out_new.cpu().numpy(), out_ref.cpu().numpy()
         assert not np.any(got == 123456.0)
         assert_parity(got, ref, what=f"no-alloc call {call + 1} ({tokens} tokens)")
         assert np.array_equal(got, ref)
+        assert_parity(got, zo.gemm(blocks.Q8_0, w, x.cpu().numpy(), tokens, rows, cols, int8_acts=True), what=f"no-alloc call {call + 1} vs the int8 oracle")
 
     # a request larger than the built-in scratch is refused with a message, and nothing is launched
     too_many = 2097152 // cols + 1
     with pytest.raises(BackendError, match="exceeds the built-in scratch"):
         be.dev_gemm_q8_0_noalloc(handle, 1, 1, too_many, stream.cuda_stream)
     be.dev_free(handle)
+    # the second limit: the activations fit the element count, but their scale rows (padded to four tokens) do not fit the array
+    wide = 1 << 20
+    w_wide = seeded_weights(blocks.Q8_0, 1, wide, 920)
+    h_wide = be.dev_upload("Q8_0", w_wide, 1, wide)
+    assert 2 * wide <= 2097152 and be.gemm_workspace_bytes(2, wide) > 2097152 + 262144
+    with pytest.raises(BackendError, match="exceeds the built-in scratch"):
+        be.dev_gemm_q8_0_noalloc(h_wide, 1, 1, 2, stream.cuda_stream)
+    be.dev_free(h_wide)

@@ -33,7 +33,8 @@ ABI_SYMBOLS = (
     "zen_cuda_gemv_q8_0", "zen_cuda_gemm_q8_0", "zen_cuda_gemv_q8_0_batch", "zen_cuda_gemm_q8_0_batch",
     "zen_cuda_gemm_q6_k", "zen_cuda_gemm_q4_0", "zen_cuda_gemm_kquant", "zen_cuda_release_weights", "zen_cuda_quantize_acts",
     "zen_cuda_dev_upload", "zen_cuda_dev_free", "zen_cuda_dev_weight_bytes", "zen_cuda_dev_gemv",
-    "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_gemm_workspace_bytes", "zen_cuda_dev_gemm_q8_0",
+    "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_error_name", "zen_cuda_set_wait_budget_ms",
+    "zen_cuda_gemm_workspace_bytes", "zen_cuda_dev_gemm_q8_0",
     "zen_cuda_dev_gemm_q8_0_noalloc",
     "zen_cuda_gather_region_bytes", "zen_cuda_ipc_alloc", "zen_cuda_ipc_open", "zen_cuda_ipc_close", "zen_cuda_ipc_free",
     "zen_cuda_gather_create", "zen_cuda_gather_destroy", "zen_cuda_dev_gemv_gather", "zen_cuda_dev_gather_fetch", "zen_cuda_dev_allgather", "zen_cuda_dev_allreduce_add",
@@ -114,6 +115,9 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_dev_gemv_swiglu.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, vp, sz, i, vp]
     lib.zen_cuda_dev_gemv_fused.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, i, C.POINTER(GemvFusion), vp]
     lib.zen_cuda_dev_check.argtypes = [vp]
+    lib.zen_cuda_error_name.argtypes = [i]
+    lib.zen_cuda_error_name.restype = C.c_char_p
+    lib.zen_cuda_set_wait_budget_ms.argtypes = [C.c_uint]
     lib.zen_cuda_gemm_workspace_bytes.argtypes = [sz, sz]
     lib.zen_cuda_gemm_workspace_bytes.restype = sz
     lib.zen_cuda_dev_gemm_q8_0.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, vp, sz, vp]
@@ -436,6 +440,17 @@ class Backend:
             self._fail("dev_advance_position")
 
     def dev_check(self, stream: int = 0) -> None:
+        """Synchronises `stream` and raises if a kernel reported through the device-side error word (a bounded wait that
+        gave up, a bad token or position, a non-finite value) or the CUDA runtime reported a failure; .code holds
+        zen_cuda_dev_check's value."""
         code = self.lib.zen_cuda_dev_check(stream)
         if code:
-            raise BackendError(f"a device-side wait timed out (code {code})")
+            what = (self.lib.zen_cuda_error_name(code) or b"").decode()
+            err = BackendError(f"device-side error {code}: {what}" + (f" [{self.last_error()}]" if code < 0 else ""))
+            err.code = code
+            raise err
+
+    def set_wait_budget_ms(self, milliseconds: int) -> None:
+        """How long a bounded device-side wait may last before its kernel gives up (0: the default, about a second)."""
+        if not self.lib.zen_cuda_set_wait_budget_ms(int(milliseconds)):
+            self._fail("set_wait_budget_ms")

@@ -85,7 +85,7 @@ __device__ __forceinline__ bool gather_wait(const PeerGather& g, int lane, unsig
         if (ld_relaxed_sys(f) < epoch) {
             const long long t0 = clock64();
             while (ld_relaxed_sys(f) < epoch)
-                if (clock64() - t0 > kWaitBudgetCycles) { ok = false; break; }
+                if (clock64() - t0 > g_wait_budget_cycles) { ok = false; break; }
         }
     }
     __threadfence();   // GPU scope: nothing that follows is satisfied from before the flags were seen

@@ -74,6 +74,7 @@ struct State {
     bool ready{}, failed{};
     int device{};
     int sm_count{};
+    int clock_khz{};          // top SM clock, for converting a wait budget in milliseconds into cycles
     size_t smem_optin{};
     cudaStream_t stream{}, copy_stream{};
     cudaEvent_t bounce_free[2]{};
@@ -129,8 +130,25 @@ bool opted_out() {
     return out;
 }
 
+// Bounded device waits give up after this many milliseconds (converted with the top SM clock; 0 restores the default).
+bool apply_wait_budget(State& s, unsigned ms) {
+    const long long cycles = ms ? static_cast<long long>(ms) * std::max(1, s.clock_khz) : zk::kDefaultWaitBudgetCycles;
+    ZC_CUDA(s, cudaMemcpyToSymbol(zk::g_wait_budget_cycles, &cycles, sizeof cycles));
+    return true;
+}
+
+bool warm_noalloc_path(State& s);   // defined with the allocation-free entry point
+
 bool init_locked(State& s) {
-    if (s.ready) return true;
+    if (s.ready) {
+        // Entry points may be reached from any thread, and a new thread starts on device 0: make the backend's device
+        // current before anything allocates or launches on its behalf.
+        int cur = -1;
+        if (cudaGetDevice(&cur) != cudaSuccess || cur != s.device) {
+            if (cudaSetDevice(s.device) != cudaSuccess) return set_error(s, "cudaSetDevice to the backend's device failed");
+        }
+        return true;
+    }
     if (s.failed) return false;
     auto fail = [&s](const std::string& why) { s.failed = true; s.last_error = why; return false; };
     int n = 0;
@@ -145,6 +163,7 @@ bool init_locked(State& s) {
     s.device = dev;
     s.sm_count = prop.multiProcessorCount;
     s.smem_optin = prop.sharedMemPerBlockOptin;
+    if (cudaDeviceGetAttribute(&s.clock_khz, cudaDevAttrClockRate, dev) != cudaSuccess) s.clock_khz = 1965000;
     std::snprintf(s.adapter.name, sizeof(s.adapter.name), "%.127s", prop.name);
     s.adapter.dedicated_vram = prop.totalGlobalMem;
     s.adapter.shared_memory = prop.sharedMemPerBlockOptin;
@@ -175,6 +194,12 @@ bool init_locked(State& s) {
             s.encode_tiled = nullptr;
     }
     if (const char* m = std::getenv("ZEN_CUDA_GEMV_CTAS")) s.ctas_per_sm = static_cast<unsigned>(std::max(1, std::min(4, std::atoi(m))));
+    if (const char* m = std::getenv("ZEN_CUDA_WAIT_MS")) {
+        if (!apply_wait_budget(s, static_cast<unsigned>(std::max(0, std::atoi(m))))) return fail("setting the wait budget failed");
+    }
+    // Everything the allocation-free entry point needs that may itself allocate (module loading, the scratch array's
+    // address, the GEMM's shared-memory opt-in) happens here, where allocating is allowed.
+    if (!warm_noalloc_path(s)) return fail("preparing the allocation-free GEMM path failed: " + s.last_error);
     s.ready = true;
     return true;
 }
@@ -568,17 +593,22 @@ size_t gemm_ws_bytes(size_t tokens, size_t cols) {
     return ((tokens * cols + 255) & ~size_t(255)) + (cols / 32) * t_ld * sizeof(float);
 }
 
+// The shared-memory opt-in of the GEMM kernel; done once, at start-up (it loads the kernel's module, which may allocate).
+template <int kNTile>
+cudaError_t configure_gemm() {
+    static bool configured = false;
+    if (configured) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(&zk::gemm_q8_0_i8_kernel<kNTile>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(zk::gemm_smem_bytes(kNTile)));
+    if (e == cudaSuccess) configured = true;
+    return e;
+}
+
 template <int kNTile>
 cudaError_t launch_gemm(const zk::GemmParams& p, unsigned grid, cudaStream_t st) {
-    auto* fn = &zk::gemm_q8_0_i8_kernel<kNTile>;
-    const size_t smem = zk::gemm_smem_bytes(kNTile);
-    static bool configured = false;
-    if (!configured) {
-        const cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
-    fn<<<grid, zk::kGemmThreads, smem, st>>>(p);
+    const cudaError_t e = configure_gemm<kNTile>();
+    if (e != cudaSuccess) return e;
+    zk::gemm_q8_0_i8_kernel<kNTile><<<grid, zk::kGemmThreads, zk::gemm_smem_bytes(kNTile), st>>>(p);
     return cudaGetLastError();
 }
 
@@ -664,6 +694,19 @@ bool noalloc_scratch_address(State& s, uint8_t** out) {
         by_device[dev] = static_cast<uint8_t*>(p);
     }
     *out = by_device[dev];
+    return true;
+}
+
+// Called once while the backend starts (allocating is still allowed there): resolves the scratch array's address on the
+// backend's device, opts the GEMM kernel into its shared memory and loads the code of every kernel the entry point
+// launches, so that the entry point itself never triggers a lazy module load.
+bool warm_noalloc_path(State& s) {
+    uint8_t* scratch = nullptr;
+    if (!noalloc_scratch_address(s, &scratch)) return false;
+    ZC_CUDA(s, configure_gemm<128>());
+    cudaFuncAttributes attr{};
+    ZC_CUDA(s, cudaFuncGetAttributes(&attr, zk::quantize_acts_gemm_kernel));
+    ZC_CUDA(s, cudaFuncGetAttributes(&attr, zk::gemm_zero_split_tiles_kernel));
     return true;
 }
 
@@ -789,7 +832,7 @@ bool check_error_word(State& s) {
     if (*s.h_error == 0) return true;
     const int code = *s.h_error;
     *s.h_error = 0;
-    return set_error(s, "device wait timed out (code " + std::to_string(code) + ")");
+    return set_error(s, std::string("device-side error word: ") + zen_cuda_error_name(code) + " (code " + std::to_string(code) + ")");
 }
 
 // Host-pointer batched product: `count` tensors sharing `tokens` activation rows.
@@ -1498,11 +1541,41 @@ int zen_cuda_dev_advance_position(int* d_pos, int delta, void* stream) {
 int zen_cuda_dev_check(void* stream) {
     State& s = state();
     std::lock_guard<std::mutex> lock(s.mutex);
-    if (!s.ready) return 0;
-    cudaStreamSynchronize(stream ? static_cast<cudaStream_t>(stream) : s.stream);
+    if (!s.ready) { set_error(s, "dev_check: backend not initialised"); return -1; }
+    cudaError_t e = cudaStreamSynchronize(stream ? static_cast<cudaStream_t>(stream) : s.stream);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) {   // a failed launch or a fault: not one of the kernels' own codes
+        set_error(s, std::string("dev_check: ") + cudaGetErrorString(e));
+        return -static_cast<int>(e) - 1;
+    }
     const int code = *s.h_error;
     *s.h_error = 0;
+    if (code) set_error(s, std::string("device-side error word: ") + zen_cuda_error_name(code));
     return code;
+}
+
+const char* zen_cuda_error_name(int code) {
+    switch (code) {
+    case 0: return "none";
+    case zk::kErrFullWaitTimeout: return "wait for a weight stage to land timed out";
+    case zk::kErrEmptyWaitTimeout: return "wait for a free weight stage timed out";
+    case zk::kErrDrainTimeout: return "wait for copies in flight at kernel exit timed out";
+    case zk::kErrTmemWaitTimeout: return "wait for a tensor-memory accumulator timed out";
+    case zk::kErrPeerWaitTimeout: return "a peer GPU did not publish its outputs in time";
+    case zk::kErrBadToken: return "token id outside the embedding table";
+    case zk::kErrBadPosition: return "position outside the KV cache";
+    case zk::kErrNonFinite: return "non-finite value in attention";
+    case zk::kErrInputWaitTimeout: return "wait for a work-list item's input timed out";
+    default: return code < 0 ? "CUDA runtime error (see zen_cuda_last_error)" : "unknown";
+    }
+}
+
+int zen_cuda_set_wait_budget_ms(unsigned milliseconds) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    ZC_CUDA(s, cudaStreamSynchronize(s.stream));
+    return apply_wait_budget(s, milliseconds) ? 1 : 0;
 }
 
 #ifdef ZK_TRACE

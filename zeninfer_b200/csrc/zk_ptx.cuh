@@ -8,13 +8,18 @@
 namespace zk {
 
 // Longest time any device-side wait may last before the kernel gives up, sets
-// the error word and returns.  ~1 s at the B200's top SM clock.
-constexpr long long kWaitBudgetCycles = 2000000000LL;
+// the error word and returns: SM clock cycles, ~1 s at the B200's top clock by
+// default.  A constant-memory word so that the host can shorten it (set at
+// start-up from ZEN_CUDA_WAIT_MS, or by zen_cuda_set_wait_budget_ms); it is read
+// only on the slow path of a wait, after a first test of the barrier has failed.
+constexpr long long kDefaultWaitBudgetCycles = 2000000000LL;
+__constant__ long long g_wait_budget_cycles = kDefaultWaitBudgetCycles;
 
 // Error codes written to the kernel's error word (0 = success).
 enum : int { kErrNone = 0, kErrFullWaitTimeout = 1, kErrEmptyWaitTimeout = 2, kErrDrainTimeout = 3, kErrTmemWaitTimeout = 4,
              /* 5: a peer did not publish in time (peer_gather.cuh) */
-             kErrBadToken = 6, kErrBadPosition = 7, kErrNonFinite = 8 };
+             kErrBadToken = 6, kErrBadPosition = 7, kErrNonFinite = 8,
+             kErrInputWaitTimeout = 9 /* a work-list item's input was not produced in time (gemv_q8_0.cuh) */ };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -42,7 +47,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity))
-        if (clock64() - t0 > kWaitBudgetCycles) return false;
+        if (clock64() - t0 > g_wait_budget_cycles) return false;
     return true;
 }
 

@@ -107,7 +107,8 @@ class LlamaDecoder:
     synthetic_tensors does; matrices must be Q8_0 raw blocks [rows, row_bytes]."""
 
     def __init__(self, backend: Backend, cfg: LlamaConfig, tensors, act_mode: int = ACT_INT8, max_positions: int | None = None, device=None,
-                 fused: bool | str = "nr", rank: int = 0, world: int = 1, group=None, gather: str = "peer", cut: str = "rows+cols"):
+                 fused: bool | str = "nr", rank: int = 0, world: int = 1, group=None, gather: str = "peer", cut: str = "rows+cols",
+                 prompt_act_mode: int | None = None):
         """fused: which of the layer's small operators are folded into the projection launches, as a string of letters:
         'n' RMSNorm into the q|k|v, gate|up and lm_head prologues, 's' SwiGLU into the down projection's prologue,
         'r' the residual adds into the o and down projections' stores.  True = all (5 launches per layer), False =
@@ -118,9 +119,14 @@ class LlamaDecoder:
         gather: "peer" = the library's own all-gather kernel over NVLink peer memory (the group only carries the IPC
         handles and host barriers, any backend), "nccl" = all_gather_into_tensor (the group must be NCCL).
         cut: "rows" = every matrix by output rows (four gathers per layer); "rows+cols" (default) = o and down by columns,
-        summed by an all-reduce (two exchanges per layer; with gather="nccl" the row cut is used)."""
+        summed by an all-reduce (two exchanges per layer; with gather="nccl" the row cut is used).
+        prompt_act_mode: activation mode of the layer products while the prompt is consumed, when it differs from act_mode.
+        The reference with ZEN_CPU_Q8_ACT=1 is such a mix: its prompt block goes through the fp32-activation GEMM
+        (src/quant.cpp:1667-1680) and only single-token products quantise their input to int8 (:1088-1123); ACT_FP32 here
+        with act_mode=ACT_INT8 reproduces it (the prompt then goes token by token, outside the step graphs)."""
         import torch
         self.torch, self.be, self.cfg, self.act_mode = torch, backend, cfg, act_mode
+        self.prompt_act_mode = prompt_act_mode if prompt_act_mode not in (None, act_mode) else None
         self.fuse = "nsr" if fused is True else "" if fused is False else str(fused)
         self.rank, self.world, self.group = int(rank), int(world), group
         if not 0 <= self.rank < self.world:
@@ -368,7 +374,7 @@ class LlamaDecoder:
         torch = self.torch
         ids = torch.tensor(prompt, dtype=torch.int64).pin_memory()
         if batched_prefill is None:
-            batched_prefill = self.act_mode == ACT_INT8 and self.world == 1
+            batched_prefill = self.act_mode == ACT_INT8 and self.world == 1 and self.prompt_act_mode is None
         with torch.cuda.stream(self.stream):
             done = 0
             if batched_prefill and len(prompt) >= self.PREFILL_MIN:
@@ -381,7 +387,17 @@ class LlamaDecoder:
                     self._enqueue_head()      # the first pick, from the last prompt token's hidden state
             for i in range(done, len(prompt)):
                 self.token.copy_(ids[i:i + 1], non_blocking=True)
-                self.step(want_token=(i + 1 == len(prompt)))
+                last = i + 1 == len(prompt)
+                if self.prompt_act_mode is None:
+                    self.step(want_token=last)
+                    continue
+                decode_mode, self.act_mode = self.act_mode, self.prompt_act_mode
+                try:
+                    self._enqueue_layers()            # eager: the captured graphs hold the decode mode
+                finally:
+                    self.act_mode = decode_mode
+                if last:
+                    self._enqueue_head()              # a single-token product: the decode mode
 
     def generate(self, prompt: list[int], max_new: int, on_token=None, batched_prefill: bool | None = None) -> list[int]:
         """Greedy generation: the prompt, then max_new picks (each read back, as the reference's per-token callback
