@@ -188,6 +188,35 @@ typedef struct zen_cuda_gemv_fusion {
 int zen_cuda_dev_gemv_fused(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x, size_t tokens, int act_mode,
                             const zen_cuda_gemv_fusion* fusion, void* stream);
 
+/* Several batch-1 Q8_0 products in ONE persistent launch: what the reference's fused D3D12 submissions do for a layer's
+ * chain of matvecs (ffn_residual_fused: o, residual, norm, gate|up, SwiGLU, down, residual in one command list, and
+ * layer_decode_pipeline, include/zen/d3d12_backend.h:289-352, zen::quant::ffn_residual_fused src/quant.cpp:1566-1611).
+ * An item is one zen_cuda_dev_gemv_fused product (up to ZEN_CUDA_MAX_BATCH tensors sharing d_x, one token); the items
+ * run in order, the weight stream never pauses between them, and every result is bit-identical to the same products
+ * launched one by one.
+ *   - depends_on_earlier_items != 0: the item's input (d_x, gate) or accumulated output is written by earlier items of
+ *     the same list; its arithmetic starts once all of them are complete.  Leave it 0 for items that only read what
+ *     was complete before the launch (independent tensors sharing an input, the bench's weight copies): hazards
+ *     between such items are the caller's business.
+ *   - fusion: as zen_cuda_dev_gemv_fused (warm_next is ignored: the list streams ahead by itself).
+ *   - The list is built once (the items are copied to the device) and launched any number of times, like a graph; one
+ *     list must not be in flight twice at the same time.  Pointers inside must stay valid while it exists.
+ *   - The launch uses one CTA per SM and relies on all of them being resident together; waits are bounded like every
+ *     device-side wait here (zen_cuda_dev_check code 9 when an item's input did not arrive). */
+typedef struct zen_cuda_gemv_list zen_cuda_gemv_list;
+typedef struct zen_cuda_gemv_list_item {
+    const zen_cuda_weights* const* w;
+    float* const* d_y;
+    size_t count;
+    const float* d_x;
+    zen_cuda_gemv_fusion fusion;
+    int depends_on_earlier_items;
+} zen_cuda_gemv_list_item;
+zen_cuda_gemv_list* zen_cuda_gemv_list_create(const zen_cuda_gemv_list_item* items, size_t count, int act_mode);
+void zen_cuda_gemv_list_destroy(zen_cuda_gemv_list* list);
+uint64_t zen_cuda_gemv_list_bytes(const zen_cuda_gemv_list* list); /* raw GGUF bytes + fp32 inputs and outputs of all items */
+int zen_cuda_dev_gemv_list(const zen_cuda_gemv_list* list, void* stream);
+
 /* Prefill product on the tensor cores (Q8_0, int8 activations): d_out[i] = d_x * W[i]^T, token-major
  * [tokens][rows_i].  d_x: device fp32 [tokens][columns]; `workspace` is device scratch of at least
  * zen_cuda_gemm_workspace_bytes(tokens, columns) bytes that must stay untouched until the work has run (it

@@ -161,19 +161,36 @@ def test_generation_matches_the_reference(be, golden, graphs, fused):
 def test_int8_activation_decode_matches_the_reference(be, golden, graphs):
     """The reference run with ZEN_CPU_Q8_ACT=1 (ids_int8 / last_logits_int8 of the golden file): its prompt block goes
     through the fp32-activation GEMM and every single-token product quantises its input to int8, which is
-    LlamaDecoder(act_mode=ACT_INT8, prompt_act_mode=ACT_FP32).  Ids identical, logits within 1e-3."""
+    LlamaDecoder(act_mode=ACT_INT8, prompt_act_mode=ACT_FP32).
+
+    Bars: all sixteen picked ids identical; the logits of the first pick (one int8 product after the prompt) within 5e-3
+    of the numpy restatement of that reference run; the logits after fifteen chained int8 steps within 3e-2.  These
+    bars are wider than a single product's 1e-3 because rounding to int8 codes is discontinuous.  One activation code
+    that rounds the other way shifts an output by (amax / 127) x one weight, which for this model's 256 columns is
+    1.5e-3 of the largest logit, and the prompt's fp32-equivalent products (2e-5 from exact) are enough to flip one.
+    Chained, the flips compound: in the reference's OWN arithmetic a relative perturbation of 1e-6 of every product's
+    outputs (less than a change of summation order gives) moves the final logits by up to 1.1e-2 of their maximum
+    (tests/test_llama_oracle_cpu.py shows it), so no implementation that sums in a different order can hold 1e-3
+    there.  With identical codes every single product is held to 1e-3 by the GEMV tests."""
+    from oracle import llama as ol
+    from zeninfer_b200.llama import tensor_plan
     cfg, meta, prompt, ids_fp32, _ = golden
     with np.load(GOLDEN) as g:
         ids, logits = g["ids_int8"].copy(), g["last_logits_int8"].copy()
     assert ids.tolist() != ids_fp32.tolist()
+    tensors = {n: a for n, a, _ in synthetic_tensors(cfg, meta["seed"], meta["weight_std"])}
+    first_ids, first_logits = ol.generate(cfg, tensors, {n: sh for n, sh, _ in tensor_plan(cfg)}, prompt, 1, int8_single_token=True)
+    assert first_ids == ids[:1].tolist()
     dec = LlamaDecoder(be, cfg, synthetic_tensors(cfg, meta["seed"], meta["weight_std"]), act_mode=ACT_INT8, prompt_act_mode=ACT_FP32)
     try:
         if graphs:
             dec.capture()
+        assert dec.generate(prompt.tolist(), 1) == ids[:1].tolist()
+        assert_parity(dec.last_logits(), first_logits, 5e-3, "logits of the first pick (prompt in fp32, lm_head in int8)")
         for _ in range(2):
             got = dec.generate(prompt.tolist(), meta["max_new"])
             assert got == ids.tolist()
-            assert_parity(dec.last_logits(), logits, 1e-3, "last logits, int8 single-token products")
+            assert_parity(dec.last_logits(), logits, 3e-2, "last logits after fifteen chained int8 steps")
     finally:
         dec.close()
 

@@ -34,6 +34,7 @@ ABI_SYMBOLS = (
     "zen_cuda_gemm_q6_k", "zen_cuda_gemm_q4_0", "zen_cuda_gemm_kquant", "zen_cuda_release_weights", "zen_cuda_quantize_acts",
     "zen_cuda_dev_upload", "zen_cuda_dev_free", "zen_cuda_dev_weight_bytes", "zen_cuda_dev_gemv",
     "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_error_name", "zen_cuda_set_wait_budget_ms",
+    "zen_cuda_gemv_list_create", "zen_cuda_gemv_list_destroy", "zen_cuda_gemv_list_bytes", "zen_cuda_dev_gemv_list",
     "zen_cuda_gemm_workspace_bytes", "zen_cuda_dev_gemm_q8_0",
     "zen_cuda_dev_gemm_q8_0_noalloc",
     "zen_cuda_gather_region_bytes", "zen_cuda_ipc_alloc", "zen_cuda_ipc_open", "zen_cuda_ipc_close", "zen_cuda_ipc_free",
@@ -75,6 +76,11 @@ class GemvFusion(C.Structure):
     _fields_ = [("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("accumulate", C.c_int), ("gate", C.c_void_p), ("warm_next", C.c_void_p)]
 
 
+class GemvListItem(C.Structure):
+    _fields_ = [("w", C.POINTER(C.c_void_p)), ("d_y", C.POINTER(C.c_void_p)), ("count", C.c_size_t), ("d_x", C.c_void_p),
+                ("fusion", GemvFusion), ("depends_on_earlier_items", C.c_int)]
+
+
 class PickSegment(C.Structure):
     _fields_ = [("base", C.c_void_p), ("len", C.c_uint32), ("first_index", C.c_uint32), ("token_stride", C.c_uint32), ("reserved", C.c_uint32)]
 
@@ -114,6 +120,13 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_dev_quantize_acts.argtypes = [vp, vp, vp, sz, sz, vp]
     lib.zen_cuda_dev_gemv_swiglu.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, vp, sz, i, vp]
     lib.zen_cuda_dev_gemv_fused.argtypes = [C.POINTER(vp), C.POINTER(vp), sz, vp, sz, i, C.POINTER(GemvFusion), vp]
+    lib.zen_cuda_gemv_list_create.argtypes = [C.POINTER(GemvListItem), sz, i]
+    lib.zen_cuda_gemv_list_create.restype = vp
+    lib.zen_cuda_gemv_list_destroy.argtypes = [vp]
+    lib.zen_cuda_gemv_list_destroy.restype = None
+    lib.zen_cuda_gemv_list_bytes.argtypes = [vp]
+    lib.zen_cuda_gemv_list_bytes.restype = C.c_uint64
+    lib.zen_cuda_dev_gemv_list.argtypes = [vp, vp]
     lib.zen_cuda_dev_check.argtypes = [vp]
     lib.zen_cuda_error_name.argtypes = [i]
     lib.zen_cuda_error_name.restype = C.c_char_p
@@ -296,6 +309,35 @@ class Backend:
         f = GemvFusion(norm_weight, norm_eps, int(accumulate), gate, warm_next)
         if not self.lib.zen_cuda_dev_gemv_fused(hs, ys, n, d_x, tokens, act_mode, C.byref(f), stream):
             self._fail("dev_gemv_fused")
+
+    def gemv_list_create(self, items: Sequence[dict], act_mode: int) -> int:
+        """Builds a list of batch-1 Q8_0 products for one persistent launch (zen_cuda_gemv_list_create).  An item is a dict:
+        handles, d_y (device addresses), d_x, and optionally norm_weight, norm_eps, gate, accumulate (as dev_gemv_fused) and
+        depends (True when the item reads or accumulates into what earlier items of the list write)."""
+        n = len(items)
+        arr = (GemvListItem * n)()
+        keep = []
+        for dst, it in zip(arr, items):
+            k = len(it["handles"])
+            hs, ys = (C.c_void_p * k)(*it["handles"]), (C.c_void_p * k)(*it["d_y"])
+            keep.append((hs, ys))
+            dst.w, dst.d_y, dst.count, dst.d_x = hs, ys, k, it["d_x"]
+            dst.fusion = GemvFusion(it.get("norm_weight"), it.get("norm_eps", 0.0), int(bool(it.get("accumulate"))), it.get("gate"), None)
+            dst.depends_on_earlier_items = int(bool(it.get("depends")))
+        h = self.lib.zen_cuda_gemv_list_create(arr, n, act_mode)
+        if not h:
+            self._fail("gemv_list_create")
+        return int(h)
+
+    def gemv_list_destroy(self, handle: int) -> None:
+        self.lib.zen_cuda_gemv_list_destroy(handle)
+
+    def gemv_list_bytes(self, handle: int) -> int:
+        return int(self.lib.zen_cuda_gemv_list_bytes(handle))
+
+    def dev_gemv_list(self, handle: int, stream: int = 0) -> None:
+        if not self.lib.zen_cuda_dev_gemv_list(handle, stream):
+            self._fail("dev_gemv_list")
 
     def gemm_workspace_bytes(self, tokens: int, columns: int) -> int:
         return int(self.lib.zen_cuda_gemm_workspace_bytes(tokens, columns))

@@ -29,6 +29,7 @@
 #include "gemm_q8_0_i8.cuh"
 #include "gemv_k45.cuh"
 #include "gemv_kq.cuh"
+#include "gemv_list.cuh"
 #include "gemv_q8_0.cuh"
 #include "greedy_pick.cuh"
 #include "quantize_acts.cuh"
@@ -37,6 +38,15 @@
 struct zen_cuda_gather {
     zk::PeerGather dev{};     // what the kernels receive
     void* counters{};         // local device words: epoch (u64), CTA arrival count (u32), published (u64)
+};
+
+struct zen_cuda_gemv_list {
+    zk::GemvListItem* d_items{};   // the items, then the launch's counter word, in one device allocation
+    unsigned int* d_counter{};
+    uint32_t nitems{}, kpad_blocks{};
+    int digits{};
+    size_t smem{};
+    uint64_t algorithmic_bytes{};  // raw GGUF bytes of all tensors + fp32 inputs and outputs
 };
 
 struct zen_cuda_weights {
@@ -566,6 +576,94 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
     return true;
 }
 
+
+// ---- a list of products in one persistent launch (gemv_list.cuh) ---------------------------------------------------
+
+template <int kDigits>
+cudaError_t launch_gemv_list(const zk::GemvListParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
+    auto* fn = &zk::gemv_q8_0_list_kernel<kDigits>;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        configured = smem;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(zk::kGemvThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, fn, p);
+}
+
+zen_cuda_gemv_list* list_create_locked(State& s, const zen_cuda_gemv_list_item* items, size_t count, int act_mode) {
+    auto bad = [&s](const char* why) { set_error(s, std::string("gemv_list_create: ") + why); return static_cast<zen_cuda_gemv_list*>(nullptr); };
+    if (!items || !count || count > 4096) return bad("bad item list");
+    if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return bad("bad activation mode");
+    std::vector<zk::GemvListItem> host(count);
+    uint32_t kpad = 0;
+    uint64_t bytes = 0;
+    for (size_t i = 0; i < count; ++i) {
+        const zen_cuda_gemv_list_item& in = items[i];
+        zk::GemvListItem& it = host[i];
+        if (!in.w || !in.d_y || !in.count || in.count > zk::kMaxTasks || !in.d_x) return bad("an item needs tensors, outputs and an input");
+        if (in.fusion.gate && in.fusion.norm_weight) return bad("a fused input is either SwiGLU or RMSNorm");
+        uint32_t total_rows = 0;
+        for (size_t k = 0; k < in.count; ++k) {
+            const zen_cuda_weights* w = in.w[k];
+            if (!w || !in.d_y[k] || w->format != ZEN_CUDA_Q8_0 || w->cols != in.w[0]->cols) return bad("the tensors of an item must be Q8_0 and share their columns");
+            it.task[k].codes = static_cast<const uint8_t*>(w->plane[0]);
+            it.task[k].scales = static_cast<const __half*>(w->plane[1]);
+            it.task[k].y = in.d_y[k];
+            it.task[k].rows = static_cast<uint32_t>(w->rows);
+            it.task[k].first_row = total_rows;
+            total_rows += static_cast<uint32_t>(w->rows);
+            bytes += w->raw_bytes + w->rows * sizeof(float);
+        }
+        const size_t cols = in.w[0]->cols;
+        const uint32_t nb = static_cast<uint32_t>(cols / 32);
+        if (in.w[0]->nb != nb || in.w[0]->nbp != ((nb + 7) & ~7u)) return bad("resident tensor has an unexpected scale pitch");
+        if ((reinterpret_cast<uintptr_t>(in.d_x) | reinterpret_cast<uintptr_t>(in.fusion.gate) | reinterpret_cast<uintptr_t>(in.fusion.norm_weight)) % 16)
+            return bad("inputs must be 16-byte aligned");
+        bytes += cols * sizeof(float);
+        it.x = in.d_x;
+        it.x_gate = in.fusion.gate;
+        it.norm_weight = in.fusion.norm_weight;
+        it.norm_eps = in.fusion.norm_eps;
+        it.flags = (in.fusion.gate ? zk::kGemvFlagSwiglu : 0u) | (in.fusion.norm_weight ? zk::kGemvFlagNorm : 0u) |
+                   (in.fusion.accumulate ? zk::kGemvFlagAccumulate : 0u) | (in.depends_on_earlier_items ? zk::kListFlagDepends : 0u);
+        it.K = static_cast<uint32_t>(cols);
+        it.total_rows = total_rows;
+        it.ntasks = static_cast<uint32_t>(in.count);
+        kpad = std::max(kpad, ((nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks) * zk::kGemvSegBlocks);
+    }
+    const int digits = act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1;
+    const size_t smem = zk::gemv_list_smem_bytes(kpad, digits);
+    if (smem > s.smem_optin) return bad("the widest input does not fit shared memory beside the weight ring");
+    auto* list = new zen_cuda_gemv_list;
+    const size_t item_bytes = count * sizeof(zk::GemvListItem);
+    void* dev = nullptr;
+    if (cudaMalloc(&dev, item_bytes + 16) != cudaSuccess) { delete list; return bad("out of device memory"); }
+    list->d_items = static_cast<zk::GemvListItem*>(dev);
+    list->d_counter = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(dev) + item_bytes);
+    if (cudaMemcpy(list->d_items, host.data(), item_bytes, cudaMemcpyHostToDevice) != cudaSuccess || cudaMemset(list->d_counter, 0, 16) != cudaSuccess) {
+        cudaFree(dev);
+        delete list;
+        return bad("copying the items failed");
+    }
+    list->nitems = static_cast<uint32_t>(count);
+    list->kpad_blocks = kpad;
+    list->digits = digits;
+    list->smem = smem;
+    list->algorithmic_bytes = bytes;
+    return list;
+}
 
 // ---- prefill GEMM (tcgen05) -----------------------------------------------------------------------------------
 
@@ -1146,6 +1244,43 @@ int zen_cuda_dev_gemv_fused(const zen_cuda_weights* const* w, float* const* d_y,
     if (!w || !d_y || !d_x || !fusion) return set_error(s, "dev_gemv_fused: bad arguments") ? 1 : 0;
     return enqueue_gemv(s, w, d_y, count, d_x, tokens, act_mode, stream ? static_cast<cudaStream_t>(stream) : s.stream, nullptr, fusion->gate,
                         fusion->norm_weight, fusion->norm_eps, fusion->accumulate != 0, fusion->warm_next) ? 1 : 0;
+}
+
+zen_cuda_gemv_list* zen_cuda_gemv_list_create(const zen_cuda_gemv_list_item* items, size_t count, int act_mode) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return nullptr;
+    return list_create_locked(s, items, count, act_mode);
+}
+
+void zen_cuda_gemv_list_destroy(zen_cuda_gemv_list* list) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!list) return;
+    if (s.ready) { cudaDeviceSynchronize(); cudaFree(list->d_items); }
+    delete list;
+}
+
+uint64_t zen_cuda_gemv_list_bytes(const zen_cuda_gemv_list* list) { return list ? list->algorithmic_bytes : 0; }
+
+int zen_cuda_dev_gemv_list(const zen_cuda_gemv_list* list, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!list) return set_error(s, "dev_gemv_list: bad arguments") ? 1 : 0;
+    zk::GemvListParams p{};
+    p.items = list->d_items;
+    p.nitems = list->nitems;
+    p.kpad_blocks = list->kpad_blocks;
+    p.counter = list->d_counter;
+    p.error_word = s.d_error;
+    cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : s.stream;
+    // one CTA per SM, all resident at once: the items' dependency waits need every CTA to make progress
+    const unsigned grid = static_cast<unsigned>(s.sm_count);
+    const cudaError_t e = list->digits == 2 ? launch_gemv_list<2>(p, grid, list->smem, st, s.pdl) : launch_gemv_list<1>(p, grid, list->smem, st, s.pdl);
+    if (e != cudaSuccess) return set_error(s, std::string("dev_gemv_list launch: ") + cudaGetErrorString(e)) ? 1 : 0;
+    ++s.stats.dispatches;
+    return 1;
 }
 
 size_t zen_cuda_gemm_workspace_bytes(size_t tokens, size_t columns) { return gemm_ws_bytes(tokens, columns); }
