@@ -63,7 +63,7 @@ __device__ __forceinline__ float quantise_block_quad(const float (&v)[8], uint2&
         amax = other > amax ? other : amax;
     }
     const float d = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 0.0f;
-    const float inv = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    const float inv = d > 0.0f ? __frcp_rn(d) : 0.0f;   // the correctly rounded reciprocal is the IEEE quotient 1 / d
     const float inv256 = __fmul_rn(inv, 256.0f);
     uint32_t w1[2] = {0, 0}, w2[2] = {0, 0};
 #pragma unroll

@@ -41,9 +41,9 @@ struct zen_cuda_gather {
 };
 
 struct zen_cuda_gemv_list {
-    zk::GemvListItem* d_items{};   // the items, then the launch's counter word, in one device allocation
-    unsigned int* d_counter{};
-    uint32_t nitems{}, kpad_blocks{};
+    std::vector<zk::GemvListItem> items;   // they travel as kernel parameters, up to zk::kListMaxItems per launch
+    unsigned int* d_counter{};              // device word the CTAs count finished items on (zero between launches)
+    uint32_t kpad_blocks{};
     int digits{};
     size_t smem{};
     uint64_t algorithmic_bytes{};  // raw GGUF bytes of all tensors + fp32 inputs and outputs
@@ -101,6 +101,7 @@ struct State {
     float* d_x{}; size_t d_x_bytes{};
     float* d_y{}; size_t d_y_bytes{};
     uint8_t* d_gemm_ws{}; size_t d_gemm_ws_bytes{};  // quantised activations of the prefill GEMM: codes, then block-major scales
+    unsigned list_ahead_units{0};   // list launches: row groups of the next item the producer asks L2 for at an item boundary (ZEN_CUDA_LIST_AHEAD; measured: no gain, default off)
     bool warm_hints{true};    // honour zen_cuda_gemv_fusion.warm_next (ZEN_CUDA_WARM=0 ignores the hints)
     bool gemm_stream_k{true}; // prefill GEMM: even K-tile shares when tiles do not divide the SMs (ZEN_CUDA_GEMM_STREAMK=0 turns it off)
     bool use_gemm{true};     // tensor-core prefill path (ZEN_CUDA_GEMM=0 falls back to chunks of eight tokens on the decode kernel)
@@ -204,6 +205,7 @@ bool init_locked(State& s) {
             s.encode_tiled = nullptr;
     }
     if (const char* m = std::getenv("ZEN_CUDA_GEMV_CTAS")) s.ctas_per_sm = static_cast<unsigned>(std::max(1, std::min(4, std::atoi(m))));
+    if (const char* m = std::getenv("ZEN_CUDA_LIST_AHEAD")) s.list_ahead_units = static_cast<unsigned>(std::max(0, std::min(64, std::atoi(m))));
     if (const char* m = std::getenv("ZEN_CUDA_WAIT_MS")) {
         if (!apply_wait_budget(s, static_cast<unsigned>(std::max(0, std::atoi(m))))) return fail("setting the wait budget failed");
     }
@@ -579,9 +581,9 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
 
 // ---- a list of products in one persistent launch (gemv_list.cuh) ---------------------------------------------------
 
-template <int kDigits>
-cudaError_t launch_gemv_list(const zk::GemvListParams& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
-    auto* fn = &zk::gemv_q8_0_list_kernel<kDigits>;
+template <int kDigits, int kItems>
+cudaError_t launch_gemv_list(const zk::GemvListParams<kItems>& p, unsigned grid, size_t smem, cudaStream_t st, bool pdl) {
+    auto* fn = &zk::gemv_q8_0_list_kernel<kDigits, kItems>;
     static size_t configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -591,7 +593,7 @@ cudaError_t launch_gemv_list(const zk::GemvListParams& p, unsigned grid, size_t 
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(zk::kGemvThreads);
+    cfg.blockDim = dim3(zk::kListThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr{};
@@ -600,6 +602,24 @@ cudaError_t launch_gemv_list(const zk::GemvListParams& p, unsigned grid, size_t 
     cfg.attrs = &attr;
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, fn, p);
+}
+
+// One launch for items [first, first + n) of the list.
+template <int kItems>
+cudaError_t launch_list_piece(State& s, const zen_cuda_gemv_list& list, size_t first, size_t n, cudaStream_t st) {
+    static zk::GemvListParams<kItems> p;   // 30 KB for the long instantiation: not on the stack; calls are serialised by the backend mutex
+    std::memcpy(p.items, list.items.data() + first, n * sizeof(zk::GemvListItem));
+    p.nitems = static_cast<uint32_t>(n);
+    p.kpad_blocks = list.kpad_blocks;
+    p.counter = list.d_counter;
+    p.error_word = s.d_error;
+    p.ahead_units = s.list_ahead_units;
+#ifdef ZK_TRACE
+    p.trace = g_trace;
+#endif
+    // one CTA per SM, all resident at once: the items' dependency waits need every CTA to make progress
+    const unsigned grid = static_cast<unsigned>(s.sm_count);
+    return list.digits == 2 ? launch_gemv_list<2, kItems>(p, grid, list.smem, st, s.pdl) : launch_gemv_list<1, kItems>(p, grid, list.smem, st, s.pdl);
 }
 
 zen_cuda_gemv_list* list_create_locked(State& s, const zen_cuda_gemv_list_item* items, size_t count, int act_mode) {
@@ -640,24 +660,29 @@ zen_cuda_gemv_list* list_create_locked(State& s, const zen_cuda_gemv_list_item* 
                    (in.fusion.accumulate ? zk::kGemvFlagAccumulate : 0u) | (in.depends_on_earlier_items ? zk::kListFlagDepends : 0u);
         it.K = static_cast<uint32_t>(cols);
         it.total_rows = total_rows;
-        it.ntasks = static_cast<uint32_t>(in.count);
-        kpad = std::max(kpad, ((nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks) * zk::kGemvSegBlocks);
+        // the device does no division: the geometry of the rows in the ring and the CTAs' row cut are settled here
+        const uint32_t grid = static_cast<uint32_t>(s.sm_count);
+        it.rows_q = total_rows / grid;
+        it.rows_rem = total_rows % grid;
+        it.nb = nb;
+        it.nbp = (nb + 7) & ~7u;
+        it.nseg = (nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks;
+        it.segb = ((nb + it.nseg - 1) / it.nseg + 7) & ~7u;
+        if (it.nseg == 1 && it.nb == it.nbp) it.flags |= zk::kListFlagContiguous;
+        kpad = std::max(kpad, it.nseg * zk::kGemvSegBlocks);
     }
     const int digits = act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1;
     const size_t smem = zk::gemv_list_smem_bytes(kpad, digits);
     if (smem > s.smem_optin) return bad("the widest input does not fit shared memory beside the weight ring");
     auto* list = new zen_cuda_gemv_list;
-    const size_t item_bytes = count * sizeof(zk::GemvListItem);
     void* dev = nullptr;
-    if (cudaMalloc(&dev, item_bytes + 16) != cudaSuccess) { delete list; return bad("out of device memory"); }
-    list->d_items = static_cast<zk::GemvListItem*>(dev);
-    list->d_counter = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(dev) + item_bytes);
-    if (cudaMemcpy(list->d_items, host.data(), item_bytes, cudaMemcpyHostToDevice) != cudaSuccess || cudaMemset(list->d_counter, 0, 16) != cudaSuccess) {
-        cudaFree(dev);
+    if (cudaMalloc(&dev, 16) != cudaSuccess || cudaMemset(dev, 0, 16) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+        if (dev) cudaFree(dev);
         delete list;
-        return bad("copying the items failed");
+        return bad("out of device memory");
     }
-    list->nitems = static_cast<uint32_t>(count);
+    list->d_counter = static_cast<unsigned int*>(dev);
+    list->items = std::move(host);
     list->kpad_blocks = kpad;
     list->digits = digits;
     list->smem = smem;
@@ -1257,7 +1282,7 @@ void zen_cuda_gemv_list_destroy(zen_cuda_gemv_list* list) {
     State& s = state();
     std::lock_guard<std::mutex> lock(s.mutex);
     if (!list) return;
-    if (s.ready) { cudaDeviceSynchronize(); cudaFree(list->d_items); }
+    if (s.ready) { cudaDeviceSynchronize(); cudaFree(list->d_counter); }
     delete list;
 }
 
@@ -1268,18 +1293,16 @@ int zen_cuda_dev_gemv_list(const zen_cuda_gemv_list* list, void* stream) {
     std::lock_guard<std::mutex> lock(s.mutex);
     if (!init_locked(s)) return 0;
     if (!list) return set_error(s, "dev_gemv_list: bad arguments") ? 1 : 0;
-    zk::GemvListParams p{};
-    p.items = list->d_items;
-    p.nitems = list->nitems;
-    p.kpad_blocks = list->kpad_blocks;
-    p.counter = list->d_counter;
-    p.error_word = s.d_error;
     cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : s.stream;
-    // one CTA per SM, all resident at once: the items' dependency waits need every CTA to make progress
-    const unsigned grid = static_cast<unsigned>(s.sm_count);
-    const cudaError_t e = list->digits == 2 ? launch_gemv_list<2>(p, grid, list->smem, st, s.pdl) : launch_gemv_list<1>(p, grid, list->smem, st, s.pdl);
-    if (e != cudaSuccess) return set_error(s, std::string("dev_gemv_list launch: ") + cudaGetErrorString(e)) ? 1 : 0;
-    ++s.stats.dispatches;
+    // The items travel as kernel parameters: a long list goes out in pieces of zk::kListMaxItems, which stream order
+    // chains (a piece's first item then waits for the whole piece before it, as any launch does).
+    for (size_t first = 0; first < list->items.size(); first += zk::kListMaxItems) {
+        const size_t n = std::min<size_t>(zk::kListMaxItems, list->items.size() - first);
+        const cudaError_t e = n <= static_cast<size_t>(zk::kListFewItems) ? launch_list_piece<zk::kListFewItems>(s, *list, first, n, st)
+                                                                          : launch_list_piece<zk::kListMaxItems>(s, *list, first, n, st);
+        if (e != cudaSuccess) return set_error(s, std::string("dev_gemv_list launch: ") + cudaGetErrorString(e)) ? 1 : 0;
+        ++s.stats.dispatches;
+    }
     return 1;
 }
 
