@@ -5,9 +5,15 @@
 
 Workload ``q8_0_gemv`` (default) is the decode GEMV of the first benchmark configuration: W 4096 x 4096
 (seed 0, N(0, 0.02), packed to Q8_0), x fp32[4096] (seed 1), batch 1.  One such matrix is 17.8 MB and
-would sit in the 126 MB L2, so a step sweeps COPIES distinct weight copies (same values, different
-addresses, 570 MB in all): every launch streams its weights from HBM.  A step is one pass over all
-copies with one launch per copy, replayed from a CUDA graph.
+would sit in the 126 MB L2, so a pass sweeps COPIES distinct weight copies (same values, different
+addresses, 570 MB in all): every launch streams its weights from HBM.  The 32 products of a pass are
+submitted eight at a time, the reference's own batched form (zen::quant::gemv_batch, src/quant.cpp:1441-1502:
+up to kMaxBatch = 8 matvecs sharing one input per submission; zen_cuda_dev_gemv / zen_cuda_gemv_q8_0_batch
+here), on both arms.  A step is PASSES_PER_STEP passes, replayed from a CUDA graph (28 ms, so that a clock
+sampler sees the timed region).  The line's ``detail`` object carries the same products launched one at a
+time and as one list launch, and the other terms of the headline metric, each measured by the workload of
+the same name in a short form: the prefill GEMM (``q8_0_gemm``), the lm_head (``lm_head``) and the greedy
+decode (``decode``), the last two on all N GPUs.
 
   value      whole-job GB/s, algorithmic bytes (34 B per 32-weight block + x + y) / device time, inputs
              resident in HBM, CUDA events on the launching stream, max over ranks.
@@ -45,14 +51,17 @@ sys.path.insert(0, ROOT)
 
 ROWS, COLS = 4096, 4096
 COPIES = 32
+GROUP = 8                 # products per submission: zen::quant::gemv_batch, up to kMaxBatch = 8 tensors sharing one input
+PASSES_PER_STEP = 300     # a step of the default workload: 300 passes over the 32 copies, about 28 ms
 BLOCK_BYTES, BLOCK_ELEMS = 34, 32
-ALGO_BYTES_PER_LAUNCH = ROWS * (COLS // BLOCK_ELEMS) * BLOCK_BYTES + COLS * 4 + ROWS * 4  # 17,858,560
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu capture of this same
-# workload (the summaries under profiles/ give the command): the decode kernel reads every byte once and writes
-# nothing back (y stays in L2); the prefill kernel moves 85.8 MB + 16.3 MB against 94.2 MB algorithmic.
+ALGO_BYTES_PER_LAUNCH = ROWS * (COLS // BLOCK_ELEMS) * BLOCK_BYTES + COLS * 4 + ROWS * 4  # 17,858,560: one product launched alone
+ALGO_BYTES_PER_GROUP = GROUP * (ROWS * (COLS // BLOCK_ELEMS) * BLOCK_BYTES + ROWS * 4) + COLS * 4  # 142,753,792: eight products sharing one read of x
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from an ncu capture of this workload;
+# None where no capture of the current kernel has been taken.
 GEMV_NCU_TRAFFIC_BYTES = 17_867_776
-GEMM_NCU_TRAFFIC_BYTES = 102_143_488
-WORKLOAD = "Q8_0 decode GEMV batch 1, W 4096x4096 (config 0), %d rotating weight copies" % COPIES
+GEMM_NCU_TRAFFIC_BYTES = None
+WORKLOAD = ("Q8_0 decode GEMV batch 1, W 4096x4096 (config 0), %d rotating weight copies, submitted %d products at a time "
+            "(zen::quant::gemv_batch: tensors sharing one input)" % (COPIES, GROUP))
 
 
 def peaks() -> tuple[float, str]:
@@ -121,6 +130,13 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm), "scope": scope}
 
 
+def config0() -> dict:
+    """The `config` object of the default workload, the same for the GPU arm and the reference arm."""
+    return {"workload": WORKLOAD, "rows_per_gpu": ROWS, "columns": COLS, "batch": 1, "activations": "int8 (bit-exact reference codes)",
+            "generator": "numpy.random.default_rng(seed).standard_normal(float32): W seed 0 x 0.02 packed to Q8_0, x seed 1",
+            "l2": "inputs larger than the last-level cache: rotating weight copies, every product streams its weights from memory"}
+
+
 def make_inputs():
     from zeninfer_b200 import blocks
     w = np.random.default_rng(0).standard_normal((ROWS, COLS), dtype=np.float32) * np.float32(0.02)
@@ -159,29 +175,32 @@ class CpuReference:
         self.x, self.copies = x, copies
         self.kind = "reference" if oracle.reference_available() else "port"
         self.ws = [packed.copy() for _ in range(copies)]  # distinct addresses: the CPU caches do not hold them all
+        self.groups = [self.ws[g:g + GROUP] for g in range(0, copies, GROUP)]
+        outs = [np.empty(ROWS, np.float32) for _ in range(GROUP)]
         if self.kind == "reference":
             zr = oracle.Reference()
             self.cores = min(zr.pool_workers(), os.cpu_count() or 1)
-            self.run = lambda w: zr.gemv(oracle.Q8_0, w, x, ROWS, COLS, workers=0)  # workers=0: the reference's own policy
-            self.run_with = lambda w, n: zr.gemv(oracle.Q8_0, w, x, ROWS, COLS, workers=n)
+            # one submission = GROUP products sharing x (zen::quant::gemv_batch); workers=0: the reference's own policy
+            self.run = lambda ws: zr.gemv_batch(oracle.Q8_0, ws, x, [ROWS] * len(ws), COLS, workers=0, outs=outs)
+            self.run_with = lambda ws, n: zr.gemv_batch(oracle.Q8_0, ws, x, [ROWS] * len(ws), COLS, workers=n, outs=outs)
         else:
             zo = oracle.Oracle()
             self.cores = 1
-            self.run = lambda w: zo.gemv(oracle.Q8_0, w, x, ROWS, COLS, int8_acts=True)
+            self.run = lambda ws: [zo.gemv(oracle.Q8_0, w, x, ROWS, COLS, int8_acts=True) for w in ws]
             self.run_with = None
-        self.run(self.ws[0])
+        self.run(self.groups[0])
 
     def sample(self, budget_s: float) -> dict:
         t0 = time.perf_counter()
         n = 0
         while True:
-            self.run(self.ws[n % self.copies])
+            self.run(self.groups[n % len(self.groups)])
             n += 1
             if time.perf_counter() - t0 > budget_s:
                 break
         dt = time.perf_counter() - t0
-        return {"value": ALGO_BYTES_PER_LAUNCH * n / dt / 1e9, "unit": "GB/s", "cores": self.cores, "kind": self.kind,
-                "sample": f"{n} GEMV calls over {self.copies} weight copies in {dt:.2f} s, int8 activations (ZEN_CPU_Q8_ACT=1), reference worker policy",
+        return {"value": ALGO_BYTES_PER_GROUP * n / dt / 1e9, "unit": "GB/s", "cores": self.cores, "kind": self.kind,
+                "sample": f"{n} gemv_batch submissions of {GROUP} products over {self.copies} weight copies in {dt:.2f} s, int8 activations (ZEN_CPU_Q8_ACT=1), reference worker policy",
                 "workers": "0 (the reference's planner default; its pool is capped at 32 threads)", **cpu_description()}
 
     def worker_sweep(self, budget_each_s: float) -> dict:
@@ -192,12 +211,12 @@ class CpuReference:
         counts = sorted({1, desc["physical_cores"] or 1, min(32, desc["logical_cpus"] or 1)})
         out = {}
         for workers in counts:
-            self.run_with(self.ws[0], workers)
+            self.run_with(self.groups[0], workers)
             t0, n = time.perf_counter(), 0
             while n == 0 or time.perf_counter() - t0 < budget_each_s:
-                self.run_with(self.ws[n % self.copies], workers)
+                self.run_with(self.groups[n % len(self.groups)], workers)
                 n += 1
-            out[str(workers)] = ALGO_BYTES_PER_LAUNCH * n / (time.perf_counter() - t0) / 1e9
+            out[str(workers)] = ALGO_BYTES_PER_GROUP * n / (time.perf_counter() - t0) / 1e9
         return out
 
 
@@ -213,7 +232,7 @@ def run_reference_arm(args) -> None:
     if rank != 0:
         return
     packed, x = make_inputs()
-    ref = CpuReference(packed, x, 8)
+    ref = CpuReference(packed, x, 16)
     # a step is a bounded sample of the workload; the whole run is sized to about a minute
     per_step_budget = max(0.02, min(20.0, 60.0 / max(1, args.steps + args.warmup)))
     leg = None
@@ -226,12 +245,12 @@ def run_reference_arm(args) -> None:
     elapsed = time.perf_counter() - t0
     value = statistics.mean(vals)
     leg["value"] = value
-    leg["sample"] = f"{args.steps} steps of {per_step_budget:.2f} s each over 8 weight copies, int8 activations (ZEN_CPU_Q8_ACT=1), reference worker policy"
+    leg["sample"] = f"{args.steps} steps of {per_step_budget:.2f} s each, gemv_batch submissions of {GROUP} products over 16 weight copies, int8 activations (ZEN_CPU_Q8_ACT=1), reference worker policy"
     print(json.dumps({
         "impl": "reference", "metric": "q8_0_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed * 1e3 / max(1, args.steps),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "inputs larger than the CPU caches (8 weight copies)"},
+        "config": config0(), "notes": "16 rotating weight copies (285 MB, larger than the CPU caches), two submissions of eight per pass",
         "cpu_baseline": leg, "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -250,16 +269,17 @@ def int8_peak_tops() -> tuple[float, str]:
         return 2.0 * 1590.0, "2 x fallback bf16"
 
 
-def run_gemm_workload(args) -> None:
+def run_gemm_workload(args, brief: bool = False) -> dict:
     """Q8_0 prefill GEMM, Llama-3-8B FFN-up shape: activations fp32 512x4096 (seed 2), W 14336x4096 Q8_0 (seed 3),
     out fp32 512x14336.  A step is one product (activation quantise + tcgen05 GEMM) on the next of GEMM_COPIES weight
     copies with its own output buffer (4 x 100 MB, larger than L2)."""
     import torch
     from zeninfer_b200 import Backend, blocks
-    if int(os.environ.get("WORLD_SIZE", "1")) != 1 or args.gpus != 1:
+    if not brief and (int(os.environ.get("WORLD_SIZE", "1")) != 1 or args.gpus != 1):
         raise SystemExit("workload q8_0_gemm is a single-GPU workload")
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(0)
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(local)
     be = Backend()
     w = np.random.default_rng(3).standard_normal((GEMM_ROWS, GEMM_COLS), dtype=np.float32) * np.float32(0.02)
     packed = np.ascontiguousarray(blocks.quantize_q8_0(w))
@@ -276,14 +296,14 @@ def run_gemm_workload(args) -> None:
         for h, o in zip(handles, outs):
             be.dev_gemm_q8_0([h], [o.data_ptr()], d_x.data_ptr(), GEMM_T, ws.data_ptr(), ws_bytes, stream.cuda_stream)
 
-    steps = max(1, args.steps // GEMM_COPIES)  # a graph replay is GEMM_COPIES steps
+    steps = 250 if brief else max(1, args.steps // GEMM_COPIES)  # a graph replay is GEMM_COPIES steps
     with torch.cuda.stream(stream):
         one_pass()
         stream.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             one_pass()
-        with ClockSampler(0) as clocks:
+        with ClockSampler(local) as clocks:
             t_warm, n_warm = time.time(), 0
             while n_warm * GEMM_COPIES < args.warmup or time.time() - t_warm < 0.3:
                 graph.replay(); n_warm += 1
@@ -308,7 +328,7 @@ def run_gemm_workload(args) -> None:
     copies = [packed] + [packed.copy() for _ in range(GEMM_COPIES - 1)]
     for c in copies:
         y_host = be.gemm("Q8_0", c, x_host, GEMM_T, GEMM_ROWS, GEMM_COLS)
-    e2e_steps = 3
+    e2e_steps = 1 if brief else 3
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         for c in copies:
@@ -317,8 +337,12 @@ def run_gemm_workload(args) -> None:
     e2e_value = GEMM_OPS * e2e_steps * GEMM_COPIES / e2e_s / 1e12
     assert np.array_equal(y_host, outs[-1].cpu().numpy()), "host-pointer and device-pointer paths disagree"
 
+    for c in copies:
+        be.release_weights(c)
+    for h in handles:
+        be.dev_free(h)
     cpu = None
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and not brief:
         import oracle
         if oracle.reference_available():
             zr = oracle.Reference()
@@ -335,7 +359,7 @@ def run_gemm_workload(args) -> None:
         cpu = {**cpu_description(), "value": GEMM_OPS * frac * n / dt / 1e12, "unit": "TOPS", "cores": cores, "kind": kind,
                "sample": f"{n} full products in {dt:.1f} s, the reference's default fp32-activation K-blocked kernel (it has no int8 GEMM), its own worker policy"}
 
-    print(json.dumps({
+    return ({
         "metric": "q8_0_prefill_gemm_int8_tops", "value": value, "unit": "TOPS", "n_gpus": 1, "steps": n_products, "warmup": args.warmup,
         "ms_per_step": per_product_us / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": "Q8_0 prefill GEMM 512 x 14336 x 4096 (config 1): activation quantise + tcgen05 kind::i8 GEMM per step",
@@ -347,7 +371,7 @@ def run_gemm_workload(args) -> None:
         "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": GEMM_T * GEMM_COLS * 4, "d2h_bytes_per_step": GEMM_T * GEMM_ROWS * 4,
                 "api": "zen_cuda_gemm_q8_0 (host pointers)", "steps": e2e_steps * GEMM_COPIES},
         "gpu_launches": 2 * n_products,
-    }))
+    })
 
 
 # ---- workload layer_sweep: mixed-format decode GEMV sweep over one Llama-3-8B layer (third benchmark configuration) ----
@@ -364,7 +388,7 @@ def tensor_bytes(fmt: str, rows: int, cols: int) -> int:
     return rows * (cols // elems) * nbytes
 
 
-def run_layer_sweep(args) -> None:
+def run_layer_sweep(args) -> dict:
     """All seven projections of one layer (weights N(0, 0.02), inputs N(0, 1), one generator seeded 4) in Q4_0, Q8_0 and
     Q6_K, batch 1.  Every launch kind is timed on its own over enough rotating weight copies to exceed L2, and the
     whole layer (four launches) is timed as a sequence over rotating layer copies.  value = the Q8_0 layer."""
@@ -497,7 +521,7 @@ def run_layer_sweep(args) -> None:
                "sample": f"{n} passes over the seven Q8_0 projections of the layer in {dt:.1f} s, one call per projection, int8 activations"}
 
     dom = q8["gate_up"]
-    print(json.dumps({
+    return ({
         "metric": "layer_decode_gemv_hbm_gbs", "value": q8["layer"]["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": max(3, args.warmup),
         "ms_per_step": q8["layer"]["us"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": "decode GEMV sweep over one Llama-3-8B layer, batch 1, Q8_0 / Q4_0 / Q6_K (config 2); value = the Q8_0 layer, "
@@ -511,19 +535,59 @@ def run_layer_sweep(args) -> None:
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * (3 * 4096 + 14336), "d2h_bytes_per_step": 4 * sum(r for _, r, _ in LAYER_TENSORS),
                 "api": "zen_cuda_gemv_q8_0_batch + zen_cuda_gemv_q8_0 (host pointers)", "steps": e2e_steps},
         "gpu_launches": launches_total,
-    }))
+    })
 
 
 # ---- workload lm_head: row-sharded Q6_K lm_head, fused all-gather of the logits, greedy pick (fourth configuration) ----
 LM_ROWS, LM_COLS = 128256, 4096
 
 
-def lm_head_shard(first: int, last: int) -> np.ndarray:
-    """Rows [first, last) of W 128256 x 4096 ~ N(0, 0.02) from the generator seeded 5, packed to Q6_K.  The stream is
-    drawn in row chunks from the start so that every rank sees the same matrix; only the own rows are packed."""
+def torch_q6_k_pack(w):
+    """fp32 [rows, K] on the GPU -> uint8 [rows, K/256*210] raw GGUF Q6_K super-blocks: zeninfer_b200.blocks.quantize_q6_k
+    (a plain valid encoder: group scale amax/31, super-block d maps the largest group scale to 127, codes
+    round(x / (d*sc)) + 32) and pack_q6_k restated on torch, because packing half a billion weights with numpy takes a
+    minute of box time.  Benchmark input preparation only."""
+    import torch
+    rows, k = w.shape
+    n = rows * (k // 256)
+    grp = w.reshape(n, 16, 16)
+    gscale = grp.abs().amax(dim=2) / 31.0
+    d = (gscale.amax(dim=1) / 127.0).to(torch.float16)
+    d32 = d.to(torch.float32)
+    sc = torch.where(d32[:, None] > 0, torch.round(gscale / d32[:, None].clamp_min(1e-30)), torch.zeros_like(gscale)).clamp_(1, 127)
+    eff = d32[:, None] * sc
+    q = torch.where(eff[..., None] > 0, torch.round(grp / eff[..., None].clamp_min(1e-30)), torch.zeros_like(grp))
+    q = (q.clamp_(-32, 31) + 32).to(torch.uint8).reshape(n, 2, 4, 32)
+    out = torch.zeros((n, 210), dtype=torch.uint8, device=w.device)
+    ql, qh = out[:, :128].view(n, 2, 2, 32), out[:, 128:192].view(n, 2, 32)
+    ql[:, :, 0, :] = (q[:, :, 0, :] & 15) | ((q[:, :, 2, :] & 15) << 4)
+    ql[:, :, 1, :] = (q[:, :, 1, :] & 15) | ((q[:, :, 3, :] & 15) << 4)
+    qh[:] = (q[:, :, 0, :] >> 4) | ((q[:, :, 1, :] >> 4) << 2) | ((q[:, :, 2, :] >> 4) << 4) | ((q[:, :, 3, :] >> 4) << 6)
+    out[:, 192:208] = sc.to(torch.int8).view(torch.uint8)
+    out[:, 208:210] = d.view(torch.uint8).view(n, 2)
+    return out.view(rows, -1)
+
+
+def lm_head_shard(first: int, last: int, dev=None) -> np.ndarray:
+    """Rows [first, last) of W 128256 x 4096 ~ N(0, 0.02), packed to Q6_K.  With `dev` the rows are drawn and packed
+    on the GPU (torch generator seeded 5, one draw per 8016-row chunk from the start, so every rank sees the same
+    matrix); without it, numpy's generator seeded 5 and the numpy packer.  Only the own rows are packed."""
+    out, chunk = [], 8016
+    if dev is not None:
+        import torch
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(5)
+        for r0 in range(0, LM_ROWS, chunk):
+            r1 = min(LM_ROWS, r0 + chunk)
+            if r0 >= last:
+                break
+            w = torch.randn((r1 - r0, LM_COLS), generator=gen, device=dev, dtype=torch.float32)
+            a, b = max(first, r0), min(last, r1)
+            if a < b:
+                out.append(torch_q6_k_pack(w[a - r0:b - r0] * 0.02).cpu().numpy())
+        return np.ascontiguousarray(np.concatenate(out, axis=0))
     from zeninfer_b200 import blocks
     rng = np.random.default_rng(5)
-    out, chunk = [], 8016
     for r0 in range(0, LM_ROWS, chunk):
         r1 = min(LM_ROWS, r0 + chunk)
         if r0 >= last:
@@ -535,7 +599,7 @@ def lm_head_shard(first: int, last: int) -> np.ndarray:
     return np.ascontiguousarray(np.concatenate(out, axis=0))
 
 
-def run_lm_head(args) -> None:
+def run_lm_head(args, brief: bool = False) -> dict | None:
     """Q6_K lm_head 128256 x 4096 at batch 1 (value) and batch 8, rows sharded over the ranks.  A step on every rank: the
     shard product with the all-gather fused in (or followed by an NCCL all-gather), then the greedy pick over the
     gathered logits.  Total work is fixed as N grows: strong scaling."""
@@ -551,13 +615,13 @@ def run_lm_head(args) -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
     be = Backend()
     plan = shard.shard_plan(LM_ROWS, world)
     first, last = plan[rank]
     my_rows, widest = last - first, max(b - a for a, b in plan)
-    packed = lm_head_shard(first, last)
+    packed = lm_head_shard(first, last, dev if (brief or args.device_pack) else None)
     shard_bytes = tensor_bytes("Q6_K", my_rows, LM_COLS)
     ncopy = int(SWEEP_MIN_BYTES // shard_bytes) + 1
     handles = [be.dev_upload("Q6_K", packed, my_rows, LM_COLS) for _ in range(ncopy)]
@@ -600,7 +664,7 @@ def run_lm_head(args) -> None:
                     graph.replay()
                 stream.synchronize()
                 be.dev_check(stream.cuda_stream)
-                replays = max(1, args.steps // ncopy)
+                replays = (200 if brief else max(1, args.steps // ncopy))
                 if world > 1:
                     dist.barrier()
                 torch.cuda.synchronize()
@@ -640,12 +704,8 @@ def run_lm_head(args) -> None:
                 stream.synchronize()
                 pg.close()
 
-    def leave():
-        if world > 1:
-            sys.stdout.flush()
-            torch.cuda.synchronize()
-            dist.barrier()
-            os._exit(0)
+    for h in handles:
+        be.dev_free(h)
 
     # e2e (single GPU): the host-pointer Q6_K call, hidden state host->device and all logits device->host per step
     e2e = None
@@ -657,11 +717,11 @@ def run_lm_head(args) -> None:
         e2e_s = time.perf_counter() - t0
         e2e = {"value": results[1]["algorithmic_bytes"] * e2e_steps / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 4 * LM_COLS,
                "d2h_bytes_per_step": 4 * LM_ROWS, "api": "zen_cuda_gemm_q6_k (host pointers, tokens = 1)", "steps": e2e_steps}
+        be.release_weights(packed)
     if rank != 0:
-        leave()
-        return
+        return None
     cpu = None
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not brief:
         import oracle
         if oracle.reference_available():
             zr = oracle.Reference()
@@ -678,7 +738,7 @@ def run_lm_head(args) -> None:
                "sample": f"{n} full lm_head products (batch 1) in {dt:.1f} s, the reference's Q6_K kernel, its own worker policy"}
     r1 = results[1]
     per_gpu = r1["gbs"] / world
-    print(json.dumps({
+    return ({
         "metric": "lm_head_q6_k_hbm_gbs", "value": r1["gbs"], "unit": "GB/s", "n_gpus": world, "steps": r1["steps"], "warmup": max(3, args.warmup),
         "ms_per_step": r1["us_per_step"] / 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": "Q6_K lm_head 128256 x 4096 (config 3), batch 1 (value) and batch 8, rows sharded over the GPUs, logits all-gathered, greedy pick",
@@ -689,8 +749,7 @@ def run_lm_head(args) -> None:
                      "algorithmic_bytes_per_launch": r1["algorithmic_bytes"] // world},
         "detail": {"batch1": r1, "batch8": results[8]}, "cpu_baseline": cpu, "clocks": clocks.summary(), "e2e": e2e,
         "gpu_launches": sum(r["steps"] for r in results.values()) * (4 if fused else 3),
-    }))
-    leave()
+    })
 
 
 # ---- workload decode: full greedy decode of a random-init Llama-3-8B-shaped Q8_0 model (fifth configuration) ----------
@@ -712,11 +771,12 @@ def torch_q8_0_pack(w):
     return out.view(rows, -1)
 
 
-def run_decode(args) -> None:
+def run_decode(args, brief: bool = False) -> dict | None:
     """Config: 32 layers, d 4096, 32 query / 8 KV heads of 128, SwiGLU 14336, vocab 128256, eps 1e-5, theta 500000,
-    weights N(0, 0.02) seed 6, a prompt of 512 uniform-random ids (consumed as tensor-core blocks, timed separately), then greedy decode steps.  A step is one decoded
-    token: 165 launches replayed from two CUDA graphs (norms, SwiGLU and residual adds are folded into the projections).  The prompt is consumed token by token through the same step
-    and is not timed."""
+    weights N(0, 0.02) seed 6, a prompt of 512 uniform-random ids, then greedy decode steps.  On one GPU the prompt is
+    consumed as blocks of tensor-core products and timed separately (prefill_ms); a sharded decoder takes it token by
+    token.  A step is one decoded token: the launches of 32 layers, the lm_head and the pick, replayed from two CUDA
+    graphs (RMSNorm and the residual adds are folded into the projection launches)."""
     import torch
     from zeninfer_b200 import Backend
     from zeninfer_b200.backend import ACT_INT8
@@ -729,12 +789,12 @@ def run_decode(args) -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
     dev = torch.device("cuda", local)
     torch.cuda.set_device(local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
     be = Backend()
     cfg = LlamaConfig()
     prompt_len = args.prompt_len
-    steps = args.steps if args.steps != 2000 else 125      # the default run: 3 warm-up + 125 timed = the 128 greedy steps
+    steps = 125 if (brief or args.steps == DEFAULT_STEPS) else args.steps      # the default run: 3 warm-up + 125 timed = the 128 greedy steps
     warm = max(3, args.warmup)
 
     def tensors():
@@ -820,13 +880,10 @@ def run_decode(args) -> None:
         e2e_tok_s = float(t.item())
     if rank != 0:
         dec.close()
-        sys.stdout.flush()
-        torch.cuda.synchronize()
-        dist.barrier()
-        os._exit(0)
+        return None
 
     cpu = None
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and not brief:
         import oracle
         from zeninfer_b200 import blocks
         os.environ.setdefault("ZEN_CPU_Q8_ACT", "1")
@@ -854,7 +911,7 @@ def run_decode(args) -> None:
     per_layer = 5 + (0 if (fn and fr) else 2) + (0 if fs else 1)   # q|k|v, attention block, o, gate|up, down + norm / residual / SwiGLU launches
     launches_per_step = 1 + (0 if fn else 1) + per_layer * cfg.layers + 1 + 1 + 2   # embed, layers, advance, lm_head, pick (2): per rank
     gathers = ((2 if dec.col_cut else 4) * cfg.layers + 1) if world > 1 else 0
-    print(json.dumps({
+    line = ({
         "metric": "decode_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
         "higher_is_better": True, "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {"workload": "greedy decode, random-init Llama-3-8B shape in Q8_0 (config 4): 32 layers, d 4096, 32/8 heads of 128, ffn 14336, "
@@ -876,55 +933,33 @@ def run_decode(args) -> None:
                 "api": "LlamaDecoder.generate: each picked token id is read back to the host, and fed to the next step from pinned host memory, "
                        "as the reference's generate loop does", "steps": e2e_new - 1},
         "gpu_launches": steps * (launches_per_step + (gathers if dec.peer is not None else 0)) * world,
-    }))
+    })
     dec.close()
-    if world > 1:
-        sys.stdout.flush()
-        torch.cuda.synchronize()
-        dist.barrier()
-        os._exit(0)
+    return line
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200")
-    ap.add_argument("--workload", default="q8_0_gemv")
-    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU time for the cpu_baseline leg")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cut", default="rows+cols", choices=["rows", "rows+cols"],
-                    help="workload decode, N > 1: every matrix by output rows (four gathers per layer), or o and down by columns "
-                         "(two all-reduces per layer)")
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
-                    help="N > 1: how the output shards are all-gathered after each product -- by the product kernel itself "
-                         "(peer stores over NVLink, the default) or by an NCCL all-gather launched after it")
-    ap.add_argument("--fuse", default="nr", help="workload decode: operators folded into the projection launches (letters n, s, r; see LlamaDecoder)")
-    ap.add_argument("--token-prefill", action="store_true", help="workload decode: consume the prompt token by token instead of in tensor-core blocks")
-    ap.add_argument("--prompt-len", type=int, default=512, help="workload decode: prompt tokens consumed before the timed steps")
-    ap.add_argument("--min-warmup", type=int, default=1500,
-                    help="floor on the warm-up step count of the decode workload (about 0.3 s, so the clock sampler is up before "
-                         "the timed region); a profiler run lowers it so that few launches precede the captured ones")
-    args = ap.parse_args()
-    args.warmup = max(3, args.warmup) if args.impl != "reference" else args.warmup
+DEFAULT_STEPS = 20
 
-    if args.workload == "q8_0_gemm" and args.impl != "reference":
-        run_gemm_workload(args)
-        return
-    if args.workload == "layer_sweep" and args.impl != "reference":
-        run_layer_sweep(args)
-        return
-    if args.workload == "lm_head" and args.impl != "reference":
-        run_lm_head(args)
-        return
-    if args.workload == "decode" and args.impl != "reference":
-        run_decode(args)
-        return
-    if args.impl == "reference":
-        run_reference_arm(args)
-        return
 
+def brief_detail(line: dict | None, keep: tuple[str, ...]) -> dict | None:
+    """The figures of a workload's line that the default line's `detail` carries."""
+    if line is None:
+        return None
+    out = {k: line[k] for k in ("metric", "value", "unit", "n_gpus", "ms_per_step", "scaling") if k in line}
+    out["frac_of_peak"] = line["roofline"]["frac"]
+    out["peak"] = {"value": line["roofline"]["peak"], "unit": line["roofline"]["unit"], "kind": line["roofline"]["peak_kind"]}
+    out["workload"] = line["config"]["workload"]
+    for k in keep:
+        if k in line["config"]:
+            out[k] = line["config"][k]
+    if line.get("detail"):
+        out["detail"] = line["detail"]
+    out["e2e"] = line.get("e2e")
+    out["clocks"] = line.get("clocks")
+    return out
+
+
+def run_gemv_workload(args) -> dict | None:
     import torch
     import torch.distributed as dist
     from zeninfer_b200 import Backend
@@ -937,151 +972,251 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
 
     be = Backend()  # raises if the CUDA library or a B200 is missing: there is no fallback
     packed, x_host = make_inputs()
 
-    # --- resident inputs: COPIES weight shards on this rank, x and y in HBM ---
+    # --- resident inputs: COPIES weight shards on this rank, x and the outputs in HBM ---
     handles = [be.dev_upload("Q8_0", packed, ROWS, COLS) for _ in range(COPIES)]
+    groups = [handles[g:g + GROUP] for g in range(0, COPIES, GROUP)]
     d_x = torch.from_numpy(x_host).to(dev)
-    d_y = torch.zeros(ROWS, dtype=torch.float32, device=dev)
-    d_all = torch.zeros(ROWS * world, dtype=torch.float32, device=dev) if world > 1 else None
+    ys = torch.zeros((COPIES, ROWS), dtype=torch.float32, device=dev)
+    y_ptrs = [ys[i].data_ptr() for i in range(COPIES)]
+    d_all = torch.zeros((world, GROUP * ROWS), dtype=torch.float32, device=dev) if world > 1 else None
     stream = torch.cuda.Stream(device=dev)
     fused = world > 1 and args.gather == "fused"
     pg = None
     if fused:
         from zeninfer_b200.shard import PeerGather
-        pg = PeerGather(be, world, rank, ROWS)  # collective: IPC handles travel through torch.distributed, once
+        pg = PeerGather(be, world, rank, GROUP * ROWS)  # collective: IPC handles travel through torch.distributed, once
 
     def one_pass():
-        for i, h in enumerate(handles):
+        for g, hs in enumerate(groups):
+            outs = y_ptrs[g * GROUP:(g + 1) * GROUP]
             if fused:   # the product kernel stores its outputs into every rank's gather region and publishes the launch;
                         # the next launch waits on the device until all ranks have published: no collective launch
-                pg.gemv([h], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream, d_y=[d_y.data_ptr()])
+                pg.gemv(hs, d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream, d_y=outs)
                 continue
-            if world == 1:   # the launch also asks L2 for the start of the tensor the next launch reads (a hint, no result changes)
-                be.dev_gemv_fused([h], [d_y.data_ptr()], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream, warm_next=handles[(i + 1) % COPIES])
-                continue
-            be.dev_gemv([h], [d_y.data_ptr()], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream)
-            dist.all_gather_into_tensor(d_all, d_y)
+            be.dev_gemv(hs, outs, d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream)
+            if world > 1:
+                dist.all_gather_into_tensor(d_all.view(-1), ys[g * GROUP:(g + 1) * GROUP].reshape(-1))
 
-    with torch.cuda.stream(stream):
-        one_pass()  # first launch sets function attributes; keep it out of the capture
-        stream.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            one_pass()
-        with ClockSampler(local) as clocks:
-            # At least W steps, and enough of them (about 0.3 s) for the clock sampler to come up.  The count is fixed,
-            # never time-based: every rank must replay the same number of collectives.
-            for n_warm in range(max(args.warmup, args.min_warmup)):
+    def time_passes(enqueue, steps, warm_steps, clocks=None):
+        """Captures one pass, replays it PASSES_PER_STEP times per step; returns the milliseconds of `steps` timed steps (max
+        over ranks).  The replay counts are fixed, never time-based: every rank replays the same number of collectives."""
+        with torch.cuda.stream(stream):
+            enqueue()  # first launch sets function attributes; keep it out of the capture
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                enqueue()
+            for n in range(warm_steps * PASSES_PER_STEP):
                 graph.replay()
-                if n_warm % 64 == 63:
+                if n % 64 == 63:
                     stream.synchronize()
             stream.synchronize()
             be.dev_check(stream.cuda_stream)
-
-            # --- timed region: K graph replays, CUDA events on the launching stream ---
             if world > 1:
                 dist.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            clocks.mark_start()
+            if clocks:
+                clocks.mark_start()
             e0.record(stream)
-            for _ in range(args.steps):
+            for _ in range(steps * PASSES_PER_STEP):
                 graph.replay()
             e1.record(stream)
             stream.synchronize()
-            clocks.mark_end()
-        torch.cuda.synchronize()
+            if clocks:
+                clocks.mark_end()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            ms = e0.elapsed_time(e1)
+        be.dev_check(stream.cuda_stream)
+        del graph
         if world > 1:
-            dist.barrier()
-        ms = e0.elapsed_time(e1)
-    be.dev_check(stream.cuda_stream)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
 
-    launches = args.steps * COPIES
-    total_bytes = ALGO_BYTES_PER_LAUNCH * launches * world
+    with ClockSampler(local) as clocks:
+        ms = time_passes(one_pass, args.steps, args.warmup, clocks)
+    launches = args.steps * PASSES_PER_STEP * len(groups)
+    total_bytes = ALGO_BYTES_PER_GROUP * launches * world
     value = total_bytes / (ms * 1e-3) / 1e9
     per_launch_us = ms * 1e3 / launches
-    achieved = ALGO_BYTES_PER_LAUNCH / (per_launch_us * 1e-6) / 1e9
+    achieved = ALGO_BYTES_PER_GROUP / (per_launch_us * 1e-6) / 1e9
     peak, peak_kind = peaks()
 
     # --- correctness of what was timed (not part of the timed region) ---
-    y_dev = d_y.cpu().numpy()
+    y_dev = ys[0].cpu().numpy()
+    assert bool((ys == ys[0][None, :]).all().item()), "the copies' products differ"
     if world > 1:
         if fused:
             pg.fetch(d_all.data_ptr(), stream.cuda_stream)
             stream.synchronize()
             be.dev_check(stream.cuda_stream)
-        # every rank holds the same weights and input here, so every gathered shard must equal the local product
-        assert bool((d_all.view(world, ROWS) == d_y[None, :]).all().item()), "gathered shards differ from the local product"
+        # every rank holds the same weights and input here, so every gathered shard must equal the local products
+        assert bool((d_all.view(world, GROUP, ROWS) == ys[None, -GROUP:, :]).all().item()), "gathered shards differ from the local products"
 
-    # --- e2e: the host-pointer call, host buffers, copies inside the timed region ---
+    # --- the same 32 products submitted differently (one GPU): one tensor per launch, and all of them as one list launch ---
+    variants = {"batch8": {"gbs": achieved, "us_per_product": per_launch_us / GROUP, "frac": achieved / peak, "launches_per_pass": len(groups),
+                           "api": "zen_cuda_dev_gemv, eight tensors sharing the input per launch (zen::quant::gemv_batch); this is `value`"}}
+    if world == 1:
+        short = max(3, args.steps // 4)
+        ys.zero_()
+
+        def single_pass():   # each launch also asks L2 for the start of the tensor the next launch reads (a hint, no result changes)
+            for i, h in enumerate(handles):
+                be.dev_gemv_fused([h], [y_ptrs[i]], d_x.data_ptr(), 1, ACT_INT8, stream.cuda_stream, warm_next=handles[(i + 1) % COPIES])
+
+        ms_s = time_passes(single_pass, short, 1)
+        assert bool((ys == torch.from_numpy(y_dev).to(dev)[None, :]).all().item()), "single launches differ from batched launches"
+        ys.zero_()
+        lst = be.gemv_list_create([dict(handles=[h], d_y=[y_ptrs[i]], d_x=d_x.data_ptr()) for i, h in enumerate(handles)], ACT_INT8)
+        ms_l = time_passes(lambda: be.dev_gemv_list(lst, stream.cuda_stream), short, 1)
+        assert bool((ys == torch.from_numpy(y_dev).to(dev)[None, :]).all().item()), "the list launch differs from batched launches"
+        be.gemv_list_destroy(lst)
+        for name, ms_v, lp, api in (("single_launch", ms_s, COPIES, "zen_cuda_dev_gemv_fused, one tensor per launch, next tensor hinted to L2"),
+                                    ("list", ms_l, 1, "zen_cuda_dev_gemv_list, all 32 products as items of one persistent launch")):
+            us = ms_v * 1e3 / (short * PASSES_PER_STEP * COPIES)
+            variants[name] = {"gbs": ALGO_BYTES_PER_LAUNCH / us / 1e3, "us_per_product": us, "frac": ALGO_BYTES_PER_LAUNCH / us / 1e3 / peak,
+                              "launches_per_pass": lp, "api": api}
+
+    # --- e2e: the host-pointer C-ABI call, host buffers, copies inside the timed region ---
+    from zeninfer_b200.backend import GemvTask
     e2e_copies = [packed.copy() for _ in range(COPIES)]  # distinct host addresses => distinct resident tensors
-    y_host = None
-    for w in e2e_copies:
-        y_host = be.gemv("Q8_0", w, x_host, ROWS, COLS)  # upload + warm
-    for _ in range(2):
-        for w in e2e_copies:
-            be.gemv("Q8_0", w, x_host, ROWS, COLS)
-    e2e_steps = max(3, min(args.steps, 20))
+    y_out = [np.empty(ROWS, np.float32) for _ in range(GROUP)]
+    task_groups = [(GemvTask * GROUP)(*[GemvTask(w.ctypes.data, y.ctypes.data, ROWS, COLS) for w, y in zip(e2e_copies[g:g + GROUP], y_out)])
+                   for g in range(0, COPIES, GROUP)]
+    call = be.lib.zen_cuda_gemv_q8_0_batch    # the entry point a ZenInfer build binds for gemv_batch: host pointers in, host pointers out
+    xp = x_host.ctypes.data
+    for _ in range(3):                         # upload, warm, capture
+        for tasks in task_groups:
+            if not call(xp, tasks, GROUP):
+                raise RuntimeError("zen_cuda_gemv_q8_0_batch failed: " + be.last_error())
+    y_single = be.gemv("Q8_0", e2e_copies[0], x_host, ROWS, COLS)
+    e2e_passes = max(30, min(args.steps * 15, 300))
     if world > 1:
         dist.barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        for w in e2e_copies:
-            be.gemv("Q8_0", w, x_host, ROWS, COLS)
+    for _ in range(e2e_passes):
+        for tasks in task_groups:
+            if not call(xp, tasks, GROUP):
+                raise RuntimeError("zen_cuda_gemv_q8_0_batch failed: " + be.last_error())
     e2e_s = time.perf_counter() - t0
+    # and one product per call (zen_cuda_gemv_q8_0), for the detail
+    single_call, wp0, yp0 = be.lib.zen_cuda_gemv_q8_0, [w.ctypes.data for w in e2e_copies], y_out[0].ctypes.data
+    for wp in wp0:
+        single_call(wp, xp, yp0, ROWS, COLS)
+    t1 = time.perf_counter()
+    for _ in range(max(10, e2e_passes // 4)):
+        for wp in wp0:
+            if not single_call(wp, xp, yp0, ROWS, COLS):
+                raise RuntimeError("zen_cuda_gemv_q8_0 failed: " + be.last_error())
+    single_us = (time.perf_counter() - t1) * 1e6 / (max(10, e2e_passes // 4) * COPIES)
     if world > 1:
         t = torch.tensor([e2e_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-    e2e_value = ALGO_BYTES_PER_LAUNCH * COPIES * e2e_steps * world / e2e_s / 1e9
-    assert np.array_equal(y_host, y_dev), "host-pointer and device-pointer paths disagree"
-
-    def leave():
-        """Multi-rank exit: meet once more, then leave without tearing NCCL down under a live CUDA graph (a
-        destroy_process_group here was seen to block for ever); all results are already out."""
-        if world > 1:
-            sys.stdout.flush()
-            torch.cuda.synchronize()
-            dist.barrier()
-            os._exit(0)
-
+    e2e_value = ALGO_BYTES_PER_GROUP * len(task_groups) * e2e_passes * world / e2e_s / 1e9
+    assert np.array_equal(y_single, y_dev) and all(np.array_equal(y, y_dev) for y in y_out), "host-pointer and device-pointer paths disagree"
+    variants["batch8"]["e2e_us_per_call"] = e2e_s * 1e6 / (e2e_passes * len(task_groups))
+    if "single_launch" in variants:
+        variants["single_launch"]["e2e_us_per_call"] = single_us
+        variants["single_launch"]["e2e_gbs"] = ALGO_BYTES_PER_LAUNCH / single_us / 1e3
+    for w in e2e_copies:
+        be.release_weights(w)
+    if pg is not None:
+        stream.synchronize()
+        pg.close()
+    for h in handles:
+        be.dev_free(h)
     if rank != 0:
-        leave()
-        return
+        return None
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_reference_leg(packed, x_host, args.cpu_budget, 8)
+        cpu = cpu_reference_leg(packed, x_host, args.cpu_budget, 16)
 
-    line = {
+    return {
         "metric": "q8_0_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8",
-        "data": "synthetic",
-        "config": {"workload": WORKLOAD, "rows_per_gpu": ROWS, "columns": COLS, "batch": 1, "activations": "int8 (bit-exact reference codes)",
-                   "generator": "numpy.random.default_rng(seed).standard_normal(float32): W seed 0 x 0.02 packed to Q8_0, x seed 1",
-                   "l2": f"inputs larger than L2: {COPIES} weight copies, {COPIES * ALGO_BYTES_PER_LAUNCH / 1e6:.0f} MB per pass",
-                   "launch": "CUDA graph replay, one kernel per copy" + (
-                       "; each launch hints the next launch's tensor to L2 (zen_cuda_gemv_fusion.warm_next)" if world == 1 else "; output shards all-gathered by the product kernel itself (peer stores over NVLink, device-side epoch flags)"
-                       if fused else "; NCCL all-gather of output shards after each")},
+        "data": "synthetic", "config": config0(),
+        "notes": f"a step is {PASSES_PER_STEP} passes over {COPIES} weight copies ({COPIES * ALGO_BYTES_PER_LAUNCH / 1e6:.0f} MB per pass), CUDA graph replay, "
+                 f"{len(groups)} launches of {GROUP} tensors per pass" + (
+            "" if world == 1 else
+            "; output shards all-gathered by the product kernel itself (peer stores over NVLink, device-side epoch flags)" if fused else "; NCCL all-gather of output shards after each launch"),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                     "traffic": GEMV_NCU_TRAFFIC_BYTES, "launch_us": per_launch_us, "algorithmic_bytes_per_launch": ALGO_BYTES_PER_LAUNCH},
+                     "traffic": None, "launch_us": per_launch_us, "algorithmic_bytes_per_launch": ALGO_BYTES_PER_GROUP,
+                     "kernel": f"gemv_q8_0_kernel<1,1>, {GROUP} tensors of 4096 x 4096 per launch; ncu traffic of one single-tensor launch: {GEMV_NCU_TRAFFIC_BYTES} B for {ALGO_BYTES_PER_LAUNCH} algorithmic"},
         "cpu_baseline": cpu,
         "clocks": clocks.summary(),
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": COLS * 4 * COPIES, "d2h_bytes_per_step": ROWS * 4 * COPIES,
-                "api": "zen_cuda_gemv_q8_0 (host pointers, weights resident by address)", "steps": e2e_steps},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": COLS * 4 * len(task_groups) * PASSES_PER_STEP, "d2h_bytes_per_step": ROWS * 4 * COPIES * PASSES_PER_STEP,
+                "api": "zen_cuda_gemv_q8_0_batch (host pointers, eight tensors per call, weights resident by address)", "calls": e2e_passes * len(task_groups),
+                "us_per_call": e2e_s * 1e6 / (e2e_passes * len(task_groups))},
         "gpu_launches": launches,
+        "detail": {"config0_submission": variants},
     }
-    print(json.dumps(line))
-    leave()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=DEFAULT_STEPS)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default="q8_0_gemv")
+    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU time for the cpu_baseline leg")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-detail", action="store_true", help="default workload: skip the short runs of the other workloads that fill `detail`")
+    ap.add_argument("--device-pack", action="store_true", help="workload lm_head: draw and pack the Q6_K matrix on the GPU (torch) instead of numpy")
+    ap.add_argument("--cut", default="rows+cols", choices=["rows", "rows+cols"],
+                    help="workload decode, N > 1: every matrix by output rows (four gathers per layer), or o and down by columns "
+                         "(two all-reduces per layer)")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: how the output shards are all-gathered after each product -- by the product kernel itself "
+                         "(peer stores over NVLink, the default) or by an NCCL all-gather launched after it")
+    ap.add_argument("--fuse", default="nr", help="workload decode: operators folded into the projection launches (letters n, s, r; see LlamaDecoder)")
+    ap.add_argument("--token-prefill", action="store_true", help="workload decode: consume the prompt token by token instead of in tensor-core blocks")
+    ap.add_argument("--prompt-len", type=int, default=512, help="workload decode: prompt tokens consumed before the timed steps")
+    args = ap.parse_args()
+    args.warmup = max(3, args.warmup) if args.impl != "reference" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    runners = {"q8_0_gemm": run_gemm_workload, "layer_sweep": run_layer_sweep, "lm_head": run_lm_head, "decode": run_decode}
+    if args.workload in runners:
+        line = runners[args.workload](args)
+    elif args.workload == "q8_0_gemv":
+        line = run_gemv_workload(args)
+        if not args.no_detail:
+            # the other terms of the headline metric, each by its own workload in a short form (all ranks take part in the
+            # sharded ones; the prefill product is a one-GPU workload)
+            detail = line["detail"] if line is not None else {}
+            if world == 1:
+                detail["q8_0_gemm"] = brief_detail(run_gemm_workload(args, brief=True), ())
+            detail["lm_head"] = brief_detail(run_lm_head(args, brief=True), ("gather",))
+            detail["decode"] = brief_detail(run_decode(args, brief=True), ("sharding", "prefill", "prefill_ms", "prefill_tokens_per_s", "launch"))
+    else:
+        raise SystemExit(f"unknown workload {args.workload!r}")
+    if line is not None:
+        print(json.dumps(line))
+    if world > 1:
+        # Multi-rank exit: meet once more, then leave without tearing NCCL down under live CUDA graphs (a
+        # destroy_process_group here was seen to block for ever); all results are already out.
+        import torch
+        import torch.distributed as dist
+        sys.stdout.flush()
+        torch.cuda.synchronize()
+        dist.barrier()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -156,6 +156,7 @@ class Reference:
         L.zr_decode_fp16.argtypes = [C.POINTER(C.c_uint16), _f32p, _sz]
         L.zr_gemv.argtypes = [C.c_int, _u8p, _f32p, _f32p, _sz, _sz, C.c_uint]
         L.zr_gemm.argtypes = [C.c_int, _u8p, _f32p, _f32p, _sz, _sz, _sz, C.c_uint]
+        L.zr_gemv_batch.argtypes = [C.c_int, C.POINTER(C.c_void_p), _f32p, C.POINTER(C.c_void_p), C.POINTER(_sz), _sz, _sz, C.c_uint]
         L.zr_gemv_q8_0_i8_prequant.argtypes = [_u8p, _i8p, _f32p, _f32p, _sz, _sz]
         L.zr_gemv_q6k_avx2.argtypes = [_u8p, _f32p, _f32p, _sz, _sz]
         for name in ("zr_gemm_q8_0_avx2", "zr_gemm_q8_0_kblk_avx2", "zr_gemm_q6k_kblk_avx2"):
@@ -190,6 +191,18 @@ class Reference:
         if not self.lib.zr_gemv(fmt, _ptr(w, _u8p), _ptr(x, _f32p), _ptr(y, _f32p), rows, cols, workers):
             raise ValueError("reference declined gemv")
         return y
+
+    def gemv_batch(self, fmt: int, ws, x, rows, cols: int, workers: int = 1, outs=None) -> list[np.ndarray]:
+        """zen::quant::gemv_batch: several matvecs sharing x in one submission (one parallel_for over the concatenated rows)."""
+        ws, x = [_u8(w) for w in ws], _f32(x)
+        n = len(ws)
+        ys = outs if outs is not None else [np.empty(r, np.float32) for r in rows]
+        wp = (C.c_void_p * n)(*[w.ctypes.data for w in ws])
+        yp = (C.c_void_p * n)(*[y.ctypes.data for y in ys])
+        rs = (_sz * n)(*rows)
+        if not self.lib.zr_gemv_batch(fmt, wp, _ptr(x, _f32p), yp, rs, cols, n, workers):
+            raise ValueError("reference declined gemv_batch")
+        return ys
 
     def gemm(self, fmt: int, w, x, tokens: int, rows: int, cols: int, workers: int = 1) -> np.ndarray:
         w, x = _u8(w), _f32(x)

@@ -113,6 +113,13 @@ struct State {
     float* h_result{}; float* d_result{}; size_t h_result_bytes{};
     float* h_input{}; float* d_input{};   // mapped pinned staging for small activations, read by stage_in_kernel
     volatile unsigned* h_done{}; unsigned* d_done{}; unsigned done_seq{};
+    unsigned* d_seq{};        // device word: number of results published so far (the copy-out kernel counts, so a captured launch can be replayed)
+    // Host-pointer calls that are one product launch long are replayed from a captured graph (fetch -> product -> copy-out):
+    // one cudaGraphLaunch instead of three kernel launches per call.  Keyed by the resident tensors and the call's shape;
+    // dropped whenever a pointer inside could have changed (scratch regrown, a tensor released, shutdown).
+    struct HostGraph { cudaGraphExec_t exec{}; };
+    std::unordered_map<uint64_t, HostGraph> host_graphs;
+    bool use_host_graphs{true};   // ZEN_CUDA_HOST_GRAPHS=0 turns the replay off
 };
 
 State& state() { static State s; return s; }
@@ -198,6 +205,7 @@ bool init_locked(State& s) {
     if (const char* m = std::getenv("ZEN_CUDA_GEMM")) s.use_gemm = m[0] != '0';
     if (const char* m = std::getenv("ZEN_CUDA_GEMM_STREAMK")) s.gemm_stream_k = m[0] != '0';
     if (const char* m = std::getenv("ZEN_CUDA_WARM")) s.warm_hints = m[0] != '0';
+    if (const char* m = std::getenv("ZEN_CUDA_HOST_GRAPHS")) s.use_host_graphs = m[0] != '0';
     {
         cudaDriverEntryPointQueryResult qres{};
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &s.encode_tiled, cudaEnableDefault, &qres) != cudaSuccess ||
@@ -833,6 +841,12 @@ bool warm_noalloc_path(State& s) {
     return true;
 }
 
+void drop_host_graphs(State& s) {
+    for (auto& kv : s.host_graphs)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    s.host_graphs.clear();
+}
+
 bool ensure_gemm_ws(State& s, size_t bytes) {
     if (bytes <= s.d_gemm_ws_bytes) return true;
     if (s.d_gemm_ws) { cudaStreamSynchronize(s.stream); cudaFree(s.d_gemm_ws); }
@@ -844,6 +858,7 @@ bool ensure_gemm_ws(State& s, size_t bytes) {
 
 bool ensure_scratch(State& s, size_t x_bytes, size_t y_bytes) {
     const auto t0 = clock_type::now();
+    if (x_bytes > s.d_x_bytes || y_bytes > s.d_y_bytes) { cudaStreamSynchronize(s.stream); drop_host_graphs(s); }   // captured launches hold the old addresses
     if (x_bytes > s.d_x_bytes) {
         if (s.d_x) cudaFree(s.d_x);
         s.d_x = nullptr; s.d_x_bytes = 0;
@@ -876,12 +891,16 @@ constexpr size_t kDirectInputBytes = size_t(256) << 10;  // activations up to th
 // write one float per row from different warps, which would cross PCIe as thousands of 4-byte writes), and then
 // raises the sequence number.  One CTA.
 __global__ void __launch_bounds__(1024) copy_out_publish_kernel(float4* __restrict__ host_dst, const float4* __restrict__ src, size_t n16,
-                                                                volatile unsigned* done, unsigned seq) {
+                                                                volatile unsigned* done, unsigned* seq_counter) {
     zk::pdl_wait();
     for (size_t i = threadIdx.x; i < n16; i += blockDim.x) host_dst[i] = __ldcg(src + i);
     __threadfence_system();
     __syncthreads();
-    if (threadIdx.x == 0) *done = seq;
+    if (threadIdx.x == 0) {   // the number of this result: counted on the device, so that a captured launch can be replayed
+        const unsigned seq = *seq_counter + 1;
+        *seq_counter = seq;
+        *done = seq;
+    }
 }
 
 // Fetches the activations from mapped host memory into HBM.  It lets the next launch start at once: the product
@@ -898,6 +917,12 @@ bool ensure_direct_result(State& s, size_t bytes) {
         ZC_CUDA(s, cudaHostAlloc(reinterpret_cast<void**>(&s.h_input), kDirectInputBytes, cudaHostAllocMapped));
         ZC_CUDA(s, cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.d_input), s.h_input, 0));
     }
+    if (!s.d_seq) {
+        ZC_CUDA(s, cudaMalloc(reinterpret_cast<void**>(&s.d_seq), 16));
+        ZC_CUDA(s, cudaMemset(s.d_seq, 0, 16));
+        ZC_CUDA(s, cudaDeviceSynchronize());
+        s.done_seq = 0;
+    }
     if (!s.h_done) {
         unsigned* h = nullptr;
         ZC_CUDA(s, cudaHostAlloc(reinterpret_cast<void**>(&h), 64, cudaHostAllocMapped));
@@ -906,7 +931,7 @@ bool ensure_direct_result(State& s, size_t bytes) {
         ZC_CUDA(s, cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.d_done), h, 0));
     }
     if (bytes > s.h_result_bytes) {
-        if (s.h_result) { cudaStreamSynchronize(s.stream); cudaFreeHost(s.h_result); }
+        if (s.h_result) { cudaStreamSynchronize(s.stream); cudaFreeHost(s.h_result); drop_host_graphs(s); }
         s.h_result = nullptr; s.d_result = nullptr; s.h_result_bytes = 0;
         const size_t cap = (std::max(bytes, size_t(64) << 10) + 255) & ~size_t(255);   // the copy-out kernel moves whole 16-byte words
         ZC_CUDA(s, cudaHostAlloc(reinterpret_cast<void**>(&s.h_result), cap, cudaHostAllocMapped));
@@ -924,7 +949,11 @@ bool wait_done(State& s, unsigned seq) {
     while (*s.h_done != seq) {
         if ((++spins & 1023u) == 0 && us_since(t0) > 2000) {
             ZC_CUDA(s, cudaStreamSynchronize(s.stream));
-            if (*s.h_done != seq) return set_error(s, "result flag was not raised");
+            if (*s.h_done != seq) {   // a launch in the chain failed: take the device's count, so that later calls agree with it again
+                unsigned now = 0;
+                if (cudaMemcpy(&now, s.d_seq, sizeof now, cudaMemcpyDeviceToHost) == cudaSuccess) s.done_seq = now;
+                return set_error(s, "result flag was not raised");
+            }
             break;
         }
 #if defined(__x86_64__) || defined(__i386__)
@@ -978,20 +1007,6 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     if (direct && !ensure_direct_result(s, y_bytes)) return false;
     float* const d_result = s.d_y;
     const float* const h_result = direct ? s.h_result : s.h_stage;
-    auto t0 = clock_type::now();
-    if (direct && x_bytes <= kDirectInputBytes) {
-        std::memcpy(s.h_input, x, x_bytes);
-        const size_t n16 = x_bytes / sizeof(float4);
-        stage_in_kernel<<<static_cast<unsigned>(std::min<size_t>((n16 + 255) / 256, 32)), 256, 0, s.stream>>>(
-            reinterpret_cast<float4*>(s.d_x), reinterpret_cast<const float4*>(s.d_input), n16);
-        ++s.stats.dispatches;
-        if (cudaGetLastError() != cudaSuccess) return set_error(s, "activation fetch launch failed");
-    } else {
-        std::memcpy(s.h_stage, x, x_bytes);
-        ZC_CUDA(s, cudaMemcpyAsync(s.d_x, s.h_stage, x_bytes, cudaMemcpyHostToDevice, s.stream));
-    }
-    s.stats.transfer_us += us_since(t0);
-    t0 = clock_type::now();
     // Token chunks of up to eight rows per launch; each task's device output is [tokens][rows_i].
     float* d_out[zk::kMaxTasks];
     size_t off = 0;
@@ -1000,20 +1015,16 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     if (!chunk) return set_error(s, "columns too large: one activation row does not fit shared memory");
     // More than one decode launch worth of int8-activation Q8_0 tokens: the tensor-core GEMM.
     const bool tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q8_0 && act_mode == ZEN_CUDA_ACT_INT8 && tokens > 8;
-    if (tensor_path) {
-        if (!ensure_gemm_ws(s, gemm_ws_bytes(tokens, cols))) return false;
-        if (!enqueue_gemm_q8_0(s, w, d_out, count, s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
-    }
-    for (size_t t0k = 0; !tensor_path && t0k < tokens; t0k += chunk) {
-        const size_t nt = std::min<size_t>(chunk, tokens - t0k);
-        float* d_chunk[zk::kMaxTasks];
-        for (size_t i = 0; i < count; ++i) d_chunk[i] = d_out[i] + t0k * rows[i];
-        if (!enqueue_gemv(s, w, d_chunk, count, s.d_x + t0k * cols, nt, act_mode, s.stream)) return false;
-    }
-    s.stats.launch_us += us_since(t0);
-    t0 = clock_type::now();
-    if (direct) {
-        const unsigned seq = ++s.done_seq;
+    const bool fetch_by_kernel = direct && x_bytes <= kDirectInputBytes;
+
+    // The three launches of a small call (fetch the activations, the product, copy the result out and publish it).
+    auto enqueue_chain = [&]() -> bool {
+        const size_t n16 = x_bytes / sizeof(float4);
+        stage_in_kernel<<<static_cast<unsigned>(std::min<size_t>((n16 + 255) / 256, 32)), 256, 0, s.stream>>>(
+            reinterpret_cast<float4*>(s.d_x), reinterpret_cast<const float4*>(s.d_input), n16);
+        ++s.stats.dispatches;
+        if (cudaGetLastError() != cudaSuccess) return set_error(s, "activation fetch launch failed");
+        if (!enqueue_gemv(s, w, d_out, count, s.d_x, tokens, act_mode, s.stream)) return false;
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(1);
         cfg.blockDim = dim3(1024);
@@ -1025,12 +1036,103 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
         cfg.numAttrs = s.pdl ? 1 : 0;
         ++s.stats.dispatches;
         if (cudaLaunchKernelEx(&cfg, copy_out_publish_kernel, reinterpret_cast<float4*>(s.d_result), reinterpret_cast<const float4*>(s.d_y),
-                               (y_bytes + 15) / 16, s.d_done, seq) != cudaSuccess)
+                               (y_bytes + 15) / 16, s.d_done, s.d_seq) != cudaSuccess)
             return set_error(s, "result copy launch failed");
-        if (!wait_done(s, seq)) return false;
+        return true;
+    };
+
+    auto t0 = clock_type::now();
+    const bool one_launch = fetch_by_kernel && !tensor_path && tokens <= chunk;
+    if (one_launch) {
+        // The whole call is one fixed chain of launches over fixed addresses: replay it from a graph.  The first call with a
+        // given set of tensors runs the chain as plain launches (kernel attributes are set there, outside any capture),
+        // the second captures it, every later one is a single cudaGraphLaunch.
+        std::memcpy(s.h_input, x, x_bytes);
+        s.stats.transfer_us += us_since(t0);
+        t0 = clock_type::now();
+        uint64_t key = 1469598103934665603ull;
+        auto mix = [&key](uint64_t v) { key = (key ^ v) * 1099511628211ull; };
+        for (size_t i = 0; i < count; ++i) mix(reinterpret_cast<uintptr_t>(w[i]));
+        mix(tokens); mix(static_cast<uint64_t>(act_mode)); mix(count);
+        auto it = s.use_host_graphs ? s.host_graphs.find(key) : s.host_graphs.end();
+        if (it != s.host_graphs.end() && it->second.exec) {
+            ZC_CUDA(s, cudaGraphLaunch(it->second.exec, s.stream));
+            s.stats.dispatches += 3;
+        } else if (it != s.host_graphs.end()) {
+            cudaGraph_t graph = nullptr;
+            ZC_CUDA(s, cudaStreamBeginCapture(s.stream, cudaStreamCaptureModeThreadLocal));
+            const bool ok = enqueue_chain();
+            const cudaError_t e = cudaStreamEndCapture(s.stream, &graph);
+            if (!ok || e != cudaSuccess || !graph) {
+                if (graph) cudaGraphDestroy(graph);
+                s.host_graphs.erase(it);
+                s.use_host_graphs = false;          // this driver does not capture the chain: plain launches from now on
+                if (ok) set_error(s, std::string("capturing the call failed: ") + cudaGetErrorString(e));
+                cudaGetLastError();
+                if (!enqueue_chain()) return false;
+            } else {
+                cudaGraphExec_t exec = nullptr;
+                const cudaError_t ei = cudaGraphInstantiate(&exec, graph, 0);
+                cudaGraphDestroy(graph);
+                if (ei != cudaSuccess) return set_error(s, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(ei));
+                it->second.exec = exec;
+                ZC_CUDA(s, cudaGraphLaunch(exec, s.stream));
+            }
+        } else {
+            if (s.use_host_graphs) {
+                if (s.host_graphs.size() >= 4096) drop_host_graphs(s);
+                s.host_graphs.emplace(key, State::HostGraph{});
+            }
+            if (!enqueue_chain()) return false;
+        }
+        s.stats.launch_us += us_since(t0);
+        t0 = clock_type::now();
+        if (!wait_done(s, ++s.done_seq)) return false;
     } else {
-        ZC_CUDA(s, cudaMemcpyAsync(s.h_stage, s.d_y, y_bytes, cudaMemcpyDeviceToHost, s.stream));
-        ZC_CUDA(s, cudaStreamSynchronize(s.stream));
+        if (fetch_by_kernel) {
+            std::memcpy(s.h_input, x, x_bytes);
+            const size_t n16 = x_bytes / sizeof(float4);
+            stage_in_kernel<<<static_cast<unsigned>(std::min<size_t>((n16 + 255) / 256, 32)), 256, 0, s.stream>>>(
+                reinterpret_cast<float4*>(s.d_x), reinterpret_cast<const float4*>(s.d_input), n16);
+            ++s.stats.dispatches;
+            if (cudaGetLastError() != cudaSuccess) return set_error(s, "activation fetch launch failed");
+        } else {
+            std::memcpy(s.h_stage, x, x_bytes);
+            ZC_CUDA(s, cudaMemcpyAsync(s.d_x, s.h_stage, x_bytes, cudaMemcpyHostToDevice, s.stream));
+        }
+        s.stats.transfer_us += us_since(t0);
+        t0 = clock_type::now();
+        if (tensor_path) {
+            if (!ensure_gemm_ws(s, gemm_ws_bytes(tokens, cols))) return false;
+            if (!enqueue_gemm_q8_0(s, w, d_out, count, s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
+        }
+        for (size_t t0k = 0; !tensor_path && t0k < tokens; t0k += chunk) {
+            const size_t nt = std::min<size_t>(chunk, tokens - t0k);
+            float* d_chunk[zk::kMaxTasks];
+            for (size_t i = 0; i < count; ++i) d_chunk[i] = d_out[i] + t0k * rows[i];
+            if (!enqueue_gemv(s, w, d_chunk, count, s.d_x + t0k * cols, nt, act_mode, s.stream)) return false;
+        }
+        s.stats.launch_us += us_since(t0);
+        t0 = clock_type::now();
+        if (direct) {
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(1);
+            cfg.blockDim = dim3(1024);
+            cfg.stream = s.stream;
+            cudaLaunchAttribute attr{};
+            attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr.val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = &attr;
+            cfg.numAttrs = s.pdl ? 1 : 0;
+            ++s.stats.dispatches;
+            if (cudaLaunchKernelEx(&cfg, copy_out_publish_kernel, reinterpret_cast<float4*>(s.d_result), reinterpret_cast<const float4*>(s.d_y),
+                                   (y_bytes + 15) / 16, s.d_done, s.d_seq) != cudaSuccess)
+                return set_error(s, "result copy launch failed");
+            if (!wait_done(s, ++s.done_seq)) return false;
+        } else {
+            ZC_CUDA(s, cudaMemcpyAsync(s.h_stage, s.d_y, y_bytes, cudaMemcpyDeviceToHost, s.stream));
+            ZC_CUDA(s, cudaStreamSynchronize(s.stream));
+        }
     }
     s.stats.wait_us += us_since(t0);
     if (!check_error_word(s)) return false;
@@ -1070,6 +1172,9 @@ void zen_cuda_shutdown(void) {
         cudaSetDevice(s.device);
         cudaStreamSynchronize(s.stream);
         cudaStreamSynchronize(s.copy_stream);
+        drop_host_graphs(s);
+        if (s.d_seq) cudaFree(s.d_seq);
+        s.d_seq = nullptr;
         for (auto& kv : s.resident) free_weights(s, kv.second);
         s.resident.clear();
         if (s.d_x) cudaFree(s.d_x);
@@ -1197,6 +1302,7 @@ void zen_cuda_release_weights(const uint8_t* weights) {
     std::lock_guard<std::mutex> lock(s.mutex);
     if (!s.ready) return;
     cudaStreamSynchronize(s.stream);
+    drop_host_graphs(s);   // a captured call may name the tensor that goes away
     for (auto it = s.resident.begin(); it != s.resident.end();) {
         if (it->first.ptr == weights) { free_weights(s, it->second); it = s.resident.erase(it); }
         else ++it;
