@@ -20,7 +20,7 @@ decode (``decode``), the last two on all N GPUs.
   e2e        the same metric through the host-pointer C-ABI call a ZenInfer build would make
              (zen_cuda_gemv_q8_0): x travels host->device and y device->host inside the timed region.
   roofline   achieved = algorithmic bytes per launch / mean launch time inside the timed region;
-             peak = MEASURED_PEAKS.json hbm_gbs (a device copy measured on this pool).
+             peak = MEASURED_PEAKS.json hbm_gbs (a measured device-to-device copy rate).
   cpu_baseline  the reference's own CPU kernels (oracle/_ref, built from the reference sources) on
              the same workload, bounded sample, on this box's host cores.
 
@@ -296,7 +296,7 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
         for h, o in zip(handles, outs):
             be.dev_gemm_q8_0([h], [o.data_ptr()], d_x.data_ptr(), GEMM_T, ws.data_ptr(), ws_bytes, stream.cuda_stream)
 
-    steps = 250 if brief else max(1, args.steps // GEMM_COPIES)  # a graph replay is GEMM_COPIES steps
+    steps = 1 if args.profile else 250 if brief else max(1, args.steps // GEMM_COPIES)  # a graph replay is GEMM_COPIES steps
     with torch.cuda.stream(stream):
         one_pass()
         stream.synchronize()
@@ -305,7 +305,7 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
             one_pass()
         with ClockSampler(local) as clocks:
             t_warm, n_warm = time.time(), 0
-            while n_warm * GEMM_COPIES < args.warmup or time.time() - t_warm < 0.3:
+            while n_warm * GEMM_COPIES < args.warmup or (time.time() - t_warm < 0.3 and not args.profile):
                 graph.replay(); n_warm += 1
                 stream.synchronize()
             be.dev_check(stream.cuda_stream)
@@ -324,6 +324,9 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
     value = GEMM_OPS / (per_product_us * 1e-6) / 1e12
     peak, peak_kind = int8_peak_tops()
 
+    if args.profile:
+        return {"metric": "q8_0_prefill_gemm_int8_tops", "profile_run": True, "value": value, "unit": "TOPS", "launch_us": per_product_us,
+                "launches": "per product: quantize_acts_gemm_kernel, gemm_zero_split_tiles_kernel, gemm_q8_0_i8_kernel; 4 products untimed, 4 + 4 replayed"}
     # e2e: the host-pointer call, activations host->device and the 29 MB result device->host inside the timed region
     copies = [packed] + [packed.copy() for _ in range(GEMM_COPIES - 1)]
     for c in copies:
@@ -408,7 +411,7 @@ def run_layer_sweep(args) -> dict:
     d_y = {name: torch.zeros(rows, dtype=torch.float32, device=dev) for name, rows, _ in LAYER_TENSORS}
     stream = torch.cuda.Stream(device=dev)
     peak, peak_kind = peaks()
-    reps = max(3, args.steps // 100)
+    reps = 1 if args.profile else max(3, args.steps // 100)
 
     def time_graph(enqueue, launches_per_replay):
         with torch.cuda.stream(stream):
@@ -417,7 +420,7 @@ def run_layer_sweep(args) -> dict:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 enqueue()
-            for _ in range(max(3, args.warmup)):
+            for _ in range(1 if args.profile else max(3, args.warmup)):
                 graph.replay()
             stream.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -432,7 +435,7 @@ def run_layer_sweep(args) -> dict:
     detail, packed_q8, launches_total = {}, None, 0
     with ClockSampler(0) as clocks:
         clocks.mark_start()
-        for fmt in ("Q8_0", "Q4_0", "Q6_K"):
+        for fmt in [f for f in ("Q8_0", "Q4_0", "Q6_K") if f in args.formats.split(",")]:
             mode = ACT_INT8 if fmt == "Q8_0" else ACT_FP32
             packed = {name: np.ascontiguousarray(blocks.quantize(FORMAT_IDS[fmt], dense[name])) for name in dense}
             if fmt == "Q8_0":
@@ -479,6 +482,9 @@ def run_layer_sweep(args) -> dict:
                         be.dev_free(h)
         clocks.mark_end()
 
+    if args.profile or packed_q8 is None:
+        return {"metric": "layer_decode_gemv_hbm_gbs", "profile_run": args.profile, "detail": detail,
+                "launches": "per format: q|k|v, o, gate|up, down copies in turn (one untimed pass, two replays each), then the layer sequence"}
     # e2e: the Q8_0 layer through the host-pointer calls (zen_cuda_gemv_q8_0_batch / zen_cuda_gemv_q8_0), host buffers
     hosts = [{n: (packed_q8[n] if c == 0 else packed_q8[n].copy()) for n in packed_q8} for c in range(2)]
 
@@ -792,10 +798,10 @@ def run_decode(args, brief: bool = False) -> dict | None:
     if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=dev)
     be = Backend()
-    cfg = LlamaConfig()
+    cfg = LlamaConfig(layers=args.layers) if args.layers else LlamaConfig()
     prompt_len = args.prompt_len
-    steps = 125 if (brief or args.steps == DEFAULT_STEPS) else args.steps      # the default run: 3 warm-up + 125 timed = the 128 greedy steps
-    warm = max(3, args.warmup)
+    steps = 2 if args.profile else 125 if (brief or args.steps == DEFAULT_STEPS) else args.steps      # the default run: 3 warm-up + 125 timed = the 128 greedy steps
+    warm = 1 if args.profile else max(3, args.warmup)
 
     def tensors():
         gen = torch.Generator(device=dev)
@@ -864,6 +870,9 @@ def run_decode(args, brief: bool = False) -> dict | None:
     peak *= world
     achieved = algo / (ms * 1e-3 / steps) / 1e9
 
+    if args.profile:
+        dec.close()
+        return {"metric": "decode_tokens_per_s", "profile_run": True, "value": tok_s, "unit": "tokens/s", "layers": cfg.layers, "prefill_ms": prefill_ms} if rank == 0 else None
     # e2e: the public generate() call; every picked token is read back to the host as it is produced
     stamps = []
     e2e_new = 33
@@ -1003,8 +1012,10 @@ def run_gemv_workload(args) -> dict | None:
             if world > 1:
                 dist.all_gather_into_tensor(d_all.view(-1), ys[g * GROUP:(g + 1) * GROUP].reshape(-1))
 
+    passes = 1 if args.profile else PASSES_PER_STEP
+
     def time_passes(enqueue, steps, warm_steps, clocks=None):
-        """Captures one pass, replays it PASSES_PER_STEP times per step; returns the milliseconds of `steps` timed steps (max
+        """Captures one pass, replays it `passes` times per step; returns the milliseconds of `steps` timed steps (max
         over ranks).  The replay counts are fixed, never time-based: every rank replays the same number of collectives."""
         with torch.cuda.stream(stream):
             enqueue()  # first launch sets function attributes; keep it out of the capture
@@ -1012,7 +1023,7 @@ def run_gemv_workload(args) -> dict | None:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 enqueue()
-            for n in range(warm_steps * PASSES_PER_STEP):
+            for n in range(warm_steps * passes):
                 graph.replay()
                 if n % 64 == 63:
                     stream.synchronize()
@@ -1025,7 +1036,7 @@ def run_gemv_workload(args) -> dict | None:
             if clocks:
                 clocks.mark_start()
             e0.record(stream)
-            for _ in range(steps * PASSES_PER_STEP):
+            for _ in range(steps * passes):
                 graph.replay()
             e1.record(stream)
             stream.synchronize()
@@ -1045,7 +1056,7 @@ def run_gemv_workload(args) -> dict | None:
 
     with ClockSampler(local) as clocks:
         ms = time_passes(one_pass, args.steps, args.warmup, clocks)
-    launches = args.steps * PASSES_PER_STEP * len(groups)
+    launches = args.steps * passes * len(groups)
     total_bytes = ALGO_BYTES_PER_GROUP * launches * world
     value = total_bytes / (ms * 1e-3) / 1e9
     per_launch_us = ms * 1e3 / launches
@@ -1066,6 +1077,12 @@ def run_gemv_workload(args) -> dict | None:
     # --- the same 32 products submitted differently (one GPU): one tensor per launch, and all of them as one list launch ---
     variants = {"batch8": {"gbs": achieved, "us_per_product": per_launch_us / GROUP, "frac": achieved / peak, "launches_per_pass": len(groups),
                            "api": "zen_cuda_dev_gemv, eight tensors sharing the input per launch (zen::quant::gemv_batch); this is `value`"}}
+    if args.profile:
+        if pg is not None:
+            stream.synchronize()
+            pg.close()
+        return {"metric": "q8_0_gemv_hbm_gbs", "profile_run": True, "value": value, "unit": "GB/s", "launch_us": per_launch_us,
+                "launches": {"untimed": len(groups), "captured_replays": 2 * len(groups)}} if rank == 0 else None
     if world == 1:
         short = max(3, args.steps // 4)
         ys.zero_()
@@ -1083,7 +1100,7 @@ def run_gemv_workload(args) -> dict | None:
         be.gemv_list_destroy(lst)
         for name, ms_v, lp, api in (("single_launch", ms_s, COPIES, "zen_cuda_dev_gemv_fused, one tensor per launch, next tensor hinted to L2"),
                                     ("list", ms_l, 1, "zen_cuda_dev_gemv_list, all 32 products as items of one persistent launch")):
-            us = ms_v * 1e3 / (short * PASSES_PER_STEP * COPIES)
+            us = ms_v * 1e3 / (short * passes * COPIES)
             variants[name] = {"gbs": ALGO_BYTES_PER_LAUNCH / us / 1e3, "us_per_product": us, "frac": ALGO_BYTES_PER_LAUNCH / us / 1e3 / peak,
                               "launches_per_pass": lp, "api": api}
 
@@ -1173,6 +1190,11 @@ def main() -> None:
     ap.add_argument("--workload", default="q8_0_gemv")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU time for the cpu_baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="a short form of the workload for a profiler capture: one untimed pass, one captured-graph replay as warm-up and one "
+                         "as the timed step, no end-to-end leg, no CPU baseline, no detail (its figures are not benchmark values)")
+    ap.add_argument("--layers", type=int, default=0, help="workload decode: number of layers (default: the configuration's 32)")
+    ap.add_argument("--formats", default="Q8_0,Q4_0,Q6_K", help="workload layer_sweep: formats to run")
     ap.add_argument("--no-detail", action="store_true", help="default workload: skip the short runs of the other workloads that fill `detail`")
     ap.add_argument("--device-pack", action="store_true", help="workload lm_head: draw and pack the Q6_K matrix on the GPU (torch) instead of numpy")
     ap.add_argument("--cut", default="rows+cols", choices=["rows", "rows+cols"],
@@ -1186,6 +1208,9 @@ def main() -> None:
     ap.add_argument("--prompt-len", type=int, default=512, help="workload decode: prompt tokens consumed before the timed steps")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl != "reference" else args.warmup
+    if args.profile:
+        args.no_detail = args.no_cpu_baseline = True
+        args.steps, args.warmup = 1, 1
 
     if args.impl == "reference":
         run_reference_arm(args)
