@@ -56,10 +56,11 @@ PASSES_PER_STEP = 300     # a step of the default workload: 300 passes over the 
 BLOCK_BYTES, BLOCK_ELEMS = 34, 32
 ALGO_BYTES_PER_LAUNCH = ROWS * (COLS // BLOCK_ELEMS) * BLOCK_BYTES + COLS * 4 + ROWS * 4  # 17,858,560: one product launched alone
 ALGO_BYTES_PER_GROUP = GROUP * (ROWS * (COLS // BLOCK_ELEMS) * BLOCK_BYTES + ROWS * 4) + COLS * 4  # 142,753,792: eight products sharing one read of x
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel from an ncu capture of this workload;
-# None where no capture of the current kernel has been taken.
-GEMV_NCU_TRAFFIC_BYTES = 17_867_776
-GEMM_NCU_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from ncu captures of `bench.py --profile`
+# and `bench.py --workload q8_0_gemm --profile`: an eight-tensor decode launch reads 142,679,808 B and writes 3,889,920 B
+# (142,753,792 B algorithmic); the prefill kernel moves 81,239,808 + 13,685,504 B (94,109,696 B algorithmic).
+GEMV_NCU_TRAFFIC_BYTES = 146_569_728
+GEMM_NCU_TRAFFIC_BYTES = 94_925_312
 WORKLOAD = ("Q8_0 decode GEMV batch 1, W 4096x4096 (config 0), %d rotating weight copies, submitted %d products at a time "
             "(zen::quant::gemv_batch: tensors sharing one input)" % (COPIES, GROUP))
 
@@ -1169,8 +1170,8 @@ def run_gemv_workload(args) -> dict | None:
             "" if world == 1 else
             "; output shards all-gathered by the product kernel itself (peer stores over NVLink, device-side epoch flags)" if fused else "; NCCL all-gather of output shards after each launch"),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                     "traffic": None, "launch_us": per_launch_us, "algorithmic_bytes_per_launch": ALGO_BYTES_PER_GROUP,
-                     "kernel": f"gemv_q8_0_kernel<1,1>, {GROUP} tensors of 4096 x 4096 per launch; ncu traffic of one single-tensor launch: {GEMV_NCU_TRAFFIC_BYTES} B for {ALGO_BYTES_PER_LAUNCH} algorithmic"},
+                     "traffic": GEMV_NCU_TRAFFIC_BYTES, "launch_us": per_launch_us, "algorithmic_bytes_per_launch": ALGO_BYTES_PER_GROUP,
+                     "kernel": f"gemv_q8_0_kernel<1,1>, {GROUP} tensors of 4096 x 4096 per launch"},
         "cpu_baseline": cpu,
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": COLS * 4 * len(task_groups) * PASSES_PER_STEP, "d2h_bytes_per_step": ROWS * 4 * COPIES * PASSES_PER_STEP,
