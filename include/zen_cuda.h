@@ -314,6 +314,24 @@ typedef struct zen_cuda_pick_segment {
 } zen_cuda_pick_segment;
 int zen_cuda_dev_greedy_pick(const zen_cuda_pick_segment* segments, size_t count, size_t tokens, int64_t* d_pick, void* stream);
 
+/* Temperature / top-k / top-p sampling on the device: the non-greedy branch of the reference's sampler
+ * (sampling_distribution + sample_distribution, src/adapters/dense_transformer_runtime.cpp:349-390).  Among the finite
+ * logits the top_k highest are kept (ties at the cut go to the lowest ids), p_i = exp((v_i - max) / temperature) is
+ * normalised over them in double, the top-p cut keeps the shortest prefix (by descending probability) whose cumulative
+ * probability reaches top_p (at least one token), and the token is drawn from the kept ones IN TOKEN-ID ORDER as the
+ * first whose cumulative probability reaches u -- the walk std::discrete_distribution does over the reference's
+ * id-indexed probability vector; u is a uniform number in [0, 1) from the caller's generator, which stays on the host.
+ *   temperature > 0 (use zen_cuda_dev_greedy_pick otherwise); top_p >= 1 or <= 0: no top-p cut.
+ *   At most ZEN_CUDA_SAMPLE_MAX_CANDIDATES tokens are considered: with top_k == 0 or larger the tail beyond the 1024
+ *   most likely tokens is dropped, and *d_truncated (optional) is set when the top-p nucleus did not fit into them.
+ *   d_pick: device int64, -1 when no logit is finite.  d_kept_ids / d_kept_probs (optional, room for
+ *   ZEN_CUDA_SAMPLE_MAX_CANDIDATES entries) receive the kept ids in ascending order and their probabilities (sum 1),
+ *   d_kept_count (optional) their number: a host that wants to draw itself reads these instead.
+ * Logit bias and allowed-token lists of the reference's options are applied by the caller to the logits beforehand. */
+#define ZEN_CUDA_SAMPLE_MAX_CANDIDATES 1024
+int zen_cuda_dev_sample(const float* d_logits, size_t n, float temperature, uint32_t top_k, float top_p, double u, int64_t* d_pick,
+                        int32_t* d_kept_ids, double* d_kept_probs, int32_t* d_kept_count, int32_t* d_truncated, void* stream);
+
 /* ---- the decode-step operators between the projections (device pointers, stream-ordered, no synchronisation) -----
  * With these a whole token step of a dense Llama-style layer stays in HBM on one stream.  They answer the reference's
  * host loop in DenseTransformerRuntime::forward (src/adapters/dense_transformer_runtime.cpp:3670-4600) and the

@@ -39,7 +39,7 @@ ABI_SYMBOLS = (
     "zen_cuda_dev_gemm_q8_0_noalloc",
     "zen_cuda_gather_region_bytes", "zen_cuda_ipc_alloc", "zen_cuda_ipc_open", "zen_cuda_ipc_close", "zen_cuda_ipc_free",
     "zen_cuda_gather_create", "zen_cuda_gather_destroy", "zen_cuda_dev_gemv_gather", "zen_cuda_dev_gather_fetch", "zen_cuda_dev_allgather", "zen_cuda_dev_allreduce_add",
-    "zen_cuda_dev_greedy_pick",
+    "zen_cuda_dev_greedy_pick", "zen_cuda_dev_sample",
     "zen_cuda_dev_embed_q8_0", "zen_cuda_dev_rms_norm", "zen_cuda_dev_rope_kv_append", "zen_cuda_dev_attention", "zen_cuda_dev_silu_mul",
     "zen_cuda_dev_advance_position", "zen_cuda_dev_gemv_swiglu", "zen_cuda_dev_attention_block", "zen_cuda_dev_gemv_fused",
     "zen_cuda_dev_embed_rows_q8_0", "zen_cuda_dev_rope_kv_append_rows", "zen_cuda_dev_attention_prefill",
@@ -154,6 +154,7 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_dev_allgather.argtypes = [vp, vp, sz, vp, vp]
     lib.zen_cuda_dev_allreduce_add.argtypes = [vp, vp, sz, vp, vp]
     lib.zen_cuda_dev_greedy_pick.argtypes = [C.POINTER(PickSegment), sz, sz, vp, vp]
+    lib.zen_cuda_dev_sample.argtypes = [vp, sz, C.c_float, C.c_uint32, C.c_float, C.c_double, vp, vp, vp, vp, vp, vp]
     lib.zen_cuda_dev_embed_q8_0.argtypes = [vp, vp, vp, vp]
     lib.zen_cuda_dev_rms_norm.argtypes = [vp, vp, vp, vp, sz, sz, C.c_float, vp]
     lib.zen_cuda_dev_rope_kv_append.argtypes = [vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, i, vp, vp, sz, vp]
@@ -427,6 +428,15 @@ class Backend:
         segs = (PickSegment * n)(*[PickSegment(b, ln, first, stride, 0) for b, ln, first, stride in segments])
         if not self.lib.zen_cuda_dev_greedy_pick(segs, n, tokens, d_pick, stream):
             self._fail("dev_greedy_pick")
+
+    SAMPLE_MAX_CANDIDATES = 1024
+
+    def dev_sample(self, d_logits: int, n: int, temperature: float, top_k: int, top_p: float, u: float, d_pick: int, stream: int = 0, *,
+                   d_kept_ids: int | None = None, d_kept_probs: int | None = None, d_kept_count: int | None = None, d_truncated: int | None = None) -> None:
+        """Temperature / top-k / top-p sampling of one token on the device (the non-greedy branch of the reference's sampler);
+        u is a uniform number in [0, 1) from the caller's generator."""
+        if not self.lib.zen_cuda_dev_sample(d_logits, n, temperature, top_k, top_p, u, d_pick, d_kept_ids, d_kept_probs, d_kept_count, d_truncated, stream):
+            self._fail("dev_sample")
 
     # ---- decode-step operators between the projections ----
     def dev_embed_q8_0(self, handle: int, d_token: int, d_out: int, stream: int = 0) -> None:

@@ -34,6 +34,7 @@
 #include "greedy_pick.cuh"
 #include "quantize_acts.cuh"
 #include "repack.cuh"
+#include "sample_pick.cuh"
 
 struct zen_cuda_gather {
     zk::PeerGather dev{};     // what the kernels receive
@@ -1629,6 +1630,23 @@ int zen_cuda_dev_greedy_pick(const zen_cuda_pick_segment* segments, size_t count
         e = launch_pdl(s, zk::pick_finish_kernel, dim3(static_cast<unsigned>((tokens + 63) / 64)), dim3(64), 0, st, p.keys, static_cast<uint32_t>(tokens));
     s.stats.dispatches += 2;
     if (e != cudaSuccess) return set_error(s, "dev_greedy_pick: launch failed") ? 1 : 0;
+    return 1;
+}
+
+int zen_cuda_dev_sample(const float* d_logits, size_t n, float temperature, uint32_t top_k, float top_p, double u, int64_t* d_pick,
+                        int32_t* d_kept_ids, double* d_kept_probs, int32_t* d_kept_count, int32_t* d_truncated, void* stream) {
+    static_assert(ZEN_CUDA_SAMPLE_MAX_CANDIDATES == zk::kSampleMaxCandidates, "candidate limit");
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!d_logits || !n || n > 0xffffffffull || !d_pick || !(temperature > 0.0f) || !std::isfinite(temperature) || !(u >= 0.0 && u < 1.0))
+        return set_error(s, "dev_sample: bad arguments (temperature > 0, u in [0, 1))") ? 1 : 0;
+    zk::SampleParams p{};
+    p.logits = d_logits; p.n = static_cast<uint32_t>(n); p.temperature = temperature; p.top_k = top_k; p.top_p = top_p; p.u = u;
+    p.pick = reinterpret_cast<long long*>(d_pick); p.kept_ids = d_kept_ids; p.kept_probs = d_kept_probs; p.kept_count = d_kept_count; p.truncated = d_truncated;
+    const cudaError_t e = launch_pdl(s, zk::sample_top_kernel, dim3(1), dim3(zk::kSampleThreads), 0, stream ? static_cast<cudaStream_t>(stream) : s.stream, p);
+    ++s.stats.dispatches;
+    if (e != cudaSuccess) return set_error(s, std::string("dev_sample: launch failed: ") + cudaGetErrorString(e)) ? 1 : 0;
     return 1;
 }
 

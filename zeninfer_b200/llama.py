@@ -399,9 +399,16 @@ class LlamaDecoder:
                 if last:
                     self._enqueue_head()              # a single-token product: the decode mode
 
-    def generate(self, prompt: list[int], max_new: int, on_token=None, batched_prefill: bool | None = None) -> list[int]:
-        """Greedy generation: the prompt, then max_new picks (each read back, as the reference's per-token callback
-        does).  The prompt goes through prefill() in blocks when the decoder computes with int8 activations (the
+    def _sample(self, temperature: float, top_k: int, top_p: float, u: float) -> None:
+        """Replaces the greedy pick in self.token by a draw from the filtered distribution of self.logits."""
+        self.be.dev_sample(self.logits.data_ptr(), self.cfg.vocab, temperature, top_k, top_p, u, self.token.data_ptr(), self.stream.cuda_stream)
+
+    def generate(self, prompt: list[int], max_new: int, on_token=None, batched_prefill: bool | None = None, temperature: float = 0.0,
+                 top_k: int = 0, top_p: float = 1.0, seed: int = 0) -> list[int]:
+        """Generation: the prompt, then max_new picks (each read back, as the reference's per-token callback does).  With
+        temperature <= 0 the picks are greedy; otherwise every token is drawn on the device from the temperature / top-k /
+        top-p distribution of the step's logits (GenerationOptions, sample_logits :391-418), with one uniform number per
+        token from a host generator seeded with `seed` (the generator stays on the host, as the reference's does).  The prompt goes through prefill() in blocks when the decoder computes with int8 activations (the
         tensor-core product has no fp32-equivalent mode), token by token otherwise; batched_prefill overrides the choice.
         Raises when the context would overflow."""
         torch = self.torch
@@ -410,9 +417,12 @@ class LlamaDecoder:
         self.reset()
         self.sync_ranks()
         out: list[int] = []
+        rng = np.random.default_rng(seed) if temperature > 0.0 else None
         with torch.cuda.stream(self.stream):
             self.feed_prompt(prompt, batched_prefill)
             for n in range(max_new):
+                if rng is not None:               # the step left the greedy pick in self.token: draw instead
+                    self._sample(temperature, top_k, top_p, float(rng.random()))
                 tok = int(self.token.item())      # device -> host read of the step's result
                 out.append(tok)
                 if on_token:
