@@ -44,5 +44,12 @@ inline bool gemm_q4_0(const std::uint8_t* w, const float* in, float* out, std::s
 inline bool gemm_kquant(const std::uint8_t* w, const float* in, float* out, std::size_t tokens, std::size_t rows, std::size_t cols, bool q5) noexcept {
     return zen_cuda_gemm_kquant(w, in, out, tokens, rows, cols, q5 ? 1 : 0) != 0;
 }
+inline bool rms_norm(const float* x, const float* weight, float* y, std::size_t rows, std::size_t cols, float epsilon) noexcept {
+    return zen_cuda_rms_norm(x, weight, y, rows, cols, epsilon) != 0;
+}
+inline bool gemv_q8_0_ffn(const std::uint8_t* gate, const std::uint8_t* up, const std::uint8_t* down, const float* x, float* y,
+                          std::size_t ffn_rows, std::size_t cols, std::size_t out_rows) noexcept {
+    return zen_cuda_gemv_q8_0_ffn(gate, up, down, x, y, ffn_rows, cols, out_rows) != 0;
+}
 inline void release_weights(const std::uint8_t* w) noexcept { zen_cuda_release_weights(w); }
 }  // namespace zen::cuda

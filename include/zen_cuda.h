@@ -131,6 +131,31 @@ int zen_cuda_gemm_q4_0(const uint8_t* weights, const float* input, float* output
  * no fused input, accumulation or gather).  A first, untuned kernel. */
 int zen_cuda_gemm_kquant(const uint8_t* weights, const float* input, float* output, size_t tokens, size_t rows, size_t columns, int q5);
 
+/* zen::hip::rms_norm, include/zen/hip_backend.h:74-76 (device side hip_backend.hip:724-776): row-wise root-mean-square
+ * normalisation, y[r][c] = x[r][c] * rsqrt(mean_c(x[r]^2) + epsilon) * weight[c].  Host buffers x, y [rows][columns],
+ * weight [columns].  The sum of squares is taken in double, as the reference's CPU rms_norm does
+ * (src/adapters/dense_transformer_runtime.cpp:117-125). */
+int zen_cuda_rms_norm(const float* x, const float* weight, float* y, size_t rows, size_t columns, float epsilon);
+
+/* zen::hip::gemv_q8_0_ffn, include/zen/hip_backend.h:78-83 (hook site src/quant.cpp:1553-1580, device side
+ * hip_backend.hip:778-870): y = down * (silu(gate * x) * (up * x)) as one submission, the ffn_rows-wide activation staying
+ * on the device.  gate, up: raw Q8_0 [ffn_rows][columns]; down: raw Q8_0 [out_rows][ffn_rows]; x [columns]; y [out_rows].
+ * Two launches: gate and up share one; the down projection applies silu(g) * u as it loads its activations.
+ * Activations enter as the backend's Q8_0 mode says (zen_cuda_set_q8_act_mode). */
+int zen_cuda_gemv_q8_0_ffn(const uint8_t* gate, const uint8_t* up, const uint8_t* down, const float* x, float* y, size_t ffn_rows,
+                           size_t columns, size_t out_rows);
+
+/* Residency budget of the pointer-keyed weights: kVRAMBudgetPercent, src/backends/hip/hip_backend.hip:50 and :459-476.
+ * The tensors the host-pointer calls keep resident stay below the budget (80 % of the device's memory unless set here
+ * or by ZEN_CUDA_VRAM_BUDGET_MB; bytes == 0 restores the default).  A tensor that would cross it evicts the WHOLE keyed
+ * set first (the loader asks in the same order every run, so evicting a part would only churn); one that does not fit
+ * the budget by itself makes the call return 0, as does a batch whose tensors do not fit together.  An eviction in the
+ * middle of a batch is followed by resolving the batch's tensors again before anything is launched.  Tensors held
+ * through zen_cuda_dev_upload belong to the caller: they count toward the bytes held and are never evicted. */
+int zen_cuda_set_vram_budget(uint64_t bytes);
+/* Any pointer may be null.  held_bytes counts keyed and caller-held tensors; tensors counts the keyed set. */
+int zen_cuda_residency(uint64_t* budget_bytes, uint64_t* held_bytes, uint64_t* tensors, uint64_t* evictions);
+
 /* zen::d3d12::release_q8_0_weights / release_kquant_weights, include/zen/d3d12_backend.h:80,88.
  * Call before unmapping or reusing a weight address; drops every resident shape at that address. */
 void zen_cuda_release_weights(const uint8_t* weights);

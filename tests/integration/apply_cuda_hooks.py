@@ -5,9 +5,11 @@
 
 The copy is made at build time and never committed: the reference's source stays where it is.  The hooks are the ones
 INTEGRATION.md lists, placed beside the reference's own `#ifdef ZEN_HAS_HIP` blocks (src/quant.cpp:1007-1012 gemv,
-:1457-1468 gemv_batch, :1528-1543 gemm_batch, :1656-1659 gemm), and they count their attempts on the reference's own route
-counters (g_gemv_routes / g_gemm_routes, :48-75).  Every hook `return`s its result: this backend has no CPU route behind
-it, so a failed call is the caller's error, not a fall-through.  Each anchor must match exactly once, or the script stops.
+:1457-1468 gemv_batch, :1528-1543 gemm_batch, :1656-1659 gemm, :1553-1580 ffn_gemv), and they count their attempts on the reference's own route
+counters (g_gemv_routes / g_gemm_routes, :48-75).  The product hooks `return` their result: this backend has no CPU route
+behind it, so a failed call is the caller's error, not a fall-through.  The ffn_gemv hook keeps the reference's own
+contract for that function (false = "no backend took the fused FFN", after which the runtime issues the three products
+separately).  Each anchor must match exactly once, or the script stops.
 """
 import sys
 
@@ -72,6 +74,14 @@ GEMM = '''#ifdef ZEN_HAS_CUDA
 #endif
 '''
 
+FFN = '''#ifdef ZEN_HAS_CUDA
+    if(gate_format.encoding==Encoding::q8_0&&up_format.encoding==Encoding::q8_0&&
+       down_format.encoding==Encoding::q8_0&&zen::cuda::enabled()&&
+       zen::cuda::gemv_q8_0_ffn(gate_weights,up_weights,down_weights,input,output,
+                                ffn_rows,columns,output_rows))return true;
+#endif
+'''
+
 # (anchor text that starts the line group the block goes BEFORE, block)
 HOOKS = [
     ('#include "zen/compute_pool.h"\n', INCLUDE),
@@ -79,6 +89,8 @@ HOOKS = [
     ('#ifdef ZEN_HAS_HIP\n    if(format.encoding==Encoding::q8_0&&scale==1.0f&&count>1&&count<=zen::hip::kMaxBatch', GEMV_BATCH),
     ('    // No GPU batch (gate off, HIP-only build', GEMM_BATCH),
     ('#ifdef ZEN_HAS_HIP\n    if(f.encoding==Encoding::q8_0&&scale==1.0f&&zen::hip::enabled()&&\n       zen::hip::gemm_q8_0(', GEMM),
+    ('#ifdef ZEN_HAS_D3D12\n    if(gate_format.encoding==Encoding::q8_0&&up_format.encoding==Encoding::q8_0&&\n'
+     '       down_format.encoding==Encoding::q8_0&&zen::d3d12::enabled()&&\n       zen::d3d12::gemv_q8_0_ffn(', FFN),
 ]
 
 

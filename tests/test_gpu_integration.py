@@ -66,8 +66,10 @@ def test_reference_runtime_generates_the_golden_ids_through_the_cuda_backend():
     E, F, V, KW = cfg["embedding"], cfg["ffn"], cfg["vocab"], cfg["kv_heads"] * cfg["head_dim"]
     per_layer = (2 * E * E + 2 * KW * E + 3 * F * E) // 32 * 34
     assert upload_bytes == cfg["layers"] * per_layer + V * E // 32 * 34
-    # decode steps alone are 15 tokens x (2 layers x 4 submissions + lm_head): the prompt block adds its own
-    assert submits >= 15 * (cfg["layers"] * 4 + 1)
+    # decode steps alone are 15 tokens x (2 layers x 3 submissions + lm_head): q|k|v, o and the fused gate|up|silu|down
+    # (quant::ffn_gemv -> zen::cuda::gemv_q8_0_ffn); the prompt block adds its own
+    # (8 tokens, 25 submissions here); with the three FFN products submitted separately the decode steps alone would be 135
+    assert 15 * (cfg["layers"] * 3 + 1) <= submits < 15 * (cfg["layers"] * 4 + 1), submits
 
 
 @pytest.mark.skipif(not os.path.exists(LIB), reason="tests/integration/_build/libzenrt_cuda.so not built")

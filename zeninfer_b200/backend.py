@@ -32,6 +32,7 @@ ABI_SYMBOLS = (
     "zen_cuda_last_error", "zen_cuda_set_q8_act_mode", "zen_cuda_get_q8_act_mode",
     "zen_cuda_gemv_q8_0", "zen_cuda_gemm_q8_0", "zen_cuda_gemv_q8_0_batch", "zen_cuda_gemm_q8_0_batch",
     "zen_cuda_gemm_q6_k", "zen_cuda_gemm_q4_0", "zen_cuda_gemm_kquant", "zen_cuda_release_weights", "zen_cuda_quantize_acts",
+    "zen_cuda_rms_norm", "zen_cuda_gemv_q8_0_ffn", "zen_cuda_set_vram_budget", "zen_cuda_residency",
     "zen_cuda_dev_upload", "zen_cuda_dev_free", "zen_cuda_dev_weight_bytes", "zen_cuda_dev_gemv",
     "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_error_name", "zen_cuda_set_wait_budget_ms",
     "zen_cuda_gemv_list_create", "zen_cuda_gemv_list_destroy", "zen_cuda_gemv_list_bytes", "zen_cuda_dev_gemv_list",
@@ -108,6 +109,10 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_gemm_q4_0.argtypes = [vp, vp, vp, sz, sz, sz]
     lib.zen_cuda_gemm_kquant.argtypes = [vp, vp, vp, sz, sz, sz, C.c_int]
     lib.zen_cuda_release_weights.argtypes = [vp]
+    lib.zen_cuda_rms_norm.argtypes = [vp, vp, vp, sz, sz, C.c_float]
+    lib.zen_cuda_gemv_q8_0_ffn.argtypes = [vp, vp, vp, vp, vp, sz, sz, sz]
+    lib.zen_cuda_set_vram_budget.argtypes = [C.c_uint64]
+    lib.zen_cuda_residency.argtypes = [C.POINTER(C.c_uint64)] * 4
     lib.zen_cuda_release_weights.restype = None
     lib.zen_cuda_quantize_acts.argtypes = [vp, vp, vp, sz, sz]
     lib.zen_cuda_dev_upload.argtypes = [i, vp, sz, sz, sz, sz]
@@ -259,6 +264,36 @@ class Backend:
 
     def release_weights(self, weights: np.ndarray) -> None:
         self.lib.zen_cuda_release_weights(_addr(weights))
+
+    def rms_norm(self, x, weight, epsilon: float) -> np.ndarray:
+        """zen::hip::rms_norm (include/zen/hip_backend.h:74-76): x [rows, columns] normalised row by row, times weight."""
+        x = np.ascontiguousarray(x, np.float32)
+        weight = np.ascontiguousarray(weight, np.float32)
+        rows, columns = x.reshape(-1, x.shape[-1]).shape
+        y = np.empty_like(x)
+        if not self.lib.zen_cuda_rms_norm(_addr(x), _addr(weight), _addr(y), rows, columns, epsilon):
+            self._fail(f"rms_norm {rows}x{columns}")
+        return y
+
+    def gemv_ffn(self, gate: np.ndarray, up: np.ndarray, down: np.ndarray, x, ffn_rows: int, columns: int, out_rows: int) -> np.ndarray:
+        """zen::hip::gemv_q8_0_ffn (include/zen/hip_backend.h:78-83): down * (silu(gate * x) * (up * x)), raw Q8_0 tensors."""
+        x = np.ascontiguousarray(x, np.float32).reshape(columns)
+        y = np.empty(out_rows, np.float32)
+        if not self.lib.zen_cuda_gemv_q8_0_ffn(_addr(self._weights(gate)), _addr(self._weights(up)), _addr(self._weights(down)), _addr(x), _addr(y),
+                                               ffn_rows, columns, out_rows):
+            self._fail(f"gemv_q8_0_ffn {ffn_rows}x{columns} -> {out_rows}")
+        return y
+
+    def set_vram_budget(self, nbytes: int) -> None:
+        """Residency budget of the pointer-keyed weights in bytes; 0 restores 80 % of the device's memory."""
+        if not self.lib.zen_cuda_set_vram_budget(int(nbytes)):
+            self._fail("set_vram_budget")
+
+    def residency(self) -> dict:
+        v = [C.c_uint64() for _ in range(4)]
+        if not self.lib.zen_cuda_residency(*[C.byref(c) for c in v]):
+            self._fail("residency")
+        return dict(zip(("budget_bytes", "held_bytes", "tensors", "evictions"), (int(c.value) for c in v)))
 
     def quantize_acts(self, x) -> tuple[np.ndarray, np.ndarray]:
         """fp32 [tokens, K] -> (int8 codes [tokens, K], fp32 scales [tokens, K/32]); quantise_acts_q8_0 on the device."""

@@ -97,6 +97,9 @@ struct State {
     bool pdl{true};          // programmatic dependent launch of the GEMV kernels (ZEN_CUDA_PDL=0 turns it off)
     unsigned ctas_per_sm{1}; // persistent GEMV CTAs per SM (ZEN_CUDA_GEMV_CTAS)
     std::unordered_map<ResidentKey, zen_cuda_weights*, ResidentKeyHash> resident;
+    // Residency budget of the pointer-keyed set (zen::hip keeps weights below 80 % of VRAM, hip_backend.hip:50 and :459-476).
+    uint64_t vram_budget{};   // bytes; 0 = no limit
+    uint64_t evictions{};     // times the whole keyed set was dropped to make room
     // pinned host staging + device scratch for the host-pointer calls (grow-only)
     float* h_stage{}; size_t h_stage_bytes{};
     float* d_x{}; size_t d_x_bytes{};
@@ -158,6 +161,7 @@ bool apply_wait_budget(State& s, unsigned ms) {
 
 bool warm_noalloc_path(State& s);   // defined with the allocation-free entry point
 
+uint64_t default_vram_budget(const State& s);
 bool init_locked(State& s) {
     if (s.ready) {
         // Entry points may be reached from any thread, and a new thread starts on device 0: make the backend's device
@@ -185,6 +189,8 @@ bool init_locked(State& s) {
     if (cudaDeviceGetAttribute(&s.clock_khz, cudaDevAttrClockRate, dev) != cudaSuccess) s.clock_khz = 1965000;
     std::snprintf(s.adapter.name, sizeof(s.adapter.name), "%.127s", prop.name);
     s.adapter.dedicated_vram = prop.totalGlobalMem;
+    s.vram_budget = default_vram_budget(s);
+    if (const char* m = std::getenv("ZEN_CUDA_VRAM_BUDGET_MB")) s.vram_budget = static_cast<uint64_t>(std::max(0ll, std::atoll(m))) << 20;
     s.adapter.shared_memory = prop.sharedMemPerBlockOptin;
     s.adapter.sm_count = prop.multiProcessorCount;
     s.adapter.warp_size = prop.warpSize;
@@ -225,6 +231,9 @@ bool init_locked(State& s) {
     return true;
 }
 
+// zen::hip's kVRAMBudgetPercent (hip_backend.hip:50): resident weights stay below 80 % of the device's memory.
+uint64_t default_vram_budget(const State& s) { return s.adapter.dedicated_vram / 100 * 80; }
+
 void free_weights(State& s, zen_cuda_weights* w) {
     if (!w) return;
     for (void* p : w->plane) if (p) cudaFree(p);
@@ -257,6 +266,26 @@ bool stream_to_device(State& s, void* dst, const uint8_t* src, size_t bytes) {
     return true;
 }
 
+// Device bytes of each plane of a tensor; every plane gets slack for bulk copies whose size was rounded up to 16 bytes.
+void plane_sizes(int fmt, size_t nrows, size_t cols, size_t plane_bytes[4]) {
+    const uint32_t nb = static_cast<uint32_t>(cols / block_elems(fmt)), nbp = (nb + 7u) & ~7u;
+    plane_bytes[0] = plane_bytes[1] = plane_bytes[2] = plane_bytes[3] = 0;
+    if (raw_layout(fmt)) {
+        plane_bytes[0] = nrows * static_cast<size_t>(nb) * block_bytes(fmt) + 64;   // the super-blocks as they are in the file
+    } else if (fmt == ZEN_CUDA_Q8_0) {
+        plane_bytes[0] = nrows * cols + 64;                                // int8 codes
+        plane_bytes[1] = nrows * static_cast<size_t>(nbp) * 2 + 64;        // f16 scales
+    } else if (fmt == ZEN_CUDA_Q4_0) {
+        plane_bytes[0] = nrows * (cols / 2) + 64;                          // nibble bytes
+        plane_bytes[1] = nrows * static_cast<size_t>(nbp) * 2 + 64;        // f16 scales
+    } else {  // Q6_K: nb counts 256-weight super-blocks
+        plane_bytes[0] = nrows * (cols / 2) + 64;                          // ql
+        plane_bytes[1] = nrows * (cols / 4) + 64;                          // qh
+        plane_bytes[2] = nrows * (cols / 16) + 64;                         // int8 group scales
+        plane_bytes[3] = nrows * static_cast<size_t>(nbp) * 2 + 64;        // f16 super-block scales
+    }
+}
+
 // Uploads rows [first_row, first_row+nrows) and re-lays them out into planes on the device.
 zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t rows_total, size_t cols, size_t first_row, size_t nrows) {
     const uint32_t be = block_elems(fmt), bb = block_bytes(fmt);
@@ -275,22 +304,8 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
     auto t0 = clock_type::now();
     const bool raw = raw_layout(fmt);
     bool ok = raw || cudaMalloc(reinterpret_cast<void**>(&d_raw), w->raw_bytes + 16) == cudaSuccess;
-    size_t plane_bytes[4] = {0, 0, 0, 0};
-    // every plane gets slack for bulk copies whose size was rounded up to 16 bytes
-    if (raw) {
-        plane_bytes[0] = w->raw_bytes + 64;                                // the super-blocks as they are in the file
-    } else if (fmt == ZEN_CUDA_Q8_0) {
-        plane_bytes[0] = nrows * cols + 64;                                // int8 codes
-        plane_bytes[1] = nrows * static_cast<size_t>(w->nbp) * 2 + 64;     // f16 scales
-    } else if (fmt == ZEN_CUDA_Q4_0) {
-        plane_bytes[0] = nrows * (cols / 2) + 64;                          // nibble bytes
-        plane_bytes[1] = nrows * static_cast<size_t>(w->nbp) * 2 + 64;     // f16 scales
-    } else {  // Q6_K: nb counts 256-weight super-blocks
-        plane_bytes[0] = nrows * (cols / 2) + 64;                          // ql
-        plane_bytes[1] = nrows * (cols / 4) + 64;                          // qh
-        plane_bytes[2] = nrows * (cols / 16) + 64;                         // int8 group scales
-        plane_bytes[3] = nrows * static_cast<size_t>(w->nbp) * 2 + 64;     // f16 super-block scales
-    }
+    size_t plane_bytes[4];
+    plane_sizes(fmt, nrows, cols, plane_bytes);
     for (int i = 0; ok && i < 4; ++i)
         if (plane_bytes[i]) {
             ok = cudaMalloc(&w->plane[i], plane_bytes[i]) == cudaSuccess;
@@ -341,10 +356,33 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
     return w;
 }
 
+void drop_host_graphs(State& s);   // defined below
+
+// Frees the whole pointer-keyed set.  The reference evicts everything rather than a part (hip_backend.hip:462-471: the
+// loader asks for tensors in the same order every run, so a partial eviction would only churn).  Tensors uploaded through
+// zen_cuda_dev_upload belong to their caller and stay.
+void evict_resident_locked(State& s) {
+    cudaStreamSynchronize(s.stream);   // nothing queued may still read them
+    drop_host_graphs(s);               // captured calls name their addresses
+    for (auto& kv : s.resident) free_weights(s, kv.second);
+    s.resident.clear();
+    ++s.evictions;
+}
+
 zen_cuda_weights* lookup_locked(State& s, int fmt, const uint8_t* host, size_t rows, size_t cols) {
     const ResidentKey key{host, rows, cols, fmt};
     auto it = s.resident.find(key);
     if (it != s.resident.end()) return it->second;
+    if (s.vram_budget && block_bytes(fmt) && cols && cols % block_elems(fmt) == 0) {
+        size_t pb[4];
+        plane_sizes(fmt, rows, cols, pb);
+        const uint64_t need = pb[0] + pb[1] + pb[2] + pb[3];
+        if (s.stats.weight_bytes + need > s.vram_budget && !s.resident.empty()) evict_resident_locked(s);
+        if (s.stats.weight_bytes + need > s.vram_budget) {
+            set_error(s, "upload: the tensor does not fit the residency budget");
+            return nullptr;
+        }
+    }
     zen_cuda_weights* w = upload_locked(s, fmt, host, rows, cols, 0, rows);
     if (w) s.resident.emplace(key, w);
     return w;
@@ -988,6 +1026,21 @@ bool check_error_word(State& s) {
     return set_error(s, std::string("device-side error word: ") + zen_cuda_error_name(code) + " (code " + std::to_string(code) + ")");
 }
 
+// Resolves every tensor of one submission before anything is queued.  An eviction in the middle frees the tensors
+// resolved before it, so the pass is repeated once; a submission that evicts again does not fit the budget as a whole.
+// (The reference resolves first and launches after for the same reason, hip_backend.hip:625-636 and :784-797.)
+bool lookup_all_locked(State& s, int fmt, const uint8_t* const* weights, const size_t* rows, size_t count, size_t cols, const zen_cuda_weights** w) {
+    for (int pass = 0; pass < 2; ++pass) {
+        const uint64_t before = s.evictions;
+        for (size_t i = 0; i < count; ++i) {
+            w[i] = lookup_locked(s, fmt, weights[i], rows[i], cols);
+            if (!w[i]) return false;
+        }
+        if (s.evictions == before) return true;
+    }
+    return set_error(s, "the tensors of one submission do not fit the residency budget together");
+}
+
 // Host-pointer batched product: `count` tensors sharing `tokens` activation rows.
 // Outputs are token-major [tokens][rows_i] in the caller's buffers.
 bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weights, float* const* ys, const size_t* rows,
@@ -998,10 +1051,9 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     size_t total_rows = 0;
     for (size_t i = 0; i < count; ++i) {
         if (!weights[i] || !ys[i] || !rows[i]) return set_error(s, "bad task");
-        w[i] = lookup_locked(s, fmt, weights[i], rows[i], cols);
-        if (!w[i]) return false;
         total_rows += rows[i];
     }
+    if (!lookup_all_locked(s, fmt, weights, rows, count, cols, w)) return false;
     const size_t x_bytes = tokens * cols * sizeof(float), y_bytes = tokens * total_rows * sizeof(float);
     const bool direct = y_bytes <= kDirectResultBytes;
     if (!ensure_scratch(s, x_bytes, y_bytes)) return false;
@@ -1146,6 +1198,116 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     s.stats.readback_us += us_since(t0);
     ++s.stats.submits;
     if (count > 1) ++s.stats.batches;
+    return true;
+}
+
+// ---- the two other host-pointer submissions of the backend contract ------------------------------------------------
+// Both follow host_product's data path: small inputs are fetched from mapped host memory by a kernel and small results
+// are stored to mapped host memory by the copy-out kernel; anything larger crosses on the copy engine.
+
+// Lays `parts` (each padded to 16 bytes) end to end at the start of s.d_x.  offsets[i] receives part i's float offset.
+bool host_fetch_parts(State& s, const void* const* parts, const size_t* bytes, size_t nparts, size_t* offsets, size_t y_bytes) {
+    size_t total = 0;
+    for (size_t i = 0; i < nparts; ++i) { offsets[i] = total / sizeof(float); total += (bytes[i] + 15) & ~size_t(15); }
+    if (!ensure_scratch(s, total, y_bytes)) return false;
+    const bool direct = y_bytes <= kDirectResultBytes;
+    if (direct && !ensure_direct_result(s, y_bytes)) return false;
+    const auto t0 = clock_type::now();
+    const bool by_kernel = direct && total <= kDirectInputBytes;
+    uint8_t* stage = reinterpret_cast<uint8_t*>(by_kernel ? s.h_input : s.h_stage);
+    for (size_t i = 0; i < nparts; ++i) std::memcpy(stage + offsets[i] * sizeof(float), parts[i], bytes[i]);
+    if (by_kernel) {
+        const size_t n16 = total / sizeof(float4);
+        stage_in_kernel<<<static_cast<unsigned>(std::min<size_t>((n16 + 255) / 256, 32)), 256, 0, s.stream>>>(
+            reinterpret_cast<float4*>(s.d_x), reinterpret_cast<const float4*>(s.d_input), n16);
+        ++s.stats.dispatches;
+        if (cudaGetLastError() != cudaSuccess) return set_error(s, "activation fetch launch failed");
+    } else {
+        ZC_CUDA(s, cudaMemcpyAsync(s.d_x, s.h_stage, total, cudaMemcpyHostToDevice, s.stream));
+    }
+    s.stats.transfer_us += us_since(t0);
+    return true;
+}
+
+// Brings the first y_bytes of s.d_y to `y` and finishes the call (error word, counters).
+bool host_return(State& s, void* y, size_t y_bytes) {
+    auto t0 = clock_type::now();
+    const bool direct = y_bytes <= kDirectResultBytes;
+    if (direct) {
+        ++s.stats.dispatches;
+        if (launch_pdl(s, copy_out_publish_kernel, dim3(1), dim3(1024), 0, s.stream, reinterpret_cast<float4*>(s.d_result),
+                       reinterpret_cast<const float4*>(s.d_y), (y_bytes + 15) / 16, s.d_done, s.d_seq) != cudaSuccess)
+            return set_error(s, "result copy launch failed");
+        if (!wait_done(s, ++s.done_seq)) return false;
+    } else {
+        ZC_CUDA(s, cudaMemcpyAsync(s.h_stage, s.d_y, y_bytes, cudaMemcpyDeviceToHost, s.stream));
+        ZC_CUDA(s, cudaStreamSynchronize(s.stream));
+    }
+    s.stats.wait_us += us_since(t0);
+    if (!check_error_word(s)) return false;
+    t0 = clock_type::now();
+    std::memcpy(y, direct ? s.h_result : s.h_stage, y_bytes);
+    s.stats.readback_us += us_since(t0);
+    ++s.stats.submits;
+    return true;
+}
+
+// zen::hip::rms_norm_locked, hip_backend.hip:724-776: y[r] = x[r] * rsqrt(mean(x[r]^2) + eps) * weight, row by row.
+bool host_rms_norm(State& s, const float* x, const float* weight, float* y, size_t rows, size_t cols, float eps) {
+    if (!x || !weight || !y || !rows || !cols) return set_error(s, "rms_norm: bad arguments");
+    if (rows > (size_t(1) << 31) / cols) return set_error(s, "rms_norm: too large");
+    const size_t bytes = rows * cols * sizeof(float);
+    const void* parts[2] = {x, weight};
+    const size_t part_bytes[2] = {bytes, cols * sizeof(float)};
+    size_t off[2];
+    if (!host_fetch_parts(s, parts, part_bytes, 2, off, bytes)) return false;
+    const auto t0 = clock_type::now();
+    for (size_t r0 = 0; r0 < rows; r0 += 65535) {
+        const size_t nr = std::min<size_t>(65535, rows - r0);
+        const cudaError_t e = launch_pdl(s, zk::residual_rms_norm_kernel, dim3(static_cast<unsigned>(nr)), dim3(zk::kNormThreads), 0, s.stream,
+                                         s.d_x + off[0] + r0 * cols, static_cast<const float*>(nullptr), static_cast<const float*>(s.d_x + off[1]),
+                                         s.d_y + r0 * cols, static_cast<uint32_t>(cols), eps);
+        if (e != cudaSuccess) return set_error(s, std::string("rms_norm launch: ") + cudaGetErrorString(e));
+        ++s.stats.dispatches;
+    }
+    s.stats.launch_us += us_since(t0);
+    return host_return(s, y, bytes);
+}
+
+// zen::hip::gemv_ffn_locked, hip_backend.hip:778-870: y = down * (silu(gate * x) * (up * x)) as one submission, the
+// intermediate activation never leaving the device.  Two launches here: gate|up share one, and the down projection
+// applies silu(g) * u while it loads its activations.
+bool host_ffn(State& s, const uint8_t* gate, const uint8_t* up, const uint8_t* down, const float* x, float* y,
+              size_t ffn_rows, size_t cols, size_t out_rows) {
+    if (!gate || !up || !down || !x || !y || !ffn_rows || !out_rows || !cols) return set_error(s, "gemv_q8_0_ffn: bad arguments");
+    if (cols % 32 || ffn_rows % 32) return set_error(s, "gemv_q8_0_ffn: widths are not block aligned");
+    // all three resolved before anything is queued; a pass that evicted is repeated once
+    const zen_cuda_weights* w[3];
+    for (int pass = 0;; ++pass) {
+        const uint64_t before = s.evictions;
+        w[0] = lookup_locked(s, ZEN_CUDA_Q8_0, gate, ffn_rows, cols);
+        w[1] = w[0] ? lookup_locked(s, ZEN_CUDA_Q8_0, up, ffn_rows, cols) : nullptr;
+        w[2] = w[1] ? lookup_locked(s, ZEN_CUDA_Q8_0, down, out_rows, ffn_rows) : nullptr;
+        if (!w[2]) return false;
+        if (s.evictions == before) break;
+        if (pass) return set_error(s, "the tensors of one submission do not fit the residency budget together");
+    }
+    const int mode = s.q8_act_mode;
+    if (!max_tokens_per_launch(s, ZEN_CUDA_Q8_0, cols, mode) || !max_tokens_per_launch(s, ZEN_CUDA_Q8_0, ffn_rows, mode))
+        return set_error(s, "gemv_q8_0_ffn: one activation row does not fit shared memory");
+    const size_t out_pad = (out_rows + 63) & ~size_t(63);   // the result first (the copy-out kernel reads the start of the buffer)
+    const void* parts[1] = {x};
+    const size_t part_bytes[1] = {cols * sizeof(float)};
+    size_t off[1];
+    if (!host_fetch_parts(s, parts, part_bytes, 1, off, (out_pad + 2 * ffn_rows) * sizeof(float))) return false;
+    const auto t0 = clock_type::now();
+    float* d_gate_up[2] = {s.d_y + out_pad, s.d_y + out_pad + ffn_rows};
+    float* d_out[1] = {s.d_y};
+    if (!enqueue_gemv(s, w, d_gate_up, 2, s.d_x, 1, mode, s.stream)) return false;
+    if (!enqueue_gemv(s, w + 2, d_out, 1, d_gate_up[1], 1, mode, s.stream, nullptr, d_gate_up[0])) return false;
+    s.stats.launch_us += us_since(t0);
+    if (!host_return(s, y, out_rows * sizeof(float))) return false;
+    ++s.stats.batches;
     return true;
 }
 
@@ -1296,6 +1458,41 @@ int zen_cuda_gemm_kquant(const uint8_t* weights, const float* input, float* outp
     std::lock_guard<std::mutex> lock(s.mutex);
     if (!init_locked(s)) return 0;
     return host_product(s, q5 ? ZEN_CUDA_Q5_K : ZEN_CUDA_Q4_K, input, &weights, &output, &rows, 1, tokens, columns, ZEN_CUDA_ACT_FP32) ? 1 : 0;
+}
+
+/* ---- the backend contract's two fused submissions and the residency budget ---- */
+int zen_cuda_rms_norm(const float* x, const float* weight, float* y, size_t rows, size_t columns, float epsilon) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    return host_rms_norm(s, x, weight, y, rows, columns, epsilon) ? 1 : 0;
+}
+
+int zen_cuda_gemv_q8_0_ffn(const uint8_t* gate, const uint8_t* up, const uint8_t* down, const float* x, float* y, size_t ffn_rows,
+                           size_t columns, size_t out_rows) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    return host_ffn(s, gate, up, down, x, y, ffn_rows, columns, out_rows) ? 1 : 0;
+}
+
+int zen_cuda_set_vram_budget(uint64_t bytes) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    s.vram_budget = bytes ? bytes : default_vram_budget(s);
+    return 1;
+}
+
+int zen_cuda_residency(uint64_t* budget_bytes, uint64_t* held_bytes, uint64_t* tensors, uint64_t* evictions) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!s.ready) return 0;
+    if (budget_bytes) *budget_bytes = s.vram_budget;
+    if (held_bytes) *held_bytes = s.stats.weight_bytes;
+    if (tensors) *tensors = s.resident.size();
+    if (evictions) *evictions = s.evictions;
+    return 1;
 }
 
 void zen_cuda_release_weights(const uint8_t* weights) {
