@@ -289,13 +289,15 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
     handles = [be.dev_upload("Q8_0", packed, GEMM_ROWS, GEMM_COLS) for _ in range(GEMM_COPIES)]
     d_x = torch.from_numpy(x_host).to(dev)
     outs = [torch.empty((GEMM_T, GEMM_ROWS), dtype=torch.float32, device=dev) for _ in range(GEMM_COPIES)]
-    ws_bytes = be.gemm_workspace_bytes(GEMM_T, GEMM_COLS)
+    from zeninfer_b200.backend import ACT_FP32, ACT_INT8
+    ws_bytes = be.gemm_workspace_bytes(GEMM_T, GEMM_COLS, ACT_FP32)      # large enough for either mode
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     stream = torch.cuda.Stream(device=dev)
+    main_mode = ACT_FP32 if args.act == "fp32" else ACT_INT8
 
-    def one_pass():
+    def one_pass(mode=main_mode):
         for h, o in zip(handles, outs):
-            be.dev_gemm_q8_0([h], [o.data_ptr()], d_x.data_ptr(), GEMM_T, ws.data_ptr(), ws_bytes, stream.cuda_stream)
+            be.dev_gemm_q8_0([h], [o.data_ptr()], d_x.data_ptr(), GEMM_T, ws.data_ptr(), ws_bytes, stream.cuda_stream, act_mode=mode)
 
     steps = 1 if args.profile else 250 if brief else max(1, args.steps // GEMM_COPIES)  # a graph replay is GEMM_COPIES steps
     with torch.cuda.stream(stream):
@@ -322,6 +324,25 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
     be.dev_check(stream.cuda_stream)
     n_products = steps * GEMM_COPIES
     per_product_us = ms * 1e3 / n_products
+    # the other activation mode, plain launches over the same rotating copies (the products are long enough to hide them)
+    other_mode = ACT_INT8 if main_mode == ACT_FP32 else ACT_FP32
+    other_us = None
+    if not args.profile:
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                one_pass(other_mode)
+            stream.synchronize()
+            e0.record(stream)
+            n_other = 10 if brief else 25
+            for _ in range(n_other):
+                one_pass(other_mode)
+            e1.record(stream)
+            stream.synchronize()
+        other_us = e0.elapsed_time(e1) * 1e3 / (n_other * GEMM_COPIES)
+        with torch.cuda.stream(stream):
+            one_pass()                       # the outputs hold the timed mode's results again
+        be.dev_check(stream.cuda_stream)
+    mode_name = {ACT_INT8: "int8_activations", ACT_FP32: "fp32_equivalent_activations"}
     value = GEMM_OPS / (per_product_us * 1e-6) / 1e12
     peak, peak_kind = int8_peak_tops()
 
@@ -330,6 +351,7 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
                 "launches": "per product: quantize_acts_gemm_kernel, gemm_zero_split_tiles_kernel, gemm_q8_0_i8_kernel; 4 products untimed, 4 + 4 replayed"}
     # e2e: the host-pointer call, activations host->device and the 29 MB result device->host inside the timed region
     copies = [packed] + [packed.copy() for _ in range(GEMM_COPIES - 1)]
+    be.set_q8_act_mode(main_mode)
     for c in copies:
         y_host = be.gemm("Q8_0", c, x_host, GEMM_T, GEMM_ROWS, GEMM_COLS)
     e2e_steps = 1 if brief else 3
@@ -341,6 +363,7 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
     e2e_value = GEMM_OPS * e2e_steps * GEMM_COPIES / e2e_s / 1e12
     assert np.array_equal(y_host, outs[-1].cpu().numpy()), "host-pointer and device-pointer paths disagree"
 
+    be.set_q8_act_mode(ACT_INT8)
     for c in copies:
         be.release_weights(c)
     for h in handles:
@@ -369,7 +392,9 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
         "config": {"workload": "Q8_0 prefill GEMM 512 x 14336 x 4096 (config 1): activation quantise + tcgen05 kind::i8 GEMM per step",
                    "l2": f"inputs larger than L2: {GEMM_COPIES} weight copies and output buffers, 100 MB per product", "launch": "CUDA graph replay"},
         "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TOPS", "frac": value / peak, "peak_kind": peak_kind, "traffic": GEMM_NCU_TRAFFIC_BYTES,
-                     "launch_us": per_product_us, "algorithmic_ops_per_launch": GEMM_OPS,
+                     "launch_us": per_product_us, "algorithmic_ops_per_launch": GEMM_OPS, "activations": mode_name[main_mode],
+                     "other_mode": {"activations": mode_name[other_mode], "launch_us": other_us, "tops_of_the_same_product": GEMM_OPS / (other_us * 1e-6) / 1e12,
+                                    "note": "fp32-equivalent = two int8 digits per activation, two MMAs per block (the reference's default prefill arithmetic)"},
                      "note": "time includes the activation-quantise kernel; the per-block scale epilogue runs on CUDA cores and bounds the kernel"},
         "cpu_baseline": cpu, "clocks": clocks.summary(),
         "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": GEMM_T * GEMM_COLS * 4, "d2h_bytes_per_step": GEMM_T * GEMM_ROWS * 4,
@@ -959,6 +984,8 @@ def brief_detail(line: dict | None, keep: tuple[str, ...]) -> dict | None:
     out["frac_of_peak"] = line["roofline"]["frac"]
     out["peak"] = {"value": line["roofline"]["peak"], "unit": line["roofline"]["unit"], "kind": line["roofline"]["peak_kind"]}
     out["workload"] = line["config"]["workload"]
+    if line["roofline"].get("other_mode"):
+        out["other_mode"] = line["roofline"]["other_mode"]
     for k in keep:
         if k in line["config"]:
             out[k] = line["config"][k]
@@ -1196,6 +1223,7 @@ def main() -> None:
                          "as the timed step, no end-to-end leg, no CPU baseline, no detail (its figures are not benchmark values)")
     ap.add_argument("--layers", type=int, default=0, help="workload decode: number of layers (default: the configuration's 32)")
     ap.add_argument("--formats", default="Q8_0,Q4_0,Q6_K", help="workload layer_sweep: formats to run")
+    ap.add_argument("--act", default="int8", choices=["int8", "fp32"], help="workload q8_0_gemm: activation mode of the timed product (the other one is timed briefly beside it)")
     ap.add_argument("--no-detail", action="store_true", help="default workload: skip the short runs of the other workloads that fill `detail`")
     ap.add_argument("--device-pack", action="store_true", help="workload lm_head: draw and pack the Q6_K matrix on the GPU (torch) instead of numpy")
     ap.add_argument("--cut", default="rows+cols", choices=["rows", "rows+cols"],

@@ -250,6 +250,15 @@ int zen_cuda_dev_gemv_list(const zen_cuda_gemv_list* list, void* stream);
 size_t zen_cuda_gemm_workspace_bytes(size_t tokens, size_t columns);
 int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x,
                            size_t tokens, void* workspace, size_t workspace_bytes, void* stream);
+/* The same product with the activation mode named.  ZEN_CUDA_ACT_FP32 is the tensor-core counterpart of the reference's
+ * default prefill kernel, which takes fp32 activations (src/quant.cpp:1667-1680 -> gemm_q8_0_kblk_avx2,
+ * kernels/avx2.cpp:878-1248): every activation enters as two int8 digits, a block costs two MMAs, and results stay
+ * within ~1e-5 of the fp32-activation product (the bar is 1e-3).  Its workspace also holds the second digit:
+ * zen_cuda_gemm_workspace_bytes_act(tokens, columns, act_mode).  The host-pointer calls (zen_cuda_gemm_q8_0,
+ * zen_cuda_gemm_q8_0_batch) take this path for more than eight tokens in either mode. */
+size_t zen_cuda_gemm_workspace_bytes_act(size_t tokens, size_t columns, int act_mode);
+int zen_cuda_dev_gemm_q8_0_act(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x,
+                               size_t tokens, int act_mode, void* workspace, size_t workspace_bytes, void* stream);
 
 /* No counterpart in the reference.  The same prefill product as zen_cuda_dev_gemm_q8_0 for ONE tensor, for callers
  * that may not allocate device memory at the time of the call: a plug-in living inside a host runtime that owns all of

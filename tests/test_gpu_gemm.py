@@ -7,9 +7,9 @@ scales, sum_b d_x d_w sum_k q_x q_w equals (q_x * d_x) @ (q_w * d_w)^T evaluated
 import numpy as np
 import pytest
 
-from helpers import assert_parity, seeded_acts, seeded_weights
+from helpers import assert_parity, ref_fp32_f64, seeded_acts, seeded_weights
 from zeninfer_b200 import blocks
-from zeninfer_b200.backend import ACT_INT8
+from zeninfer_b200.backend import ACT_FP32, ACT_INT8, BackendError
 
 pytestmark = pytest.mark.gpu
 Q8_0 = blocks.Q8_0
@@ -103,3 +103,99 @@ def test_config1_full_size(be, zo):
     ref = zo.gemm(Q8_0, sub, x[:32], 32, len(sel), cols, int8_acts=True)
     assert_parity(got[:32][:, sel], ref, what="config 1 sampled rows vs oracle")
     be.release_weights(w)
+
+
+# ---- fp32-equivalent activations (two int8 digits per element) on the same tensor-core kernel: the counterpart of the
+# reference's default prefill path, which takes fp32 activations (src/quant.cpp:1667-1680, kernels/avx2.cpp:878-1248)
+
+@pytest.fixture()
+def be_fp32(be):
+    be.set_q8_act_mode(ACT_FP32)
+    yield be
+    be.set_q8_act_mode(ACT_INT8)
+
+
+@pytest.mark.parametrize("tokens,rows,cols", [
+    (9, 128, 128), (16, 100, 544), (17, 300, 96), (33, 67, 32), (64, 256, 4096), (65, 130, 2048),
+    (129, 129, 4096), (171, 2048, 2048), (256, 1000, 14336), (300, 4096, 4096)])
+def test_gemm_fp32_mode_vs_fp32_oracle(be_fp32, zo, tokens, rows, cols):
+    w = seeded_weights(Q8_0, rows, cols, 500 + rows)
+    x = seeded_acts(tokens, cols, 600 + tokens)
+    x[0, :32] = 0.0                                   # an all-zero block: scale 0, both digits 0
+    x[1 % tokens, 5] = 20.0                           # a 20-sigma outlier stretches its block's scale (the digits resolve amax / 65024)
+    got = be_fp32.gemm("Q8_0", w, x, tokens, rows, cols)
+    if tokens * rows * cols <= 64 * 256 * 4096:
+        assert_parity(got, zo.gemm(Q8_0, w, x, tokens, rows, cols, int8_acts=False), what=f"fp32-mode gemm {tokens}x{rows}x{cols} vs oracle")
+    rel = assert_parity(got, ref_fp32_f64(Q8_0, w, x, rows, cols), what=f"fp32-mode gemm {tokens}x{rows}x{cols} vs float64")
+    assert rel < 1e-4                                 # two digits: far inside the bar
+    be_fp32.release_weights(w)
+
+
+def test_gemm_fp32_mode_token_ladder_from_reference(be_fp32, zo):
+    # tests/core_tests.cpp:345-372 again, now against the fp32-activation kernels the reference runs by default there.
+    # Unit block scales and codes up to +-128 make this the hard case for two activation digits: an activation is
+    # resolved to d_x / 512, so a result may be off by sum_k |w[r,k]| * d_x[t, block(k)] / 512.  The test holds the kernel
+    # to that bound element by element (plus the gate on max_abs / max_ref); the reference's own absolute gate of 1e-3
+    # on results near zero is missed here by a factor of about 1.4, which the two-digit scheme cannot close.
+    rows, cols = 100, 544
+    r = np.arange(rows)[:, None, None]
+    blk = np.arange(17)[None, :, None]
+    j = np.arange(2, 34)[None, None, :]
+    packed = np.zeros((rows, 17, 34), np.uint8)
+    packed[..., 1] = 0x3C
+    packed[..., 2:] = (r * 5 + blk * 11 + j * 3) & 255
+    packed = np.ascontiguousarray(packed.reshape(rows, -1))
+    w_abs = np.abs(blocks.dequantize(Q8_0, packed, rows, cols).astype(np.float64)).reshape(rows, 17, 32).sum(axis=2)    # [rows, blocks]
+    for T in (9, 16, 32, 171):
+        t = np.arange(T)[:, None]
+        c = np.arange(cols)[None, :]
+        xin = (((t * 7 + c) % 15 - 7).astype(np.float32) * np.float32(0.017)).astype(np.float32)
+        got = be_fp32.gemm("Q8_0", packed, xin, T, rows, cols).astype(np.float64)
+        ref = ref_fp32_f64(Q8_0, packed, xin, rows, cols)
+        assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-4
+        d_x = zo.quantise_acts(xin)[1].astype(np.float64)                       # [T, blocks]
+        bound = d_x @ w_abs.T / 512.0 + 1e-5 * np.maximum(1.0, np.abs(ref))     # + fp32 accumulation slack
+        assert np.all(np.abs(got - ref) <= bound), float((np.abs(got - ref) / bound).max())
+        assert np.abs(got - ref).max() < 3e-3
+    be_fp32.release_weights(packed)
+
+
+def test_gemm_fp32_mode_batch_and_device_call(be_fp32, zo):
+    import torch
+    cols, rows, tokens = 1024, [12800, 3190, 3200, 130], 40      # 150 row tiles in one launch and a second launch
+    ws = [seeded_weights(Q8_0, r, cols, 530 + i) for i, r in enumerate(rows)]
+    x = seeded_acts(tokens, cols, 540)
+    outs = be_fp32.gemm_batch("Q8_0", ws, x, rows, tokens, cols)
+    for w, r, o in zip(ws, rows, outs):
+        assert_parity(o, ref_fp32_f64(Q8_0, w, x, r, cols), what=f"fp32-mode batched gemm rows={r}")
+    # device pointers: same kernel, caller's workspace
+    handles = [be_fp32.dev_upload("Q8_0", w, r, cols) for w, r in zip(ws[:3], rows[:3])]
+    d_x = torch.from_numpy(x).cuda()
+    d_out = [torch.empty(tokens, r, device="cuda") for r in rows[:3]]
+    nbytes = be_fp32.gemm_workspace_bytes(tokens, cols, ACT_FP32)
+    assert nbytes > be_fp32.gemm_workspace_bytes(tokens, cols, ACT_INT8)
+    ws_dev = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    be_fp32.dev_gemm_q8_0(handles, [o.data_ptr() for o in d_out], d_x.data_ptr(), tokens, ws_dev.data_ptr(), nbytes, act_mode=ACT_FP32)
+    be_fp32.dev_check()
+    for o, host in zip(d_out, outs):
+        assert np.array_equal(o.cpu().numpy(), host)
+    with pytest.raises(BackendError, match="workspace too small"):
+        be_fp32.dev_gemm_q8_0(handles, [o.data_ptr() for o in d_out], d_x.data_ptr(), tokens, ws_dev.data_ptr(),
+                              be_fp32.gemm_workspace_bytes(tokens, cols, ACT_INT8), act_mode=ACT_FP32)
+    for h in handles:
+        be_fp32.dev_free(h)
+    for w in ws:
+        be_fp32.release_weights(w)
+
+
+def test_config1_full_size_fp32_mode(be_fp32, zo):
+    tokens, rows, cols = 512, 14336, 4096
+    w = seeded_weights(Q8_0, rows, cols, 3)
+    x = seeded_acts(tokens, cols, 2)
+    got = be_fp32.gemm("Q8_0", w, x, tokens, rows, cols)
+    rel = assert_parity(got, ref_fp32_f64(Q8_0, w, x, rows, cols), what="config 1, fp32-equivalent activations, vs float64")
+    assert rel < 1e-4
+    sel = np.arange(0, rows, 997)
+    sub = np.ascontiguousarray(w[sel])
+    assert_parity(got[:32][:, sel], zo.gemm(Q8_0, sub, x[:32], 32, len(sel), cols, int8_acts=False), what="config 1 sampled rows vs the fp32 oracle")
+    be_fp32.release_weights(w)

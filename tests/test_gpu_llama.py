@@ -420,3 +420,24 @@ def test_batched_prefill_matches_token_by_token(be, golden):
         assert_parity(lb, la, 1e-3, "logits after a batched prefill vs token by token")
     finally:
         dec.close()
+
+
+@pytest.mark.parametrize("decode_mode", [ACT_FP32, ACT_INT8])
+def test_batched_prefill_with_fp32_equivalent_activations(be, golden, decode_mode):
+    # the prompt block on the tensor cores with two activation digits: the reference's default prompt arithmetic
+    # (fp32 activations for more than one token, src/quant.cpp:1667-1680), with either decode mode behind it
+    cfg, meta, _, _, _ = golden
+    prompt = np.random.default_rng(78).integers(3, cfg.vocab, size=45).tolist()
+    dec = LlamaDecoder(be, cfg, synthetic_tensors(cfg, meta["seed"], meta["weight_std"]), act_mode=decode_mode, prompt_act_mode=ACT_FP32)
+    try:
+        dec.PREFILL_CHUNK = 32
+        dec._pf = None
+        a = dec.generate(prompt, 1, batched_prefill=False)
+        la = dec.last_logits()
+        b = dec.generate(prompt, 1)                      # the default: blocks through prefill()
+        lb = dec.last_logits()
+        assert a == b
+        # first pick: fp32-equivalent products both ways (the head alone runs in the decode mode, on the same input up to 1e-5)
+        assert_parity(lb, la, 1e-3 if decode_mode == ACT_FP32 else 5e-3, "first logits after a two-digit block prefill vs token by token")
+    finally:
+        dec.close()

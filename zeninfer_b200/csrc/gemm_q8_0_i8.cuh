@@ -19,6 +19,13 @@
 // Weights are the M operand so that, for a fixed token, the 32 lanes of a warp hold 32 consecutive weight rows:
 // the token-major output [T][rows] is written with full 128-byte lines.
 //
+// Two activation digits (kDigits == 2): the reference's default prefill kernel takes fp32 activations
+// (src/quant.cpp:1667-1680 -> gemm_q8_0_kblk_avx2, kernels/avx2.cpp:878-1248).  Here an activation enters as
+// (d/256) * (256 * q1 + q2), q1 the Q8 code and q2 the code of the residual (quantize_acts.cuh; error below d/512), so
+// a block costs two MMAs (weights x q1, weights x q2) into the two buffers of a TMEM pair, and the epilogue forms
+// 256 * S1 + S2 with one integer multiply-add before the single conversion.  |256 * S1 + S2| < 2^27, so that
+// conversion rounds at 2^-24 relative: the result stays within ~1e-5 of the fp32-activation product.
+//
 // Roofline: the tensor work is 2*T*rows*K int8 operations.  The epilogue costs one conversion and two fp32
 // operations per (row, token, block) on CUDA cores, about six times the tensor time of the block's MMA, so
 // this kernel is bound by the fp32/int32 pipes, not by the tensor pipe.
@@ -48,6 +55,7 @@ constexpr int kGemmMaxTensors = 3;     // weight tensors of one launch (they sha
 struct GemmParams {
     CUtensorMap map_w[kGemmMaxTensors];  // weight codes  [rows][K] int8, box 128 B x 128 rows, SWIZZLE_128B
     CUtensorMap map_x;                 // act codes     [tokens_padded][K] int8, box 128 B x n_tile rows, SWIZZLE_128B
+    CUtensorMap map_x2;                // fine digits   same shape (two-digit kernels only)
     CUtensorMap map_xs;                // act scales    [nb][t_ld] fp32 (block-major), box n_tile x 4
     const __half* w_scales[kGemmMaxTensors];   // [rows][nbp]
     float* out[kGemmMaxTensors];               // [tokens][rows]
@@ -60,11 +68,11 @@ struct GemmParams {
     int* error_word;
 };
 
-__host__ __device__ inline uint32_t gemm_stage_bytes(uint32_t n_tile) {
-    return kGemmM * kGemmKTile + n_tile * kGemmKTile + kGemmBlocksPerTile * n_tile * 4;
+__host__ __device__ inline uint32_t gemm_stage_bytes(uint32_t n_tile, uint32_t digits = 1) {
+    return kGemmM * kGemmKTile + digits * n_tile * kGemmKTile + kGemmBlocksPerTile * n_tile * 4;
 }
-__host__ __device__ inline size_t gemm_smem_bytes(uint32_t n_tile) {
-    return 1024 /* alignment slack */ + static_cast<size_t>(kGemmStages) * gemm_stage_bytes(n_tile) + 256 /* barriers */;
+__host__ __device__ inline size_t gemm_smem_bytes(uint32_t n_tile, uint32_t digits = 1) {
+    return 1024 /* alignment slack */ + static_cast<size_t>(kGemmStages) * gemm_stage_bytes(n_tile, digits) + 256 /* barriers */;
 }
 
 // Packed fp32 pairs (sm_100 f32x2 arithmetic): one instruction scales or accumulates two token columns.
@@ -113,6 +121,17 @@ __device__ __forceinline__ void gemm_fma32(const uint32_t (&v)[32], uint64_t sw2
     ZK_LDS128(s, sx_addr, 80);  gemm_fma4(v + 20, sw2, s, acc + 10);
     ZK_LDS128(s, sx_addr, 96);  gemm_fma4(v + 24, sw2, s, acc + 12);
     ZK_LDS128(s, sx_addr, 112); gemm_fma4(v + 28, sw2, s, acc + 14);
+}
+
+// Sixteen token columns of a two-digit block: v1 holds the sums over the Q8 codes, v2 those over the fine digits.
+__device__ __forceinline__ void gemm_fma16_two(uint32_t (&v1)[16], const uint32_t (&v2)[16], uint64_t sw2, uint32_t sx_addr, uint64_t* __restrict__ acc) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v1[i] = static_cast<uint32_t>(static_cast<int>(v1[i]) * 256 + static_cast<int>(v2[i]));
+    uint4 s;
+    ZK_LDS128(s, sx_addr, 0);   gemm_fma4(v1 + 0, sw2, s, acc + 0);
+    ZK_LDS128(s, sx_addr, 16);  gemm_fma4(v1 + 4, sw2, s, acc + 2);
+    ZK_LDS128(s, sx_addr, 32);  gemm_fma4(v1 + 8, sw2, s, acc + 4);
+    ZK_LDS128(s, sx_addr, 48);  gemm_fma4(v1 + 12, sw2, s, acc + 6);
 }
 
 // Which tensor a row tile of the launch belongs to, and its index there.
@@ -169,12 +188,15 @@ __global__ void gemm_zero_split_tiles_kernel(const __grid_constant__ GemmParams 
 
 // Eighteen warps put five on one of the SM's four register files (16384 registers each), so 96 registers per thread is
 // the ceiling: 5 x 32 x 96 = 15360.
-template <int kNTile>
+template <int kNTile, int kDigits = 1>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __grid_constant__ GemmParams p) {
+    static_assert(kDigits == 1 || kDigits == 2, "one or two activation digits");
     constexpr int kNHalf = kNTile / kGemmSplit;     // token columns per epilogue warp
     static_assert(kNHalf % 32 == 0, "an epilogue warp takes whole 32-column chunks");
     constexpr uint32_t kPairs = 2;                   // TMEM accumulator buffers come in pairs: one hand-off per two blocks
-    constexpr uint32_t kStageBytes = kGemmM * kGemmKTile + kNTile * kGemmKTile + kGemmBlocksPerTile * kNTile * 4;
+    constexpr uint32_t kStageBytes = kGemmM * kGemmKTile + kDigits * kNTile * kGemmKTile + kGemmBlocksPerTile * kNTile * 4;
+    constexpr uint32_t kScaleOff = kGemmM * kGemmKTile + kDigits * kNTile * kGemmKTile;   // the stage: weights | codes | (fine digits) | scales
+    static_assert(kStageBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
     constexpr uint32_t kTmemCols = 2 * kPairs * kNTile;  // 512: a power of two
     static_assert(kTmemCols == 512, "four accumulator buffers of 128 columns");
     extern __shared__ uint8_t smem_raw[];
@@ -202,6 +224,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
         mbar_fence_init();
         for (uint32_t i = 0; i < p.tensors; ++i) tma_prefetch_descriptor(&p.map_w[i]);
         tma_prefetch_descriptor(&p.map_x);
+        if (kDigits == 2) tma_prefetch_descriptor(&p.map_x2);
         tma_prefetch_descriptor(&p.map_xs);
     }
     if (warp == 1) tmem_alloc(tmem_base_slot, kTmemCols);
@@ -232,8 +255,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                     mbar_arrive_expect_tx(&full[stage], kStageBytes);
                     tma_load_2d(st, map_w, static_cast<int>(kt * kGemmKTile), static_cast<int>(mt * kGemmM), &full[stage]);
                     tma_load_2d(st + kGemmM * kGemmKTile, &p.map_x, static_cast<int>(kt * kGemmKTile), static_cast<int>(nt * kNTile), &full[stage]);
-                    tma_load_2d(st + kGemmM * kGemmKTile + kNTile * kGemmKTile, &p.map_xs, static_cast<int>(nt * kNTile),
-                                static_cast<int>(kt * kGemmBlocksPerTile), &full[stage]);
+                    if (kDigits == 2)
+                        tma_load_2d(st + kGemmM * kGemmKTile + kNTile * kGemmKTile, &p.map_x2, static_cast<int>(kt * kGemmKTile), static_cast<int>(nt * kNTile), &full[stage]);
+                    tma_load_2d(st + kScaleOff, &p.map_xs, static_cast<int>(nt * kNTile), static_cast<int>(kt * kGemmBlocksPerTile), &full[stage]);
                 }
             }
         }
@@ -256,7 +280,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                     const uint32_t a_addr = smem_u32(smem + stage * kStageBytes);
                     const uint64_t a_desc = umma_desc_k_sw128(a_addr), b_desc = umma_desc_k_sw128(a_addr + kGemmM * kGemmKTile);
                     const uint32_t nblk = min(static_cast<uint32_t>(kGemmBlocksPerTile), p.nb - kt * kGemmBlocksPerTile);
-                    for (uint32_t j0 = 0; j0 < nblk; j0 += 2, ++pair) {
+                    for (uint32_t j0 = 0; j0 < nblk; j0 += (kDigits == 2 ? 1 : 2), ++pair) {
                         const uint32_t pr = pair % kPairs;
                         if (pair >= kPairs) {
                             if (!mbar_wait(&tmem_empty[pr], ((pair / kPairs) - 1) & 1)) {
@@ -266,8 +290,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                             tc_fence_after_sync();
                         }
                         // one Q8_0 block per instruction: 32 bytes of K = two 16-byte units further into the swizzle atom
-                        tc_mma_i8(tmem_base + (2 * pr) * kNTile, a_desc + 2 * j0, b_desc + 2 * j0, idesc, 0u);
-                        if (j0 + 1 < nblk) tc_mma_i8(tmem_base + (2 * pr + 1) * kNTile, a_desc + 2 * (j0 + 1), b_desc + 2 * (j0 + 1), idesc, 0u);
+                        if (kDigits == 2) {   // the block's two digits fill the pair
+                            const uint64_t b2_desc = umma_desc_k_sw128(a_addr + kGemmM * kGemmKTile + kNTile * kGemmKTile);
+                            tc_mma_i8(tmem_base + (2 * pr) * kNTile, a_desc + 2 * j0, b_desc + 2 * j0, idesc, 0u);
+                            tc_mma_i8(tmem_base + (2 * pr + 1) * kNTile, a_desc + 2 * j0, b2_desc + 2 * j0, idesc, 0u);
+                        } else {
+                            tc_mma_i8(tmem_base + (2 * pr) * kNTile, a_desc + 2 * j0, b_desc + 2 * j0, idesc, 0u);
+                            if (j0 + 1 < nblk) tc_mma_i8(tmem_base + (2 * pr + 1) * kNTile, a_desc + 2 * (j0 + 1), b_desc + 2 * (j0 + 1), idesc, 0u);
+                        }
                         tc_commit(&tmem_full[pr]);
                     }
                     if (ok) tc_commit(&empty[stage]);  // the stage is free once its MMAs have read it
@@ -304,10 +334,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                     ok = false;
                     break;
                 }
-                const uint32_t sxs = smem_u32(smem + stage * kStageBytes + kGemmM * kGemmKTile + kNTile * kGemmKTile) + half * kNHalf * 4;
+                const uint32_t sxs = smem_u32(smem + stage * kStageBytes + kScaleOff) + half * kNHalf * 4;
                 const __half2 h01 = *reinterpret_cast<const __half2*>(&sw4.x), h23 = *reinterpret_cast<const __half2*>(&sw4.y);
                 const float swf[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
                 const uint32_t nblk = min(static_cast<uint32_t>(kGemmBlocksPerTile), p.nb - kt * kGemmBlocksPerTile);
+                if constexpr (kDigits == 2) {
+#pragma unroll
+                    for (uint32_t j = 0; j < kGemmBlocksPerTile; ++j) {
+                        if (j < nblk && ok) {
+                            const uint32_t pr = pair % kPairs;
+                            if (!mbar_wait(&tmem_full[pr], (pair / kPairs) & 1)) {
+                                if (lane == 0) { *abort_word = 1; atomicExch(p.error_word, kErrTmemWaitTimeout); }
+                                ok = false;
+                            } else {
+                                tc_fence_after_sync();
+                                const uint64_t sw2 = pack2(swf[j] * 0.00390625f, swf[j] * 0.00390625f);   // the digits' common unit is d / 256
+                                uint32_t v1[16], v2[16];
+#pragma unroll
+                                for (int c = 0; c < kNHalf; c += 16) {
+                                    tmem_ld_32x16(taddr0 + (2 * pr) * kNTile + c, v1);
+                                    tmem_ld_32x16(taddr0 + (2 * pr + 1) * kNTile + c, v2);
+                                    tmem_ld_wait();
+                                    if (c + 16 == kNHalf) { tc_fence_before_sync(); __syncwarp(); if (lane == 0) mbar_arrive(&tmem_empty[pr]); }
+                                    gemm_fma16_two(v1, v2, sw2, sxs + (j * kNTile + c) * 4, acc + c / 2);
+                                }
+                                ++pair;
+                            }
+                        }
+                    }
+                } else {
 #pragma unroll
                 for (uint32_t j0 = 0; j0 < kGemmBlocksPerTile; j0 += 2) {
                     if (j0 < nblk && ok) {
@@ -342,6 +397,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                             ++pair;
                         }
                     }
+                }
                 }
                 if (!ok) break;
                 __syncwarp();
@@ -378,8 +434,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
 
 // Activation quantiser for the GEMM: codes [t_pad][K] int8 (rows >= tokens are zero-filled by the caller's memset)
 // and scales in block-major order [nb][t_ld] fp32, so the scales of one block for a tile of tokens are contiguous.
+// q2 != nullptr: also the fine digits of the two-digit kernels.
 __global__ void __launch_bounds__(256) quantize_acts_gemm_kernel(const float* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ sc_t,
-                                                                 uint32_t tokens, uint32_t nb, uint32_t t_ld) {
+                                                                 uint32_t tokens, uint32_t nb, uint32_t t_ld, int8_t* __restrict__ q2) {
     const size_t wid = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wid >= static_cast<size_t>(tokens) * nb) return;
@@ -387,6 +444,7 @@ __global__ void __launch_bounds__(256) quantize_acts_gemm_kernel(const float* __
     int c1, c2;
     const float d = quantise_block_lane(x[wid * 32 + lane], c1, c2);
     q[wid * 32 + lane] = static_cast<int8_t>(c1);
+    if (q2) q2[wid * 32 + lane] = static_cast<int8_t>(c2);   // the fine digit, same layout
     if (lane == 0) sc_t[static_cast<size_t>(b) * t_ld + t] = d;
 }
 

@@ -758,43 +758,51 @@ bool make_map_2d(State& s, CUtensorMap* map, CUtensorMapDataType type, size_t el
     return true;
 }
 
-size_t gemm_ws_bytes(size_t tokens, size_t cols) {
+// Workspace of one prefill product: codes [tokens][cols] int8 (padded to 256 bytes), block-major scales [cols/32][t_ld]
+// fp32 and, with two activation digits, the fine digits [tokens][cols] behind them on the next 256-byte boundary.
+size_t gemm_ws_bytes(size_t tokens, size_t cols, int digits = 1) {
     const size_t t_ld = (tokens + 3) & ~size_t(3);
-    return ((tokens * cols + 255) & ~size_t(255)) + (cols / 32) * t_ld * sizeof(float);
+    const size_t codes = (tokens * cols + 255) & ~size_t(255);
+    const size_t one = codes + (cols / 32) * t_ld * sizeof(float);
+    return digits == 2 ? ((one + 255) & ~size_t(255)) + codes : one;
 }
 
 // The shared-memory opt-in of the GEMM kernel; done once, at start-up (it loads the kernel's module, which may allocate).
-template <int kNTile>
+template <int kNTile, int kDigits = 1>
 cudaError_t configure_gemm() {
     static bool configured = false;
     if (configured) return cudaSuccess;
-    const cudaError_t e = cudaFuncSetAttribute(&zk::gemm_q8_0_i8_kernel<kNTile>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(zk::gemm_smem_bytes(kNTile)));
+    const cudaError_t e = cudaFuncSetAttribute(&zk::gemm_q8_0_i8_kernel<kNTile, kDigits>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(zk::gemm_smem_bytes(kNTile, kDigits)));
     if (e == cudaSuccess) configured = true;
     return e;
 }
 
-template <int kNTile>
+template <int kNTile, int kDigits = 1>
 cudaError_t launch_gemm(const zk::GemmParams& p, unsigned grid, cudaStream_t st) {
-    const cudaError_t e = configure_gemm<kNTile>();
+    const cudaError_t e = configure_gemm<kNTile, kDigits>();
     if (e != cudaSuccess) return e;
-    zk::gemm_q8_0_i8_kernel<kNTile><<<grid, zk::kGemmThreads, zk::gemm_smem_bytes(kNTile), st>>>(p);
+    zk::gemm_q8_0_i8_kernel<kNTile, kDigits><<<grid, zk::kGemmThreads, zk::gemm_smem_bytes(kNTile, kDigits), st>>>(p);
     return cudaGetLastError();
 }
 
 // Quantises d_x [tokens][cols] into the workspace `ws` (gemm_ws_bytes) and enqueues one GEMM per tensor.
-// Everything is stream-ordered on `st`; `ws` must stay untouched until the work has run.
+// Everything is stream-ordered on `st`; `ws` must stay untouched until the work has run.  act_mode ZEN_CUDA_ACT_FP32:
+// two activation digits (the workspace is the larger one, gemm_ws_bytes(..., 2)).
 bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x, size_t tokens,
-                       uint8_t* ws, cudaStream_t st) {
+                       uint8_t* ws, cudaStream_t st, int act_mode = ZEN_CUDA_ACT_INT8) {
     if (!count || !tokens || !d_x || !ws) return set_error(s, "gemm: bad arguments");
+    if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemm: bad activation mode");
+    const int digits = act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1;
     const size_t cols = w[0]->cols;
     const uint32_t nb = w[0]->nb;
     const size_t t_ld = (tokens + 3) & ~size_t(3);
     int8_t* xq = reinterpret_cast<int8_t*>(ws);
     float* xs_t = reinterpret_cast<float*>(ws + ((tokens * cols + 255) & ~size_t(255)));
+    int8_t* xq2 = digits == 2 ? reinterpret_cast<int8_t*>(ws + ((gemm_ws_bytes(tokens, cols, 1) + 255) & ~size_t(255))) : nullptr;
     const size_t nblk = tokens * nb;
     zk::quantize_acts_gemm_kernel<<<static_cast<unsigned>((nblk + 7) / 8), 256, 0, st>>>(d_x, xq, xs_t, static_cast<uint32_t>(tokens), nb,
-                                                                                      static_cast<uint32_t>(t_ld));
+                                                                                      static_cast<uint32_t>(t_ld), xq2);
     if (cudaGetLastError() != cudaSuccess) return set_error(s, "gemm: quantise launch failed");
     ++s.stats.dispatches;
     const uint32_t n_tile = 128u;  // tokens per tile: sixteen epilogue warps take 32 token columns each
@@ -819,6 +827,7 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
             m_tiles += (p.rows[j] + zk::kGemmM - 1) / zk::kGemmM;
         }
         if (!make_map_2d(s, &p.map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, cols, tokens, cols, zk::kGemmKTile, n_tile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+        if (xq2 && !make_map_2d(s, &p.map_x2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq2, cols, tokens, cols, zk::kGemmKTile, n_tile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
         if (!make_map_2d(s, &p.map_xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, xs_t, t_ld, nb, t_ld * sizeof(float), n_tile, zk::kGemmBlocksPerTile,
                          CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
         p.tensors = static_cast<uint32_t>(n);
@@ -838,7 +847,7 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
             zk::gemm_zero_split_tiles_kernel<<<grid, 256, 0, st>>>(p, ktiles);
             ++s.stats.dispatches;
         }
-        const cudaError_t e = launch_gemm<128>(p, grid, st);
+        const cudaError_t e = digits == 2 ? launch_gemm<128, 2>(p, grid, st) : launch_gemm<128, 1>(p, grid, st);
         if (e != cudaSuccess) return set_error(s, std::string("gemm launch: ") + cudaGetErrorString(e));
         ++s.stats.dispatches;
     }
@@ -1067,7 +1076,7 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     const size_t chunk = max_tokens_per_launch(s, fmt, cols, act_mode);
     if (!chunk) return set_error(s, "columns too large: one activation row does not fit shared memory");
     // More than one decode launch worth of int8-activation Q8_0 tokens: the tensor-core GEMM.
-    const bool tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q8_0 && act_mode == ZEN_CUDA_ACT_INT8 && tokens > 8;
+    const bool tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q8_0 && tokens > 8;   // either activation mode
     const bool fetch_by_kernel = direct && x_bytes <= kDirectInputBytes;
 
     // The three launches of a small call (fetch the activations, the product, copy the result out and publish it).
@@ -1156,8 +1165,8 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
         s.stats.transfer_us += us_since(t0);
         t0 = clock_type::now();
         if (tensor_path) {
-            if (!ensure_gemm_ws(s, gemm_ws_bytes(tokens, cols))) return false;
-            if (!enqueue_gemm_q8_0(s, w, d_out, count, s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
+            if (!ensure_gemm_ws(s, gemm_ws_bytes(tokens, cols, act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1))) return false;
+            if (!enqueue_gemm_q8_0(s, w, d_out, count, s.d_x, tokens, s.d_gemm_ws, s.stream, act_mode)) return false;
         }
         for (size_t t0k = 0; !tensor_path && t0k < tokens; t0k += chunk) {
             const size_t nt = std::min<size_t>(chunk, tokens - t0k);
@@ -1611,6 +1620,21 @@ int zen_cuda_dev_gemv_list(const zen_cuda_gemv_list* list, void* stream) {
 }
 
 size_t zen_cuda_gemm_workspace_bytes(size_t tokens, size_t columns) { return gemm_ws_bytes(tokens, columns); }
+size_t zen_cuda_gemm_workspace_bytes_act(size_t tokens, size_t columns, int act_mode) {
+    return gemm_ws_bytes(tokens, columns, act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1);
+}
+
+int zen_cuda_dev_gemm_q8_0_act(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x, size_t tokens, int act_mode,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!w || !d_out || !count || count > ZEN_CUDA_MAX_BATCH || !w[0]) return set_error(s, "dev_gemm: bad arguments") ? 1 : 0;
+    if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "dev_gemm: bad activation mode") ? 1 : 0;
+    if (workspace_bytes < gemm_ws_bytes(tokens, w[0]->cols, act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1)) return set_error(s, "dev_gemm: workspace too small") ? 1 : 0;
+    return enqueue_gemm_q8_0(s, w, d_out, count, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream,
+                             act_mode) ? 1 : 0;
+}
 
 int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x, size_t tokens,
                            void* workspace, size_t workspace_bytes, void* stream) {

@@ -123,7 +123,8 @@ class LlamaDecoder:
         prompt_act_mode: activation mode of the layer products while the prompt is consumed, when it differs from act_mode.
         The reference with ZEN_CPU_Q8_ACT=1 is such a mix: its prompt block goes through the fp32-activation GEMM
         (src/quant.cpp:1667-1680) and only single-token products quantise their input to int8 (:1088-1123); ACT_FP32 here
-        with act_mode=ACT_INT8 reproduces it (the prompt then goes token by token, outside the step graphs)."""
+        with act_mode=ACT_INT8 reproduces it (prompt blocks go through the two-digit tensor-core product, leftover prompt
+        tokens one by one outside the step graphs)."""
         import torch
         self.torch, self.be, self.cfg, self.act_mode = torch, backend, cfg, act_mode
         self.prompt_act_mode = prompt_act_mode if prompt_act_mode not in (None, act_mode) else None
@@ -328,24 +329,31 @@ class LlamaDecoder:
         if getattr(self, "_pf", None) is None:
             torch, cfg, T = self.torch, self.cfg, self.PREFILL_CHUNK
             f32 = dict(dtype=torch.float32, device=self.dev)
-            ws_bytes = max(self.be.gemm_workspace_bytes(T, cfg.embedding), self.be.gemm_workspace_bytes(T, cfg.ffn), self.be.gemm_workspace_bytes(T, cfg.q_width))
+            mode = self._prefill_mode()
+            ws_bytes = max(self.be.gemm_workspace_bytes(T, n, mode) for n in (cfg.embedding, cfg.ffn, cfg.q_width))
             self._pf = dict(x=torch.zeros((T, cfg.embedding), **f32), xn=torch.zeros((T, cfg.embedding), **f32), tmp=torch.zeros((T, cfg.embedding), **f32),
                             q=torch.zeros((T, cfg.q_width), **f32), k=torch.zeros((T, cfg.kv_width), **f32), v=torch.zeros((T, cfg.kv_width), **f32),
                             att=torch.zeros((T, cfg.q_width), **f32), gate=torch.zeros((T, cfg.ffn), **f32), up=torch.zeros((T, cfg.ffn), **f32),
                             hid=torch.zeros((T, cfg.ffn), **f32), ws=torch.zeros(ws_bytes, dtype=torch.uint8, device=self.dev), ws_bytes=ws_bytes)
         return self._pf
 
+    def _prefill_mode(self) -> int:
+        """Activation mode of the prompt block's products: prompt_act_mode when one was given, else the decode mode."""
+        return self.prompt_act_mode if self.prompt_act_mode is not None else self.act_mode
+
     def prefill(self, d_tokens, count: int) -> None:
         """Consumes `count` tokens (device int64) at positions pos .. pos + count - 1 as one block: the projections run
-        as tcgen05 GEMMs (int8 activations), the attention as the causal block kernel; afterwards the residual stream and
-        its normalised copy of the LAST token are in self.x / self.xn, ready for the lm_head, and pos has advanced."""
+        as tcgen05 GEMMs (int8 activations, or two int8 digits per activation in the fp32-equivalent mode), the attention
+        as the causal block kernel; afterwards the residual stream and its normalised copy of the LAST token are in
+        self.x / self.xn, ready for the lm_head, and pos has advanced."""
         if self.world > 1:
             raise ValueError("the block prefill is not sharded: a row-sharded decoder takes its prompt token by token")
         be, cfg, st = self.be, self.cfg, self.stream.cuda_stream
         b = self._prefill_buffers()
         P = lambda t: t.data_ptr()
         T, E, eps = count, cfg.embedding, cfg.rms_eps
-        gemm = lambda hs, outs, x: be.dev_gemm_q8_0(hs, [P(o) for o in outs], P(x), T, P(b["ws"]), b["ws_bytes"], st)
+        mode = self._prefill_mode()
+        gemm = lambda hs, outs, x: be.dev_gemm_q8_0(hs, [P(o) for o in outs], P(x), T, P(b["ws"]), b["ws_bytes"], st, act_mode=mode)
         be.dev_embed_rows_q8_0(self.h["token_embd.weight"], P(d_tokens), T, P(b["x"]), st)
         be.dev_rms_norm(P(b["x"]), None, P(self.norm["blk.0.attn_norm.weight"]), P(b["xn"]), E, T, eps, st)
         for layer in range(cfg.layers):
@@ -369,12 +377,12 @@ class LlamaDecoder:
 
     def feed_prompt(self, prompt: list[int], batched_prefill: bool | None = None) -> None:
         """Enqueues the whole prompt from position self.pos on, ending with the first pick (left in self.token).  Blocks of
-        at least PREFILL_MIN tokens go through prefill() when batched_prefill (default: when the decoder computes with
-        int8 activations), the rest token by token."""
+        at least PREFILL_MIN tokens go through prefill() when batched_prefill (default: on one GPU), the rest token by
+        token."""
         torch = self.torch
         ids = torch.tensor(prompt, dtype=torch.int64).pin_memory()
         if batched_prefill is None:
-            batched_prefill = self.act_mode == ACT_INT8 and self.world == 1 and self.prompt_act_mode is None
+            batched_prefill = self.world == 1
         with torch.cuda.stream(self.stream):
             done = 0
             if batched_prefill and len(prompt) >= self.PREFILL_MIN:
@@ -408,8 +416,9 @@ class LlamaDecoder:
         """Generation: the prompt, then max_new picks (each read back, as the reference's per-token callback does).  With
         temperature <= 0 the picks are greedy; otherwise every token is drawn on the device from the temperature / top-k /
         top-p distribution of the step's logits (GenerationOptions, sample_logits :391-418), with one uniform number per
-        token from a host generator seeded with `seed` (the generator stays on the host, as the reference's does).  The prompt goes through prefill() in blocks when the decoder computes with int8 activations (the
-        tensor-core product has no fp32-equivalent mode), token by token otherwise; batched_prefill overrides the choice.
+        token from a host generator seeded with `seed` (the generator stays on the host, as the reference's does).  On one
+        GPU the prompt goes through prefill() in blocks (in the prompt's activation mode), token by token on a sharded
+        decoder; batched_prefill overrides the choice.
         Raises when the context would overflow."""
         torch = self.torch
         if not prompt or len(prompt) + max_new > self.max_positions:
