@@ -408,7 +408,7 @@ LAYER_TENSORS = (("q", 4096, 4096), ("k", 1024, 4096), ("v", 1024, 4096), ("o", 
                  ("gate", 14336, 4096), ("up", 14336, 4096), ("down", 4096, 14336))
 # what a decode step launches: projections that share an input go out as one launch (zen::quant::gemv_batch)
 LAYER_LAUNCHES = (("qkv", ("q", "k", "v")), ("o", ("o",)), ("gate_up", ("gate", "up")), ("down", ("down",)))
-FORMAT_BLOCK = {"Q4_0": (32, 18), "Q8_0": (32, 34), "Q6_K": (256, 210)}
+FORMAT_BLOCK = {"Q4_0": (32, 18), "Q8_0": (32, 34), "Q6_K": (256, 210), "Q4_K": (256, 144), "Q5_K": (256, 176)}
 SWEEP_MIN_BYTES = 300e6   # bytes a timing loop sweeps before it meets an address again: well past the 126 MB L2
 
 
@@ -461,9 +461,12 @@ def run_layer_sweep(args) -> dict:
     detail, packed_q8, launches_total = {}, None, 0
     with ClockSampler(0) as clocks:
         clocks.mark_start()
-        for fmt in [f for f in ("Q8_0", "Q4_0", "Q6_K") if f in args.formats.split(",")]:
+        for fmt in [f for f in ("Q8_0", "Q4_0", "Q6_K", "Q4_K", "Q5_K") if f in args.formats.split(",")]:
             mode = ACT_INT8 if fmt == "Q8_0" else ACT_FP32
-            packed = {name: np.ascontiguousarray(blocks.quantize(FORMAT_IDS[fmt], dense[name])) for name in dense}
+            if fmt in ("Q4_K", "Q5_K"):   # no quantiser for these (the reference has none): valid random super-blocks, weights of the order of 0.02
+                packed = {name: blocks.random_k_blocks(FORMAT_IDS[fmt], *shape[name], seed=40 + i) for i, name in enumerate(dense)}
+            else:
+                packed = {name: np.ascontiguousarray(blocks.quantize(FORMAT_IDS[fmt], dense[name])) for name in dense}
             if fmt == "Q8_0":
                 packed_q8 = packed
             layer_bytes = sum(tensor_bytes(fmt, *shape[n]) for n in shape)
@@ -556,7 +559,7 @@ def run_layer_sweep(args) -> dict:
     return ({
         "metric": "layer_decode_gemv_hbm_gbs", "value": q8["layer"]["gbs"], "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": max(3, args.warmup),
         "ms_per_step": q8["layer"]["us"] / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "decode GEMV sweep over one Llama-3-8B layer, batch 1, Q8_0 / Q4_0 / Q6_K (config 2); value = the Q8_0 layer, "
+        "config": {"workload": "decode GEMV sweep over one Llama-3-8B layer, batch 1, Q8_0 / Q4_0 / Q6_K (config 2) and Q4_K / Q5_K; value = the Q8_0 layer, "
                                "four launches (q|k|v, o, gate|up, down)",
                    "l2": f"inputs larger than L2: every timing loop sweeps at least {SWEEP_MIN_BYTES / 1e6:.0f} MB of distinct weight copies",
                    "launch": "CUDA graph replay"},
@@ -1222,7 +1225,7 @@ def main() -> None:
                     help="a short form of the workload for a profiler capture: one untimed pass, one captured-graph replay as warm-up and one "
                          "as the timed step, no end-to-end leg, no CPU baseline, no detail (its figures are not benchmark values)")
     ap.add_argument("--layers", type=int, default=0, help="workload decode: number of layers (default: the configuration's 32)")
-    ap.add_argument("--formats", default="Q8_0,Q4_0,Q6_K", help="workload layer_sweep: formats to run")
+    ap.add_argument("--formats", default="Q8_0,Q4_0,Q6_K,Q4_K,Q5_K", help="workload layer_sweep: formats to run")
     ap.add_argument("--act", default="int8", choices=["int8", "fp32"], help="workload q8_0_gemm: activation mode of the timed product (the other one is timed briefly beside it)")
     ap.add_argument("--no-detail", action="store_true", help="default workload: skip the short runs of the other workloads that fill `detail`")
     ap.add_argument("--device-pack", action="store_true", help="workload lm_head: draw and pack the Q6_K matrix on the GPU (torch) instead of numpy")

@@ -15,7 +15,7 @@ Block layouts (little endian):
                                                                  w = (d * sc_j) * q - dmin * m_j, j = element / 32
   Q5_K 176 B / 256 el: Q4_K with a 32-byte plane of fifth bits between the scales and the nibbles (src/quant.cpp:439-476)
 
-Q4_K and Q5_K are known here by size and decoder only (host side and CPU checker); the device library does not take them yet.
+Q4_K and Q5_K have no quantiser here (the reference has none either): random_k_blocks draws valid rows for tests and benchmarks.
 """
 from __future__ import annotations
 

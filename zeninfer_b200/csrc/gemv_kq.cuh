@@ -1,4 +1,4 @@
-// Decode-time matrix-vector products for Q4_0 and Q6_K (batch 1..8).
+// Decode-time matrix-vector products for Q4_0, Q6_K, Q4_K and Q5_K (batch 1..8).
 //
 // The reference evaluates both formats with fp32 activations: Q4_0 through its generic
 // dequantise-then-dot route (src/quant.cpp:1135-1162 over gemv_avx2, kernels/avx2.cpp:16-40) and
@@ -10,11 +10,17 @@
 //
 //   Q4_0 : y += d_w * (d_x/256) * ( sum n*(256*q1+q2)  -  8 * sum(256*q1+q2) )      n = nibble 0..15
 //   Q6_K : y += d * sc_g * (d_x/256) * sum (q-32)*(256*q1+q2)                        per 16-weight group
+//   Q4_K / Q5_K (the reference: gemv_q4k_q5k_avx2, kernels/avx2.cpp:329-378, fp32 activations; its GPU entry is
+//          zen::d3d12::gemm_kquant, include/zen/d3d12_backend.h:75), per 32-weight sub-block g of a super-block:
+//          y += d * sc_g * (d_x/256) * sum q*(256*q1+q2)  -  dmin * m_g * (d_x/256) * sum (256*q1+q2)
+//          with q the 4-bit (Q4_K) or 5-bit (Q5_K: nibble + 16 * fifth bit) code
 //
 // Same streaming skeleton as the Q8_0 kernel (gemv_q8_0.cuh): a persistent CTA per SM owns a
 // byte-balanced row slice, a producer warp feeds a ring of shared-memory stages with TMA bulk
 // copies, sixteen consumer warps in two teams own one row each.  Algorithmic traffic is the raw
-// GGUF size (18 B per Q4_0 block, 210 B per Q6_K super-block).
+// GGUF size (18 B per Q4_0 block, 210 B per Q6_K super-block, 144 / 176 B per Q4_K / Q5_K super-block; the device
+// planes of the last two are 4 bytes per super-block larger, because the 12 packed bytes of 6-bit scales and minimums
+// are kept unpacked as 16, see repack.cuh).
 #pragma once
 #include <cuda_fp16.h>
 
@@ -43,6 +49,23 @@ template <> struct KqFormat<14> {  // Q6_K: ql [K/2], qh [K/4], int8 sc [K/16], 
     }
     __host__ __device__ static constexpr uint32_t bytes_per_256(int plane) { return plane == 0 ? 128 : plane == 1 ? 64 : plane == 2 ? 16 : 2; }
 };
+
+template <> struct KqFormat<12> {  // Q4_K: nibbles [K/2], unpacked sub-block scales|minimums [K/16], (d, dmin) f16 pairs [K/256]
+    static constexpr int kPlanes = 3;
+    static constexpr int kStages = 6;
+    __host__ __device__ static constexpr uint32_t seg_bytes(int plane) { return plane == 0 ? kKqSegElems / 2 : plane == 1 ? kKqSegElems / 16 : kKqSegElems / 256 * 4; }
+    __host__ __device__ static constexpr uint32_t bytes_per_256(int plane) { return plane == 0 ? 128 : plane == 1 ? 16 : 4; }
+};
+template <> struct KqFormat<13> {  // Q5_K: nibbles [K/2], fifth bits [K/8], scales|minimums [K/16], (d, dmin) [K/256]
+    static constexpr int kPlanes = 4;
+    static constexpr int kStages = 4;
+    __host__ __device__ static constexpr uint32_t seg_bytes(int plane) {
+        return plane == 0 ? kKqSegElems / 2 : plane == 1 ? kKqSegElems / 8 : plane == 2 ? kKqSegElems / 16 : kKqSegElems / 256 * 4;
+    }
+    __host__ __device__ static constexpr uint32_t bytes_per_256(int plane) { return plane == 0 ? 128 : plane == 1 ? 32 : plane == 2 ? 16 : 4; }
+};
+// Q4_K and Q5_K share everything but the fifth-bit plane.
+template <int kFormat> constexpr bool kq_is_k45 = kFormat == 12 || kFormat == 13;
 
 template <int kFormat> __host__ __device__ constexpr uint32_t kq_row_stage_bytes() {
     uint32_t b = 0;
@@ -320,10 +343,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
         // times the weight bytes in wavefronts and capped the kernel at a third of the HBM rate).
         //   Q4_0: warp = (K slice of 32 blocks, half of the eight rows); a lane owns one 32-weight block
         //   Q6_K: warp = K slice of two super-blocks, all eight rows;     a lane owns one 16-weight scale group
-        constexpr int kR = kFormat == 2 ? 4 : 8;                       // rows per warp
-        constexpr int kSlices = kFormat == 2 ? 4 : 8;                  // K slices per segment
+        //   Q4_K / Q5_K: warp = (K slice of four super-blocks, half of the eight rows); a lane owns 16 nibble bytes, i.e. 16
+        //         weights of sub-block 2j (low nibbles) and the 16 of sub-block 2j+1 at the same positions (high nibbles)
+        constexpr bool kK45 = kq_is_k45<kFormat>;
+        constexpr int kR = (kFormat == 2 || kK45) ? 4 : 8;             // rows per warp
+        constexpr int kSlices = (kFormat == 2 || kK45) ? 4 : 8;        // K slices per segment
         const uint32_t kslice = static_cast<uint32_t>(twarp) % kSlices;
-        const uint32_t rowbase = kFormat == 2 ? (static_cast<uint32_t>(twarp) / kSlices) * kR : 0u;
+        const uint32_t rowbase = kR == 4 ? (static_cast<uint32_t>(twarp) / kSlices) * kR : 0u;
+        // Q4_K / Q5_K lane geometry (src/quant.cpp:133-141 and the kernels at kernels/avx2.cpp:329-378): element
+        // g*32 + l of a super-block is the nibble (g & 1) of byte (g >> 1)*32 + l, its fifth bit is bit g of qh[l]
+        const uint32_t k_sb = kslice * 4 + (static_cast<uint32_t>(lane) >> 3), k_j = (static_cast<uint32_t>(lane) >> 1) & 3, k_h = lane & 1;
+        float k_xs_hi = 0.0f, k_f_lo = 0.0f, k_f_hi = 0.0f;   // the high sub-block's activation scale; scale x code sum of both
         // Q6_K lane geometry (src/quant.cpp:500-517): element e = half*128 + group*32 + l lives in ql byte
         // half*64 + (group%2)*32 + l (low nibble for group < 2), qh byte half*32 + l bits 2*group.., scale half*8 + group*2 + l/16
         const uint32_t sg = lane & 15, qhalf = sg >> 3, group = (sg >> 1) & 3, six = sg & 1;
@@ -347,6 +377,19 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                 xs = live ? xscale[b] * (1.0f / 16.0f) : 0.0f;   // high nibbles enter sixteen-fold, so every sum is sixteen-fold
                 bias = live ? -128 * xsum[b] : 0;                 // -8 * sum, sixteen-fold
                 wofs = live ? kslice * 32 + lane : 0u;
+            } else if (kK45) {
+                const uint32_t e_lo = seg * kKqSegElems + k_sb * 256 + k_j * 64 + k_h * 16, e_hi = e_lo + 32;
+                const bool live = e_lo < p.K;   // K is a multiple of 256: the lane's two sub-blocks are both inside or both outside
+                xa = live ? *reinterpret_cast<const uint4*>(xd + e_lo) : zero;
+                xb = live ? *reinterpret_cast<const uint4*>(xd + e_hi) : zero;
+                xc = live ? *reinterpret_cast<const uint4*>(xd + kpad + e_lo) : zero;
+                xd4 = live ? *reinterpret_cast<const uint4*>(xd + kpad + e_hi) : zero;
+                xs = live ? xscale[e_lo / 32] : 0.0f;
+                k_xs_hi = live ? xscale[e_hi / 32] : 0.0f;
+                const uint4 ones = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+                k_f_lo = xs * static_cast<float>(dot16(ones, xa) * 256 + dot16(ones, xc));        // for the minimum term
+                k_f_hi = k_xs_hi * static_cast<float>(dot16(ones, xb) * 256 + dot16(ones, xd4));
+                wofs = live ? k_sb : 0u;
             } else {
                 const uint32_t e0 = seg * kKqSegElems + sbl * 256 + qhalf * 128 + group * 32 + six * 16;
                 const bool live = e0 < p.K;
@@ -390,6 +433,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                 if (kFormat == 2) {
                     w0 = st + kq_plane_offset<kFormat>(0) + rowbase * F::seg_bytes(0) + wofs * 16;   // nibbles
                     w1 = st + kq_plane_offset<kFormat>(1) + rowbase * F::seg_bytes(1) + wofs * 2;    // scale
+                } else if (kK45) {
+                    constexpr int kScm = F::kPlanes - 2, kDd = F::kPlanes - 1;
+                    w0 = st + kq_plane_offset<kFormat>(0) + rowbase * F::seg_bytes(0) + wofs * 128 + k_j * 32 + k_h * 16;   // nibbles
+                    w1 = st + kq_plane_offset<kFormat>(1) + rowbase * F::seg_bytes(1) + wofs * 32 + k_h * 16;             // Q5_K: fifth bits
+                    sc = reinterpret_cast<const int8_t*>(st + kq_plane_offset<kFormat>(kScm) + rowbase * F::seg_bytes(kScm)) + wofs * 16 + k_j * 2;
+                    dd = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(kDd) + rowbase * F::seg_bytes(kDd)) + wofs * 2;
                 } else {
                     w0 = st + kq_plane_offset<kFormat>(0) + wofs * 128 + qhalf * 64 + (group & 1) * 32 + six * 16;   // ql
                     w1 = st + kq_plane_offset<kFormat>(1) + wofs * 64 + qhalf * 32 + six * 16;                       // qh
@@ -410,6 +459,26 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                         // 16 * (256 * (lo.q1 + hi.q1) + (lo.q2 + hi.q2) - 8 * sum) = 4096 a + 256 b + 16 c + d
                         const int isum = ((a * 16 + b) * 16 + c) * 16 + d;
                         acc[r] = fmaf(dw * xs, static_cast<float>(isum), acc[r]);
+                    } else if (kK45) {
+                        constexpr int kScm = F::kPlanes - 2, kDd = F::kPlanes - 1;
+                        const uint4 w = *reinterpret_cast<const uint4*>(w0 + r * F::seg_bytes(0));
+                        const uint32_t m = 0x0F0F0F0Fu;
+                        uint4 lo = make_uint4(w.x & m, w.y & m, w.z & m, w.w & m);
+                        uint4 hi = make_uint4((w.x >> 4) & m, (w.y >> 4) & m, (w.z >> 4) & m, (w.w >> 4) & m);
+                        if (kFormat == 13) {
+                            const uint4 q5 = *reinterpret_cast<const uint4*>(w1 + r * F::seg_bytes(1));
+                            const uint32_t s_lo = 2 * k_j, s_hi = 2 * k_j + 1, one = 0x01010101u;
+                            lo.x |= ((q5.x >> s_lo) & one) << 4; lo.y |= ((q5.y >> s_lo) & one) << 4; lo.z |= ((q5.z >> s_lo) & one) << 4; lo.w |= ((q5.w >> s_lo) & one) << 4;
+                            hi.x |= ((q5.x >> s_hi) & one) << 4; hi.y |= ((q5.y >> s_hi) & one) << 4; hi.z |= ((q5.z >> s_hi) & one) << 4; hi.w |= ((q5.w >> s_hi) & one) << 4;
+                        }
+                        const int i_lo = dot16(lo, xa) * 256 + dot16(lo, xc);     // codes are 0..31: signed and unsigned dp4a agree
+                        const int i_hi = dot16(hi, xb) * 256 + dot16(hi, xd4);
+                        const uint32_t sc2 = *reinterpret_cast<const uint16_t*>(sc + r * F::seg_bytes(kScm));        // scales of sub-blocks 2j, 2j+1
+                        const uint32_t mn2 = *reinterpret_cast<const uint16_t*>(sc + r * F::seg_bytes(kScm) + 8);    // their minimums
+                        const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(dd + r * (F::seg_bytes(kDd) / 2)));
+                        const float pos = static_cast<float>(sc2 & 0xffu) * (xs * static_cast<float>(i_lo)) + static_cast<float>(sc2 >> 8) * (k_xs_hi * static_cast<float>(i_hi));
+                        const float neg = static_cast<float>(mn2 & 0xffu) * k_f_lo + static_cast<float>(mn2 >> 8) * k_f_hi;
+                        acc[r] = fmaf(dm.x, pos, fmaf(-dm.y, neg, acc[r]));
                     } else {
                         const uint4 l4 = *reinterpret_cast<const uint4*>(w0 + r * F::seg_bytes(0));
                         const uint4 h4 = *reinterpret_cast<const uint4*>(w1 + r * F::seg_bytes(1));
@@ -503,6 +572,52 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                                     const int i2 = dot16(lo, x2[0]) + dot16(hi, x2[1]);
                                     const int isum = i1 * 256 + i2 - 8 * xsum[static_cast<size_t>(tk) * (kpad / 32) + b];
                                     acc[tk] = fmaf(dw * xscale[static_cast<size_t>(tk) * (kpad / 32) + b], static_cast<float>(isum), acc[tk]);
+                                }
+                            }
+                        }
+                    } else if (kq_is_k45<kFormat>) {
+                        // ---- Q4_K / Q5_K: a lane owns 16 nibble bytes (16 weights of sub-block 2j and 16 of 2j+1); a warp covers four super-blocks a pass ----
+                        constexpr int kScm = F::kPlanes - 2, kDd = F::kPlanes - 1;
+                        const uint8_t* qs = st + kq_plane_offset<kFormat>(0) + twarp * F::seg_bytes(0);
+                        const uint8_t* q5p = st + kq_plane_offset<kFormat>(1) + twarp * F::seg_bytes(1);
+                        const uint8_t* scm = st + kq_plane_offset<kFormat>(kScm) + twarp * F::seg_bytes(kScm);
+                        const __half2* dd = reinterpret_cast<const __half2*>(st + kq_plane_offset<kFormat>(kDd) + twarp * F::seg_bytes(kDd));
+                        const uint32_t j = (static_cast<uint32_t>(lane) >> 1) & 3, h = lane & 1;
+    #pragma unroll
+                        for (int i = 0; i < kKqSegElems / 256 / 4; ++i) {
+                            const uint32_t sbl = i * 4 + (lane >> 3);
+                            if (sbl * 256 < elems) {
+                                const uint4 w = *reinterpret_cast<const uint4*>(qs + sbl * 128 + j * 32 + h * 16);
+                                const uint32_t m = 0x0F0F0F0Fu;
+                                uint4 lo = make_uint4(w.x & m, w.y & m, w.z & m, w.w & m);
+                                uint4 hi = make_uint4((w.x >> 4) & m, (w.y >> 4) & m, (w.z >> 4) & m, (w.w >> 4) & m);
+                                if (kFormat == 13) {
+                                    const uint4 q5 = *reinterpret_cast<const uint4*>(q5p + sbl * 32 + h * 16);
+                                    const uint32_t s_lo = 2 * j, s_hi = 2 * j + 1, one = 0x01010101u;
+                                    lo.x |= ((q5.x >> s_lo) & one) << 4; lo.y |= ((q5.y >> s_lo) & one) << 4; lo.z |= ((q5.z >> s_lo) & one) << 4; lo.w |= ((q5.w >> s_lo) & one) << 4;
+                                    hi.x |= ((q5.x >> s_hi) & one) << 4; hi.y |= ((q5.y >> s_hi) & one) << 4; hi.z |= ((q5.z >> s_hi) & one) << 4; hi.w |= ((q5.w >> s_hi) & one) << 4;
+                                }
+                                const uint32_t sc2 = *reinterpret_cast<const uint16_t*>(scm + sbl * 16 + j * 2);
+                                const uint32_t mn2 = *reinterpret_cast<const uint16_t*>(scm + sbl * 16 + 8 + j * 2);
+                                const float2 dm = __half22float2(dd[sbl]);
+                                const float ds_lo = dm.x * static_cast<float>(sc2 & 0xffu), ds_hi = dm.x * static_cast<float>(sc2 >> 8);   // (d * scale), (dmin * m):
+                                const float ms_lo = dm.y * static_cast<float>(mn2 & 0xffu), ms_hi = dm.y * static_cast<float>(mn2 >> 8);   // the reference's factors
+                                const uint32_t e_lo = e_base + sbl * 256 + j * 64 + h * 16, e_hi = e_lo + 32;
+                                const uint4 ones = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+    #pragma unroll
+                                for (int tk = 0; tk < kBatch; ++tk) {
+                                    const uint8_t* xt = xd + static_cast<size_t>(tk) * 2 * kpad;
+                                    const uint4 a1 = *reinterpret_cast<const uint4*>(xt + e_lo), b1 = *reinterpret_cast<const uint4*>(xt + e_hi);
+                                    const uint4 a2 = *reinterpret_cast<const uint4*>(xt + kpad + e_lo), b2 = *reinterpret_cast<const uint4*>(xt + kpad + e_hi);
+                                    const float xs_lo = xscale[static_cast<size_t>(tk) * (kpad / 32) + e_lo / 32], xs_hi = xscale[static_cast<size_t>(tk) * (kpad / 32) + e_hi / 32];
+                                    const int i_lo = dot16(lo, a1) * 256 + dot16(lo, a2), i_hi = dot16(hi, b1) * 256 + dot16(hi, b2);
+                                    const int s_lo = dot16(ones, a1) * 256 + dot16(ones, a2), s_hi = dot16(ones, b1) * 256 + dot16(ones, b2);
+                                    float v = acc[tk];
+                                    v = fmaf(ds_lo * xs_lo, static_cast<float>(i_lo), v);
+                                    v = fmaf(ds_hi * xs_hi, static_cast<float>(i_hi), v);
+                                    v = fmaf(-ms_lo * xs_lo, static_cast<float>(s_lo), v);
+                                    v = fmaf(-ms_hi * xs_hi, static_cast<float>(s_hi), v);
+                                    acc[tk] = v;
                                 }
                             }
                         }

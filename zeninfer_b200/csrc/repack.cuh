@@ -12,6 +12,11 @@
 //   Q4_0: nibs   [rows][K/2]    uint8     scales [rows][nbp] f16
 //   Q6_K: ql     [rows][K/2]    uint8     qh [rows][K/4] uint8
 //         sc     [rows][K/16]   int8      d  [rows][sbp] f16       (sbp = super-blocks rounded up to 8)
+//   Q4_K: qs     [rows][K/2]    uint8     scm [rows][K/16] uint8   dd [rows][sbp] (f16 d, f16 dmin)
+//   Q5_K: qs     [rows][K/2]    uint8     qh  [rows][K/8]  uint8   scm, dd as Q4_K
+//         scm holds, per super-block, the eight 6-bit sub-block scales and the eight 6-bit minimums unpacked to one
+//         byte each (16 bytes instead of the 12 packed ones, src/quant.cpp:133-141): the only plane that is not a pure
+//         byte move, and the values are unchanged.
 #pragma once
 #include <cstdint>
 #include <cuda_fp16.h>
@@ -65,6 +70,46 @@ __global__ void repack_q6_k_kernel(const uint8_t* __restrict__ raw, uint8_t* __r
     for (int k = 0; k < 32; ++k) o_qh[k] = p[64 + k];
     for (int k = 0; k < 8; ++k) o_sc[k] = p[96 + k];
     d[r * sbp + b] = p[104];
+}
+
+// One thread per 256-element super-block.  raw: [rows][nsb*144] (Q4_K: d, dmin, scales[12], qs[128]) or
+// [rows][nsb*176] (Q5_K: d, dmin, scales[12], qh[32], qs[128]).  Both sizes are multiples of 16.
+template <bool kQ5>
+__global__ void repack_k45_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ qs, uint8_t* __restrict__ qh, uint8_t* __restrict__ scm,
+                                  uint32_t* __restrict__ dd, size_t rows, uint32_t nsb, uint32_t sbp) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= rows * nsb) return;
+    const size_t r = i / nsb;
+    const uint32_t b = static_cast<uint32_t>(i % nsb);
+    const uint8_t* p = raw + i * (kQ5 ? 176 : 144);
+    dd[r * sbp + b] = *reinterpret_cast<const uint32_t*>(p);
+    const uint8_t* s8 = p + 4;
+    uint8_t out[16];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        if (g < 4) {
+            out[g] = s8[g] & 63u;
+            out[8 + g] = s8[g + 4] & 63u;
+        } else {
+            out[g] = static_cast<uint8_t>((s8[g + 4] & 15u) | ((s8[g - 4] >> 6) << 4));
+            out[8 + g] = static_cast<uint8_t>((s8[g + 4] >> 4) | ((s8[g] >> 6) << 4));
+        }
+    }
+    uint4 packed;
+    packed.x = out[0] | (out[1] << 8) | (out[2] << 16) | (static_cast<uint32_t>(out[3]) << 24);
+    packed.y = out[4] | (out[5] << 8) | (out[6] << 16) | (static_cast<uint32_t>(out[7]) << 24);
+    packed.z = out[8] | (out[9] << 8) | (out[10] << 16) | (static_cast<uint32_t>(out[11]) << 24);
+    packed.w = out[12] | (out[13] << 8) | (out[14] << 16) | (static_cast<uint32_t>(out[15]) << 24);
+    *reinterpret_cast<uint4*>(scm + (r * nsb + b) * 16) = packed;
+    const uint4* src = reinterpret_cast<const uint4*>(p + 16);
+    if (kQ5) {
+        uint4* o = reinterpret_cast<uint4*>(qh + (r * nsb + b) * 32);
+        o[0] = src[0]; o[1] = src[1];
+        src += 2;
+    }
+    uint4* o = reinterpret_cast<uint4*>(qs + (r * nsb + b) * 128);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = src[k];
 }
 
 }  // namespace zk

@@ -27,7 +27,6 @@
 
 #include "decode_ops.cuh"
 #include "gemm_q8_0_i8.cuh"
-#include "gemv_k45.cuh"
 #include "gemv_kq.cuh"
 #include "gemv_list.cuh"
 #include "gemv_q8_0.cuh"
@@ -241,8 +240,9 @@ void free_weights(State& s, zen_cuda_weights* w) {
     delete w;
 }
 
-bool raw_layout(int fmt) { return fmt == ZEN_CUDA_Q4_K || fmt == ZEN_CUDA_Q5_K; }   // kept as GGUF super-blocks on the device
-uint32_t block_elems(int fmt) { return (fmt == ZEN_CUDA_Q6_K || raw_layout(fmt)) ? 256u : 32u; }
+bool super_block_format(int fmt) { return fmt == ZEN_CUDA_Q6_K || fmt == ZEN_CUDA_Q4_K || fmt == ZEN_CUDA_Q5_K; }
+uint32_t block_elems(int fmt) { return super_block_format(fmt) ? 256u : 32u; }
+int plane_count(int fmt) { return fmt == ZEN_CUDA_Q8_0 || fmt == ZEN_CUDA_Q4_0 ? 2 : fmt == ZEN_CUDA_Q4_K ? 3 : 4; }
 uint32_t block_bytes(int fmt) {
     return fmt == ZEN_CUDA_Q8_0 ? 34u : fmt == ZEN_CUDA_Q4_0 ? 18u : fmt == ZEN_CUDA_Q6_K ? 210u : fmt == ZEN_CUDA_Q4_K ? 144u : fmt == ZEN_CUDA_Q5_K ? 176u : 0u;
 }
@@ -270,8 +270,12 @@ bool stream_to_device(State& s, void* dst, const uint8_t* src, size_t bytes) {
 void plane_sizes(int fmt, size_t nrows, size_t cols, size_t plane_bytes[4]) {
     const uint32_t nb = static_cast<uint32_t>(cols / block_elems(fmt)), nbp = (nb + 7u) & ~7u;
     plane_bytes[0] = plane_bytes[1] = plane_bytes[2] = plane_bytes[3] = 0;
-    if (raw_layout(fmt)) {
-        plane_bytes[0] = nrows * static_cast<size_t>(nb) * block_bytes(fmt) + 64;   // the super-blocks as they are in the file
+    if (fmt == ZEN_CUDA_Q4_K || fmt == ZEN_CUDA_Q5_K) {   // nb counts 256-weight super-blocks
+        int i = 0;
+        plane_bytes[i++] = nrows * (cols / 2) + 64;                        // nibbles
+        if (fmt == ZEN_CUDA_Q5_K) plane_bytes[i++] = nrows * (cols / 8) + 64;   // fifth bits
+        plane_bytes[i++] = nrows * (cols / 16) + 64;                       // unpacked sub-block scales | minimums
+        plane_bytes[i++] = nrows * static_cast<size_t>(nbp) * 4 + 64;      // (d, dmin) f16 pairs
     } else if (fmt == ZEN_CUDA_Q8_0) {
         plane_bytes[0] = nrows * cols + 64;                                // int8 codes
         plane_bytes[1] = nrows * static_cast<size_t>(nbp) * 2 + 64;        // f16 scales
@@ -302,8 +306,7 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
     w->raw_bytes = nrows * row_raw;
     uint8_t* d_raw = nullptr;
     auto t0 = clock_type::now();
-    const bool raw = raw_layout(fmt);
-    bool ok = raw || cudaMalloc(reinterpret_cast<void**>(&d_raw), w->raw_bytes + 16) == cudaSuccess;
+    bool ok = cudaMalloc(reinterpret_cast<void**>(&d_raw), w->raw_bytes + 16) == cudaSuccess;
     size_t plane_bytes[4];
     plane_sizes(fmt, nrows, cols, plane_bytes);
     for (int i = 0; ok && i < 4; ++i)
@@ -320,12 +323,9 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
         return nullptr;
     }
     t0 = clock_type::now();
-    ok = stream_to_device(s, raw ? w->plane[0] : d_raw, host + first_row * row_raw, w->raw_bytes);
+    ok = stream_to_device(s, d_raw, host + first_row * row_raw, w->raw_bytes);
     s.stats.transfer_us += us_since(t0);
-    if (ok && raw) {
-        ok = cudaStreamSynchronize(s.copy_stream) == cudaSuccess;
-        if (!ok) set_error(s, "upload: copy failed");
-    } else if (ok) {
+    if (ok) {
         t0 = clock_type::now();
         const size_t nblocks = nrows * w->nb;
         const unsigned grid = static_cast<unsigned>((nblocks + 255) / 256);
@@ -335,6 +335,12 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
         else if (fmt == ZEN_CUDA_Q4_0)
             zk::repack_q4_0_kernel<<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]),
                                                                    static_cast<uint16_t*>(w->plane[1]), nrows, w->nb, w->nbp);
+        else if (fmt == ZEN_CUDA_Q4_K)
+            zk::repack_k45_kernel<false><<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]), nullptr, static_cast<uint8_t*>(w->plane[1]),
+                                                                         static_cast<uint32_t*>(w->plane[2]), nrows, w->nb, w->nbp);
+        else if (fmt == ZEN_CUDA_Q5_K)
+            zk::repack_k45_kernel<true><<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]), static_cast<uint8_t*>(w->plane[1]),
+                                                                        static_cast<uint8_t*>(w->plane[2]), static_cast<uint32_t*>(w->plane[3]), nrows, w->nb, w->nbp);
         else
             zk::repack_q6_k_kernel<<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]), static_cast<uint8_t*>(w->plane[1]),
                                                                    static_cast<int8_t*>(w->plane[2]), static_cast<uint16_t*>(w->plane[3]),
@@ -480,14 +486,15 @@ cudaError_t dispatch_kq(int batch, const zk::KqParams& p, unsigned grid, size_t 
 }
 
 size_t gemv_smem_bytes(int format, size_t cols, size_t tokens, int act_mode) {
-    if (raw_layout(format)) return 0;   // the Q4_K / Q5_K kernel stages nothing
     if (format == ZEN_CUDA_Q8_0) {
         const uint32_t nb = static_cast<uint32_t>(cols / 32), nseg = (nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks;
         return zk::gemv_q8_0_smem_bytes(nseg, static_cast<int>(tokens), act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1);
     }
     const uint32_t nseg = static_cast<uint32_t>((cols + zk::kKqSegElems - 1) / zk::kKqSegElems);
-    return format == ZEN_CUDA_Q4_0 ? zk::gemv_kq_smem_bytes<ZEN_CUDA_Q4_0>(nseg, static_cast<int>(tokens))
-                                   : zk::gemv_kq_smem_bytes<ZEN_CUDA_Q6_K>(nseg, static_cast<int>(tokens));
+    return format == ZEN_CUDA_Q4_0   ? zk::gemv_kq_smem_bytes<ZEN_CUDA_Q4_0>(nseg, static_cast<int>(tokens))
+           : format == ZEN_CUDA_Q4_K ? zk::gemv_kq_smem_bytes<ZEN_CUDA_Q4_K>(nseg, static_cast<int>(tokens))
+           : format == ZEN_CUDA_Q5_K ? zk::gemv_kq_smem_bytes<ZEN_CUDA_Q5_K>(nseg, static_cast<int>(tokens))
+                                     : zk::gemv_kq_smem_bytes<ZEN_CUDA_Q6_K>(nseg, static_cast<int>(tokens));
 }
 
 // Largest number of activation rows (<= 8) one launch can keep in shared memory beside the weight ring; 0 if not even one.
@@ -503,7 +510,7 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
     if (gather) p.gather = *gather;
     uint32_t total_rows = 0;
     const int fmt = w[0]->format;
-    const int planes = fmt == ZEN_CUDA_Q4_0 ? 2 : 4;
+    const int planes = plane_count(fmt);
     for (size_t i = 0; i < count; ++i) {
         for (int k = 0; k < planes; ++k) p.task[i].plane[k] = static_cast<const uint8_t*>(w[i]->plane[k]);
         p.task[i].y = d_y ? d_y[i] : nullptr;
@@ -519,6 +526,10 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
     if (fmt == ZEN_CUDA_Q4_0) {
         p.pitch[0] = p.K / 2;
         p.pitch[1] = w[0]->nbp * 2;
+    } else if (fmt == ZEN_CUDA_Q4_K) {
+        p.pitch[0] = p.K / 2; p.pitch[1] = p.K / 16; p.pitch[2] = w[0]->nbp * 4;
+    } else if (fmt == ZEN_CUDA_Q5_K) {
+        p.pitch[0] = p.K / 2; p.pitch[1] = p.K / 8; p.pitch[2] = p.K / 16; p.pitch[3] = w[0]->nbp * 4;
     } else {
         p.pitch[0] = p.K / 2; p.pitch[1] = p.K / 4; p.pitch[2] = p.K / 16; p.pitch[3] = w[0]->nbp * 2;
     }
@@ -528,8 +539,10 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
     const size_t smem = gemv_smem_bytes(fmt, w[0]->cols, tokens, ZEN_CUDA_ACT_FP32)
                         + (gather ? zk::gather_stash_bytes(total_rows, grid, static_cast<int>(tokens)) : 0);
     if (smem > s.smem_optin) return set_error(s, "gemv: activation rows do not fit shared memory (columns x tokens too large)");
-    const cudaError_t e = fmt == ZEN_CUDA_Q4_0 ? dispatch_kq<ZEN_CUDA_Q4_0>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
-                                               : dispatch_kq<ZEN_CUDA_Q6_K>(static_cast<int>(tokens), p, grid, smem, st, s.pdl);
+    const cudaError_t e = fmt == ZEN_CUDA_Q4_0   ? dispatch_kq<ZEN_CUDA_Q4_0>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
+                          : fmt == ZEN_CUDA_Q4_K ? dispatch_kq<ZEN_CUDA_Q4_K>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
+                          : fmt == ZEN_CUDA_Q5_K ? dispatch_kq<ZEN_CUDA_Q5_K>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
+                                                 : dispatch_kq<ZEN_CUDA_Q6_K>(static_cast<int>(tokens), p, grid, smem, st, s.pdl);
     if (e != cudaSuccess) return set_error(s, std::string("gemv launch: ") + cudaGetErrorString(e));
     ++s.stats.dispatches;
     return true;
@@ -540,20 +553,6 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(State& s, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args);   // defined below
 
-// Q4_K / Q5_K: one launch per tensor, a warp per row, straight from the raw super-blocks.
-bool enqueue_gemv_k45(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x, size_t tokens, cudaStream_t st) {
-    for (size_t i = 0; i < count; ++i) {
-        const unsigned grid = static_cast<unsigned>((w[i]->rows + zk::kK45Warps - 1) / zk::kK45Warps);
-        const cudaError_t e = w[i]->format == ZEN_CUDA_Q5_K
-            ? launch_pdl(s, zk::gemv_k45_kernel<true>, dim3(grid), dim3(zk::kK45Warps * 32), 0, st, static_cast<const uint8_t*>(w[i]->plane[0]), d_x, d_y[i],
-                         static_cast<uint32_t>(w[i]->rows), w[i]->nb, static_cast<uint32_t>(tokens))
-            : launch_pdl(s, zk::gemv_k45_kernel<false>, dim3(grid), dim3(zk::kK45Warps * 32), 0, st, static_cast<const uint8_t*>(w[i]->plane[0]), d_x, d_y[i],
-                         static_cast<uint32_t>(w[i]->rows), w[i]->nb, static_cast<uint32_t>(tokens));
-        if (e != cudaSuccess) return set_error(s, std::string("gemv launch: ") + cudaGetErrorString(e));
-        ++s.stats.dispatches;
-    }
-    return true;
-}
 bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
                   size_t tokens, int act_mode, cudaStream_t st, const zk::PeerGather* gather = nullptr, const float* d_gate = nullptr,
                   const float* d_norm_weight = nullptr, float norm_eps = 0.0f, bool accumulate = false, const zen_cuda_weights* warm_next = nullptr) {
@@ -578,12 +577,8 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
         p.gather = *gather;
     }
     if (w[0]->format != ZEN_CUDA_Q8_0) {
-        if (act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: Q4_0 and Q6_K take fp32-equivalent activations only");
+        if (act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: Q4_0, Q6_K, Q4_K and Q5_K take fp32-equivalent activations only");
         if (d_gate || d_norm_weight || accumulate) return set_error(s, "gemv: fused inputs and accumulation are Q8_0 paths");
-        if (raw_layout(w[0]->format)) {
-            if (gather || !d_x || (reinterpret_cast<uintptr_t>(d_x) % 16)) return set_error(s, "gemv: Q4_K / Q5_K take a 16-byte aligned input and no gather");
-            return enqueue_gemv_k45(s, w, d_y, count, d_x, tokens, st);
-        }
         return enqueue_gemv_kq(s, w, d_y, count, d_x, tokens, st, gather);   // a warm_next hint is not used by these kernels (measured: no gain)
     }
     if (d_gate && d_norm_weight) return set_error(s, "gemv: a fused input is either SwiGLU or RMSNorm");
