@@ -945,8 +945,8 @@ def run_decode(args, brief: bool = False) -> dict | None:
                              f"worker policy), scaled to 32 layers + lm_head by bytes; attention, norms and sampling not included, so an upper bound "
                              f"for the reference's decode rate on these cores"}
 
-    fn, fs, fr = ("n" in dec.fuse), ("s" in dec.fuse), ("r" in dec.fuse)
-    per_layer = 5 + (0 if (fn and fr) else 2) + (0 if fs else 1)   # q|k|v, attention block, o, gate|up, down + norm / residual / SwiGLU launches
+    fn, fs, fr, fp = ("n" in dec.fuse), ("s" in dec.fuse), ("r" in dec.fuse), ("p" in dec.fuse)
+    per_layer = 5 + (0 if (fn and fr) else 2) + (0 if (fs or fp) else 1)   # q|k|v, attention block, o, gate|up, down + norm / residual / SwiGLU launches
     launches_per_step = 1 + (0 if fn else 1) + per_layer * cfg.layers + 1 + 1 + 2   # embed, layers, advance, lm_head, pick (2): per rank
     gathers = ((2 if dec.col_cut else 4) * cfg.layers + 1) if world > 1 else 0
     line = ({
@@ -1235,7 +1235,7 @@ def main() -> None:
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: how the output shards are all-gathered after each product -- by the product kernel itself "
                          "(peer stores over NVLink, the default) or by an NCCL all-gather launched after it")
-    ap.add_argument("--fuse", default="nr", help="workload decode: operators folded into the projection launches (letters n, s, r; see LlamaDecoder)")
+    ap.add_argument("--fuse", default="nrp", help="workload decode: operators folded into the projection launches (letters n, s, r, p; see LlamaDecoder)")
     ap.add_argument("--token-prefill", action="store_true", help="workload decode: consume the prompt token by token instead of in tensor-core blocks")
     ap.add_argument("--prompt-len", type=int, default=512, help="workload decode: prompt tokens consumed before the timed steps")
     args = ap.parse_args()

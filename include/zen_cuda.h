@@ -202,13 +202,19 @@ int zen_cuda_dev_gemv_swiglu(const zen_cuda_weights* const* w, float* const* d_y
  *   warm_next != NULL   : a hint, the resident Q8_0 tensor the stream's next product will read: once its own copies are
  *                         issued the launch asks L2 for the start of that tensor (up to 192 KB per CTA), so the next launch
  *                         does not begin with a DRAM round trip.  Honoured for launches of at most 32 MB of weights (a larger
- *                         one keeps HBM busy by itself).  Changes no result; any field combination is allowed. */
+ *                         one keeps HBM busy by itself).  Changes no result; any field combination is allowed.
+ *   swiglu_pair != 0    : the launch holds exactly two tensors of equal shape, gate and up (w[0], w[1]); the two halves of
+ *                         every CTA compute row r of both at the same time and d_y[0] receives silu(W0 x) * (W1 x), the
+ *                         input of the down projection (silu_mul, src/adapters/dense_transformer_runtime.cpp:193-199);
+ *                         d_y[1] is not written.  With norm_weight this is gate|up of a layer in one launch, no SwiGLU
+ *                         launch after it.  Not with accumulate; not in a list item. */
 typedef struct zen_cuda_gemv_fusion {
     const float* norm_weight;
     float norm_eps;
     int accumulate;
     const float* gate;
     const zen_cuda_weights* warm_next;
+    int swiglu_pair;
 } zen_cuda_gemv_fusion;
 int zen_cuda_dev_gemv_fused(const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x, size_t tokens, int act_mode,
                             const zen_cuda_gemv_fusion* fusion, void* stream);

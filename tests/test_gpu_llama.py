@@ -141,7 +141,7 @@ def test_silu_mul(be):
     assert_parity(out.cpu().numpy(), (g.astype(np.float64) / (1 + np.exp(-g.astype(np.float64)))) * u, 1e-6, "silu_mul")
 
 
-@pytest.mark.parametrize("fused", [False, True, "r", "nr", "s"])
+@pytest.mark.parametrize("fused", [False, True, "r", "nr", "s", "nrp", "p"])
 @pytest.mark.parametrize("graphs", [False, True])
 def test_generation_matches_the_reference(be, golden, graphs, fused):
     cfg, meta, prompt, ids, logits = golden
@@ -441,3 +441,33 @@ def test_batched_prefill_with_fp32_equivalent_activations(be, golden, decode_mod
         assert_parity(lb, la, 1e-3 if decode_mode == ACT_FP32 else 5e-3, "first logits after a two-digit block prefill vs token by token")
     finally:
         dec.close()
+
+
+@pytest.mark.parametrize("mode", [ACT_INT8, ACT_FP32])
+@pytest.mark.parametrize("rows,cols,tokens,norm", [(14336, 4096, 1, True), (100, 544, 1, False), (1027, 4096, 3, True), (64, 8192, 2, False), (8, 32, 1, False)])
+def test_gate_up_launch_with_the_swiglu_store(be, mode, rows, cols, tokens, norm):
+    # the pair launch computes the two products exactly as a plain two-tensor launch does (same lanes, same order) and
+    # applies the expression of silu_mul to the two sums: equal to the separate launches bit for bit
+    import torch
+    rng = np.random.default_rng(rows + cols)
+    packed = [np.ascontiguousarray(blocks.quantize_q8_0(rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(0.05))) for _ in range(2)]
+    hs = [be.dev_upload("Q8_0", w, rows, cols) for w in packed]
+    x = dev(rng.standard_normal((tokens, cols), dtype=np.float32))
+    nw = dev(rng.standard_normal(cols, dtype=np.float32)) if norm else None
+    g, u, hid, ref = (torch.zeros((tokens, rows), device="cuda") for _ in range(4))
+    kw = dict(norm_weight=nw.data_ptr(), norm_eps=1e-5) if norm else {}
+    torch.cuda.synchronize()
+    be.dev_gemv_fused(hs, [g.data_ptr(), u.data_ptr()], x.data_ptr(), tokens, mode, 0, **kw)
+    be.dev_silu_mul(g.data_ptr(), u.data_ptr(), ref.data_ptr(), tokens * rows, 0)
+    be.dev_gemv_fused(hs, [hid.data_ptr(), None], x.data_ptr(), tokens, mode, 0, swiglu_pair=True, **kw)
+    torch.cuda.synchronize()
+    be.dev_check(0)
+    assert torch.equal(hid, ref)
+    assert float(ref.abs().max()) > 0
+    from zeninfer_b200 import BackendError
+    with pytest.raises(BackendError):
+        be.dev_gemv_fused(hs[:1], [hid.data_ptr()], x.data_ptr(), tokens, mode, 0, swiglu_pair=True)          # needs two tensors
+    with pytest.raises(BackendError):
+        be.dev_gemv_fused(hs, [hid.data_ptr(), None], x.data_ptr(), tokens, mode, 0, swiglu_pair=True, accumulate=True)
+    for h in hs:
+        be.dev_free(h)

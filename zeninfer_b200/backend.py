@@ -74,7 +74,7 @@ class GemmTask(C.Structure):
 
 
 class GemvFusion(C.Structure):
-    _fields_ = [("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("accumulate", C.c_int), ("gate", C.c_void_p), ("warm_next", C.c_void_p)]
+    _fields_ = [("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("accumulate", C.c_int), ("gate", C.c_void_p), ("warm_next", C.c_void_p), ("swiglu_pair", C.c_int)]
 
 
 class GemvListItem(C.Structure):
@@ -339,13 +339,14 @@ class Backend:
 
     def dev_gemv_fused(self, handles: Sequence[int], d_y: Sequence[int], d_x: int, tokens: int, act_mode: int, stream: int = 0, *,
                        norm_weight: int | None = None, norm_eps: float = 0.0, gate: int | None = None, accumulate: bool = False,
-                       warm_next: int | None = None) -> None:
+                       warm_next: int | None = None, swiglu_pair: bool = False) -> None:
         """dev_gemv (Q8_0) with RMSNorm or SwiGLU applied to the input inside the launch and/or y += W x; warm_next
-        names the tensor the stream's next product reads, whose start this launch pulls into L2."""
+        names the tensor the stream's next product reads, whose start this launch pulls into L2; swiglu_pair: the two
+        tensors are gate and up, and d_y[0] receives silu(gate . x) * (up . x)."""
         n = len(handles)
         hs = (C.c_void_p * n)(*handles)
         ys = (C.c_void_p * n)(*d_y)
-        f = GemvFusion(norm_weight, norm_eps, int(accumulate), gate, warm_next)
+        f = GemvFusion(norm_weight, norm_eps, int(accumulate), gate, warm_next, int(swiglu_pair))
         if not self.lib.zen_cuda_dev_gemv_fused(hs, ys, n, d_x, tokens, act_mode, C.byref(f), stream):
             self._fail("dev_gemv_fused")
 
@@ -361,7 +362,7 @@ class Backend:
             hs, ys = (C.c_void_p * k)(*it["handles"]), (C.c_void_p * k)(*it["d_y"])
             keep.append((hs, ys))
             dst.w, dst.d_y, dst.count, dst.d_x = hs, ys, k, it["d_x"]
-            dst.fusion = GemvFusion(it.get("norm_weight"), it.get("norm_eps", 0.0), int(bool(it.get("accumulate"))), it.get("gate"), None)
+            dst.fusion = GemvFusion(it.get("norm_weight"), it.get("norm_eps", 0.0), int(bool(it.get("accumulate"))), it.get("gate"), None, 0)
             dst.depends_on_earlier_items = int(bool(it.get("depends")))
         h = self.lib.zen_cuda_gemv_list_create(arr, n, act_mode)
         if not h:

@@ -73,6 +73,10 @@ constexpr uint32_t kGemvFlagSwiglu = 1u;      // input = silu(x_gate) * x
 constexpr uint32_t kGemvFlagNorm = 2u;        // input = RMSNorm(x) * norm_weight, formed in the prologue
 constexpr uint32_t kGemvFlagAccumulate = 4u;  // y += W x instead of y = W x (the residual add)
 constexpr uint32_t kGemvFlagWarm = 8u;        // pull the start of the next launch's tensor into L2 (producer warp only)
+// Two tasks of equal shape, gate and up: row r of both is computed by the two teams of one CTA at the same time, and
+// task 0's output receives silu(gate . x) * (up . x) (silu_mul, src/adapters/dense_transformer_runtime.cpp:193-199).
+// The launch's row space is ONE task's rows (total_rows = rows, both first_row = 0).
+constexpr uint32_t kGemvFlagPairSwiglu = 64u;
 constexpr uint32_t kWarmCapBytes = 192 * 1024;   // per CTA
 
 struct GemvTask {
@@ -144,11 +148,20 @@ struct RowGroup {
 // Walks a row slice in groups of at most kTeamWarps rows that never straddle two tasks.
 struct GroupWalk {
     uint32_t r, r_end, ti;
-    __device__ GroupWalk(uint32_t first, uint32_t last) : r(first), r_end(last), ti(0) {}
+    bool paired;   // kGemvFlagPairSwiglu: every group goes out twice in a row, for task 0 and then for task 1
+    __device__ GroupWalk(uint32_t first, uint32_t last, bool paired_ = false) : r(first), r_end(last), ti(0), paired(paired_) {}
     __device__ bool done() const { return r >= r_end; }
     __device__ RowGroup next(const GemvParams& p) {
         RowGroup g{0, 0, 0};
         if (done()) return g;
+        if (paired) {
+            g.task = ti;
+            g.row0 = r;
+            g.nrows = min(static_cast<uint32_t>(kTeamWarps), r_end - r);
+            if (ti) r += g.nrows;
+            ti ^= 1u;
+            return g;
+        }
         while (r >= p.task[ti].first_row + p.task[ti].rows) ++ti;
         g.task = ti;
         g.row0 = r - p.task[ti].first_row;
@@ -230,7 +243,7 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
         bool announce = p.gather.world != 0 && blockIdx.x == 0;
         uint32_t unit = 0;
         bool ok = true;
-        GroupWalk walk(r_first, r_last);
+        GroupWalk walk(r_first, r_last, kFuse && (p.flags & kGemvFlagPairSwiglu));
         while (!walk.done() && ok) {
             RowGroup pair[kTeams];
 #pragma unroll
@@ -461,7 +474,10 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
     ZK_STAMP(4);
 
     uint32_t pair_base = 0;  // unit index of the current pair's first unit
-    GroupWalk walk(r_first, r_last);
+    const bool pair_swiglu = kFuse && (flags & kGemvFlagPairSwiglu);
+    float* pair_buf = reinterpret_cast<float*>(norm_part);   // [2 parities][batch][row of the group]: the prologue is done with norm_part
+    uint32_t pair_parity = 0;
+    GroupWalk walk(r_first, r_last, pair_swiglu);
     while (!walk.done() && ok) {
         RowGroup pair[kTeams];
 #pragma unroll
@@ -534,6 +550,37 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
 #endif
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);
+        }
+        if (kFuse && pair_swiglu) {
+            // team 1 (up) hands its row sums to team 0 (gate) through shared memory; the barrier also agrees on failure,
+            // so that no warp waits at it for one that gave up
+            float v[kBatch];
+#pragma unroll
+            for (int tk = 0; tk < kBatch; ++tk) {
+                v[tk] = acc[tk];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v[tk] += __shfl_xor_sync(0xffffffffu, v[tk], o);
+            }
+            float* slot = pair_buf + pair_parity * (kBatch * kTeamWarps);
+            if (team == 1 && lane == 0) {
+#pragma unroll
+                for (int tk = 0; tk < kBatch; ++tk) slot[tk * kTeamWarps + twarp] = v[tk];
+            }
+            uint32_t any_failed;
+            asm volatile(
+                "{ .reg .pred p, q; setp.ne.u32 q, %2, 0; barrier.red.or.pred p, 2, %1, q; selp.u32 %0, 1, 0, p; }"
+                : "=r"(any_failed) : "r"(kGemvWarps * 32), "r"(static_cast<uint32_t>(!ok)) : "memory");
+            if (any_failed) { ok = false; break; }
+            if (team == 0 && lane == 0 && valid && t.y) {
+#pragma unroll
+                for (int tk = 0; tk < kBatch; ++tk) {
+                    const float z = v[tk];
+                    t.y[static_cast<size_t>(tk) * t.rows + row] = (z / (1.0f + expf(-z))) * slot[tk * kTeamWarps + twarp];
+                }
+            }
+            pair_parity ^= 1u;
+            pair_base += kTeams * nseg;
+            continue;
         }
         if (!ok) break;
 #ifdef ZK_TRACE

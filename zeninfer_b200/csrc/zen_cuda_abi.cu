@@ -555,14 +555,16 @@ cudaError_t launch_pdl(State& s, void (*kernel)(KArgs...), dim3 grid, dim3 block
 
 bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y, size_t count, const float* d_x,
                   size_t tokens, int act_mode, cudaStream_t st, const zk::PeerGather* gather = nullptr, const float* d_gate = nullptr,
-                  const float* d_norm_weight = nullptr, float norm_eps = 0.0f, bool accumulate = false, const zen_cuda_weights* warm_next = nullptr) {
+                  const float* d_norm_weight = nullptr, float norm_eps = 0.0f, bool accumulate = false, const zen_cuda_weights* warm_next = nullptr,
+                  bool swiglu_pair = false) {
     if (!count || count > zk::kMaxTasks || !tokens || tokens > 8 || (!d_x && !gather)) return set_error(s, "gemv: bad batch");
     if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: bad activation mode");
     zk::GemvParams p{};
     uint32_t total_rows = 0;
     for (size_t i = 0; i < count; ++i) {
         const bool has_y = d_y && d_y[i];
-        if (!w[i] || (!has_y && !gather) || w[i]->format != w[0]->format || w[i]->cols != w[0]->cols) return set_error(s, "gemv: tasks must share format and columns");
+        if (!w[i] || (!has_y && !gather && !(swiglu_pair && i == 1)) || w[i]->format != w[0]->format || w[i]->cols != w[0]->cols)
+            return set_error(s, "gemv: tasks must share format and columns");
         p.task[i].codes = static_cast<const uint8_t*>(w[i]->plane[0]);
         p.task[i].scales = static_cast<const __half*>(w[i]->plane[1]);
         p.task[i].y = has_y ? d_y[i] : nullptr;
@@ -578,10 +580,18 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
     }
     if (w[0]->format != ZEN_CUDA_Q8_0) {
         if (act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemv: Q4_0, Q6_K, Q4_K and Q5_K take fp32-equivalent activations only");
-        if (d_gate || d_norm_weight || accumulate) return set_error(s, "gemv: fused inputs and accumulation are Q8_0 paths");
+        if (d_gate || d_norm_weight || accumulate || swiglu_pair) return set_error(s, "gemv: fused inputs, outputs and accumulation are Q8_0 paths");
         return enqueue_gemv_kq(s, w, d_y, count, d_x, tokens, st, gather);   // a warm_next hint is not used by these kernels (measured: no gain)
     }
     if (d_gate && d_norm_weight) return set_error(s, "gemv: a fused input is either SwiGLU or RMSNorm");
+    if (swiglu_pair) {
+        // gate and up as one row space: the two teams of a CTA compute row r of both, task 0's output gets silu(g) * u
+        if (count != 2 || w[0]->rows != w[1]->rows || gather || accumulate || !d_y || !d_y[0])
+            return set_error(s, "gemv: a SwiGLU pair is two tensors of equal shape with an output for the first, without gather or accumulation");
+        p.flags |= zk::kGemvFlagPairSwiglu;
+        p.task[1].first_row = 0;
+        total_rows = static_cast<uint32_t>(w[0]->rows);
+    }
     if (d_gate) { p.flags |= zk::kGemvFlagSwiglu; p.x_gate = d_gate; }
     if (d_norm_weight) { p.flags |= zk::kGemvFlagNorm; p.norm_weight = d_norm_weight; p.norm_eps = norm_eps; }
     if (accumulate) p.flags |= zk::kGemvFlagAccumulate;
@@ -676,6 +686,7 @@ zen_cuda_gemv_list* list_create_locked(State& s, const zen_cuda_gemv_list_item* 
         zk::GemvListItem& it = host[i];
         if (!in.w || !in.d_y || !in.count || in.count > zk::kMaxTasks || !in.d_x) return bad("an item needs tensors, outputs and an input");
         if (in.fusion.gate && in.fusion.norm_weight) return bad("a fused input is either SwiGLU or RMSNorm");
+        if (in.fusion.swiglu_pair) return bad("a SwiGLU pair is not a list item");
         uint32_t total_rows = 0;
         for (size_t k = 0; k < in.count; ++k) {
             const zen_cuda_weights* w = in.w[k];
@@ -1576,7 +1587,7 @@ int zen_cuda_dev_gemv_fused(const zen_cuda_weights* const* w, float* const* d_y,
     if (!init_locked(s)) return 0;
     if (!w || !d_y || !d_x || !fusion) return set_error(s, "dev_gemv_fused: bad arguments") ? 1 : 0;
     return enqueue_gemv(s, w, d_y, count, d_x, tokens, act_mode, stream ? static_cast<cudaStream_t>(stream) : s.stream, nullptr, fusion->gate,
-                        fusion->norm_weight, fusion->norm_eps, fusion->accumulate != 0, fusion->warm_next) ? 1 : 0;
+                        fusion->norm_weight, fusion->norm_eps, fusion->accumulate != 0, fusion->warm_next, fusion->swiglu_pair != 0) ? 1 : 0;
 }
 
 zen_cuda_gemv_list* zen_cuda_gemv_list_create(const zen_cuda_gemv_list_item* items, size_t count, int act_mode) {

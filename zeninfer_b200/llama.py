@@ -107,15 +107,16 @@ class LlamaDecoder:
     synthetic_tensors does; matrices must be Q8_0 raw blocks [rows, row_bytes]."""
 
     def __init__(self, backend: Backend, cfg: LlamaConfig, tensors, act_mode: int = ACT_INT8, max_positions: int | None = None, device=None,
-                 fused: bool | str = "nr", rank: int = 0, world: int = 1, group=None, gather: str = "peer", cut: str = "rows+cols",
+                 fused: bool | str = "nrp", rank: int = 0, world: int = 1, group=None, gather: str = "peer", cut: str = "rows+cols",
                  prompt_act_mode: int | None = None):
         """fused: which of the layer's small operators are folded into the projection launches, as a string of letters:
         'n' RMSNorm into the q|k|v, gate|up and lm_head prologues, 's' SwiGLU into the down projection's prologue,
-        'r' the residual adds into the o and down projections' stores.  True = all (5 launches per layer), False =
-        none (8 per layer); the default folds what pays: the norm costs a CTA one extra pass over a 16 KB row, SwiGLU would
-        cost every CTA 14336 exponentials.  Same arithmetic either way.
+        'r' the residual adds into the o and down projections' stores, 'p' SwiGLU into the gate|up launch's store (the two
+        halves of a CTA compute row r of gate and of up together and store silu(g) * u; not together with 's').  True =
+        "nsr", False = none (8 launches per layer); the default folds what pays: the norm costs a CTA one extra pass over a
+        16 KB row, 's' would cost every CTA 14336 exponentials, 'p' costs a barrier per row group.  Same arithmetic either way.
         rank, world, group: this process's share of a row-sharded model and the torch.distributed group of the ranks; world
-        must divide the KV heads, the embedding, the ffn width and the vocabulary, and fused must be "nr".
+        must divide the KV heads, the embedding, the ffn width and the vocabulary, and fused must be "nr" or "nrp".
         gather: "peer" = the library's own all-gather kernel over NVLink peer memory (the group only carries the IPC
         handles and host barriers, any backend), "nccl" = all_gather_into_tensor (the group must be NCCL).
         cut: "rows" = every matrix by output rows (four gathers per layer); "rows+cols" (default) = o and down by columns,
@@ -129,6 +130,8 @@ class LlamaDecoder:
         self.torch, self.be, self.cfg, self.act_mode = torch, backend, cfg, act_mode
         self.prompt_act_mode = prompt_act_mode if prompt_act_mode not in (None, act_mode) else None
         self.fuse = "nsr" if fused is True else "" if fused is False else str(fused)
+        if "p" in self.fuse and "s" in self.fuse:
+            raise ValueError("SwiGLU is folded into the gate|up store ('p') or into the down prologue ('s'), not both")
         self.rank, self.world, self.group = int(rank), int(world), group
         if not 0 <= self.rank < self.world:
             raise ValueError(f"rank {rank} of {world}")
@@ -136,8 +139,8 @@ class LlamaDecoder:
             for what, n in (("kv_heads", cfg.kv_heads), ("embedding", cfg.embedding), ("ffn", cfg.ffn), ("vocab", cfg.vocab)):
                 if n % self.world:
                     raise ValueError(f"{what} = {n} does not split over {self.world} ranks")
-            if set(self.fuse) != set("nr"):
-                raise ValueError('a row-sharded decoder runs with fused="nr"')
+            if set(self.fuse) - {"p"} != set("nr"):
+                raise ValueError('a row-sharded decoder runs with fused="nr" or "nrp"')
             import torch.distributed  # noqa: F401  (the collectives of _gather, handle exchange, host barriers)
             if gather not in ("peer", "nccl"):
                 raise ValueError(f"gather = {gather!r}")
@@ -204,10 +207,10 @@ class LlamaDecoder:
             return cls(backend, cfg, gguf.llama_tensors(g, cfg), **kwargs)   # uploads complete before the mapping closes
 
     # ---- one token step, as launches on self.stream ----
-    def _gemv(self, handles, outs, x, *, norm=None, gate=None, acc=False, warm=None) -> None:
+    def _gemv(self, handles, outs, x, *, norm=None, gate=None, acc=False, warm=None, pair=False) -> None:
         """One product launch on the decoder's stream; `warm` is the tensor the next product launch will read."""
         self.be.dev_gemv_fused(handles, outs, x, 1, self.act_mode, self.stream.cuda_stream, norm_weight=norm, norm_eps=self.cfg.rms_eps if norm else 0.0,
-                               gate=gate, accumulate=acc, warm_next=warm)
+                               gate=gate, accumulate=acc, warm_next=warm, swiglu_pair=pair)
 
     def _gather(self, whole, piece) -> None:
         """Every rank's piece into every rank's whole vector, in place (piece is this rank's slice of whole), ordered on
@@ -228,7 +231,7 @@ class LlamaDecoder:
         be, cfg, st = self.be, self.cfg, self.stream.cuda_stream
         P = lambda t: t.data_ptr()
         E, eps = cfg.embedding, cfg.rms_eps
-        fn, fs, fr = "n" in self.fuse, "s" in self.fuse, "r" in self.fuse
+        fn, fs, fr, fp = "n" in self.fuse, "s" in self.fuse, "r" in self.fuse, "p" in self.fuse
         # the residual stream is self.x; a projection's input is x itself (norm folded in) or its normalised copy self.xn
         be.dev_embed_q8_0(self.h["token_embd.weight"], P(self.token), P(self.x), st)
         if not fn:
@@ -255,9 +258,9 @@ class LlamaDecoder:
                 be.dev_rms_norm(P(self.x), None if fr else P(self.tmp), P(self.norm[p + "ffn_norm.weight"]), P(self.xn), E, 1, eps, st)
             elif not fr:
                 be.dev_rms_norm(P(self.x), P(self.tmp), None, None, E, 1, eps, st)                                 # x += tmp only
-            self._gemv([self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]], [P(self.gate), P(self.up)], P(self.x) if fn else P(self.xn),
-                       norm=P(self.norm[p + "ffn_norm.weight"]) if fn else None, warm=self.h[p + "ffn_down.weight"])
-            if not fs:
+            self._gemv([self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]], [P(self.hid_mine), None] if fp else [P(self.gate), P(self.up)],
+                       P(self.x) if fn else P(self.xn), norm=P(self.norm[p + "ffn_norm.weight"]) if fn else None, warm=self.h[p + "ffn_down.weight"], pair=fp)
+            if not fs and not fp:
                 be.dev_silu_mul(P(self.gate), P(self.up), P(self.hid_mine), cfg.ffn // self.world, st)
             if self.col_cut:
                 self._gemv([self.h[p + "ffn_down.weight"]], [P(self.tmp)], P(self.hid_mine), warm=nxt_q)
