@@ -808,9 +808,9 @@ def torch_q8_0_pack(w):
 
 def run_decode(args, brief: bool = False) -> dict | None:
     """Config: 32 layers, d 4096, 32 query / 8 KV heads of 128, SwiGLU 14336, vocab 128256, eps 1e-5, theta 500000,
-    weights N(0, 0.02) seed 6, a prompt of 512 uniform-random ids, then greedy decode steps.  On one GPU the prompt is
-    consumed as blocks of tensor-core products and timed separately (prefill_ms); a sharded decoder takes it token by
-    token.  A step is one decoded token: the launches of 32 layers, the lm_head and the pick, replayed from two CUDA
+    weights N(0, 0.02) seed 6, a prompt of 512 uniform-random ids, then greedy decode steps.  The prompt is consumed as
+    blocks of tensor-core products and timed separately (prefill_ms); sharded, the block's partial products are summed by
+    two NCCL all-reduces per layer.  A step is one decoded token: the launches of 32 layers, the lm_head and the pick, replayed from two CUDA
     graphs (RMSNorm and the residual adds are folded into the projection launches)."""
     import torch
     from zeninfer_b200 import Backend
@@ -847,7 +847,7 @@ def run_decode(args, brief: bool = False) -> dict | None:
                        gather="nccl" if args.gather == "nccl" else "peer", cut=args.cut)
     load_s = time.perf_counter() - t0
     dec.capture()
-    token_prefill = args.token_prefill or world > 1     # the block prefill is not sharded
+    token_prefill = args.token_prefill or not dec.can_prefill_blocks()     # sharded: blocks need the column cut and the NCCL group
     prompt = np.random.default_rng(6).integers(0, cfg.vocab, size=prompt_len, dtype=np.int64)
     stream = dec.stream
     with ClockSampler(local) as clocks:
@@ -961,7 +961,8 @@ def run_decode(args, brief: bool = False) -> dict | None:
                                 + ("(o and down cut by columns, their partial products all-reduced into the residual stream; logits gathered), "
                                    if dec.col_cut else "(all-gathers of attention output, o, SwiGLU activation, down; logits), ")
                                 + ("NCCL collectives" if args.gather == "nccl" else "each one launch of a peer-store kernel over NVLink")),
-                   "load_s": load_s, "prefill": ("token by token" if token_prefill else "blocks of up to 512 tokens through the tcgen05 GEMM + causal block attention"),
+                   "load_s": load_s, "prefill": ("token by token" if token_prefill else "blocks of up to 512 tokens through the tcgen05 GEMM + causal block attention"
+                               + (", two all-reduces of the block's partial products per layer (NCCL)" if world > 1 else "")),
                    "prefill_ms": prefill_ms, "prefill_tokens_per_s": prompt_len / (prefill_ms * 1e-3)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "traffic": None,
                      "kernel": "whole token step (projections through gemv_q8_0_kernel<1,1>)", "launch_us": ms * 1e3 / steps,

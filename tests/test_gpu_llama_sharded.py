@@ -68,6 +68,34 @@ def _rank_main(rank: int, world: int, port: int, out_dir: str):
                     dist.barrier()
                     dec.close()
                     whole.close()
+        # the prompt as sharded blocks (q|k|v, gate, up by rows; o and down by columns, their partial products of the whole
+        # block all-reduced): against the same decoder taking the prompt token by token and against one GPU's block prefill
+        long_prompt = np.random.default_rng(79).integers(3, cfg.vocab, size=45).tolist()
+        for mode, tag in ((ACT_INT8, "pf8"), (ACT_FP32, "pf32")):
+            model = lambda: synthetic_tensors(cfg, meta["seed"], meta["weight_std"])
+            dec = LlamaDecoder(be, cfg, model(), act_mode=mode, rank=rank, world=world, gather="peer", cut="rows+cols")
+            whole = LlamaDecoder(be, cfg, model(), act_mode=mode)
+            try:
+                assert dec.can_prefill_blocks()
+                dec.PREFILL_CHUNK = whole.PREFILL_CHUNK = 32       # a 32-token block, then 13 tokens one by one
+                result[tag + "_ids_blocks"] = dec.generate(long_prompt, 6)
+                result[tag + "_logits_blocks"] = dec.last_logits()
+                result[tag + "_ids_tokens"] = dec.generate(long_prompt, 6, batched_prefill=False)
+                result[tag + "_logits_tokens"] = dec.last_logits()
+                result[tag + "_ids_whole"] = whole.generate(long_prompt, 6)
+                result[tag + "_logits_whole"] = whole.last_logits()
+            except BaseException:
+                failed = True
+                raise
+            finally:
+                if not failed:
+                    dist.barrier()
+                    dec.close()
+                    whole.close()
+        rows_only = LlamaDecoder(be, cfg, synthetic_tensors(cfg, meta["seed"], meta["weight_std"]), rank=rank, world=world, gather="peer", cut="rows")
+        assert not rows_only.can_prefill_blocks()
+        dist.barrier()
+        rows_only.close()
         with pytest.raises(ValueError):
             LlamaDecoder(be, cfg, (), rank=rank, world=world, fused="n")
         torch.save(result, os.path.join(out_dir, f"rank{rank}.pt"))
@@ -112,3 +140,10 @@ def test_row_sharded_generation_matches_the_reference_and_the_unsharded_decoder(
             first = torch.load(os.path.join(tmp_path, "rank0.pt"), weights_only=False)
             for tag in ("cols", "cols8"):
                 assert np.array_equal(got[f"{tag}_logits_{how}"], first[f"{tag}_logits_{how}"]), f"rank {r} and rank 0 differ ({tag}, {how})"
+        # int8: rounding to codes is discontinuous, so the different summation order of the block products flips a few codes
+        # and the difference is carried through the six generated tokens (the bar of the int8 golden test's final logits)
+        for tag, tol in (("pf32", 1e-3), ("pf8", 5e-2)):
+            assert got[f"{tag}_ids_blocks"] == got[f"{tag}_ids_tokens"] == got[f"{tag}_ids_whole"], f"rank {r} {tag}"
+            assert_parity(got[f"{tag}_logits_blocks"], got[f"{tag}_logits_tokens"], tol, f"rank {r} {tag}: sharded blocks vs sharded token by token")
+            assert_parity(got[f"{tag}_logits_blocks"], got[f"{tag}_logits_whole"], tol, f"rank {r} {tag}: sharded blocks vs one GPU's blocks")
+            assert np.array_equal(got[f"{tag}_logits_blocks"], first[f"{tag}_logits_blocks"]), f"rank {r} and rank 0 differ after a sharded block prefill ({tag})"

@@ -330,47 +330,66 @@ class LlamaDecoder:
 
     def _prefill_buffers(self):
         if getattr(self, "_pf", None) is None:
-            torch, cfg, T = self.torch, self.cfg, self.PREFILL_CHUNK
+            torch, cfg, T, w = self.torch, self.cfg, self.PREFILL_CHUNK, self.world
             f32 = dict(dtype=torch.float32, device=self.dev)
             mode = self._prefill_mode()
-            ws_bytes = max(self.be.gemm_workspace_bytes(T, n, mode) for n in (cfg.embedding, cfg.ffn, cfg.q_width))
+            ws_bytes = max(self.be.gemm_workspace_bytes(T, n, mode) for n in (cfg.embedding, cfg.ffn // w, cfg.q_width // w))
+            # x, xn, tmp are whole on every rank; q, k, v, att, gate, up, hid hold this rank's heads / ffn rows
             self._pf = dict(x=torch.zeros((T, cfg.embedding), **f32), xn=torch.zeros((T, cfg.embedding), **f32), tmp=torch.zeros((T, cfg.embedding), **f32),
-                            q=torch.zeros((T, cfg.q_width), **f32), k=torch.zeros((T, cfg.kv_width), **f32), v=torch.zeros((T, cfg.kv_width), **f32),
-                            att=torch.zeros((T, cfg.q_width), **f32), gate=torch.zeros((T, cfg.ffn), **f32), up=torch.zeros((T, cfg.ffn), **f32),
-                            hid=torch.zeros((T, cfg.ffn), **f32), ws=torch.zeros(ws_bytes, dtype=torch.uint8, device=self.dev), ws_bytes=ws_bytes)
+                            q=torch.zeros((T, cfg.q_width // w), **f32), k=torch.zeros((T, cfg.kv_width // w), **f32), v=torch.zeros((T, cfg.kv_width // w), **f32),
+                            att=torch.zeros((T, cfg.q_width // w), **f32), gate=torch.zeros((T, cfg.ffn // w), **f32), up=torch.zeros((T, cfg.ffn // w), **f32),
+                            hid=torch.zeros((T, cfg.ffn // w), **f32), ws=torch.zeros(ws_bytes, dtype=torch.uint8, device=self.dev), ws_bytes=ws_bytes)
         return self._pf
 
     def _prefill_mode(self) -> int:
         """Activation mode of the prompt block's products: prompt_act_mode when one was given, else the decode mode."""
         return self.prompt_act_mode if self.prompt_act_mode is not None else self.act_mode
 
+    def can_prefill_blocks(self) -> bool:
+        """One GPU, or a sharded decoder whose o and down projections are cut by columns and whose group is NCCL: the
+        block's two exchanges per layer are then all-reduces of [tokens, embedding] partial products."""
+        if self.world == 1:
+            return True
+        return self.col_cut and self.torch.distributed.get_backend(self.group) == "nccl"
+
     def prefill(self, d_tokens, count: int) -> None:
         """Consumes `count` tokens (device int64) at positions pos .. pos + count - 1 as one block: the projections run
         as tcgen05 GEMMs (int8 activations, or two int8 digits per activation in the fp32-equivalent mode), the attention
         as the causal block kernel; afterwards the residual stream and its normalised copy of the LAST token are in
-        self.x / self.xn, ready for the lm_head, and pos has advanced."""
-        if self.world > 1:
-            raise ValueError("the block prefill is not sharded: a row-sharded decoder takes its prompt token by token")
-        be, cfg, st = self.be, self.cfg, self.stream.cuda_stream
+        self.x / self.xn, ready for the lm_head, and pos has advanced.
+        Sharded (can_prefill_blocks): q|k|v, gate and up are this rank's rows (its heads, its slice of the ffn), attention
+        and the KV cache are rank-local, o and down multiply this rank's columns and the ranks' partial products of the
+        whole block are summed by one NCCL all-reduce each (two per layer, [tokens, embedding] fp32), after which every
+        rank adds the same sum to its copy of the residual stream."""
+        if not self.can_prefill_blocks():
+            raise ValueError("the block prefill needs one GPU, or the column cut with an NCCL group; this decoder takes its prompt token by token")
+        be, cfg, st, w = self.be, self.cfg, self.stream.cuda_stream, self.world
         b = self._prefill_buffers()
         P = lambda t: t.data_ptr()
         T, E, eps = count, cfg.embedding, cfg.rms_eps
         mode = self._prefill_mode()
         gemm = lambda hs, outs, x: be.dev_gemm_q8_0(hs, [P(o) for o in outs], P(x), T, P(b["ws"]), b["ws_bytes"], st, act_mode=mode)
+
+        def reduce_partials():
+            if w > 1:   # tmp[:T] holds this rank's partial product of every output
+                self.torch.distributed.all_reduce(b["tmp"][:T], group=self.group)
+
         be.dev_embed_rows_q8_0(self.h["token_embd.weight"], P(d_tokens), T, P(b["x"]), st)
         be.dev_rms_norm(P(b["x"]), None, P(self.norm["blk.0.attn_norm.weight"]), P(b["xn"]), E, T, eps, st)
         for layer in range(cfg.layers):
             p = f"blk.{layer}."
             gemm([self.h[p + "attn_q.weight"], self.h[p + "attn_k.weight"], self.h[p + "attn_v.weight"]], [b["q"], b["k"], b["v"]], b["xn"])
-            be.dev_rope_kv_append_rows(P(b["q"]), P(b["k"]), P(b["v"]), T, P(self.cos), P(self.sin), P(self.pos), cfg.heads, cfg.kv_heads, cfg.head_dim,
+            be.dev_rope_kv_append_rows(P(b["q"]), P(b["k"]), P(b["v"]), T, P(self.cos), P(self.sin), P(self.pos), cfg.heads // w, cfg.kv_heads // w, cfg.head_dim,
                                        cfg.head_dim // 2, True, P(self.k_cache[layer]), P(self.v_cache[layer]), self.max_positions, st)
-            be.dev_attention_prefill(P(b["q"]), P(self.k_cache[layer]), P(self.v_cache[layer]), P(self.pos), P(b["att"]), T, cfg.heads, cfg.kv_heads,
+            be.dev_attention_prefill(P(b["q"]), P(self.k_cache[layer]), P(self.v_cache[layer]), P(self.pos), P(b["att"]), T, cfg.heads // w, cfg.kv_heads // w,
                                      cfg.head_dim, self.max_positions, 0.0, 0, st)
             gemm([self.h[p + "attn_output.weight"]], [b["tmp"]], b["att"])
+            reduce_partials()
             be.dev_rms_norm(P(b["x"]), P(b["tmp"]), P(self.norm[p + "ffn_norm.weight"]), P(b["xn"]), E, T, eps, st)          # x += o; xn = norm(x)
             gemm([self.h[p + "ffn_gate.weight"], self.h[p + "ffn_up.weight"]], [b["gate"], b["up"]], b["xn"])
-            be.dev_silu_mul(P(b["gate"]), P(b["up"]), P(b["hid"]), T * cfg.ffn, st)
+            be.dev_silu_mul(P(b["gate"]), P(b["up"]), P(b["hid"]), T * (cfg.ffn // w), st)
             gemm([self.h[p + "ffn_down.weight"]], [b["tmp"]], b["hid"])
+            reduce_partials()
             nxt = self.norm[f"blk.{layer + 1}.attn_norm.weight"] if layer + 1 < cfg.layers else self.norm["output_norm.weight"]
             be.dev_rms_norm(P(b["x"]), P(b["tmp"]), P(nxt), P(b["xn"]), E, T, eps, st)                                       # x += down; xn = next norm
         be.dev_advance_position(P(self.pos), T, st)
@@ -380,12 +399,12 @@ class LlamaDecoder:
 
     def feed_prompt(self, prompt: list[int], batched_prefill: bool | None = None) -> None:
         """Enqueues the whole prompt from position self.pos on, ending with the first pick (left in self.token).  Blocks of
-        at least PREFILL_MIN tokens go through prefill() when batched_prefill (default: on one GPU), the rest token by
-        token."""
+        at least PREFILL_MIN tokens go through prefill() when batched_prefill (default: wherever can_prefill_blocks()), the
+        rest token by token."""
         torch = self.torch
         ids = torch.tensor(prompt, dtype=torch.int64).pin_memory()
         if batched_prefill is None:
-            batched_prefill = self.world == 1
+            batched_prefill = self.can_prefill_blocks()
         with torch.cuda.stream(self.stream):
             done = 0
             if batched_prefill and len(prompt) >= self.PREFILL_MIN:
@@ -419,9 +438,9 @@ class LlamaDecoder:
         """Generation: the prompt, then max_new picks (each read back, as the reference's per-token callback does).  With
         temperature <= 0 the picks are greedy; otherwise every token is drawn on the device from the temperature / top-k /
         top-p distribution of the step's logits (GenerationOptions, sample_logits :391-418), with one uniform number per
-        token from a host generator seeded with `seed` (the generator stays on the host, as the reference's does).  On one
-        GPU the prompt goes through prefill() in blocks (in the prompt's activation mode), token by token on a sharded
-        decoder; batched_prefill overrides the choice.
+        token from a host generator seeded with `seed` (the generator stays on the host, as the reference's does).  The
+        prompt goes through prefill() in blocks (in the prompt's activation mode) on one GPU and on a column-cut sharded
+        decoder with an NCCL group, token by token otherwise; batched_prefill overrides the choice.
         Raises when the context would overflow."""
         torch = self.torch
         if not prompt or len(prompt) + max_new > self.max_positions:
