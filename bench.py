@@ -780,8 +780,10 @@ def run_lm_head(args, brief: bool = False) -> dict | None:
                    "gather": ("none (one GPU)" if world == 1 else "fused into the product kernel (peer stores over NVLink)" if fused else "NCCL all-gather"),
                    "l2": f"inputs larger than L2: {ncopy} rotating copies of the {shard_bytes / 1e6:.0f} MB shard per GPU", "launch": "CUDA graph replay"},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak, "peak_kind": peak_kind, "traffic": None,
-                     "kernel": "gemv_kq_kernel<Q6_K, 1> (per GPU; step time includes the gather wait and the pick)", "launch_us": r1["us_per_step"],
-                     "algorithmic_bytes_per_launch": r1["algorithmic_bytes"] // world},
+                     "kernel": "gemv_kq_kernel<Q6_K codes unpacked, 1> (per GPU; step time includes the gather wait and the pick)", "launch_us": r1["us_per_step"],
+                     "algorithmic_bytes_per_launch": r1["algorithmic_bytes"] // world,
+                     "device_layout": "6-bit codes unpacked on upload to one int8 per weight: the kernel streams 1.30 x the algorithmic (file) bytes, "
+                                      "272 B per 256 weights for 210, and no longer rebuilds codes from ql | qh (ZEN_CUDA_Q6K_CODES=0 keeps the file's planes: 143 us)"},
         "detail": {"batch1": r1, "batch8": results[8]}, "cpu_baseline": cpu, "clocks": clocks.summary(), "e2e": e2e,
         "gpu_launches": sum(r["steps"] for r in results.values()) * (4 if fused else 3),
     })

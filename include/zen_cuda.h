@@ -145,6 +145,15 @@ int zen_cuda_rms_norm(const float* x, const float* weight, float* y, size_t rows
 int zen_cuda_gemv_q8_0_ffn(const uint8_t* gate, const uint8_t* up, const uint8_t* down, const float* x, float* y, size_t ffn_rows,
                            size_t columns, size_t out_rows);
 
+/* Device layout of Q6_K tensors uploaded from now on (tensors already resident keep theirs; a launch takes tensors of one
+ * layout).  on != 0 (the default; ZEN_CUDA_Q6K_CODES=0 changes it): the 6-bit codes are unpacked on upload to one int8
+ * per weight (q - 32, element order), beside the group scales and super-block scales: 1.07 bytes per weight of device
+ * memory and HBM traffic instead of the file's 0.82, and the decode kernel no longer rebuilds codes from ql and qh, which
+ * bound it by instruction issue.
+ * on == 0: the file's ql | qh | scales planes.  Results are the same bit for bit.  Returns the previous setting, -1 on
+ * failure. */
+int zen_cuda_set_q6k_codes(int on);
+
 /* Residency budget of the pointer-keyed weights: kVRAMBudgetPercent, src/backends/hip/hip_backend.hip:50 and :459-476.
  * The tensors the host-pointer calls keep resident stay below the budget (80 % of the device's memory unless set here
  * or by ZEN_CUDA_VRAM_BUDGET_MB; bytes == 0 restores the default).  A tensor that would cross it evicts the WHOLE keyed

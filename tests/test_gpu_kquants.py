@@ -162,3 +162,38 @@ def test_long_run_of_overlapped_launches_is_deterministic(be, zo, fmt):
     assert_parity(first.cpu().numpy(), zo.gemv(fmt, w, x[0], rows, cols), what=f"{NAMES[fmt]} first launch vs oracle")
     for h in handles:
         be.dev_free(h)
+
+
+@pytest.mark.parametrize("rows,cols,tokens", [(1, 256, 1), (67, 1280, 1), (1027, 4096, 1), (64, 14336, 1), (130, 2048, 3), (300, 4096, 8), (9, 4352, 11)])
+def test_q6_k_both_device_layouts_give_the_same_bits(be, zo, golden, rows, cols, tokens):
+    # the default device layout keeps the 6-bit codes unpacked (one int8 per weight); the file's ql | qh planes remain
+    # selectable.  Both kernels form the same integer sums, so the results are equal bit for bit, and both meet the oracle.
+    import torch
+    from zeninfer_b200.backend import ACT_FP32
+    w = seeded_weights(Q6_K, rows, cols, 800 + rows)
+    x = seeded_acts(tokens, cols, 810 + cols)
+    outs, sizes = [], []
+    before = be.set_q6k_codes(True)
+    try:
+        for codes in (True, False):
+            be.set_q6k_codes(codes)
+            h = be.dev_upload("Q6_K", w, rows, cols)
+            sizes.append(be.dev_weight_bytes(h))
+            d_x = torch.from_numpy(x).cuda()
+            y = torch.zeros((tokens, rows), device="cuda")
+            step = 8 if cols <= 4096 else 2      # the activation rows of a launch share shared memory with the weight ring
+            for t0 in range(0, tokens, step):
+                n = min(step, tokens - t0)
+                be.dev_gemv([h], [y[t0:].data_ptr()], d_x[t0:].data_ptr(), n, ACT_FP32)
+            be.dev_check()
+            outs.append(y.cpu().numpy())
+            be.dev_free(h)
+        host = be.gemm("Q6_K", w, x, tokens, rows, cols)        # the host-pointer call, resident in the layout set last
+        be.release_weights(w)
+    finally:
+        be.set_q6k_codes(before)
+    assert np.array_equal(outs[0], outs[1])
+    assert_parity(host, outs[1], 1e-5, "host-pointer call")    # its token chunks may differ: a one-token launch sums a row in another order
+    assert sizes[0] >= sizes[1] and (rows * cols < 65536 or sizes[0] > 1.25 * sizes[1])     # 1.07 against 0.82 bytes per weight, plus 64 bytes of slack per plane
+    ref = np.stack([zo.gemv(Q6_K, w, x[t], rows, cols) for t in range(tokens)])
+    assert_parity(outs[0], ref, what=f"Q6_K unpacked codes {tokens}x{rows}x{cols}")

@@ -32,7 +32,7 @@ ABI_SYMBOLS = (
     "zen_cuda_last_error", "zen_cuda_set_q8_act_mode", "zen_cuda_get_q8_act_mode",
     "zen_cuda_gemv_q8_0", "zen_cuda_gemm_q8_0", "zen_cuda_gemv_q8_0_batch", "zen_cuda_gemm_q8_0_batch",
     "zen_cuda_gemm_q6_k", "zen_cuda_gemm_q4_0", "zen_cuda_gemm_kquant", "zen_cuda_release_weights", "zen_cuda_quantize_acts",
-    "zen_cuda_rms_norm", "zen_cuda_gemv_q8_0_ffn", "zen_cuda_set_vram_budget", "zen_cuda_residency",
+    "zen_cuda_rms_norm", "zen_cuda_gemv_q8_0_ffn", "zen_cuda_set_vram_budget", "zen_cuda_residency", "zen_cuda_set_q6k_codes",
     "zen_cuda_dev_upload", "zen_cuda_dev_free", "zen_cuda_dev_weight_bytes", "zen_cuda_dev_gemv",
     "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_error_name", "zen_cuda_set_wait_budget_ms",
     "zen_cuda_gemv_list_create", "zen_cuda_gemv_list_destroy", "zen_cuda_gemv_list_bytes", "zen_cuda_dev_gemv_list",
@@ -286,6 +286,14 @@ class Backend:
                                                ffn_rows, columns, out_rows):
             self._fail(f"gemv_q8_0_ffn {ffn_rows}x{columns} -> {out_rows}")
         return y
+
+    def set_q6k_codes(self, on: bool) -> bool:
+        """Device layout of Q6_K tensors uploaded from now on: unpacked int8 codes (True, the default) or the file's
+        ql | qh planes.  Returns the previous setting."""
+        before = self.lib.zen_cuda_set_q6k_codes(int(bool(on)))
+        if before < 0:
+            self._fail("set_q6k_codes")
+        return bool(before)
 
     def set_vram_budget(self, nbytes: int) -> None:
         """Residency budget of the pointer-keyed weights in bytes; 0 restores 80 % of the device's memory."""

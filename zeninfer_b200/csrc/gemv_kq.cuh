@@ -64,6 +64,18 @@ template <> struct KqFormat<13> {  // Q5_K: nibbles [K/2], fifth bits [K/8], sca
     }
     __host__ __device__ static constexpr uint32_t bytes_per_256(int plane) { return plane == 0 ? 128 : plane == 1 ? 32 : plane == 2 ? 16 : 4; }
 };
+// Q6_K with the codes unpacked on upload (kFormatQ6KCodes): q - 32 as one int8 per weight in element order, the group
+// scales and super-block scales as in the packed layout.  The device copy is 1.07 bytes per weight instead of the file's
+// 0.82, and the inner loop loses the 24 shift/mask operations per 16 weights that rebuild a code from ql and qh: the
+// packed kernel is bound by instruction issue at 0.45 of the HBM rate, this one streams 1.3 x the bytes at 0.9 of it.
+// The integer sums, and therefore the results, are the packed kernel's bit for bit.
+constexpr int kFormatQ6KCodes = 114;
+template <> struct KqFormat<kFormatQ6KCodes> {  // codes [K] int8, sc [K/16] int8, d [K/256] f16
+    static constexpr int kPlanes = 3;
+    static constexpr int kStages = 4;
+    __host__ __device__ static constexpr uint32_t seg_bytes(int plane) { return plane == 0 ? kKqSegElems : plane == 1 ? kKqSegElems / 16 : kKqSegElems / 256 * 2; }
+    __host__ __device__ static constexpr uint32_t bytes_per_256(int plane) { return plane == 0 ? 256 : plane == 1 ? 16 : 2; }
+};
 // Q4_K and Q5_K share everything but the fifth-bit plane.
 template <int kFormat> constexpr bool kq_is_k45 = kFormat == 12 || kFormat == 13;
 
@@ -346,6 +358,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
         //   Q4_K / Q5_K: warp = (K slice of four super-blocks, half of the eight rows); a lane owns 16 nibble bytes, i.e. 16
         //         weights of sub-block 2j (low nibbles) and the 16 of sub-block 2j+1 at the same positions (high nibbles)
         constexpr bool kK45 = kq_is_k45<kFormat>;
+        constexpr bool kCodes = kFormat == kFormatQ6KCodes;   // a lane owns the 16 weights of group (lane & 15) of its super-block, in element order
         constexpr int kR = (kFormat == 2 || kK45) ? 4 : 8;             // rows per warp
         constexpr int kSlices = (kFormat == 2 || kK45) ? 4 : 8;        // K slices per segment
         const uint32_t kslice = static_cast<uint32_t>(twarp) % kSlices;
@@ -390,6 +403,13 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                 k_f_lo = xs * static_cast<float>(dot16(ones, xa) * 256 + dot16(ones, xc));        // for the minimum term
                 k_f_hi = k_xs_hi * static_cast<float>(dot16(ones, xb) * 256 + dot16(ones, xd4));
                 wofs = live ? k_sb : 0u;
+            } else if (kCodes) {
+                const uint32_t e0 = seg * kKqSegElems + sbl * 256 + sg * 16;
+                const bool live = e0 < p.K;
+                xa = live ? *reinterpret_cast<const uint4*>(xd + e0) : zero;
+                xc = live ? *reinterpret_cast<const uint4*>(xd + kpad + e0) : zero;
+                xs = live ? xscale[e0 / 32] : 0.0f;
+                wofs = live ? sbl : 0u;
             } else {
                 const uint32_t e0 = seg * kKqSegElems + sbl * 256 + qhalf * 128 + group * 32 + six * 16;
                 const bool live = e0 < p.K;
@@ -439,6 +459,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                     w1 = st + kq_plane_offset<kFormat>(1) + rowbase * F::seg_bytes(1) + wofs * 32 + k_h * 16;             // Q5_K: fifth bits
                     sc = reinterpret_cast<const int8_t*>(st + kq_plane_offset<kFormat>(kScm) + rowbase * F::seg_bytes(kScm)) + wofs * 16 + k_j * 2;
                     dd = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(kDd) + rowbase * F::seg_bytes(kDd)) + wofs * 2;
+                } else if (kCodes) {
+                    w0 = st + kq_plane_offset<kFormat>(0) + wofs * 256 + sg * 16;   // codes
+                    w1 = w0;
+                    sc = reinterpret_cast<const int8_t*>(st + kq_plane_offset<kFormat>(1)) + wofs * 16 + sg;
+                    dd = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(2)) + wofs;
                 } else {
                     w0 = st + kq_plane_offset<kFormat>(0) + wofs * 128 + qhalf * 64 + (group & 1) * 32 + six * 16;   // ql
                     w1 = st + kq_plane_offset<kFormat>(1) + wofs * 64 + qhalf * 32 + six * 16;                       // qh
@@ -479,6 +504,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                         const float pos = static_cast<float>(sc2 & 0xffu) * (xs * static_cast<float>(i_lo)) + static_cast<float>(sc2 >> 8) * (k_xs_hi * static_cast<float>(i_hi));
                         const float neg = static_cast<float>(mn2 & 0xffu) * k_f_lo + static_cast<float>(mn2 >> 8) * k_f_hi;
                         acc[r] = fmaf(dm.x, pos, fmaf(-dm.y, neg, acc[r]));
+                    } else if (kCodes) {
+                        const uint4 q = *reinterpret_cast<const uint4*>(w0 + r * F::seg_bytes(0));
+                        const int a = dot16(q, xa), c = dot16(q, xc);
+                        const float dsc = __half2float(dd[r * (F::seg_bytes(2) / 2)]) * static_cast<float>(sc[r * F::seg_bytes(1)]);  // (d * scale), the reference's order
+                        acc[r] = fmaf(dsc * xs, static_cast<float>(a * 256 + c), acc[r]);
                     } else {
                         const uint4 l4 = *reinterpret_cast<const uint4*>(w0 + r * F::seg_bytes(0));
                         const uint4 h4 = *reinterpret_cast<const uint4*>(w1 + r * F::seg_bytes(1));
@@ -618,6 +648,28 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                                     v = fmaf(-ms_lo * xs_lo, static_cast<float>(s_lo), v);
                                     v = fmaf(-ms_hi * xs_hi, static_cast<float>(s_hi), v);
                                     acc[tk] = v;
+                                }
+                            }
+                        }
+                    } else if (kFormat == kFormatQ6KCodes) {
+                        // ---- Q6_K, unpacked codes: a lane owns one 16-weight group in element order; two super-blocks a pass ----
+                        const uint8_t* qc = st + kq_plane_offset<kFormat>(0) + twarp * F::seg_bytes(0);
+                        const int8_t* sc = reinterpret_cast<const int8_t*>(st + kq_plane_offset<kFormat>(1) + twarp * F::seg_bytes(1));
+                        const __half* dd = reinterpret_cast<const __half*>(st + kq_plane_offset<kFormat>(2) + twarp * F::seg_bytes(2));
+                        const uint32_t sg = lane & 15;
+    #pragma unroll 4
+                        for (int i = 0; i < kKqSegElems / 256 / 2; ++i) {
+                            const uint32_t sbl = i * 2 + (lane >> 4);
+                            if (sbl * 256 < elems) {
+                                const uint4 q = *reinterpret_cast<const uint4*>(qc + sbl * 256 + sg * 16);
+                                const float dsc = __half2float(dd[sbl]) * static_cast<float>(sc[sbl * 16 + sg]);
+                                const uint32_t e0 = e_base + sbl * 256 + sg * 16;
+    #pragma unroll
+                                for (int tk = 0; tk < kBatch; ++tk) {
+                                    const uint4 x1 = *reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + e0);
+                                    const uint4 x2 = *reinterpret_cast<const uint4*>(xd + static_cast<size_t>(tk) * 2 * kpad + kpad + e0);
+                                    const int isum = dot16(q, x1) * 256 + dot16(q, x2);
+                                    acc[tk] = fmaf(dsc * xscale[static_cast<size_t>(tk) * (kpad / 32) + e0 / 32], static_cast<float>(isum), acc[tk]);
                                 }
                             }
                         }

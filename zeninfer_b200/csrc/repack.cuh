@@ -112,4 +112,32 @@ __global__ void repack_k45_kernel(const uint8_t* __restrict__ raw, uint8_t* __re
     for (int k = 0; k < 8; ++k) o[k] = src[k];
 }
 
+// Q6_K with the codes unpacked: one thread per 16-weight group.  codes [rows][K] int8 = q - 32 in element order (element
+// half*128 + g*32 + l of a super-block is ql byte half*64 + (g%2)*32 + l, low nibble for g < 2, plus bits 2g.. of qh byte
+// half*32 + l, src/quant.cpp:500-517); sc and d as repack_q6_k_kernel leaves them.
+__global__ void unpack_q6_k_codes_kernel(const uint8_t* __restrict__ raw, int8_t* __restrict__ codes, int8_t* __restrict__ sc, uint16_t* __restrict__ d,
+                                         size_t rows, uint32_t nsb, uint32_t sbp) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;   // group index over the tensor
+    if (i >= rows * nsb * 16) return;
+    const size_t sb = i / 16;
+    const uint32_t g16 = static_cast<uint32_t>(i % 16);      // 16-weight group within the super-block: elements g16*16 ..
+    const size_t r = sb / nsb;
+    const uint32_t b = static_cast<uint32_t>(sb % nsb);
+    const uint8_t* p = raw + sb * 210;
+    const uint32_t e0 = g16 * 16, half = e0 >> 7, g = (e0 >> 5) & 3, l0 = e0 & 31;
+    int8_t out[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const uint32_t l = l0 + k;
+        const uint32_t lo = (p[half * 64 + (g & 1) * 32 + l] >> (g >= 2 ? 4 : 0)) & 15u;
+        const uint32_t hi = (p[128 + half * 32 + l] >> (2 * g)) & 3u;
+        out[k] = static_cast<int8_t>(static_cast<int>(lo | (hi << 4)) - 32);
+    }
+    int8_t* dst = codes + (r * nsb + b) * 256 + e0;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) dst[k] = out[k];
+    sc[(r * nsb + b) * 16 + g16] = static_cast<int8_t>(p[192 + g16]);
+    if (g16 == 0) d[r * sbp + b] = static_cast<uint16_t>(p[208] | (p[209] << 8));
+}
+
 }  // namespace zk

@@ -54,6 +54,7 @@ struct zen_cuda_weights {
     size_t rows{}, cols{};
     uint32_t nb{}, nbp{};     // blocks per row, padded to 8
     void* plane[4]{};         // format-specific planes (see repack.cuh)
+    int kernel_format{};      // what the decode kernel is instantiated for: the format, or zk::kFormatQ6KCodes for Q6_K with unpacked codes
     size_t device_bytes{};
     size_t raw_bytes{};
 };
@@ -96,6 +97,7 @@ struct State {
     bool pdl{true};          // programmatic dependent launch of the GEMV kernels (ZEN_CUDA_PDL=0 turns it off)
     unsigned ctas_per_sm{1}; // persistent GEMV CTAs per SM (ZEN_CUDA_GEMV_CTAS)
     std::unordered_map<ResidentKey, zen_cuda_weights*, ResidentKeyHash> resident;
+    bool q6k_codes{true};     // Q6_K tensors keep their codes unpacked on the device (1.07 B per weight for 0.82; ZEN_CUDA_Q6K_CODES=0 keeps ql | qh)
     // Residency budget of the pointer-keyed set (zen::hip keeps weights below 80 % of VRAM, hip_backend.hip:50 and :459-476).
     uint64_t vram_budget{};   // bytes; 0 = no limit
     uint64_t evictions{};     // times the whole keyed set was dropped to make room
@@ -218,6 +220,7 @@ bool init_locked(State& s) {
             qres != cudaDriverEntryPointSuccess)
             s.encode_tiled = nullptr;
     }
+    if (const char* m = std::getenv("ZEN_CUDA_Q6K_CODES")) s.q6k_codes = std::atoi(m) != 0;
     if (const char* m = std::getenv("ZEN_CUDA_GEMV_CTAS")) s.ctas_per_sm = static_cast<unsigned>(std::max(1, std::min(4, std::atoi(m))));
     if (const char* m = std::getenv("ZEN_CUDA_LIST_AHEAD")) s.list_ahead_units = static_cast<unsigned>(std::max(0, std::min(64, std::atoi(m))));
     if (const char* m = std::getenv("ZEN_CUDA_WAIT_MS")) {
@@ -267,7 +270,7 @@ bool stream_to_device(State& s, void* dst, const uint8_t* src, size_t bytes) {
 }
 
 // Device bytes of each plane of a tensor; every plane gets slack for bulk copies whose size was rounded up to 16 bytes.
-void plane_sizes(int fmt, size_t nrows, size_t cols, size_t plane_bytes[4]) {
+void plane_sizes(int fmt, size_t nrows, size_t cols, size_t plane_bytes[4], bool q6k_codes) {
     const uint32_t nb = static_cast<uint32_t>(cols / block_elems(fmt)), nbp = (nb + 7u) & ~7u;
     plane_bytes[0] = plane_bytes[1] = plane_bytes[2] = plane_bytes[3] = 0;
     if (fmt == ZEN_CUDA_Q4_K || fmt == ZEN_CUDA_Q5_K) {   // nb counts 256-weight super-blocks
@@ -282,6 +285,10 @@ void plane_sizes(int fmt, size_t nrows, size_t cols, size_t plane_bytes[4]) {
     } else if (fmt == ZEN_CUDA_Q4_0) {
         plane_bytes[0] = nrows * (cols / 2) + 64;                          // nibble bytes
         plane_bytes[1] = nrows * static_cast<size_t>(nbp) * 2 + 64;        // f16 scales
+    } else if (q6k_codes) {   // Q6_K, codes unpacked
+        plane_bytes[0] = nrows * cols + 64;                                // q - 32, int8
+        plane_bytes[1] = nrows * (cols / 16) + 64;                         // int8 group scales
+        plane_bytes[2] = nrows * static_cast<size_t>(nbp) * 2 + 64;        // f16 super-block scales
     } else {  // Q6_K: nb counts 256-weight super-blocks
         plane_bytes[0] = nrows * (cols / 2) + 64;                          // ql
         plane_bytes[1] = nrows * (cols / 4) + 64;                          // qh
@@ -308,7 +315,9 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
     auto t0 = clock_type::now();
     bool ok = cudaMalloc(reinterpret_cast<void**>(&d_raw), w->raw_bytes + 16) == cudaSuccess;
     size_t plane_bytes[4];
-    plane_sizes(fmt, nrows, cols, plane_bytes);
+    const bool codes_layout = fmt == ZEN_CUDA_Q6_K && s.q6k_codes;
+    w->kernel_format = codes_layout ? zk::kFormatQ6KCodes : fmt;
+    plane_sizes(fmt, nrows, cols, plane_bytes, s.q6k_codes);
     for (int i = 0; ok && i < 4; ++i)
         if (plane_bytes[i]) {
             ok = cudaMalloc(&w->plane[i], plane_bytes[i]) == cudaSuccess;
@@ -341,6 +350,9 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
         else if (fmt == ZEN_CUDA_Q5_K)
             zk::repack_k45_kernel<true><<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]), static_cast<uint8_t*>(w->plane[1]),
                                                                         static_cast<uint8_t*>(w->plane[2]), static_cast<uint32_t*>(w->plane[3]), nrows, w->nb, w->nbp);
+        else if (codes_layout)
+            zk::unpack_q6_k_codes_kernel<<<static_cast<unsigned>((nblocks * 16 + 255) / 256), 256, 0, s.copy_stream>>>(
+                d_raw, static_cast<int8_t*>(w->plane[0]), static_cast<int8_t*>(w->plane[1]), static_cast<uint16_t*>(w->plane[2]), nrows, w->nb, w->nbp);
         else
             zk::repack_q6_k_kernel<<<grid, 256, 0, s.copy_stream>>>(d_raw, static_cast<uint8_t*>(w->plane[0]), static_cast<uint8_t*>(w->plane[1]),
                                                                    static_cast<int8_t*>(w->plane[2]), static_cast<uint16_t*>(w->plane[3]),
@@ -381,7 +393,7 @@ zen_cuda_weights* lookup_locked(State& s, int fmt, const uint8_t* host, size_t r
     if (it != s.resident.end()) return it->second;
     if (s.vram_budget && block_bytes(fmt) && cols && cols % block_elems(fmt) == 0) {
         size_t pb[4];
-        plane_sizes(fmt, rows, cols, pb);
+        plane_sizes(fmt, rows, cols, pb, s.q6k_codes);
         const uint64_t need = pb[0] + pb[1] + pb[2] + pb[3];
         if (s.stats.weight_bytes + need > s.vram_budget && !s.resident.empty()) evict_resident_locked(s);
         if (s.stats.weight_bytes + need > s.vram_budget) {
@@ -485,7 +497,7 @@ cudaError_t dispatch_kq(int batch, const zk::KqParams& p, unsigned grid, size_t 
     }
 }
 
-size_t gemv_smem_bytes(int format, size_t cols, size_t tokens, int act_mode) {
+size_t gemv_smem_bytes(int format, size_t cols, size_t tokens, int act_mode) {   // format: a kernel format (zen_cuda_weights::kernel_format)
     if (format == ZEN_CUDA_Q8_0) {
         const uint32_t nb = static_cast<uint32_t>(cols / 32), nseg = (nb + zk::kGemvSegBlocks - 1) / zk::kGemvSegBlocks;
         return zk::gemv_q8_0_smem_bytes(nseg, static_cast<int>(tokens), act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1);
@@ -494,6 +506,7 @@ size_t gemv_smem_bytes(int format, size_t cols, size_t tokens, int act_mode) {
     return format == ZEN_CUDA_Q4_0   ? zk::gemv_kq_smem_bytes<ZEN_CUDA_Q4_0>(nseg, static_cast<int>(tokens))
            : format == ZEN_CUDA_Q4_K ? zk::gemv_kq_smem_bytes<ZEN_CUDA_Q4_K>(nseg, static_cast<int>(tokens))
            : format == ZEN_CUDA_Q5_K ? zk::gemv_kq_smem_bytes<ZEN_CUDA_Q5_K>(nseg, static_cast<int>(tokens))
+           : format == zk::kFormatQ6KCodes ? zk::gemv_kq_smem_bytes<zk::kFormatQ6KCodes>(nseg, static_cast<int>(tokens))
                                      : zk::gemv_kq_smem_bytes<ZEN_CUDA_Q6_K>(nseg, static_cast<int>(tokens));
 }
 
@@ -509,8 +522,8 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
     zk::KqParams p{};
     if (gather) p.gather = *gather;
     uint32_t total_rows = 0;
-    const int fmt = w[0]->format;
-    const int planes = plane_count(fmt);
+    const int fmt = w[0]->kernel_format;
+    const int planes = fmt == zk::kFormatQ6KCodes ? 3 : plane_count(fmt);
     for (size_t i = 0; i < count; ++i) {
         for (int k = 0; k < planes; ++k) p.task[i].plane[k] = static_cast<const uint8_t*>(w[i]->plane[k]);
         p.task[i].y = d_y ? d_y[i] : nullptr;
@@ -530,6 +543,8 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
         p.pitch[0] = p.K / 2; p.pitch[1] = p.K / 16; p.pitch[2] = w[0]->nbp * 4;
     } else if (fmt == ZEN_CUDA_Q5_K) {
         p.pitch[0] = p.K / 2; p.pitch[1] = p.K / 8; p.pitch[2] = p.K / 16; p.pitch[3] = w[0]->nbp * 4;
+    } else if (fmt == zk::kFormatQ6KCodes) {
+        p.pitch[0] = p.K; p.pitch[1] = p.K / 16; p.pitch[2] = w[0]->nbp * 2;
     } else {
         p.pitch[0] = p.K / 2; p.pitch[1] = p.K / 4; p.pitch[2] = p.K / 16; p.pitch[3] = w[0]->nbp * 2;
     }
@@ -542,6 +557,7 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
     const cudaError_t e = fmt == ZEN_CUDA_Q4_0   ? dispatch_kq<ZEN_CUDA_Q4_0>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
                           : fmt == ZEN_CUDA_Q4_K ? dispatch_kq<ZEN_CUDA_Q4_K>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
                           : fmt == ZEN_CUDA_Q5_K ? dispatch_kq<ZEN_CUDA_Q5_K>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
+                          : fmt == zk::kFormatQ6KCodes ? dispatch_kq<zk::kFormatQ6KCodes>(static_cast<int>(tokens), p, grid, smem, st, s.pdl)
                                                  : dispatch_kq<ZEN_CUDA_Q6_K>(static_cast<int>(tokens), p, grid, smem, st, s.pdl);
     if (e != cudaSuccess) return set_error(s, std::string("gemv launch: ") + cudaGetErrorString(e));
     ++s.stats.dispatches;
@@ -563,7 +579,8 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
     uint32_t total_rows = 0;
     for (size_t i = 0; i < count; ++i) {
         const bool has_y = d_y && d_y[i];
-        if (!w[i] || (!has_y && !gather && !(swiglu_pair && i == 1)) || w[i]->format != w[0]->format || w[i]->cols != w[0]->cols)
+        if (!w[i] || (!has_y && !gather && !(swiglu_pair && i == 1)) || w[i]->format != w[0]->format || w[i]->kernel_format != w[0]->kernel_format ||
+            w[i]->cols != w[0]->cols)
             return set_error(s, "gemv: tasks must share format and columns");
         p.task[i].codes = static_cast<const uint8_t*>(w[i]->plane[0]);
         p.task[i].scales = static_cast<const __half*>(w[i]->plane[1]);
@@ -1079,7 +1096,7 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     float* d_out[zk::kMaxTasks];
     size_t off = 0;
     for (size_t i = 0; i < count; ++i) { d_out[i] = d_result + off; off += tokens * rows[i]; }
-    const size_t chunk = max_tokens_per_launch(s, fmt, cols, act_mode);
+    const size_t chunk = max_tokens_per_launch(s, w[0]->kernel_format, cols, act_mode);
     if (!chunk) return set_error(s, "columns too large: one activation row does not fit shared memory");
     // More than one decode launch worth of int8-activation Q8_0 tokens: the tensor-core GEMM.
     const bool tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q8_0 && tokens > 8;   // either activation mode
@@ -1489,6 +1506,15 @@ int zen_cuda_gemv_q8_0_ffn(const uint8_t* gate, const uint8_t* up, const uint8_t
     std::lock_guard<std::mutex> lock(s.mutex);
     if (!init_locked(s)) return 0;
     return host_ffn(s, gate, up, down, x, y, ffn_rows, columns, out_rows) ? 1 : 0;
+}
+
+int zen_cuda_set_q6k_codes(int on) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return -1;
+    const int before = s.q6k_codes ? 1 : 0;
+    s.q6k_codes = on != 0;
+    return before;
 }
 
 int zen_cuda_set_vram_budget(uint64_t bytes) {
