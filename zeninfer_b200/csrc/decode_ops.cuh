@@ -133,13 +133,22 @@ __global__ void __launch_bounds__(1024) rope_kv_append_kernel(float* __restrict_
 }
 
 // Grouped-query attention for one new token.  A cluster of kAttnSplit CTAs serves one query head: CTA `rank` takes
-// positions first + rank, first + rank + kAttnSplit, ... (the KV rows of a step are read by 8 x heads CTAs at once,
-// with several rows in flight per warp, and the value rows are pulled into L2 while the scores are computed: at a few
-// hundred positions the kernel is bound by memory latency, not bandwidth).  Each CTA computes its scores q . k[t] * scale (a warp per position, four dimensions per lane), its
-// own maximum, exp(score - maximum), their sum in double and its share of sum_t e[t] * v[t]; rank 0 then reads the
-// other CTAs' (maximum, sum, partial output) through distributed shared memory and combines them:
-// out = sum_r w_r out_r / sum_r w_r s_r with w_r = exp(max_r - max), which is exp(score - max) / denominator applied
-// to v, the reference's formula.  D must be a multiple of 4 and at most 256.
+// positions first + rank, first + rank + kAttnSplit, ...; inside a CTA a warp takes a position at a time, four dimensions
+// per lane, kAttnUnroll positions in flight.  At a few hundred positions the kernel is bound by memory latency, not
+// bandwidth, so it is built to pay as few dependent round trips as possible: the key AND value rows of a warp's
+// positions are requested together, and every warp keeps a running maximum m, denominator l and output accumulator
+// (the streaming form of the softmax: when a new maximum arrives, l and the accumulator are rescaled by
+// exp(m_old - m_new)), so nothing waits for a block-wide maximum between the keys and the values.  Eight warps x four
+// positions x eight CTAs cover 256 positions per round (kWide: head dimensions above 128, eight floats per lane).
+// Resources are part of the design: the kernel runs between two projection launches that overlap with it, so a CTA
+// stays at 256 threads and at most 85 registers.  Measured inside a Llama-3-8B layer at position 575: 8.5 us with four
+// positions per warp and 85 registers; 11.2 us with eight positions and 128 registers although that version is the
+// faster one when timed alone (6.8 against 8.6 us); 512 threads ran the clusters in two waves (19 us); builds that
+// spill to reach 48 or 64 registers lose more than they gain.  The warps' (m, l, accumulator) are merged in shared memory,
+// rank 0 merges the CTAs' shares through distributed shared memory:
+// out = sum_r w_r out_r / sum_r w_r l_r with w_r = exp(m_r - max m), which is exp(score - max) / denominator applied
+// to v, the reference's formula (src/adapters/dense_transformer_runtime.cpp:4284-4337); denominators are kept in double as there.
+// D must be a multiple of 4 and at most 256.
 constexpr int kAttnThreads = 256;
 constexpr int kAttnSplit = 8;
 constexpr int kAttnMaxD = 256;
@@ -169,8 +178,8 @@ __device__ __forceinline__ void rope_quad(float4& v, uint32_t base, uint32_t pai
 // rotated key and the value to the caches.  This is the reference's attention_block contract
 // (include/zen/d3d12_backend.h:247).  Other clusters never read the cache at the current position, so the append
 // races with nothing.
-template <bool kFused>
-__global__ void __cluster_dims__(kAttnSplit, 1, 1) __launch_bounds__(kAttnThreads)
+template <bool kFused, bool kWide>
+__global__ void __cluster_dims__(kAttnSplit, 1, 1) __launch_bounds__(kAttnThreads, kWide ? 2 : 3)
     attention_decode_kernel(const float* __restrict__ q, const float* __restrict__ k_cache_in, const float* __restrict__ v_cache_in,
                             const int* __restrict__ pos_ptr, float* __restrict__ out, uint32_t heads, uint32_t kv_heads, uint32_t D, float scale,
                             uint32_t window, uint32_t max_positions, int* error_word, const float* __restrict__ k_new, const float* __restrict__ v_new,
@@ -178,132 +187,129 @@ __global__ void __cluster_dims__(kAttnSplit, 1, 1) __launch_bounds__(kAttnThread
     const float* k_cache = kFused ? k_cache_out : k_cache_in;   // fused: the caches are also written here, so no read-only promise
     const float* v_cache = kFused ? v_cache_out : v_cache_in;
     namespace cg = cooperative_groups;
-    extern __shared__ float scores[];                 // this CTA's positions
+    constexpr int kWarps = kAttnThreads / 32, kAttnUnroll = 4;
     __shared__ AttnShare share;
-    __shared__ __align__(16) float partial[(kAttnThreads / 32) * kAttnMaxD];   // [warp][dimension]
-    __shared__ float red[kAttnThreads / 32];
-    __shared__ double scratch[8];
+    __shared__ __align__(16) float partial[kWarps * kAttnMaxD];   // [warp][dimension]: the warps' accumulators
+    __shared__ float warp_max[kWarps];
+    __shared__ double warp_sum[kWarps];
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t rank = cluster.block_rank();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t h = blockIdx.y, kh = h / (heads / kv_heads), kw = kv_heads * D;
+    const bool lo_on = 4u * lane < D, hi_on = kWide && 128u + 4u * lane < D;   // !kWide: the compiler drops the upper halves
     pdl_launch_dependents();
     pdl_wait();
+    // the first round trip: the position, and beside it everything whose address does not depend on it
     const int pos = *pos_ptr;
+    const float* qh = q + static_cast<size_t>(h) * D;
+    float4 q0 = make_float4(0.f, 0.f, 0.f, 0.f), q1 = q0;
+    if (lo_on) q0 = __ldcg(reinterpret_cast<const float4*>(qh + 4 * lane));      // q, k_new, v_new: written by the launch before this one
+    if (hi_on) q1 = __ldcg(reinterpret_cast<const float4*>(qh + 128 + 4 * lane));
+    const float* knew = kFused ? k_new + static_cast<size_t>(kh) * D : nullptr;
+    const float* vnew = kFused ? v_new + static_cast<size_t>(kh) * D : nullptr;
+    float4 kn0 = make_float4(0.f, 0.f, 0.f, 0.f), kn1 = kn0, vn0 = kn0, vn1 = kn0;   // the token in flight, every warp's copy
+    if (kFused) {
+        if (lo_on) { kn0 = __ldcg(reinterpret_cast<const float4*>(knew + 4 * lane)); vn0 = __ldcg(reinterpret_cast<const float4*>(vnew + 4 * lane)); }
+        if (hi_on) { kn1 = __ldcg(reinterpret_cast<const float4*>(knew + 128 + 4 * lane)); vn1 = __ldcg(reinterpret_cast<const float4*>(vnew + 128 + 4 * lane)); }
+    }
     const bool bad = pos < 0 || static_cast<uint32_t>(pos) >= max_positions;
     if (bad && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) atomicExch(error_word, kErrBadPosition);
-    const uint32_t h = blockIdx.y, kh = h / (heads / kv_heads), kw = kv_heads * D;
     const uint32_t first = (window && static_cast<uint32_t>(pos) + 1 > window) ? static_cast<uint32_t>(pos) + 1 - window : 0u;
     const uint32_t count = bad ? 0u : static_cast<uint32_t>(pos) + 1 - first;                 // positions attended by the head
     const uint32_t mine = count > rank ? (count - rank + kAttnSplit - 1) / kAttnSplit : 0u;   // ... by this CTA
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float* qh = q + static_cast<size_t>(h) * D;
     const float* kbase = k_cache + static_cast<size_t>(first + rank) * kw + static_cast<size_t>(kh) * D;
     const float* vbase = v_cache + static_cast<size_t>(first + rank) * kw + static_cast<size_t>(kh) * D;
     const size_t step = static_cast<size_t>(kAttnSplit) * kw;     // floats between this CTA's consecutive positions
-    // q for this lane: dimensions 4 * lane + {0..3} (+ 128 when D > 128)
-    const bool lo_on = 4u * lane < D, hi_on = 128u + 4u * lane < D;
-    float4 q0 = make_float4(0.f, 0.f, 0.f, 0.f), q1 = q0;
-    if (lo_on) q0 = *reinterpret_cast<const float4*>(qh + 4 * lane);
-    if (hi_on) q1 = *reinterpret_cast<const float4*>(qh + 128 + 4 * lane);
-    const float* cs = nullptr;
-    const float* sn = nullptr;
-    const float* knew = nullptr;
-    const float* vnew = nullptr;
     const uint32_t last = count ? count - 1 : 0;                  // index of the current position among the attended ones
-    if (kFused && !bad) {
-        cs = cos_t + static_cast<size_t>(pos) * pairs;
-        sn = sin_t + static_cast<size_t>(pos) * pairs;
-        knew = k_new + static_cast<size_t>(kh) * D;
-        vnew = v_new + static_cast<size_t>(kh) * D;
-        if (lo_on) rope_quad(q0, 4u * lane, pairs, cs, sn);
-        if (hi_on) rope_quad(q1, 128u + 4u * lane, pairs, cs, sn);
-        // append: the cluster of the KV group's first query head, the CTA that owns the current position
-        if (h % (heads / kv_heads) == 0 && rank == last % kAttnSplit && threadIdx.x < D) {
-            const uint32_t dd = threadIdx.x, pr = dd >> 1;
-            float a = knew[dd & ~1u], b = knew[dd | 1u];
-            if (pr < pairs) rope_pair(a, b, cs[pr], sn[pr]);
-            k_cache_out[static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D + dd] = (dd & 1u) ? b : a;
-            v_cache_out[static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D + dd] = vnew[dd];
-        }
-    }
-    float local_max = -INFINITY;
-    constexpr int kWarps = kAttnThreads / 32, kUnroll = 4;
-    for (uint32_t i0 = warp; i0 < mine; i0 += kWarps * kUnroll) {
-        float4 ka[kUnroll], kb[kUnroll];
+
+    float run_max = -INFINITY;
+    double run_sum = 0.0;
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    bool rotated = false;
+    for (uint32_t i0 = warp; i0 < mine; i0 += kWarps * kAttnUnroll) {
+        // the second round trip: keys and values of this round's positions together (and, the first time, the cos/sin row)
+        float4 ka[kAttnUnroll], kb[kAttnUnroll], va[kAttnUnroll], vb[kAttnUnroll];
+        bool fresh[kAttnUnroll];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {          // all loads first: several rows in flight per warp
+        for (int u = 0; u < kAttnUnroll; ++u) {
             const uint32_t i = i0 + u * kWarps;
-            ka[u] = kb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (i < mine) {
-                const bool fresh = kFused && rank + i * kAttnSplit == last;     // the token in flight: not in the cache yet
-                const float* kt = fresh ? knew : kbase + static_cast<size_t>(i) * step;
-                if (lo_on) ka[u] = __ldcg(reinterpret_cast<const float4*>(kt + 4 * lane));
-                if (hi_on) kb[u] = __ldcg(reinterpret_cast<const float4*>(kt + 128 + 4 * lane));
-                if (!fresh && lane * 32u < D)    // one lane per 128-byte line of the position's value row
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(vbase + static_cast<size_t>(i) * step + lane * 32));
-                if (fresh) {
-                    if (lo_on) rope_quad(ka[u], 4u * lane, pairs, cs, sn);
-                    if (hi_on) rope_quad(kb[u], 128u + 4u * lane, pairs, cs, sn);
-                }
+            ka[u] = kb[u] = va[u] = vb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            fresh[u] = kFused && i < mine && rank + i * kAttnSplit == last;     // the token in flight: not in the cache yet
+            if (i < mine && !fresh[u]) {
+                const float* kt = kbase + static_cast<size_t>(i) * step;
+                const float* vt = vbase + static_cast<size_t>(i) * step;
+                if (lo_on) { ka[u] = __ldcg(reinterpret_cast<const float4*>(kt + 4 * lane)); va[u] = __ldcg(reinterpret_cast<const float4*>(vt + 4 * lane)); }
+                if (hi_on) { kb[u] = __ldcg(reinterpret_cast<const float4*>(kt + 128 + 4 * lane)); vb[u] = __ldcg(reinterpret_cast<const float4*>(vt + 128 + 4 * lane)); }
             }
         }
+        if (kFused && !rotated && !bad) {   // rotate q and the new key once (table rows of the current position)
+            const float* cs = cos_t + static_cast<size_t>(pos) * pairs;
+            const float* sn = sin_t + static_cast<size_t>(pos) * pairs;
+            if (lo_on) { rope_quad(q0, 4u * lane, pairs, cs, sn); rope_quad(kn0, 4u * lane, pairs, cs, sn); }
+            if (hi_on) { rope_quad(q1, 128u + 4u * lane, pairs, cs, sn); rope_quad(kn1, 128u + 4u * lane, pairs, cs, sn); }
+            rotated = true;
+        }
+        float sc[kAttnUnroll];
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const uint32_t i = i0 + u * kWarps;
+        for (int u = 0; u < kAttnUnroll; ++u) {
+            if (fresh[u]) { ka[u] = kn0; kb[u] = kn1; va[u] = vn0; vb[u] = vn1; }
             float acc = q0.x * ka[u].x + q0.y * ka[u].y + q0.z * ka[u].z + q0.w * ka[u].w + q1.x * kb[u].x + q1.y * kb[u].y + q1.z * kb[u].z + q1.w * kb[u].w;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (i < mine) {
-                const float sc = acc * scale;
-                if (lane == 0) scores[i] = sc;
-                local_max = fmaxf(local_max, sc);
-            }
+            sc[u] = i0 + u * kWarps < mine ? acc * scale : -INFINITY;
         }
-    }
-    if (lane == 0) red[warp] = local_max;
-    __syncthreads();
-    float max_score = red[0];
+        float new_max = run_max;
 #pragma unroll
-    for (int w = 1; w < kWarps; ++w) max_score = fmaxf(max_score, red[w]);
-    double part = 0.0;
-    for (uint32_t i = threadIdx.x; i < mine; i += kAttnThreads) {
-        const float e = expf(scores[i] - max_score);
-        scores[i] = e;
-        part += e;
-    }
-    const double sum = block_sum_double(part, scratch);   // also orders the score writes before the reads below
-    // this CTA's share of sum_t e[t] * v[t]: a warp per position (in turn), four dimensions per lane as for the keys
-    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-    for (uint32_t i0 = warp; i0 < mine; i0 += kWarps * kUnroll) {
-        float4 va[kUnroll], vb[kUnroll];
+        for (int u = 0; u < kAttnUnroll; ++u) new_max = fmaxf(new_max, sc[u]);
+        // i0 < mine, so at least sc[0] is a real score; a non-finite maximum (NaN or +inf scores) is caught by the final check
+        const float corr = run_max == -INFINITY ? 0.0f : expf(run_max - new_max);
+        a0.x *= corr; a0.y *= corr; a0.z *= corr; a0.w *= corr;
+        a1.x *= corr; a1.y *= corr; a1.z *= corr; a1.w *= corr;
+        double add = 0.0;
 #pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const uint32_t i = i0 + u * kWarps;
-            va[u] = vb[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (i < mine) {
-                const bool fresh = kFused && rank + i * kAttnSplit == last;
-                const float* vt = fresh ? vnew : vbase + static_cast<size_t>(i) * step;
-                if (lo_on) va[u] = __ldcg(reinterpret_cast<const float4*>(vt + 4 * lane));
-                if (hi_on) vb[u] = __ldcg(reinterpret_cast<const float4*>(vt + 128 + 4 * lane));
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-            const uint32_t i = i0 + u * kWarps;
-            const float e = i < mine ? scores[i] : 0.0f;
+        for (int u = 0; u < kAttnUnroll; ++u) {
+            const float e = sc[u] == -INFINITY ? 0.0f : expf(sc[u] - new_max);
+            add += e;
             a0.x += e * va[u].x; a0.y += e * va[u].y; a0.z += e * va[u].z; a0.w += e * va[u].w;
             a1.x += e * vb[u].x; a1.y += e * vb[u].y; a1.z += e * vb[u].z; a1.w += e * vb[u].w;
         }
+        run_sum = run_sum * static_cast<double>(corr) + add;
+        run_max = new_max;
     }
+    // append: the cluster of the KV group's first query head, the CTA that owns the current position
+    if (kFused && !bad && h % (heads / kv_heads) == 0 && rank == last % kAttnSplit && threadIdx.x < D) {
+        const float* cs = cos_t + static_cast<size_t>(pos) * pairs;
+        const float* sn = sin_t + static_cast<size_t>(pos) * pairs;
+        const uint32_t dd = threadIdx.x, pr = dd >> 1;
+        float a = __ldcg(knew + (dd & ~1u)), b = __ldcg(knew + (dd | 1u));
+        if (pr < pairs) rope_pair(a, b, cs[pr], sn[pr]);
+        k_cache_out[static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D + dd] = (dd & 1u) ? b : a;
+        v_cache_out[static_cast<size_t>(pos) * kw + static_cast<size_t>(kh) * D + dd] = __ldcg(vnew + dd);
+    }
+    // merge the warps: this CTA's (maximum, denominator, output share)
     if (lo_on) *reinterpret_cast<float4*>(&partial[warp * kAttnMaxD + 4 * lane]) = a0;
     if (hi_on) *reinterpret_cast<float4*>(&partial[warp * kAttnMaxD + 128 + 4 * lane]) = a1;
+    if (lane == 0) { warp_max[warp] = run_max; warp_sum[warp] = run_sum; }
     __syncthreads();
+    float cta_max = warp_max[0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) cta_max = fmaxf(cta_max, warp_max[w]);
     if (threadIdx.x < D) {
         float total = 0.0f;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) total += partial[w * kAttnMaxD + threadIdx.x];
+        for (int w = 0; w < kWarps; ++w) {
+            const float wm = warp_max[w];
+            if (wm != -INFINITY) total += expf(wm - cta_max) * partial[w * kAttnMaxD + threadIdx.x];
+        }
         share.out[threadIdx.x] = total;
     }
-    if (threadIdx.x == 0) { share.max_score = max_score; share.sum = sum; }
+    if (threadIdx.x == 0) {
+        double sum = 0.0;
+        for (int w = 0; w < kWarps; ++w)
+            if (warp_max[w] != -INFINITY) sum += static_cast<double>(expf(warp_max[w] - cta_max)) * warp_sum[w];
+        share.max_score = cta_max;
+        share.sum = sum;
+    }
     cluster.sync();                                   // every CTA's share is complete and visible
     if (rank == 0 && !bad) {
         float m = -INFINITY;

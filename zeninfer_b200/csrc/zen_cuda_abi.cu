@@ -1955,28 +1955,21 @@ bool enqueue_attention(State& s, cudaStream_t st, bool fused, const float* d_q, 
     if (!d_q || !d_k_cache || !d_v_cache || !d_pos || !d_out || !heads || !kv_heads || heads % kv_heads || !head_dim || head_dim % 4 || head_dim > 256 ||
         !max_positions || (fused && (!d_k || !d_v || !d_cos || !d_sin || 2 * pairs > head_dim)))
         return set_error(s, "attention: bad arguments");
-    const size_t span = window ? std::min(window, max_positions) : max_positions;
-    const size_t smem = ((span + zk::kAttnSplit - 1) / zk::kAttnSplit) * sizeof(float);   // a CTA of the cluster holds its own positions' scores
-    if (smem + 12288 > s.smem_optin) return set_error(s, "attention: the attended span does not fit shared memory");
-    static size_t configured[2] = {36 * 1024, 36 * 1024};
-    if (smem > configured[fused]) {
-        const cudaError_t ea = fused ? cudaFuncSetAttribute(zk::attention_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))
-                                     : cudaFuncSetAttribute(zk::attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (ea != cudaSuccess) return set_error(s, "attention: shared memory opt-in failed");
-        configured[fused] = smem;
-    }
+    const size_t smem = 0;   // the streaming softmax keeps no per-position scores
     if (scale == 0.0f) scale = 1.0f / std::sqrt(static_cast<float>(head_dim));
     const dim3 grid(zk::kAttnSplit, static_cast<unsigned>(heads)), block(zk::kAttnThreads);
-    const cudaError_t e =
-        fused ? launch_pdl(s, zk::attention_decode_kernel<true>, grid, block, smem, st, d_q, static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
-                           d_pos, d_out, static_cast<uint32_t>(heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(head_dim), scale,
-                           static_cast<uint32_t>(window), static_cast<uint32_t>(max_positions), s.d_error, d_k, d_v, d_cos, d_sin, static_cast<uint32_t>(pairs),
-                           d_k_cache, d_v_cache)
-              : launch_pdl(s, zk::attention_decode_kernel<false>, grid, block, smem, st, d_q, static_cast<const float*>(d_k_cache),
-                           static_cast<const float*>(d_v_cache), d_pos, d_out, static_cast<uint32_t>(heads), static_cast<uint32_t>(kv_heads),
-                           static_cast<uint32_t>(head_dim), scale, static_cast<uint32_t>(window), static_cast<uint32_t>(max_positions), s.d_error,
-                           static_cast<const float*>(nullptr), static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
-                           static_cast<const float*>(nullptr), 0u, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+    const bool wide = head_dim > 128;
+    auto launch = [&](auto kernel) {
+        return fused ? launch_pdl(s, kernel, grid, block, smem, st, d_q, static_cast<const float*>(nullptr), static_cast<const float*>(nullptr), d_pos, d_out,
+                                  static_cast<uint32_t>(heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(head_dim), scale, static_cast<uint32_t>(window),
+                                  static_cast<uint32_t>(max_positions), s.d_error, d_k, d_v, d_cos, d_sin, static_cast<uint32_t>(pairs), d_k_cache, d_v_cache)
+                     : launch_pdl(s, kernel, grid, block, smem, st, d_q, static_cast<const float*>(d_k_cache), static_cast<const float*>(d_v_cache), d_pos, d_out,
+                                  static_cast<uint32_t>(heads), static_cast<uint32_t>(kv_heads), static_cast<uint32_t>(head_dim), scale, static_cast<uint32_t>(window),
+                                  static_cast<uint32_t>(max_positions), s.d_error, static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
+                                  static_cast<const float*>(nullptr), static_cast<const float*>(nullptr), 0u, static_cast<float*>(nullptr), static_cast<float*>(nullptr));
+    };
+    const cudaError_t e = fused ? (wide ? launch(zk::attention_decode_kernel<true, true>) : launch(zk::attention_decode_kernel<true, false>))
+                                : (wide ? launch(zk::attention_decode_kernel<false, true>) : launch(zk::attention_decode_kernel<false, false>));
     ++s.stats.dispatches;
     if (e != cudaSuccess) return set_error(s, "attention: launch failed");
     return true;
