@@ -230,3 +230,34 @@ def test_bad_arguments_are_errors(be):
     with pytest.raises(BackendError):
         be.gemm("Q8_0", w, np.zeros((1, 48), np.float32), 1, 4, 48)  # 48 is not a multiple of 32
     assert be.stats()["fallbacks"] >= 1
+
+
+@pytest.mark.parametrize("rows,cols", [(4096, 14336), (1027, 4128), (300, 8192), (77, 12288), (5, 4128), (33, 14336)])
+def test_rows_of_several_segments_int8(be, zo, rows, cols):
+    # more than 4096 columns, one int8 token: a warp walks two rows segment by segment with the segment's activations in
+    # registers (the down projection's shape class); plain, accumulating, and two tensors in one launch
+    import torch
+    be.set_q8_act_mode(ACT_INT8)
+    w = seeded_weights(Q8_0, rows, cols, 60 + rows)
+    w2 = seeded_weights(Q8_0, rows // 2 + 3, cols, 61 + rows)
+    x = seeded_acts(1, cols, 70 + cols)[0]
+    ref = zo.gemv(Q8_0, w, x, rows, cols, int8_acts=True)
+    ref2 = zo.gemv(Q8_0, w2, x, w2.shape[0], cols, int8_acts=True)
+    assert_parity(be.gemv("Q8_0", w, x, rows, cols), ref, what=f"host gemv {rows}x{cols}")
+    h, h2 = be.dev_upload("Q8_0", w, rows, cols), be.dev_upload("Q8_0", w2, w2.shape[0], cols)
+    d_x = torch.from_numpy(x).cuda()
+    y, y2 = torch.zeros(rows, device="cuda"), torch.zeros(w2.shape[0], device="cuda")
+    be.dev_gemv([h, h2], [y.data_ptr(), y2.data_ptr()], d_x.data_ptr(), 1, ACT_INT8)
+    be.dev_check()
+    assert_parity(y.cpu().numpy(), ref, what="two tensors in one launch, first")
+    assert_parity(y2.cpu().numpy(), ref2, what="two tensors in one launch, second")
+    base = torch.full((rows,), 0.5, device="cuda")
+    be.dev_gemv_fused([h], [base.data_ptr()], d_x.data_ptr(), 1, ACT_INT8, accumulate=True)
+    be.dev_check()
+    assert torch.equal(base, y + 0.5)
+    # eight tokens keep the activations in shared memory: a different summation order, the same oracle
+    x8 = seeded_acts(2, cols, 71 + cols)
+    got8 = be.gemm("Q8_0", w, x8, 2, rows, cols)
+    assert_parity(got8, np.stack([zo.gemv(Q8_0, w, x8[t], rows, cols, int8_acts=True) for t in range(2)]), what="two tokens")
+    be.dev_free(h); be.dev_free(h2)
+    be.release_weights(w)

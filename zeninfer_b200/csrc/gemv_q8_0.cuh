@@ -35,6 +35,7 @@
 //
 // Algorithmic traffic is the raw GGUF size: 34 bytes per block.
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "peer_gather.cuh"
@@ -79,6 +80,15 @@ constexpr uint32_t kGemvFlagWarm = 8u;        // pull the start of the next laun
 constexpr uint32_t kGemvFlagPairSwiglu = 64u;
 constexpr uint32_t kWarmCapBytes = 192 * 1024;   // per CTA
 
+// Tensor maps of one resident tensor whose rows span several K segments (built on upload, kept in device memory):
+// codes as [rows][K / 256][256] bytes with boxes of n rows x 16 x 256 (one segment of a row group; a tile's innermost
+// extent is limited to 256 elements, hence the split of K), scales as [rows][nbp] halves with boxes of n x 128;
+// n = 8, 4, 2, 1: a partial group (the end of a CTA's row slice) is fetched with the smaller boxes.
+struct alignas(64) GemvTileMaps {
+    CUtensorMap codes[4];
+    CUtensorMap scales[4];
+};
+
 struct GemvTask {
     const uint8_t* codes;    // [rows][K] int8
     const __half* scales;    // [rows][nbp]
@@ -109,6 +119,9 @@ struct GemvParams {
     uint32_t warm_rows, warm_K, warm_nbp;
     const uint8_t* warm_codes;
     const __half* warm_scales;
+    // Rows of several K segments: per task, the tensor maps in device memory (GemvTileMaps) through which one copy per
+    // plane fetches a segment of a row group; null where a tensor has none (its rows then go one copy each).
+    const GemvTileMaps* tile_maps[kMaxTasks];
 #ifdef ZK_TRACE
     unsigned long long* trace;  // [grid][16] phase stamps (profiling builds only)
 #endif
@@ -299,6 +312,27 @@ __global__ void __launch_bounds__(kGemvThreads, (kBatch * kDigits == 1 ? ZK_GEMV
 #ifdef ZK_TRACE
                             if (trace_base && unit == 0) trace_base[blockIdx.x * 16 + 11] = zk_globaltimer();
 #endif
+                        }
+                    } else if (p.tile_maps[g.task] != nullptr) {
+                        // tiled copies, one per plane for a whole row group (boxes of 4, 2 and 1 rows for a partial one),
+                        // instead of one copy per row and plane: sixteen small copies a stage held this path at 0.67 of the
+                        // HBM rate where the contiguous one reaches 0.86.  Columns past the end of the row arrive as zeros
+                        // and count as bytes like the rest of the box.
+                        if (lane == 0) {
+                            const GemvTileMaps* maps = p.tile_maps[g.task];
+                            mbar_arrive_expect_tx(&full[stage], g.nrows * (kGemvSegBlocks * 32 + kGemvSegBlocks * 2));
+                            uint32_t done_rows = 0;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const uint32_t box = 8u >> k;
+                                if (g.nrows - done_rows >= box) {
+                                    tma_load_3d(st + done_rows * (kGemvSegBlocks * 32), &maps->codes[k], 0, static_cast<int>(s * (kGemvSegBlocks * 32 / 256)),
+                                                static_cast<int>(g.row0 + done_rows), &full[stage]);
+                                    tma_load_2d(st + kQ8StageCodeBytes + done_rows * (kGemvSegBlocks * 2), &maps->scales[k], static_cast<int>(s * kGemvSegBlocks),
+                                                static_cast<int>(g.row0 + done_rows), &full[stage]);
+                                    done_rows += box;
+                                }
+                            }
                         }
                     } else {
                         const uint32_t nblk = min(static_cast<uint32_t>(kGemvSegBlocks), nb - s * kGemvSegBlocks);

@@ -54,6 +54,7 @@ struct zen_cuda_weights {
     size_t rows{}, cols{};
     uint32_t nb{}, nbp{};     // blocks per row, padded to 8
     void* plane[4]{};         // format-specific planes (see repack.cuh)
+    void* d_tile_maps{};      // Q8_0 rows of several K segments: zk::GemvTileMaps in device memory (see make_tile_maps), else null
     int kernel_format{};      // what the decode kernel is instantiated for: the format, or zk::kFormatQ6KCodes for Q6_K with unpacked codes
     size_t device_bytes{};
     size_t raw_bytes{};
@@ -239,6 +240,7 @@ uint64_t default_vram_budget(const State& s) { return s.adapter.dedicated_vram /
 void free_weights(State& s, zen_cuda_weights* w) {
     if (!w) return;
     for (void* p : w->plane) if (p) cudaFree(p);
+    if (w->d_tile_maps) cudaFree(w->d_tile_maps);
     s.stats.weight_bytes -= std::min<uint64_t>(s.stats.weight_bytes, w->device_bytes);
     delete w;
 }
@@ -296,6 +298,8 @@ void plane_sizes(int fmt, size_t nrows, size_t cols, size_t plane_bytes[4], bool
         plane_bytes[3] = nrows * static_cast<size_t>(nbp) * 2 + 64;        // f16 super-block scales
     }
 }
+
+bool make_tile_maps(State& s, zen_cuda_weights* w);   // defined with the other tensor-map code below
 
 // Uploads rows [first_row, first_row+nrows) and re-lays them out into planes on the device.
 zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t rows_total, size_t cols, size_t first_row, size_t nrows) {
@@ -364,6 +368,11 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
     }
     if (d_raw) cudaFree(d_raw);
     if (!ok) {
+        for (void* p : w->plane) if (p) cudaFree(p);
+        delete w;
+        return nullptr;
+    }
+    if (fmt == ZEN_CUDA_Q8_0 && !make_tile_maps(s, w)) {
         for (void* p : w->plane) if (p) cudaFree(p);
         delete w;
         return nullptr;
@@ -584,6 +593,7 @@ bool enqueue_gemv(State& s, const zen_cuda_weights* const* w, float* const* d_y,
             return set_error(s, "gemv: tasks must share format and columns");
         p.task[i].codes = static_cast<const uint8_t*>(w[i]->plane[0]);
         p.task[i].scales = static_cast<const __half*>(w[i]->plane[1]);
+        p.tile_maps[i] = static_cast<const zk::GemvTileMaps*>(w[i]->d_tile_maps);
         p.task[i].y = has_y ? d_y[i] : nullptr;
         p.task[i].rows = static_cast<uint32_t>(w[i]->rows);
         p.task[i].first_row = total_rows;
@@ -783,6 +793,41 @@ bool make_map_2d(State& s, CUtensorMap* map, CUtensorMapDataType type, size_t el
 
 // Workspace of one prefill product: codes [tokens][cols] int8 (padded to 256 bytes), block-major scales [cols/32][t_ld]
 // fp32 and, with two activation digits, the fine digits [tokens][cols] behind them on the next 256-byte boundary.
+// Q8_0 tensors whose rows span several K segments (more than 4096 columns) and whose columns are a multiple of 256: the
+// two tiled views through which the decode kernel fetches a segment of a whole row group with one copy per plane.
+// Other tensors keep none (their rows are contiguous per group, or go row by row).
+bool make_tile_maps(State& s, zen_cuda_weights* w) {
+    if (w->cols <= static_cast<size_t>(zk::kGemvSegBlocks) * 32 || w->cols % 256 || !s.encode_tiled) return true;
+    zk::GemvTileMaps maps;
+    std::memset(&maps, 0, sizeof maps);
+    const auto encode = reinterpret_cast<EncodeTiledFn>(s.encode_tiled);
+    for (int k = 0; k < 4; ++k) {   // boxes of 8, 4, 2 and 1 rows
+        const cuuint32_t box_rows = static_cast<cuuint32_t>(zk::kTeamWarps) >> k;
+        {
+            const cuuint64_t dims[3] = {256, w->cols / 256, w->rows};
+            const cuuint64_t strides[2] = {256, w->cols};
+            const cuuint32_t box[3] = {256, static_cast<cuuint32_t>(zk::kGemvSegBlocks * 32 / 256), box_rows};
+            const cuuint32_t estr[3] = {1, 1, 1};
+            const CUresult r = encode(&maps.codes[k], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w->plane[0], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return set_error(s, "upload: cuTensorMapEncodeTiled (codes) failed (" + std::to_string(static_cast<int>(r)) + ")");
+        }
+        {
+            const cuuint64_t dims[2] = {w->nbp, w->rows};
+            const cuuint64_t strides[1] = {static_cast<cuuint64_t>(w->nbp) * 2};
+            const cuuint32_t box[2] = {static_cast<cuuint32_t>(zk::kGemvSegBlocks), box_rows};
+            const cuuint32_t estr[2] = {1, 1};
+            const CUresult r = encode(&maps.scales[k], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w->plane[1], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r != CUDA_SUCCESS) return set_error(s, "upload: cuTensorMapEncodeTiled (scales) failed (" + std::to_string(static_cast<int>(r)) + ")");
+        }
+    }
+    ZC_CUDA(s, cudaMalloc(&w->d_tile_maps, sizeof maps));
+    ZC_CUDA(s, cudaMemcpy(w->d_tile_maps, &maps, sizeof maps, cudaMemcpyHostToDevice));
+    w->device_bytes += sizeof maps;
+    return true;
+}
+
 size_t gemm_ws_bytes(size_t tokens, size_t cols, int digits = 1) {
     const size_t t_ld = (tokens + 3) & ~size_t(3);
     const size_t codes = (tokens * cols + 255) & ~size_t(255);

@@ -85,6 +85,11 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const void* tensor_map, i
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(smem_u32(dst)), "l"(tensor_map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
+// 3-D tile; x as above.
+__device__ __forceinline__ void tma_load_3d(void* dst, const void* tensor_map, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_u32(dst)), "l"(tensor_map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_descriptor(const void* tensor_map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
 }
