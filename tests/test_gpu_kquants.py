@@ -197,3 +197,22 @@ def test_q6_k_both_device_layouts_give_the_same_bits(be, zo, golden, rows, cols,
     assert sizes[0] >= sizes[1] and (rows * cols < 65536 or sizes[0] > 1.25 * sizes[1])     # 1.07 against 0.82 bytes per weight, plus 64 bytes of slack per plane
     ref = np.stack([zo.gemv(Q6_K, w, x[t], rows, cols) for t in range(tokens)])
     assert_parity(outs[0], ref, what=f"Q6_K unpacked codes {tokens}x{rows}x{cols}")
+
+
+@pytest.mark.parametrize("fmt", [Q4_0, Q6_K])
+@pytest.mark.parametrize("rows,cols,tokens", [(1027, 8192, 1), (77, 12288, 1), (301, 14336, 3), (4096, 14336, 1), (13, 4608, 1)])
+def test_rows_of_several_segments(be, zo, fmt, rows, cols, tokens):
+    # more than 4096 columns: a row group's segment arrives by one tiled copy per plane (partial groups by boxes of 4, 2
+    # and 1 rows; 4608 columns have a pitch that is not a multiple of 256 in some planes and take the per-row copies)
+    w = seeded_weights(fmt, rows, cols, 700 + rows)
+    x = seeded_acts(tokens, cols, 710 + cols)
+    for codes in ((True, False) if fmt == Q6_K else (True,)):
+        before = be.set_q6k_codes(codes)
+        try:
+            got = be.gemm(NAMES[fmt], w, x, tokens, rows, cols)
+            be.release_weights(w)
+        finally:
+            be.set_q6k_codes(before)
+        ref = np.stack([zo.gemv(fmt, w, x[t], rows, cols) for t in range(tokens)])
+        rel = assert_parity(got, ref, what=f"{NAMES[fmt]} {tokens}x{rows}x{cols} codes={codes}")
+        assert rel < 1e-4

@@ -34,7 +34,7 @@ def test_against_the_reference_vectors(be, fmt, name, tag):
 
 @pytest.mark.parametrize("fmt,name,tag", FORMATS)
 @pytest.mark.parametrize("rows,cols,tokens", [(1, 256, 1), (5, 512, 1), (67, 1280, 3), (130, 2048, 8), (1024, 4096, 1), (64, 14336, 2), (300, 768, 11),
-                                              (2050, 4096, 8), (33, 4096, 40), (9, 4352, 5), (8, 8192, 7)])
+                                              (2050, 4096, 8), (33, 4096, 40), (9, 4352, 5), (8, 8192, 7), (1027, 8192, 1), (4096, 14336, 1), (77, 12288, 2)])
 def test_host_pointer_product_vs_oracle(be, zo, fmt, name, tag, rows, cols, tokens):
     w = blocks.random_k_blocks(fmt, rows, cols, 500 + rows)
     x = seeded_acts(tokens, cols, 510 + cols)

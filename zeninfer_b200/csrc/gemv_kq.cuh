@@ -22,6 +22,7 @@
 // planes of the last two are 4 bytes per super-block larger, because the 12 packed bytes of 6-bit scales and minimums
 // are kept unpacked as 16, see repack.cuh).
 #pragma once
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "gemv_q8_0.cuh"
@@ -91,6 +92,14 @@ template <int kFormat> __host__ __device__ constexpr uint32_t kq_plane_offset(in
 }
 template <int kFormat> __host__ __device__ constexpr uint32_t kq_stage_bytes() { return kq_row_stage_bytes<kFormat>() * kTeamWarps; }
 
+// Tensor maps of one resident tensor whose rows span several K segments (built on upload, kept in device memory): per
+// plane, boxes of 8, 4, 2 and 1 rows x one segment.  A plane whose segment is at most 256 bytes is a 2-D byte view
+// [rows][pitch]; a wider one is the 3-D view [rows][pitch / 256][256], because a tile's innermost extent is limited to
+// 256 elements.  One copy per plane then fetches a row group's segment where the per-row path issues 16 to 32 small ones.
+struct alignas(64) KqTileMaps {
+    CUtensorMap map[kKqMaxPlanes][4];
+};
+
 struct KqTask {
     const uint8_t* plane[kKqMaxPlanes];
     float* y;               // [batch][rows]
@@ -107,6 +116,7 @@ struct KqParams {
     uint32_t pitch[kKqMaxPlanes];  // global row pitch of each plane, bytes
     int* error_word;
     PeerGather gather;      // world == 0: outputs go to task[].y only
+    const KqTileMaps* tile_maps[kMaxTasks];   // null: the tensor's rows go one copy per row and plane when K spans several segments
 };
 
 template <int kFormat>
@@ -272,13 +282,42 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kq_kernel(const __grid_c
                     uint32_t row_bytes = 0;
 #pragma unroll
                     for (int pl = 0; pl < F::kPlanes; ++pl) row_bytes += (elems / 256 * F::bytes_per_256(pl) + (elems % 256) * F::bytes_per_256(pl) / 256 + 15) & ~15u;
-                    if (lane == 0) mbar_arrive_expect_tx(&full[stage], g.nrows * row_bytes);
+                    const bool tiled = !contiguous && p.tile_maps[g.task] != nullptr;
+                    // A tiled copy always delivers whole segments (columns past the row arrive as zeros).  A tile must land on a
+                    // 128-byte boundary, so planes whose segment is narrower than that always arrive as ONE box of eight rows
+                    // (the rows past a partial group are a few bytes that nobody reads; past the tensor they are zeros).
+                    uint32_t tiled_bytes = 0;
+#pragma unroll
+                    for (int pl = 0; pl < F::kPlanes; ++pl) tiled_bytes += (F::seg_bytes(pl) < 128 ? static_cast<uint32_t>(kTeamWarps) : g.nrows) * F::seg_bytes(pl);
+                    if (lane == 0) mbar_arrive_expect_tx(&full[stage], tiled ? tiled_bytes : g.nrows * row_bytes);
                     __syncwarp();
                     if (contiguous) {
                         // rows of one full segment follow each other in every plane: one copy per plane for the whole group
                         if (lane < F::kPlanes) {
                             bulk_g2s(ring + stage * kStageBytes + kq_plane_offset<kFormat>(lane),
                                      t.plane[lane] + static_cast<size_t>(g.row0) * p.pitch[lane], g.nrows * F::seg_bytes(lane), &full[stage]);
+                        }
+                    } else if (tiled) {
+                        // tiled copies: per plane one for a whole row group, or boxes of 4, 2 and 1 rows for a partial one
+                        if (lane == 0) {
+                            const KqTileMaps* maps = p.tile_maps[g.task];
+#pragma unroll
+                            for (int pl = 0; pl < F::kPlanes; ++pl) {
+                                uint32_t done_rows = 0;
+                                const uint32_t want = F::seg_bytes(pl) < 128 ? static_cast<uint32_t>(kTeamWarps) : g.nrows;
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const uint32_t box = 8u >> k;
+                                    if (want - done_rows >= box) {
+                                        uint8_t* dst = ring + stage * kStageBytes + kq_plane_offset<kFormat>(pl) + done_rows * F::seg_bytes(pl);
+                                        if (F::seg_bytes(pl) <= 256)
+                                            tma_load_2d(dst, &maps->map[pl][k], static_cast<int>(s * F::seg_bytes(pl)), static_cast<int>(g.row0 + done_rows), &full[stage]);
+                                        else
+                                            tma_load_3d(dst, &maps->map[pl][k], 0, static_cast<int>(s * (F::seg_bytes(pl) / 256)), static_cast<int>(g.row0 + done_rows), &full[stage]);
+                                        done_rows += box;
+                                    }
+                                }
+                            }
                         }
                     } else if (my_row < static_cast<int>(g.nrows) && my_row < kTeamWarps) {
                         const uint32_t per256 = F::bytes_per_256(my_plane);

@@ -300,6 +300,7 @@ void plane_sizes(int fmt, size_t nrows, size_t cols, size_t plane_bytes[4], bool
 }
 
 bool make_tile_maps(State& s, zen_cuda_weights* w);   // defined with the other tensor-map code below
+bool make_kq_tile_maps(State& s, zen_cuda_weights* w);
 
 // Uploads rows [first_row, first_row+nrows) and re-lays them out into planes on the device.
 zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t rows_total, size_t cols, size_t first_row, size_t nrows) {
@@ -372,7 +373,7 @@ zen_cuda_weights* upload_locked(State& s, int fmt, const uint8_t* host, size_t r
         delete w;
         return nullptr;
     }
-    if (fmt == ZEN_CUDA_Q8_0 && !make_tile_maps(s, w)) {
+    if (!(fmt == ZEN_CUDA_Q8_0 ? make_tile_maps(s, w) : make_kq_tile_maps(s, w))) {
         for (void* p : w->plane) if (p) cudaFree(p);
         delete w;
         return nullptr;
@@ -535,6 +536,7 @@ bool enqueue_gemv_kq(State& s, const zen_cuda_weights* const* w, float* const* d
     const int planes = fmt == zk::kFormatQ6KCodes ? 3 : plane_count(fmt);
     for (size_t i = 0; i < count; ++i) {
         for (int k = 0; k < planes; ++k) p.task[i].plane[k] = static_cast<const uint8_t*>(w[i]->plane[k]);
+        p.tile_maps[i] = static_cast<const zk::KqTileMaps*>(w[i]->d_tile_maps);
         p.task[i].y = d_y ? d_y[i] : nullptr;
         p.task[i].rows = static_cast<uint32_t>(w[i]->rows);
         p.task[i].first_row = total_rows;
@@ -820,6 +822,53 @@ bool make_tile_maps(State& s, zen_cuda_weights* w) {
             const CUresult r = encode(&maps.scales[k], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w->plane[1], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (r != CUDA_SUCCESS) return set_error(s, "upload: cuTensorMapEncodeTiled (scales) failed (" + std::to_string(static_cast<int>(r)) + ")");
+        }
+    }
+    ZC_CUDA(s, cudaMalloc(&w->d_tile_maps, sizeof maps));
+    ZC_CUDA(s, cudaMemcpy(w->d_tile_maps, &maps, sizeof maps, cudaMemcpyHostToDevice));
+    w->device_bytes += sizeof maps;
+    return true;
+}
+
+// The same for the planes of the Q4_0 / Q6_K / Q4_K / Q5_K kernel (zk::KqTileMaps): per plane the row pitch and the bytes
+// of one 4096-column segment; planes wider than 256 bytes a segment need a pitch that is a multiple of 256.
+bool make_kq_tile_maps(State& s, zen_cuda_weights* w) {
+    if (w->cols <= static_cast<size_t>(zk::kKqSegElems) || !s.encode_tiled) return true;
+    const int kf = w->kernel_format;
+    size_t pitch[4] = {0, 0, 0, 0}, seg[4] = {0, 0, 0, 0};
+    int planes = 0;
+    const size_t K = w->cols, E = zk::kKqSegElems;
+    if (kf == ZEN_CUDA_Q4_0) { planes = 2; pitch[0] = K / 2; seg[0] = E / 2; pitch[1] = size_t(w->nbp) * 2; seg[1] = E / 32 * 2; }
+    else if (kf == ZEN_CUDA_Q6_K) { planes = 4; pitch[0] = K / 2; seg[0] = E / 2; pitch[1] = K / 4; seg[1] = E / 4; pitch[2] = K / 16; seg[2] = E / 16; pitch[3] = size_t(w->nbp) * 2; seg[3] = E / 256 * 2; }
+    else if (kf == zk::kFormatQ6KCodes) { planes = 3; pitch[0] = K; seg[0] = E; pitch[1] = K / 16; seg[1] = E / 16; pitch[2] = size_t(w->nbp) * 2; seg[2] = E / 256 * 2; }
+    else if (kf == ZEN_CUDA_Q4_K) { planes = 3; pitch[0] = K / 2; seg[0] = E / 2; pitch[1] = K / 16; seg[1] = E / 16; pitch[2] = size_t(w->nbp) * 4; seg[2] = E / 256 * 4; }
+    else if (kf == ZEN_CUDA_Q5_K) { planes = 4; pitch[0] = K / 2; seg[0] = E / 2; pitch[1] = K / 8; seg[1] = E / 8; pitch[2] = K / 16; seg[2] = E / 16; pitch[3] = size_t(w->nbp) * 4; seg[3] = E / 256 * 4; }
+    else return true;
+    for (int pl = 0; pl < planes; ++pl)
+        if (pitch[pl] % 16 || (seg[pl] > 256 && pitch[pl] % 256)) return true;   // no maps: the rows go one copy each
+    zk::KqTileMaps maps;
+    std::memset(&maps, 0, sizeof maps);
+    const auto encode = reinterpret_cast<EncodeTiledFn>(s.encode_tiled);
+    for (int pl = 0; pl < planes; ++pl) {
+        for (int k = 0; k < 4; ++k) {
+            const cuuint32_t box_rows = 8u >> k;
+            CUresult r;
+            if (seg[pl] <= 256) {
+                const cuuint64_t dims[2] = {pitch[pl], w->rows};
+                const cuuint64_t strides[1] = {pitch[pl]};
+                const cuuint32_t box[2] = {static_cast<cuuint32_t>(seg[pl]), box_rows};
+                const cuuint32_t estr[2] = {1, 1};
+                r = encode(&maps.map[pl][k], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w->plane[pl], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            } else {
+                const cuuint64_t dims[3] = {256, pitch[pl] / 256, w->rows};
+                const cuuint64_t strides[2] = {256, pitch[pl]};
+                const cuuint32_t box[3] = {256, static_cast<cuuint32_t>(seg[pl] / 256), box_rows};
+                const cuuint32_t estr[3] = {1, 1, 1};
+                r = encode(&maps.map[pl][k], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w->plane[pl], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            }
+            if (r != CUDA_SUCCESS) return set_error(s, "upload: cuTensorMapEncodeTiled (plane " + std::to_string(pl) + ") failed (" + std::to_string(static_cast<int>(r)) + ")");
         }
     }
     ZC_CUDA(s, cudaMalloc(&w->d_tile_maps, sizeof maps));
