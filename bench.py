@@ -1127,13 +1127,18 @@ def run_gemv_workload(args) -> dict | None:
 
         ms_s = time_passes(single_pass, short, 1)
         assert bool((ys == torch.from_numpy(y_dev).to(dev)[None, :]).all().item()), "single launches differ from batched launches"
-        ys.zero_()
-        lst = be.gemv_list_create([dict(handles=[h], d_y=[y_ptrs[i]], d_x=d_x.data_ptr()) for i, h in enumerate(handles)], ACT_INT8)
-        ms_l = time_passes(lambda: be.dev_gemv_list(lst, stream.cuda_stream), short, 1)
-        assert bool((ys == torch.from_numpy(y_dev).to(dev)[None, :]).all().item()), "the list launch differs from batched launches"
-        be.gemv_list_destroy(lst)
-        for name, ms_v, lp, api in (("single_launch", ms_s, COPIES, "zen_cuda_dev_gemv_fused, one tensor per launch, next tensor hinted to L2"),
-                                    ("list", ms_l, 1, "zen_cuda_dev_gemv_list, all 32 products as items of one persistent launch")):
+        timed = [("single_launch", ms_s, COPIES, "zen_cuda_dev_gemv_fused, one tensor per launch, next tensor hinted to L2")]
+        # The persistent list launch keeps state in device memory between its CTAs; a profiler that serialises or replays
+        # kernels does not get along with it (an ncu launch list of this command stopped there), so it is left out under one.
+        under_profiler = any(k in os.environ for k in ("CUDA_INJECTION64_PATH", "NV_COMPUTE_PROFILER_PERFWORKS_DIR", "NV_NSIGHT_INJECTION_PORT_BASE"))
+        if not args.no_list and not under_profiler:
+            ys.zero_()
+            lst = be.gemv_list_create([dict(handles=[h], d_y=[y_ptrs[i]], d_x=d_x.data_ptr()) for i, h in enumerate(handles)], ACT_INT8)
+            ms_l = time_passes(lambda: be.dev_gemv_list(lst, stream.cuda_stream), short, 1)
+            assert bool((ys == torch.from_numpy(y_dev).to(dev)[None, :]).all().item()), "the list launch differs from batched launches"
+            be.gemv_list_destroy(lst)
+            timed.append(("list", ms_l, 1, "zen_cuda_dev_gemv_list, all 32 products as items of one persistent launch"))
+        for name, ms_v, lp, api in timed:
             us = ms_v * 1e3 / (short * passes * COPIES)
             variants[name] = {"gbs": ALGO_BYTES_PER_LAUNCH / us / 1e3, "us_per_product": us, "frac": ALGO_BYTES_PER_LAUNCH / us / 1e3 / peak,
                               "launches_per_pass": lp, "api": api}
@@ -1230,6 +1235,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0, help="workload decode: number of layers (default: the configuration's 32)")
     ap.add_argument("--formats", default="Q8_0,Q4_0,Q6_K,Q4_K,Q5_K", help="workload layer_sweep: formats to run")
     ap.add_argument("--act", default="int8", choices=["int8", "fp32"], help="workload q8_0_gemm: activation mode of the timed product (the other one is timed briefly beside it)")
+    ap.add_argument("--no-list", action="store_true", help="default workload: skip the persistent list launch among the config 0 submission variants")
     ap.add_argument("--no-detail", action="store_true", help="default workload: skip the short runs of the other workloads that fill `detail`")
     ap.add_argument("--device-pack", action="store_true", help="workload lm_head: draw and pack the Q6_K matrix on the GPU (torch) instead of numpy")
     ap.add_argument("--cut", default="rows+cols", choices=["rows", "rows+cols"],
