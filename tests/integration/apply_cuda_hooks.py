@@ -3,8 +3,8 @@
 
     python tests/integration/apply_cuda_hooks.py <reference>/src/quant.cpp <out>/quant_cuda.cpp
 
-The copy is made at build time and never committed: the reference's source stays where it is.  The hooks are the ones
-INTEGRATION.md lists, placed beside the reference's own `#ifdef ZEN_HAS_HIP` blocks (src/quant.cpp:1007-1012 gemv,
+The copy is made at build time and never committed: the reference's source stays where it is.  The hooks are the ones a
+maintainer would add, placed beside the reference's own `#ifdef ZEN_HAS_HIP` blocks (src/quant.cpp:1007-1012 gemv,
 :1457-1468 gemv_batch, :1528-1543 gemm_batch, :1656-1659 gemm, :1553-1580 ffn_gemv), and they count their attempts on the reference's own route
 counters (g_gemv_routes / g_gemm_routes, :48-75).  The product hooks `return` their result: this backend has no CPU route
 behind it, so a failed call is the caller's error, not a fall-through.  The ffn_gemv hook keeps the reference's own
