@@ -95,6 +95,11 @@ class ClockSampler:
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            # nvidia-smi needs a moment before its first line (seconds on a box with eight GPUs): wait for it here, before
+            # any warm-up, so that short timed regions still fall between samples
+            t0 = time.time()
+            while not self.rows and self.proc.poll() is None and time.time() - t0 < 10.0:
+                time.sleep(0.02)
         except Exception:
             self.proc = None
         return self
