@@ -460,8 +460,8 @@ __global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(const flo
     const uint32_t my_first = (window && my_last + 1 > window) ? my_last + 1 - window : 0u;
     uint64_t q01[R][per4], q23[R][per4], a01[R][per4], a23[R][per4];
     // The softmax state of a row lives in one lane: the score reduction below leaves the token's lane `part` with the
-    // full sum of head my_row, and that lane keeps the row's running maximum and denominator.
-    const uint32_t my_row = R == 4 ? ((part >> 2) << 1 | ((part >> 1) & 1)) : R == 2 ? (part >> 2) : 0u;
+    // full sum of one head (head ((part >> 2) << 1 | ((part >> 1) & 1)) for R == 4, part >> 2 for R == 2), and that lane
+    // keeps the row's running maximum and denominator.
     float m = -INFINITY;
     double l = 0.0;
 #pragma unroll
@@ -537,7 +537,7 @@ __global__ void __launch_bounds__(kPfThreads) attention_prefill_kernel(const flo
                 }
             }
             // Sum over the token's eight lanes, halving the rows a lane carries at each exchange: lane `part` ends with
-            // the full score of head my_row (R + 1 or 3 shuffles, where one reduction per row would take 3 R).
+            // the full score of its head (R + 1 or 3 shuffles, where one reduction per row would take 3 R).
             float sc[kPfStep];
 #pragma unroll
             for (int u = 0; u < kPfStep; ++u) {
