@@ -812,7 +812,7 @@ bool make_tile_maps(State& s, zen_cuda_weights* w) {
             const cuuint32_t estr[3] = {1, 1, 1};
             const CUresult r = encode(&maps.codes[k], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w->plane[0], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r != CUDA_SUCCESS) return set_error(s, "upload: cuTensorMapEncodeTiled (codes) failed (" + std::to_string(static_cast<int>(r)) + ")");
+            if (r != CUDA_SUCCESS) return true;   // no maps: the rows go one copy each, as before
         }
         {
             const cuuint64_t dims[2] = {w->nbp, w->rows};
@@ -821,7 +821,7 @@ bool make_tile_maps(State& s, zen_cuda_weights* w) {
             const cuuint32_t estr[2] = {1, 1};
             const CUresult r = encode(&maps.scales[k], CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, w->plane[1], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r != CUDA_SUCCESS) return set_error(s, "upload: cuTensorMapEncodeTiled (scales) failed (" + std::to_string(static_cast<int>(r)) + ")");
+            if (r != CUDA_SUCCESS) return true;
         }
     }
     ZC_CUDA(s, cudaMalloc(&w->d_tile_maps, sizeof maps));
@@ -868,7 +868,7 @@ bool make_kq_tile_maps(State& s, zen_cuda_weights* w) {
                 r = encode(&maps.map[pl][k], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w->plane[pl], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             }
-            if (r != CUDA_SUCCESS) return set_error(s, "upload: cuTensorMapEncodeTiled (plane " + std::to_string(pl) + ") failed (" + std::to_string(static_cast<int>(r)) + ")");
+            if (r != CUDA_SUCCESS) return true;   // no maps: the rows go one copy each
         }
     }
     ZC_CUDA(s, cudaMalloc(&w->d_tile_maps, sizeof maps));
