@@ -275,6 +275,16 @@ size_t zen_cuda_gemm_workspace_bytes_act(size_t tokens, size_t columns, int act_
 int zen_cuda_dev_gemm_q8_0_act(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x,
                                size_t tokens, int act_mode, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Q6_K product for two or more activation rows on the tensor cores (the batched lm_head of config 3, and the reference's
+ * batched Q6_K product gemm_q6k_kblk_avx2, kernels/avx2.cpp:1762-1770, GPU entry zen::d3d12::gemm_q6_k,
+ * include/zen/d3d12_backend.h:169): fp32-equivalent activations (two int8 digits), out [tokens][rows] fp32.  The tensor
+ * must be resident with its codes unpacked (the default layout, zen_cuda_set_q6k_codes).  `workspace` is device memory of
+ * at least zen_cuda_gemm_q6_k_workspace_bytes(tokens, columns), untouched until the stream has run the work.  The
+ * host-pointer call zen_cuda_gemm_q6_k takes this path by itself from two rows on. */
+size_t zen_cuda_gemm_q6_k_workspace_bytes(size_t tokens, size_t columns);
+int zen_cuda_dev_gemm_q6_k(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 /* No counterpart in the reference.  The same prefill product as zen_cuda_dev_gemm_q8_0 for ONE tensor, for callers
  * that may not allocate device memory at the time of the call: a plug-in living inside a host runtime that owns all of
  * HBM (weights, KV cache and arenas were sized at start-up and nothing is left to ask for), or a serving loop that can

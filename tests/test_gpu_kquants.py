@@ -216,3 +216,46 @@ def test_rows_of_several_segments(be, zo, fmt, rows, cols, tokens):
         ref = np.stack([zo.gemv(fmt, w, x[t], rows, cols) for t in range(tokens)])
         rel = assert_parity(got, ref, what=f"{NAMES[fmt]} {tokens}x{rows}x{cols} codes={codes}")
         assert rel < 1e-4
+
+
+@pytest.mark.parametrize("rows,cols,tokens", [(1, 256, 2), (130, 2048, 3), (300, 4096, 8), (1027, 1280, 16), (64, 14336, 5), (9, 4352, 37), (19000, 512, 8)])
+def test_q6_k_tensor_core_product_vs_oracle(be, zo, rows, cols, tokens):
+    # two or more activation rows: the tcgen05 product with one column per token and group parity (the batched lm_head of
+    # config 3, the reference's gemm_q6k_kblk_avx2); device pointers and a caller workspace, then the host-pointer call.
+    # 19000 rows are 149 row tiles: one more than the SMs, so the K range of a tile is shared between two CTAs.
+    import torch
+    w = seeded_weights(Q6_K, rows, cols, 900 + rows)
+    x = seeded_acts(tokens, cols, 910 + cols)
+    ref = np.stack([zo.gemv(Q6_K, w, x[t], rows, cols) for t in range(tokens)])
+    h = be.dev_upload("Q6_K", w, rows, cols)
+    d_x = torch.from_numpy(x).cuda()
+    y = torch.full((tokens, rows), float("nan"), device="cuda")
+    ws_bytes = be.gemm_q6_k_workspace_bytes(tokens, cols)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+    be.dev_gemm_q6_k(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
+    be.dev_check()
+    rel = assert_parity(y.cpu().numpy(), ref, what=f"Q6_K tensor product {tokens}x{rows}x{cols}")
+    assert rel < 1e-4
+    be.dev_free(h)
+    host = be.gemm("Q6_K", w, x, tokens, rows, cols)
+    assert_parity(host, ref, what="host-pointer call")
+    be.release_weights(w)
+
+
+def test_q6_k_tensor_core_product_needs_the_unpacked_codes(be):
+    import torch
+    rows, cols, tokens = 64, 512, 4
+    w = seeded_weights(Q6_K, rows, cols, 950)
+    before = be.set_q6k_codes(False)
+    try:
+        h = be.dev_upload("Q6_K", w, rows, cols)
+    finally:
+        be.set_q6k_codes(before)
+    d_x = torch.zeros((tokens, cols), device="cuda")
+    y = torch.zeros((tokens, rows), device="cuda")
+    ws_bytes = be.gemm_q6_k_workspace_bytes(tokens, cols)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+    from zeninfer_b200.backend import BackendError
+    with pytest.raises(BackendError, match="codes unpacked"):
+        be.dev_gemm_q6_k(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
+    be.dev_free(h)

@@ -57,7 +57,9 @@ struct GemmParams {
     CUtensorMap map_x;                 // act codes     [tokens_padded][K] int8, box 128 B x n_tile rows, SWIZZLE_128B
     CUtensorMap map_x2;                // fine digits   same shape (two-digit kernels only)
     CUtensorMap map_xs;                // act scales    [nb][t_ld] fp32 (block-major), box n_tile x 4
-    const __half* w_scales[kGemmMaxTensors];   // [rows][nbp]
+    const __half* w_scales[kGemmMaxTensors];   // [rows][nbp]: Q8_0 block scales; Q6_K: super-block scales
+    const int8_t* w_group_scales[kGemmMaxTensors];   // Q6_K only: [rows][group_pitch] int8, one per 16 weights
+    uint32_t group_pitch;
     float* out[kGemmMaxTensors];               // [tokens][rows]
     uint32_t rows[kGemmMaxTensors];
     uint32_t m_start[kGemmMaxTensors];         // first row tile of each tensor in the launch's row-tile numbering (0xffffffff: unused)
@@ -68,8 +70,10 @@ struct GemmParams {
     int* error_word;
 };
 
-__host__ __device__ inline uint32_t gemm_stage_bytes(uint32_t n_tile, uint32_t digits = 1) {
-    return kGemmM * kGemmKTile + digits * n_tile * kGemmKTile + kGemmBlocksPerTile * n_tile * 4;
+// A stage: weight tile | activation codes | (fine digits) | activation scales, the last rounded up so that the next
+// stage's swizzled tiles start on a 1024-byte boundary again.
+__host__ __device__ constexpr uint32_t gemm_stage_bytes(uint32_t n_tile, uint32_t digits = 1) {
+    return kGemmM * kGemmKTile + digits * n_tile * kGemmKTile + ((kGemmBlocksPerTile * n_tile * 4 + 1023u) & ~1023u);
 }
 __host__ __device__ inline size_t gemm_smem_bytes(uint32_t n_tile, uint32_t digits = 1) {
     return 1024 /* alignment slack */ + static_cast<size_t>(kGemmStages) * gemm_stage_bytes(n_tile, digits) + 256 /* barriers */;
@@ -188,17 +192,31 @@ __global__ void gemm_zero_split_tiles_kernel(const __grid_constant__ GemmParams 
 
 // Eighteen warps put five on one of the SM's four register files (16384 registers each), so 96 registers per thread is
 // the ceiling: 5 x 32 x 96 = 15360.
-template <int kNTile, int kDigits = 1>
+//
+// kQ6K: the weights are Q6_K with the codes unpacked (q - 32 as int8 [rows][K], gemv_kq.cuh), two activation digits.  A
+// 16-weight group has its own int8 scale (src/quant.cpp:500-517), but one instruction sums K = 32 = two groups.  The
+// groups are kept apart on the activation side: token t enters as TWO columns, 2 t with the codes of the odd groups
+// zeroed and 2 t + 1 with those of the even groups zeroed (quantize_acts_q6k_gemm_kernel).  Column 2 t of a block's sums
+// is then the even group's integer dot product and column 2 t + 1 the odd group's, and the packed pair of accumulators
+// (2 t, 2 t + 1) takes the pair of group scales (d * sc_even, d * sc_odd); a token's output is the sum of its pair.  A tile
+// of kNTile columns holds kNTile / 2 tokens; with kNTile = 32 this is the product for the two to sixteen activation rows of
+// batched decoding (the lm_head for eight sequences) as well as the reference's gemm_q6k_kblk_avx2 (kernels/avx2.cpp:1762-1770).
+template <int kNTile, int kDigits = 1, bool kQ6K = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __grid_constant__ GemmParams p) {
     static_assert(kDigits == 1 || kDigits == 2, "one or two activation digits");
-    constexpr int kNHalf = kNTile / kGemmSplit;     // token columns per epilogue warp
-    static_assert(kNHalf % 32 == 0, "an epilogue warp takes whole 32-column chunks");
+    static_assert(!kQ6K || kDigits == 2, "Q6_K takes fp32-equivalent activations");
+    constexpr int kSplit = kNTile >= 128 ? kGemmSplit : kNTile / 16;   // warps of a lane quadrant that share a tile's columns
+    constexpr int kEpiActive = 4 * kSplit;                              // narrow tiles leave the other epilogue warps idle
+    static_assert(kSplit >= 1 && kSplit <= kGemmSplit, "tile width");
+    constexpr int kNHalf = kNTile / kSplit;         // token columns per epilogue warp
+    static_assert(kNHalf % (kDigits == 2 ? 16 : 32) == 0, "an epilogue warp takes whole 32-column (two digits: 16-column) chunks");
     constexpr uint32_t kPairs = 2;                   // TMEM accumulator buffers come in pairs: one hand-off per two blocks
-    constexpr uint32_t kStageBytes = kGemmM * kGemmKTile + kDigits * kNTile * kGemmKTile + kGemmBlocksPerTile * kNTile * 4;
+    constexpr uint32_t kStageBytes = gemm_stage_bytes(kNTile, kDigits);
     constexpr uint32_t kScaleOff = kGemmM * kGemmKTile + kDigits * kNTile * kGemmKTile;   // the stage: weights | codes | (fine digits) | scales
+    constexpr uint32_t kLoadBytes = kScaleOff + kGemmBlocksPerTile * kNTile * 4;           // what the four copies of a stage deliver
     static_assert(kStageBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
-    constexpr uint32_t kTmemCols = 2 * kPairs * kNTile;  // 512: a power of two
-    static_assert(kTmemCols == 512, "four accumulator buffers of 128 columns");
+    constexpr uint32_t kTmemCols = 2 * kPairs * kNTile;  // four accumulator buffers of kNTile columns: a power of two
+    static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM allocations are powers of two from 32 to 512 columns");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGemmStages * kStageBytes);
@@ -214,11 +232,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
     if (threadIdx.x == 0) {
         for (int s = 0; s < kGemmStages; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1 + kGemmEpiWarps);
+            mbar_init(&empty[s], 1 + kEpiActive);
         }
         for (int b = 0; b < static_cast<int>(kPairs); ++b) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], kGemmEpiWarps);
+            mbar_init(&tmem_empty[b], kEpiActive);
         }
         *abort_word = 0;
         mbar_fence_init();
@@ -252,7 +270,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                     if (*abort_word) ok = false;
                     if (!ok) break;
                     uint8_t* st = smem + stage * kStageBytes;
-                    mbar_arrive_expect_tx(&full[stage], kStageBytes);
+                    mbar_arrive_expect_tx(&full[stage], kLoadBytes);
                     tma_load_2d(st, map_w, static_cast<int>(kt * kGemmKTile), static_cast<int>(mt * kGemmM), &full[stage]);
                     tma_load_2d(st + kGemmM * kGemmKTile, &p.map_x, static_cast<int>(kt * kGemmKTile), static_cast<int>(nt * kNTile), &full[stage]);
                     if (kDigits == 2)
@@ -304,7 +322,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                 }
             }
         }
-    } else {
+    } else if (warp - 2 < kEpiActive) {
         // ---------------- epilogue warps ----------------
         const int e = warp - 2;
         const uint32_t quad = static_cast<uint32_t>(warp) & 3;   // the TMEM lanes a warp may touch: 32 * (warp id % 4)
@@ -323,12 +341,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
 #pragma unroll
             for (int c = 0; c < kNHalf / 2; ++c) acc[c] = 0ull;
             // the four weight scales of row r per K tile (8-byte aligned: nbp is a multiple of 8), fetched one K tile ahead
-            const uint2* sw_row = reinterpret_cast<const uint2*>(p.w_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nbp);
+            // Q6_K: a K tile is eight groups, i.e. eight int8 group scales (8-byte aligned) and half a super-block
+            const uint2* sw_row = kQ6K ? reinterpret_cast<const uint2*>(p.w_group_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.group_pitch)
+                                       : reinterpret_cast<const uint2*>(p.w_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nbp);
+            const __half* d_row = p.w_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nbp;   // Q6_K: super-block scales
             uint2 sw_next = __ldg(sw_row + kt0);
             for (uint32_t kt = kt0; kt < kt1 && ok; ++kt, ++it) {
                 const uint32_t stage = it % kGemmStages;
                 const uint2 sw4 = sw_next;
                 if (kt + 1 < kt1) sw_next = __ldg(sw_row + kt + 1);
+                float dq = 0.0f;
+                if constexpr (kQ6K) dq = __half2float(__ldg(d_row + (kt >> 1))) * 0.00390625f;   // the digits' common unit is d_x / 256
                 if (*abort_word || !mbar_wait(&full[stage], (it / kGemmStages) & 1)) {
                     if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrFullWaitTimeout); }
                     ok = false;
@@ -348,7 +371,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                                 ok = false;
                             } else {
                                 tc_fence_after_sync();
-                                const uint64_t sw2 = pack2(swf[j] * 0.00390625f, swf[j] * 0.00390625f);   // the digits' common unit is d / 256
+                                uint64_t sw2;
+                                if constexpr (kQ6K) {   // the block's even and odd group: (d * scale), the reference's factor (kernels/avx2.cpp:380-422)
+                                    const uint32_t two = (j < 2 ? sw4.x : sw4.y) >> (16 * (j & 1));
+                                    sw2 = pack2(dq * static_cast<float>(static_cast<int8_t>(two)), dq * static_cast<float>(static_cast<int8_t>(two >> 8)));
+                                } else {
+                                    sw2 = pack2(swf[j] * 0.00390625f, swf[j] * 0.00390625f);   // the digits' common unit is d / 256
+                                }
                                 uint32_t v1[16], v2[16];
 #pragma unroll
                                 for (int c = 0; c < kNHalf; c += 16) {
@@ -412,6 +441,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                     const uint32_t t = nt * kNTile + half * kNHalf + c;
                     float lo, hi;
                     unpack2(acc[c / 2], lo, hi);
+                    if constexpr (kQ6K) {   // columns (2 t, 2 t + 1) are token t's even and odd groups
+                        const uint32_t tok = t >> 1;
+                        float* o = out_t + static_cast<size_t>(tok) * rows + r;
+                        if (tok < p.tokens) { if (whole) o[0] = lo + hi; else atomicAdd(o, lo + hi); }
+                        continue;
+                    }
                     float* o = out_t + static_cast<size_t>(t) * rows + r;
                     if (whole) {
                         if (t < p.tokens) o[0] = lo;
@@ -446,6 +481,26 @@ __global__ void __launch_bounds__(256) quantize_acts_gemm_kernel(const float* __
     q[wid * 32 + lane] = static_cast<int8_t>(c1);
     if (q2) q2[wid * 32 + lane] = static_cast<int8_t>(c2);   // the fine digit, same layout
     if (lane == 0) sc_t[static_cast<size_t>(b) * t_ld + t] = d;
+}
+
+// The same for the Q6_K product: token t becomes rows 2 t (codes of the odd 16-weight groups zeroed) and 2 t + 1 (codes
+// of the even groups zeroed) of q and q2, and both rows carry the block's scale.  One warp per (token, block).
+__global__ void __launch_bounds__(256) quantize_acts_q6k_gemm_kernel(const float* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ sc_t,
+                                                                     uint32_t tokens, uint32_t nb, uint32_t t_ld, int8_t* __restrict__ q2) {
+    const size_t wid = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= static_cast<size_t>(tokens) * nb) return;
+    const uint32_t t = static_cast<uint32_t>(wid / nb), b = static_cast<uint32_t>(wid % nb);
+    int c1, c2;
+    const float d = quantise_block_lane(x[wid * 32 + lane], c1, c2);
+    const size_t K = static_cast<size_t>(nb) * 32;
+    const size_t even = (2 * static_cast<size_t>(t)) * K + b * 32 + lane, odd = even + K;
+    const bool in_even = lane < 16;   // elements 0..15 of a block are group 2 b, elements 16..31 group 2 b + 1
+    q[even] = static_cast<int8_t>(in_even ? c1 : 0);
+    q[odd] = static_cast<int8_t>(in_even ? 0 : c1);
+    q2[even] = static_cast<int8_t>(in_even ? c2 : 0);
+    q2[odd] = static_cast<int8_t>(in_even ? 0 : c2);
+    if (lane < 2) sc_t[static_cast<size_t>(b) * t_ld + 2 * t + lane] = d;
 }
 
 }  // namespace zk

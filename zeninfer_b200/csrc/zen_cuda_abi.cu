@@ -885,21 +885,21 @@ size_t gemm_ws_bytes(size_t tokens, size_t cols, int digits = 1) {
 }
 
 // The shared-memory opt-in of the GEMM kernel; done once, at start-up (it loads the kernel's module, which may allocate).
-template <int kNTile, int kDigits = 1>
+template <int kNTile, int kDigits = 1, bool kQ6K = false>
 cudaError_t configure_gemm() {
     static bool configured = false;
     if (configured) return cudaSuccess;
-    const cudaError_t e = cudaFuncSetAttribute(&zk::gemm_q8_0_i8_kernel<kNTile, kDigits>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    const cudaError_t e = cudaFuncSetAttribute(&zk::gemm_q8_0_i8_kernel<kNTile, kDigits, kQ6K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                static_cast<int>(zk::gemm_smem_bytes(kNTile, kDigits)));
     if (e == cudaSuccess) configured = true;
     return e;
 }
 
-template <int kNTile, int kDigits = 1>
+template <int kNTile, int kDigits = 1, bool kQ6K = false>
 cudaError_t launch_gemm(const zk::GemmParams& p, unsigned grid, cudaStream_t st) {
-    const cudaError_t e = configure_gemm<kNTile, kDigits>();
+    const cudaError_t e = configure_gemm<kNTile, kDigits, kQ6K>();
     if (e != cudaSuccess) return e;
-    zk::gemm_q8_0_i8_kernel<kNTile, kDigits><<<grid, zk::kGemmThreads, zk::gemm_smem_bytes(kNTile, kDigits), st>>>(p);
+    zk::gemm_q8_0_i8_kernel<kNTile, kDigits, kQ6K><<<grid, zk::kGemmThreads, zk::gemm_smem_bytes(kNTile, kDigits), st>>>(p);
     return cudaGetLastError();
 }
 
@@ -968,6 +968,59 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
         if (e != cudaSuccess) return set_error(s, std::string("gemm launch: ") + cudaGetErrorString(e));
         ++s.stats.dispatches;
     }
+    return true;
+}
+
+// Q6_K (codes unpacked on upload) times `tokens` >= 2 activation rows on the tensor cores: every token enters as two
+// columns, one per parity of the 16-weight groups (gemm_q8_0_i8.cuh), in tiles of 32 columns = 16 tokens.  The workspace
+// is gemm_ws_bytes(2 * tokens, cols, 2).  Stream-ordered on `st`.
+constexpr uint32_t kQ6kGemmNTile = 32;
+size_t gemm_q6k_ws_bytes(size_t tokens, size_t cols) { return gemm_ws_bytes(2 * tokens, cols, 2); }
+
+bool enqueue_gemm_q6k(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, cudaStream_t st) {
+    if (!w || !d_out || !d_x || !ws || !tokens) return set_error(s, "gemm q6_k: bad arguments");
+    if (w->kernel_format != zk::kFormatQ6KCodes || w->cols % 256) return set_error(s, "gemm q6_k: the tensor is not resident with its codes unpacked");
+    const size_t cols = w->cols, columns = 2 * tokens;
+    const uint32_t nb = static_cast<uint32_t>(cols / 32);
+    const size_t t_ld = (columns + 3) & ~size_t(3);
+    int8_t* xq = reinterpret_cast<int8_t*>(ws);
+    float* xs_t = reinterpret_cast<float*>(ws + ((columns * cols + 255) & ~size_t(255)));
+    int8_t* xq2 = reinterpret_cast<int8_t*>(ws + ((gemm_ws_bytes(columns, cols, 1) + 255) & ~size_t(255)));
+    const size_t nblk = tokens * nb;
+    zk::quantize_acts_q6k_gemm_kernel<<<static_cast<unsigned>((nblk + 7) / 8), 256, 0, st>>>(d_x, xq, xs_t, static_cast<uint32_t>(tokens), nb,
+                                                                                          static_cast<uint32_t>(t_ld), xq2);
+    if (cudaGetLastError() != cudaSuccess) return set_error(s, "gemm q6_k: quantise launch failed");
+    ++s.stats.dispatches;
+    zk::GemmParams p{};
+    p.m_start[0] = 0; p.m_start[1] = p.m_start[2] = 0xffffffffu;
+    if (!make_map_2d(s, &p.map_w[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->plane[0], cols, w->rows, cols, zk::kGemmKTile, zk::kGemmM, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if (!make_map_2d(s, &p.map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, cols, columns, cols, zk::kGemmKTile, kQ6kGemmNTile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if (!make_map_2d(s, &p.map_x2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq2, cols, columns, cols, zk::kGemmKTile, kQ6kGemmNTile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if (!make_map_2d(s, &p.map_xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, xs_t, t_ld, nb, t_ld * sizeof(float), kQ6kGemmNTile, zk::kGemmBlocksPerTile,
+                     CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+    p.w_group_scales[0] = static_cast<const int8_t*>(w->plane[1]);
+    p.group_pitch = static_cast<uint32_t>(cols / 16);
+    p.w_scales[0] = static_cast<const __half*>(w->plane[2]);
+    p.out[0] = d_out;
+    p.rows[0] = static_cast<uint32_t>(w->rows);
+    p.tensors = 1;
+    p.tokens = static_cast<uint32_t>(tokens);
+    p.nb = nb;
+    p.nbp = w->nbp;
+    p.n_tile = kQ6kGemmNTile / 2;   // tokens per tile
+    p.m_tiles = (p.rows[0] + zk::kGemmM - 1) / zk::kGemmM;
+    p.n_tiles = (p.tokens + p.n_tile - 1) / p.n_tile;
+    p.error_word = s.d_error;
+    const unsigned tiles = p.m_tiles * p.n_tiles, ktiles = nb / zk::kGemmBlocksPerTile;
+    const unsigned grid = std::min<unsigned>(tiles, static_cast<unsigned>(s.sm_count));
+    p.stream_k = (s.gemm_stream_k && tiles % grid != 0 && static_cast<uint64_t>(tiles) * ktiles / grid >= ktiles) ? 1u : 0u;
+    if (p.stream_k) {
+        zk::gemm_zero_split_tiles_kernel<<<grid, 256, 0, st>>>(p, ktiles);
+        ++s.stats.dispatches;
+    }
+    const cudaError_t e = launch_gemm<kQ6kGemmNTile, 2, true>(p, grid, st);
+    if (e != cudaSuccess) return set_error(s, std::string("gemm q6_k launch: ") + cudaGetErrorString(e));
+    ++s.stats.dispatches;
     return true;
 }
 
@@ -1193,7 +1246,11 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     const size_t chunk = max_tokens_per_launch(s, w[0]->kernel_format, cols, act_mode);
     if (!chunk) return set_error(s, "columns too large: one activation row does not fit shared memory");
     // More than one decode launch worth of int8-activation Q8_0 tokens: the tensor-core GEMM.
-    const bool tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q8_0 && tokens > 8;   // either activation mode
+    // Q6_K with its codes unpacked: the tensor-core product from two activation rows on (a one-row product streams faster
+    // through the decode kernel).
+    bool q6k_tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q6_K && tokens >= 2;
+    for (size_t i = 0; i < count; ++i) q6k_tensor_path = q6k_tensor_path && w[i]->kernel_format == zk::kFormatQ6KCodes;   // the file's planes: decode kernel
+    const bool tensor_path = q6k_tensor_path || (s.use_gemm && fmt == ZEN_CUDA_Q8_0 && tokens > 8);   // Q8_0: either activation mode
     const bool fetch_by_kernel = direct && x_bytes <= kDirectInputBytes;
 
     // The three launches of a small call (fetch the activations, the product, copy the result out and publish it).
@@ -1281,7 +1338,11 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
         }
         s.stats.transfer_us += us_since(t0);
         t0 = clock_type::now();
-        if (tensor_path) {
+        if (tensor_path && fmt == ZEN_CUDA_Q6_K) {
+            if (!ensure_gemm_ws(s, gemm_q6k_ws_bytes(tokens, cols))) return false;
+            for (size_t i = 0; i < count; ++i)    // stream-ordered: the tensors share the workspace one after the other
+                if (!enqueue_gemm_q6k(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
+        } else if (tensor_path) {
             if (!ensure_gemm_ws(s, gemm_ws_bytes(tokens, cols, act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1))) return false;
             if (!enqueue_gemm_q8_0(s, w, d_out, count, s.d_x, tokens, s.d_gemm_ws, s.stream, act_mode)) return false;
         }
@@ -1771,6 +1832,19 @@ int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out
     if (workspace_bytes < gemm_ws_bytes(tokens, w[0]->cols)) return set_error(s, "dev_gemm: workspace too small") ? 1 : 0;
     return enqueue_gemm_q8_0(s, w, d_out, count, d_x, tokens, static_cast<uint8_t*>(workspace),
                              stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
+}
+
+size_t zen_cuda_gemm_q6_k_workspace_bytes(size_t tokens, size_t columns) { return gemm_q6k_ws_bytes(tokens, columns); }
+
+int zen_cuda_dev_gemm_q6_k(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!w || !d_out || !d_x || !tokens) return set_error(s, "dev_gemm_q6_k: bad arguments") ? 1 : 0;
+    if (w->format != ZEN_CUDA_Q6_K) return set_error(s, "dev_gemm_q6_k: not a Q6_K tensor") ? 1 : 0;
+    if (workspace_bytes < gemm_q6k_ws_bytes(tokens, w->cols)) return set_error(s, "dev_gemm_q6_k: workspace too small") ? 1 : 0;
+    return enqueue_gemm_q6k(s, w, d_out, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
 }
 
 int zen_cuda_dev_gemm_q8_0_noalloc(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* stream) {
