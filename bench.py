@@ -682,9 +682,20 @@ def run_lm_head(args, brief: bool = False) -> dict | None:
             if world == 1:
                 segs = [(d_local.data_ptr(), LM_ROWS, 0, LM_ROWS)]
 
+            # two or more rows: the tensor-core product, then (several GPUs, equal shards) the one-launch peer all-gather
+            tensor = tokens >= 2 and not args.no_q6k_tensor and (not fused or my_rows == widest)
+            ws_bytes = be.gemm_q6_k_workspace_bytes(tokens, LM_COLS)
+            d_ws = torch.zeros(ws_bytes if tensor else 16, dtype=torch.uint8, device=dev)
+
             def one_pass():
                 for h in handles:
-                    if fused:
+                    if tensor:
+                        be.dev_gemm_q6_k(h, d_local.data_ptr(), d_h.data_ptr(), tokens, d_ws.data_ptr(), ws_bytes, stream.cuda_stream)
+                        if fused:
+                            pg.allgather(d_local.data_ptr(), tokens * my_rows, d_all.data_ptr(), stream.cuda_stream)
+                        elif world > 1:
+                            dist.all_gather_into_tensor(d_all.view(world * tokens, widest), d_local)
+                    elif fused:
                         pg.gemv([h], d_h.data_ptr(), tokens, ACT_FP32, stream.cuda_stream, d_y=[d_local.data_ptr()])
                         pg.fetch(d_all.data_ptr(), stream.cuda_stream)
                     else:
@@ -739,7 +750,8 @@ def run_lm_head(args, brief: bool = False) -> dict | None:
             assert bool((shard.greedy_pick(full) == d_pick).all().item()), "device pick differs from the first maximum of the logits"
             algo = tensor_bytes("Q6_K", LM_ROWS, LM_COLS) + tokens * 4 * (LM_COLS + LM_ROWS)
             results[tokens] = {"us_per_step": ms * 1e3 / steps, "gbs": algo / (ms * 1e-3 / steps) / 1e9, "steps": steps,
-                               "algorithmic_bytes": algo, "picks_per_s": tokens * steps / (ms * 1e-3)}
+                               "algorithmic_bytes": algo, "picks_per_s": tokens * steps / (ms * 1e-3),
+                               "kernel": "gemm_q8_0_i8_kernel<32, 2, Q6_K> (tcgen05)" if tensor else "gemv_kq_kernel (dp4a)"}
             if pg is not None:
                 stream.synchronize()
                 pg.close()
@@ -1241,6 +1253,7 @@ def main() -> None:
     ap.add_argument("--formats", default="Q8_0,Q4_0,Q6_K,Q4_K,Q5_K", help="workload layer_sweep: formats to run")
     ap.add_argument("--act", default="int8", choices=["int8", "fp32"], help="workload q8_0_gemm: activation mode of the timed product (the other one is timed briefly beside it)")
     ap.add_argument("--no-list", action="store_true", help="default workload: skip the persistent list launch among the config 0 submission variants")
+    ap.add_argument("--no-q6k-tensor", action="store_true", help="workload lm_head: batch 8 through the decode kernel (dp4a) instead of the tensor-core product")
     ap.add_argument("--no-detail", action="store_true", help="default workload: skip the short runs of the other workloads that fill `detail`")
     ap.add_argument("--device-pack", action="store_true", help="workload lm_head: draw and pack the Q6_K matrix on the GPU (torch) instead of numpy")
     ap.add_argument("--cut", default="rows+cols", choices=["rows", "rows+cols"],

@@ -279,8 +279,10 @@ int zen_cuda_dev_gemm_q8_0_act(const zen_cuda_weights* const* w, float* const* d
  * batched Q6_K product gemm_q6k_kblk_avx2, kernels/avx2.cpp:1762-1770, GPU entry zen::d3d12::gemm_q6_k,
  * include/zen/d3d12_backend.h:169): fp32-equivalent activations (two int8 digits), out [tokens][rows] fp32.  The tensor
  * must be resident with its codes unpacked (the default layout, zen_cuda_set_q6k_codes).  `workspace` is device memory of
- * at least zen_cuda_gemm_q6_k_workspace_bytes(tokens, columns), untouched until the stream has run the work.  The
- * host-pointer call zen_cuda_gemm_q6_k takes this path by itself from two rows on. */
+ * at least zen_cuda_gemm_q6_k_workspace_bytes(tokens, columns), untouched until the stream has run the work.  Up to
+ * sixteen rows go through tiles of 32 columns (a token is two columns, one per parity of its 16-weight groups), more
+ * through the prefill GEMM's 128.  The host-pointer call zen_cuda_gemm_q6_k takes this path by itself from seven rows
+ * on; below that the decode kernel is faster. */
 size_t zen_cuda_gemm_q6_k_workspace_bytes(size_t tokens, size_t columns);
 int zen_cuda_dev_gemm_q6_k(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace,
                            size_t workspace_bytes, void* stream);

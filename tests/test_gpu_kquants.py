@@ -218,11 +218,12 @@ def test_rows_of_several_segments(be, zo, fmt, rows, cols, tokens):
         assert rel < 1e-4
 
 
-@pytest.mark.parametrize("rows,cols,tokens", [(1, 256, 2), (130, 2048, 3), (300, 4096, 8), (1027, 1280, 16), (64, 14336, 5), (9, 4352, 37), (19000, 512, 8)])
+@pytest.mark.parametrize("rows,cols,tokens", [(1, 256, 2), (130, 2048, 3), (300, 4096, 8), (1027, 1280, 16), (64, 14336, 5), (9, 4352, 37), (19000, 512, 8), (130, 2048, 70), (300, 1024, 129)])
 def test_q6_k_tensor_core_product_vs_oracle(be, zo, rows, cols, tokens):
     # two or more activation rows: the tcgen05 product with one column per token and group parity (the batched lm_head of
     # config 3, the reference's gemm_q6k_kblk_avx2); device pointers and a caller workspace, then the host-pointer call.
-    # 19000 rows are 149 row tiles: one more than the SMs, so the K range of a tile is shared between two CTAs.
+    # 19000 rows are 149 row tiles: one more than the SMs, so the K range of a tile is shared between two CTAs.  More than
+    # sixteen rows take the 128-column tiles of the prefill GEMM (64 tokens a tile).
     import torch
     w = seeded_weights(Q6_K, rows, cols, 900 + rows)
     x = seeded_acts(tokens, cols, 910 + cols)

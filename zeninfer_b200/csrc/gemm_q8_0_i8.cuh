@@ -42,6 +42,9 @@ constexpr int kGemmM = 128;            // weight rows per tile (TMEM lanes)
 constexpr int kGemmKTile = 128;        // K bytes per stage = 4 Q8_0 blocks
 constexpr int kGemmBlocksPerTile = kGemmKTile / 32;
 constexpr int kGemmStages = 4;
+// Narrow tiles (32 columns: a handful of activation rows) are bound by the latency of the hand-offs, not by bytes or
+// arithmetic: they get a deeper ring and, below, all of TMEM as accumulator buffers.
+__host__ __device__ constexpr int gemm_stages(uint32_t n_tile) { return n_tile <= 32 ? 8 : kGemmStages; }
 #ifndef ZK_GEMM_EPI_WARPS
 #define ZK_GEMM_EPI_WARPS 16
 #endif
@@ -76,7 +79,7 @@ __host__ __device__ constexpr uint32_t gemm_stage_bytes(uint32_t n_tile, uint32_
     return kGemmM * kGemmKTile + digits * n_tile * kGemmKTile + ((kGemmBlocksPerTile * n_tile * 4 + 1023u) & ~1023u);
 }
 __host__ __device__ inline size_t gemm_smem_bytes(uint32_t n_tile, uint32_t digits = 1) {
-    return 1024 /* alignment slack */ + static_cast<size_t>(kGemmStages) * gemm_stage_bytes(n_tile, digits) + 256 /* barriers */;
+    return 1024 /* alignment slack */ + static_cast<size_t>(gemm_stages(n_tile)) * gemm_stage_bytes(n_tile, digits) + 512 /* barriers */;
 }
 
 // Packed fp32 pairs (sm_100 f32x2 arithmetic): one instruction scales or accumulates two token columns.
@@ -210,7 +213,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
     static_assert(kSplit >= 1 && kSplit <= kGemmSplit, "tile width");
     constexpr int kNHalf = kNTile / kSplit;         // token columns per epilogue warp
     static_assert(kNHalf % (kDigits == 2 ? 16 : 32) == 0, "an epilogue warp takes whole 32-column (two digits: 16-column) chunks");
-    constexpr uint32_t kPairs = 2;                   // TMEM accumulator buffers come in pairs: one hand-off per two blocks
+    constexpr int kStages = gemm_stages(kNTile);
+    constexpr uint32_t kPairs = 512 / (2 * kNTile) < 8 ? 512 / (2 * kNTile) : 8;   // TMEM accumulator buffers come in pairs (one hand-off per pair): 2 pairs of 128 columns, 8 of 32
     constexpr uint32_t kStageBytes = gemm_stage_bytes(kNTile, kDigits);
     constexpr uint32_t kScaleOff = kGemmM * kGemmKTile + kDigits * kNTile * kGemmKTile;   // the stage: weights | codes | (fine digits) | scales
     constexpr uint32_t kLoadBytes = kScaleOff + kGemmBlocksPerTile * kNTile * 4;           // what the four copies of a stage deliver
@@ -219,18 +223,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
     static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM allocations are powers of two from 32 to 512 columns");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kGemmStages * kStageBytes);
-    uint64_t* empty = full + kGemmStages;
-    uint64_t* tmem_full = empty + kGemmStages;
-    uint64_t* tmem_empty = tmem_full + 4;
-    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 4);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    uint64_t* empty = full + kStages;
+    uint64_t* tmem_full = empty + kStages;
+    uint64_t* tmem_empty = tmem_full + kPairs;
+    uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + kPairs);
+    static_assert((2 * kStages + 2 * kPairs) * 8 + 8 <= 512, "barrier area");
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t ktiles = (p.nb + kGemmBlocksPerTile - 1) / kGemmBlocksPerTile;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kGemmStages; ++s) {
+        for (int s = 0; s < kStages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1 + kEpiActive);
         }
@@ -263,8 +268,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                 gemm_locate(p, tile % p.m_tiles, ti, mt);
                 const CUtensorMap* map_w = &p.map_w[ti];
                 for (uint32_t kt = kt0; kt < kt1; ++kt, ++it) {
-                    const uint32_t stage = it % kGemmStages;
-                    if (it >= kGemmStages && !mbar_wait(&empty[stage], ((it / kGemmStages) - 1) & 1)) {
+                    const uint32_t stage = it % kStages;
+                    if (it >= kStages && !mbar_wait(&empty[stage], ((it / kStages) - 1) & 1)) {
                         *abort_word = 1; atomicExch(p.error_word, kErrEmptyWaitTimeout); ok = false;
                     }
                     if (*abort_word) ok = false;
@@ -288,8 +293,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
             GemmWork work(p, ktiles);
             while (ok && work.next(tile, kt0, kt1)) {
                 for (uint32_t kt = kt0; kt < kt1 && ok; ++kt, ++it) {
-                    const uint32_t stage = it % kGemmStages;
-                    if (*abort_word || !mbar_wait(&full[stage], (it / kGemmStages) & 1)) {
+                    const uint32_t stage = it % kStages;
+                    if (*abort_word || !mbar_wait(&full[stage], (it / kStages) & 1)) {
                         if (!*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrFullWaitTimeout); }
                         ok = false;
                         break;
@@ -337,6 +342,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
             gemm_locate(p, tile % p.m_tiles, ti, mt);
             const uint32_t r = mt * kGemmM + quad * 32 + lane, rows = p.rows[ti];
             const bool row_ok = r < rows;
+            // Q6_K: a warp whose columns all lie past the last token (eight rows fill half a tile) only keeps the hand-offs going
+            const bool live_cols = !kQ6K || nt * kNTile + half * kNHalf < 2 * p.tokens;
             uint64_t acc[kNHalf / 2];  // packed pairs of fp32 accumulators, token columns (2i, 2i+1)
 #pragma unroll
             for (int c = 0; c < kNHalf / 2; ++c) acc[c] = 0ull;
@@ -347,12 +354,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
             const __half* d_row = p.w_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nbp;   // Q6_K: super-block scales
             uint2 sw_next = __ldg(sw_row + kt0);
             for (uint32_t kt = kt0; kt < kt1 && ok; ++kt, ++it) {
-                const uint32_t stage = it % kGemmStages;
+                const uint32_t stage = it % kStages;
                 const uint2 sw4 = sw_next;
                 if (kt + 1 < kt1) sw_next = __ldg(sw_row + kt + 1);
                 float dq = 0.0f;
                 if constexpr (kQ6K) dq = __half2float(__ldg(d_row + (kt >> 1))) * 0.00390625f;   // the digits' common unit is d_x / 256
-                if (*abort_word || !mbar_wait(&full[stage], (it / kGemmStages) & 1)) {
+                if (*abort_word || !mbar_wait(&full[stage], (it / kStages) & 1)) {
                     if (lane == 0 && !*abort_word) { *abort_word = 1; atomicExch(p.error_word, kErrFullWaitTimeout); }
                     ok = false;
                     break;
@@ -371,6 +378,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                                 ok = false;
                             } else {
                                 tc_fence_after_sync();
+                                if (!live_cols) {
+                                    tc_fence_before_sync(); __syncwarp();
+                                    if (lane == 0) mbar_arrive(&tmem_empty[pr]);
+                                    ++pair;
+                                    continue;
+                                }
                                 uint64_t sw2;
                                 if constexpr (kQ6K) {   // the block's even and odd group: (d * scale), the reference's factor (kernels/avx2.cpp:380-422)
                                     const uint32_t two = (j < 2 ? sw4.x : sw4.y) >> (16 * (j & 1));

@@ -974,7 +974,11 @@ bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const*
 // Q6_K (codes unpacked on upload) times `tokens` >= 2 activation rows on the tensor cores: every token enters as two
 // columns, one per parity of the 16-weight groups (gemm_q8_0_i8.cuh), in tiles of 32 columns = 16 tokens.  The workspace
 // is gemm_ws_bytes(2 * tokens, cols, 2).  Stream-ordered on `st`.
-constexpr uint32_t kQ6kGemmNTile = 32;
+// Narrow tiles (32 columns = 16 tokens) up to kQ6kNarrowMaxTokens rows, the prefill GEMM's 128 columns (64 tokens) beyond.
+constexpr size_t kQ6kNarrowMaxTokens = 16;
+// From this many activation rows on the host-pointer call takes the tensor-core product: the narrow-tile kernel takes the
+// same ~270 us for the 128256 x 4096 lm_head whatever the row count, the decode kernel 43 + 41 us per row.
+constexpr size_t kQ6kTensorMinTokens = 7;
 size_t gemm_q6k_ws_bytes(size_t tokens, size_t cols) { return gemm_ws_bytes(2 * tokens, cols, 2); }
 
 bool enqueue_gemm_q6k(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, cudaStream_t st) {
@@ -994,9 +998,10 @@ bool enqueue_gemm_q6k(State& s, const zen_cuda_weights* w, float* d_out, const f
     zk::GemmParams p{};
     p.m_start[0] = 0; p.m_start[1] = p.m_start[2] = 0xffffffffu;
     if (!make_map_2d(s, &p.map_w[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->plane[0], cols, w->rows, cols, zk::kGemmKTile, zk::kGemmM, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
-    if (!make_map_2d(s, &p.map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, cols, columns, cols, zk::kGemmKTile, kQ6kGemmNTile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
-    if (!make_map_2d(s, &p.map_x2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq2, cols, columns, cols, zk::kGemmKTile, kQ6kGemmNTile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
-    if (!make_map_2d(s, &p.map_xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, xs_t, t_ld, nb, t_ld * sizeof(float), kQ6kGemmNTile, zk::kGemmBlocksPerTile,
+    const uint32_t n_tile = tokens <= kQ6kNarrowMaxTokens ? 32u : 128u;   // columns per tile: two per token
+    if (!make_map_2d(s, &p.map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, cols, columns, cols, zk::kGemmKTile, n_tile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if (!make_map_2d(s, &p.map_x2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq2, cols, columns, cols, zk::kGemmKTile, n_tile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if (!make_map_2d(s, &p.map_xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, xs_t, t_ld, nb, t_ld * sizeof(float), n_tile, zk::kGemmBlocksPerTile,
                      CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
     p.w_group_scales[0] = static_cast<const int8_t*>(w->plane[1]);
     p.group_pitch = static_cast<uint32_t>(cols / 16);
@@ -1007,7 +1012,7 @@ bool enqueue_gemm_q6k(State& s, const zen_cuda_weights* w, float* d_out, const f
     p.tokens = static_cast<uint32_t>(tokens);
     p.nb = nb;
     p.nbp = w->nbp;
-    p.n_tile = kQ6kGemmNTile / 2;   // tokens per tile
+    p.n_tile = n_tile / 2;   // tokens per tile
     p.m_tiles = (p.rows[0] + zk::kGemmM - 1) / zk::kGemmM;
     p.n_tiles = (p.tokens + p.n_tile - 1) / p.n_tile;
     p.error_word = s.d_error;
@@ -1018,7 +1023,7 @@ bool enqueue_gemm_q6k(State& s, const zen_cuda_weights* w, float* d_out, const f
         zk::gemm_zero_split_tiles_kernel<<<grid, 256, 0, st>>>(p, ktiles);
         ++s.stats.dispatches;
     }
-    const cudaError_t e = launch_gemm<kQ6kGemmNTile, 2, true>(p, grid, st);
+    const cudaError_t e = n_tile == 32 ? launch_gemm<32, 2, true>(p, grid, st) : launch_gemm<128, 2, true>(p, grid, st);
     if (e != cudaSuccess) return set_error(s, std::string("gemm q6_k launch: ") + cudaGetErrorString(e));
     ++s.stats.dispatches;
     return true;
@@ -1246,9 +1251,9 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     const size_t chunk = max_tokens_per_launch(s, w[0]->kernel_format, cols, act_mode);
     if (!chunk) return set_error(s, "columns too large: one activation row does not fit shared memory");
     // More than one decode launch worth of int8-activation Q8_0 tokens: the tensor-core GEMM.
-    // Q6_K with its codes unpacked: the tensor-core product from two activation rows on (a one-row product streams faster
+    // Q6_K with its codes unpacked: the tensor-core product from kQ6kTensorMinTokens activation rows on (fewer stream faster
     // through the decode kernel).
-    bool q6k_tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q6_K && tokens >= 2;
+    bool q6k_tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q6_K && tokens >= kQ6kTensorMinTokens;
     for (size_t i = 0; i < count; ++i) q6k_tensor_path = q6k_tensor_path && w[i]->kernel_format == zk::kFormatQ6KCodes;   // the file's planes: decode kernel
     const bool tensor_path = q6k_tensor_path || (s.use_gemm && fmt == ZEN_CUDA_Q8_0 && tokens > 8);   // Q8_0: either activation mode
     const bool fetch_by_kernel = direct && x_bytes <= kDirectInputBytes;
