@@ -72,7 +72,20 @@ def test_lm_head_device_pick_matches_oracle_argmax(be, zo, lm_head, tokens):
         stream.synchronize()
         be.dev_check(stream.cuda_stream)
         logits = d_y.cpu().numpy()
-        assert np.array_equal(logits, be.gemm("Q6_K", packed, hidden[:tokens], tokens, ROWS, COLS))   # host-pointer call = same kernels
+        host = be.gemm("Q6_K", packed, hidden[:tokens], tokens, ROWS, COLS)
+        if tokens == 1:
+            assert np.array_equal(logits, host)   # host-pointer call = same kernel
+        else:
+            # from seven rows on the host-pointer call takes the tensor-core product: equal to the device entry point of
+            # that product bit for bit, and to the decode kernel up to the order of the fp32 additions
+            ws_bytes = be.gemm_q6_k_workspace_bytes(tokens, COLS)
+            d_ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=dev)
+            d_t = torch.zeros((tokens, ROWS), dtype=torch.float32, device=dev)
+            be.dev_gemm_q6_k(h, d_t.data_ptr(), d_x.data_ptr(), tokens, d_ws.data_ptr(), ws_bytes, stream.cuda_stream)
+            stream.synchronize()
+            be.dev_check(stream.cuda_stream)
+            assert np.array_equal(d_t.cpu().numpy(), host)
+            assert_parity(host, logits, 1e-5, "tensor-core product against the decode kernel")
         assert d_pick.cpu().tolist() == [zo.argmax(logits[t]) for t in range(tokens)]
     finally:
         be.dev_free(h)
