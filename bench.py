@@ -677,13 +677,13 @@ def run_lm_head(args, brief: bool = False) -> dict | None:
             d_local = torch.zeros((tokens, my_rows), dtype=torch.float32, device=dev)
             d_all = torch.zeros((world, tokens * widest), dtype=torch.float32, device=dev)
             d_pick = torch.full((tokens,), -7, dtype=torch.int64, device=dev)
-            pg = shard.PeerGather(be, world, rank, tokens * widest) if fused else None
+            # two or more rows: the tensor-core product, then (several GPUs, equal shards) an NCCL all-gather of the logits
+            tensor = tokens >= 2 and not args.no_q6k_tensor and my_rows == widest
+            pg = shard.PeerGather(be, world, rank, tokens * widest) if fused and not tensor else None
             segs = [(d_all.data_ptr() + 4 * r * tokens * widest, b - a, a, b - a) for r, (a, b) in enumerate(plan)]
             if world == 1:
                 segs = [(d_local.data_ptr(), LM_ROWS, 0, LM_ROWS)]
 
-            # two or more rows: the tensor-core product, then (several GPUs, equal shards) the one-launch peer all-gather
-            tensor = tokens >= 2 and not args.no_q6k_tensor and (not fused or my_rows == widest)
             ws_bytes = be.gemm_q6_k_workspace_bytes(tokens, LM_COLS)
             d_ws = torch.zeros(ws_bytes if tensor else 16, dtype=torch.uint8, device=dev)
 
@@ -691,9 +691,7 @@ def run_lm_head(args, brief: bool = False) -> dict | None:
                 for h in handles:
                     if tensor:
                         be.dev_gemm_q6_k(h, d_local.data_ptr(), d_h.data_ptr(), tokens, d_ws.data_ptr(), ws_bytes, stream.cuda_stream)
-                        if fused:
-                            pg.allgather(d_local.data_ptr(), tokens * my_rows, d_all.data_ptr(), stream.cuda_stream)
-                        elif world > 1:
+                        if world > 1:
                             dist.all_gather_into_tensor(d_all.view(world * tokens, widest), d_local)
                     elif fused:
                         pg.gemv([h], d_h.data_ptr(), tokens, ACT_FP32, stream.cuda_stream, d_y=[d_local.data_ptr()])
@@ -751,7 +749,7 @@ def run_lm_head(args, brief: bool = False) -> dict | None:
             algo = tensor_bytes("Q6_K", LM_ROWS, LM_COLS) + tokens * 4 * (LM_COLS + LM_ROWS)
             results[tokens] = {"us_per_step": ms * 1e3 / steps, "gbs": algo / (ms * 1e-3 / steps) / 1e9, "steps": steps,
                                "algorithmic_bytes": algo, "picks_per_s": tokens * steps / (ms * 1e-3),
-                               "kernel": "gemm_q8_0_i8_kernel<32, 2, Q6_K> (tcgen05)" if tensor else "gemv_kq_kernel (dp4a)"}
+                               "kernel": ("gemm_q8_0_i8_kernel<32, 2, Q6_K> (tcgen05)" + (", NCCL all-gather" if world > 1 else "")) if tensor else "gemv_kq_kernel (dp4a)"}
             if pg is not None:
                 stream.synchronize()
                 pg.close()
