@@ -471,3 +471,36 @@ def test_gate_up_launch_with_the_swiglu_store(be, mode, rows, cols, tokens, norm
         be.dev_gemv_fused(hs, [hid.data_ptr(), None], x.data_ptr(), tokens, mode, 0, swiglu_pair=True, accumulate=True)
     for h in hs:
         be.dev_free(h)
+
+
+@pytest.mark.parametrize("mode", [ACT_FP32, ACT_INT8])
+def test_forward_block_gives_the_tail_logits_of_a_verify_block(be, golden, mode):
+    # forward_batch(proposals, ..., tail_count = proposals.size()) of speculative verification
+    # (src/adapters/dense_transformer_runtime.cpp:4874): teacher-forced with the tokens the greedy run produced, row i of
+    # the block's logits must pick the token that followed proposal i
+    import torch
+    cfg, meta, prompt, _, _ = golden
+    dec = LlamaDecoder(be, cfg, synthetic_tensors(cfg, meta["seed"], meta["weight_std"]), act_mode=mode)
+    try:
+        prompt = prompt.tolist()
+        toks = dec.generate(prompt, 12)
+        last = dec.last_logits()                       # after consuming toks[10]: they picked toks[11]
+        dec.reset()
+        with torch.cuda.stream(dec.stream):
+            dec.feed_prompt(prompt)                    # position len(prompt); the first pick is toks[0]
+        n = 7
+        lg = dec.forward_block(toks[:n], tail_count=n).clone()
+        assert dec.block_picks[:n].cpu().tolist() == toks[1:n + 1]
+        assert int(dec.token.item()) == toks[n] and int(dec.pos.item()) == len(prompt) + n
+        # a rejection after proposal n - 3: the next block starts behind the last accepted token and overwrites the cache rows
+        lg2 = dec.forward_block(toks[n - 2:n], start_pos=len(prompt) + n - 2, tail_count=2)
+        assert_parity(lg2.cpu().numpy(), lg[n - 2:].cpu().numpy(), 1e-5, "re-run of the rejected tail")
+        # more than eight tail rows take the GEMM; the last row is what the token-by-token run saw
+        lg3 = dec.forward_block(toks[:11], start_pos=len(prompt), tail_count=11)
+        assert dec.block_picks[:11].cpu().tolist() == toks[1:12]
+        assert_parity(lg3[10].cpu().numpy(), last, 1e-3 if mode == ACT_FP32 else 5e-3, "last row of the block vs the token-by-token logits")
+        assert_parity(lg3[:n].cpu().numpy(), lg.cpu().numpy(), 1e-3 if mode == ACT_FP32 else 5e-3, "GEMM head vs decode-kernel head")
+        with pytest.raises(ValueError):
+            dec.forward_block(toks[:3], tail_count=4)
+    finally:
+        dec.close()

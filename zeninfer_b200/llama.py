@@ -397,6 +397,46 @@ class LlamaDecoder:
             self.x.copy_(b["x"][T - 1])
             self.xn.copy_(b["xn"][T - 1])
 
+    def forward_block(self, tokens: list[int], start_pos: int | None = None, tail_count: int = 1):
+        """DenseTransformerRuntime::forward_batch (src/adapters/dense_transformer_runtime.cpp:2298): consumes `tokens` as one
+        block at positions start_pos .. (default: the current position) and returns the logits of the last `tail_count` of
+        them, [tail_count][vocab] fp32 on the device, with the greedy pick of every row in self.block_picks[:tail_count].
+        Speculative verification is this call with tail_count = len(proposals) (:4874): row i is the target model's
+        distribution after proposal i.  Afterwards the position is start_pos + len(tokens); a caller that rejects proposals
+        passes the position after the last accepted token as the next start_pos (the cache rows past it are overwritten,
+        as in the reference, whose caches are indexed by the position it is given).
+        The layers run through prefill() (tcgen05 GEMMs, causal block attention); the lm_head takes the tail rows through
+        the decode kernel (up to eight, in the decode activation mode) or the GEMM (more, in the block's mode).  One GPU only."""
+        if self.world != 1:
+            raise ValueError("forward_block: the sharded decoder keeps only its shard of the logits; use one GPU")
+        T = len(tokens)
+        if not 1 <= tail_count <= T or T > self.PREFILL_CHUNK:
+            raise ValueError("forward_block: 1 <= tail_count <= len(tokens) <= PREFILL_CHUNK")
+        torch, be, cfg, st = self.torch, self.be, self.cfg, self.stream.cuda_stream
+        if start_pos is None:
+            self.stream.synchronize()
+            start_pos = int(self.pos.item())
+        if start_pos + T > self.max_positions:
+            raise ValueError("forward_block: the block does not fit the configured positions")
+        with torch.cuda.stream(self.stream):
+            self.pos.fill_(start_pos)
+            d_ids = torch.tensor(tokens, dtype=torch.int64).pin_memory().to(self.dev, non_blocking=True)
+            self.prefill(d_ids, T)
+            b = self._prefill_buffers()
+            if getattr(self, "block_logits", None) is None or self.block_logits.shape[0] < tail_count:
+                self.block_logits = torch.zeros((max(tail_count, 8), cfg.vocab), dtype=torch.float32, device=self.dev)
+                self.block_picks = torch.zeros((max(tail_count, 8),), dtype=torch.int64, device=self.dev)
+            xn_tail = b["xn"][T - tail_count:T]       # normalised with the output norm by the block's last step
+            head, out = self.h["output.weight"], self.block_logits
+            if tail_count <= 8:
+                be.dev_gemv([head], [out.data_ptr()], xn_tail.data_ptr(), tail_count, self.act_mode, st)
+            else:
+                be.dev_gemm_q8_0([head], [out.data_ptr()], xn_tail.data_ptr(), tail_count, b["ws"].data_ptr(), b["ws_bytes"], st, act_mode=self._prefill_mode())
+            be.dev_greedy_pick([(out.data_ptr(), cfg.vocab, 0, cfg.vocab)], tail_count, self.block_picks.data_ptr(), st)
+            self.logits.copy_(out[tail_count - 1])     # what a following single step or last_logits() sees
+            self.token.copy_(self.block_picks[tail_count - 1:tail_count])
+        return self.block_logits[:tail_count]
+
     def feed_prompt(self, prompt: list[int], batched_prefill: bool | None = None) -> None:
         """Enqueues the whole prompt from position self.pos on, ending with the first pick (left in self.token).  Blocks of
         at least PREFILL_MIN tokens go through prefill() when batched_prefill (default: wherever can_prefill_blocks()), the
