@@ -287,6 +287,16 @@ size_t zen_cuda_gemm_q6_k_workspace_bytes(size_t tokens, size_t columns);
 int zen_cuda_dev_gemm_q6_k(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace,
                            size_t workspace_bytes, void* stream);
 
+/* Q4_0 times many activation rows on the tensor cores (the reference multiplies Q4_0 through its generic fp32 route,
+ * src/quant.cpp:1135-1162, and has no GPU entry for the format): the nibbles are widened to int8 codes n - 8 in the
+ * workspace, which with the tensor's f16 block scales is a Q8_0 tensor, then the Q8_0 GEMM runs with fp32-equivalent
+ * activations.  `workspace`: device memory of at least zen_cuda_gemm_q4_0_workspace_bytes(tokens, rows, columns) --
+ * rows x columns bytes of codes plus the GEMM's own workspace -- untouched until the stream has run the work; columns
+ * must be a multiple of 128.  The host-pointer call zen_cuda_gemm_q4_0 takes this path by itself from 32 rows on. */
+size_t zen_cuda_gemm_q4_0_workspace_bytes(size_t tokens, size_t rows, size_t columns);
+int zen_cuda_dev_gemm_q4_0(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 /* No counterpart in the reference.  The same prefill product as zen_cuda_dev_gemm_q8_0 for ONE tensor, for callers
  * that may not allocate device memory at the time of the call: a plug-in living inside a host runtime that owns all of
  * HBM (weights, KV cache and arenas were sized at start-up and nothing is left to ask for), or a serving loop that can

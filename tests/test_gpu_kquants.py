@@ -260,3 +260,27 @@ def test_q6_k_tensor_core_product_needs_the_unpacked_codes(be):
     with pytest.raises(BackendError, match="codes unpacked"):
         be.dev_gemm_q6_k(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
     be.dev_free(h)
+
+
+@pytest.mark.parametrize("rows,cols,tokens", [(300, 4096, 40), (1027, 1280, 33), (64, 14336, 64), (130, 2048, 129), (7, 128, 32)])
+def test_q4_0_tensor_core_product_vs_oracle(be, zo, rows, cols, tokens):
+    # many activation rows: nibbles widened to int8 codes n - 8 in the workspace, then the Q8_0 GEMM with two activation
+    # digits; the oracle is the reference's fp32-activation route for Q4_0.  Device entry point, then the host-pointer call
+    # (which takes the same path from 32 rows on).
+    import torch
+    w = seeded_weights(Q4_0, rows, cols, 960 + rows)
+    x = seeded_acts(tokens, cols, 970 + cols)
+    ref = np.stack([zo.gemv(Q4_0, w, x[t], rows, cols) for t in range(tokens)])
+    h = be.dev_upload("Q4_0", w, rows, cols)
+    d_x = torch.from_numpy(x).cuda()
+    y = torch.full((tokens, rows), float("nan"), device="cuda")
+    ws_bytes = be.gemm_q4_0_workspace_bytes(tokens, rows, cols)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+    be.dev_gemm_q4_0(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
+    be.dev_check()
+    rel = assert_parity(y.cpu().numpy(), ref, what=f"Q4_0 tensor product {tokens}x{rows}x{cols}")
+    assert rel < 1e-4
+    be.dev_free(h)
+    host = be.gemm("Q4_0", w, x, tokens, rows, cols)
+    assert np.array_equal(host, y.cpu().numpy())       # the same kernels on the same bytes
+    be.release_weights(w)

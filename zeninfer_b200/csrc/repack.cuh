@@ -140,4 +140,19 @@ __global__ void unpack_q6_k_codes_kernel(const uint8_t* __restrict__ raw, int8_t
     if (g16 == 0) d[r * sbp + b] = static_cast<uint16_t>(p[208] | (p[209] << 8));
 }
 
+// Q4_0 nibble plane -> int8 codes n - 8 in element order, [rows][K]: with the tensor's own f16 block scales this is a
+// Q8_0 tensor, which is how the tensor-core GEMM multiplies Q4_0 (a pass per call into scratch memory; the resident copy
+// stays 4-bit).  One thread per 32-weight block; low nibbles are elements 0..15, high nibbles 16..31 (src/quant.cpp:391-397).
+__global__ void unpack_q4_0_codes_kernel(const uint8_t* __restrict__ nibs, int8_t* __restrict__ codes, size_t blocks) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= blocks) return;
+    const uint4 w = reinterpret_cast<const uint4*>(nibs)[i];
+    // n - 8 per byte without borrows between bytes: set the top bit, subtract, flip it back
+    auto sub8 = [](uint32_t n) { return ((n | 0x80808080u) - 0x08080808u) ^ 0x80808080u; };
+    const uint32_t m = 0x0F0F0F0Fu;
+    uint4* out = reinterpret_cast<uint4*>(codes + i * 32);
+    out[0] = make_uint4(sub8(w.x & m), sub8(w.y & m), sub8(w.z & m), sub8(w.w & m));
+    out[1] = make_uint4(sub8((w.x >> 4) & m), sub8((w.y >> 4) & m), sub8((w.z >> 4) & m), sub8((w.w >> 4) & m));
+}
+
 }  // namespace zk

@@ -1029,6 +1029,32 @@ bool enqueue_gemm_q6k(State& s, const zen_cuda_weights* w, float* d_out, const f
     return true;
 }
 
+// Q4_0 times many activation rows: the nibbles are widened to int8 codes n - 8 in scratch memory (with the tensor's own
+// f16 block scales that is a Q8_0 tensor), then the Q8_0 GEMM with two activation digits, the fp32-activation arithmetic
+// the reference uses for this format (generic route, src/quant.cpp:1135-1162).  The workspace holds the codes
+// (rows x cols bytes, padded to 256) followed by the GEMM's own workspace.
+constexpr size_t kQ4TensorMinTokens = 32;   // below: chunks of eight through the decode kernel are as fast
+size_t gemm_q4_0_ws_bytes(size_t tokens, size_t rows, size_t cols) {
+    return ((rows * cols + 255) & ~size_t(255)) + gemm_ws_bytes(tokens, cols, 2);
+}
+
+bool enqueue_gemm_q4_0(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, cudaStream_t st) {
+    if (!w || !d_out || !d_x || !ws || !tokens) return set_error(s, "gemm q4_0: bad arguments");
+    if (w->format != ZEN_CUDA_Q4_0) return set_error(s, "gemm q4_0: not a Q4_0 tensor");
+    const size_t blocks = w->rows * w->nb;
+    zk::unpack_q4_0_codes_kernel<<<static_cast<unsigned>((blocks + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(w->plane[0]),
+                                                                                             reinterpret_cast<int8_t*>(ws), blocks);
+    if (cudaGetLastError() != cudaSuccess) return set_error(s, "gemm q4_0: unpack launch failed");
+    ++s.stats.dispatches;
+    zen_cuda_weights as_q8 = *w;          // a view: the widened codes and the tensor's own scale plane
+    as_q8.format = as_q8.kernel_format = ZEN_CUDA_Q8_0;
+    as_q8.plane[0] = ws;
+    as_q8.d_tile_maps = nullptr;
+    const zen_cuda_weights* wp[1] = {&as_q8};
+    float* outs[1] = {d_out};
+    return enqueue_gemm_q8_0(s, wp, outs, 1, d_x, tokens, ws + ((w->rows * w->cols + 255) & ~size_t(255)), st, ZEN_CUDA_ACT_FP32);
+}
+
 // Scratch of the allocation-free GEMM entry point: part of the library image, one copy per GPU that loads it.
 // In host code this name is only a handle for the runtime; the device address comes from cudaGetSymbolAddress.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[ZEN_CUDA_NOALLOC_SCRATCH_BYTES];
@@ -1255,7 +1281,8 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     // through the decode kernel).
     bool q6k_tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q6_K && tokens >= kQ6kTensorMinTokens;
     for (size_t i = 0; i < count; ++i) q6k_tensor_path = q6k_tensor_path && w[i]->kernel_format == zk::kFormatQ6KCodes;   // the file's planes: decode kernel
-    const bool tensor_path = q6k_tensor_path || (s.use_gemm && fmt == ZEN_CUDA_Q8_0 && tokens > 8);   // Q8_0: either activation mode
+    const bool q4_tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q4_0 && tokens >= kQ4TensorMinTokens && cols % 128 == 0;
+    const bool tensor_path = q6k_tensor_path || q4_tensor_path || (s.use_gemm && fmt == ZEN_CUDA_Q8_0 && tokens > 8);   // Q8_0: either activation mode
     const bool fetch_by_kernel = direct && x_bytes <= kDirectInputBytes;
 
     // The three launches of a small call (fetch the activations, the product, copy the result out and publish it).
@@ -1343,7 +1370,13 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
         }
         s.stats.transfer_us += us_since(t0);
         t0 = clock_type::now();
-        if (tensor_path && fmt == ZEN_CUDA_Q6_K) {
+        if (tensor_path && fmt == ZEN_CUDA_Q4_0) {
+            size_t need = 0;
+            for (size_t i = 0; i < count; ++i) need = std::max(need, gemm_q4_0_ws_bytes(tokens, rows[i], cols));
+            if (!ensure_gemm_ws(s, need)) return false;
+            for (size_t i = 0; i < count; ++i)    // stream-ordered: the tensors share the scratch one after the other
+                if (!enqueue_gemm_q4_0(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
+        } else if (tensor_path && fmt == ZEN_CUDA_Q6_K) {
             if (!ensure_gemm_ws(s, gemm_q6k_ws_bytes(tokens, cols))) return false;
             for (size_t i = 0; i < count; ++i)    // stream-ordered: the tensors share the workspace one after the other
                 if (!enqueue_gemm_q6k(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
@@ -1840,6 +1873,19 @@ int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out
 }
 
 size_t zen_cuda_gemm_q6_k_workspace_bytes(size_t tokens, size_t columns) { return gemm_q6k_ws_bytes(tokens, columns); }
+
+size_t zen_cuda_gemm_q4_0_workspace_bytes(size_t tokens, size_t rows, size_t columns) { return gemm_q4_0_ws_bytes(tokens, rows, columns); }
+
+int zen_cuda_dev_gemm_q4_0(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!w || !d_out || !d_x || !tokens) return set_error(s, "dev_gemm_q4_0: bad arguments") ? 1 : 0;
+    if (w->format != ZEN_CUDA_Q4_0 || w->cols % 128) return set_error(s, "dev_gemm_q4_0: a Q4_0 tensor whose columns are a multiple of 128") ? 1 : 0;
+    if (workspace_bytes < gemm_q4_0_ws_bytes(tokens, w->rows, w->cols)) return set_error(s, "dev_gemm_q4_0: workspace too small") ? 1 : 0;
+    return enqueue_gemm_q4_0(s, w, d_out, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
+}
 
 int zen_cuda_dev_gemm_q6_k(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace, size_t workspace_bytes,
                            void* stream) {
