@@ -292,7 +292,7 @@ int zen_cuda_dev_gemm_q6_k(const zen_cuda_weights* w, float* d_out, const float*
  * workspace, which with the tensor's f16 block scales is a Q8_0 tensor, then the Q8_0 GEMM runs with fp32-equivalent
  * activations.  `workspace`: device memory of at least zen_cuda_gemm_q4_0_workspace_bytes(tokens, rows, columns) --
  * rows x columns bytes of codes plus the GEMM's own workspace -- untouched until the stream has run the work; columns
- * must be a multiple of 128.  The host-pointer call zen_cuda_gemm_q4_0 takes this path by itself from 32 rows on. */
+ * must be a multiple of 128.  The host-pointer call zen_cuda_gemm_q4_0 takes this path by itself from 12 rows on. */
 size_t zen_cuda_gemm_q4_0_workspace_bytes(size_t tokens, size_t rows, size_t columns);
 int zen_cuda_dev_gemm_q4_0(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace,
                            size_t workspace_bytes, void* stream);

@@ -262,11 +262,11 @@ def test_q6_k_tensor_core_product_needs_the_unpacked_codes(be):
     be.dev_free(h)
 
 
-@pytest.mark.parametrize("rows,cols,tokens", [(300, 4096, 40), (1027, 1280, 33), (64, 14336, 64), (130, 2048, 129), (7, 128, 32)])
+@pytest.mark.parametrize("rows,cols,tokens", [(300, 4096, 40), (1027, 1280, 33), (64, 14336, 64), (130, 2048, 129), (7, 128, 12)])
 def test_q4_0_tensor_core_product_vs_oracle(be, zo, rows, cols, tokens):
     # many activation rows: nibbles widened to int8 codes n - 8 in the workspace, then the Q8_0 GEMM with two activation
     # digits; the oracle is the reference's fp32-activation route for Q4_0.  Device entry point, then the host-pointer call
-    # (which takes the same path from 32 rows on).
+    # (which takes the same path from 12 rows on).
     import torch
     w = seeded_weights(Q4_0, rows, cols, 960 + rows)
     x = seeded_acts(tokens, cols, 970 + cols)
