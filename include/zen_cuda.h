@@ -297,6 +297,17 @@ size_t zen_cuda_gemm_q4_0_workspace_bytes(size_t tokens, size_t rows, size_t col
 int zen_cuda_dev_gemm_q4_0(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace,
                            size_t workspace_bytes, void* stream);
 
+/* Q4_K / Q5_K times many activation rows on the tensor cores (the reference's batched K-quant products gemm_q4k_kblk_avx2 /
+ * gemm_q5k_kblk_avx2, kernels/avx2.cpp:1605-1620; GPU entry zen::d3d12::gemm_kquant, include/zen/d3d12_backend.h:75): the
+ * 4- and 5-bit codes are widened to int8 in the workspace together with the fp32 factors of every 32-weight sub-block
+ * (d * sc and dmin * m, as the reference forms them), then the GEMM runs with fp32-equivalent activations and subtracts
+ * the minimum term in its epilogue.  `workspace`: at least zen_cuda_gemm_kquant_workspace_bytes(tokens, rows, columns) of
+ * device memory, untouched until the stream has run the work.  The host-pointer call zen_cuda_gemm_kquant takes this path
+ * by itself from 12 rows on. */
+size_t zen_cuda_gemm_kquant_workspace_bytes(size_t tokens, size_t rows, size_t columns);
+int zen_cuda_dev_gemm_kquant(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
 /* No counterpart in the reference.  The same prefill product as zen_cuda_dev_gemm_q8_0 for ONE tensor, for callers
  * that may not allocate device memory at the time of the call: a plug-in living inside a host runtime that owns all of
  * HBM (weights, KV cache and arenas were sized at start-up and nothing is left to ask for), or a serving loop that can

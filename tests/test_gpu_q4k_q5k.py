@@ -70,3 +70,29 @@ def test_device_pointer_calls(be, zo, fmt, name, tag):
         be.dev_gemv(hs[:1], [outs[0].data_ptr()], d_x.data_ptr(), tokens, ACT_INT8, stream.cuda_stream)   # fp32-equivalent activations only
     for h in hs + [part]:
         be.dev_free(h)
+
+
+@pytest.mark.parametrize("fmt,name,tag", FORMATS)
+@pytest.mark.parametrize("rows,cols,tokens", [(300, 4096, 40), (1027, 1280, 12), (64, 14336, 64), (130, 2048, 129), (19000, 256, 16)])
+def test_tensor_core_product_vs_oracle(be, zo, fmt, name, tag, rows, cols, tokens):
+    # many activation rows: codes widened to int8 in the workspace with the fp32 factors d * sc and dmin * m of every
+    # sub-block, then the tcgen05 GEMM with two activation digits whose epilogue subtracts the minimum term.  Device entry
+    # point with a caller workspace, then the host-pointer call (the same path from twelve rows on).  19000 rows are 149
+    # row tiles: the K range of one tile is shared between two CTAs.
+    import torch
+    w = blocks.random_k_blocks(fmt, rows, cols, 600 + rows)
+    x = seeded_acts(tokens, cols, 610 + cols)
+    ref = np.stack([zo.gemv(fmt, w, x[t], rows, cols) for t in range(tokens)])
+    h = be.dev_upload(name, w, rows, cols)
+    d_x = torch.from_numpy(x).cuda()
+    y = torch.full((tokens, rows), float("nan"), device="cuda")
+    ws_bytes = be.gemm_kquant_workspace_bytes(tokens, rows, cols)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+    be.dev_gemm_kquant(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
+    be.dev_check()
+    rel = assert_parity(y.cpu().numpy(), ref, what=f"{name} tensor product {tokens}x{rows}x{cols}")
+    assert rel < 1e-4
+    be.dev_free(h)
+    host = be.gemm(name, w, x, tokens, rows, cols)
+    assert np.array_equal(host, y.cpu().numpy())       # the same kernels on the same bytes
+    be.release_weights(w)

@@ -38,6 +38,7 @@ ABI_SYMBOLS = (
     "zen_cuda_gemv_list_create", "zen_cuda_gemv_list_destroy", "zen_cuda_gemv_list_bytes", "zen_cuda_dev_gemv_list",
     "zen_cuda_gemm_workspace_bytes", "zen_cuda_dev_gemm_q8_0", "zen_cuda_gemm_workspace_bytes_act", "zen_cuda_dev_gemm_q8_0_act",
     "zen_cuda_gemm_q6_k_workspace_bytes", "zen_cuda_dev_gemm_q6_k", "zen_cuda_gemm_q4_0_workspace_bytes", "zen_cuda_dev_gemm_q4_0",
+    "zen_cuda_gemm_kquant_workspace_bytes", "zen_cuda_dev_gemm_kquant",
     "zen_cuda_dev_gemm_q8_0_noalloc",
     "zen_cuda_gather_region_bytes", "zen_cuda_ipc_alloc", "zen_cuda_ipc_open", "zen_cuda_ipc_close", "zen_cuda_ipc_free",
     "zen_cuda_gather_create", "zen_cuda_gather_destroy", "zen_cuda_dev_gemv_gather", "zen_cuda_dev_gather_fetch", "zen_cuda_dev_allgather", "zen_cuda_dev_allreduce_add",
@@ -149,6 +150,9 @@ def load_library(path: str | None = None) -> C.CDLL:
     lib.zen_cuda_gemm_q4_0_workspace_bytes.argtypes = [sz, sz, sz]
     lib.zen_cuda_gemm_q4_0_workspace_bytes.restype = sz
     lib.zen_cuda_dev_gemm_q4_0.argtypes = [vp, vp, vp, sz, vp, sz, vp]
+    lib.zen_cuda_gemm_kquant_workspace_bytes.argtypes = [sz, sz, sz]
+    lib.zen_cuda_gemm_kquant_workspace_bytes.restype = sz
+    lib.zen_cuda_dev_gemm_kquant.argtypes = [vp, vp, vp, sz, vp, sz, vp]
     lib.zen_cuda_dev_gemm_q8_0_noalloc.argtypes = [vp, vp, vp, sz, vp]
     lib.zen_cuda_gather_region_bytes.argtypes = [sz, sz]
     lib.zen_cuda_gather_region_bytes.restype = sz
@@ -421,6 +425,15 @@ class Backend:
         """Q4_0 times many activation rows: nibbles widened to int8 codes in the workspace, then the Q8_0 tensor-core GEMM."""
         if not self.lib.zen_cuda_dev_gemm_q4_0(handle, d_out, d_x, tokens, workspace, workspace_bytes, stream):
             self._fail("dev_gemm_q4_0")
+
+    def gemm_kquant_workspace_bytes(self, tokens: int, rows: int, columns: int) -> int:
+        return int(self.lib.zen_cuda_gemm_kquant_workspace_bytes(tokens, rows, columns))
+
+    def dev_gemm_kquant(self, handle: int, d_out: int, d_x: int, tokens: int, workspace: int, workspace_bytes: int, stream: int = 0) -> None:
+        """Q4_K / Q5_K times many activation rows: codes widened to int8 in the workspace, then the tensor-core GEMM with
+        fp32 sub-block scales and the minimum term in its epilogue."""
+        if not self.lib.zen_cuda_dev_gemm_kquant(handle, d_out, d_x, tokens, workspace, workspace_bytes, stream):
+            self._fail("dev_gemm_kquant")
 
     def dev_gemm_q8_0_noalloc(self, handle: int, d_out: int, d_x: int, tokens: int, stream: int = 0) -> None:
         """The prefill product for one resident tensor without any device allocation: the quantised activations live in a

@@ -63,6 +63,9 @@ struct GemmParams {
     const __half* w_scales[kGemmMaxTensors];   // [rows][nbp]: Q8_0 block scales; Q6_K: super-block scales
     const int8_t* w_group_scales[kGemmMaxTensors];   // Q6_K only: [rows][group_pitch] int8, one per 16 weights
     uint32_t group_pitch;
+    CUtensorMap map_zs;                // kOffsets only: [nb][t_ld] fp32, (d_x / 256) * (sum of the block's two-digit activation codes)
+    const float* w_scales32[kGemmMaxTensors];   // kOffsets only: [rows][nb] fp32 block scales (d * sc) ...
+    const float* w_offsets[kGemmMaxTensors];    // ... and block offsets (dmin * m), subtracted per unit of activation sum
     float* out[kGemmMaxTensors];               // [tokens][rows]
     uint32_t rows[kGemmMaxTensors];
     uint32_t m_start[kGemmMaxTensors];         // first row tile of each tensor in the launch's row-tile numbering (0xffffffff: unused)
@@ -75,11 +78,11 @@ struct GemmParams {
 
 // A stage: weight tile | activation codes | (fine digits) | activation scales, the last rounded up so that the next
 // stage's swizzled tiles start on a 1024-byte boundary again.
-__host__ __device__ constexpr uint32_t gemm_stage_bytes(uint32_t n_tile, uint32_t digits = 1) {
-    return kGemmM * kGemmKTile + digits * n_tile * kGemmKTile + ((kGemmBlocksPerTile * n_tile * 4 + 1023u) & ~1023u);
+__host__ __device__ constexpr uint32_t gemm_stage_bytes(uint32_t n_tile, uint32_t digits = 1, bool offsets = false) {
+    return kGemmM * kGemmKTile + digits * n_tile * kGemmKTile + (offsets ? 2u : 1u) * ((kGemmBlocksPerTile * n_tile * 4 + 1023u) & ~1023u);
 }
-__host__ __device__ inline size_t gemm_smem_bytes(uint32_t n_tile, uint32_t digits = 1) {
-    return 1024 /* alignment slack */ + static_cast<size_t>(gemm_stages(n_tile)) * gemm_stage_bytes(n_tile, digits) + 512 /* barriers */;
+__host__ __device__ inline size_t gemm_smem_bytes(uint32_t n_tile, uint32_t digits = 1, bool offsets = false) {
+    return 1024 /* alignment slack */ + static_cast<size_t>(gemm_stages(n_tile)) * gemm_stage_bytes(n_tile, digits, offsets) + 512 /* barriers */;
 }
 
 // Packed fp32 pairs (sm_100 f32x2 arithmetic): one instruction scales or accumulates two token columns.
@@ -139,6 +142,20 @@ __device__ __forceinline__ void gemm_fma16_two(uint32_t (&v1)[16], const uint32_
     ZK_LDS128(s, sx_addr, 16);  gemm_fma4(v1 + 4, sw2, s, acc + 2);
     ZK_LDS128(s, sx_addr, 32);  gemm_fma4(v1 + 8, sw2, s, acc + 4);
     ZK_LDS128(s, sx_addr, 48);  gemm_fma4(v1 + 12, sw2, s, acc + 6);
+}
+
+// Sixteen token columns of the offset term of a block: acc -= offset * zs[c], zs = (d_x / 256) * (sum of the block's codes).
+__device__ __forceinline__ void gemm_off16(uint64_t neg_off2, uint32_t zs_addr, uint64_t* __restrict__ acc) {
+    uint4 z;
+    uint64_t z01, z23;
+#define ZK_OFF4(byte_off, a)                                                     \
+    ZK_LDS128(z, zs_addr, byte_off);                                             \
+    asm("mov.b64 %0, {%1, %2};" : "=l"(z01) : "r"(z.x), "r"(z.y));                \
+    asm("mov.b64 %0, {%1, %2};" : "=l"(z23) : "r"(z.z), "r"(z.w));                \
+    acc[a] = fma2(z01, neg_off2, acc[a]);                                        \
+    acc[a + 1] = fma2(z23, neg_off2, acc[a + 1]);
+    ZK_OFF4(0, 0) ZK_OFF4(16, 2) ZK_OFF4(32, 4) ZK_OFF4(48, 6)
+#undef ZK_OFF4
 }
 
 // Which tensor a row tile of the launch belongs to, and its index there.
@@ -204,10 +221,16 @@ __global__ void gemm_zero_split_tiles_kernel(const __grid_constant__ GemmParams 
 // (2 t, 2 t + 1) takes the pair of group scales (d * sc_even, d * sc_odd); a token's output is the sum of its pair.  A tile
 // of kNTile columns holds kNTile / 2 tokens; with kNTile = 32 this is the product for the two to sixteen activation rows of
 // batched decoding (the lm_head for eight sequences) as well as the reference's gemm_q6k_kblk_avx2 (kernels/avx2.cpp:1762-1770).
-template <int kNTile, int kDigits = 1, bool kQ6K = false>
+//
+// kOffsets: blocks of the form w = scale * q - offset with fp32 scale and offset per (row, 32-block): Q4_K and Q5_K with
+// their codes widened to int8 per call (scale = d * sc, offset = dmin * m; repack.cuh, unpack_k45_codes_kernel).  The
+// epilogue takes the scales from a fp32 plane and subtracts offset * zs[t, b], zs = (d_x / 256) * (sum of the block's
+// two-digit activation codes), which travels through the ring like the activation scales.
+template <int kNTile, int kDigits = 1, bool kQ6K = false, bool kOffsets = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __grid_constant__ GemmParams p) {
     static_assert(kDigits == 1 || kDigits == 2, "one or two activation digits");
     static_assert(!kQ6K || kDigits == 2, "Q6_K takes fp32-equivalent activations");
+    static_assert(!kOffsets || (kDigits == 2 && !kQ6K), "offset blocks take fp32-equivalent activations");
     constexpr int kSplit = kNTile >= 128 ? kGemmSplit : kNTile / 16;   // warps of a lane quadrant that share a tile's columns
     constexpr int kEpiActive = 4 * kSplit;                              // narrow tiles leave the other epilogue warps idle
     static_assert(kSplit >= 1 && kSplit <= kGemmSplit, "tile width");
@@ -215,9 +238,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
     static_assert(kNHalf % (kDigits == 2 ? 16 : 32) == 0, "an epilogue warp takes whole 32-column (two digits: 16-column) chunks");
     constexpr int kStages = gemm_stages(kNTile);
     constexpr uint32_t kPairs = 512 / (2 * kNTile) < 8 ? 512 / (2 * kNTile) : 8;   // TMEM accumulator buffers come in pairs (one hand-off per pair): 2 pairs of 128 columns, 8 of 32
-    constexpr uint32_t kStageBytes = gemm_stage_bytes(kNTile, kDigits);
-    constexpr uint32_t kScaleOff = kGemmM * kGemmKTile + kDigits * kNTile * kGemmKTile;   // the stage: weights | codes | (fine digits) | scales
-    constexpr uint32_t kLoadBytes = kScaleOff + kGemmBlocksPerTile * kNTile * 4;           // what the four copies of a stage deliver
+    constexpr uint32_t kStageBytes = gemm_stage_bytes(kNTile, kDigits, kOffsets);
+    constexpr uint32_t kScaleOff = kGemmM * kGemmKTile + kDigits * kNTile * kGemmKTile;   // the stage: weights | codes | (fine digits) | scales | (code sums)
+    constexpr uint32_t kZsOff = kScaleOff + ((kGemmBlocksPerTile * kNTile * 4 + 1023u) & ~1023u);
+    constexpr uint32_t kLoadBytes = kScaleOff + (kOffsets ? 2 : 1) * kGemmBlocksPerTile * kNTile * 4;   // what the copies of a stage deliver
     static_assert(kStageBytes % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
     constexpr uint32_t kTmemCols = 2 * kPairs * kNTile;  // four accumulator buffers of kNTile columns: a power of two
     static_assert(kTmemCols >= 32 && kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM allocations are powers of two from 32 to 512 columns");
@@ -249,6 +273,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
         tma_prefetch_descriptor(&p.map_x);
         if (kDigits == 2) tma_prefetch_descriptor(&p.map_x2);
         tma_prefetch_descriptor(&p.map_xs);
+        if (kOffsets) tma_prefetch_descriptor(&p.map_zs);
     }
     if (warp == 1) tmem_alloc(tmem_base_slot, kTmemCols);
     tc_fence_before_sync();
@@ -281,6 +306,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                     if (kDigits == 2)
                         tma_load_2d(st + kGemmM * kGemmKTile + kNTile * kGemmKTile, &p.map_x2, static_cast<int>(kt * kGemmKTile), static_cast<int>(nt * kNTile), &full[stage]);
                     tma_load_2d(st + kScaleOff, &p.map_xs, static_cast<int>(nt * kNTile), static_cast<int>(kt * kGemmBlocksPerTile), &full[stage]);
+                    if (kOffsets) tma_load_2d(st + kZsOff, &p.map_zs, static_cast<int>(nt * kNTile), static_cast<int>(kt * kGemmBlocksPerTile), &full[stage]);
                 }
             }
         }
@@ -349,14 +375,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
             for (int c = 0; c < kNHalf / 2; ++c) acc[c] = 0ull;
             // the four weight scales of row r per K tile (8-byte aligned: nbp is a multiple of 8), fetched one K tile ahead
             // Q6_K: a K tile is eight groups, i.e. eight int8 group scales (8-byte aligned) and half a super-block
-            const uint2* sw_row = kQ6K ? reinterpret_cast<const uint2*>(p.w_group_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.group_pitch)
-                                       : reinterpret_cast<const uint2*>(p.w_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nbp);
-            const __half* d_row = p.w_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nbp;   // Q6_K: super-block scales
-            uint2 sw_next = __ldg(sw_row + kt0);
+            // offset blocks: four fp32 scales and four fp32 offsets per K tile (16-byte aligned: nb is a multiple of 8)
+            const uint2* sw_row = kOffsets ? nullptr
+                                  : kQ6K   ? reinterpret_cast<const uint2*>(p.w_group_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.group_pitch)
+                                           : reinterpret_cast<const uint2*>(p.w_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nbp);
+            const __half* d_row = kOffsets ? nullptr : p.w_scales[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nbp;   // Q6_K: super-block scales
+            const float4* s32_row = kOffsets ? reinterpret_cast<const float4*>(p.w_scales32[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nb) : nullptr;
+            const float4* o32_row = kOffsets ? reinterpret_cast<const float4*>(p.w_offsets[ti] + static_cast<size_t>(row_ok ? r : 0) * p.nb) : nullptr;
+            uint2 sw_next = make_uint2(0u, 0u);
+            float4 s32_next = make_float4(0.f, 0.f, 0.f, 0.f), o32_next = s32_next;
+            if constexpr (kOffsets) { s32_next = __ldg(s32_row + kt0); o32_next = __ldg(o32_row + kt0); }
+            else sw_next = __ldg(sw_row + kt0);
             for (uint32_t kt = kt0; kt < kt1 && ok; ++kt, ++it) {
                 const uint32_t stage = it % kStages;
                 const uint2 sw4 = sw_next;
-                if (kt + 1 < kt1) sw_next = __ldg(sw_row + kt + 1);
+                const float4 s32 = s32_next, o32 = o32_next;
+                if (kt + 1 < kt1) {
+                    if constexpr (kOffsets) { s32_next = __ldg(s32_row + kt + 1); o32_next = __ldg(o32_row + kt + 1); }
+                    else sw_next = __ldg(sw_row + kt + 1);
+                }
                 float dq = 0.0f;
                 if constexpr (kQ6K) dq = __half2float(__ldg(d_row + (kt >> 1))) * 0.00390625f;   // the digits' common unit is d_x / 256
                 if (*abort_word || !mbar_wait(&full[stage], (it / kStages) & 1)) {
@@ -366,7 +403,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                 }
                 const uint32_t sxs = smem_u32(smem + stage * kStageBytes + kScaleOff) + half * kNHalf * 4;
                 const __half2 h01 = *reinterpret_cast<const __half2*>(&sw4.x), h23 = *reinterpret_cast<const __half2*>(&sw4.y);
-                const float swf[4] = {__low2float(h01), __high2float(h01), __low2float(h23), __high2float(h23)};
+                const float swf[4] = {kOffsets ? s32.x : __low2float(h01), kOffsets ? s32.y : __high2float(h01), kOffsets ? s32.z : __low2float(h23),
+                                      kOffsets ? s32.w : __high2float(h23)};
+                const float off[4] = {o32.x, o32.y, o32.z, o32.w};
+                const uint32_t zss = smem_u32(smem + stage * kStageBytes + kZsOff) + half * kNHalf * 4;
                 const uint32_t nblk = min(static_cast<uint32_t>(kGemmBlocksPerTile), p.nb - kt * kGemmBlocksPerTile);
                 if constexpr (kDigits == 2) {
 #pragma unroll
@@ -399,6 +439,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
                                     tmem_ld_wait();
                                     if (c + 16 == kNHalf) { tc_fence_before_sync(); __syncwarp(); if (lane == 0) mbar_arrive(&tmem_empty[pr]); }
                                     gemm_fma16_two(v1, v2, sw2, sxs + (j * kNTile + c) * 4, acc + c / 2);
+                                    if constexpr (kOffsets) gemm_off16(pack2(-off[j], -off[j]), zss + (j * kNTile + c) * 4, acc + c / 2);
                                 }
                                 ++pair;
                             }
@@ -483,8 +524,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_q8_0_i8_kernel(const __g
 // Activation quantiser for the GEMM: codes [t_pad][K] int8 (rows >= tokens are zero-filled by the caller's memset)
 // and scales in block-major order [nb][t_ld] fp32, so the scales of one block for a tile of tokens are contiguous.
 // q2 != nullptr: also the fine digits of the two-digit kernels.
+// zs_t != nullptr (offset blocks): also (d / 256) * sum over the block of (256 * q1 + q2), same layout as the scales.
 __global__ void __launch_bounds__(256) quantize_acts_gemm_kernel(const float* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ sc_t,
-                                                                 uint32_t tokens, uint32_t nb, uint32_t t_ld, int8_t* __restrict__ q2) {
+                                                                 uint32_t tokens, uint32_t nb, uint32_t t_ld, int8_t* __restrict__ q2,
+                                                                 float* __restrict__ zs_t = nullptr) {
     const size_t wid = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wid >= static_cast<size_t>(tokens) * nb) return;
@@ -494,6 +537,12 @@ __global__ void __launch_bounds__(256) quantize_acts_gemm_kernel(const float* __
     q[wid * 32 + lane] = static_cast<int8_t>(c1);
     if (q2) q2[wid * 32 + lane] = static_cast<int8_t>(c2);   // the fine digit, same layout
     if (lane == 0) sc_t[static_cast<size_t>(b) * t_ld + t] = d;
+    if (zs_t) {
+        int sum = c1 * 256 + c2;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) zs_t[static_cast<size_t>(b) * t_ld + t] = (d * 0.00390625f) * static_cast<float>(sum);
+    }
 }
 
 // The same for the Q6_K product: token t becomes rows 2 t (codes of the odd 16-weight groups zeroed) and 2 t + 1 (codes

@@ -155,4 +155,42 @@ __global__ void unpack_q4_0_codes_kernel(const uint8_t* __restrict__ nibs, int8_
     out[1] = make_uint4(sub8((w.x >> 4) & m), sub8((w.y >> 4) & m), sub8((w.z >> 4) & m), sub8((w.w >> 4) & m));
 }
 
+// Q4_K / Q5_K planes -> int8 codes (0..15, 0..31) in element order [rows][K] plus, per 32-weight sub-block, the fp32
+// factors the reference forms (kernels/avx2.cpp:329-378): scale = d * sc and offset = dmin * m, [rows][K / 32] each, so
+// that w = scale * q - offset.  One thread per 32 nibble bytes = sub-blocks 2 j (low nibbles) and 2 j + 1 (high nibbles)
+// of a super-block; the fifth bits of both are bits 2 j and 2 j + 1 of the same 32 qh bytes (src/quant.cpp:133-141).
+template <bool kQ5>
+__global__ void unpack_k45_codes_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ qh, const uint8_t* __restrict__ scm,
+                                        const uint32_t* __restrict__ dd, int8_t* __restrict__ codes, float* __restrict__ scales,
+                                        float* __restrict__ offsets, size_t rows, uint32_t nsb, uint32_t sbp) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= rows * nsb * 4) return;
+    const size_t sbi = i / 4;                       // r * nsb + b
+    const uint32_t j = static_cast<uint32_t>(i % 4);
+    const size_t r = sbi / nsb;
+    const uint32_t b = static_cast<uint32_t>(sbi % nsb);
+    const uint4* src = reinterpret_cast<const uint4*>(qs + sbi * 128 + j * 32);
+    const uint4 w[2] = {src[0], src[1]};
+    uint4 h[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    if (kQ5) {
+        const uint4* q5 = reinterpret_cast<const uint4*>(qh + sbi * 32);
+        h[0] = q5[0]; h[1] = q5[1];
+    }
+    const uint32_t m = 0x0F0F0F0Fu, one = 0x01010101u, s_lo = 2 * j, s_hi = 2 * j + 1;
+    auto lo = [&](uint32_t v, uint32_t f) { return (v & m) | (((f >> s_lo) & one) << 4); };
+    auto hi = [&](uint32_t v, uint32_t f) { return ((v >> 4) & m) | (((f >> s_hi) & one) << 4); };
+    uint4* out = reinterpret_cast<uint4*>(codes + sbi * 256 + j * 64);
+    out[0] = make_uint4(lo(w[0].x, h[0].x), lo(w[0].y, h[0].y), lo(w[0].z, h[0].z), lo(w[0].w, h[0].w));
+    out[1] = make_uint4(lo(w[1].x, h[1].x), lo(w[1].y, h[1].y), lo(w[1].z, h[1].z), lo(w[1].w, h[1].w));
+    out[2] = make_uint4(hi(w[0].x, h[0].x), hi(w[0].y, h[0].y), hi(w[0].z, h[0].z), hi(w[0].w, h[0].w));
+    out[3] = make_uint4(hi(w[1].x, h[1].x), hi(w[1].y, h[1].y), hi(w[1].z, h[1].z), hi(w[1].w, h[1].w));
+    const uint8_t* sm = scm + sbi * 16;
+    const float2 dm = __half22float2(*reinterpret_cast<const __half2*>(dd + r * sbp + b));
+    const size_t o = (r * nsb + b) * 8 + 2 * j;     // block index of sub-block 2 j within the row-major [rows][K / 32] planes
+    scales[o] = dm.x * static_cast<float>(sm[2 * j]);
+    scales[o + 1] = dm.x * static_cast<float>(sm[2 * j + 1]);
+    offsets[o] = dm.y * static_cast<float>(sm[8 + 2 * j]);
+    offsets[o + 1] = dm.y * static_cast<float>(sm[8 + 2 * j + 1]);
+}
+
 }  // namespace zk

@@ -885,21 +885,21 @@ size_t gemm_ws_bytes(size_t tokens, size_t cols, int digits = 1) {
 }
 
 // The shared-memory opt-in of the GEMM kernel; done once, at start-up (it loads the kernel's module, which may allocate).
-template <int kNTile, int kDigits = 1, bool kQ6K = false>
+template <int kNTile, int kDigits = 1, bool kQ6K = false, bool kOffsets = false>
 cudaError_t configure_gemm() {
     static bool configured = false;
     if (configured) return cudaSuccess;
-    const cudaError_t e = cudaFuncSetAttribute(&zk::gemm_q8_0_i8_kernel<kNTile, kDigits, kQ6K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               static_cast<int>(zk::gemm_smem_bytes(kNTile, kDigits)));
+    const cudaError_t e = cudaFuncSetAttribute(&zk::gemm_q8_0_i8_kernel<kNTile, kDigits, kQ6K, kOffsets>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               static_cast<int>(zk::gemm_smem_bytes(kNTile, kDigits, kOffsets)));
     if (e == cudaSuccess) configured = true;
     return e;
 }
 
-template <int kNTile, int kDigits = 1, bool kQ6K = false>
+template <int kNTile, int kDigits = 1, bool kQ6K = false, bool kOffsets = false>
 cudaError_t launch_gemm(const zk::GemmParams& p, unsigned grid, cudaStream_t st) {
-    const cudaError_t e = configure_gemm<kNTile, kDigits, kQ6K>();
+    const cudaError_t e = configure_gemm<kNTile, kDigits, kQ6K, kOffsets>();
     if (e != cudaSuccess) return e;
-    zk::gemm_q8_0_i8_kernel<kNTile, kDigits, kQ6K><<<grid, zk::kGemmThreads, zk::gemm_smem_bytes(kNTile, kDigits), st>>>(p);
+    zk::gemm_q8_0_i8_kernel<kNTile, kDigits, kQ6K, kOffsets><<<grid, zk::kGemmThreads, zk::gemm_smem_bytes(kNTile, kDigits, kOffsets), st>>>(p);
     return cudaGetLastError();
 }
 
@@ -1053,6 +1053,81 @@ bool enqueue_gemm_q4_0(State& s, const zen_cuda_weights* w, float* d_out, const 
     const zen_cuda_weights* wp[1] = {&as_q8};
     float* outs[1] = {d_out};
     return enqueue_gemm_q8_0(s, wp, outs, 1, d_x, tokens, ws + ((w->rows * w->cols + 255) & ~size_t(255)), st, ZEN_CUDA_ACT_FP32);
+}
+
+// Q4_K / Q5_K times many activation rows: codes widened to int8 in scratch memory together with the fp32 scale and offset
+// of every 32-weight sub-block (w = scale * q - offset), then the tensor-core GEMM with two activation digits whose
+// epilogue also subtracts offset x (activation sum of the block).  Workspace: codes | scales | offsets | GEMM workspace |
+// block-major activation sums.
+constexpr size_t kK45TensorMinTokens = 12;
+size_t align256(size_t n) { return (n + 255) & ~size_t(255); }
+size_t gemm_k45_ws_bytes(size_t tokens, size_t rows, size_t cols) {
+    const size_t t_ld = (tokens + 3) & ~size_t(3);
+    return align256(rows * cols) + 2 * align256(rows * (cols / 32) * sizeof(float)) + align256(gemm_ws_bytes(tokens, cols, 2)) + (cols / 32) * t_ld * sizeof(float);
+}
+
+bool enqueue_gemm_k45(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, cudaStream_t st) {
+    if (!w || !d_out || !d_x || !ws || !tokens) return set_error(s, "gemm k-quant: bad arguments");
+    const bool q5 = w->format == ZEN_CUDA_Q5_K;
+    if (!q5 && w->format != ZEN_CUDA_Q4_K) return set_error(s, "gemm k-quant: not a Q4_K or Q5_K tensor");
+    const size_t rows = w->rows, cols = w->cols;
+    const uint32_t nsb = w->nb, nb = static_cast<uint32_t>(cols / 32);
+    int8_t* codes = reinterpret_cast<int8_t*>(ws);
+    float* scales = reinterpret_cast<float*>(ws + align256(rows * cols));
+    float* offsets = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scales) + align256(rows * nb * sizeof(float)));
+    uint8_t* gws = reinterpret_cast<uint8_t*>(offsets) + align256(rows * nb * sizeof(float));
+    float* zs_t = reinterpret_cast<float*>(gws + align256(gemm_ws_bytes(tokens, cols, 2)));
+    const size_t threads = rows * nsb * 4;
+    const unsigned ugrid = static_cast<unsigned>((threads + 255) / 256);
+    if (q5)
+        zk::unpack_k45_codes_kernel<true><<<ugrid, 256, 0, st>>>(static_cast<const uint8_t*>(w->plane[0]), static_cast<const uint8_t*>(w->plane[1]),
+                                                                 static_cast<const uint8_t*>(w->plane[2]), static_cast<const uint32_t*>(w->plane[3]), codes,
+                                                                 scales, offsets, rows, nsb, w->nbp);
+    else
+        zk::unpack_k45_codes_kernel<false><<<ugrid, 256, 0, st>>>(static_cast<const uint8_t*>(w->plane[0]), nullptr, static_cast<const uint8_t*>(w->plane[1]),
+                                                                  static_cast<const uint32_t*>(w->plane[2]), codes, scales, offsets, rows, nsb, w->nbp);
+    if (cudaGetLastError() != cudaSuccess) return set_error(s, "gemm k-quant: unpack launch failed");
+    ++s.stats.dispatches;
+    const size_t t_ld = (tokens + 3) & ~size_t(3);
+    int8_t* xq = reinterpret_cast<int8_t*>(gws);
+    float* xs_t = reinterpret_cast<float*>(gws + ((tokens * cols + 255) & ~size_t(255)));
+    int8_t* xq2 = reinterpret_cast<int8_t*>(gws + ((gemm_ws_bytes(tokens, cols, 1) + 255) & ~size_t(255)));
+    const size_t nblk = tokens * nb;
+    zk::quantize_acts_gemm_kernel<<<static_cast<unsigned>((nblk + 7) / 8), 256, 0, st>>>(d_x, xq, xs_t, static_cast<uint32_t>(tokens), nb,
+                                                                                      static_cast<uint32_t>(t_ld), xq2, zs_t);
+    if (cudaGetLastError() != cudaSuccess) return set_error(s, "gemm k-quant: quantise launch failed");
+    ++s.stats.dispatches;
+    const uint32_t n_tile = 128u;
+    zk::GemmParams p{};
+    p.m_start[0] = 0; p.m_start[1] = p.m_start[2] = 0xffffffffu;
+    if (!make_map_2d(s, &p.map_w[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, codes, cols, rows, cols, zk::kGemmKTile, zk::kGemmM, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if (!make_map_2d(s, &p.map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, cols, tokens, cols, zk::kGemmKTile, n_tile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if (!make_map_2d(s, &p.map_x2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq2, cols, tokens, cols, zk::kGemmKTile, n_tile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+    if (!make_map_2d(s, &p.map_xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, xs_t, t_ld, nb, t_ld * sizeof(float), n_tile, zk::kGemmBlocksPerTile, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+    if (!make_map_2d(s, &p.map_zs, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, zs_t, t_ld, nb, t_ld * sizeof(float), n_tile, zk::kGemmBlocksPerTile, CU_TENSOR_MAP_SWIZZLE_NONE)) return false;
+    p.w_scales32[0] = scales;
+    p.w_offsets[0] = offsets;
+    p.out[0] = d_out;
+    p.rows[0] = static_cast<uint32_t>(rows);
+    p.tensors = 1;
+    p.tokens = static_cast<uint32_t>(tokens);
+    p.nb = nb;
+    p.nbp = nb;
+    p.n_tile = n_tile;
+    p.m_tiles = (p.rows[0] + zk::kGemmM - 1) / zk::kGemmM;
+    p.n_tiles = (p.tokens + n_tile - 1) / n_tile;
+    p.error_word = s.d_error;
+    const unsigned tiles = p.m_tiles * p.n_tiles, ktiles = nb / zk::kGemmBlocksPerTile;
+    const unsigned grid = std::min<unsigned>(tiles, static_cast<unsigned>(s.sm_count));
+    p.stream_k = (s.gemm_stream_k && tiles % grid != 0 && static_cast<uint64_t>(tiles) * ktiles / grid >= ktiles) ? 1u : 0u;
+    if (p.stream_k) {
+        zk::gemm_zero_split_tiles_kernel<<<grid, 256, 0, st>>>(p, ktiles);
+        ++s.stats.dispatches;
+    }
+    const cudaError_t e = launch_gemm<128, 2, false, true>(p, grid, st);
+    if (e != cudaSuccess) return set_error(s, std::string("gemm k-quant launch: ") + cudaGetErrorString(e));
+    ++s.stats.dispatches;
+    return true;
 }
 
 // Scratch of the allocation-free GEMM entry point: part of the library image, one copy per GPU that loads it.
@@ -1282,7 +1357,8 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
     bool q6k_tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q6_K && tokens >= kQ6kTensorMinTokens;
     for (size_t i = 0; i < count; ++i) q6k_tensor_path = q6k_tensor_path && w[i]->kernel_format == zk::kFormatQ6KCodes;   // the file's planes: decode kernel
     const bool q4_tensor_path = s.use_gemm && fmt == ZEN_CUDA_Q4_0 && tokens >= kQ4TensorMinTokens && cols % 128 == 0;
-    const bool tensor_path = q6k_tensor_path || q4_tensor_path || (s.use_gemm && fmt == ZEN_CUDA_Q8_0 && tokens > 8);   // Q8_0: either activation mode
+    const bool k45_tensor_path = s.use_gemm && (fmt == ZEN_CUDA_Q4_K || fmt == ZEN_CUDA_Q5_K) && tokens >= kK45TensorMinTokens;
+    const bool tensor_path = q6k_tensor_path || q4_tensor_path || k45_tensor_path || (s.use_gemm && fmt == ZEN_CUDA_Q8_0 && tokens > 8);   // Q8_0: either activation mode
     const bool fetch_by_kernel = direct && x_bytes <= kDirectInputBytes;
 
     // The three launches of a small call (fetch the activations, the product, copy the result out and publish it).
@@ -1370,7 +1446,13 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
         }
         s.stats.transfer_us += us_since(t0);
         t0 = clock_type::now();
-        if (tensor_path && fmt == ZEN_CUDA_Q4_0) {
+        if (tensor_path && (fmt == ZEN_CUDA_Q4_K || fmt == ZEN_CUDA_Q5_K)) {
+            size_t need = 0;
+            for (size_t i = 0; i < count; ++i) need = std::max(need, gemm_k45_ws_bytes(tokens, rows[i], cols));
+            if (!ensure_gemm_ws(s, need)) return false;
+            for (size_t i = 0; i < count; ++i)
+                if (!enqueue_gemm_k45(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
+        } else if (tensor_path && fmt == ZEN_CUDA_Q4_0) {
             size_t need = 0;
             for (size_t i = 0; i < count; ++i) need = std::max(need, gemm_q4_0_ws_bytes(tokens, rows[i], cols));
             if (!ensure_gemm_ws(s, need)) return false;
@@ -1875,6 +1957,19 @@ int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out
 size_t zen_cuda_gemm_q6_k_workspace_bytes(size_t tokens, size_t columns) { return gemm_q6k_ws_bytes(tokens, columns); }
 
 size_t zen_cuda_gemm_q4_0_workspace_bytes(size_t tokens, size_t rows, size_t columns) { return gemm_q4_0_ws_bytes(tokens, rows, columns); }
+
+size_t zen_cuda_gemm_kquant_workspace_bytes(size_t tokens, size_t rows, size_t columns) { return gemm_k45_ws_bytes(tokens, rows, columns); }
+
+int zen_cuda_dev_gemm_kquant(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return 0;
+    if (!w || !d_out || !d_x || !tokens) return set_error(s, "dev_gemm_kquant: bad arguments") ? 1 : 0;
+    if (w->format != ZEN_CUDA_Q4_K && w->format != ZEN_CUDA_Q5_K) return set_error(s, "dev_gemm_kquant: a Q4_K or Q5_K tensor") ? 1 : 0;
+    if (workspace_bytes < gemm_k45_ws_bytes(tokens, w->rows, w->cols)) return set_error(s, "dev_gemm_kquant: workspace too small") ? 1 : 0;
+    return enqueue_gemm_k45(s, w, d_out, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
+}
 
 int zen_cuda_dev_gemm_q4_0(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace, size_t workspace_bytes,
                            void* stream) {
