@@ -639,6 +639,98 @@ def lm_head_shard(first: int, last: int, dev=None) -> np.ndarray:
     return np.ascontiguousarray(np.concatenate(out, axis=0))
 
 
+def run_gemm_formats(args) -> dict:
+    """The config 1 shape (512 x 14336 x 4096) for every format's many-row product, next to the same rows in chunks of
+    eight through the decode kernel: Q8_0 with fp32-equivalent activations, Q4_0, Q6_K, Q4_K and Q5_K (the reference
+    multiplies these with fp32 activations).  Per format GEMM_COPIES weight copies take turns (larger than L2 together
+    with the outputs); a timed step is one product.  One GPU."""
+    import torch
+    from zeninfer_b200 import Backend, blocks
+    from zeninfer_b200.backend import ACT_FP32
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1 or args.gpus != 1:
+        raise SystemExit("workload gemm_formats is a single-GPU workload")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    be = Backend()
+    T, R, K = GEMM_T, GEMM_ROWS, GEMM_COLS
+    tokens_list = [T] if args.profile else [16, 128, T]
+    d_x = torch.from_numpy(np.random.default_rng(2).standard_normal((T, K), dtype=np.float32)).to(dev)
+    stream = torch.cuda.Stream(device=dev)
+    S = stream.cuda_stream
+    detail = {}
+    wanted = [f for f in args.formats.split(",") if f]
+    with ClockSampler(0) as clocks:
+        clocks.mark_start()
+        for name in wanted:
+            if name == "Q8_0":
+                w = np.random.default_rng(3).standard_normal((R, K), dtype=np.float32) * np.float32(0.02)
+                packed = np.ascontiguousarray(blocks.quantize_q8_0(w))
+            elif name == "Q4_0":
+                w = np.random.default_rng(3).standard_normal((R, K), dtype=np.float32) * np.float32(0.02)
+                packed = np.ascontiguousarray(blocks.quantize_q4_0(w))
+            elif name == "Q6_K":
+                packed = lm_head_shard(0, R, dev)
+            else:
+                packed = blocks.random_k_blocks(blocks.Q4_K if name == "Q4_K" else blocks.Q5_K, R, K, 3)
+            copies = 2 if args.profile else GEMM_COPIES
+            handles = [be.dev_upload(name, packed, R, K) for _ in range(copies)]
+            y = torch.empty((T, R), dtype=torch.float32, device=dev)
+            ws_bytes = max(be.gemm_workspace_bytes(T, K, ACT_FP32), be.gemm_q6_k_workspace_bytes(T, K), be.gemm_q4_0_workspace_bytes(T, R, K),
+                           be.gemm_kquant_workspace_bytes(T, R, K))
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+
+            def tensor(h, n):
+                if name == "Q8_0":
+                    be.dev_gemm_q8_0([h], [y.data_ptr()], d_x.data_ptr(), n, ws.data_ptr(), ws_bytes, S, act_mode=ACT_FP32)
+                elif name == "Q4_0":
+                    be.dev_gemm_q4_0(h, y.data_ptr(), d_x.data_ptr(), n, ws.data_ptr(), ws_bytes, S)
+                elif name == "Q6_K":
+                    be.dev_gemm_q6_k(h, y.data_ptr(), d_x.data_ptr(), n, ws.data_ptr(), ws_bytes, S)
+                else:
+                    be.dev_gemm_kquant(h, y.data_ptr(), d_x.data_ptr(), n, ws.data_ptr(), ws_bytes, S)
+
+            def chunks(h, n):
+                for t0 in range(0, n, 8):
+                    be.dev_gemv([h], [y[t0:].data_ptr()], d_x[t0:].data_ptr(), min(8, n - t0), ACT_FP32, S)
+
+            rows_out = {}
+            for n in tokens_list:
+                for label, fn in (("tensor_cores", tensor), ("decode_kernel_chunks_of_8", chunks)):
+                    if args.profile and label != "tensor_cores":
+                        continue
+                    with torch.cuda.stream(stream):
+                        fn(handles[0], n)
+                        stream.synchronize()
+                        graph = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(graph, stream=stream):
+                            for h in handles:
+                                fn(h, n)
+                        for _ in range(1 if args.profile else 3):
+                            graph.replay()
+                        stream.synchronize()
+                        reps = 1 if args.profile else 5
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(stream)
+                        for _ in range(reps):
+                            graph.replay()
+                        e1.record(stream)
+                        stream.synchronize()
+                    us = e0.elapsed_time(e1) * 1e3 / (reps * len(handles))
+                    rows_out.setdefault(str(n), {})[label] = {"us": us, "tops": 2.0 * n * R * K / us / 1e6}
+            be.dev_check(S)
+            detail[name] = rows_out
+            for h in handles:
+                be.dev_free(h)
+            del ws, y
+        clocks.mark_end()
+    first = detail[wanted[0]][str(T)]["tensor_cores"]
+    return {"metric": "many_row_product_tops_by_format", "value": first["tops"], "unit": "TOPS", "n_gpus": 1, "higher_is_better": True, "dtype": "s8 x s8 -> s32, fp32 scales",
+            "data": "synthetic", "profile_run": args.profile,
+            "config": {"workload": f"{T} x {R} x {K} (the config 1 shape) by weight format, fp32-equivalent activations (two int8 digits); also 16 and 128 rows",
+                       "value_is": f"{wanted[0]} at {T} rows"},
+            "detail": detail, "clocks": clocks.summary(), "vs_baseline": None}
+
+
 def run_lm_head(args, brief: bool = False) -> dict | None:
     """Q6_K lm_head 128256 x 4096 at batch 1 (value) and batch 8, rows sharded over the ranks.  A step on every rank: the
     shard product with the all-gather fused in (or followed by an NCCL all-gather), then the greedy pick over the
@@ -1248,7 +1340,7 @@ def main() -> None:
                     help="a short form of the workload for a profiler capture: one untimed pass, one captured-graph replay as warm-up and one "
                          "as the timed step, no end-to-end leg, no CPU baseline, no detail (its figures are not benchmark values)")
     ap.add_argument("--layers", type=int, default=0, help="workload decode: number of layers (default: the configuration's 32)")
-    ap.add_argument("--formats", default="Q8_0,Q4_0,Q6_K,Q4_K,Q5_K", help="workload layer_sweep: formats to run")
+    ap.add_argument("--formats", default="Q8_0,Q4_0,Q6_K,Q4_K,Q5_K", help="workloads layer_sweep and gemm_formats: formats to run")
     ap.add_argument("--act", default="int8", choices=["int8", "fp32"], help="workload q8_0_gemm: activation mode of the timed product (the other one is timed briefly beside it)")
     ap.add_argument("--no-list", action="store_true", help="default workload: skip the persistent list launch among the config 0 submission variants")
     ap.add_argument("--no-q6k-tensor", action="store_true", help="workload lm_head: batch 8 through the decode kernel (dp4a) instead of the tensor-core product")
@@ -1273,7 +1365,7 @@ def main() -> None:
         run_reference_arm(args)
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    runners = {"q8_0_gemm": run_gemm_workload, "layer_sweep": run_layer_sweep, "lm_head": run_lm_head, "decode": run_decode}
+    runners = {"q8_0_gemm": run_gemm_workload, "layer_sweep": run_layer_sweep, "lm_head": run_lm_head, "decode": run_decode, "gemm_formats": run_gemm_formats}
     if args.workload in runners:
         line = runners[args.workload](args)
     elif args.workload == "q8_0_gemv":
