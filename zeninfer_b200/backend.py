@@ -32,7 +32,7 @@ ABI_SYMBOLS = (
     "zen_cuda_last_error", "zen_cuda_set_q8_act_mode", "zen_cuda_get_q8_act_mode",
     "zen_cuda_gemv_q8_0", "zen_cuda_gemm_q8_0", "zen_cuda_gemv_q8_0_batch", "zen_cuda_gemm_q8_0_batch",
     "zen_cuda_gemm_q6_k", "zen_cuda_gemm_q4_0", "zen_cuda_gemm_kquant", "zen_cuda_release_weights", "zen_cuda_quantize_acts",
-    "zen_cuda_rms_norm", "zen_cuda_gemv_q8_0_ffn", "zen_cuda_set_vram_budget", "zen_cuda_residency", "zen_cuda_set_q6k_codes",
+    "zen_cuda_rms_norm", "zen_cuda_gemv_q8_0_ffn", "zen_cuda_set_vram_budget", "zen_cuda_residency", "zen_cuda_set_q6k_codes", "zen_cuda_set_gemm_groups",
     "zen_cuda_dev_upload", "zen_cuda_dev_free", "zen_cuda_dev_weight_bytes", "zen_cuda_dev_gemv",
     "zen_cuda_dev_quantize_acts", "zen_cuda_dev_check", "zen_cuda_error_name", "zen_cuda_set_wait_budget_ms",
     "zen_cuda_gemv_list_create", "zen_cuda_gemv_list_destroy", "zen_cuda_gemv_list_bytes", "zen_cuda_dev_gemv_list",
@@ -304,6 +304,14 @@ class Backend:
         before = self.lib.zen_cuda_set_q6k_codes(int(bool(on)))
         if before < 0:
             self._fail("set_q6k_codes")
+        return bool(before)
+
+    def set_gemm_groups(self, on: bool) -> bool:
+        """Q8_0 many-row products through the group-scale kernel (True, the default) or the per-block kernel.  Returns the
+        previous setting."""
+        before = self.lib.zen_cuda_set_gemm_groups(int(bool(on)))
+        if before < 0:
+            self._fail("set_gemm_groups")
         return bool(before)
 
     def set_vram_budget(self, nbytes: int) -> None:

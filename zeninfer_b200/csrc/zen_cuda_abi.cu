@@ -27,6 +27,7 @@
 
 #include "decode_ops.cuh"
 #include "gemm_q8_0_i8.cuh"
+#include "gemm_groups.cuh"
 #include "gemv_kq.cuh"
 #include "gemv_list.cuh"
 #include "gemv_q8_0.cuh"
@@ -56,6 +57,12 @@ struct zen_cuda_weights {
     void* plane[4]{};         // format-specific planes (see repack.cuh)
     void* d_tile_maps{};      // Q8_0 rows of several K segments: zk::GemvTileMaps in device memory (see make_tile_maps), else null
     int kernel_format{};      // what the decode kernel is instantiated for: the format, or zk::kFormatQ6KCodes for Q6_K with unpacked codes
+    // Two-digit planes under one scale per 256 weights (gemm_groups.cuh), built at the tensor's first many-row product and
+    // kept: wh, wl [rows][cols] int8, units [rows][cols / 256] fp32.
+    mutable void* g_hi{};
+    mutable void* g_lo{};
+    mutable float* g_unit{};
+    mutable size_t g_bytes{};
     size_t device_bytes{};
     size_t raw_bytes{};
 };
@@ -111,6 +118,7 @@ struct State {
     bool warm_hints{true};    // honour zen_cuda_gemv_fusion.warm_next (ZEN_CUDA_WARM=0 ignores the hints)
     bool gemm_stream_k{true}; // prefill GEMM: even K-tile shares when tiles do not divide the SMs (ZEN_CUDA_GEMM_STREAMK=0 turns it off)
     bool use_gemm{true};     // tensor-core prefill path (ZEN_CUDA_GEMM=0 falls back to chunks of eight tokens on the decode kernel)
+    bool gemm_groups{true};  // Q8_0 many-row products through the group-scale kernel (ZEN_CUDA_GEMM_GROUPS=0: the per-block kernel)
     void* encode_tiled{};    // cuTensorMapEncodeTiled, resolved through the runtime
     int* h_error{};   // mapped pinned word the kernels write on a bounded-wait timeout
     int* d_error{};   // device alias of h_error
@@ -212,6 +220,7 @@ bool init_locked(State& s) {
     }
     if (const char* m = std::getenv("ZEN_CUDA_PDL")) s.pdl = m[0] != '0';
     if (const char* m = std::getenv("ZEN_CUDA_GEMM")) s.use_gemm = m[0] != '0';
+    if (const char* m = std::getenv("ZEN_CUDA_GEMM_GROUPS")) s.gemm_groups = m[0] != '0';
     if (const char* m = std::getenv("ZEN_CUDA_GEMM_STREAMK")) s.gemm_stream_k = m[0] != '0';
     if (const char* m = std::getenv("ZEN_CUDA_WARM")) s.warm_hints = m[0] != '0';
     if (const char* m = std::getenv("ZEN_CUDA_HOST_GRAPHS")) s.use_host_graphs = m[0] != '0';
@@ -241,7 +250,10 @@ void free_weights(State& s, zen_cuda_weights* w) {
     if (!w) return;
     for (void* p : w->plane) if (p) cudaFree(p);
     if (w->d_tile_maps) cudaFree(w->d_tile_maps);
-    s.stats.weight_bytes -= std::min<uint64_t>(s.stats.weight_bytes, w->device_bytes);
+    if (w->g_hi) cudaFree(w->g_hi);
+    if (w->g_lo) cudaFree(w->g_lo);
+    if (w->g_unit) cudaFree(w->g_unit);
+    s.stats.weight_bytes -= std::min<uint64_t>(s.stats.weight_bytes, w->device_bytes + w->g_bytes);
     delete w;
 }
 
@@ -903,13 +915,132 @@ cudaError_t launch_gemm(const zk::GemmParams& p, unsigned grid, cudaStream_t st)
     return cudaGetLastError();
 }
 
+// ---- the group-scale kernel (gemm_groups.cuh) ---------------------------------------------------------------------------
+// Workspace: xh | xl ([tokens][cols] int8 each, padded to 256 bytes) | activation units [cols / 256][t_ld] fp32, t_ld =
+// tokens rounded up to whole 128-column tiles.
+size_t gemm_groups_ws_bytes(size_t tokens, size_t cols) {
+    const size_t t_ld = (tokens + zk::kGgNTile - 1) / zk::kGgNTile * zk::kGgNTile;
+    return 2 * ((tokens * cols + 255) & ~size_t(255)) + (cols / zk::kGgGroup) * t_ld * sizeof(float);
+}
+
+// Makes sure the tensor's two-digit planes exist.  They are built once, on `st`, and the call returns after the build has
+// run (other streams may use them at once).  False without an error: not now (the stream is being captured, or memory is
+// short) -- the caller takes the per-block kernel.
+bool ensure_group_digits(State& s, const zen_cuda_weights* w, cudaStream_t st) {
+    if (w->g_hi) return true;
+    if (w->format != ZEN_CUDA_Q8_0 || w->cols % zk::kGgGroup) return false;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return false;
+    const size_t n = w->rows * w->cols, groups = w->cols / zk::kGgGroup;
+    void *hi = nullptr, *lo = nullptr;
+    float* unit = nullptr;
+    if (cudaMalloc(&hi, n) != cudaSuccess || cudaMalloc(&lo, n) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&unit), w->rows * groups * sizeof(float)) != cudaSuccess) {
+        cudaGetLastError();
+        if (hi) cudaFree(hi);
+        if (lo) cudaFree(lo);
+        if (unit) cudaFree(unit);
+        return false;
+    }
+    const size_t warps = w->rows * groups;
+    zk::group_digits_q8_0_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(static_cast<const int8_t*>(w->plane[0]), static_cast<const __half*>(w->plane[1]),
+                                                                                        w->nbp, static_cast<int8_t*>(hi), static_cast<int8_t*>(lo), unit, w->rows,
+                                                                                        static_cast<uint32_t>(w->cols));
+    const bool ok = cudaGetLastError() == cudaSuccess && cudaStreamSynchronize(st) == cudaSuccess;
+    ++s.stats.dispatches;
+    if (!ok) { cudaFree(hi); cudaFree(lo); cudaFree(unit); return false; }
+    w->g_hi = hi; w->g_lo = lo; w->g_unit = unit;
+    w->g_bytes = 2 * n + w->rows * groups * sizeof(float);
+    s.stats.weight_bytes += w->g_bytes;
+    return true;
+}
+
+cudaError_t configure_gemm_groups() {
+    static bool configured = false;
+    if (configured) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(&zk::gemm_groups_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(zk::gemm_groups_smem_bytes()));
+    if (e == cudaSuccess) configured = true;
+    return e;
+}
+
+// All tensors have their two-digit planes (ensure_group_digits) and share the columns; `ws` holds gemm_groups_ws_bytes.
+bool enqueue_gemm_groups(State& s, const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x, size_t tokens, uint8_t* ws,
+                         cudaStream_t st, int act_mode) {
+    const size_t cols = w[0]->cols;
+    const uint32_t groups = static_cast<uint32_t>(cols / zk::kGgGroup);
+    const uint32_t n_tiles = static_cast<uint32_t>((tokens + zk::kGgNTile - 1) / zk::kGgNTile), t_ld = n_tiles * zk::kGgNTile;
+    const size_t plane = (tokens * cols + 255) & ~size_t(255);
+    int8_t* xh = reinterpret_cast<int8_t*>(ws);
+    int8_t* xl = reinterpret_cast<int8_t*>(ws + plane);
+    float* x_unit = reinterpret_cast<float*>(ws + 2 * plane);
+    if (tokens % zk::kGgNTile)      // the columns past the last token carry a zero unit
+        if (cudaMemsetAsync(x_unit, 0, static_cast<size_t>(groups) * t_ld * sizeof(float), st) != cudaSuccess) return set_error(s, "gemm: clearing the activation units failed");
+    const size_t warps = tokens * groups;
+    zk::group_digits_acts_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(d_x, xh, xl, x_unit, static_cast<uint32_t>(tokens), static_cast<uint32_t>(cols),
+                                                                                        t_ld, act_mode == ZEN_CUDA_ACT_INT8 ? 1 : 0);
+    if (cudaGetLastError() != cudaSuccess) return set_error(s, "gemm: activation digits launch failed");
+    ++s.stats.dispatches;
+    if (configure_gemm_groups() != cudaSuccess) return set_error(s, "gemm: shared-memory opt-in failed");
+    for (size_t i0 = 0; i0 < count; i0 += zk::kGemmMaxTensors) {
+        const size_t n = std::min<size_t>(zk::kGemmMaxTensors, count - i0);
+        zk::GroupGemmParams p{};
+        uint32_t m_tiles = 0;
+        for (size_t j = 0; j < static_cast<size_t>(zk::kGemmMaxTensors); ++j) {
+            if (j >= n) { p.m_start[j] = 0xffffffffu; continue; }
+            const zen_cuda_weights* wt = w[i0 + j];
+            if (!make_map_2d(s, &p.map_wh[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wt->g_hi, cols, wt->rows, cols, zk::kGemmKTile, zk::kGemmM, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+            if (!make_map_2d(s, &p.map_wl[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, wt->g_lo, cols, wt->rows, cols, zk::kGemmKTile, zk::kGemmM, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+            p.w_unit[j] = wt->g_unit;
+            p.out[j] = d_out[i0 + j];
+            p.rows[j] = static_cast<uint32_t>(wt->rows);
+            p.m_start[j] = m_tiles;
+            m_tiles += (p.rows[j] + zk::kGemmM - 1) / zk::kGemmM;
+        }
+        if (!make_map_2d(s, &p.map_xh, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xh, cols, tokens, cols, zk::kGemmKTile, zk::kGgNTile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+        if (!make_map_2d(s, &p.map_xl, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xl, cols, tokens, cols, zk::kGemmKTile, zk::kGgNTile, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+        p.x_unit = x_unit;
+        p.tensors = static_cast<uint32_t>(n);
+        p.tokens = static_cast<uint32_t>(tokens);
+        p.groups = groups;
+        p.t_ld = t_ld;
+        p.m_tiles = m_tiles;
+        p.n_tiles = n_tiles;
+        p.error_word = s.d_error;
+        const unsigned tiles = p.m_tiles * p.n_tiles;
+        const unsigned grid = std::min<unsigned>(tiles, static_cast<unsigned>(s.sm_count));
+        p.stream_k = (s.gemm_stream_k && tiles % grid != 0 && static_cast<uint64_t>(tiles) * groups / grid >= groups) ? 1u : 0u;
+        if (p.stream_k) {
+            zk::gg_zero_split_tiles_kernel<<<grid, 256, 0, st>>>(p);
+            ++s.stats.dispatches;
+        }
+        zk::gemm_groups_kernel<<<grid, zk::kGgThreads, zk::gemm_groups_smem_bytes(), st>>>(p);
+        if (cudaGetLastError() != cudaSuccess) return set_error(s, std::string("gemm launch: ") + cudaGetErrorString(cudaGetLastError()));
+        ++s.stats.dispatches;
+    }
+    return true;
+}
+
+// What a caller's workspace must hold for either kernel.
+size_t gemm_ws_bytes_any(const State& s, size_t tokens, size_t cols, int act_mode) {
+    const size_t per_block = gemm_ws_bytes(tokens, cols, act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1);
+    return s.gemm_groups && cols % zk::kGgGroup == 0 ? std::max(per_block, gemm_groups_ws_bytes(tokens, cols)) : per_block;
+}
+
 // Quantises d_x [tokens][cols] into the workspace `ws` (gemm_ws_bytes) and enqueues one GEMM per tensor.
 // Everything is stream-ordered on `st`; `ws` must stay untouched until the work has run.  act_mode ZEN_CUDA_ACT_FP32:
 // two activation digits (the workspace is the larger one, gemm_ws_bytes(..., 2)).
+// ws_bytes: what `ws` holds; with room for gemm_groups_ws_bytes, whole 256-weight groups and every tensor's two-digit planes
+// at hand the product goes through the group-scale kernel, otherwise through the per-block kernel below.
 bool enqueue_gemm_q8_0(State& s, const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x, size_t tokens,
-                       uint8_t* ws, cudaStream_t st, int act_mode = ZEN_CUDA_ACT_INT8) {
+                       uint8_t* ws, cudaStream_t st, int act_mode = ZEN_CUDA_ACT_INT8, size_t ws_bytes = 0) {
     if (!count || !tokens || !d_x || !ws) return set_error(s, "gemm: bad arguments");
     if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "gemm: bad activation mode");
+    if (s.gemm_groups && w[0] && w[0]->cols % zk::kGgGroup == 0 && ws_bytes >= gemm_groups_ws_bytes(tokens, w[0]->cols)) {
+        bool all = true;
+        for (size_t i = 0; i < count && all; ++i)
+            all = w[i] && d_out[i] && w[i]->format == ZEN_CUDA_Q8_0 && w[i]->cols == w[0]->cols && ensure_group_digits(s, w[i], st);
+        if (all) return enqueue_gemm_groups(s, w, d_out, count, d_x, tokens, ws, st, act_mode);
+    }
     const int digits = act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1;
     const size_t cols = w[0]->cols;
     const uint32_t nb = w[0]->nb;
@@ -1463,8 +1594,8 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
             for (size_t i = 0; i < count; ++i)    // stream-ordered: the tensors share the workspace one after the other
                 if (!enqueue_gemm_q6k(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
         } else if (tensor_path) {
-            if (!ensure_gemm_ws(s, gemm_ws_bytes(tokens, cols, act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1))) return false;
-            if (!enqueue_gemm_q8_0(s, w, d_out, count, s.d_x, tokens, s.d_gemm_ws, s.stream, act_mode)) return false;
+            if (!ensure_gemm_ws(s, gemm_ws_bytes_any(s, tokens, cols, act_mode))) return false;
+            if (!enqueue_gemm_q8_0(s, w, d_out, count, s.d_x, tokens, s.d_gemm_ws, s.stream, act_mode, s.d_gemm_ws_bytes)) return false;
         }
         for (size_t t0k = 0; !tensor_path && t0k < tokens; t0k += chunk) {
             const size_t nt = std::min<size_t>(chunk, tokens - t0k);
@@ -1792,6 +1923,15 @@ int zen_cuda_set_q6k_codes(int on) {
     return before;
 }
 
+int zen_cuda_set_gemm_groups(int on) {
+    State& s = state();
+    std::lock_guard<std::mutex> lock(s.mutex);
+    if (!init_locked(s)) return -1;
+    const int before = s.gemm_groups ? 1 : 0;
+    s.gemm_groups = on != 0;
+    return before;
+}
+
 int zen_cuda_set_vram_budget(uint64_t bytes) {
     State& s = state();
     std::lock_guard<std::mutex> lock(s.mutex);
@@ -1926,10 +2066,8 @@ int zen_cuda_dev_gemv_list(const zen_cuda_gemv_list* list, void* stream) {
     return 1;
 }
 
-size_t zen_cuda_gemm_workspace_bytes(size_t tokens, size_t columns) { return gemm_ws_bytes(tokens, columns); }
-size_t zen_cuda_gemm_workspace_bytes_act(size_t tokens, size_t columns, int act_mode) {
-    return gemm_ws_bytes(tokens, columns, act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1);
-}
+size_t zen_cuda_gemm_workspace_bytes(size_t tokens, size_t columns) { return gemm_ws_bytes_any(state(), tokens, columns, ZEN_CUDA_ACT_INT8); }
+size_t zen_cuda_gemm_workspace_bytes_act(size_t tokens, size_t columns, int act_mode) { return gemm_ws_bytes_any(state(), tokens, columns, act_mode); }
 
 int zen_cuda_dev_gemm_q8_0_act(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x, size_t tokens, int act_mode,
                                void* workspace, size_t workspace_bytes, void* stream) {
@@ -1940,7 +2078,7 @@ int zen_cuda_dev_gemm_q8_0_act(const zen_cuda_weights* const* w, float* const* d
     if (act_mode != ZEN_CUDA_ACT_INT8 && act_mode != ZEN_CUDA_ACT_FP32) return set_error(s, "dev_gemm: bad activation mode") ? 1 : 0;
     if (workspace_bytes < gemm_ws_bytes(tokens, w[0]->cols, act_mode == ZEN_CUDA_ACT_FP32 ? 2 : 1)) return set_error(s, "dev_gemm: workspace too small") ? 1 : 0;
     return enqueue_gemm_q8_0(s, w, d_out, count, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream,
-                             act_mode) ? 1 : 0;
+                             act_mode, workspace_bytes) ? 1 : 0;
 }
 
 int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out, size_t count, const float* d_x, size_t tokens,
@@ -1951,7 +2089,7 @@ int zen_cuda_dev_gemm_q8_0(const zen_cuda_weights* const* w, float* const* d_out
     if (!w || !d_out || !count || count > ZEN_CUDA_MAX_BATCH || !w[0]) return set_error(s, "dev_gemm: bad arguments") ? 1 : 0;
     if (workspace_bytes < gemm_ws_bytes(tokens, w[0]->cols)) return set_error(s, "dev_gemm: workspace too small") ? 1 : 0;
     return enqueue_gemm_q8_0(s, w, d_out, count, d_x, tokens, static_cast<uint8_t*>(workspace),
-                             stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
+                             stream ? static_cast<cudaStream_t>(stream) : s.stream, ZEN_CUDA_ACT_INT8, workspace_bytes) ? 1 : 0;
 }
 
 size_t zen_cuda_gemm_q6_k_workspace_bytes(size_t tokens, size_t columns) { return gemm_q6k_ws_bytes(tokens, columns); }
