@@ -58,9 +58,10 @@ ALGO_BYTES_PER_LAUNCH = ROWS * (COLS // BLOCK_ELEMS) * BLOCK_BYTES + COLS * 4 + 
 ALGO_BYTES_PER_GROUP = GROUP * (ROWS * (COLS // BLOCK_ELEMS) * BLOCK_BYTES + ROWS * 4) + COLS * 4  # 142,753,792: eight products sharing one read of x
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from ncu captures of `bench.py --profile`
 # and `bench.py --workload q8_0_gemm --profile`: an eight-tensor decode launch reads 142,679,808 B and writes 3,889,920 B
-# (142,753,792 B algorithmic); the prefill kernel moves 81,239,808 + 13,685,504 B (94,109,696 B algorithmic).
+# (142,753,792 B algorithmic); the prefill kernel (group-scale form, two weight digits = 117 MB of planes) reads
+# 141,972,736 B and writes 21,978,112 B of DRAM (the per-block kernel: 81,239,808 + 13,685,504 B for 94,109,696 B algorithmic).
 GEMV_NCU_TRAFFIC_BYTES = 146_569_728
-GEMM_NCU_TRAFFIC_BYTES = 94_925_312
+GEMM_NCU_TRAFFIC_BYTES = 163_950_848
 WORKLOAD = ("Q8_0 decode GEMV batch 1, W 4096x4096 (config 0), %d rotating weight copies, submitted %d products at a time "
             "(zen::quant::gemv_batch: tensors sharing one input)" % (COPIES, GROUP))
 
@@ -353,7 +354,7 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
 
     if args.profile:
         return {"metric": "q8_0_prefill_gemm_int8_tops", "profile_run": True, "value": value, "unit": "TOPS", "launch_us": per_product_us,
-                "launches": "per product: quantize_acts_gemm_kernel, gemm_zero_split_tiles_kernel, gemm_q8_0_i8_kernel; 4 products untimed, 4 + 4 replayed"}
+                "launches": "per product: group_digits_acts_kernel, gg_zero_split_tiles_kernel, gemm_groups_kernel (the first product of a tensor also builds its two-digit planes: group_digits_q8_0_kernel); 4 products untimed, 4 + 4 replayed"}
     # e2e: the host-pointer call, activations host->device and the 29 MB result device->host inside the timed region
     copies = [packed] + [packed.copy() for _ in range(GEMM_COPIES - 1)]
     be.set_q8_act_mode(main_mode)
@@ -394,13 +395,13 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
     return ({
         "metric": "q8_0_prefill_gemm_int8_tops", "value": value, "unit": "TOPS", "n_gpus": 1, "steps": n_products, "warmup": args.warmup,
         "ms_per_step": per_product_us / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "Q8_0 prefill GEMM 512 x 14336 x 4096 (config 1): activation quantise + tcgen05 kind::i8 GEMM per step",
+        "config": {"workload": "Q8_0 prefill GEMM 512 x 14336 x 4096 (config 1): activation digits + tcgen05 kind::i8 GEMM per step",
                    "l2": f"inputs larger than L2: {GEMM_COPIES} weight copies and output buffers, 100 MB per product", "launch": "CUDA graph replay"},
         "roofline": {"bound": "tensor", "achieved": value, "peak": peak, "unit": "TOPS", "frac": value / peak, "peak_kind": peak_kind, "traffic": GEMM_NCU_TRAFFIC_BYTES,
                      "launch_us": per_product_us, "algorithmic_ops_per_launch": GEMM_OPS, "activations": mode_name[main_mode],
                      "other_mode": {"activations": mode_name[other_mode], "launch_us": other_us, "tops_of_the_same_product": GEMM_OPS / (other_us * 1e-6) / 1e12,
-                                    "note": "fp32-equivalent = two int8 digits per activation, two MMAs per block (the reference's default prefill arithmetic)"},
-                     "note": "time includes the activation-quantise kernel; the per-block scale epilogue runs on CUDA cores and bounds the kernel"},
+                                    "note": "fp32-equivalent activations = the reference's default prefill arithmetic; int8 = its ZEN_CPU_Q8_ACT route; the group-scale kernel runs the same three MMAs per 32 columns for both"},
+                     "note": "time includes the activation kernel; weights and activations are two int8 digits under one scale per 256 weights, a group accumulates in TMEM; bound by the L2 -> shared-memory operand traffic (950 MB per product at 9.4 TB/s), tensor pipe 46 % busy"},
         "cpu_baseline": cpu, "clocks": clocks.summary(),
         "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": GEMM_T * GEMM_COLS * 4, "d2h_bytes_per_step": GEMM_T * GEMM_ROWS * 4,
                 "api": "zen_cuda_gemm_q8_0 (host pointers)", "steps": e2e_steps * GEMM_COPIES},
