@@ -700,7 +700,8 @@ def run_gemm_formats(args) -> dict:
                     if args.profile and label != "tensor_cores":
                         continue
                     with torch.cuda.stream(stream):
-                        fn(handles[0], n)
+                        for h in handles:      # outside the capture: a tensor's first many-row product builds its two-digit planes
+                            fn(h, n)
                         stream.synchronize()
                         graph = torch.cuda.CUDAGraph()
                         with torch.cuda.graph(graph, stream=stream):
@@ -842,7 +843,7 @@ def run_lm_head(args, brief: bool = False) -> dict | None:
             algo = tensor_bytes("Q6_K", LM_ROWS, LM_COLS) + tokens * 4 * (LM_COLS + LM_ROWS)
             results[tokens] = {"us_per_step": ms * 1e3 / steps, "gbs": algo / (ms * 1e-3 / steps) / 1e9, "steps": steps,
                                "algorithmic_bytes": algo, "picks_per_s": tokens * steps / (ms * 1e-3),
-                               "kernel": ("gemm_q8_0_i8_kernel<32, 2, Q6_K> (tcgen05)" + (", NCCL all-gather" if world > 1 else "")) if tensor else "gemv_kq_kernel (dp4a)"}
+                               "kernel": ("gemm_groups_kernel (tcgen05)" + (", NCCL all-gather" if world > 1 else "")) if tensor else "gemv_kq_kernel (dp4a)"}
             if pg is not None:
                 stream.synchronize()
                 pg.close()

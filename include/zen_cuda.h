@@ -154,8 +154,8 @@ int zen_cuda_gemv_q8_0_ffn(const uint8_t* gate, const uint8_t* up, const uint8_t
  * failure. */
 int zen_cuda_set_q6k_codes(int on);
 
-/* Which kernel the Q8_0 many-row products take (zen_cuda_gemm_q8_0 and its batch form from nine rows on, the
- * zen_cuda_dev_gemm_q8_0 entry points).  on != 0 (the default; ZEN_CUDA_GEMM_GROUPS=0 changes it): weights and activations
+/* Which kernel the many-row products take (zen_cuda_gemm_q8_0 and its batch form from nine rows on, the
+ * zen_cuda_dev_gemm_q8_0 entry points, and the Q4_0 / Q6_K / Q4_K / Q5_K products below).  on != 0 (the default; ZEN_CUDA_GEMM_GROUPS=0 changes it): weights and activations
  * as two int8 digits under one scale per 256 weights, so that a whole group accumulates on the tensor cores and the sums
  * are read back once per group: results within ~5e-5 of the reference's sums in either activation mode (its bar is 1e-3),
  * three to four times the speed.  The tensor's two-digit planes (2 bytes per weight of device memory) are built at its
@@ -293,7 +293,8 @@ int zen_cuda_dev_gemm_q8_0_act(const zen_cuda_weights* const* w, float* const* d
  * at least zen_cuda_gemm_q6_k_workspace_bytes(tokens, columns), untouched until the stream has run the work.  Up to
  * sixteen rows go through tiles of 32 columns (a token is two columns, one per parity of its 16-weight groups), more
  * through the prefill GEMM's 128.  The host-pointer call zen_cuda_gemm_q6_k takes this path by itself from seven rows
- * on; below that the decode kernel is faster. */
+ * on; below that the decode kernel is faster.  With the group-scale kernel enabled (zen_cuda_set_gemm_groups) the product
+ * runs over the tensor's cached two-digit planes instead. */
 size_t zen_cuda_gemm_q6_k_workspace_bytes(size_t tokens, size_t columns);
 int zen_cuda_dev_gemm_q6_k(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace,
                            size_t workspace_bytes, void* stream);
@@ -303,7 +304,9 @@ int zen_cuda_dev_gemm_q6_k(const zen_cuda_weights* w, float* d_out, const float*
  * workspace, which with the tensor's f16 block scales is a Q8_0 tensor, then the Q8_0 GEMM runs with fp32-equivalent
  * activations.  `workspace`: device memory of at least zen_cuda_gemm_q4_0_workspace_bytes(tokens, rows, columns) --
  * rows x columns bytes of codes plus the GEMM's own workspace -- untouched until the stream has run the work; columns
- * must be a multiple of 128.  The host-pointer call zen_cuda_gemm_q4_0 takes this path by itself from 12 rows on. */
+ * must be a multiple of 128.  The host-pointer call zen_cuda_gemm_q4_0 takes this path by itself from nine rows on.  With
+ * whole 256-weight groups and the group-scale kernel enabled (zen_cuda_set_gemm_groups) the product runs over the tensor's
+ * cached two-digit planes instead and nothing is widened per call. */
 size_t zen_cuda_gemm_q4_0_workspace_bytes(size_t tokens, size_t rows, size_t columns);
 int zen_cuda_dev_gemm_q4_0(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace,
                            size_t workspace_bytes, void* stream);
@@ -314,7 +317,8 @@ int zen_cuda_dev_gemm_q4_0(const zen_cuda_weights* w, float* d_out, const float*
  * (d * sc and dmin * m, as the reference forms them), then the GEMM runs with fp32-equivalent activations and subtracts
  * the minimum term in its epilogue.  `workspace`: at least zen_cuda_gemm_kquant_workspace_bytes(tokens, rows, columns) of
  * device memory, untouched until the stream has run the work.  The host-pointer call zen_cuda_gemm_kquant takes this path
- * by itself from 12 rows on. */
+ * by itself from nine rows on.  With the group-scale kernel enabled (zen_cuda_set_gemm_groups) the product runs over the
+ * tensor's cached two-digit planes instead and nothing is widened per call. */
 size_t zen_cuda_gemm_kquant_workspace_bytes(size_t tokens, size_t rows, size_t columns);
 int zen_cuda_dev_gemm_kquant(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace,
                              size_t workspace_bytes, void* stream);

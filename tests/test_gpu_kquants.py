@@ -233,10 +233,18 @@ def test_q6_k_tensor_core_product_vs_oracle(be, zo, rows, cols, tokens):
     y = torch.full((tokens, rows), float("nan"), device="cuda")
     ws_bytes = be.gemm_q6_k_workspace_bytes(tokens, cols)
     ws = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
-    be.dev_gemm_q6_k(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
-    be.dev_check()
-    rel = assert_parity(y.cpu().numpy(), ref, what=f"Q6_K tensor product {tokens}x{rows}x{cols}")
-    assert rel < 1e-4
+    # more than sixteen rows take the group-scale kernel (two digits per 256-weight group, ~5e-5); with it switched off, and
+    # up to sixteen rows, the per-block kernel with one column per token and group parity (~1e-5)
+    for groups in (True, False):
+        before = be.set_gemm_groups(groups)
+        try:
+            y.fill_(float("nan"))
+            be.dev_gemm_q6_k(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
+            be.dev_check()
+        finally:
+            be.set_gemm_groups(before)
+        rel = assert_parity(y.cpu().numpy(), ref, what=f"Q6_K tensor product {tokens}x{rows}x{cols} groups={groups}")
+        assert rel < (3e-4 if groups and tokens > 16 else 1e-4)
     be.dev_free(h)
     host = be.gemm("Q6_K", w, x, tokens, rows, cols)
     assert_parity(host, ref, what="host-pointer call")
@@ -266,7 +274,7 @@ def test_q6_k_tensor_core_product_needs_the_unpacked_codes(be):
 def test_q4_0_tensor_core_product_vs_oracle(be, zo, rows, cols, tokens):
     # many activation rows: nibbles widened to int8 codes n - 8 in the workspace, then the Q8_0 GEMM with two activation
     # digits; the oracle is the reference's fp32-activation route for Q4_0.  Device entry point, then the host-pointer call
-    # (which takes the same path from 12 rows on).
+    # (which takes the same path from nine rows on).
     import torch
     w = seeded_weights(Q4_0, rows, cols, 960 + rows)
     x = seeded_acts(tokens, cols, 970 + cols)
@@ -276,11 +284,21 @@ def test_q4_0_tensor_core_product_vs_oracle(be, zo, rows, cols, tokens):
     y = torch.full((tokens, rows), float("nan"), device="cuda")
     ws_bytes = be.gemm_q4_0_workspace_bytes(tokens, rows, cols)
     ws = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
-    be.dev_gemm_q4_0(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
-    be.dev_check()
-    rel = assert_parity(y.cpu().numpy(), ref, what=f"Q4_0 tensor product {tokens}x{rows}x{cols}")
-    assert rel < 1e-4
+    # whole 256-weight groups: the group-scale kernel over the tensor's cached two-digit planes (~5e-5); otherwise, and with
+    # it switched off, nibbles widened per call and the per-block Q8_0 kernel (~1e-5)
+    outs = {}
+    for groups in (False, True):
+        before = be.set_gemm_groups(groups)
+        try:
+            y.fill_(float("nan"))
+            be.dev_gemm_q4_0(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
+            be.dev_check()
+        finally:
+            be.set_gemm_groups(before)
+        outs[groups] = y.cpu().numpy()
+        rel = assert_parity(outs[groups], ref, what=f"Q4_0 tensor product {tokens}x{rows}x{cols} groups={groups}")
+        assert rel < (3e-4 if groups and cols % 256 == 0 else 1e-4)
     be.dev_free(h)
     host = be.gemm("Q4_0", w, x, tokens, rows, cols)
-    assert np.array_equal(host, y.cpu().numpy())       # the same kernels on the same bytes
+    assert np.array_equal(host, outs[True])       # the same kernels on the same bytes
     be.release_weights(w)

@@ -85,7 +85,7 @@ def test_lm_head_device_pick_matches_oracle_argmax(be, zo, lm_head, tokens):
             stream.synchronize()
             be.dev_check(stream.cuda_stream)
             assert np.array_equal(d_t.cpu().numpy(), host)
-            assert_parity(host, logits, 1e-5, "tensor-core product against the decode kernel")
+            assert assert_parity(host, logits, what="tensor-core product against the decode kernel") < 3e-4   # two digits per 256-weight group: ~5e-5
         assert d_pick.cpu().tolist() == [zo.argmax(logits[t]) for t in range(tokens)]
     finally:
         be.dev_free(h)

@@ -41,7 +41,7 @@ def test_host_pointer_product_vs_oracle(be, zo, fmt, name, tag, rows, cols, toke
     got = be.gemm(name, w, x, tokens, rows, cols)       # more than 8 tokens: several launches
     ref = np.stack([zo.gemv(fmt, w, x[t], rows, cols) for t in range(tokens)])
     rel = assert_parity(got, ref, what=f"{name} {tokens}x{rows}x{cols}")
-    assert rel < 1e-4
+    assert rel < (3e-4 if tokens >= 9 else 1e-4)        # nine rows and more: the group-scale tensor-core kernel (~5e-5)
     be.release_weights(w)
 
 
@@ -77,7 +77,7 @@ def test_device_pointer_calls(be, zo, fmt, name, tag):
 def test_tensor_core_product_vs_oracle(be, zo, fmt, name, tag, rows, cols, tokens):
     # many activation rows: codes widened to int8 in the workspace with the fp32 factors d * sc and dmin * m of every
     # sub-block, then the tcgen05 GEMM with two activation digits whose epilogue subtracts the minimum term.  Device entry
-    # point with a caller workspace, then the host-pointer call (the same path from twelve rows on).  19000 rows are 149
+    # point with a caller workspace, then the host-pointer call (the same path from nine rows on).  19000 rows are 149
     # row tiles: the K range of one tile is shared between two CTAs.
     import torch
     w = blocks.random_k_blocks(fmt, rows, cols, 600 + rows)
@@ -88,11 +88,27 @@ def test_tensor_core_product_vs_oracle(be, zo, fmt, name, tag, rows, cols, token
     y = torch.full((tokens, rows), float("nan"), device="cuda")
     ws_bytes = be.gemm_kquant_workspace_bytes(tokens, rows, cols)
     ws = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
-    be.dev_gemm_kquant(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
-    be.dev_check()
-    rel = assert_parity(y.cpu().numpy(), ref, what=f"{name} tensor product {tokens}x{rows}x{cols}")
-    assert rel < 1e-4
+    # the group-scale kernel over the tensor's cached two-digit planes (~5e-5); with it switched off, codes widened per call
+    # and the per-block kernel with fp32 sub-block scales and the minimum term in its epilogue (~1e-5)
+    outs = {}
+    for groups in (False, True):
+        before = be.set_gemm_groups(groups)
+        try:
+            y.fill_(float("nan"))
+            be.dev_gemm_kquant(h, y.data_ptr(), d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes)
+            be.dev_check()
+        finally:
+            be.set_gemm_groups(before)
+        outs[groups] = y.cpu().numpy()
+        if groups:
+            # 16-bit fixed point per 256-weight group: the error scales with the LARGEST result (these random blocks give results
+            # in the hundreds), so only the gate on max_abs / max_ref applies; the per-element gate is the other kernel's
+            rel = float(np.abs(outs[groups].astype(np.float64) - ref).max() / np.abs(ref).max())
+            assert np.all(np.isfinite(outs[groups])) and rel < 3e-4, rel
+        else:
+            rel = assert_parity(outs[groups], ref, what=f"{name} tensor product {tokens}x{rows}x{cols} groups={groups}")
+            assert rel < 1e-4
     be.dev_free(h)
     host = be.gemm(name, w, x, tokens, rows, cols)
-    assert np.array_equal(host, y.cpu().numpy())       # the same kernels on the same bytes
+    assert np.array_equal(host, outs[True])       # the same kernels on the same bytes
     be.release_weights(w)

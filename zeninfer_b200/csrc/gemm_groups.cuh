@@ -18,11 +18,14 @@
 //
 // and the last term (at most 2^-16 of the first per product) is dropped: three MMAs per 32 columns of K, two TMEM
 // accumulators A = sum wh xh and B = sum wh xl + sum wl xh over the group's eight K steps, and the epilogue forms
-// (256 * u_w * u_x) * (256 * A + B) once per group.  Results agree with the reference's sums to ~2e-5 relative (bar 1e-3).
+// (256 * u_w * u_x) * (256 * A + B) once per group.  Results agree with the reference's sums to ~5e-5 of the largest result
+// (bar 1e-3).
 //
 // Replaces zen::quant::gemm / gemm_batch at prefill sizes (src/quant.cpp:1613-1680, :1521-1565) for both activation
-// modes.  The two-digit weight planes are built once per resident tensor (group_digits_q8_0_kernel) and kept beside the
-// decode planes: 2 bytes per weight of extra device memory.
+// modes, and the batched products of the other formats (gemm_q6k_kblk_avx2, gemm_q4k_kblk_avx2, gemm_q5k_kblk_avx2,
+// kernels/avx2.cpp:1605-1620, :1762-1770; Q4_0's generic route).  The two-digit weight planes are built once per resident
+// tensor (group_digits_q8_0_kernel, group_digits_kq_kernel) and kept beside the decode planes: 2 bytes per weight of extra
+// device memory.
 //
 // Shape: one persistent CTA per SM, 18 warps.  Warp 0: TMA producer, per 128-wide K tile four tiles (wh, wl, xh, xl; 128
 // rows x 128 B, K-major, 128-byte swizzle) into a 3-stage ring.  Warp 1: MMA issuer, tcgen05.mma kind::i8, M = 128 weight
@@ -343,6 +346,62 @@ __global__ void __launch_bounds__(256) group_digits_q8_0_kernel(const int8_t* __
     for (int k = 0; k < 8; ++k) v[k] = d * static_cast<float>(static_cast<int8_t>((k < 4 ? q.x : q.y) >> (8 * (k & 3))));
     uint2 hi, lo;
     const float u = group_digits8(v, hi, lo);
+    *reinterpret_cast<uint2*>(wh + e0) = hi;
+    *reinterpret_cast<uint2*>(wl + e0) = lo;
+    if (lane == 0) unit[r * groups + g] = u;
+}
+
+// The same from the device planes of the other formats (repack.cuh): the dequantised value of every weight, formed as the
+// reference forms it, then the group's two digits.  A lane owns eight consecutive weights of the group.
+//   Q4_0        w = d * (n - 8)                          nibble plane [rows][K / 2], f16 scales [rows][nbp]
+//   Q6_K codes  w = (d * sc) * q                         codes q - 32 [rows][K] int8, sc [rows][K / 16], d [rows][sbp]
+//   Q4_K, Q5_K  w = (d * sc) * q - (dmin * m)            nibbles [rows][K / 2], (fifth bits [rows][K / 8],) scales|mins [rows][K / 16], (d, dmin) [rows][sbp]
+template <int kFormat>
+__global__ void __launch_bounds__(256) group_digits_kq_kernel(const uint8_t* __restrict__ p0, const uint8_t* __restrict__ p1, const uint8_t* __restrict__ p2,
+                                                              const uint8_t* __restrict__ p3, uint32_t nbp, int8_t* __restrict__ wh, int8_t* __restrict__ wl,
+                                                              float* __restrict__ unit, size_t rows, uint32_t K) {
+    const size_t wid = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t groups = K / kGgGroup;
+    if (wid >= rows * groups) return;
+    const size_t r = wid / groups;
+    const uint32_t g = static_cast<uint32_t>(wid % groups);
+    float v[8];
+    if constexpr (kFormat == 2) {          // Q4_0: block g * 8 + lane / 4, elements (lane % 4) * 8 .. + 7 of it
+        const uint32_t b = g * 8 + (lane >> 2), o = (lane & 3) * 8;
+        const uint2 n = *reinterpret_cast<const uint2*>(p0 + r * (K / 2) + static_cast<size_t>(b) * 16 + (o & 15));
+        const uint32_t sh = o >= 16 ? 4u : 0u;      // low nibbles are elements 0..15, high nibbles 16..31 (src/quant.cpp:391-397)
+        const float d = __half2float(reinterpret_cast<const __half*>(p1)[r * nbp + b]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = d * static_cast<float>(static_cast<int>(((k < 4 ? n.x : n.y) >> (8 * (k & 3) + sh)) & 15u) - 8);
+    } else if constexpr (kFormat == 114) { // Q6_K, codes unpacked: super-block g, group lane / 2
+        const uint2 q = *reinterpret_cast<const uint2*>(p0 + r * K + static_cast<size_t>(g) * 256 + lane * 8);
+        const float sc = static_cast<float>(reinterpret_cast<const int8_t*>(p1)[r * (K / 16) + g * 16 + (lane >> 1)]);
+        const float ds = __half2float(reinterpret_cast<const __half*>(p2)[r * nbp + g]) * sc;     // (d * scale): the reference's order (kernels/avx2.cpp:380-422)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = ds * static_cast<float>(static_cast<int8_t>((k < 4 ? q.x : q.y) >> (8 * (k & 3))));
+    } else {                               // Q4_K (12) / Q5_K (13): sub-block j = lane / 4, elements l = (lane % 4) * 8 .. + 7 of it
+        constexpr bool kQ5 = kFormat == 13;
+        const uint8_t* scm = kQ5 ? p2 : p1;
+        const uint8_t* dd = kQ5 ? p3 : p2;
+        const uint32_t j = lane >> 2, l = (lane & 3) * 8;
+        const uint2 n = *reinterpret_cast<const uint2*>(p0 + r * (K / 2) + static_cast<size_t>(g) * 128 + (j >> 1) * 32 + l);
+        uint2 h = make_uint2(0u, 0u);
+        if (kQ5) h = *reinterpret_cast<const uint2*>(p1 + r * (K / 8) + static_cast<size_t>(g) * 32 + l);
+        const uint32_t sh = (j & 1) * 4;
+        const uint8_t* sm = scm + r * (K / 16) + static_cast<size_t>(g) * 16;
+        const float2 dm = __half22float2(reinterpret_cast<const __half2*>(dd)[r * nbp + g]);
+        const float ds = dm.x * static_cast<float>(sm[j]), ms = dm.y * static_cast<float>(sm[8 + j]);   // the reference's factors (kernels/avx2.cpp:329-378)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t nw = k < 4 ? n.x : n.y, hw = k < 4 ? h.x : h.y;
+            const uint32_t q = ((nw >> (8 * (k & 3) + sh)) & 15u) | (((hw >> (8 * (k & 3) + j)) & 1u) << 4);
+            v[k] = ds * static_cast<float>(q) - ms;
+        }
+    }
+    uint2 hi, lo;
+    const float u = group_digits8(v, hi, lo);
+    const size_t e0 = r * K + static_cast<size_t>(g) * kGgGroup + lane * 8;
     *reinterpret_cast<uint2*>(wh + e0) = hi;
     *reinterpret_cast<uint2*>(wl + e0) = lo;
     if (lane == 0) unit[r * groups + g] = u;

@@ -928,10 +928,12 @@ size_t gemm_groups_ws_bytes(size_t tokens, size_t cols) {
 // short) -- the caller takes the per-block kernel.
 bool ensure_group_digits(State& s, const zen_cuda_weights* w, cudaStream_t st) {
     if (w->g_hi) return true;
-    if (w->format != ZEN_CUDA_Q8_0 || w->cols % zk::kGgGroup) return false;
+    const int kf = w->kernel_format;
+    if (w->cols % zk::kGgGroup || kf == ZEN_CUDA_Q6_K) return false;      // Q6_K with the file's planes: no builder
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return false;
     const size_t n = w->rows * w->cols, groups = w->cols / zk::kGgGroup;
+    if (s.vram_budget && s.stats.weight_bytes + 2 * n > s.vram_budget) return false;   // the planes count as residency; no eviction for them
     void *hi = nullptr, *lo = nullptr;
     float* unit = nullptr;
     if (cudaMalloc(&hi, n) != cudaSuccess || cudaMalloc(&lo, n) != cudaSuccess ||
@@ -943,9 +945,22 @@ bool ensure_group_digits(State& s, const zen_cuda_weights* w, cudaStream_t st) {
         return false;
     }
     const size_t warps = w->rows * groups;
-    zk::group_digits_q8_0_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(static_cast<const int8_t*>(w->plane[0]), static_cast<const __half*>(w->plane[1]),
-                                                                                        w->nbp, static_cast<int8_t*>(hi), static_cast<int8_t*>(lo), unit, w->rows,
-                                                                                        static_cast<uint32_t>(w->cols));
+    const unsigned dgrid = static_cast<unsigned>((warps + 7) / 8);
+    const uint32_t K = static_cast<uint32_t>(w->cols);
+    const auto pl = [&](int i) { return static_cast<const uint8_t*>(w->plane[i]); };
+    int8_t* h8 = static_cast<int8_t*>(hi);
+    int8_t* l8 = static_cast<int8_t*>(lo);
+    if (kf == ZEN_CUDA_Q8_0)
+        zk::group_digits_q8_0_kernel<<<dgrid, 256, 0, st>>>(static_cast<const int8_t*>(w->plane[0]), static_cast<const __half*>(w->plane[1]), w->nbp, h8, l8, unit,
+                                                            w->rows, K);
+    else if (kf == ZEN_CUDA_Q4_0)
+        zk::group_digits_kq_kernel<2><<<dgrid, 256, 0, st>>>(pl(0), pl(1), nullptr, nullptr, w->nbp, h8, l8, unit, w->rows, K);
+    else if (kf == zk::kFormatQ6KCodes)
+        zk::group_digits_kq_kernel<114><<<dgrid, 256, 0, st>>>(pl(0), pl(1), pl(2), nullptr, w->nbp, h8, l8, unit, w->rows, K);
+    else if (kf == ZEN_CUDA_Q4_K)
+        zk::group_digits_kq_kernel<12><<<dgrid, 256, 0, st>>>(pl(0), pl(1), pl(2), nullptr, w->nbp, h8, l8, unit, w->rows, K);
+    else
+        zk::group_digits_kq_kernel<13><<<dgrid, 256, 0, st>>>(pl(0), pl(1), pl(2), pl(3), w->nbp, h8, l8, unit, w->rows, K);
     const bool ok = cudaGetLastError() == cudaSuccess && cudaStreamSynchronize(st) == cudaSuccess;
     ++s.stats.dispatches;
     if (!ok) { cudaFree(hi); cudaFree(lo); cudaFree(unit); return false; }
@@ -1018,6 +1033,18 @@ bool enqueue_gemm_groups(State& s, const zen_cuda_weights* const* w, float* cons
         ++s.stats.dispatches;
     }
     return true;
+}
+
+// One tensor of any format through the group-scale kernel when it can be: whole 256-weight groups, room in the workspace,
+// the tensor's two-digit planes at hand or buildable now.  `launched` tells the caller whether it still has to take its own path.
+bool try_gemm_groups(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, size_t ws_bytes, cudaStream_t st,
+                     bool& launched) {
+    launched = false;
+    if (!s.gemm_groups || !w || w->cols % zk::kGgGroup || ws_bytes < gemm_groups_ws_bytes(tokens, w->cols) || !ensure_group_digits(s, w, st)) return true;
+    launched = true;
+    const zen_cuda_weights* wp[1] = {w};
+    float* outs[1] = {d_out};
+    return enqueue_gemm_groups(s, wp, outs, 1, d_x, tokens, ws, st, ZEN_CUDA_ACT_FP32);
 }
 
 // What a caller's workspace must hold for either kernel.
@@ -1110,10 +1137,15 @@ constexpr size_t kQ6kNarrowMaxTokens = 16;
 // From this many activation rows on the host-pointer call takes the tensor-core product: the narrow-tile kernel takes the
 // same ~270 us for the 128256 x 4096 lm_head whatever the row count, the decode kernel 43 + 41 us per row.
 constexpr size_t kQ6kTensorMinTokens = 7;
-size_t gemm_q6k_ws_bytes(size_t tokens, size_t cols) { return gemm_ws_bytes(2 * tokens, cols, 2); }
+size_t gemm_q6k_ws_bytes(size_t tokens, size_t cols) { return std::max(gemm_ws_bytes(2 * tokens, cols, 2), gemm_groups_ws_bytes(tokens, cols)); }
 
-bool enqueue_gemm_q6k(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, cudaStream_t st) {
+bool enqueue_gemm_q6k(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, cudaStream_t st, size_t ws_bytes = 0) {
     if (!w || !d_out || !d_x || !ws || !tokens) return set_error(s, "gemm q6_k: bad arguments");
+    {                                       // the group-scale kernel when it can be
+        bool launched = false;
+        if (!try_gemm_groups(s, w, d_out, d_x, tokens, ws, ws_bytes, st, launched)) return false;
+        if (launched) return true;
+    }
     if (w->kernel_format != zk::kFormatQ6KCodes || w->cols % 256) return set_error(s, "gemm q6_k: the tensor is not resident with its codes unpacked");
     const size_t cols = w->cols, columns = 2 * tokens;
     const uint32_t nb = static_cast<uint32_t>(cols / 32);
@@ -1164,14 +1196,19 @@ bool enqueue_gemm_q6k(State& s, const zen_cuda_weights* w, float* d_out, const f
 // f16 block scales that is a Q8_0 tensor), then the Q8_0 GEMM with two activation digits, the fp32-activation arithmetic
 // the reference uses for this format (generic route, src/quant.cpp:1135-1162).  The workspace holds the codes
 // (rows x cols bytes, padded to 256) followed by the GEMM's own workspace.
-constexpr size_t kQ4TensorMinTokens = 12;   // 14336 x 4096: ~96 us up to 128 rows on this path, 75 us per chunk of eight through the decode kernel
+constexpr size_t kQ4TensorMinTokens = 9;    // 14336 x 4096: 37 us up to 128 rows through the group-scale kernel (96 us with nibbles widened per call), 75 us per chunk of eight through the decode kernel
 size_t gemm_q4_0_ws_bytes(size_t tokens, size_t rows, size_t cols) {
-    return ((rows * cols + 255) & ~size_t(255)) + gemm_ws_bytes(tokens, cols, 2);
+    return std::max(((rows * cols + 255) & ~size_t(255)) + gemm_ws_bytes(tokens, cols, 2), gemm_groups_ws_bytes(tokens, cols));
 }
 
-bool enqueue_gemm_q4_0(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, cudaStream_t st) {
+bool enqueue_gemm_q4_0(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, cudaStream_t st, size_t ws_bytes = 0) {
     if (!w || !d_out || !d_x || !ws || !tokens) return set_error(s, "gemm q4_0: bad arguments");
     if (w->format != ZEN_CUDA_Q4_0) return set_error(s, "gemm q4_0: not a Q4_0 tensor");
+    {
+        bool launched = false;
+        if (!try_gemm_groups(s, w, d_out, d_x, tokens, ws, ws_bytes, st, launched)) return false;
+        if (launched) return true;
+    }
     const size_t blocks = w->rows * w->nb;
     zk::unpack_q4_0_codes_kernel<<<static_cast<unsigned>((blocks + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(w->plane[0]),
                                                                                              reinterpret_cast<int8_t*>(ws), blocks);
@@ -1190,17 +1227,23 @@ bool enqueue_gemm_q4_0(State& s, const zen_cuda_weights* w, float* d_out, const 
 // of every 32-weight sub-block (w = scale * q - offset), then the tensor-core GEMM with two activation digits whose
 // epilogue also subtracts offset x (activation sum of the block).  Workspace: codes | scales | offsets | GEMM workspace |
 // block-major activation sums.
-constexpr size_t kK45TensorMinTokens = 12;
+constexpr size_t kK45TensorMinTokens = 9;
 size_t align256(size_t n) { return (n + 255) & ~size_t(255); }
 size_t gemm_k45_ws_bytes(size_t tokens, size_t rows, size_t cols) {
     const size_t t_ld = (tokens + 3) & ~size_t(3);
-    return align256(rows * cols) + 2 * align256(rows * (cols / 32) * sizeof(float)) + align256(gemm_ws_bytes(tokens, cols, 2)) + (cols / 32) * t_ld * sizeof(float);
+    return std::max(align256(rows * cols) + 2 * align256(rows * (cols / 32) * sizeof(float)) + align256(gemm_ws_bytes(tokens, cols, 2)) + (cols / 32) * t_ld * sizeof(float),
+                    gemm_groups_ws_bytes(tokens, cols));
 }
 
-bool enqueue_gemm_k45(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, cudaStream_t st) {
+bool enqueue_gemm_k45(State& s, const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, uint8_t* ws, cudaStream_t st, size_t ws_bytes = 0) {
     if (!w || !d_out || !d_x || !ws || !tokens) return set_error(s, "gemm k-quant: bad arguments");
     const bool q5 = w->format == ZEN_CUDA_Q5_K;
     if (!q5 && w->format != ZEN_CUDA_Q4_K) return set_error(s, "gemm k-quant: not a Q4_K or Q5_K tensor");
+    {
+        bool launched = false;
+        if (!try_gemm_groups(s, w, d_out, d_x, tokens, ws, ws_bytes, st, launched)) return false;
+        if (launched) return true;
+    }
     const size_t rows = w->rows, cols = w->cols;
     const uint32_t nsb = w->nb, nb = static_cast<uint32_t>(cols / 32);
     int8_t* codes = reinterpret_cast<int8_t*>(ws);
@@ -1582,17 +1625,17 @@ bool host_product(State& s, int fmt, const float* x, const uint8_t* const* weigh
             for (size_t i = 0; i < count; ++i) need = std::max(need, gemm_k45_ws_bytes(tokens, rows[i], cols));
             if (!ensure_gemm_ws(s, need)) return false;
             for (size_t i = 0; i < count; ++i)
-                if (!enqueue_gemm_k45(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
+                if (!enqueue_gemm_k45(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream, s.d_gemm_ws_bytes)) return false;
         } else if (tensor_path && fmt == ZEN_CUDA_Q4_0) {
             size_t need = 0;
             for (size_t i = 0; i < count; ++i) need = std::max(need, gemm_q4_0_ws_bytes(tokens, rows[i], cols));
             if (!ensure_gemm_ws(s, need)) return false;
             for (size_t i = 0; i < count; ++i)    // stream-ordered: the tensors share the scratch one after the other
-                if (!enqueue_gemm_q4_0(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
+                if (!enqueue_gemm_q4_0(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream, s.d_gemm_ws_bytes)) return false;
         } else if (tensor_path && fmt == ZEN_CUDA_Q6_K) {
             if (!ensure_gemm_ws(s, gemm_q6k_ws_bytes(tokens, cols))) return false;
             for (size_t i = 0; i < count; ++i)    // stream-ordered: the tensors share the workspace one after the other
-                if (!enqueue_gemm_q6k(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream)) return false;
+                if (!enqueue_gemm_q6k(s, w[i], d_out[i], s.d_x, tokens, s.d_gemm_ws, s.stream, s.d_gemm_ws_bytes)) return false;
         } else if (tensor_path) {
             if (!ensure_gemm_ws(s, gemm_ws_bytes_any(s, tokens, cols, act_mode))) return false;
             if (!enqueue_gemm_q8_0(s, w, d_out, count, s.d_x, tokens, s.d_gemm_ws, s.stream, act_mode, s.d_gemm_ws_bytes)) return false;
@@ -2106,7 +2149,7 @@ int zen_cuda_dev_gemm_kquant(const zen_cuda_weights* w, float* d_out, const floa
     if (!w || !d_out || !d_x || !tokens) return set_error(s, "dev_gemm_kquant: bad arguments") ? 1 : 0;
     if (w->format != ZEN_CUDA_Q4_K && w->format != ZEN_CUDA_Q5_K) return set_error(s, "dev_gemm_kquant: a Q4_K or Q5_K tensor") ? 1 : 0;
     if (workspace_bytes < gemm_k45_ws_bytes(tokens, w->rows, w->cols)) return set_error(s, "dev_gemm_kquant: workspace too small") ? 1 : 0;
-    return enqueue_gemm_k45(s, w, d_out, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
+    return enqueue_gemm_k45(s, w, d_out, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream, workspace_bytes) ? 1 : 0;
 }
 
 int zen_cuda_dev_gemm_q4_0(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace, size_t workspace_bytes,
@@ -2117,7 +2160,7 @@ int zen_cuda_dev_gemm_q4_0(const zen_cuda_weights* w, float* d_out, const float*
     if (!w || !d_out || !d_x || !tokens) return set_error(s, "dev_gemm_q4_0: bad arguments") ? 1 : 0;
     if (w->format != ZEN_CUDA_Q4_0 || w->cols % 128) return set_error(s, "dev_gemm_q4_0: a Q4_0 tensor whose columns are a multiple of 128") ? 1 : 0;
     if (workspace_bytes < gemm_q4_0_ws_bytes(tokens, w->rows, w->cols)) return set_error(s, "dev_gemm_q4_0: workspace too small") ? 1 : 0;
-    return enqueue_gemm_q4_0(s, w, d_out, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
+    return enqueue_gemm_q4_0(s, w, d_out, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream, workspace_bytes) ? 1 : 0;
 }
 
 int zen_cuda_dev_gemm_q6_k(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* workspace, size_t workspace_bytes,
@@ -2128,7 +2171,7 @@ int zen_cuda_dev_gemm_q6_k(const zen_cuda_weights* w, float* d_out, const float*
     if (!w || !d_out || !d_x || !tokens) return set_error(s, "dev_gemm_q6_k: bad arguments") ? 1 : 0;
     if (w->format != ZEN_CUDA_Q6_K) return set_error(s, "dev_gemm_q6_k: not a Q6_K tensor") ? 1 : 0;
     if (workspace_bytes < gemm_q6k_ws_bytes(tokens, w->cols)) return set_error(s, "dev_gemm_q6_k: workspace too small") ? 1 : 0;
-    return enqueue_gemm_q6k(s, w, d_out, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream) ? 1 : 0;
+    return enqueue_gemm_q6k(s, w, d_out, d_x, tokens, static_cast<uint8_t*>(workspace), stream ? static_cast<cudaStream_t>(stream) : s.stream, workspace_bytes) ? 1 : 0;
 }
 
 int zen_cuda_dev_gemm_q8_0_noalloc(const zen_cuda_weights* w, float* d_out, const float* d_x, size_t tokens, void* stream) {
