@@ -80,3 +80,22 @@ def test_block_sizes_match_reference_registry():
     assert (blocks.BLOCK_ELEMENTS[blocks.Q6_K], blocks.BLOCK_BYTES[blocks.Q6_K]) == (256, 210)
     assert blocks.row_bytes(blocks.Q8_0, 4096) == 4352 and blocks.row_bytes(blocks.Q4_0, 4096) == 2304 and blocks.row_bytes(blocks.Q6_K, 4096) == 3360
     assert blocks.row_bytes(blocks.Q8_0, 48) == 0 and blocks.row_bytes(blocks.Q6_K, 4096 + 32) == 0
+
+
+def test_workspace_sizes_are_plain_arithmetic(lib_path):
+    # the size queries need no device: callers size their workspaces before anything is resident
+    lib = backend.load_library(lib_path)
+    ACT_INT8, ACT_FP32 = backend.ACT_INT8, backend.ACT_FP32
+    for tokens, rows, cols in [(9, 128, 256), (40, 300, 4096), (512, 14336, 4096), (129, 4096, 14336), (16, 100, 544)]:
+        g = lib.zen_cuda_gemm_workspace_bytes_act(tokens, cols, ACT_FP32)
+        i8 = lib.zen_cuda_gemm_workspace_bytes_act(tokens, cols, ACT_INT8)
+        assert lib.zen_cuda_gemm_workspace_bytes(tokens, cols) == i8
+        assert g >= i8 >= tokens * cols                                   # at least one int8 plane of the activations
+        if cols % 256 == 0:
+            assert i8 >= 2 * tokens * cols                                # the group-scale kernel: two digit planes in either mode
+        # the per-format products: never less than what the group-scale kernel needs, and room for the widened codes
+        assert lib.zen_cuda_gemm_q4_0_workspace_bytes(tokens, rows, cols) >= rows * cols + 2 * tokens * cols
+        assert lib.zen_cuda_gemm_kquant_workspace_bytes(tokens, rows, cols) >= rows * cols + 2 * rows * (cols // 32) * 4 + 2 * tokens * cols
+        assert lib.zen_cuda_gemm_q6_k_workspace_bytes(tokens, cols) >= 4 * tokens * cols     # a token is two columns of two digits
+        bigger = lib.zen_cuda_gemm_workspace_bytes_act(tokens + 1, cols, ACT_FP32)
+        assert bigger >= g
