@@ -89,3 +89,46 @@ class Q6KFixture:
                         p[half * 64 + 32 + l] = (q[1] & 15) | ((q[3] & 15) << 4)
                         p[128 + half * 32 + l] = (q[0] >> 4) | ((q[1] >> 4) << 2) | ((q[2] >> 4) << 4) | ((q[3] >> 4) << 6)
         return packed, expected
+
+
+# ---- the group-scale product, restated (zeninfer_b200/csrc/gemm_groups.cuh) -------------------------------------------
+
+GROUP = 256
+FULL_SCALE = np.float32(32639.0)        # 256 * 127 + 127
+
+
+def group_digits(v: np.ndarray) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """v [n, K] fp32, K a multiple of 256 -> (hi, lo) int32 [n, K] and unit fp32 [n, K / 256] with
+    v ~= unit * (256 * hi + lo): unit = max|v| of the group / 32639 (fp32 division), the fixed-point value is
+    rint(v * (1 / unit)) clamped to +-32639, hi = floor((V + 128) / 256), lo = V - 256 hi in -128..127.  fp32 throughout, as
+    group_digits8 computes it."""
+    v = np.asarray(v, np.float32)
+    n, K = v.shape
+    g = v.reshape(n, K // GROUP, GROUP)
+    amax = np.abs(g).max(axis=2)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        unit = np.where(amax > 0, amax / FULL_SCALE, np.float32(0)).astype(np.float32)
+        inv = np.where(unit > 0, np.float32(1) / unit, np.float32(0)).astype(np.float32)
+    V = np.clip(np.rint(g * inv[..., None]).astype(np.int32), -32639, 32639)
+    hi = (V + 128) >> 8
+    lo = V - 256 * hi
+    return hi.reshape(n, K), lo.reshape(n, K), unit
+
+
+def group_product(w_values: np.ndarray, x_values: np.ndarray) -> np.ndarray:
+    """The kernel's arithmetic on dequantised weights [rows, K] and activation values [T, K]: per group the integer sums
+    A = sum wh xh and B = sum wh xl + sum wl xh (the wl xl term is dropped), then out += (256 u_w u_x) * (256 A + B) group by
+    group in fp32 (each step one fused multiply-add, emulated in float64).  Returns [T, rows] fp32."""
+    wh, wl, uw = group_digits(w_values)
+    xh, xl, ux = group_digits(x_values)
+    rows, K = wh.shape
+    T = xh.shape[0]
+    out = np.zeros((T, rows), np.float32)
+    for g in range(K // GROUP):
+        s = slice(g * GROUP, (g + 1) * GROUP)
+        A = xh[:, s].astype(np.int64) @ wh[:, s].astype(np.int64).T
+        B = xl[:, s].astype(np.int64) @ wh[:, s].astype(np.int64).T + xh[:, s].astype(np.int64) @ wl[:, s].astype(np.int64).T
+        f = (256.0 * A.astype(np.float32).astype(np.float64) + B.astype(np.float32).astype(np.float64)).astype(np.float32)
+        scale = (ux[:, g][:, None] * (uw[:, g] * np.float32(256.0))[None, :]).astype(np.float32)
+        out = (f.astype(np.float64) * scale.astype(np.float64) + out.astype(np.float64)).astype(np.float32)
+    return out

@@ -209,3 +209,36 @@ def test_config1_full_size_fp32_mode(be_fp32, zo):
     sub = np.ascontiguousarray(w[sel])
     assert_parity(got[:32][:, sel], zo.gemm(Q8_0, sub, x[:32], 32, len(sel), cols, int8_acts=False), what="config 1 sampled rows vs the fp32 oracle")
     be_fp32.release_weights(w)
+
+
+@pytest.mark.parametrize("int8", [False, True])
+@pytest.mark.parametrize("tokens,rows,cols", [(9, 128, 256), (40, 300, 4096), (130, 257, 2048), (16, 64, 14336)])
+def test_group_scale_kernel_equals_its_restatement(zo, tokens, rows, cols, int8):
+    # the kernel against helpers.group_product: the same digits, the same integer sums, the same fp32 steps group by group.
+    # Few enough tiles that no tile's K range is split between two CTAs (a split adds two partial sums in another order).
+    import torch
+    from helpers import group_product
+    from zeninfer_b200 import Backend
+    from zeninfer_b200.backend import ACT_FP32, ACT_INT8
+    be = Backend()
+    w = seeded_weights(Q8_0, rows, cols, 700 + rows)
+    x = seeded_acts(tokens, cols, 710 + tokens)
+    x[0, :256] = 0.0
+    h = be.dev_upload("Q8_0", w, rows, cols)
+    mode = ACT_INT8 if int8 else ACT_FP32
+    ws_bytes = be.gemm_workspace_bytes(tokens, cols, mode)
+    ws = torch.zeros(ws_bytes, dtype=torch.uint8, device="cuda")
+    y = torch.full((tokens, rows), float("nan"), device="cuda")
+    d_x = torch.from_numpy(x).cuda()
+    be.dev_gemm_q8_0([h], [y.data_ptr()], d_x.data_ptr(), tokens, ws.data_ptr(), ws_bytes, act_mode=mode)
+    be.dev_check()
+    got = y.cpu().numpy()
+    be.dev_free(h)
+    xv = x
+    if int8:
+        xq, xsc = zo.quantise_acts(x)
+        xv = (xq.astype(np.float32).reshape(tokens, -1, 32) * xsc.astype(np.float32)[..., None]).reshape(tokens, cols)
+    want = group_product(blocks.dequantize(Q8_0, w, rows, cols), xv)
+    # equal up to the last bit of a step here and there: the restatement rounds a fused multiply-add through float64
+    assert np.abs(got.astype(np.float64) - want).max() <= 2e-6 * np.abs(want).max()
+    assert np.mean(got == want) > 0.9
