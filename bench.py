@@ -401,7 +401,7 @@ def run_gemm_workload(args, brief: bool = False) -> dict:
                      "launch_us": per_product_us, "algorithmic_ops_per_launch": GEMM_OPS, "activations": mode_name[main_mode],
                      "other_mode": {"activations": mode_name[other_mode], "launch_us": other_us, "tops_of_the_same_product": GEMM_OPS / (other_us * 1e-6) / 1e12,
                                     "note": "fp32-equivalent activations = the reference's default prefill arithmetic; int8 = its ZEN_CPU_Q8_ACT route; the group-scale kernel runs the same three MMAs per 32 columns for both"},
-                     "note": "time includes the activation kernel; weights and activations are two int8 digits under one scale per 256 weights, a group accumulates in TMEM; bound by the L2 -> shared-memory operand traffic (950 MB per product at 9.4 TB/s), tensor pipe 46 % busy"},
+                     "note": "time includes the activation kernel; weights and activations are two int8 digits under one scale per 256 weights, a group accumulates in TMEM; tensor pipe 46 % busy, L2 39 % of its peak (950 MB of operand traffic per product): it waits for operands with two 64 KB K tiles in flight per SM"},
         "cpu_baseline": cpu, "clocks": clocks.summary(),
         "e2e": {"value": e2e_value, "unit": "TOPS", "h2d_bytes_per_step": GEMM_T * GEMM_COLS * 4, "d2h_bytes_per_step": GEMM_T * GEMM_ROWS * 4,
                 "api": "zen_cuda_gemm_q8_0 (host pointers)", "steps": e2e_steps * GEMM_COPIES},
