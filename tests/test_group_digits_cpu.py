@@ -42,3 +42,18 @@ def test_group_product_meets_the_bar_in_both_activation_modes(zo, tokens, rows, 
     ref8 = ref_int8_f64(w, xq, xsc, rows, cols)
     assert np.abs(got8 - ref8).max() / np.abs(ref8).max() < 2e-4
     assert np.all(np.abs(got8 - ref8) <= 1e-3 * np.maximum(1.0, np.abs(ref8)))
+
+
+@pytest.mark.parametrize("fmt", [blocks.Q4_0, blocks.Q6_K, blocks.Q4_K, blocks.Q5_K])
+def test_group_product_on_the_other_formats(fmt):
+    # the same arithmetic on the dequantised values of the other formats (w = d (n - 8), (d sc) q, (d sc) q - dmin m): the
+    # error is relative to the largest result, which is how the GPU tests of these formats gate the group-scale kernel
+    rows, cols, tokens = 48, 2048, 6
+    if fmt in (blocks.Q4_K, blocks.Q5_K):
+        w = blocks.random_k_blocks(fmt, rows, cols, 77)
+    else:
+        w = seeded_weights(fmt, rows, cols, 77)
+    x = seeded_acts(tokens, cols, 78)
+    got = group_product(blocks.dequantize(fmt, w, rows, cols), x).astype(np.float64)
+    ref = ref_fp32_f64(fmt, w, x, rows, cols)
+    assert np.abs(got - ref).max() / np.abs(ref).max() < 3e-4
